@@ -1,0 +1,176 @@
+/* C ABI of the B200 (sm_100a) implementation of the semblo sparse-attention hot path.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer unless noted.
+ * All buffers are allocated and owned by the caller; no entry point here allocates
+ * device memory.  `stream` is a cudaStream_t passed as void*.  Each entry point
+ * returns 0 on success or a negative code after host-side validation failed
+ * (-1 invalid argument, -2 CUDA error, -3 workspace too small; text from
+ * semblo_last_error()).  Device-side conditions (a bounded wait that ran out, a
+ * sized buffer that would overflow) are written to the caller's int32 `status`
+ * word and never trap: 0 ok, 101-104 wait timed out (load / mma / softmax /
+ * epilogue role), 201 overflow.
+ *
+ * The reference is pure Python (torch + Triton) and has no C ABI of its own; each
+ * declaration names the reference function whose device work it replaces
+ * (paths relative to the reference checkout).
+ */
+#ifndef SEMBLO_B200_H_
+#define SEMBLO_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { SEMBLO_BF16 = 0, SEMBLO_F32 = 1 };
+
+int semblo_version(void);
+const char* semblo_last_error(void);
+
+/* ---- index build -------------------------------------------------------------- */
+
+/* semblo/vllm_plugin/routing_map.py:35-64 (routing_normalize, whole-vector mode) and
+ * semblo/inference/flat_index.py:144-166 (routing_space).  x [n_rows, dim] with the given
+ * row stride (elements).  out (same dtype, may be NULL) = x / max(|x|, 1e-12) rounded to
+ * the dtype; space_f32 / space_bf16 (may be NULL) = the fp32 re-normalisation of `out`.
+ * query_mode = 1 gives semblo/vllm_plugin/trivial_router.py:48-75 instead: the second
+ * normalisation is rounded to the dtype as well (space_* receive the rounded value).
+ * query_mode = 2 takes x as already routed keys and applies the second step only. */
+int semblo_routing_normalize(const void* x, int dtype, int64_t n_rows, int dim, int64_t row_stride,
+                             void* out, float* space_f32, void* space_bf16, int query_mode,
+                             void* stream);
+
+/* Row gather for the k-means sample (semblo/inference/flat_index.py:254, 260-262). */
+int semblo_gather_rows(const float* src, const int64_t* idx, int64_t m, int dim, float* dst_f32,
+                       void* dst_bf16, void* stream);
+
+/* semblo/inference/flat_index.py:356-382 (_argmax_sim_chunked / assign_flat_buckets):
+ * arg-max over centroids of the bf16-rounded fp32-accumulated similarity, lowest id on
+ * ties.  x_bf16 [n, dim], cent_bf16 [num_centroids, dim], assign_out [n] = id + id_offset. */
+int semblo_assign_argmax(const void* x_bf16, int64_t n, const void* cent_bf16, int num_centroids,
+                         int dim, int32_t* assign_out, int id_offset, int32_t* status, void* stream);
+
+/* torch.bincount + the padded / unpadded prefix sums of semblo/vllm_plugin/state.py:44-84
+ * and the empty-cluster test of semblo/inference/flat_index.py:270-285.
+ * assign [heads, head_stride]; counts [heads, C]; ip_orig / ip_pad [heads, C+1] (ip_pad,
+ * empty_rank [heads, C], n_empty [heads] may be NULL). */
+int semblo_cluster_counts(const int32_t* assign, int64_t n, int64_t head_stride, int heads,
+                          int num_clusters, int align, int32_t* counts, int32_t* ip_orig,
+                          int32_t* ip_pad, int32_t* empty_rank, int32_t* n_empty, void* stream);
+
+/* semblo/inference/flat_index.py:271-288: deterministic per-cluster sums (members added in
+ * index order), empty clusters restarted on sample[repl[rank]] (repl may be NULL when no
+ * cluster is empty), mean, re-normalisation.  ip_orig / empty_rank from
+ * semblo_cluster_counts (heads = 1, align = 1). */
+int semblo_kmeans_update(const float* sample, const int32_t* assign, int64_t n, int num_clusters,
+                         int dim, const int32_t* ip_orig, const int32_t* empty_rank,
+                         const int64_t* repl, float* cent_f32, void* cent_bf16, void* workspace,
+                         int64_t workspace_bytes, void* stream);
+
+/* semblo/vllm_plugin/state.py:877-886: codebooks [2, C, dim/2] (bf16) = halves of
+ * normalize(cents); cluster c takes row c - row_offset of cents, zero outside [0, num_rows). */
+int semblo_split_descriptor(const float* cents, int num_rows, int row_offset, int num_clusters,
+                            int dim, void* codebook_bf16, void* stream);
+
+int64_t semblo_layout_workspace_bytes(int64_t n, int heads);
+
+/* semblo/vllm_plugin/state.py:850-914 (_build_flat tail) with _page_align_order (44-84):
+ * assign [heads, n] -> sizes [heads, C] (true), indptr [heads, C+1] (page-aligned starts),
+ * posting [heads, posting_stride] (cluster-major, position-ascending; padding and tail rows
+ * repeat the first entry), inverse [heads, n] (position -> packed row).
+ * workspace >= semblo_layout_workspace_bytes(n, heads) + heads * (C + 1) * 4 bytes. */
+int semblo_build_layout(const int32_t* assign, int64_t n, int heads, int num_clusters, int align,
+                        int32_t* posting, int64_t posting_stride, int32_t* indptr, int32_t* sizes,
+                        int32_t* inverse, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* semblo/vllm_plugin/state.py:950-997 (pack_prompt_kv): packed [2, packed_rows, Hkv, D] from
+ * k, v [L, Hkv, D] through posting[:, :width]; rows >= width are zero.  With page_table the
+ * packed row r lands in physical 16-row page page_table[r / 16] (a vLLM-style paged pool). */
+int semblo_pack_kv(const void* k, const void* v, const int32_t* posting, int64_t posting_stride,
+                   int64_t width, int64_t packed_rows, int num_kv_heads, int head_dim, void* packed,
+                   int64_t kv_stride_elems, const int32_t* page_table, void* stream);
+
+/* semblo/vllm_plugin/fused_prefill.py:126-135 (CausalSnapshot.advance):
+ * sizes[h][c] += |{p in [lo, hi) : assign[h][p] == c}|. */
+int semblo_snapshot_advance(const int32_t* assign, int64_t head_stride, int heads, int64_t lo,
+                            int64_t hi, int num_clusters, int32_t* sizes, void* stream);
+
+/* ---- prefill selection ---------------------------------------------------------- */
+
+/* semblo/vllm_plugin/fused_select.py:1061-1357 (flat_mixture_scores_qtiled) fused with the
+ * score transform of fused_select.py:609-613: score [Q, Hkv, C] fp32 =
+ * log(max(sum_t softmax_c(q_t . mu_c / tau), 1e-38)) - beta log(1 + n_c), -3.4e38 where
+ * n_c == 0.  vectors [Q, Hq, D] bf16 routing vectors, codebooks [Hkv, 2, C, D/2] bf16,
+ * select_sizes [Hkv, C] (the sink cluster already held out by the caller). */
+int semblo_score_clusters(const void* vectors_bf16, int num_queries, int num_q_heads, int head_dim,
+                          const void* codebooks_bf16, int num_kv_heads, int num_clusters,
+                          const int32_t* select_sizes, float temperature, float beta, float* score,
+                          int32_t* status, void* stream);
+
+/* semblo/vllm_plugin/fused_select.py:604-647 (_streaming_select_kernel) plus
+ * fused_prefill.py:212-216 (_force_sink_bit): the bisected threshold and the packed
+ * per-query bitmask qmask [Q, Hkv, C/32]; counts / tokens [Q, Hkv] may be NULL. */
+int semblo_select_clusters(const float* score, const int32_t* select_sizes, int num_queries,
+                           int num_kv_heads, int num_clusters, int target_tokens, int iters,
+                           int force_sink, int32_t* qmask, int32_t* counts, int32_t* tokens,
+                           void* stream);
+
+/* ---- prefill attention ---------------------------------------------------------- */
+
+/* semblo/vllm_plugin/kv_outer.py:482-816 (kv_outer_attention incl. the fused local window
+ * and combine_partials) and semblo/vllm_plugin/fused_prefill.py:155-189
+ * (_dense_chunk_attention).  For every query of the chunk: one softmax over
+ *   { rows [indptr[c], indptr[c] + causal_sizes[c]) of the clusters c set in its qmask }
+ *   U { positions [local_start, q_position] of the position-ordered K/V }.
+ * q, out [Q, Hq, D] bf16; q_positions [Q]; q_order [Hkv, Q] optional permutation of the
+ * chunk's queries (tiles are formed in this order); packed_k / packed_v [packed_rows, Hkv, D]
+ * (page_table optional: packed row / 16 -> physical 16-row page); ordered_k / ordered_v
+ * [ordered_rows, Hkv, D] hold positions ordered_pos0 ...; qmask == NULL gives the exact
+ * dense causal attention, ordered_k == NULL the sparse part only.  lse [Q, Hq] (natural log)
+ * and attended (sum over (query, KV head) of attended keys) may be NULL. */
+int semblo_sparse_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
+                          int head_dim, const int32_t* q_positions, const int32_t* q_order,
+                          const void* packed_k, const void* packed_v, int64_t packed_rows,
+                          const int32_t* page_table, const int32_t* qmask,
+                          const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
+                          const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
+                          int ordered_pos0, int local_start, float sm_scale, void* out, float* lse,
+                          unsigned long long* attended, int32_t* status, void* stream);
+
+/* ---- decode ----------------------------------------------------------------------- */
+
+int64_t semblo_decode_workspace_bytes(int num_q_heads, int num_kv_heads, int head_dim,
+                                      int num_clusters, int64_t packed_width, int num_splits);
+
+/* Byte offsets of the workspace members, in order: tickets, logit [Hkv, G, C] f32,
+ * block (max, sum) partials, score [Hkv, C] f32, rstart, rlen, rcum [Hkv, C] i32,
+ * rcount, rtokens [Hkv] i32, rows [Hkv, packed_width] i32, pacc, pml, vectors [Hq, D] bf16.
+ * The workspace must be zeroed once before its first use. */
+int semblo_decode_workspace_offsets(int num_q_heads, int num_kv_heads, int head_dim,
+                                    int num_clusters, int64_t packed_width, int num_splits,
+                                    int64_t* offsets /* host, [13] */);
+
+/* semblo/vllm_plugin/fused_decode.py:393-521 (fused_decode_step): the whole decode step of
+ * one layer over the decode arena (semblo/vllm_plugin/arena.py:66-253): suffix write at
+ * positions[0] through the block table, query router, selection over the full sizes with
+ * the sink rule, attention over the selected rows with posting <= position plus the
+ * suffix positions [prompt_length, position], merged into output [Hq * D] bf16.
+ * k_post / v_new / k_pre [Hkv, D] may be NULL (layers sharing another layer's K/V).
+ * stage_mask: bit 0 score + suffix write, bit 1 select, bit 2 attend + merge (7 = all). */
+int semblo_decode_step(const void* q_post, const void* q_pre, const void* k_post, const void* v_new,
+                       const void* k_pre, const void* positions, int pos_is_int64,
+                       const void* codebooks, const int32_t* sizes, const int32_t* indptr,
+                       const int32_t* posting, const void* packed_kv, int64_t packed_width,
+                       void* suffix_kv, void* suffix_kpre, const int32_t* suffix_table,
+                       int suffix_blocks, int suffix_block, int table_len,
+                       const int32_t* prompt_length, int num_q_heads, int num_kv_heads,
+                       int head_dim, int num_clusters, float temperature, float beta,
+                       int target_tokens, int sink_tokens, int iters, float sm_scale, int num_splits,
+                       void* workspace, int64_t workspace_bytes, void* output, int32_t* status,
+                       int stage_mask, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SEMBLO_B200_H_ */

@@ -1,0 +1,687 @@
+// Block-sparse decode step over the decode arena: suffix write, query routing,
+// centroid scoring, threshold selection with CSR emission, split-KV gather attention
+// over the selected cluster rows plus the exact generated suffix, and the LSE merge.
+//
+// The step is HBM-bound (codebook read + gathered K/V rows), so the kernels are
+// plain coalesced 16-byte loads spread over the whole GPU:
+//   decode_score_kernel   grid [Hkv, blocks]: suffix write (block 0,0), router, logits of a
+//                         slice of the codebook and the slice's (max, sum-exp) per head
+//   decode_select_kernel  grid [Hkv]: log-sum-exp, cluster probabilities, penalised score,
+//                         bisection, CSR (start, len, cum) and the flat list of selected rows
+//   decode_attend_kernel  grid [Hkv, splits]: each half-warp streams whole K/V rows
+//                         (16 lanes x 16 B = one 256-B request per row and tensor); the last
+//                         CTA of a head merges the splits and writes the output
+// No host reads, no allocations, fixed addresses: the step can be captured in a CUDA graph.
+//
+// Reference behaviour restated here:
+//   semblo/vllm_plugin/fused_decode.py:38-78     suffix write through the block table
+//   semblo/vllm_plugin/trivial_router.py:23-45   query routing vector
+//   semblo/vllm_plugin/fused_decode.py:80-199    selection with the sink rule, CSR in cluster order
+//   semblo/vllm_plugin/fused_decode.py:201-358   attention over CSR rows + suffix, merge
+#include <algorithm>
+#include <climits>
+
+#include "../../include/semblo_b200.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+using semblo::ceil_div;
+
+namespace {
+
+constexpr float NEG_BIG = -3.4e38f;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr int MAX_G = 8;
+constexpr int SCORE_BLOCKS_TARGET = 296;     // 2 CTAs per SM
+
+struct DecodeArgs {
+  int num_q_heads, num_kv_heads, head_dim, num_clusters, group;
+  // inputs of the step
+  const __nv_bfloat16 *q_post, *q_pre, *k_post, *v_new, *k_pre;
+  const void* positions;
+  int pos_is_int64;
+  // arena
+  const __nv_bfloat16* codebooks;
+  const int32_t *sizes, *indptr, *posting;
+  const __nv_bfloat16* packed_kv;
+  int64_t packed_width;
+  __nv_bfloat16* suffix_kv;
+  __nv_bfloat16* suffix_kpre;
+  const int32_t* suffix_table;
+  int suffix_blocks, suffix_block, table_len;
+  const int32_t* prompt_length;
+  // parameters
+  float scale_log2_router, beta, sm_scale_log2;
+  int target_tokens, sink_tokens, iters, num_splits, score_blocks;
+  // workspace
+  float* ws_logit;      // [Hkv, G, C]
+  float* ws_ml;         // [Hkv, score_blocks, G, 2]
+  float* ws_score;      // [Hkv, C]
+  int32_t *rstart, *rlen, *rcum;   // [Hkv, C]
+  int32_t *rcount, *rtokens;       // [Hkv]
+  int32_t* rows;        // [Hkv, packed_width]
+  float* pacc;          // [Hq, splits, D]
+  float* pml;           // [Hq, splits, 2]
+  int32_t* tickets;     // [Hkv]
+  __nv_bfloat16* vectors;   // [Hq, D] routing vectors (kept for inspection)
+  __nv_bfloat16* out;
+  int* status;
+};
+
+__device__ __forceinline__ long long load_pos(const DecodeArgs& a) {
+  return a.pos_is_int64 ? *reinterpret_cast<const long long*>(a.positions)
+                        : (long long)*reinterpret_cast<const int*>(a.positions);
+}
+
+__device__ __forceinline__ double warp_sumd(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ score
+__global__ void __launch_bounds__(256)
+decode_score_kernel(const DecodeArgs a) {
+  extern __shared__ float smf[];
+  float* qv = smf;                                   // [G][D] routing vectors as fp32
+  float* red = smf + a.group * a.head_dim;           // [8 warps][G][2]
+  const int h = blockIdx.x, blk = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = a.head_dim, G = a.group, C = a.num_clusters;
+
+  if (h == 0 && blk == 0 && a.k_post != nullptr) {
+    // the token's K/V (and pre-RoPE key) into the suffix store
+    const long long pos = load_pos(a);
+    const long long block = pos / a.suffix_block;
+    if (block >= 0 && block < a.table_len) {
+      const long long phys = a.suffix_table[block];
+      const long long off = pos - block * a.suffix_block;
+      const int64_t plane = (int64_t)a.suffix_blocks * a.suffix_block * a.num_kv_heads * D;
+      const int64_t dst = (phys * a.suffix_block + off) * a.num_kv_heads * D;
+      for (int i = threadIdx.x; i < a.num_kv_heads * D; i += blockDim.x) {
+        a.suffix_kv[dst + i] = a.k_post[i];
+        a.suffix_kv[plane + dst + i] = a.v_new[i];
+        if (a.suffix_kpre && a.k_pre) a.suffix_kpre[dst + i] = a.k_pre[i];
+      }
+    } else if (threadIdx.x == 0) {
+      atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
+    }
+  }
+  // router: normalise in fp32, round to bf16, normalise again, round again
+  for (int t = warp; t < G; t += 8) {
+    const __nv_bfloat16* src = a.q_pre + (int64_t)(h * G + t) * D;
+    float v[8];
+    double ss = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane + 32 * i;
+      v[i] = d < D ? __bfloat162float(src[d]) : 0.f;
+      ss += (double)v[i] * v[i];
+    }
+    const float n1 = fmaxf((float)sqrt(warp_sumd(ss)), 1e-12f);
+    double ss2 = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = __bfloat162float(__float2bfloat16_rn(v[i] / n1));
+      ss2 += (double)v[i] * v[i];
+    }
+    const float n2 = fmaxf((float)sqrt(warp_sumd(ss2)), 1e-12f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) {
+        const __nv_bfloat16 r = __float2bfloat16_rn(v[i] / n2);
+        qv[t * D + d] = __bfloat162float(r);
+        if (blk == 0) a.vectors[(int64_t)(h * G + t) * D + d] = r;
+      }
+    }
+  }
+  __syncthreads();
+
+  // logits of this block's centroid slice.  Lanes [0, hl) read half 0, [hl, 2 hl) half 1.
+  const int half = D / 2;
+  const int lanes_per_half = half / 8;               // 16-byte chunks per half
+  const int lanes_per_row = 2 * lanes_per_half;      // 32 (D = 256) or 16 (D = 128)
+  const int rows_per_warp = 32 / lanes_per_row;
+  const int sub = lane / lanes_per_row, l_in = lane % lanes_per_row;
+  const int f = l_in / lanes_per_half, chunk = l_in % lanes_per_half;
+  const int per_block = (int)ceil_div(C, gridDim.y);
+  const int c_lo = blk * per_block, c_hi = min(C, c_lo + per_block);
+  const int d0 = f * half + chunk * 8;
+  float qreg[MAX_G][8];
+#pragma unroll
+  for (int t = 0; t < MAX_G; ++t)
+    if (t < G)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) qreg[t][e] = qv[t * D + d0 + e];
+  float m_run[MAX_G], l_run[MAX_G];
+#pragma unroll
+  for (int t = 0; t < MAX_G; ++t) { m_run[t] = -INFINITY; l_run[t] = 0.f; }
+  const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * half + chunk * 8;
+  for (int cw = c_lo + warp * rows_per_warp; cw < c_hi; cw += 8 * rows_per_warp) {
+    const int c = cw + sub;
+    const bool live = c < c_hi;                       // the trip count is warp-uniform
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(cb + (int64_t)c * half);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float x[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f2 = __bfloat1622float2(p2[e]);
+      x[2 * e] = f2.x;
+      x[2 * e + 1] = f2.y;
+    }
+#pragma unroll
+    for (int t = 0; t < MAX_G; ++t) {
+      if (t < G) {
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot = fmaf(qreg[t][e], x[e], dot);
+        for (int o = lanes_per_row >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (live) {
+          const float s2 = dot * a.scale_log2_router;
+          if (l_in == 0) a.ws_logit[((int64_t)h * G + t) * C + c] = s2;
+          const float mx = fmaxf(m_run[t], s2);
+          l_run[t] = l_run[t] * exp2f(m_run[t] - mx) + exp2f(s2 - mx);
+          m_run[t] = mx;
+        }
+      }
+    }
+  }
+  // combine the (max, sum) of the block: lanes with l_in == 0 of each sub-row hold them
+#pragma unroll
+  for (int t = 0; t < MAX_G; ++t) {
+    if (t < G) {
+      float m = m_run[t], l = l_run[t];
+      if (rows_per_warp == 2) {
+        const float m_o = __shfl_xor_sync(0xffffffffu, m, 16), l_o = __shfl_xor_sync(0xffffffffu, l, 16);
+        const float mx = fmaxf(m, m_o);
+        l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
+        m = mx;
+      }
+      if (lane == 0) { red[(warp * G + t) * 2] = m; red[(warp * G + t) * 2 + 1] = l; }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int t = threadIdx.x;
+    float m = -INFINITY, l = 0.f;
+    for (int w = 0; w < 8; ++w) {
+      const float m_o = red[(w * G + t) * 2], l_o = red[(w * G + t) * 2 + 1];
+      const float mx = fmaxf(m, m_o);
+      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
+      m = mx;
+    }
+    float* dst = a.ws_ml + (((int64_t)h * gridDim.y + blk) * G + t) * 2;
+    dst[0] = m;
+    dst[1] = l;
+  }
+}
+
+// ------------------------------------------------------------------ select
+template <typename T, typename Op>
+__device__ __forceinline__ T block_reduce(T v, Op op, T* scratch /* [33] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    T w = lane < nw ? scratch[lane] : scratch[0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) w = op(w, __shfl_xor_sync(0xffffffffu, w, o));
+    if (lane == 0) scratch[32] = w;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+constexpr int SEL_THREADS = 1024;
+constexpr int SEL_MAX_PER = 16;        // clusters per thread: C <= 16384
+
+__global__ void __launch_bounds__(SEL_THREADS)
+decode_select_kernel(const DecodeArgs a) {
+  __shared__ float fscr[33];
+  __shared__ float lse2[MAX_G];
+  __shared__ int scan_a[SEL_THREADS], scan_b[SEL_THREADS];
+  const int h = blockIdx.x;
+  const int C = a.num_clusters, G = a.group;
+  // per-head log-sum-exp from the block partials
+  if (threadIdx.x < G) {
+    const int t = threadIdx.x;
+    float m = -INFINITY, l = 0.f;
+    for (int b = 0; b < a.score_blocks; ++b) {
+      const float* src = a.ws_ml + (((int64_t)h * a.score_blocks + b) * G + t) * 2;
+      const float m_o = src[0], l_o = src[1];
+      const float mx = fmaxf(m, m_o);
+      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
+      m = mx;
+    }
+    lse2[t] = m + log2f(l);
+  }
+  __syncthreads();
+  const int per = (C + SEL_THREADS - 1) / SEL_THREADS;        // consecutive clusters per thread
+  const int c0 = threadIdx.x * per;
+  float score[SEL_MAX_PER];
+  int real[SEL_MAX_PER];
+  const float budget = (float)max(a.target_tokens - a.sink_tokens, 0);
+  const bool has_sink = a.sink_tokens > 0;
+  auto seen_size = [&](int i) { return (has_sink && c0 + i == 0) ? 0.f : (float)real[i]; };
+  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < SEL_MAX_PER; ++i) {
+    const int c = c0 + i;
+    score[i] = NEG_BIG;
+    real[i] = 0;
+    if (i < per && c < C) {
+      float prob = 0.f;
+      for (int t = 0; t < G; ++t) prob += exp2f(a.ws_logit[((int64_t)h * G + t) * C + c] - lse2[t]);
+      real[i] = a.sizes[(int64_t)h * C + c];
+      const float n = seen_size(i);
+      float sc = log2f(fmaxf(prob, 1e-38f)) * LN2;
+      if (a.beta != 0.f) sc -= a.beta * logf(1.0f + n);
+      score[i] = n > 0.f ? sc : NEG_BIG;
+      a.ws_score[(int64_t)h * C + c] = score[i];
+      mx = fmaxf(mx, score[i]);
+      mn = fminf(mn, n > 0.f ? score[i] : 3.4e38f);
+      tot += n > 0.f ? n : 0.f;
+    }
+  }
+  auto fmax_op = [](float x, float y) { return fmaxf(x, y); };
+  auto fmin_op = [](float x, float y) { return fminf(x, y); };
+  auto fadd_op = [](float x, float y) { return x + y; };
+  float hi = block_reduce(mx, fmax_op, fscr) + 1e-6f;
+  float lo = block_reduce(mn, fmin_op, fscr) - 1e-6f;
+  lo = fminf(lo, hi - 1e-5f);
+  const bool all_fit = block_reduce(tot, fadd_op, fscr) < budget;
+  for (int it = 0; it < a.iters; ++it) {
+    const float mid = (lo + hi) * 0.5f;
+    float above = 0.f;
+#pragma unroll
+    for (int i = 0; i < SEL_MAX_PER; ++i) above += score[i] >= mid ? seen_size(i) : 0.f;
+    above = block_reduce(above, fadd_op, fscr);
+    const bool reach = above >= budget;
+    lo = reach ? mid : lo;
+    hi = reach ? hi : mid;
+  }
+  const float theta = all_fit ? NEG_BIG : lo;
+  // selection flags, CSR positions (block scan over threads; clusters of a thread are consecutive)
+  int n_sel = 0, n_tok = 0;
+  unsigned sel_bits = 0;
+#pragma unroll
+  for (int i = 0; i < SEL_MAX_PER; ++i) {
+    const int c = c0 + i;
+    const bool is_sink = has_sink && c == 0;
+    const bool s = (i < per && c < C) &&
+                   ((seen_size(i) > 0.f && score[i] >= theta) || (is_sink && real[i] > 0));
+    sel_bits |= s ? (1u << i) : 0u;
+    n_sel += s;
+    n_tok += s ? real[i] : 0;
+  }
+  scan_a[threadIdx.x] = n_sel;
+  scan_b[threadIdx.x] = n_tok;
+  __syncthreads();
+  // Hillis-Steele inclusive scan
+  for (int off = 1; off < SEL_THREADS; off <<= 1) {
+    int va = 0, vb = 0;
+    if ((int)threadIdx.x >= off) { va = scan_a[threadIdx.x - off]; vb = scan_b[threadIdx.x - off]; }
+    __syncthreads();
+    scan_a[threadIdx.x] += va;
+    scan_b[threadIdx.x] += vb;
+    __syncthreads();
+  }
+  int pos = scan_a[threadIdx.x] - n_sel, cum = scan_b[threadIdx.x] - n_tok;
+  const int total_sel = scan_a[SEL_THREADS - 1], total_tok = scan_b[SEL_THREADS - 1];
+  int32_t* rs = a.rstart + (int64_t)h * C;
+  int32_t* rl = a.rlen + (int64_t)h * C;
+  int32_t* rc = a.rcum + (int64_t)h * C;
+#pragma unroll
+  for (int i = 0; i < SEL_MAX_PER; ++i) {
+    if ((sel_bits >> i) & 1) {
+      rs[pos] = a.indptr[(int64_t)h * (C + 1) + c0 + i];
+      rl[pos] = real[i];
+      rc[pos] = cum;
+      ++pos;
+      cum += real[i];
+    }
+  }
+  if (threadIdx.x == 0) {
+    a.rcount[h] = total_sel;
+    a.rtokens[h] = total_tok;
+    if (total_tok > a.packed_width) atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
+  }
+  __threadfence_block();
+  __syncthreads();
+  // flat list of selected packed rows: slot -> cluster by binary search over rcum
+  const int limit = min(total_tok, (int)a.packed_width);
+  int32_t* rows = a.rows + (int64_t)h * a.packed_width;
+  for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
+    int lo_r = 0, hi_r = total_sel;                 // last r with rcum[r] <= o
+    while (hi_r - lo_r > 1) {
+      const int mid = (lo_r + hi_r) >> 1;
+      if (rc[mid] <= o) lo_r = mid; else hi_r = mid;
+    }
+    rows[o] = rs[lo_r] + (o - rc[lo_r]);
+  }
+
+}
+
+// ------------------------------------------------------------------ attend + merge
+template <int D, int G>
+__global__ void __launch_bounds__(256)
+decode_attend_kernel(const DecodeArgs a) {
+  constexpr int DPL = D / 16;                  // dims per lane (a half-warp covers a row)
+  constexpr int CH = DPL / 8;                  // 16-byte chunks per lane
+  __shared__ float s_acc[8][G][D];             // per-warp partial outputs
+  __shared__ float s_ml[8][G][2];
+  __shared__ int s_last;
+  const int h = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hw = lane >> 4, l16 = lane & 15;
+  const long long q_pos = load_pos(a);
+  const int plen = *a.prompt_length;
+  const int n_prompt = min(a.rtokens[h], (int)a.packed_width);
+  const int n_suffix = (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
+  const int total = n_prompt + n_suffix;
+  const int per_split = (int)ceil_div(total, nsplit);
+  const int lo = split * per_split, hi = min(total, lo + per_split);
+
+  // q fragment: lane owns dims {ch * 128 + l16 * 8 + e}
+  float q[G][DPL];
+#pragma unroll
+  for (int t = 0; t < G; ++t)
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(a.q_post + (int64_t)(h * G + t) * D + ch * 128 + l16 * 8);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f2 = __bfloat1622float2(p2[e]);
+        q[t][ch * 8 + 2 * e] = f2.x * a.sm_scale_log2;
+        q[t][ch * 8 + 2 * e + 1] = f2.y * a.sm_scale_log2;
+      }
+    }
+  float acc[G][DPL], m_run[G], l_run[G];
+#pragma unroll
+  for (int t = 0; t < G; ++t) {
+    m_run[t] = -INFINITY;
+    l_run[t] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[t][d] = 0.f;
+  }
+  const int32_t* rows = a.rows + (int64_t)h * a.packed_width;
+  const int32_t* posting = a.posting + (int64_t)h * a.packed_width;
+  const int64_t pk_plane = a.packed_width * (int64_t)a.num_kv_heads * D;
+  const int64_t sf_plane = (int64_t)a.suffix_blocks * a.suffix_block * a.num_kv_heads * D;
+
+  for (int base = lo + warp * 2; base < hi; base += 16) {
+    const int o = base + hw;
+    const bool live = o < hi;
+    const __nv_bfloat16* kp = a.packed_kv;
+    int64_t voff = pk_plane;
+    bool keep = false;
+    if (live) {
+      if (o < n_prompt) {
+        const int r = rows[o];
+        kp = a.packed_kv + ((int64_t)r * a.num_kv_heads + h) * D;
+        keep = posting[r] <= q_pos;
+      } else {
+        const long long pos = (long long)plen + (o - n_prompt);
+        const long long block = pos / a.suffix_block;
+        const long long phys = block < a.table_len ? a.suffix_table[block] : 0;
+        kp = a.suffix_kv + (((phys * a.suffix_block + (pos - block * a.suffix_block)) * a.num_kv_heads) + h) * D;
+        voff = sf_plane;
+        keep = pos <= q_pos && block < a.table_len;
+      }
+    }
+    uint4 kraw[CH], vraw[CH];
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      kraw[ch] = make_uint4(0, 0, 0, 0);
+      vraw[ch] = make_uint4(0, 0, 0, 0);
+      if (keep) {
+        kraw[ch] = *reinterpret_cast<const uint4*>(kp + ch * 128 + l16 * 8);
+        vraw[ch] = *reinterpret_cast<const uint4*>(kp + voff + ch * 128 + l16 * 8);
+      }
+    }
+    float s2[G];
+#pragma unroll
+    for (int t = 0; t < G; ++t) s2[t] = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < CH; ++ch) {
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[ch]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f2 = __bfloat1622float2(p2[e]);
+#pragma unroll
+        for (int t = 0; t < G; ++t) {
+          s2[t] = fmaf(q[t][ch * 8 + 2 * e], f2.x, s2[t]);
+          s2[t] = fmaf(q[t][ch * 8 + 2 * e + 1], f2.y, s2[t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < G; ++t) {
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) s2[t] += __shfl_xor_sync(0xffffffffu, s2[t], off);
+    }
+    if (keep) {
+      float p[G];
+#pragma unroll
+      for (int t = 0; t < G; ++t) {
+        const float mx = fmaxf(m_run[t], s2[t]);
+        const float alpha = exp2f(m_run[t] - mx);       // 0 on the first row (m_run = -inf)
+        p[t] = exp2f(s2[t] - mx);
+        l_run[t] = l_run[t] * alpha + p[t];
+        m_run[t] = mx;
+        if (alpha != 1.f) {
+#pragma unroll
+          for (int d = 0; d < DPL; ++d) acc[t][d] *= alpha;
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch) {
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[ch]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f2 = __bfloat1622float2(p2[e]);
+#pragma unroll
+          for (int t = 0; t < G; ++t) {
+            acc[t][ch * 8 + 2 * e] = fmaf(p[t], f2.x, acc[t][ch * 8 + 2 * e]);
+            acc[t][ch * 8 + 2 * e + 1] = fmaf(p[t], f2.y, acc[t][ch * 8 + 2 * e + 1]);
+          }
+        }
+      }
+    }
+  }
+  // merge the two half-warps, then the 8 warps, into the split's partial
+#pragma unroll
+  for (int t = 0; t < G; ++t) {
+    const float m_o = __shfl_xor_sync(0xffffffffu, m_run[t], 16);
+    const float l_o = __shfl_xor_sync(0xffffffffu, l_run[t], 16);
+    const float mx = fmaxf(m_run[t], m_o);
+    const float w_s = m_run[t] == -INFINITY ? 0.f : exp2f(m_run[t] - mx);
+    const float w_o = m_o == -INFINITY ? 0.f : exp2f(m_o - mx);
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) {
+      const float other = __shfl_xor_sync(0xffffffffu, acc[t][d], 16);
+      acc[t][d] = acc[t][d] * w_s + other * w_o;
+    }
+    l_run[t] = l_run[t] * w_s + l_o * w_o;
+    m_run[t] = mx;
+    if (hw == 0) {
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s_acc[warp][t][ch * 128 + l16 * 8 + e] = acc[t][ch * 8 + e];
+      if (l16 == 0) { s_ml[warp][t][0] = m_run[t]; s_ml[warp][t][1] = l_run[t]; }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int t = idx / D, d = idx % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mx = fmaxf(mx, s_ml[w][t][0]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float m_w = s_ml[w][t][0];
+      const float sc = m_w == -INFINITY ? 0.f : exp2f(m_w - mx);
+      num += s_acc[w][t][d] * sc;
+      den += s_ml[w][t][1] * sc;
+    }
+    a.pacc[((int64_t)(h * G + t) * nsplit + split) * D + d] = num;
+    if (d == 0) {
+      a.pml[((int64_t)(h * G + t) * nsplit + split) * 2] = mx;
+      a.pml[((int64_t)(h * G + t) * nsplit + split) * 2 + 1] = den;
+    }
+  }
+  // the last CTA of the head merges every split (no waiting: a ticket counter)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&a.tickets[h], 1);
+    s_last = ticket == nsplit - 1;
+    if (s_last) a.tickets[h] = 0;                   // ready for the next step / graph replay
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int t = idx / D, d = idx % D;
+    const float* ml = a.pml + (int64_t)(h * G + t) * nsplit * 2;
+    float mx = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, __ldcg(ml + 2 * s));
+    float num = 0.f, den = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float m_s = __ldcg(ml + 2 * s);
+      const float sc = m_s == -INFINITY ? 0.f : exp2f(m_s - mx);
+      num += __ldcg(a.pacc + ((int64_t)(h * G + t) * nsplit + s) * D + d) * sc;
+      den += __ldcg(ml + 2 * s + 1) * sc;
+    }
+    a.out[(int64_t)(h * G + t) * D + d] = __float2bfloat16_rn(den == 0.f ? 0.f : num / den);
+  }
+}
+
+int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+struct WsLayout {
+  int64_t logit, ml, score, rstart, rlen, rcum, rcount, rtokens, rows, pacc, pml, tickets, vectors, total;
+};
+
+WsLayout ws_layout(int hq, int hkv, int d, int c, int64_t width, int splits, int score_blocks) {
+  const int g = hq / hkv;
+  WsLayout w;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { int64_t o = off; off = align_up(off + bytes, 256); return o; };
+  w.tickets = take((int64_t)hkv * 4);
+  w.logit = take((int64_t)hkv * g * c * 4);
+  w.ml = take((int64_t)hkv * score_blocks * g * 2 * 4);
+  w.score = take((int64_t)hkv * c * 4);
+  w.rstart = take((int64_t)hkv * c * 4);
+  w.rlen = take((int64_t)hkv * c * 4);
+  w.rcum = take((int64_t)hkv * c * 4);
+  w.rcount = take((int64_t)hkv * 4);
+  w.rtokens = take((int64_t)hkv * 4);
+  w.rows = take((int64_t)hkv * width * 4);
+  w.pacc = take((int64_t)hq * splits * d * 4);
+  w.pml = take((int64_t)hq * splits * 2 * 4);
+  w.vectors = take((int64_t)hq * d * 2);
+  w.total = off;
+  return w;
+}
+
+int score_blocks_for(int hkv, int c) {
+  int b = std::max(1, SCORE_BLOCKS_TARGET / std::max(hkv, 1));
+  b = std::min(b, std::max(1, c / 32));
+  return b;
+}
+
+}  // namespace
+
+extern "C" int64_t semblo_decode_workspace_bytes(int num_q_heads, int num_kv_heads, int head_dim,
+                                                 int num_clusters, int64_t packed_width,
+                                                 int num_splits) {
+  return ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width, num_splits,
+                   score_blocks_for(num_kv_heads, num_clusters)).total;
+}
+
+extern "C" int semblo_decode_workspace_offsets(int num_q_heads, int num_kv_heads, int head_dim,
+                                               int num_clusters, int64_t packed_width,
+                                               int num_splits, int64_t* offsets /* [13] */) {
+  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width,
+                               num_splits, score_blocks_for(num_kv_heads, num_clusters));
+  const int64_t v[13] = {w.tickets, w.logit, w.ml, w.score, w.rstart, w.rlen, w.rcum,
+                         w.rcount, w.rtokens, w.rows, w.pacc, w.pml, w.vectors};
+  for (int i = 0; i < 13; ++i) offsets[i] = v[i];
+  return 0;
+}
+
+extern "C" int semblo_decode_step(
+    const void* q_post, const void* q_pre, const void* k_post, const void* v_new, const void* k_pre,
+    const void* positions, int pos_is_int64,
+    const void* codebooks, const int32_t* sizes, const int32_t* indptr, const int32_t* posting,
+    const void* packed_kv, int64_t packed_width,
+    void* suffix_kv, void* suffix_kpre, const int32_t* suffix_table, int suffix_blocks,
+    int suffix_block, int table_len, const int32_t* prompt_length,
+    int num_q_heads, int num_kv_heads, int head_dim, int num_clusters,
+    float temperature, float beta, int target_tokens, int sink_tokens, int iters, float sm_scale,
+    int num_splits, void* workspace, int64_t workspace_bytes, void* output, int32_t* status,
+    int stage_mask, void* stream) {
+  SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
+  const int g = num_q_heads / num_kv_heads;
+  SEMBLO_REQUIRE(g <= MAX_G, "at most %d query heads per KV head", MAX_G);
+  SEMBLO_REQUIRE(head_dim == 128 || head_dim == 256, "head_dim %d must be 128 or 256", head_dim);
+  SEMBLO_REQUIRE(num_clusters >= 32 && num_clusters <= SEL_THREADS * SEL_MAX_PER,
+                 "cluster count %d outside [32, %d]", num_clusters, SEL_THREADS * SEL_MAX_PER);
+  SEMBLO_REQUIRE(temperature > 0.f && num_splits > 0, "temperature and split count must be positive");
+  SEMBLO_REQUIRE((k_post == nullptr) == (v_new == nullptr), "key and value of the new token go together");
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  const int sblocks = score_blocks_for(num_kv_heads, num_clusters);
+  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width, num_splits, sblocks);
+  SEMBLO_REQUIRE(workspace_bytes >= w.total, "decode workspace has %lld bytes, %lld needed",
+                 (long long)workspace_bytes, (long long)w.total);
+  uint8_t* ws = (uint8_t*)workspace;
+  DecodeArgs a;
+  a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim;
+  a.num_clusters = num_clusters; a.group = g;
+  a.q_post = (const __nv_bfloat16*)q_post; a.q_pre = (const __nv_bfloat16*)q_pre;
+  a.k_post = (const __nv_bfloat16*)k_post; a.v_new = (const __nv_bfloat16*)v_new;
+  a.k_pre = (const __nv_bfloat16*)k_pre;
+  a.positions = positions; a.pos_is_int64 = pos_is_int64;
+  a.codebooks = (const __nv_bfloat16*)codebooks; a.sizes = sizes; a.indptr = indptr; a.posting = posting;
+  a.packed_kv = (const __nv_bfloat16*)packed_kv; a.packed_width = packed_width;
+  a.suffix_kv = (__nv_bfloat16*)suffix_kv; a.suffix_kpre = (__nv_bfloat16*)suffix_kpre;
+  a.suffix_table = suffix_table; a.suffix_blocks = suffix_blocks; a.suffix_block = suffix_block;
+  a.table_len = table_len; a.prompt_length = prompt_length;
+  a.scale_log2_router = LOG2E / temperature; a.beta = beta; a.sm_scale_log2 = sm_scale * LOG2E;
+  a.target_tokens = target_tokens; a.sink_tokens = sink_tokens; a.iters = iters;
+  a.num_splits = num_splits; a.score_blocks = sblocks;
+  a.ws_logit = (float*)(ws + w.logit); a.ws_ml = (float*)(ws + w.ml); a.ws_score = (float*)(ws + w.score);
+  a.rstart = (int32_t*)(ws + w.rstart); a.rlen = (int32_t*)(ws + w.rlen); a.rcum = (int32_t*)(ws + w.rcum);
+  a.rcount = (int32_t*)(ws + w.rcount); a.rtokens = (int32_t*)(ws + w.rtokens);
+  a.rows = (int32_t*)(ws + w.rows); a.pacc = (float*)(ws + w.pacc); a.pml = (float*)(ws + w.pml);
+  a.tickets = (int32_t*)(ws + w.tickets); a.vectors = (__nv_bfloat16*)(ws + w.vectors);
+  a.out = (__nv_bfloat16*)output; a.status = status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (stage_mask & 1) {
+    const size_t smem = (size_t)(g * head_dim + 8 * g * 2) * sizeof(float);
+    decode_score_kernel<<<dim3(num_kv_heads, sblocks), 256, smem, st>>>(a);
+  }
+  if (stage_mask & 2) decode_select_kernel<<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+  if (stage_mask & 4) {
+    dim3 grid(num_kv_heads, num_splits);
+#define SEMBLO_DECODE_CASE(DD, GG) \
+  if (head_dim == DD && g == GG) decode_attend_kernel<DD, GG><<<grid, 256, 0, st>>>(a); else
+    SEMBLO_DECODE_CASE(256, 4)
+    SEMBLO_DECODE_CASE(128, 4)
+    SEMBLO_DECODE_CASE(128, 8)
+#undef SEMBLO_DECODE_CASE
+    return semblo::fail(semblo::SEMBLO_EINVAL, "decode attention supports 4 or 8 query heads per KV head (got %d)", g);
+  }
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}

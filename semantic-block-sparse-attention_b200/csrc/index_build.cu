@@ -1,0 +1,704 @@
+// Index build: routing-space normalisation, nearest-centroid assignment (tcgen05 GEMM
+// with a bf16-round + first-arg-max epilogue), deterministic centroid update, the
+// cluster-major page-aligned layout (stable radix sort by cluster id), and the
+// cluster-ordered K/V copy.
+//
+// Reference behaviour restated here:
+//   semblo/vllm_plugin/routing_map.py:35-64      routing_normalize (whole vector)
+//   semblo/inference/flat_index.py:144-166       routing_space
+//   semblo/inference/flat_index.py:356-373       _argmax_sim_chunked
+//   semblo/inference/flat_index.py:268-288       k-means centroid update
+//   semblo/vllm_plugin/state.py:44-84, 850-914   posting order, page alignment, inverse map
+//   semblo/vllm_plugin/state.py:950-997          pack_prompt_kv
+#include <cuda_bf16.h>
+
+#include "../../include/semblo_b200.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+using namespace sm100;
+using semblo::ceil_div;
+
+namespace {
+
+// ------------------------------------------------------------------ normalise
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per row.  stage 1: u = x / max(|x|, 1e-12), rounded to the input dtype
+// (written to `out`).  stage 2: space = u / max(|u|, 1e-12) in fp32 (written to
+// space_f32 / space_bf16).  The sums of squares are accumulated in double so the
+// norm is the correctly rounded one.
+template <typename T, int MAXD>
+__global__ void normalize_rows_kernel(const T* __restrict__ x, int64_t n_rows, int dim,
+                                      int64_t row_stride, T* __restrict__ out,
+                                      float* __restrict__ space_f32,
+                                      __nv_bfloat16* __restrict__ space_bf16, int second_round) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  constexpr int PER = MAXD / 32;
+  float v[PER];
+  double ss = 0.0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    int d = lane + 32 * i;
+    v[i] = d < dim ? (float)x[row * row_stride + d] : 0.f;
+    ss += (double)v[i] * (double)v[i];
+  }
+  ss = warp_sum_d(ss);
+  float nrm = fmaxf((float)sqrt(ss), 1e-12f);
+  double ss2 = 0.0;
+  if (second_round == 2) {
+    // the input is already the routed (stage-1) vector: one normalisation only
+    ss2 = ss;
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      T r = (T)(v[i] / nrm);
+      v[i] = (float)r;
+      int d = lane + 32 * i;
+      if (out && d < dim) out[row * (int64_t)dim + d] = r;
+      ss2 += (double)v[i] * (double)v[i];
+    }
+  }
+  if (!space_f32 && !space_bf16) return;
+  if (second_round != 2) ss2 = warp_sum_d(ss2);
+  float nrm2 = fmaxf((float)sqrt(ss2), 1e-12f);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    int d = lane + 32 * i;
+    if (d >= dim) continue;
+    float s = v[i] / nrm2;
+    if (second_round == 1) {
+      // query router: the second normalisation is rounded to the storage dtype too
+      T r = (T)s;
+      if (space_bf16) space_bf16[row * (int64_t)dim + d] = __float2bfloat16_rn((float)r);
+      if (space_f32) space_f32[row * (int64_t)dim + d] = (float)r;
+    } else {
+      if (space_f32) space_f32[row * (int64_t)dim + d] = s;
+      if (space_bf16) space_bf16[row * (int64_t)dim + d] = __float2bfloat16_rn(s);
+    }
+  }
+}
+
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int64_t* __restrict__ idx,
+                                   int64_t m, int dim, float* __restrict__ dst_f32,
+                                   __nv_bfloat16* __restrict__ dst_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= m) return;
+  const float* s = src + idx[row] * dim;
+  for (int d = lane; d < dim; d += 32) {
+    float v = s[d];
+    if (dst_f32) dst_f32[row * dim + d] = v;
+    if (dst_bf16) dst_bf16[row * dim + d] = __float2bfloat16_rn(v);
+  }
+}
+
+// ------------------------------------------------------------------ assignment GEMM
+// One CTA owns 128 rows of x and streams the codebook in chunks of 128 centroids.
+// warp 4: TMA producer, warp 5: UMMA issuer, warps 0-3: epilogue (thread = row).
+constexpr int ASG_BN = 128;        // centroids per chunk
+constexpr int ASG_STAGES = 2;
+
+template <int D>
+struct AssignSmem {
+  static constexpr int A_BYTES = 128 * D * 2;
+  static constexpr int B_BYTES = ASG_BN * D * 2;
+  static constexpr int BAR_OFF = A_BYTES + ASG_STAGES * B_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                     const __grid_constant__ CUtensorMap tmap_c, int64_t n, int num_centroids,
+                     int32_t* __restrict__ assign_out, int id_offset, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using L = AssignSmem<D>;
+  constexpr int SLABS = D / 64;
+  uint8_t* a_smem = smem;
+  uint8_t* b_smem = smem + L::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  // bars: 0 a_full, 1..2 b_full, 3..4 b_empty, 5..6 acc_full, 7..8 acc_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int num_chunks = (num_centroids + ASG_BN - 1) / ASG_BN;
+  const int64_t row0 = (int64_t)blockIdx.x * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    for (int s = 0; s < ASG_STAGES; ++s) {
+      mbar_init(smem_u32(&bars[1 + s]), 1);
+      mbar_init(smem_u32(&bars[3 + s]), 1);
+      mbar_init(smem_u32(&bars[5 + s]), 1);
+      mbar_init(smem_u32(&bars[7 + s]), 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_x);
+      tma_prefetch_desc(&tmap_c);
+      mbar_arrive_expect_tx(smem_u32(&bars[0]), L::A_BYTES);
+      for (int sl = 0; sl < SLABS; ++sl)
+        tma_load_2d(smem_u32(a_smem + sl * 128 * 128), &tmap_x, smem_u32(&bars[0]), sl * 64, (int)row0);
+      for (int j = 0; j < num_chunks; ++j) {
+        const int s = j % ASG_STAGES;
+        if (!mbar_wait(smem_u32(&bars[3 + s]), ((j / ASG_STAGES) & 1) ^ 1, abort_flag, status,
+                       STATUS_TIMEOUT_LOAD))
+          break;
+        mbar_arrive_expect_tx(smem_u32(&bars[1 + s]), L::B_BYTES);
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma_load_2d(smem_u32(b_smem + s * L::B_BYTES + sl * ASG_BN * 128), &tmap_c,
+                      smem_u32(&bars[1 + s]), sl * 64, j * ASG_BN);
+      }
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, ASG_BN, false, false);
+      bool ok = mbar_wait(smem_u32(&bars[0]), 0, abort_flag, status, STATUS_TIMEOUT_MMA);
+      for (int j = 0; ok && j < num_chunks; ++j) {
+        const int s = j % ASG_STAGES;
+        const int b = j & 1;
+        if (!mbar_wait(smem_u32(&bars[1 + s]), (j / ASG_STAGES) & 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
+        if (!mbar_wait(smem_u32(&bars[7 + b]), ((j >> 1) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_u32(a_smem);
+        const uint32_t b_base = smem_u32(b_smem + s * L::B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+          uint64_t ad = make_smem_desc(a_base + sl * 128 * 128 + ko, 16, 1024);
+          uint64_t bd = make_smem_desc(b_base + sl * ASG_BN * 128 + ko, 16, 1024);
+          umma_ss(tmem_base + b * ASG_BN, ad, bd, idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars[3 + s]));
+        umma_commit(smem_u32(&bars[5 + b]));
+      }
+    }
+  } else {
+    // epilogue: thread = row (TMEM lane), scan the centroids in ascending order
+    const int row = threadIdx.x;           // 0..127
+    float best = -INFINITY;
+    int best_id = 0;
+    bool ok = true;
+    for (int j = 0; j < num_chunks && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c4 = 0; c4 < ASG_BN / 32; ++c4) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * ASG_BN + c4 * 32, r);
+        tmem_ld_wait();
+        const int cbase = j * ASG_BN + c4 * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          // the reference's bf16 matmul output: fp32 accumulate, round to nearest even
+          float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+          bool take = (cbase + i < num_centroids) && (v > best);
+          best = take ? v : best;
+          best_id = take ? cbase + i : best_id;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars[7 + b]));
+    }
+    if (ok && row0 + row < n) assign_out[row0 + row] = best_id + id_offset;
+  }
+  __syncthreads();
+  if (*abort_flag) __nanosleep(50000);
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+}
+
+// ------------------------------------------------------------------ counts
+__global__ void count_kernel(const int32_t* __restrict__ assign, int64_t n, int64_t head_stride,
+                             int num_clusters, int32_t* __restrict__ counts) {
+  const int h = blockIdx.y;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int c = assign[h * head_stride + i];
+    if ((unsigned)c < (unsigned)num_clusters) atomicAdd(&counts[h * num_clusters + c], 1);
+  }
+}
+
+// One block per head: exclusive scans of the true and the page-padded sizes, the
+// number of empty clusters and (for the k-means restart) the rank of each empty one.
+__global__ void scan_counts_kernel(const int32_t* __restrict__ counts, int num_clusters, int align,
+                                   int32_t* __restrict__ ip_orig,     // [H, C+1]
+                                   int32_t* __restrict__ ip_pad,      // [H, C+1] or null
+                                   int32_t* __restrict__ empty_rank,  // [H, C] or null
+                                   int32_t* __restrict__ n_empty) {   // [H] or null
+  __shared__ int s_a[1024], s_b[1024], s_c[1024];
+  const int h = blockIdx.x;
+  const int* cnt = counts + (int64_t)h * num_clusters;
+  const int per = (num_clusters + blockDim.x - 1) / blockDim.x;
+  const int lo = min(num_clusters, (int)threadIdx.x * per), hi = min(num_clusters, lo + per);
+  int a = 0, b = 0, e = 0;
+  for (int c = lo; c < hi; ++c) {
+    int v = cnt[c];
+    a += v;
+    b += align > 1 ? ((v + align - 1) / align) * align : v;
+    e += v == 0;
+  }
+  s_a[threadIdx.x] = a; s_b[threadIdx.x] = b; s_c[threadIdx.x] = e;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int ra = 0, rb = 0, rc = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) {
+      int ta = s_a[t], tb = s_b[t], tc = s_c[t];
+      s_a[t] = ra; s_b[t] = rb; s_c[t] = rc;
+      ra += ta; rb += tb; rc += tc;
+    }
+    ip_orig[(int64_t)h * (num_clusters + 1) + num_clusters] = ra;
+    if (ip_pad) ip_pad[(int64_t)h * (num_clusters + 1) + num_clusters] = rb;
+    if (n_empty) n_empty[h] = rc;
+  }
+  __syncthreads();
+  a = s_a[threadIdx.x]; b = s_b[threadIdx.x]; e = s_c[threadIdx.x];
+  for (int c = lo; c < hi; ++c) {
+    int v = cnt[c];
+    ip_orig[(int64_t)h * (num_clusters + 1) + c] = a;
+    if (ip_pad) ip_pad[(int64_t)h * (num_clusters + 1) + c] = b;
+    if (empty_rank) empty_rank[(int64_t)h * num_clusters + c] = v == 0 ? e : -1;
+    a += v;
+    b += align > 1 ? ((v + align - 1) / align) * align : v;
+    e += v == 0;
+  }
+}
+
+// ------------------------------------------------------------------ stable radix sort by cluster id
+constexpr int SORT_THREADS = 256;
+constexpr int SORT_ITEMS = 8;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;     // 2048 keys per block
+
+__global__ void sort_hist_kernel(const int32_t* __restrict__ keys, int64_t n, int64_t head_stride,
+                                 int shift, int ntiles, int32_t* __restrict__ tile_hist) {
+  __shared__ int hist[256];
+  const int h = blockIdx.y, tile = blockIdx.x;
+  hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)tile * SORT_TILE;
+  for (int i = threadIdx.x; i < SORT_TILE; i += SORT_THREADS) {
+    int64_t p = base + i;
+    if (p < n) atomicAdd(&hist[(keys[h * head_stride + p] >> shift) & 255], 1);
+  }
+  __syncthreads();
+  tile_hist[((int64_t)h * 256 + threadIdx.x) * ntiles + tile] = hist[threadIdx.x];
+}
+
+// exclusive scan of [256 * ntiles] ints per head, in place (digit-major order)
+__global__ void sort_scan_kernel(int32_t* __restrict__ tile_hist, int total) {
+  __shared__ int part[1024];
+  int32_t* a = tile_hist + (int64_t)blockIdx.x * total;
+  const int per = (total + blockDim.x - 1) / blockDim.x;
+  const int lo = min(total, (int)threadIdx.x * per), hi = min(total, lo + per);
+  int s = 0;
+  for (int i = lo; i < hi; ++i) s += a[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int r = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) { int v = part[t]; part[t] = r; r += v; }
+  }
+  __syncthreads();
+  s = part[threadIdx.x];
+  for (int i = lo; i < hi; ++i) { int v = a[i]; a[i] = s; s += v; }
+}
+
+// Stable scatter of one tile.  Warp w owns keys [256 w, 256 w + 256) of the tile and
+// ranks them in 8 rounds of 32 consecutive keys.
+__global__ void sort_scatter_kernel(const int32_t* __restrict__ keys_in,
+                                    const int32_t* __restrict__ vals_in,   // null: identity
+                                    int64_t n, int64_t head_stride, int shift, int ntiles,
+                                    const int32_t* __restrict__ tile_hist,
+                                    int32_t* __restrict__ keys_out, int32_t* __restrict__ vals_out) {
+  __shared__ int cnt[8][256];
+  const int h = blockIdx.y, tile = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 8 * 256; i += SORT_THREADS) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)tile * SORT_TILE + warp * 256;
+  int key[SORT_ITEMS], val[SORT_ITEMS], rank[SORT_ITEMS];
+#pragma unroll
+  for (int r = 0; r < SORT_ITEMS; ++r) {
+    const int64_t p = base + r * 32 + lane;
+    const bool live = p < n;
+    key[r] = live ? keys_in[h * head_stride + p] : 0;
+    val[r] = live ? (vals_in ? vals_in[h * head_stride + p] : (int)p) : 0;
+    const int d = live ? ((key[r] >> shift) & 255) : 256 + lane;   // dead lanes match nobody
+    const unsigned m = __match_any_sync(0xffffffffu, d);
+    const int leader = __ffs(m) - 1;
+    int old = 0;
+    if (live && lane == leader) { old = cnt[warp][d]; cnt[warp][d] = old + __popc(m); }
+    old = __shfl_sync(0xffffffffu, old, leader);
+    rank[r] = old + __popc(m & ((1u << lane) - 1));
+    __syncwarp();
+  }
+  __syncthreads();
+  {
+    // per-digit exclusive prefix over the 8 warps, plus the tile's global base
+    const int d = threadIdx.x;
+    int run = tile_hist[((int64_t)h * 256 + d) * ntiles + tile];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { int v = cnt[w][d]; cnt[w][d] = run; run += v; }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < SORT_ITEMS; ++r) {
+    const int64_t p = base + r * 32 + lane;
+    if (p < n) {
+      const int d = (key[r] >> shift) & 255;
+      const int64_t dst = h * head_stride + cnt[warp][d] + rank[r];
+      keys_out[dst] = key[r];
+      vals_out[dst] = val[r];
+    }
+  }
+}
+
+// posting[h][row] for every padded row, and the position -> row map.
+__global__ void fill_layout_kernel(const int32_t* __restrict__ order, int64_t n, int64_t head_stride,
+                                   const int32_t* __restrict__ counts,
+                                   const int32_t* __restrict__ ip_orig,
+                                   const int32_t* __restrict__ ip_pad, int num_clusters,
+                                   int32_t* __restrict__ posting, int64_t posting_stride,
+                                   int32_t* __restrict__ inverse) {
+  const int h = blockIdx.y;
+  const int32_t* ipp = ip_pad + (int64_t)h * (num_clusters + 1);
+  const int32_t* ipo = ip_orig + (int64_t)h * (num_clusters + 1);
+  const int32_t* ord = order + h * head_stride;
+  const int total = ipp[num_clusters];
+  const int first = ord[0];
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < posting_stride;
+       r += (int64_t)gridDim.x * blockDim.x) {
+    int value = first;
+    if (r < total) {
+      int lo = 0, hi = num_clusters;          // last c with ipp[c] <= r
+      while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (ipp[mid] <= r) lo = mid; else hi = mid;
+      }
+      const int off = (int)r - ipp[lo];
+      if (off < counts[(int64_t)h * num_clusters + lo]) {
+        value = ord[ipo[lo] + off];
+        inverse[h * n + value] = (int)r;
+      }
+    }
+    posting[h * posting_stride + r] = value;
+  }
+}
+
+// ------------------------------------------------------------------ centroid update
+// One block per cluster, thread = dimension; members are summed in index order
+// (`order` is the stable sort of the sample by cluster), so the result does not
+// depend on scheduling.  Empty clusters restart on sample[repl[rank]] with count 1.
+__global__ void centroid_update_kernel(const float* __restrict__ sample, const int32_t* __restrict__ order,
+                                       const int32_t* __restrict__ ip, const int32_t* __restrict__ empty_rank,
+                                       const int64_t* __restrict__ repl, int dim,
+                                       float* __restrict__ cent_f32, __nv_bfloat16* __restrict__ cent_bf16) {
+  __shared__ double red[32];
+  const int c = blockIdx.x;
+  const int lo = ip[c], hi = ip[c + 1];
+  const int d = threadIdx.x;
+  float acc = 0.f;
+  if (hi > lo) {
+    for (int i = lo; i < hi; ++i) {
+      const float* row = sample + (int64_t)order[i] * dim;
+      if (d < dim) acc += row[d];
+    }
+    acc = acc / (float)(hi - lo);
+  } else if (repl != nullptr && d < dim) {
+    acc = sample[repl[empty_rank[c]] * dim + d];
+  }
+  // normalise (F.normalize: x / max(|x|, 1e-12))
+  double sq = (d < dim) ? (double)acc * (double)acc : 0.0;
+  sq = warp_sum_d(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    double v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0;
+    v = warp_sum_d(v);
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  const float nrm = fmaxf((float)sqrt(red[0]), 1e-12f);
+  if (d < dim) {
+    const float v = acc / nrm;
+    cent_f32[(int64_t)c * dim + d] = v;
+    if (cent_bf16) cent_bf16[(int64_t)c * dim + d] = __float2bfloat16_rn(v);
+  }
+}
+
+// codebooks[2][C][D/2] (storage dtype bf16) = the two halves of normalize(cents)
+__global__ void split_descriptor_kernel(const float* __restrict__ cents, int num_rows, int row_offset,
+                                        int num_clusters, int dim, __nv_bfloat16* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= num_clusters) return;
+  const int src = c - row_offset;
+  double ss = 0.0;
+  if (src >= 0 && src < num_rows)
+    for (int d = lane; d < dim; d += 32) { float v = cents[(int64_t)src * dim + d]; ss += (double)v * v; }
+  ss = warp_sum_d(ss);
+  const float nrm = fmaxf((float)sqrt(ss), 1e-12f);
+  const int half = dim / 2;
+  for (int d = lane; d < dim; d += 32) {
+    float v = (src >= 0 && src < num_rows) ? cents[(int64_t)src * dim + d] / nrm : 0.f;
+    const int f = d >= half;
+    out[((int64_t)f * num_clusters + c) * half + (d - f * half)] = __float2bfloat16_rn(v);
+  }
+}
+
+// ------------------------------------------------------------------ pack
+// packed[kv][row][h][:] = src_kv[posting[h][row]][h][:]; rows >= width are zero.
+// One warp moves one (row, head) K and V vector with 16-byte accesses.
+__global__ void pack_kv_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                               const int32_t* __restrict__ posting, int64_t posting_stride, int64_t width,
+                               int64_t packed_rows, int num_kv_heads, int head_dim,
+                               __nv_bfloat16* __restrict__ packed, int64_t kv_stride,
+                               const int32_t* __restrict__ page_table) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= packed_rows * num_kv_heads) return;
+  const int64_t row = item / num_kv_heads;
+  const int h = (int)(item % num_kv_heads);
+  int64_t drow = row;
+  if (page_table) drow = (int64_t)page_table[row >> 4] * 16 + (row & 15);
+  const int chunks = head_dim / 8;      // 16-byte chunks per vector
+  uint4* dk = reinterpret_cast<uint4*>(packed + (drow * num_kv_heads + h) * head_dim);
+  uint4* dv = reinterpret_cast<uint4*>(packed + kv_stride + (drow * num_kv_heads + h) * head_dim);
+  if (row < width) {
+    const int64_t src = posting[h * posting_stride + row];
+    const uint4* sk = reinterpret_cast<const uint4*>(k + (src * num_kv_heads + h) * head_dim);
+    const uint4* sv = reinterpret_cast<const uint4*>(v + (src * num_kv_heads + h) * head_dim);
+    for (int i = lane; i < chunks; i += 32) { dk[i] = sk[i]; dv[i] = sv[i]; }
+  } else {
+    for (int i = lane; i < chunks; i += 32) { dk[i] = make_uint4(0, 0, 0, 0); dv[i] = make_uint4(0, 0, 0, 0); }
+  }
+}
+
+// sizes[h][c] += |{p in [lo, hi): assign[h][p] == c}|
+__global__ void snapshot_advance_kernel(const int32_t* __restrict__ assign, int64_t head_stride,
+                                        int64_t lo, int64_t hi, int num_clusters,
+                                        int32_t* __restrict__ sizes) {
+  const int h = blockIdx.y;
+  for (int64_t p = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < hi;
+       p += (int64_t)gridDim.x * blockDim.x) {
+    int c = assign[h * head_stride + p];
+    if ((unsigned)c < (unsigned)num_clusters) atomicAdd(&sizes[(int64_t)h * num_clusters + c], 1);
+  }
+}
+
+int sort_by_cluster(const int32_t* keys, int64_t n, int64_t head_stride, int heads, int num_clusters,
+                    int32_t* order_out, int32_t* tmp_keys, int32_t* tmp_vals, int32_t* tmp_keys2,
+                    int32_t* tile_hist, cudaStream_t st) {
+  const int ntiles = (int)ceil_div(n, SORT_TILE);
+  const int passes = num_clusters <= 256 ? 1 : 2;
+  const int32_t* kin = keys;
+  const int32_t* vin = nullptr;
+  for (int p = 0; p < passes; ++p) {
+    int32_t* kout = (p == passes - 1) ? tmp_keys2 : tmp_keys;
+    int32_t* vout = (p == passes - 1) ? order_out : tmp_vals;
+    dim3 grid(ntiles, heads);
+    sort_hist_kernel<<<grid, SORT_THREADS, 0, st>>>(kin, n, head_stride, 8 * p, ntiles, tile_hist);
+    sort_scan_kernel<<<heads, 1024, 0, st>>>(tile_hist, 256 * ntiles);
+    sort_scatter_kernel<<<grid, SORT_THREADS, 0, st>>>(kin, vin, n, head_stride, 8 * p, ntiles, tile_hist, kout, vout);
+    kin = kout;
+    vin = vout;
+  }
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int D>
+int launch_assign(const void* x, int64_t n, const void* cent, int num_centroids, int32_t* out,
+                  int id_offset, int* status, cudaStream_t st) {
+  CUtensorMap mx, mc;
+  uint64_t dx[2] = {(uint64_t)D, (uint64_t)n}, sx[1] = {(uint64_t)D * 2};
+  uint64_t dc[2] = {(uint64_t)D, (uint64_t)num_centroids};
+  uint32_t box[2] = {64, 128};
+  int rc = semblo::make_tensor_map_bf16(&mx, x, 2, dx, sx, box);
+  if (rc) return rc;
+  rc = semblo::make_tensor_map_bf16(&mc, cent, 2, dc, sx, box);
+  if (rc) return rc;
+  auto kern = assign_argmax_kernel<D>;
+  SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AssignSmem<D>::TOTAL));
+  kern<<<(unsigned)ceil_div(n, 128), 192, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset, status);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+
+extern "C" int semblo_routing_normalize(const void* x, int dtype, int64_t n_rows, int dim,
+                                        int64_t row_stride, void* out, float* space_f32,
+                                        void* space_bf16, int query_mode, void* stream) {
+  SEMBLO_REQUIRE(dim > 0 && dim <= 256, "dim %d must be in (0, 256]", dim);
+  SEMBLO_REQUIRE(dtype == SEMBLO_BF16 || dtype == SEMBLO_F32, "dtype %d is not bf16 or f32", dtype);
+  if (n_rows == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int wpb = 8;
+  dim3 grid((unsigned)ceil_div(n_rows, wpb));
+  if (dtype == SEMBLO_BF16)
+    normalize_rows_kernel<__nv_bfloat16, 256><<<grid, wpb * 32, 0, st>>>(
+        (const __nv_bfloat16*)x, n_rows, dim, row_stride, (__nv_bfloat16*)out, space_f32,
+        (__nv_bfloat16*)space_bf16, query_mode);
+  else
+    normalize_rows_kernel<float, 256><<<grid, wpb * 32, 0, st>>>(
+        (const float*)x, n_rows, dim, row_stride, (float*)out, space_f32, (__nv_bfloat16*)space_bf16,
+        query_mode);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_gather_rows(const float* src, const int64_t* idx, int64_t m, int dim,
+                                  float* dst_f32, void* dst_bf16, void* stream) {
+  if (m == 0) return 0;
+  gather_rows_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, (cudaStream_t)stream>>>(
+      src, idx, m, dim, dst_f32, (__nv_bfloat16*)dst_bf16);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_assign_argmax(const void* x_bf16, int64_t n, const void* cent_bf16,
+                                    int num_centroids, int dim, int32_t* assign_out, int id_offset,
+                                    int32_t* status, void* stream) {
+  SEMBLO_REQUIRE(num_centroids > 0, "no centroids");
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  if (n == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dim) {
+    case 64: return launch_assign<64>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
+    case 128: return launch_assign<128>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
+    case 256: return launch_assign<256>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
+    default: return semblo::fail(semblo::SEMBLO_EINVAL, "routing dim %d is not 64, 128 or 256", dim);
+  }
+}
+
+extern "C" int64_t semblo_layout_workspace_bytes(int64_t n, int heads) {
+  const int64_t ntiles = ceil_div(n, SORT_TILE);
+  // order, tmp keys, tmp vals, tmp keys2 (n each per head), tile hist, ip_orig is caller's
+  return heads * (4 * n + 256 * ntiles) * (int64_t)sizeof(int32_t) + 1024;
+}
+
+extern "C" int semblo_cluster_counts(const int32_t* assign, int64_t n, int64_t head_stride, int heads,
+                                     int num_clusters, int align, int32_t* counts, int32_t* ip_orig,
+                                     int32_t* ip_pad, int32_t* empty_rank, int32_t* n_empty,
+                                     void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  SEMBLO_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (size_t)heads * num_clusters, st));
+  if (n > 0) {
+    dim3 grid((unsigned)std::min<int64_t>(ceil_div(n, 256), 1184), heads);
+    count_kernel<<<grid, 256, 0, st>>>(assign, n, head_stride, num_clusters, counts);
+  }
+  scan_counts_kernel<<<heads, 1024, 0, st>>>(counts, num_clusters, align, ip_orig, ip_pad, empty_rank, n_empty);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_kmeans_update(const float* sample, const int32_t* assign, int64_t n,
+                                    int num_clusters, int dim, const int32_t* ip_orig,
+                                    const int32_t* empty_rank, const int64_t* repl, float* cent_f32,
+                                    void* cent_bf16, void* workspace, int64_t workspace_bytes,
+                                    void* stream) {
+  SEMBLO_REQUIRE(dim <= 256 && dim % 32 == 0, "dim %d must be a multiple of 32 up to 256", dim);
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, 1), "workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* ws = (int32_t*)workspace;
+  int32_t *order = ws, *tk = ws + n, *tv = ws + 2 * n, *tk2 = ws + 3 * n, *th = ws + 4 * n;
+  int rc = sort_by_cluster(assign, n, n, 1, num_clusters, order, tk, tv, tk2, th, st);
+  if (rc) return rc;
+  centroid_update_kernel<<<num_clusters, dim, 0, st>>>(sample, order, ip_orig, empty_rank, repl, dim,
+                                                      cent_f32, (__nv_bfloat16*)cent_bf16);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_split_descriptor(const float* cents, int num_rows, int row_offset,
+                                       int num_clusters, int dim, void* codebook_bf16, void* stream) {
+  split_descriptor_kernel<<<(unsigned)ceil_div(num_clusters, 8), 256, 0, (cudaStream_t)stream>>>(
+      cents, num_rows, row_offset, num_clusters, dim, (__nv_bfloat16*)codebook_bf16);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_build_layout(const int32_t* assign, int64_t n, int heads, int num_clusters,
+                                   int align, int32_t* posting, int64_t posting_stride,
+                                   int32_t* indptr, int32_t* sizes, int32_t* inverse,
+                                   void* workspace, int64_t workspace_bytes, void* stream) {
+  SEMBLO_REQUIRE(n > 0 && heads > 0 && num_clusters > 0, "empty layout");
+  SEMBLO_REQUIRE(num_clusters <= 65536, "at most 65536 clusters");
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, heads) +
+                                        (int64_t)heads * (num_clusters + 1) * 4,
+                 "workspace too small");
+  SEMBLO_REQUIRE(posting_stride >= n + (int64_t)num_clusters * (align > 1 ? align - 1 : 0),
+                 "posting stride %lld cannot hold the padded layout", (long long)posting_stride);
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* ws = (int32_t*)workspace;
+  const int64_t hn = (int64_t)heads * n;
+  int32_t *order = ws, *tk = ws + hn, *tv = ws + 2 * hn, *tk2 = ws + 3 * hn, *th = ws + 4 * hn;
+  int32_t* ip_orig = th + (int64_t)heads * 256 * ceil_div(n, SORT_TILE);
+  int rc = semblo_cluster_counts(assign, n, n, heads, num_clusters, align, sizes, ip_orig, indptr,
+                                 nullptr, nullptr, stream);
+  if (rc) return rc;
+  rc = sort_by_cluster(assign, n, n, heads, num_clusters, order, tk, tv, tk2, th, st);
+  if (rc) return rc;
+  dim3 grid((unsigned)std::min<int64_t>(ceil_div(posting_stride, 256), 2368), heads);
+  fill_layout_kernel<<<grid, 256, 0, st>>>(order, n, n, sizes, ip_orig, indptr, num_clusters, posting,
+                                           posting_stride, inverse);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_pack_kv(const void* k, const void* v, const int32_t* posting,
+                              int64_t posting_stride, int64_t width, int64_t packed_rows,
+                              int num_kv_heads, int head_dim, void* packed, int64_t kv_stride_elems,
+                              const int32_t* page_table, void* stream) {
+  SEMBLO_REQUIRE(head_dim % 8 == 0, "head_dim %d must be a multiple of 8", head_dim);
+  SEMBLO_REQUIRE(width <= packed_rows, "packed buffer has %lld rows, the posting list %lld",
+                 (long long)packed_rows, (long long)width);
+  const int64_t items = packed_rows * num_kv_heads;
+  if (items == 0) return 0;
+  pack_kv_kernel<<<(unsigned)ceil_div(items, 8), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, posting, posting_stride, width, packed_rows,
+      num_kv_heads, head_dim, (__nv_bfloat16*)packed, kv_stride_elems, page_table);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_snapshot_advance(const int32_t* assign, int64_t head_stride, int heads,
+                                       int64_t lo, int64_t hi, int num_clusters, int32_t* sizes,
+                                       void* stream) {
+  if (hi <= lo) return 0;
+  dim3 grid((unsigned)std::min<int64_t>(ceil_div(hi - lo, 256), 1184), heads);
+  snapshot_advance_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(assign, head_stride, lo, hi,
+                                                                  num_clusters, sizes);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}

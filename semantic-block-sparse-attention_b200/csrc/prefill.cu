@@ -1,0 +1,545 @@
+// Block-sparse paged prefill attention on tcgen05 / TMEM.
+//
+// One CTA owns a tile of QT = 128 / G queries of one KV head (128 rows: query-major,
+// the G heads of a query adjacent) and keeps the output accumulator O [128, D] in
+// TMEM for the whole pass.  K/V reach shared memory as 16-row pages through TMA:
+//
+//   sparse part : the producer warp walks the per-query cluster bitmasks of the
+//                 tile, and for every cluster any query selected it pushes the
+//                 cluster's causally visible pages (rows [indptr[c], indptr[c] + n_c))
+//                 from the cluster-ordered K/V (optionally through a 16-row page
+//                 table), tagged with the 32-bit set of queries that selected it;
+//   local part  : positions [local_start, max q_pos of the tile] from the
+//                 position-ordered K/V, masked exactly causally per row.
+//
+// Four pages make a 64-key tile: S = Q K^T (UMMA, fp32 in TMEM), the softmax warps
+// (one thread per row) apply the page masks, keep a lazily rescaled running max,
+// write P as bf16 into swizzled shared memory, and O += P V is a second UMMA with V
+// as an MN-major operand.  One softmax over the union, as the reference's LSE merge.
+//
+// Reference behaviour restated here:
+//   semblo/vllm_plugin/kv_outer.py:482-816       attended set of the default prefill body
+//   semblo/vllm_plugin/fused_prefill.py:155-189  exact dense attention for short prefixes
+//   semblo/vllm_plugin/fused_prefill.py:250-279  window start / dense-prefix rule (caller)
+#include <algorithm>
+
+#include "../../include/semblo_b200.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+using namespace sm100;
+using semblo::ceil_div;
+
+namespace {
+
+constexpr int PAGE = 16;
+constexpr int PAGES_PER_TILE = 4;
+constexpr int BLOCK_N = PAGE * PAGES_PER_TILE;     // 64 keys per tile
+constexpr float LN2F = 0.6931471805599453f;
+constexpr float RESCALE_GAP = 8.0f;                // log2 units
+
+struct TileInfo {
+  int npages;          // 0 = end of stream
+  int pad[3];
+  int4 page[PAGES_PER_TILE];   // x: query bitmask, y: valid rows, z: position of row 0 (INT_MIN: no causal test)
+};
+
+template <int D>
+struct AttnCfg {
+  static constexpr int STAGES = D >= 256 ? 2 : 4;
+  static constexpr int SLABS = D / 64;
+  static constexpr int Q_BYTES = 128 * D * 2;
+  static constexpr int KV_BYTES = BLOCK_N * D * 2;
+  static constexpr int P_BYTES = 128 * BLOCK_N * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = Q_OFF + Q_BYTES;
+  static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
+  static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
+  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
+  static constexpr int INFO_OFF = BAR_OFF + 256;
+  static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64 + 1024;
+  static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
+  static constexpr int O_COL = 2 * BLOCK_N;
+};
+
+struct PrefillArgs {
+  int num_queries;
+  int num_q_heads;
+  int num_kv_heads;
+  int num_clusters;
+  const int32_t* q_positions;     // [Q]
+  const int32_t* q_order;         // [Hkv, Q] or null
+  const int32_t* qmask;           // [Q, Hkv, C/32] or null
+  const int32_t* causal_sizes;    // [Hkv, C]
+  const int32_t* indptr;          // [Hkv, C+1]
+  const int32_t* page_table;      // packed row / 16 -> physical page, or null
+  int local_start;                // first position of the window (do_local)
+  int local_pos0;                 // position held by row 0 of the position-ordered K/V
+  int local_rows;                 // rows in the position-ordered K/V
+  int do_local;
+  float scale_log2;               // sm_scale * log2(e)
+  __nv_bfloat16* out;             // [Q, Hq, D]
+  float* lse;                     // [Q, Hq] or null
+  unsigned long long* attended;   // sum over (query, KV head) of attended keys, or null
+  int* status;
+};
+
+// barrier slots
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KVFULL = 10, B_KVEMPTY = 14 };
+
+template <int D, int G>
+__global__ void __launch_bounds__(192, 1)
+sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                      const __grid_constant__ CUtensorMap tmap_pk,
+                      const __grid_constant__ CUtensorMap tmap_pv,
+                      const __grid_constant__ CUtensorMap tmap_ok,
+                      const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
+  using C = AttnCfg<D>;
+  constexpr int QT = 128 / G;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
+  TileInfo* info = reinterpret_cast<TileInfo*>(smem + C::INFO_OFF);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::INFO_OFF + STAGES * sizeof(TileInfo));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int q_tile0 = blockIdx.x * QT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(B_QFULL), 1);
+    mbar_init(bar(B_OREADY), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(B_SFULL + b), 1);
+      mbar_init(bar(B_SEMPTY + b), 128);
+      mbar_init(bar(B_PFULL + b), 128);
+      mbar_init(bar(B_PEMPTY + b), 1);
+    }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar(B_KVFULL + s), 1);
+      mbar_init(bar(B_KVEMPTY + s), 5);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    const int slot = q_tile0 + lane;
+    const bool qvalid = lane < QT && slot < a.num_queries;
+    const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
+    const int qpos = qvalid ? a.q_positions[qi] : -1;
+    const unsigned vmask = __ballot_sync(0xffffffffu, qvalid);
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_pk);
+      tma_prefetch_desc(&tmap_pv);
+      tma_prefetch_desc(&tmap_ok);
+      tma_prefetch_desc(&tmap_ov);
+      mbar_arrive_expect_tx(bar(B_QFULL), (uint32_t)__popc(vmask) * G * D * 2);
+    }
+    for (int i = 0; i < QT; ++i) {
+      const int qsrc = __shfl_sync(0xffffffffu, qi, i);
+      if (lane == 0 && ((vmask >> i) & 1)) {
+        for (int sl = 0; sl < C::SLABS; ++sl)
+          tma_load_3d(smem_u32(smem + C::Q_OFF + sl * 128 * 128 + i * G * 128), &tmap_q, bar(B_QFULL),
+                      sl * 64, h * G, qsrc);
+      }
+    }
+
+    int tile = 0, fill = 0;
+    bool ok = true;
+    auto push_page = [&](const CUtensorMap* mk, const CUtensorMap* mv, int row, int nvalid, int mask,
+                         int kpos0) {
+      // warp-uniform arguments
+      const int s = tile % STAGES;
+      if (fill == 0) {
+        if (lane == 0)
+          ok = mbar_wait(bar(B_KVEMPTY + s), ((tile / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) return;
+      }
+      if (lane == 0) {
+        const uint32_t koff = C::K_OFF + s * C::KV_BYTES + fill * PAGE * 128;
+        const uint32_t voff = C::V_OFF + s * C::KV_BYTES + fill * PAGE * 128;
+        for (int sl = 0; sl < C::SLABS; ++sl) {
+          tma_load_2d(smem_u32(smem + koff + sl * BLOCK_N * 128), mk, bar(B_KVFULL + s), h * D + sl * 64, row);
+          tma_load_2d(smem_u32(smem + voff + sl * BLOCK_N * 128), mv, bar(B_KVFULL + s), h * D + sl * 64, row);
+        }
+        info[s].page[fill] = make_int4(mask, nvalid, kpos0, 0);
+      }
+      ++fill;
+      if (fill == PAGES_PER_TILE) {
+        if (lane == 0) {
+          info[s].npages = fill;
+          mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)fill * PAGE * D * 2 * 2);
+        }
+        ++tile;
+        fill = 0;
+      }
+    };
+    auto flush_tile = [&]() {
+      if (fill > 0) {
+        const int s = tile % STAGES;
+        if (lane == 0) {
+          info[s].npages = fill;
+          mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)fill * PAGE * D * 2 * 2);
+        }
+        ++tile;
+        fill = 0;
+      }
+    };
+
+    if (a.qmask != nullptr) {
+      const int nwords = a.num_clusters >> 5;
+      const int32_t* qm = a.qmask + ((int64_t)qi * a.num_kv_heads + h) * nwords;
+      const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
+      const int32_t* ipt = a.indptr + (int64_t)h * (a.num_clusters + 1);
+      for (int w = 0; w < nwords && ok; ++w) {
+        const unsigned word = qvalid ? (unsigned)qm[w] : 0u;
+        unsigned any = __reduce_or_sync(0xffffffffu, word);
+        while (any && ok) {
+          const int bit = __ffs(any) - 1;
+          any &= any - 1;
+          const int c = w * 32 + bit;
+          const int n_c = csz[c];
+          if (n_c <= 0) continue;
+          const unsigned mask = __ballot_sync(0xffffffffu, (word >> bit) & 1u);
+          const int start = ipt[c];
+          for (int pg = 0; pg * PAGE < n_c && ok; ++pg) {
+            int row = start + pg * PAGE;
+            if (a.page_table) row = a.page_table[row >> 4] * PAGE;
+            push_page(&tmap_pk, &tmap_pv, row, min(PAGE, n_c - pg * PAGE), (int)mask, INT_MIN);
+          }
+        }
+      }
+      flush_tile();       // keep the masks of the two parts in separate tiles
+    }
+    if (a.do_local && ok) {
+      int max_qpos = qpos;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) max_qpos = max(max_qpos, __shfl_xor_sync(0xffffffffu, max_qpos, o));
+      const int last = min(max_qpos, a.local_pos0 + a.local_rows - 1);
+      for (int p = a.local_start; p <= last && ok; p += PAGE)
+        push_page(&tmap_ok, &tmap_ov, p - a.local_pos0, min(PAGE, last - p + 1), -1, p);
+      flush_tile();
+    }
+    if (ok) {
+      // end marker
+      const int s = tile % STAGES;
+      if (lane == 0) {
+        ok = mbar_wait(bar(B_KVEMPTY + s), ((tile / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
+        if (ok) {
+          info[s].npages = 0;
+          mbar_arrive(bar(B_KVFULL + s));
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (elect_one()) {
+      const uint32_t q_base = smem_u32(smem + C::Q_OFF);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
+      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+      int np_prev = 0;
+      auto issue_pv = [&](int t, int np) -> bool {
+        const int b = t & 1, s = t % STAGES;
+        if (!mbar_wait(bar(B_PFULL + b), (t >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t p_base = smem_u32(smem + C::P_OFF + b * C::P_BYTES);
+        const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
+        for (int kk = 0; kk < np; ++kk)
+          umma_ss(tmem_base + C::O_COL, make_smem_desc(p_base + kk * 32, 16, 1024),
+                  make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
+                  (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(B_KVEMPTY + s));
+        umma_commit(bar(B_PEMPTY + b));
+        return true;
+      };
+      int j = 0;
+      while (ok) {
+        const int s = j % STAGES, b = j & 1;
+        if (!mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
+        const int np = info[s].npages;
+        if (np == 0) break;
+        if (!mbar_wait(bar(B_SEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
+        const uint32_t idesc_qk = make_idesc_bf16(128, np * PAGE, false, false);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+          umma_ss(tmem_base + b * BLOCK_N, make_smem_desc(q_base + sl * 128 * 128 + ko, 16, 1024),
+                  make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(B_SFULL + b));
+        if (j > 0 && !issue_pv(j - 1, np_prev)) { ok = false; break; }
+        np_prev = np;
+        ++j;
+      }
+      if (ok && j > 0) ok = issue_pv(j - 1, np_prev);
+      if (ok) umma_commit(bar(B_OREADY));
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue (thread = row)
+    const int row = threadIdx.x;
+    const int qslot = row / G, t = row % G;
+    const int slot = q_tile0 + qslot;
+    const bool qvalid = slot < a.num_queries;
+    const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
+    const int qpos = qvalid ? a.q_positions[qi] : -1;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_ref = -INFINITY, l_run = 0.f;
+    unsigned long long att = 0;
+    bool ok = true;
+    int j = 0;
+    for (;; ++j) {
+      const int s = j % STAGES, b = j & 1;
+      ok = mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      const int np = info[s].npages;
+      if (np == 0) break;
+      int4 pg[PAGES_PER_TILE];
+#pragma unroll
+      for (int p = 0; p < PAGES_PER_TILE; ++p) pg[p] = info[s].page[p];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
+      ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem_base + lane_addr + b * BLOCK_N, r0);
+      if (np > 2) tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(bar(B_SEMPTY + b));
+      // masks, scaled logits, tile max
+      float tmax = -INFINITY;
+      int cnt = 0;
+#pragma unroll
+      for (int p = 0; p < PAGES_PER_TILE; ++p) {
+        const bool page_on = p < np && ((pg[p].x >> qslot) & 1);
+        const int nv = pg[p].y;
+        const int kp0 = pg[p].z;
+#pragma unroll
+        for (int i = 0; i < PAGE; ++i) {
+          uint32_t& slot_r = p < 2 ? r0[p * PAGE + i] : r1[(p - 2) * PAGE + i];
+          const bool causal = kp0 == INT_MIN || kp0 + i <= qpos;
+          const bool allowed = page_on && i < nv && causal;
+          const float s2 = allowed ? __uint_as_float(slot_r) * a.scale_log2 : -INFINITY;
+          slot_r = __float_as_uint(s2);
+          tmax = fmaxf(tmax, s2);
+          cnt += allowed;
+        }
+      }
+      if (t == 0) att += cnt;
+      // lazy rescale: only when the running reference falls more than 2^8 behind
+      bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
+      float alpha = 1.f;
+      if (need) {
+        alpha = exp2f(m_ref - tmax);
+        m_ref = tmax;
+        l_run *= alpha;
+      } else if (m_ref == -INFINITY) {
+        m_ref = tmax;
+      }
+      ok = mbar_wait(bar(B_PEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      if (__any_sync(0xffffffffu, need)) {
+        // O must be quiescent: the previous tile's P V has to be complete
+        ok = mbar_wait(bar(B_PEMPTY + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_base + lane_addr + C::O_COL + c * 32, o);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      uint8_t* p_row = smem + C::P_OFF + b * C::P_BYTES;
+      float add = 0.f;
+#pragma unroll
+      for (int p = 0; p < PAGES_PER_TILE; ++p) {
+        if (p < np) {
+          uint32_t packed[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t u0 = p < 2 ? r0[p * PAGE + 2 * i] : r1[(p - 2) * PAGE + 2 * i];
+            const uint32_t u1 = p < 2 ? r0[p * PAGE + 2 * i + 1] : r1[(p - 2) * PAGE + 2 * i + 1];
+            const float e0 = exp2f(__uint_as_float(u0) - m_use);
+            const float e1 = exp2f(__uint_as_float(u1) - m_use);
+            add += e0 + e1;
+            __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+            packed[i] = *reinterpret_cast<uint32_t*>(&pr);
+          }
+          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        }
+      }
+      l_run += add;
+      fence_proxy_async_smem();
+      mbar_arrive(bar(B_PFULL + b));
+    }
+    // epilogue
+    if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = a.out + ((int64_t)qi * a.num_q_heads + h * G + t) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (j > 0) {
+          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (qvalid) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv,
+                                                      __uint_as_float(o[2 * i + 1]) * inv);
+            w[i] = *reinterpret_cast<uint32_t*>(&pr);
+          }
+          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+          d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          d4[2] = make_uint4(w[8], w[9], w[10], w[11]);
+          d4[3] = make_uint4(w[12], w[13], w[14], w[15]);
+        }
+      }
+      if (qvalid && a.lse)
+        a.lse[(int64_t)qi * a.num_q_heads + h * G + t] = l_run > 0.f ? (m_ref + log2f(l_run)) * LN2F : -INFINITY;
+      if (a.attended) {
+        if (!qvalid) att = 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
+        if (lane == 0 && att) atomicAdd(a.attended, att);
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (*abort_flag) __nanosleep(50000);
+  if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+template <int D, int G>
+int launch_prefill(const void* q, const void* packed_k, const void* packed_v, int64_t packed_rows,
+                   const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
+                   const PrefillArgs& a, cudaStream_t st) {
+  using C = AttnCfg<D>;
+  constexpr int QT = 128 / G;
+  CUtensorMap mq, mpk, mpv, mok, mov;
+  {
+    uint64_t d[3] = {(uint64_t)D, (uint64_t)a.num_q_heads, (uint64_t)a.num_queries};
+    uint64_t s[2] = {(uint64_t)D * 2, (uint64_t)a.num_q_heads * D * 2};
+    uint32_t b[3] = {64, (uint32_t)G, 1};
+    int rc = semblo::make_tensor_map_bf16(&mq, q, 3, d, s, b);
+    if (rc) return rc;
+  }
+  const uint64_t row_bytes = (uint64_t)a.num_kv_heads * D * 2;
+  uint32_t box[2] = {64, PAGE};
+  const void* pk = packed_k ? packed_k : ordered_k;
+  const void* pv = packed_v ? packed_v : ordered_v;
+  const int64_t prow = packed_k ? packed_rows : ordered_rows;
+  const void* ok_ = ordered_k ? ordered_k : packed_k;
+  const void* ov_ = ordered_v ? ordered_v : packed_v;
+  const int64_t orow = ordered_k ? ordered_rows : packed_rows;
+  {
+    uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)prow};
+    int rc = semblo::make_tensor_map_bf16(&mpk, pk, 2, d, &row_bytes, box);
+    if (rc) return rc;
+    rc = semblo::make_tensor_map_bf16(&mpv, pv, 2, d, &row_bytes, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)orow};
+    int rc = semblo::make_tensor_map_bf16(&mok, ok_, 2, d, &row_bytes, box);
+    if (rc) return rc;
+    rc = semblo::make_tensor_map_bf16(&mov, ov_, 2, d, &row_bytes, box);
+    if (rc) return rc;
+  }
+  auto kern = sparse_prefill_kernel<D, G>;
+  SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+  dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
+  kern<<<grid, 192, C::TOTAL, st>>>(mq, mpk, mpv, mok, mov, a);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int semblo_sparse_prefill(
+    const void* q, int num_queries, int num_q_heads, int num_kv_heads, int head_dim,
+    const int32_t* q_positions, const int32_t* q_order,
+    const void* packed_k, const void* packed_v, int64_t packed_rows, const int32_t* page_table,
+    const int32_t* qmask, const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
+    const void* ordered_k, const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
+    int local_start, float sm_scale, void* out, float* lse, unsigned long long* attended,
+    int32_t* status, void* stream) {
+  SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  SEMBLO_REQUIRE(qmask != nullptr || ordered_k != nullptr, "nothing to attend: neither a selection nor a window");
+  SEMBLO_REQUIRE(qmask == nullptr || (packed_k && packed_v && causal_sizes && indptr && num_clusters % 32 == 0),
+                 "the sparse part needs packed K/V, sizes, indptr and a cluster count that is a multiple of 32");
+  SEMBLO_REQUIRE((ordered_k == nullptr) == (ordered_v == nullptr), "ordered K and V must be given together");
+  if (num_queries == 0) return 0;
+  PrefillArgs a;
+  a.num_queries = num_queries;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.num_clusters = num_clusters;
+  a.q_positions = q_positions;
+  a.q_order = q_order;
+  a.qmask = qmask;
+  a.causal_sizes = causal_sizes;
+  a.indptr = indptr;
+  a.page_table = page_table;
+  a.local_start = local_start;
+  a.local_pos0 = ordered_pos0;
+  a.local_rows = (int)ordered_rows;
+  a.do_local = ordered_k != nullptr;
+  a.scale_log2 = sm_scale * 1.4426950408889634f;
+  a.out = (__nv_bfloat16*)out;
+  a.lse = lse;
+  a.attended = attended;
+  a.status = status;
+  const int g = num_q_heads / num_kv_heads;
+  cudaStream_t st = (cudaStream_t)stream;
+#define SEMBLO_PREFILL_CASE(DD, GG)                                                              \
+  if (head_dim == DD && g == GG)                                                                 \
+    return launch_prefill<DD, GG>(q, packed_k, packed_v, packed_rows, ordered_k, ordered_v,      \
+                                  ordered_rows, a, st);
+  SEMBLO_PREFILL_CASE(256, 4)
+  SEMBLO_PREFILL_CASE(128, 4)
+  SEMBLO_PREFILL_CASE(256, 8)
+  SEMBLO_PREFILL_CASE(128, 8)
+  SEMBLO_PREFILL_CASE(256, 16)
+  SEMBLO_PREFILL_CASE(128, 16)
+#undef SEMBLO_PREFILL_CASE
+  return semblo::fail(semblo::SEMBLO_EINVAL,
+                      "prefill attention supports head_dim 128/256 with 4, 8 or 16 query heads per "
+                      "KV head (got head_dim %d, group %d)", head_dim, g);
+}

@@ -1,0 +1,364 @@
+// Query . centroid scoring and budgeted cluster selection for prefill chunks.
+//
+//   score kernel : [QT queries x G heads = 128 rows, D] x [D, C] on tcgen05 (TMA-fed,
+//                  TMEM accumulators), two passes over the codebook: pass 0 gives each
+//                  row's log-sum-exp over the clusters, pass 1 turns the logits into
+//                  softmax probabilities, sums them over the G heads of the KV head
+//                  (lane butterfly) and writes the penalised log score
+//                  log(max(P, 1e-38)) - beta log(1 + n_c)   (-3.4e38 where n_c = 0).
+//   select kernel: one warp per (query, KV head): the 16-step bisection for the score
+//                  threshold and the packed bitmask of the clusters at or above it.
+//
+// Reference behaviour restated here:
+//   semblo/vllm_plugin/fused_select.py:1061-1247  _flat_scores_qtiled_kernel
+//   semblo/vllm_plugin/fused_select.py:604-647    _streaming_select_kernel (resident branch)
+//   semblo/vllm_plugin/fused_prefill.py:202-216   sink hold-out and forced bit
+#include <algorithm>
+
+#include "../../include/semblo_b200.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+using namespace sm100;
+using semblo::ceil_div;
+
+namespace {
+
+constexpr int SC_BN = 128;
+constexpr int SC_STAGES = 2;
+constexpr float NEG_BIG = -3.4e38f;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+template <int D>
+struct ScoreSmem {
+  static constexpr int A_BYTES = 128 * D * 2;
+  static constexpr int B_BYTES = SC_BN * D * 2;
+  static constexpr int BAR_OFF = A_BYTES + SC_STAGES * B_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+// Sum v[] over the G adjacent lanes that hold the G heads of one query; afterwards
+// v[0 .. 32/G) are complete sums and the returned value is the column offset of v[0].
+template <int G>
+__device__ __forceinline__ int head_butterfly(float (&v)[32], int lane) {
+  int col = 0;
+  int width = 32;
+#pragma unroll
+  for (int bit = 1; bit < G; bit <<= 1) {
+    const int half = width >> 1;
+    const bool up = (lane & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i < half) {
+        const float send = up ? v[i] : v[i + half];
+        const float keep = up ? v[i + half] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+      }
+    }
+    col += up ? half : 0;
+    width = half;
+  }
+  return col;
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(192, 1)
+score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D] bf16, box (64, G, 128/G)
+             const __grid_constant__ CUtensorMap tmap_cb,   // codebooks [Hkv*2, C, D/2] bf16, box (64, 128, 1)
+             int num_queries, int num_clusters, const int32_t* __restrict__ sizes,   // [Hkv, C]
+             float scale_log2,                     // log2(e) / temperature
+             float beta, float* __restrict__ score,          // [Q, Hkv, C]
+             int num_kv_heads, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using L = ScoreSmem<D>;
+  constexpr int SLABS = D / 64;
+  constexpr int SLABS_PER_HALF = SLABS / 2;
+  constexpr int QT = 128 / G;
+  uint8_t* a_smem = smem;
+  uint8_t* b_smem = smem + L::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int q0 = blockIdx.x * QT;
+  const int chunks = (num_clusters + SC_BN - 1) / SC_BN;
+  const int total = 2 * chunks;                    // two passes over the codebook
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    for (int s = 0; s < SC_STAGES; ++s) {
+      mbar_init(smem_u32(&bars[1 + s]), 1);
+      mbar_init(smem_u32(&bars[3 + s]), 1);
+      mbar_init(smem_u32(&bars[5 + s]), 1);
+      mbar_init(smem_u32(&bars[7 + s]), 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_cb);
+      mbar_arrive_expect_tx(smem_u32(&bars[0]), L::A_BYTES);
+      for (int sl = 0; sl < SLABS; ++sl)
+        tma_load_3d(smem_u32(a_smem + sl * 128 * 128), &tmap_q, smem_u32(&bars[0]), sl * 64, h * G, q0);
+      for (int j = 0; j < total; ++j) {
+        const int s = j % SC_STAGES;
+        if (!mbar_wait(smem_u32(&bars[3 + s]), ((j / SC_STAGES) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_LOAD))
+          break;
+        mbar_arrive_expect_tx(smem_u32(&bars[1 + s]), L::B_BYTES);
+        const int c0 = (j % chunks) * SC_BN;
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma_load_3d(smem_u32(b_smem + s * L::B_BYTES + sl * SC_BN * 128), &tmap_cb,
+                      smem_u32(&bars[1 + s]), (sl % SLABS_PER_HALF) * 64, c0, h * 2 + sl / SLABS_PER_HALF);
+      }
+    }
+  } else if (warp == 5) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, SC_BN, false, false);
+      bool ok = mbar_wait(smem_u32(&bars[0]), 0, abort_flag, status, STATUS_TIMEOUT_MMA);
+      for (int j = 0; ok && j < total; ++j) {
+        const int s = j % SC_STAGES, b = j & 1;
+        if (!mbar_wait(smem_u32(&bars[1 + s]), (j / SC_STAGES) & 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
+        if (!mbar_wait(smem_u32(&bars[7 + b]), ((j >> 1) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_u32(a_smem);
+        const uint32_t b_base = smem_u32(b_smem + s * L::B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+          umma_ss(tmem_base + b * SC_BN, make_smem_desc(a_base + sl * 128 * 128 + ko, 16, 1024),
+                  make_smem_desc(b_base + sl * SC_BN * 128 + ko, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&bars[3 + s]));
+        umma_commit(smem_u32(&bars[5 + b]));
+      }
+    }
+  } else {
+    // epilogue warps: thread = row (query i = row / G, head t = row % G)
+    const int row = threadIdx.x;
+    const int qi = q0 + row / G;
+    float m_run = -INFINITY, l_run = 0.f, lse2 = 0.f;
+    const int32_t* sz = sizes + (int64_t)h * num_clusters;
+    bool ok = true;
+    for (int j = 0; j < total && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+      if (!ok) break;
+      tc_fence_after();
+      const int pass = j / chunks;
+      const int c0 = (j % chunks) * SC_BN;
+      if (j == chunks) lse2 = m_run + log2f(l_run);
+#pragma unroll 1
+      for (int c4 = 0; c4 < SC_BN / 32; ++c4) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * SC_BN + c4 * 32, r);
+        tmem_ld_wait();
+        const int cbase = c0 + c4 * 32;
+        if (pass == 0) {
+          float mx = m_run;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float s2 = __uint_as_float(r[i]) * scale_log2;
+            s2 = (cbase + i < num_clusters) ? s2 : -INFINITY;
+            r[i] = __float_as_uint(s2);
+            mx = fmaxf(mx, s2);
+          }
+          float add = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) add += exp2f(__uint_as_float(r[i]) - mx);
+          l_run = l_run * exp2f(m_run - mx) + add;
+          m_run = mx;
+        } else {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = exp2f(__uint_as_float(r[i]) * scale_log2 - lse2);
+          const int col = head_butterfly<G>(v, lane);
+          if (qi < num_queries) {
+            float* dst = score + ((int64_t)qi * num_kv_heads + h) * num_clusters;
+#pragma unroll
+            for (int i = 0; i < 32 / G; ++i) {
+              const int c = cbase + col + i;
+              if (c < num_clusters) {
+                const float n = (float)sz[c];
+                float sc = log2f(fmaxf(v[i], 1e-38f)) * LN2;
+                if (beta != 0.f) sc -= beta * logf(1.0f + n);
+                dst[c] = n > 0.f ? sc : NEG_BIG;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars[7 + b]));
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) __nanosleep(50000);
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+}
+
+// ---------------------------------------------------------------- threshold selection
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sumf(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per (query, KV head).  Dynamic smem: sizes of the head [C] floats, then one
+// [C] float score row per warp.
+__global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, C]
+                              const int32_t* __restrict__ sizes,    // [Hkv, C] (sink held out)
+                              int num_queries, int num_kv_heads, int num_clusters,
+                              float target_tokens, int iters, int force_sink,
+                              int32_t* __restrict__ qmask,          // [Q, Hkv, C/32]
+                              int32_t* __restrict__ counts,         // [Q, Hkv] or null
+                              int32_t* __restrict__ tokens) {       // [Q, Hkv] or null
+  extern __shared__ float sm[];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  float* s_size = sm;
+  float* s_score = sm + num_clusters + (int64_t)warp * num_clusters;
+  for (int c = threadIdx.x; c < num_clusters; c += blockDim.x)
+    s_size[c] = (float)sizes[(int64_t)h * num_clusters + c];
+  __syncthreads();
+  const int q = blockIdx.x * warps + warp;
+  if (q >= num_queries) return;
+  const float* row = score + ((int64_t)q * num_kv_heads + h) * num_clusters;
+  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  for (int c = lane; c < num_clusters; c += 32) {
+    const float s = row[c], n = s_size[c];
+    s_score[c] = s;
+    mx = fmaxf(mx, s);
+    mn = fminf(mn, n > 0.f ? s : 3.4e38f);
+    tot += n > 0.f ? n : 0.f;
+  }
+  __syncwarp();
+  float hi = warp_max(mx) + 1e-6f;
+  float lo = warp_min(mn) - 1e-6f;
+  lo = fminf(lo, hi - 1e-5f);
+  const bool all_fit = warp_sumf(tot) < target_tokens;
+  for (int it = 0; it < iters; ++it) {
+    const float mid = (lo + hi) * 0.5f;
+    float above = 0.f;
+    for (int c = lane; c < num_clusters; c += 32) above += s_score[c] >= mid ? s_size[c] : 0.f;
+    above = warp_sumf(above);
+    const bool reach = above >= target_tokens;
+    lo = reach ? mid : lo;
+    hi = reach ? hi : mid;
+  }
+  const float theta = all_fit ? NEG_BIG : lo;
+  int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * (num_clusters >> 5);
+  int n_sel = 0;
+  float n_tok = 0.f;
+  for (int w = 0; w < (num_clusters >> 5); ++w) {
+    const int c = w * 32 + lane;
+    const bool sel = s_size[c] > 0.f && s_score[c] >= theta;
+    unsigned bits = __ballot_sync(0xffffffffu, sel);
+    n_sel += __popc(bits);
+    n_tok += sel ? s_size[c] : 0.f;
+    if (w == 0 && force_sink) bits |= 1u;
+    if (lane == 0) qm[w] = (int32_t)bits;
+  }
+  n_tok = warp_sumf(n_tok);
+  if (lane == 0) {
+    if (counts) counts[(int64_t)q * num_kv_heads + h] = n_sel;
+    if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)n_tok;
+  }
+}
+
+template <int D, int G>
+int launch_score(const void* vectors, int num_queries, int num_q_heads, const void* codebooks,
+                 int num_kv_heads, int num_clusters, const int32_t* sizes, float temperature,
+                 float beta, float* score, int* status, cudaStream_t st) {
+  constexpr int QT = 128 / G;
+  CUtensorMap mq, mc;
+  uint64_t dq[3] = {(uint64_t)D, (uint64_t)num_q_heads, (uint64_t)num_queries};
+  uint64_t sq[2] = {(uint64_t)D * 2, (uint64_t)num_q_heads * D * 2};
+  uint32_t bq[3] = {64, (uint32_t)G, (uint32_t)QT};
+  int rc = semblo::make_tensor_map_bf16(&mq, vectors, 3, dq, sq, bq);
+  if (rc) return rc;
+  uint64_t dc[3] = {(uint64_t)D / 2, (uint64_t)num_clusters, (uint64_t)num_kv_heads * 2};
+  uint64_t sc[2] = {(uint64_t)D, (uint64_t)num_clusters * D};
+  uint32_t bc[3] = {64, (uint32_t)SC_BN, 1};
+  rc = semblo::make_tensor_map_bf16(&mc, codebooks, 3, dc, sc, bc);
+  if (rc) return rc;
+  auto kern = score_kernel<D, G>;
+  SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScoreSmem<D>::TOTAL));
+  dim3 grid((unsigned)ceil_div(num_queries, QT), num_kv_heads);
+  kern<<<grid, 192, ScoreSmem<D>::TOTAL, st>>>(mq, mc, num_queries, num_clusters, sizes,
+                                               LOG2E / temperature, beta, score, num_kv_heads, status);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int semblo_score_clusters(const void* vectors_bf16, int num_queries, int num_q_heads,
+                                     int head_dim, const void* codebooks_bf16, int num_kv_heads,
+                                     int num_clusters, const int32_t* select_sizes,
+                                     float temperature, float beta, float* score, int32_t* status,
+                                     void* stream) {
+  SEMBLO_REQUIRE(num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
+  SEMBLO_REQUIRE(temperature > 0.f, "temperature must be positive");
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  if (num_queries == 0) return 0;
+  const int g = num_q_heads / num_kv_heads;
+  cudaStream_t st = (cudaStream_t)stream;
+#define SEMBLO_SCORE_CASE(DD, GG)                                                                  \
+  if (head_dim == DD && g == GG)                                                                   \
+    return launch_score<DD, GG>(vectors_bf16, num_queries, num_q_heads, codebooks_bf16, num_kv_heads, \
+                                num_clusters, select_sizes, temperature, beta, score, status, st);
+  SEMBLO_SCORE_CASE(256, 4)
+  SEMBLO_SCORE_CASE(128, 4)
+  SEMBLO_SCORE_CASE(256, 8)
+  SEMBLO_SCORE_CASE(128, 8)
+  SEMBLO_SCORE_CASE(256, 16)
+  SEMBLO_SCORE_CASE(128, 16)
+#undef SEMBLO_SCORE_CASE
+  return semblo::fail(semblo::SEMBLO_EINVAL,
+                      "scoring supports head_dim 128/256 with 4, 8 or 16 query heads per KV head "
+                      "(got head_dim %d, group %d)", head_dim, g);
+}
+
+extern "C" int semblo_select_clusters(const float* score, const int32_t* select_sizes,
+                                      int num_queries, int num_kv_heads, int num_clusters,
+                                      int target_tokens, int iters, int force_sink, int32_t* qmask,
+                                      int32_t* counts, int32_t* tokens, void* stream) {
+  SEMBLO_REQUIRE(num_clusters % 32 == 0, "cluster count %d must be a multiple of 32", num_clusters);
+  if (num_queries == 0) return 0;
+  int warps = 8;
+  while (warps > 1 && (size_t)(warps + 1) * num_clusters * 4 > 200 * 1024) warps >>= 1;
+  const size_t smem = (size_t)(warps + 1) * num_clusters * 4;
+  SEMBLO_REQUIRE(smem <= 220 * 1024, "cluster count %d too large for the selection kernel", num_clusters);
+  SEMBLO_CUDA(cudaFuncSetAttribute(select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((unsigned)ceil_div(num_queries, warps), num_kv_heads);
+  select_kernel<<<grid, warps * 32, smem, (cudaStream_t)stream>>>(
+      score, select_sizes, num_queries, num_kv_heads, num_clusters, (float)target_tokens, iters,
+      force_sink, qmask, counts, tokens);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}

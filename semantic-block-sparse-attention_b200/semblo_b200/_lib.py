@@ -1,0 +1,112 @@
+"""ctypes binding of libsemblo_b200.so (the C ABI declared in include/semblo_b200.h).
+
+The library is the product: there is no Python or CPU fallback.  Importing this
+module does not load it; the first call of :func:`lib` does, and raises if the
+shared object has not been built."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "libsemblo_b200.so"
+_lib = None
+
+I32P = c_void_p
+_SIGNATURES = {
+    "semblo_version": (c_int, []),
+    "semblo_last_error": (c_char_p, []),
+    "semblo_routing_normalize": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "semblo_gather_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
+    "semblo_assign_argmax": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "semblo_cluster_counts": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_kmeans_update": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "semblo_split_descriptor": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "semblo_layout_workspace_bytes": (c_int64, [c_int64, c_int]),
+    "semblo_build_layout": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "semblo_pack_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "semblo_snapshot_advance": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "semblo_score_clusters": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p]),
+    "semblo_select_clusters": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_sparse_prefill": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_decode_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int64, c_int]),
+    "semblo_decode_workspace_offsets": (c_int, [c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
+    "semblo_decode_step": (c_int, [c_void_p] * 6 + [c_int] + [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int] * 3 + [c_void_p] + [c_int] * 4 + [c_float, c_float, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
+}
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def exported_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library.  Raises RuntimeError if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build the CUDA extension first "
+                "(python semantic-block-sparse-attention_b200/build.py); there is no fallback path")
+        handle = ctypes.CDLL(str(_LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def ptr(t: torch.Tensor | None):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def check(code: int) -> None:
+    if code != 0:
+        msg = lib().semblo_last_error().decode("utf-8", "replace")
+        if code == -1:
+            raise ValueError(msg)
+        raise RuntimeError(f"semblo_b200 call failed ({code}): {msg}")
+
+
+def require_cuda(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("semblo_b200 runs on CUDA tensors only; there is no CPU path")
+
+
+STATUS_TEXT = {0: "ok", 101: "load wait timed out", 102: "mma wait timed out", 103: "softmax wait timed out",
+               104: "epilogue wait timed out", 201: "a sized buffer would overflow"}
+
+
+class DeviceStatus:
+    """The int32 status word kernels report device-side conditions into."""
+
+    def __init__(self, device) -> None:
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def raise_if_set(self) -> None:
+        code = int(self.word.item())
+        if code:
+            self.word.zero_()
+            raise RuntimeError(f"semblo_b200 kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+
+
+_STATUS: dict = {}
+
+
+def status_for(device) -> DeviceStatus:
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = DeviceStatus(device)
+    return _STATUS[key]

@@ -1,0 +1,158 @@
+"""Prefill chunk driver: causal snapshot, dense-prefix rule, selection, attention body.
+
+Mirrors semblo/vllm_plugin/fused_prefill.py (CausalSnapshot 44-135,
+fused_chunk_attention 219-550 on its default path: SEMBLO_FA3_BODY=16,
+SEMBLO_KV_OUTER=1, sink rule 192-216) and the scoring/selection entry point
+theta_select_bitmask_flat (fused_select.py:806-863).  No host synchronisation in
+the chunk loop."""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, ptr, require_cuda, stream_ptr
+
+
+def _fitted_sink_tokens() -> int:
+    sink = int(os.environ.get("SEMBLO_SINK_TOKENS", "0") or "0")
+    return sink if sink > 0 else 0
+
+
+class CausalSnapshot:
+    """Running per-cluster count of keys with position <= p (fused_prefill.py:44-135)."""
+
+    def __init__(self, index) -> None:
+        self.index = index
+        self.sizes = torch.zeros_like(index.bucket_sizes)
+        self.next_pos = 0
+        self.length = int(index.prompt_length)
+        self.b_dim = int(index.num_buckets)
+        self.qmask = None
+        self.score = None
+        self.select_sizes = None
+
+    def advance(self, last_pos: int) -> torch.Tensor:
+        hi = min(int(last_pos) + 1, self.length)
+        if hi > self.next_pos:
+            ob = self.index.orig_bucket
+            check(lib().semblo_snapshot_advance(ptr(ob), ob.stride(0), ob.shape[0], self.next_pos, hi,
+                                                self.b_dim, ptr(self.sizes), stream_ptr()))
+            self.next_pos = hi
+        return self.sizes
+
+
+def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, select_sizes: torch.Tensor, *,
+                              temperature: float, beta: float, target_tokens: int, iters: int = 16,
+                              qmask: torch.Tensor | None = None, score: torch.Tensor | None = None,
+                              force_sink: bool = False, counts: torch.Tensor | None = None,
+                              tokens: torch.Tensor | None = None):
+    """Scores + bisected threshold -> per-query packed bitmask [Q, Hkv, C/32].
+
+    vectors [Q, Hq, D] bf16 routing vectors; select_sizes [Hkv, C] int32 (one snapshot for
+    the whole chunk, the sink cluster already held out).  Returns (qmask, score)."""
+    require_cuda(vectors, codebooks, select_sizes)
+    q_count, num_q_heads, dim = vectors.shape
+    num_kv_heads, _, num_clusters, _ = codebooks.shape
+    device = vectors.device
+    if score is None:
+        score = torch.empty(q_count, num_kv_heads, num_clusters, dtype=torch.float32, device=device)
+    if qmask is None:
+        qmask = torch.empty(q_count, num_kv_heads, num_clusters // 32, dtype=torch.int32, device=device)
+    status = _lib.status_for(device)
+    check(lib().semblo_score_clusters(ptr(vectors), q_count, num_q_heads, dim, ptr(codebooks), num_kv_heads,
+                                      num_clusters, ptr(select_sizes), float(temperature), float(beta),
+                                      ptr(score), ptr(status.word), stream_ptr()))
+    check(lib().semblo_select_clusters(ptr(score), ptr(select_sizes), q_count, num_kv_heads, num_clusters,
+                                       int(target_tokens), int(iters), 1 if force_sink else 0, ptr(qmask),
+                                       ptr(counts), ptr(tokens), stream_ptr()))
+    return qmask, score
+
+
+def sparse_prefill_attention(q: torch.Tensor, q_positions: torch.Tensor, *, packed_kv=None, page_table=None,
+                             qmask=None, causal_sizes=None, indptr=None, ordered_k=None, ordered_v=None,
+                             ordered_pos0: int = 0, local_start: int = 0, sm_scale: float, out=None,
+                             lse=None, attended=None, q_order=None) -> torch.Tensor:
+    """One launch of the block-sparse prefill kernel (see include/semblo_b200.h)."""
+    require_cuda(q)
+    q_count, num_q_heads, head_dim = q.shape
+    if q.dtype != torch.bfloat16:
+        raise ValueError("prefill attention takes bf16 queries")
+    q = q if q.is_contiguous() else q.contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    num_clusters = 0
+    pk = pv = None
+    packed_rows = 0
+    num_kv_heads = None
+    if qmask is not None:
+        num_clusters = int(causal_sizes.shape[1])
+        pk, pv = packed_kv[0], packed_kv[1]
+        packed_rows = int(packed_kv.shape[1])
+        num_kv_heads = int(packed_kv.shape[2])
+    if ordered_k is not None:
+        num_kv_heads = int(ordered_k.shape[1])
+        ordered_k = ordered_k if ordered_k.is_contiguous() else ordered_k.contiguous()
+        ordered_v = ordered_v if ordered_v.is_contiguous() else ordered_v.contiguous()
+    status = _lib.status_for(q.device)
+    check(lib().semblo_sparse_prefill(
+        ptr(q), q_count, num_q_heads, num_kv_heads, head_dim, ptr(q_positions), ptr(q_order),
+        ptr(pk), ptr(pv), packed_rows, ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr), num_clusters,
+        ptr(ordered_k), ptr(ordered_v), 0 if ordered_k is None else int(ordered_k.shape[0]), int(ordered_pos0),
+        int(local_start), float(sm_scale), ptr(out), ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
+    return out
+
+
+def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions: torch.Tensor,
+                          snapshot_state: CausalSnapshot, chunk_start: int, chunk_end: int, *,
+                          temperature: float, beta: float, target_tokens: int, queries_per_block: int = 32,
+                          sm_scale: float, iters: int = 16, dense_prefix_x: int = 4, out=None,
+                          attended=None, **unused) -> torch.Tensor:
+    """Attention of one query chunk (fused_prefill.py:219-482, default path).
+
+    ``query_state.vectors`` [1, Q, Hq, 1, D] routing vectors; ``index.original_kv`` must hold
+    the position-ordered (k_post, v) of the prompt: the exact window is read from it."""
+    import semblo_b200
+    semblo_b200.SPARSE_ATTENTION_CALLS += 1
+    cap = int(os.environ.get("SEMBLO_FA3_DENSE_PREFIX_X", str(dense_prefix_x))) * target_tokens
+    local = int(os.environ.get("SEMBLO_FA3_LOCAL", "0"))
+    wstart = 0 if chunk_start <= cap else max(0, chunk_start - local)
+    original_kv = getattr(index, "original_kv", None)
+    if original_kv is None:
+        raise RuntimeError("the prefill body reads the chunk's exact window from the position-ordered K/V "
+                           "(index.original_kv)")
+    k_pos, v_pos = original_kv
+    if wstart == 0:
+        return sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
+                                        ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
+                                        sm_scale=sm_scale, out=out, attended=attended)
+    base = snapshot_state.advance(wstart - 1)
+    sink = _fitted_sink_tokens()
+    if sink:
+        if snapshot_state.select_sizes is None:
+            snapshot_state.select_sizes = torch.empty_like(base)
+        select_sizes = snapshot_state.select_sizes
+        select_sizes.copy_(base)
+        select_sizes[:, 0] = 0                         # _hold_out_sink
+        select_target = max(0, int(target_tokens) - sink)
+    else:
+        select_sizes, select_target = base, int(target_tokens)
+    vectors = query_state.vectors[0]
+    vectors = vectors.reshape(vectors.shape[0], vectors.shape[1], -1)
+    q_count = q_chunk.shape[0]
+    snap = snapshot_state
+    if snap.qmask is None or snap.qmask.shape[0] < q_count:
+        snap.qmask = torch.empty(q_count, index.num_kv_heads, index.num_buckets // 32, dtype=torch.int32,
+                                 device=q_chunk.device)
+        snap.score = torch.empty(q_count, index.num_kv_heads, index.num_buckets, dtype=torch.float32,
+                                 device=q_chunk.device)
+    qmask, _ = theta_select_bitmask_flat(vectors, index.codebooks, select_sizes, temperature=temperature,
+                                         beta=beta, target_tokens=select_target, iters=iters,
+                                         qmask=snap.qmask[:q_count], score=snap.score[:q_count],
+                                         force_sink=bool(sink))
+    return sparse_prefill_attention(
+        q_chunk, q_positions, packed_kv=index.packed_kv, page_table=getattr(index, "kv_page_table", None),
+        qmask=qmask, causal_sizes=base, indptr=index.bucket_indptr, ordered_k=k_pos[wstart:chunk_end + 1],
+        ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart, sm_scale=sm_scale,
+        out=out, attended=attended)

@@ -1,0 +1,190 @@
+"""The request-local index: cluster descriptors, posting lists and the cluster-ordered
+K/V copy.  Mirrors the flat-partition half of semblo/vllm_plugin/state.py
+(ProductPostingIndex 400-452, build 476-542, _build_flat 544-948, pack_prompt_kv
+950-997, inverse_positions 999-1012)."""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from . import flat_index
+from ._lib import check, lib, ptr, require_cuda, stream_ptr
+
+_PACK_ALIGN = 256          # state.py:17
+
+
+def _sink_tokens() -> int:
+    return int(os.environ.get("SEMBLO_SINK_TOKENS", "0") or "0")
+
+
+_UNSUPPORTED_ENV = ("SEMBLO_BLOCK_TOKENS", "SEMBLO_FIXED_CODEBOOK", "SEMBLO_ROUTING_CENTER",
+                    "SEMBLO_FLAT_MIN_TOKENS", "SEMBLO_FLAT_MAX_TOKENS", "SEMBLO_HIER_SPAN",
+                    "SEMBLO_PAGE_CLUSTERS", "SEMBLO_FIT_PREFIX_TOKENS")
+
+
+def _refuse_ablation_flags() -> None:
+    """Ablation switches of the reference that this build does not implement raise
+    instead of being silently ignored."""
+    for name in _UNSUPPORTED_ENV:
+        if os.environ.get(name, "0") not in ("", "0"):
+            raise RuntimeError(f"{name} is an ablation switch of the reference that this build does not implement")
+    if (os.environ.get("SEMBLO_FLAT_INIT", "random") or "random") != "random":
+        raise RuntimeError("only SEMBLO_FLAT_INIT=random is implemented")
+    if (os.environ.get("SEMBLO_FLAT_METRIC", "cosine") or "cosine") != "cosine":
+        raise RuntimeError("only SEMBLO_FLAT_METRIC=cosine is implemented")
+    if os.environ.get("SEMBLO_FLAT_DETERMINISTIC", "1") != "1":
+        raise RuntimeError("the centroid sums are always deterministic here")
+
+
+def flat_num_clusters(length: int, target_size: int, min_clusters_log2: int) -> int:
+    """state.py:586-602."""
+    min_c_log2 = max(3, int(os.environ.get("SEMBLO_FLAT_MIN_CLUSTERS_LOG2", min_clusters_log2)))
+    raw_c = flat_index.flat_cluster_count(length, target_size)
+    num_clusters = 1 << max(min_c_log2, (max(raw_c, 1) - 1).bit_length())
+    num_clusters = min(num_clusters, 1 << (int(length).bit_length() - 1))
+    forced = int(os.environ.get("SEMBLO_FLAT_CLUSTERS", "0"))
+    return forced if forced > 0 else num_clusters
+
+
+@dataclass
+class ProductPostingIndex:
+    codebooks: torch.Tensor            # [Hkv, 2, C, D/2] key dtype
+    posting_positions: torch.Tensor    # [Hkv, W'] int32, cluster-major
+    bucket_indptr: torch.Tensor        # [Hkv, C+1] int32 (page-aligned starts)
+    bucket_sizes: torch.Tensor         # [Hkv, C] int32 (true sizes)
+    prompt_length: int
+    max_position: int
+    packed_kv: torch.Tensor | None = None
+    _inverse_positions: torch.Tensor | None = None
+    page_align: int = 0
+    flat_clusters: int = 0
+    orig_bucket: torch.Tensor | None = None      # [Hkv, L] int32 cluster of each position
+    original_kv: Any = None
+    kv_page_table: torch.Tensor | None = None    # packed row / 16 -> physical page (paged pool)
+
+    @property
+    def num_kv_heads(self) -> int:
+        return int(self.codebooks.shape[0])
+
+    @property
+    def num_buckets(self) -> int:
+        return int(self.flat_clusters)
+
+    @property
+    def is_flat(self) -> bool:
+        return True
+
+    @classmethod
+    def build(cls, product_keys: torch.Tensor, positions: torch.Tensor, *, num_centroids: int = 0,
+              kmeans_iters: int = 4, kmeans_sample_size: int = 8192, codebook_seed: int | None = None,
+              flat_unit_tokens: int = 0, flat_min_clusters_log2: int = 9, page_align: int = 0,
+              layer_idx: int | None = None, centroids: list | None = None, **unused) -> "ProductPostingIndex":
+        """Fit the per-prompt partition and lay out the posting lists (state.py:476-948).
+
+        ``product_keys`` [L, Hkv, I] is the key router's output.  ``centroids`` (one
+        fp32 [C or C-1, I] tensor per head) skips the fit: assignment and layout only."""
+        require_cuda(product_keys)
+        if product_keys.ndim != 3:
+            raise ValueError("product_keys must have shape [L,Hkv,I]")
+        length, num_kv_heads, index_dim = product_keys.shape
+        if positions.shape != (length,):
+            raise ValueError("positions must have shape [L]")
+        if length == 0:
+            raise ValueError("cannot build an index for an empty prompt")
+        _refuse_ablation_flags()
+        flat_target = int(os.environ.get("SEMBLO_FLAT_UNIT_TOKENS", flat_unit_tokens))
+        if flat_target <= 0:
+            raise ValueError("the index needs the flat partition: set SEMBLO_FLAT_UNIT_TOKENS or "
+                             "semblo_flat_unit_tokens to the mean block size")
+        device = product_keys.device
+        generator = None
+        if codebook_seed is not None:
+            generator = torch.Generator(device=device)
+            generator.manual_seed(int(codebook_seed))
+        num_clusters = flat_num_clusters(length, flat_target, flat_min_clusters_log2)
+        per_centroid = int(os.environ.get("SEMBLO_FLAT_FIT_PER_C", "32"))
+        fit_sample = min(length, max(int(kmeans_sample_size), per_centroid * num_clusters))
+        fit_iters = int(os.environ.get("SEMBLO_FLAT_FIT_ITERS", "8"))
+        page_align = int(os.environ.get("SEMBLO_FA3_ALIGN", page_align))
+        sink = _sink_tokens()
+        if sink:
+            if sink % 16:
+                raise RuntimeError(f"SEMBLO_SINK_TOKENS={sink}: a multiple of 16 keeps the sink cluster page-aligned")
+            if length <= sink or length - sink < 2 * num_clusters:
+                raise RuntimeError(f"SEMBLO_SINK_TOKENS={sink} leaves too few keys for {num_clusters - 1} clusters")
+        half = index_dim // 2
+        codebooks = torch.empty(num_kv_heads, 2, num_clusters, half, dtype=torch.bfloat16, device=device)
+        assign = torch.empty(num_kv_heads, length, dtype=torch.int32, device=device)
+        for h in range(num_kv_heads):
+            keys = product_keys[:, h]
+            _, space_f32, space_bf16 = flat_index._normalize_space(keys)
+            if sink:
+                if centroids is None:
+                    rest = flat_index.fit_flat_codebook(
+                        space_f32[sink:], space_bf16[sink:], num_clusters - 1, num_iters=fit_iters,
+                        sample_size=min(fit_sample, length - sink), generator=generator)
+                else:
+                    rest = centroids[h].float().contiguous()
+                assign[h, :sink].zero_()
+                flat_index.assign_flat_buckets(space_bf16[sink:], rest, out=assign[h, sink:], id_offset=1)
+                check(lib().semblo_split_descriptor(ptr(rest), num_clusters - 1, 1, num_clusters, index_dim,
+                                                    ptr(codebooks[h]), stream_ptr()))
+            else:
+                if centroids is None:
+                    cents = flat_index.fit_flat_codebook(space_f32, space_bf16, num_clusters, num_iters=fit_iters,
+                                                         sample_size=fit_sample, generator=generator)
+                else:
+                    cents = centroids[h].float().contiguous()
+                flat_index.assign_flat_buckets(space_bf16, cents, out=assign[h])
+                check(lib().semblo_split_descriptor(ptr(cents), num_clusters, 0, num_clusters, index_dim,
+                                                    ptr(codebooks[h]), stream_ptr()))
+        align = page_align if page_align > 1 else 1
+        cap = length + num_clusters * (align - 1)
+        cap += (-cap) % _PACK_ALIGN
+        posting = torch.empty(num_kv_heads, cap, dtype=torch.int32, device=device)
+        indptr = torch.empty(num_kv_heads, num_clusters + 1, dtype=torch.int32, device=device)
+        sizes = torch.empty(num_kv_heads, num_clusters, dtype=torch.int32, device=device)
+        inverse = torch.empty(num_kv_heads, length, dtype=torch.int32, device=device)
+        ws_bytes = int(lib().semblo_layout_workspace_bytes(length, num_kv_heads)) + num_kv_heads * (num_clusters + 1) * 4
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        check(lib().semblo_build_layout(ptr(assign), length, num_kv_heads, num_clusters, align, ptr(posting), cap,
+                                        ptr(indptr), ptr(sizes), ptr(inverse), ptr(ws), ws_bytes, stream_ptr()))
+        # one host read, as the reference's int(ip_pad[-1]): the common posting width
+        width = int(indptr[:, -1].max().item())
+        index = cls(codebooks=codebooks if product_keys.dtype == torch.bfloat16 else codebooks.to(product_keys.dtype),
+                    posting_positions=posting[:, :width], bucket_indptr=indptr, bucket_sizes=sizes,
+                    prompt_length=length, max_position=length - 1, page_align=page_align if page_align > 1 else 0,
+                    flat_clusters=num_clusters, _inverse_positions=inverse, orig_bucket=assign)
+        return index
+
+    def pack_prompt_kv(self, key: torch.Tensor, value: torch.Tensor, *, pool=None,
+                       page_table: torch.Tensor | None = None) -> torch.Tensor:
+        """state.py:950-997.  With ``page_table`` ([W / 16] int32) the cluster-ordered rows are
+        written into 16-row pages of a paged pool in that order (vLLM block-table layout)."""
+        require_cuda(key, value)
+        if key.shape != value.shape:
+            raise ValueError("key and value must have the same shape")
+        if key.ndim != 3 or key.shape[0] != self.prompt_length:
+            raise ValueError("key and value must have shape [L,Hkv,D]")
+        if key.shape[1] != self.num_kv_heads:
+            raise ValueError("key and value KV-head count differs from the index")
+        if key.dtype != torch.bfloat16:
+            raise ValueError("the cluster-ordered copy is bf16")
+        width = int(self.posting_positions.shape[1])
+        pad = (-width) % _PACK_ALIGN
+        shape = (2, width + pad, self.num_kv_heads, key.shape[-1])
+        packed = torch.empty(*shape, dtype=key.dtype, device=key.device) if pool is None else pool(shape, key.dtype, key.device)
+        k = key if key.is_contiguous() else key.contiguous()
+        v = value if value.is_contiguous() else value.contiguous()
+        check(lib().semblo_pack_kv(ptr(k), ptr(v), ptr(self.posting_positions), self.posting_positions.stride(0),
+                                   width, width + pad, self.num_kv_heads, key.shape[-1], ptr(packed),
+                                   packed.stride(0), ptr(page_table), stream_ptr()))
+        self.packed_kv = packed
+        self.kv_page_table = page_table
+        return packed
+
+    def inverse_positions(self) -> torch.Tensor:
+        return self._inverse_positions

@@ -1,0 +1,445 @@
+"""Parity of the CUDA path against the CPU oracle on the same seeded inputs.
+
+Every call goes through the C ABI (libsemblo_b200.so via ctypes).  Integer stages are
+compared bit for bit; float-dependent integer results (assignment, selection) must be
+identical wherever the oracle's own margin is not tiny; attention outputs are held to
+2e-2 max-abs / 1e-3 mean-abs in bf16 (the reference's tolerance for this path)."""
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+
+from oracle import semblo_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+MEAN_ABS = 1e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from semblo_b200 import _lib
+    _lib.lib()          # raises if the extension is missing: no silent fallback
+    return torch.device("cuda:0")
+
+
+def _status_ok(dev):
+    from semblo_b200 import _lib
+    _lib.status_for(dev).raise_if_set()
+
+
+def _close_attention(got: torch.Tensor, want: torch.Tensor, what: str):
+    diff = (got.double().cpu() - want.double().cpu()).abs()
+    assert float(diff.max()) <= MAX_ABS, f"{what}: max-abs {float(diff.max()):.4g}"
+    assert float(diff.mean()) <= MEAN_ABS, f"{what}: mean-abs {float(diff.mean()):.4g}"
+
+
+def _unit(n, d, seed, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return torch.nn.functional.normalize(torch.randn(n, d, generator=g), dim=-1).to(dtype)
+
+
+# ---------------------------------------------------------------------- routing space
+@pytest.mark.parametrize("dim", [64, 128, 256])
+def test_routing_normalize_and_query_vectors(dev, dim):
+    from semblo_b200 import flat_index, trivial_router
+    g = torch.Generator().manual_seed(dim)
+    x = (torch.randn(777, 4, dim, generator=g) * 3).to(torch.bfloat16)
+    got = flat_index.routing_normalize(x.to(dev)).cpu()
+    want = O.routing_normalize(x)
+    bad = (got.float() - want.float()).abs() > 0
+    assert float(bad.float().mean()) < 2e-3           # differences are single bf16 roundings
+    assert float((got.float() - want.float()).abs().max()) <= 2 ** -7 * 0.26
+    qv = trivial_router.trivial_router_vectors(x.to(dev)).cpu()
+    want_q = O.trivial_router_vectors(x)
+    assert float(((qv.float() - want_q.float()).abs() > 0).float().mean()) < 4e-3
+    assert float((qv.float() - want_q.float()).abs().max()) <= 2 ** -7 * 0.26
+    _, f32, b16 = flat_index._normalize_space(want.to(dev)[:, 0].contiguous())
+    torch.testing.assert_close(f32.cpu(), O.routing_space(want[:, 0]), atol=2e-7, rtol=0)
+    assert torch.equal(b16.cpu().float(), O.routing_space(want[:, 0]).to(torch.bfloat16).float()) or \
+        float(((b16.cpu().float() - O.routing_space(want[:, 0]).to(torch.bfloat16).float()).abs() > 0).float().mean()) < 1e-3
+
+
+# ---------------------------------------------------------------------- assignment
+@pytest.mark.parametrize("dim,n,clusters", [(256, 3000, 2048), (128, 1111, 127), (64, 500, 40), (256, 129, 128)])
+def test_assign_argmax_matches_oracle_outside_rounding_boundaries(dev, dim, n, clusters):
+    from semblo_b200 import flat_index
+    x = _unit(n, dim, 1)
+    # clustered data: many bf16 ties, as in a real prompt
+    c = torch.nn.functional.normalize(x[torch.randperm(n, generator=torch.Generator().manual_seed(2))[:clusters]]
+                                      + 0.05 * torch.randn(clusters, dim, generator=torch.Generator().manual_seed(3)), dim=-1)
+    want, sim32 = O.argmax_sim(x, c, return_sim=True)
+    got = flat_index.assign_flat_buckets(x.to(torch.bfloat16).to(dev), c.to(dev)).cpu().long()
+    _status_ok(dev)
+    differ = got != want
+    margin = O.assign_margin(sim32)
+    # a differing row must sit on a bf16 rounding boundary of one of its top columns
+    assert bool((margin[differ] < 3e-6).all()), f"{int(differ.sum())} rows differ, worst margin {float(margin[differ].max()) if differ.any() else 0}"
+    assert float(differ.float().mean()) < 2e-3
+    # and the chosen centroid must still tie with the oracle's after rounding
+    simb = sim32.to(torch.bfloat16).float()
+    rows = torch.nonzero(differ).flatten()
+    if rows.numel():
+        step = simb[rows, want[rows]].abs() * 2 ** -7
+        assert bool(((simb[rows, want[rows]] - simb[rows, got[rows]]).abs() <= step + 1e-12).all())
+
+
+def test_kmeans_update_with_empty_cluster_restart(dev):
+    from semblo_b200._lib import lib, ptr, check, stream_ptr
+    n, dim, clusters = 5000, 128, 96
+    sample = _unit(n, dim, 5)
+    g = torch.Generator().manual_seed(6)
+    assign = torch.randint(0, clusters - 3, (n,), generator=g)      # clusters 93..95 stay empty
+    repl = torch.randperm(n, generator=g)
+    want, _ = O.kmeans_update(sample, assign, clusters, repl)
+    s_d, a_d = sample.to(dev), assign.to(torch.int32).to(dev)
+    counts = torch.empty(clusters, dtype=torch.int32, device=dev)
+    ip = torch.empty(clusters + 1, dtype=torch.int32, device=dev)
+    er = torch.empty(clusters, dtype=torch.int32, device=dev)
+    ne = torch.empty(1, dtype=torch.int32, device=dev)
+    check(lib().semblo_cluster_counts(ptr(a_d), n, n, 1, clusters, 1, ptr(counts), ptr(ip), None, ptr(er), ptr(ne), stream_ptr()))
+    assert int(ne.item()) == 3
+    assert torch.equal(counts.cpu().long(), torch.bincount(assign, minlength=clusters))
+    ws_bytes = int(lib().semblo_layout_workspace_bytes(n, 1))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    cf = torch.empty(clusters, dim, dtype=torch.float32, device=dev)
+    cb = torch.empty(clusters, dim, dtype=torch.bfloat16, device=dev)
+    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl.to(dev)),
+                                     ptr(cf), ptr(cb), ptr(ws), ws_bytes, stream_ptr()))
+    torch.testing.assert_close(cf.cpu(), want, atol=2e-6, rtol=0)
+    assert torch.equal(cb.cpu().float(), cf.cpu().to(torch.bfloat16).float())
+    # deterministic: a second run gives the same bytes
+    cf2 = torch.empty_like(cf)
+    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl.to(dev)),
+                                     ptr(cf2), ptr(cb), ptr(ws), ws_bytes, stream_ptr()))
+    assert torch.equal(cf, cf2)
+
+
+# ---------------------------------------------------------------------- layout / pack / snapshot
+@pytest.mark.parametrize("length,heads,clusters,align", [(5000, 3, 64, 16), (70000, 2, 2048, 16), (4097, 1, 512, 1),
+                                                         (300, 2, 256, 16)])
+def test_layout_is_bit_identical(dev, length, heads, clusters, align):
+    from semblo_b200._lib import lib, ptr, check, stream_ptr
+    g = torch.Generator().manual_seed(length)
+    # skewed sizes with empty clusters
+    w = torch.rand(clusters, generator=g) ** 3
+    w[::7] = 0
+    assign = torch.multinomial(w, heads * length, replacement=True, generator=g).view(heads, length)
+    cap = length + clusters * (align - 1 if align > 1 else 0)
+    cap += (-cap) % 256
+    a_d = assign.to(torch.int32).to(dev)
+    posting = torch.empty(heads, cap, dtype=torch.int32, device=dev)
+    indptr = torch.empty(heads, clusters + 1, dtype=torch.int32, device=dev)
+    sizes = torch.empty(heads, clusters, dtype=torch.int32, device=dev)
+    inverse = torch.empty(heads, length, dtype=torch.int32, device=dev)
+    ws_bytes = int(lib().semblo_layout_workspace_bytes(length, heads)) + heads * (clusters + 1) * 4
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    check(lib().semblo_build_layout(ptr(a_d), length, heads, clusters, align, ptr(posting), cap, ptr(indptr),
+                                    ptr(sizes), ptr(inverse), ptr(ws), ws_bytes, stream_ptr()))
+    for h in range(heads):
+        order, ip, counts, inv = O.layout_from_assign(assign[h], clusters, align)
+        assert torch.equal(sizes[h].cpu(), counts)
+        assert torch.equal(indptr[h].cpu(), ip)
+        assert torch.equal(posting[h, :order.numel()].cpu(), order)
+        assert bool((posting[h, order.numel():].cpu() == order[0]).all())
+        assert torch.equal(inverse[h].cpu(), inv)
+
+
+def test_pack_and_snapshot_are_bit_identical(dev):
+    from semblo_b200.state import ProductPostingIndex
+    from semblo_b200.fused_prefill import CausalSnapshot
+    length, heads, dim, clusters = 3000, 2, 128, 64
+    keys = O.mixture_inputs(length=length, num_q_heads=heads, num_kv_heads=heads, head_dim=dim, centres=20,
+                            seed=11)["k_pre"]
+    product = O.routing_normalize(keys)
+    g = torch.Generator().manual_seed(3)
+    cents = [_unit(clusters, dim, 40 + h) for h in range(heads)]
+    os.environ["SEMBLO_FLAT_UNIT_TOKENS"] = "32"
+    try:
+        index = ProductPostingIndex.build(product.to(dev), torch.arange(length, device=dev), flat_unit_tokens=32,
+                                          flat_min_clusters_log2=6, page_align=16,
+                                          centroids=[c.to(dev) for c in cents])
+    finally:
+        os.environ.pop("SEMBLO_FLAT_UNIT_TOKENS", None)
+    assert index.num_buckets == clusters
+    # oracle layout from the kernel's own assignment: the integer stages must agree exactly
+    assign = index.orig_bucket.cpu().long()
+    ref = O.build_flat(product, unit_tokens=32, min_clusters_log2=6, page_align=16, centroids=cents)
+    assert float((assign != ref.assign).float().mean()) < 2e-3
+    for h in range(heads):
+        order, ip, counts, inv = O.layout_from_assign(assign[h], clusters, 16)
+        assert torch.equal(index.bucket_sizes[h].cpu(), counts)
+        assert torch.equal(index.bucket_indptr[h].cpu(), ip)
+        assert torch.equal(index.posting_positions[h, :order.numel()].cpu(), order)
+        assert torch.equal(index.inverse_positions()[h].cpu(), inv)
+    assert float((index.codebooks.cpu().float() - ref.codebooks.float()).abs().max()) <= 2 ** -8
+    k = torch.randn(length, heads, dim, generator=g).to(torch.bfloat16)
+    v = torch.randn(length, heads, dim, generator=g).to(torch.bfloat16)
+    packed = index.pack_prompt_kv(k.to(dev), v.to(dev)).cpu()
+    fake = O.FlatIndex(codebooks=None, posting_positions=index.posting_positions.cpu(), bucket_indptr=None,
+                       bucket_sizes=None, inverse_positions=None, assign=None, prompt_length=length, page_align=16)
+    assert torch.equal(packed.float(), O.pack_prompt_kv(fake, k, v).float())
+    # paged pool: the same rows behind a random page permutation
+    n_pages = packed.shape[1] // 16
+    table = torch.randperm(n_pages, generator=g).to(torch.int32)
+    paged = index.pack_prompt_kv(k.to(dev), v.to(dev), page_table=table.to(dev)).cpu()
+    view = paged.view(2, n_pages, 16, heads, dim)[:, table.long()].reshape(packed.shape)
+    assert torch.equal(view.float(), packed.float())
+    snap = CausalSnapshot(index)
+    for p in (0, 17, 999, 1000, 2999):
+        got = snap.advance(p).cpu()
+        want = torch.stack([torch.bincount(assign[h, :p + 1], minlength=clusters) for h in range(heads)]).int()
+        assert torch.equal(got, want)
+
+
+# ---------------------------------------------------------------------- scoring + selection
+def _small_problem(length, hq, hkv, dim, centres, seed, unit, min_log2, sink):
+    data = O.mixture_inputs(length=length, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=centres, seed=seed)
+    product = O.routing_normalize(data["k_pre"])
+    index = O.build_flat(product, unit_tokens=unit, min_clusters_log2=min_log2, kmeans_sample_size=1024,
+                         fit_iters=4, seed=0, sink=sink, page_align=16)
+    O.pack_prompt_kv(index, data["k_post"], data["v"])
+    return data, index
+
+
+def _gpu_index(index, dev):
+    from semblo_b200.state import ProductPostingIndex
+    gi = ProductPostingIndex(codebooks=index.codebooks.to(dev), posting_positions=index.posting_positions.to(dev),
+                             bucket_indptr=index.bucket_indptr.to(dev), bucket_sizes=index.bucket_sizes.to(dev),
+                             prompt_length=index.prompt_length, max_position=index.prompt_length - 1,
+                             page_align=16, flat_clusters=int(index.bucket_sizes.shape[1]),
+                             _inverse_positions=index.inverse_positions.to(dev),
+                             orig_bucket=index.assign.to(torch.int32).to(dev))
+    gi.packed_kv = index.packed_kv.to(dev)
+    return gi
+
+
+@pytest.mark.parametrize("dim,hq,hkv,sink", [(256, 8, 2, 64), (128, 8, 2, 0), (128, 16, 2, 0)])
+def test_scores_and_selection(dev, dim, hq, hkv, sink):
+    from semblo_b200.fused_prefill import theta_select_bitmask_flat
+    length, target = 6144, 512
+    data, index = _small_problem(length, hq, hkv, dim, 24, 21 + dim, 32, 7, sink)
+    clusters = index.bucket_sizes.shape[1]
+    sizes = O.causal_sizes_at(index, 4000)
+    qs = slice(4100, 4100 + 333)
+    vectors = O.trivial_router_vectors(data["q_pre"][qs])
+    sel_sizes, sel_target = (O.hold_out_sink(sizes, target, sink) if sink else (sizes, target))
+    score_ref = O.penalized_scores(O.mixture_prob(vectors, index.codebooks, 0.1, torch.float64), sel_sizes[None], 0.25)
+    sel_ref, margin = O.select_clusters(vectors, index.codebooks, sizes, temperature=0.1, beta=0.25,
+                                        target_tokens=target, sink=sink, return_margin=True)
+    counts = torch.empty(333, hkv, dtype=torch.int32, device=dev)
+    tokens = torch.empty(333, hkv, dtype=torch.int32, device=dev)
+    qmask, score = theta_select_bitmask_flat(vectors.to(dev), index.codebooks.to(dev), sel_sizes.to(dev),
+                                             temperature=0.1, beta=0.25, target_tokens=sel_target,
+                                             force_sink=bool(sink), counts=counts, tokens=tokens)
+    _status_ok(dev)
+    live = (sel_sizes > 0)[None].expand(333, -1, -1)
+    err = (score.cpu().double() - score_ref)[live].abs()
+    assert float(err.max()) < 5e-5, float(err.max())
+    assert bool((score.cpu()[~live] == O.NEG_BIG).all())
+    sel = O.unpack_bits(qmask.cpu())
+    assert sel.shape[-1] == clusters
+    differ = (sel != sel_ref).any(dim=-1)
+    assert bool((margin[differ] < 1e-4).all()), (int(differ.sum()), float(margin[differ].max()) if differ.any() else 0)
+    assert float(differ.float().mean()) < 0.02
+    # the selection the kernel reports is exactly the rule applied to its own scores
+    sel_own = O.theta_select(score.cpu(), sel_sizes[None], sel_target, 16)
+    if sink:
+        sel_own = sel_own.clone()
+        sel_own[..., 0] = True
+    assert torch.equal(sel, sel_own)
+    held = sel_own.clone()
+    if sink:
+        held[..., 0] = False
+    assert torch.equal(counts.cpu(), held.sum(-1).int())
+    assert torch.equal(tokens.cpu(), (held * sel_sizes[None]).sum(-1).int())
+
+
+# ---------------------------------------------------------------------- prefill attention
+@pytest.mark.parametrize("dim,hq,hkv", [(256, 8, 2), (128, 4, 1), (128, 16, 2)])
+def test_dense_causal_attention(dev, dim, hq, hkv):
+    from semblo_b200.fused_prefill import sparse_prefill_attention
+    length = 700
+    data = O.mixture_inputs(length=length, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=8, seed=3)
+    sm_scale = dim ** -0.5
+    qpos = torch.arange(length)
+    want, lse_want = O.dense_causal_attention(data["q_post"], data["k_post"], data["v"], qpos, sm_scale)
+    lse = torch.empty(length, hq, dtype=torch.float32, device=dev)
+    att = torch.zeros(1, dtype=torch.int64, device=dev)
+    got = sparse_prefill_attention(data["q_post"].to(dev), qpos.int().to(dev), ordered_k=data["k_post"].to(dev),
+                                   ordered_v=data["v"].to(dev), sm_scale=sm_scale, lse=lse, attended=att)
+    _status_ok(dev)
+    _close_attention(got, want, "dense prefix")
+    torch.testing.assert_close(lse.cpu().double(), lse_want, atol=2e-3, rtol=0)
+    assert int(att.item()) == hkv * length * (length + 1) // 2
+    # a later chunk over a window: positions [ws, p]
+    qs = slice(400, 700)
+    want_w, _ = O.dense_causal_attention(data["q_post"][qs], data["k_post"][200:], data["v"][200:], qpos[qs],
+                                         sm_scale, k_start=200)
+    got_w = sparse_prefill_attention(data["q_post"][qs].contiguous().to(dev), qpos[qs].int().to(dev),
+                                     ordered_k=data["k_post"][200:].contiguous().to(dev),
+                                     ordered_v=data["v"][200:].contiguous().to(dev), ordered_pos0=200,
+                                     local_start=200, sm_scale=sm_scale)
+    _close_attention(got_w, want_w, "window")
+
+
+@pytest.mark.parametrize("dim,hq,hkv,sink,paged", [(256, 8, 2, 64, True), (128, 8, 2, 0, False)])
+def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, hq, hkv, sink, paged):
+    from semblo_b200.fused_prefill import sparse_prefill_attention
+    length, target, local = 6144, 512, 128
+    data, index = _small_problem(length, hq, hkv, dim, 24, 77 + dim, 32, 7, sink)
+    cs, ce = 4096, 4096 + 499
+    ws = cs - local
+    sizes = O.causal_sizes_at(index, ws - 1)
+    qpos = torch.arange(cs, ce + 1)
+    vectors = O.trivial_router_vectors(data["q_pre"][cs:ce + 1])
+    sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=0.1, beta=0.25, target_tokens=target, sink=sink)
+    sm_scale = dim ** -0.5
+    want, natt = O.sparse_chunk_attention(data["q_post"][cs:ce + 1], index, sel, sizes, qpos,
+                                          data["k_post"][ws:ce + 1], data["v"][ws:ce + 1], ws, sm_scale)
+    packed = index.packed_kv.to(dev)
+    table = None
+    if paged:
+        n_pages = packed.shape[1] // 16
+        perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(5))
+        pool = torch.empty_like(packed).view(2, n_pages, 16, hkv, dim)
+        pool[:, perm] = packed.view(2, n_pages, 16, hkv, dim)
+        packed = pool.view(2, n_pages * 16, hkv, dim).contiguous()
+        table = perm.to(torch.int32).to(dev)
+    att = torch.zeros(1, dtype=torch.int64, device=dev)
+    got = sparse_prefill_attention(
+        data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev), packed_kv=packed, page_table=table,
+        qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev), indptr=index.bucket_indptr.to(dev),
+        ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev), ordered_v=data["v"][ws:ce + 1].contiguous().to(dev),
+        ordered_pos0=ws, local_start=ws, sm_scale=sm_scale, attended=att)
+    _status_ok(dev)
+    _close_attention(got, want, "sparse chunk")
+    assert int(att.item()) == int(natt.sum())
+    # a permuted tile order gives the same rows
+    order = torch.stack([torch.randperm(500, generator=torch.Generator().manual_seed(h)) for h in range(hkv)]).int()
+    got_p = sparse_prefill_attention(
+        data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev), packed_kv=packed, page_table=table,
+        qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev), indptr=index.bucket_indptr.to(dev),
+        ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev), ordered_v=data["v"][ws:ce + 1].contiguous().to(dev),
+        ordered_pos0=ws, local_start=ws, sm_scale=sm_scale, q_order=order.to(dev))
+    _close_attention(got_p, want, "sparse chunk, permuted tiles")
+
+
+def test_prefill_chunk_loop_end_to_end(dev):
+    """The reference's chunk loop (dense prefix chunks, then selection + sparse body) through the
+    mirrored Python entry points, against the oracle evaluated on the kernel's own selections."""
+    from types import SimpleNamespace
+    from semblo_b200.fused_prefill import CausalSnapshot, fused_chunk_attention
+    from semblo_b200.trivial_router import trivial_router_vectors
+    dim, hq, hkv, sink, length, target, local, chunk = 128, 8, 2, 64, 5120, 256, 128, 1024
+    data, index = _small_problem(length, hq, hkv, dim, 24, 5, 32, 7, sink)
+    gi = _gpu_index(index, dev)
+    gi.original_kv = (data["k_post"].to(dev), data["v"].to(dev))
+    os.environ["SEMBLO_SINK_TOKENS"] = str(sink)
+    os.environ["SEMBLO_FA3_LOCAL"] = str(local)
+    try:
+        snap = CausalSnapshot(gi)
+        out = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=dev)
+        sm_scale = dim ** -0.5
+        selections = {}
+        for cs in range(0, length, chunk):
+            ce = cs + chunk - 1
+            qv = trivial_router_vectors(data["q_pre"][cs:ce + 1].to(dev))
+            state = SimpleNamespace(vectors=qv.view(1, chunk, hq, 1, dim))
+            fused_chunk_attention(data["q_post"][cs:ce + 1].to(dev), state, gi,
+                                  torch.arange(cs, ce + 1, dtype=torch.int32, device=dev), snap, cs, ce,
+                                  temperature=0.1, beta=0.25, target_tokens=target, sm_scale=sm_scale,
+                                  out=out[cs:ce + 1])
+            if O.chunk_plan(cs, target, local) > 0:
+                selections[cs] = O.unpack_bits(snap.qmask[:chunk].cpu())
+        _status_ok(dev)
+    finally:
+        os.environ.pop("SEMBLO_SINK_TOKENS", None)
+        os.environ.pop("SEMBLO_FA3_LOCAL", None)
+    assert len(selections) == 3                     # chunks starting at 2048, 3072, 4096 are sparse
+    want = O.prefill_attention(data["q_post"], data["q_pre"], data["k_post"], data["v"], index, temperature=0.1,
+                               beta=0.25, target_tokens=target, sink=sink, local=local, sm_scale=sm_scale,
+                               chunk=chunk, selections=dict(selections))
+    _close_attention(out, want, "prefill end to end")
+    # selection parity with the oracle's own selections
+    own = {}
+    O.prefill_attention(data["q_post"], data["q_pre"], data["k_post"], data["v"], index, temperature=0.1, beta=0.25,
+                        target_tokens=target, sink=sink, local=local, sm_scale=sm_scale, chunk=chunk, selections=own)
+    rows = sum(int((selections[c] != own[c]).any(-1).sum()) for c in selections)
+    assert rows <= 0.02 * 3 * chunk * hkv
+
+
+# ---------------------------------------------------------------------- decode
+@pytest.mark.parametrize("dim,hq,hkv,sink", [(256, 8, 2, 64), (128, 8, 2, 0)])
+def test_decode_steps_through_the_arena(dev, dim, hq, hkv, sink):
+    from types import SimpleNamespace
+    from semblo_b200.arena import DecodeArena
+    from semblo_b200.fused_decode import fused_decode_step
+    length, target, steps = 6000, 512, 6
+    data, index = _small_problem(length + steps, hq, hkv, dim, 24, 9 + dim, 32, 7, sink)
+    # the index covers the prompt only
+    prompt = {k: v[:length] for k, v in data.items()}
+    product = O.routing_normalize(prompt["k_pre"])
+    index = O.build_flat(product, unit_tokens=32, min_clusters_log2=7, kmeans_sample_size=1024, fit_iters=4,
+                         seed=0, sink=sink, page_align=16)
+    O.pack_prompt_kv(index, prompt["k_post"], prompt["v"])
+    clusters = index.bucket_sizes.shape[1]
+    ref = O.make_arena(capacity=8192, num_clusters=256, num_kv_heads=hkv, head_dim=dim, page_align=16, reserve=512,
+                       kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16, keep_kpre=True)
+    O.arena_adopt(ref, index)
+    arena = DecodeArena(capacity=8192, num_kv_heads=hkv, head_dim=dim, num_clusters=256, page_align=16, device=dev,
+                        reserve=512, keep_kpre=True)
+    assert arena.width == ref.posting.shape[1] and clusters <= 256
+    arena.adopt(_gpu_index(index, dev))
+    assert torch.equal(arena.suffix_table.cpu(), ref.suffix_table)
+    layer = SimpleNamespace(num_heads=hq, num_kv_heads=hkv, head_dim=dim)
+    sm_scale = dim ** -0.5
+    out = torch.empty(1, hq * dim, dtype=torch.bfloat16, device=dev)
+    os.environ["SEMBLO_SINK_TOKENS"] = str(sink)
+    try:
+        for s in range(steps):
+            pos = length + s
+            args = dict(q_post=data["q_post"][pos], q_pre=data["q_pre"][pos], k_post=data["k_post"][pos],
+                        v=data["v"][pos], k_pre=data["k_pre"][pos])
+            vectors = O.trivial_router_vectors(args["q_pre"])
+            sel_ref, csr_ref, margin = O.decode_select(vectors, ref, temperature=0.1, beta=0.25, target_tokens=target,
+                                                       sink=sink, return_margin=True)
+            fused_decode_step(layer, arena, q_post=args["q_post"][None].contiguous().to(dev),
+                              q_pre=args["q_pre"][None].contiguous().to(dev),
+                              positions=torch.tensor([pos], device=dev), k_post=args["k_post"][None].contiguous().to(dev),
+                              v_states=args["v"][None].contiguous().to(dev), k_pre=args["k_pre"][None].contiguous().to(dev),
+                              output=out, temperature=0.1, beta=0.25, target_tokens=target, sm_scale=sm_scale,
+                              num_splits=8)
+            _status_ok(dev)
+            ws = arena.fused_decode_ws
+            assert torch.equal(ws.vectors.cpu().float(), vectors.float()) or \
+                float(((ws.vectors.cpu().float() - vectors.float()).abs() > 0).float().mean()) < 4e-3
+            # the kernel's selection, recovered from its CSR
+            sel = torch.zeros(hkv, 256, dtype=torch.bool)
+            for h in range(hkv):
+                n = int(ws.rcount[h])
+                starts = ws.rstart[h, :n].cpu()
+                ids = torch.searchsorted(ref.indptr[h].contiguous(), starts, right=True) - 1
+                # clusters with equal starts are empty: take the last one with that start
+                sel[h, ids] = True
+                lens = ws.rlen[h, :n].cpu()
+                assert torch.equal(lens, ref.sizes[h][ids])
+                assert torch.equal(ws.rcum[h, :n].cpu(), (lens.cumsum(0) - lens).int())
+                assert int(ws.rtokens[h]) == int(lens.sum())
+                rows = torch.cat([torch.arange(int(a), int(a) + int(b)) for a, b in zip(starts, lens)])
+                assert torch.equal(ws.rows[h, :rows.numel()].cpu().long(), rows)
+            differ = (sel != sel_ref).any(-1)
+            assert bool((margin[differ] < 1e-4).all())
+            want, _, _ = O.decode_step(ref, q_post=args["q_post"], q_pre=args["q_pre"], pos=pos, k_post=args["k_post"],
+                                       v=args["v"], k_pre=args["k_pre"], temperature=0.1, beta=0.25,
+                                       target_tokens=target, sink=sink, sm_scale=sm_scale, sel=sel)
+            _close_attention(out.view(hq, dim), want, f"decode step {s}")
+        assert torch.equal(arena.suffix_kv.cpu().float(), ref.suffix_kv.float())
+        assert torch.equal(arena.suffix_kpre.cpu().float(), ref.suffix_kpre.float())
+    finally:
+        os.environ.pop("SEMBLO_SINK_TOKENS", None)

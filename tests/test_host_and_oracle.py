@@ -1,0 +1,127 @@
+"""CPU-side checks: the oracle's device-only restatements against an independent float64
+loop, the C-ABI library's exported symbols, and host logic that needs no GPU."""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import semblo_oracle as O
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _problem(sink):
+    data = O.mixture_inputs(length=1536, num_q_heads=4, num_kv_heads=2, head_dim=32, centres=12, seed=4)
+    product = O.routing_normalize(data["k_pre"])
+    index = O.build_flat(product, unit_tokens=16, min_clusters_log2=5, kmeans_sample_size=512, fit_iters=3,
+                         seed=1, sink=sink, page_align=16)
+    O.pack_prompt_kv(index, data["k_post"], data["v"])
+    return data, index
+
+
+@pytest.mark.parametrize("sink", [0, 32])
+def test_prefill_body_against_a_per_query_float64_loop(sink):
+    data, index = _problem(sink)
+    target, local, cs, ce = 128, 64, 1024, 1024 + 63
+    ws = cs - local
+    sizes = O.causal_sizes_at(index, ws - 1)
+    qpos = torch.arange(cs, ce + 1)
+    vectors = O.trivial_router_vectors(data["q_pre"][cs:ce + 1])
+    sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=0.1, beta=0.25, target_tokens=target, sink=sink)
+    if sink:
+        assert bool(sel[..., 0].all())
+    out, natt = O.sparse_chunk_attention(data["q_post"][cs:ce + 1], index, sel, sizes, qpos,
+                                         data["k_post"][ws:ce + 1], data["v"][ws:ce + 1], ws, 32 ** -0.5)
+    k, v = data["k_post"].double(), data["v"].double()
+    for qi in (0, 17, 63):
+        p = cs + qi
+        for h in range(2):
+            # the attended POSITIONS: members of selected clusters below the window, plus the window
+            keys = [pos for pos in range(ws) if bool(sel[qi, h, index.assign[h, pos]])] + list(range(ws, p + 1))
+            assert len(keys) == int(natt[qi, h])
+            for t in range(2):
+                q = data["q_post"][p, h * 2 + t].double()
+                logits = (k[keys, h] @ q) * 32 ** -0.5
+                w = torch.softmax(logits, dim=0)
+                want = w @ v[keys, h]
+                torch.testing.assert_close(out[qi, h * 2 + t], want, atol=1e-9, rtol=1e-9)
+
+
+def test_decode_step_against_a_float64_loop():
+    data, index = _problem(32)
+    a = O.make_arena(capacity=2048, num_clusters=128, num_kv_heads=2, head_dim=32, page_align=16, reserve=256,
+                     kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16, keep_kpre=True)
+    short = O.build_flat(O.routing_normalize(data["k_pre"][:1500]), unit_tokens=16, min_clusters_log2=5,
+                         kmeans_sample_size=512, fit_iters=3, seed=1, sink=32, page_align=16)
+    O.pack_prompt_kv(short, data["k_post"][:1500], data["v"][:1500])
+    O.arena_adopt(a, short)
+    assert int(a.prompt_length_t) == 1500
+    for pos in range(1500, 1504):
+        out, sel, natt = O.decode_step(a, q_post=data["q_post"][pos], q_pre=data["q_pre"][pos], pos=pos,
+                                       k_post=data["k_post"][pos], v=data["v"][pos], k_pre=data["k_pre"][pos],
+                                       temperature=0.1, beta=0.25, target_tokens=128, sink=32, sm_scale=32 ** -0.5)
+        assert bool(sel[:, 0].all())
+        for h in range(2):
+            keys = [p for p in range(1500) if bool(sel[h, short.assign[h, p]])] + list(range(1500, pos + 1))
+            assert len(keys) == int(natt[h])
+            q = data["q_post"][pos, h * 2].double()
+            w = torch.softmax((data["k_post"][keys, h].double() @ q) * 32 ** -0.5, dim=0)
+            torch.testing.assert_close(out[h * 2], w @ data["v"][keys, h].double(), atol=1e-9, rtol=1e-9)
+
+
+def test_flush_moves_the_oldest_suffix_tokens_into_their_clusters():
+    data, index = _problem(0)
+    a = O.make_arena(capacity=2048, num_clusters=128, num_kv_heads=2, head_dim=32, page_align=16, reserve=256,
+                     kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16, keep_kpre=True, packed_capacity=2048 + 256)
+    short = O.build_flat(O.routing_normalize(data["k_pre"][:1400]), unit_tokens=16, min_clusters_log2=5,
+                         kmeans_sample_size=512, fit_iters=3, seed=1, page_align=16)
+    O.pack_prompt_kv(short, data["k_post"][:1400], data["v"][:1400])
+    O.arena_adopt(a, short)
+    for pos in range(1400, 1440):
+        O.suffix_write(a, pos, data["k_post"][pos], data["v"][pos], data["k_pre"][pos])
+    before = int(a.sizes.sum())
+    O.flush_arena(a, 1400, 1424, 16)
+    assert int(a.prompt_length_t) == 1424 and int(a.sizes.sum()) == before + 2 * 24
+    for h in range(2):
+        for c in range(128):
+            lo, n = int(a.indptr[h, c]), int(a.sizes[h, c])
+            pos = a.posting[h, lo:lo + n]
+            assert bool((pos[1:] > pos[:-1]).all())
+            assert torch.equal(a.packed_kv[0, lo:lo + n, h].float(), data["k_post"][pos.long(), h].float())
+
+
+def test_library_exports_every_declared_symbol():
+    from semblo_b200 import _lib
+    header = (ROOT / "include" / "semblo_b200.h").read_text()
+    declared = set(re.findall(r"\b(semblo_[a-z_0-9]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.exported_symbols())
+    handle = ctypes.CDLL(str(_lib.library_path()))
+    for name in declared:
+        assert hasattr(handle, name), name
+    assert _lib.lib().semblo_version() >= 100
+
+
+def test_product_path_refuses_cpu_tensors_and_ablation_flags(monkeypatch):
+    from semblo_b200 import flat_index
+    from semblo_b200.state import ProductPostingIndex, flat_num_clusters
+    with pytest.raises(RuntimeError, match="CUDA"):
+        flat_index.routing_normalize(torch.randn(4, 2, 64).to(torch.bfloat16))
+    monkeypatch.setenv("SEMBLO_ROUTING_NORMALIZE", "half")
+    with pytest.raises(RuntimeError, match="whole-vector"):
+        flat_index.routing_mode()
+    monkeypatch.delenv("SEMBLO_ROUTING_NORMALIZE")
+    assert [flat_num_clusters(n, 64, 7) for n in (8192, 131072, 524288, 1048576)] == [128, 2048, 8192, 16384]
+    monkeypatch.setenv("SEMBLO_FLAT_CLUSTERS", "4096")
+    assert flat_num_clusters(65536, 64, 7) == 4096
+
+
+def test_arena_cluster_count_matches_the_reference_table(golden):
+    from semblo_b200.arena import arena_cluster_count
+    for length, unit, ml, want in golden["cluster_count_table"].tolist():
+        assert arena_cluster_count(length, unit, ml) == want
