@@ -153,7 +153,7 @@ def test_layout_is_bit_identical(dev, length, heads, clusters, align):
 def test_pack_and_snapshot_are_bit_identical(dev):
     from semblo_b200.state import ProductPostingIndex
     from semblo_b200.fused_prefill import CausalSnapshot
-    length, heads, dim, clusters = 3000, 2, 128, 64
+    length, heads, dim, clusters = 2000, 2, 128, 64
     keys = O.mixture_inputs(length=length, num_q_heads=heads, num_kv_heads=heads, head_dim=dim, centres=20,
                             seed=11)["k_pre"]
     product = O.routing_normalize(keys)
@@ -191,7 +191,7 @@ def test_pack_and_snapshot_are_bit_identical(dev):
     view = paged.view(2, n_pages, 16, heads, dim)[:, table.long()].reshape(packed.shape)
     assert torch.equal(view.float(), packed.float())
     snap = CausalSnapshot(index)
-    for p in (0, 17, 999, 1000, 2999):
+    for p in (0, 17, 999, 1000, 1999):
         got = snap.advance(p).cpu()
         want = torch.stack([torch.bincount(assign[h, :p + 1], minlength=clusters) for h in range(heads)]).int()
         assert torch.equal(got, want)
