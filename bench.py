@@ -1,0 +1,582 @@
+"""Benchmark of the semblo sparse-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one full sparse prefill of one full-attention layer over one synthetic prompt:
+routing normalisation, k-means fit (8 iterations) and assignment of the keys, page-aligned
+cluster layout, the cluster-ordered paged K/V copy, then the query-chunk loop (query routing
+vectors, causal snapshot, centroid scoring, budgeted selection, block-sparse attention with
+the exact local window; exact dense attention while the prefix is below four budgets).
+
+Workload at N = 1: 131072-token prompt, 16 query / 4 KV heads, head_dim 256, bf16, partial
+RoPE on 25 % of the dims, keys from a 256-centre Gaussian mixture per head, 64-token blocks,
+budget 4096 tokens + 128-token sink + 512-token local window, 16-token pages behind a seeded
+random page permutation.  At N > 1 every rank runs that step for its own 4-KV-head shard of a
+layer with 4 N KV heads and the per-head outputs are all-gathered with NCCL after each chunk
+(head-parallel, weak scaling); the value then counts token-shards per second.
+
+The JSON line also carries the decode figure (microseconds per step at 524288 tokens) and the
+roofline of the dominant kernel of each.  ``--impl reference`` times the CPU restatement of the
+reference path (torch on the host cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+from types import SimpleNamespace
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "semantic-block-sparse-attention_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_log2=7, target=4096,
+               sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
+DECODE = dict(length=524288, hq=16, hkv=4, dim=256, centres=512, unit=64, min_log2=7, target=4096,
+              sink=128, reserve=1024, steps=256, temperature=0.1, beta=0.25, splits=74)
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return dict(hbm=float(p["hbm_gbs"]), tensor=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                    tensor_burst=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, tensor=1400.0, tensor_burst=1590.0, source="fallback")
+
+
+# ------------------------------------------------------------------------- synthetic inputs
+def mixture_inputs_device(cfg, seed, device, length=None):
+    """Seeded Gaussian-mixture keys/queries (sigma 0.3 around N(0,1) centres), N(0,1) values,
+    partial RoPE (theta 1e7) on the first quarter of the dims.  Same recipe as the oracle's
+    ``mixture_inputs``, generated on the device."""
+    length = length or cfg["length"]
+    hq, hkv, dim = cfg["hq"], cfg["hkv"], cfg["dim"]
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    group = hq // hkv
+    cent = torch.randn(hkv, cfg["centres"], dim, generator=g, device=device)
+    z = torch.randint(0, cfg["centres"], (length,), generator=g, device=device)
+    base = cent[:, z].permute(1, 0, 2)                                   # [L, Hkv, D]
+    k_pre = base + 0.3 * torch.randn(length, hkv, dim, generator=g, device=device)
+    v = torch.randn(length, hkv, dim, generator=g, device=device).to(torch.bfloat16)
+    pos = torch.arange(length, device=device)
+
+    def rope(x):
+        r = dim // 4
+        half = r // 2
+        inv = 1e7 ** (-torch.arange(half, device=device, dtype=torch.float64) / half)
+        ang = pos.double()[:, None] * inv[None]
+        cos, sin = ang.cos().float(), ang.sin().float()
+        shape = [length] + [1] * (x.ndim - 2) + [half]
+        cos, sin = cos.view(shape), sin.view(shape)
+        out = x.clone()
+        x1, x2 = x[..., :half], x[..., half:r]
+        out[..., :half] = x1 * cos - x2 * sin
+        out[..., half:r] = x2 * cos + x1 * sin
+        return out
+
+    k_post = rope(k_pre).to(torch.bfloat16)
+    k_pre = k_pre.to(torch.bfloat16)
+    q_pre = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=device)
+    q_post = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=device)
+    step = 16384
+    for lo in range(0, length, step):
+        hi = min(length, lo + step)
+        qf = base[lo:hi, :, None, :] + 0.3 * torch.randn(hi - lo, hkv, group, dim, generator=g, device=device)
+        qf = qf.reshape(hi - lo, hq, dim)
+        q_pre[lo:hi] = qf.to(torch.bfloat16)
+        r = dim // 4
+        half = r // 2
+        inv = 1e7 ** (-torch.arange(half, device=device, dtype=torch.float64) / half)
+        ang = pos[lo:hi].double()[:, None] * inv[None]
+        cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+        out = qf.clone()
+        out[..., :half] = qf[..., :half] * cos - qf[..., half:r] * sin
+        out[..., half:r] = qf[..., half:r] * cos + qf[..., :half] * sin
+        q_post[lo:hi] = out.to(torch.bfloat16)
+    return dict(q_pre=q_pre, q_post=q_post, k_pre=k_pre, k_post=k_post, v=v)
+
+
+# ------------------------------------------------------------------------- the prefill step
+class PrefillStep:
+    """The reference's prompt forward of one sparse layer (model.py:1169-1269: ingest, then the
+    query-chunk loop of _run_product_attention 856-1008) on the mirrored entry points."""
+
+    def __init__(self, cfg, device, world=1):
+        from semblo_b200 import _lib
+        self.cfg, self.device, self.world = cfg, device, world
+        self.page_table = None
+        self.attended = torch.zeros(1, dtype=torch.int64, device=device)
+        self.attn_events = []
+        self.time_attention = False
+        self.gathered = None
+        self._lib = _lib
+
+    def run(self, x, out):
+        from semblo_b200.flat_index import routing_normalize
+        from semblo_b200.fused_prefill import CausalSnapshot, fused_chunk_attention
+        from semblo_b200.state import ProductPostingIndex
+        from semblo_b200.trivial_router import trivial_router_vectors
+        cfg, dev = self.cfg, self.device
+        length, hq, dim, chunk = cfg["length"], cfg["hq"], cfg["dim"], cfg["chunk"]
+        product = routing_normalize(x["k_pre"])
+        index = ProductPostingIndex.build(product, self.positions, kmeans_sample_size=8192, codebook_seed=0,
+                                          flat_unit_tokens=cfg["unit"], flat_min_clusters_log2=cfg["min_log2"],
+                                          page_align=cfg["page"])
+        width = int(index.posting_positions.shape[1])
+        n_pages = (width + (-width) % 256) // 16
+        if self.page_table is None or self.page_table.numel() != n_pages:
+            g = torch.Generator(device=dev)
+            g.manual_seed(1234)
+            self.page_table = torch.randperm(n_pages, generator=g, device=dev).to(torch.int32)
+        index.pack_prompt_kv(x["k_post"], x["v"], page_table=self.page_table)
+        index.original_kv = (x["k_post"], x["v"])
+        snap = CausalSnapshot(index)
+        sm_scale = dim ** -0.5
+        for cs in range(0, length, chunk):
+            ce = min(length, cs + chunk) - 1
+            n = ce - cs + 1
+            qv = trivial_router_vectors(x["q_pre"][cs:ce + 1])
+            state = SimpleNamespace(vectors=qv.view(1, n, hq, 1, dim))
+            if self.time_attention:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self._pending = (e0, e1)
+            fused_chunk_attention(x["q_post"][cs:ce + 1], state, index, self.positions32[cs:ce + 1], snap, cs, ce,
+                                  temperature=cfg["temperature"], beta=cfg["beta"], target_tokens=cfg["target"],
+                                  sm_scale=sm_scale, out=out[cs:ce + 1], attended=self.attended,
+                                  _timer=self._timer if self.time_attention else None)
+            if self.world > 1:
+                import torch.distributed as dist
+                if self.gathered is None:
+                    self.gathered = torch.empty(self.world, chunk, hq, dim, dtype=torch.bfloat16, device=dev)
+                if n != chunk:
+                    raise RuntimeError("the prompt length must be a multiple of the query chunk")
+                dist.all_gather_into_tensor(self.gathered, out[cs:ce + 1])
+        return index
+
+    def _timer(self, phase):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.attn_events.append(ev)
+
+    def prepare(self):
+        L = self.cfg["length"]
+        self.positions = torch.arange(L, device=self.device)
+        self.positions32 = self.positions.to(torch.int32)
+
+
+def set_env(cfg):
+    os.environ["SEMBLO_FLAT_UNIT_TOKENS"] = str(cfg["unit"])
+    os.environ["SEMBLO_FA3_ALIGN"] = "16"
+    os.environ["SEMBLO_SINK_TOKENS"] = str(cfg["sink"])
+    if "local" in cfg:
+        os.environ["SEMBLO_FA3_LOCAL"] = str(cfg["local"])
+
+
+class ClockSampler:
+    """nvidia-smi SM clock and throttle reasons during the timed region."""
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(n)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        s = sorted(self.samples)
+        # the median over the samples taken while the GPU was busy (upper half of the readings)
+        busy = s[len(s) // 2:] if s else []
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------- launch accounting
+def kernel_launches(calls: dict, clusters: int) -> int:
+    passes = 1 if clusters <= 256 else 2
+    per_call = {"semblo_routing_normalize": 1, "semblo_gather_rows": 1, "semblo_assign_argmax": 1,
+                "semblo_cluster_counts": 2, "semblo_kmeans_update": 3 * passes + 1, "semblo_split_descriptor": 1,
+                "semblo_build_layout": 2 + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
+                "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_sparse_prefill": 1,
+                "semblo_decode_step": 3}
+    return sum(per_call.get(k, 0) * v for k, v in calls.items())
+
+
+# ------------------------------------------------------------------------- decode measurement
+def decode_measure(device, pk):
+    """Decode at 524288 tokens: build the index once, adopt it into the arena, then time decode
+    steps appended through the suffix store (eager launches and a captured CUDA graph)."""
+    from semblo_b200 import _lib
+    from semblo_b200.arena import DecodeArena
+    from semblo_b200.fused_decode import fused_decode_step
+    from semblo_b200.flat_index import routing_normalize
+    from semblo_b200.state import ProductPostingIndex, flat_num_clusters
+    cfg = DECODE
+    set_env(cfg)
+    L, hq, hkv, dim = cfg["length"], cfg["hq"], cfg["hkv"], cfg["dim"]
+    steps = cfg["steps"]
+    x = mixture_inputs_device(cfg, 3000, device, length=L + steps)
+    positions = torch.arange(L, device=device)
+    product = routing_normalize(x["k_pre"][:L])
+    index = ProductPostingIndex.build(product, positions, kmeans_sample_size=8192, codebook_seed=0,
+                                      flat_unit_tokens=cfg["unit"], flat_min_clusters_log2=cfg["min_log2"], page_align=16)
+    index.pack_prompt_kv(x["k_post"][:L].contiguous(), x["v"][:L].contiguous())
+    clusters = flat_num_clusters(L, cfg["unit"], cfg["min_log2"])
+    arena = DecodeArena(capacity=L, num_kv_heads=hkv, head_dim=dim, num_clusters=clusters, page_align=16,
+                        device=device, reserve=cfg["reserve"], keep_kpre=True)
+    arena.adopt(index)
+    del index, product
+    layer = SimpleNamespace(num_heads=hq, num_kv_heads=hkv, head_dim=dim)
+    out = torch.empty(1, hq * dim, dtype=torch.bfloat16, device=device)
+    pos_t = torch.zeros(1, dtype=torch.int64, device=device)
+    bufs = {k: torch.empty(1, *x[k].shape[1:], dtype=torch.bfloat16, device=device) for k in x}
+    sm_scale = dim ** -0.5
+
+    def step():
+        fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t,
+                          k_post=bufs["k_post"], v_states=bufs["v"], k_pre=bufs["k_pre"], output=out,
+                          temperature=cfg["temperature"], beta=cfg["beta"], target_tokens=cfg["target"],
+                          sm_scale=sm_scale, num_splits=cfg["splits"])
+
+    def load(s):
+        for k in bufs:
+            bufs[k].copy_(x[k][L + s:L + s + 1])
+        pos_t.fill_(L + s)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for s in range(4):
+        load(s)
+        step()
+    torch.cuda.synchronize()
+    _lib.status_for(device).raise_if_set()
+    # eager, L2 flushed before every step
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s in range(steps):
+        load(s)
+        flush.zero_()
+        ev[s][0].record()
+        step()
+        ev[s][1].record()
+    torch.cuda.synchronize()
+    eager_us = sorted(a.elapsed_time(b) * 1e3 for a, b in ev)
+    ws = arena.fused_decode_ws
+    n_rows = int(ws.rtokens.sum().item())
+    n_suffix = hkv * steps                      # at the last step
+    # graph replay
+    graph = torch.cuda.CUDAGraph()
+    load(steps - 1)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        step()
+    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s in range(steps):
+        load(s)
+        flush.zero_()
+        gev[s][0].record()
+        graph.replay()
+        gev[s][1].record()
+    torch.cuda.synchronize()
+    _lib.status_for(device).raise_if_set()
+    graph_us = sorted(a.elapsed_time(b) * 1e3 for a, b in gev)
+    # attend kernel alone (stage mask 4) for its own roofline
+    aev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(64)]
+    for a, b in aev:
+        flush.zero_()
+        a.record()
+        fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t, k_post=None,
+                          v_states=None, k_pre=None, output=out, temperature=cfg["temperature"], beta=cfg["beta"],
+                          target_tokens=cfg["target"], sm_scale=sm_scale, num_splits=cfg["splits"], stage_mask=4)
+        b.record()
+    torch.cuda.synchronize()
+    attend_us = sorted(a.elapsed_time(b) * 1e3 for a, b in aev)
+    med = lambda v: v[len(v) // 2]
+    gathered = (n_rows + n_suffix) * dim * 2 * 2 + n_rows * 4
+    codebook = hkv * clusters * dim * 2 + hkv * clusters * 8
+    return {
+        "metric": "decode_us_per_step", "context": L, "clusters": clusters, "steps": steps,
+        "eager_us": med(eager_us), "graph_us": med(graph_us), "attend_kernel_us": med(attend_us),
+        "selected_rows": n_rows, "gathered_bytes": gathered, "codebook_bytes": codebook,
+        "roofline_attend": {"bound": "hbm", "achieved": gathered / (med(attend_us) * 1e-6) / 1e9, "peak": pk["hbm"],
+                            "unit": "GB/s", "frac": gathered / (med(attend_us) * 1e-6) / 1e9 / pk["hbm"],
+                            "traffic": None},
+        "roofline_step": {"bound": "hbm", "achieved": (gathered + codebook) / (med(graph_us) * 1e-6) / 1e9,
+                          "peak": pk["hbm"], "unit": "GB/s",
+                          "frac": (gathered + codebook) / (med(graph_us) * 1e-6) / 1e9 / pk["hbm"], "traffic": None},
+    }
+
+
+# ------------------------------------------------------------------------- CPU baseline
+def cpu_reference_sample(cfg, threads=None):
+    """The CPU restatement of the reference path on a bounded sample of the prefill workload,
+    extrapolated to tokens per second of the whole 131072-token step.  Returns (tok/s, text)."""
+    from oracle import semblo_oracle as O
+    if threads:
+        torch.set_num_threads(threads)
+    L, hq, hkv, dim = cfg["length"], cfg["hq"], cfg["hkv"], cfg["dim"]
+    clusters = O.cluster_count(L, cfg["unit"], cfg["min_log2"])
+    t_all = time.perf_counter()
+    data = O.mixture_inputs(length=L, num_q_heads=hq // hkv, num_kv_heads=1, head_dim=dim, centres=cfg["centres"], seed=7)
+    # index build of ONE KV head with ONE k-means iteration timed, scaled to 8 iterations x Hkv heads
+    t0 = time.perf_counter()
+    space = O.routing_space(O.routing_normalize(data["k_pre"][:, 0]))
+    t_norm = time.perf_counter() - t0
+    gen = torch.Generator().manual_seed(0)
+    fit_n = min(L - cfg["sink"], max(8192, 32 * clusters))
+    sample = space[cfg["sink"]:][torch.randperm(L - cfg["sink"], generator=gen)[:fit_n]]
+    cents = sample[torch.randperm(fit_n, generator=gen)[:clusters - 1]].clone()
+    t0 = time.perf_counter()
+    assign_s = O.argmax_sim(sample, cents)
+    cents, _ = O.kmeans_update(sample, assign_s, clusters - 1, torch.randperm(fit_n, generator=gen))
+    t_iter = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    index = O.build_flat(O.routing_normalize(data["k_pre"][:, :1]), unit_tokens=cfg["unit"],
+                         min_clusters_log2=cfg["min_log2"], sink=cfg["sink"], page_align=16, centroids=[cents])
+    O.pack_prompt_kv(index, data["k_post"][:, :1], data["v"][:, :1])
+    t_layout = time.perf_counter() - t0
+    build_s = hkv * (t_norm + 8 * t_iter + t_layout)
+    # one dense and one sparse chunk, 64 queries each (all G heads of the one KV head)
+    nq = 64
+    g = hq // hkv
+    sm = dim ** -0.5
+    cs_d = cfg["chunk"]
+    qpos = torch.arange(cs_d, cs_d + nq)
+    t0 = time.perf_counter()
+    O.dense_causal_attention(data["q_post"][cs_d:cs_d + nq, :g], data["k_post"][:cs_d + nq, :1], data["v"][:cs_d + nq, :1],
+                             qpos, sm, dtype=torch.float32)
+    t_dense = time.perf_counter() - t0
+    dense_pairs_sample = float((qpos + 1).sum())
+    dense_chunks = [c for c in range(0, L, cfg["chunk"]) if O.chunk_plan(c, cfg["target"], cfg["local"]) == 0]
+    dense_pairs = sum(float((torch.arange(c, c + cfg["chunk"]) + 1).sum()) for c in dense_chunks)
+    dense_s = hkv * t_dense * dense_pairs / dense_pairs_sample
+    cs = 9 * cfg["chunk"]
+    ws = cs - cfg["local"]
+    t0 = time.perf_counter()
+    sizes = O.causal_sizes_at(index, ws - 1)
+    vectors = O.trivial_router_vectors(data["q_pre"][cs:cs + nq, :g])
+    sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=cfg["temperature"], beta=cfg["beta"],
+                            target_tokens=cfg["target"], sink=cfg["sink"])
+    t_select = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    O.sparse_chunk_attention_gather(data["q_post"][cs:cs + nq, :g], index, sel, sizes, torch.arange(cs, cs + nq),
+                                    data["k_post"][ws:cs + nq, :1], data["v"][ws:cs + nq, :1], ws, sm)
+    t_sparse = time.perf_counter() - t0
+    n_sparse = (L // cfg["chunk"]) - len(dense_chunks)
+    # within a chunk the window grows from `local` to `local + chunk` keys; the sample sits at its start
+    window_scale = (cfg["target"] + cfg["local"] + cfg["chunk"] / 2) / (cfg["target"] + cfg["local"] + nq / 2)
+    sparse_s = hkv * n_sparse * (cfg["chunk"] / nq) * (t_select + t_sparse * window_scale)
+    total = build_s + dense_s + sparse_s
+    text = (f"1 of {hkv} KV heads: normalise + 1 of 8 k-means iterations + assignment/layout/pack, {nq} queries of a "
+            f"dense chunk and {nq} of a sparse chunk; extrapolated to the whole step "
+            f"(build {build_s:.1f}s + dense {dense_s:.1f}s + sparse {sparse_s:.1f}s); "
+            f"sample wall {time.perf_counter() - t_all:.1f}s")
+    return L / total, text
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = PREFILL
+    threads = os.cpu_count() or 1
+    values = []
+    text = ""
+    for i in range(args.warmup + args.steps):
+        v, text = cpu_reference_sample(cfg, threads)
+        if i >= args.warmup:
+            values.append(v)
+    value = sum(values) / len(values)
+    line = {"impl": "reference", "metric": "sparse_prefill_tok_per_s", "value": value, "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": cfg["length"] / value * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 values, fp32 math", "data": "synthetic",
+            "config": workload_config(1),
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": text},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(world):
+    c = PREFILL
+    return {"workload": "single-layer block-sparse prefill, 131072-token prompt, GQA 16q/4kv, head_dim 256, bf16, "
+                        "partial RoPE 25%, 256-centre mixture keys, 64-token blocks (2048 clusters), budget 4096 + "
+                        "sink 128 + local window 512, query chunk 8192, 16-token pages in a random permutation",
+            "tokens": c["length"], "kv_heads_per_gpu": c["hkv"], "parallelism": f"head-parallel x{world}",
+            "l2": "inputs larger than L2 (K/V 0.8 GB, Q 2.1 GB per step)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--length", type=int, default=0, help="override the prompt length (profiling on a small case)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    from semblo_b200 import _lib
+    _lib.lib()
+    pk = peaks()
+    cfg = dict(PREFILL)
+    if args.length:
+        cfg["length"] = args.length
+    set_env(cfg)
+    x = mixture_inputs_device(cfg, 2000 + rank, device)
+    step = PrefillStep(cfg, device, world)
+    step.prepare()
+    out = torch.empty(cfg["length"], cfg["hq"], cfg["dim"], dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step.run(x, out)
+    barrier()
+    _lib.status_for(device).raise_if_set()
+    # ---- device-resident timing
+    _lib.CALLS.clear()
+    step.attended.zero_()
+    step.time_attention = True
+    step.attn_events = []
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        index = step.run(x, out)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+    _lib.status_for(device).raise_if_set()
+    calls = dict(_lib.CALLS)
+    clusters = int(index.num_buckets)
+    launches = kernel_launches(calls, clusters) // args.steps
+    attended = int(step.attended.item()) // args.steps
+    evs = step.attn_events
+    attn_ms = sum(evs[i].elapsed_time(evs[i + 1]) for i in range(0, len(evs), 2)) / args.steps
+    step.time_attention = False
+    g = cfg["hq"] // cfg["hkv"]
+    flops = 4.0 * cfg["dim"] * g * attended
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # ---- end to end: host buffers in, host result out, through the same public entry points
+    host = {k: v.cpu().pin_memory() for k, v in x.items()}
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    dev_in = {k: torch.empty_like(v) for k, v in x.items()}
+
+    def e2e_step():
+        for k in host:
+            dev_in[k].copy_(host[k], non_blocking=True)
+        step.run(dev_in, out)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+    del host, dev_in, out_host
+    if rank != 0:
+        return
+    tokens = cfg["length"] * world
+    line = {
+        "metric": "sparse_prefill_tok_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "roofline": {"bound": "tensor", "kernel": "sparse_prefill_kernel<256,4>", "achieved": flops / (attn_ms * 1e-3) / 1e12,
+                     "peak": pk["tensor"], "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"],
+                     "traffic": None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
+                     "kernel_ms_per_step": attn_ms, "attended_keys_per_step": attended,
+                     "flops_per_step": flops},
+    }
+    if world == 1 and not args.no_decode and not args.length:
+        del x, out, step, index
+        torch.cuda.empty_cache()
+        try:
+            line["decode"] = decode_measure(device, pk)
+        except Exception as exc:                      # keep the headline if the second workload fails
+            line["decode"] = {"error": repr(exc)}
+    if world == 1 and not args.no_cpu:
+        v, text = cpu_reference_sample(PREFILL, os.cpu_count() or 1)
+        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": text}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

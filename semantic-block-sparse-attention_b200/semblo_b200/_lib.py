@@ -13,6 +13,27 @@ import torch
 
 _LIB_PATH = Path(__file__).resolve().parent.parent / "libsemblo_b200.so"
 _lib = None
+CALLS: dict = {}          # entry point -> number of calls (the benchmark's launch accounting)
+
+
+class _Counting:
+    """The loaded library with a per-entry-point call counter."""
+
+    def __init__(self, handle) -> None:
+        self._handle = handle
+        self._wrapped: dict = {}
+
+    def __getattr__(self, name):
+        fn = self._wrapped.get(name)
+        if fn is None:
+            raw = getattr(self._handle, name)
+
+            def fn(*args, _raw=raw, _name=name):
+                CALLS[_name] = CALLS.get(_name, 0) + 1
+                return _raw(*args)
+
+            self._wrapped[name] = fn
+        return fn
 
 I32P = c_void_p
 _SIGNATURES = {
@@ -45,7 +66,7 @@ def exported_symbols() -> list[str]:
     return list(_SIGNATURES)
 
 
-def lib() -> ctypes.CDLL:
+def lib():
     """The loaded library.  Raises RuntimeError if it has not been built."""
     global _lib
     if _lib is None:
@@ -58,7 +79,7 @@ def lib() -> ctypes.CDLL:
             fn = getattr(handle, name)
             fn.restype = res
             fn.argtypes = args
-        _lib = handle
+        _lib = _Counting(handle)
     return _lib
 
 

@@ -108,7 +108,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                           snapshot_state: CausalSnapshot, chunk_start: int, chunk_end: int, *,
                           temperature: float, beta: float, target_tokens: int, queries_per_block: int = 32,
                           sm_scale: float, iters: int = 16, dense_prefix_x: int = 4, out=None,
-                          attended=None, **unused) -> torch.Tensor:
+                          attended=None, _timer=None, **unused) -> torch.Tensor:
     """Attention of one query chunk (fused_prefill.py:219-482, default path).
 
     ``query_state.vectors`` [1, Q, Hq, 1, D] routing vectors; ``index.original_kv`` must hold
@@ -124,9 +124,14 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                            "(index.original_kv)")
     k_pos, v_pos = original_kv
     if wstart == 0:
-        return sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
-                                        ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
-                                        sm_scale=sm_scale, out=out, attended=attended)
+        if _timer:
+            _timer("start")
+        res = sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
+                                       ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
+                                       sm_scale=sm_scale, out=out, attended=attended)
+        if _timer:
+            _timer("stop")
+        return res
     base = snapshot_state.advance(wstart - 1)
     sink = _fitted_sink_tokens()
     if sink:
@@ -151,8 +156,13 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                                          beta=beta, target_tokens=select_target, iters=iters,
                                          qmask=snap.qmask[:q_count], score=snap.score[:q_count],
                                          force_sink=bool(sink))
-    return sparse_prefill_attention(
+    if _timer:
+        _timer("start")
+    res = sparse_prefill_attention(
         q_chunk, q_positions, packed_kv=index.packed_kv, page_table=getattr(index, "kv_page_table", None),
         qmask=qmask, causal_sizes=base, indptr=index.bucket_indptr, ordered_k=k_pos[wstart:chunk_end + 1],
         ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart, sm_scale=sm_scale,
         out=out, attended=attended)
+    if _timer:
+        _timer("stop")
+    return res

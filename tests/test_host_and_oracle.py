@@ -125,3 +125,18 @@ def test_arena_cluster_count_matches_the_reference_table(golden):
     from semblo_b200.arena import arena_cluster_count
     for length, unit, ml, want in golden["cluster_count_table"].tolist():
         assert arena_cluster_count(length, unit, ml) == want
+
+
+def test_gather_form_of_the_prefill_body_agrees_with_the_masked_form():
+    data, index = _problem(32)
+    cs, ce, ws = 1024, 1024 + 15, 960
+    sizes = O.causal_sizes_at(index, ws - 1)
+    qpos = torch.arange(cs, ce + 1)
+    sel = O.select_clusters(O.trivial_router_vectors(data["q_pre"][cs:ce + 1]), index.codebooks, sizes,
+                            temperature=0.1, beta=0.25, target_tokens=128, sink=32)
+    want, _ = O.sparse_chunk_attention(data["q_post"][cs:ce + 1], index, sel, sizes, qpos, data["k_post"][ws:ce + 1],
+                                       data["v"][ws:ce + 1], ws, 32 ** -0.5)
+    got = O.sparse_chunk_attention_gather(data["q_post"][cs:ce + 1], index, sel, sizes, qpos,
+                                          data["k_post"][ws:ce + 1], data["v"][ws:ce + 1], ws, 32 ** -0.5,
+                                          dtype=torch.float64)
+    torch.testing.assert_close(got, want, atol=1e-9, rtol=1e-9)
