@@ -114,7 +114,15 @@ int semblo_score_clusters(const void* vectors_bf16, int num_queries, int num_q_h
 int semblo_select_clusters(const float* score, const int32_t* select_sizes, int num_queries,
                            int num_kv_heads, int num_clusters, int target_tokens, int iters,
                            int force_sink, int32_t* qmask, int32_t* counts, int32_t* tokens,
-                           void* stream);
+                           int32_t* top1 /* [Hkv, Q] best-scoring cluster, or NULL */, void* stream);
+
+/* Stable arg-sort of small integer keys (keys [heads, n] in [0, max_key), max_key <= 65536):
+ * order [heads, n].  Used to put queries with the same best-scoring cluster into the same
+ * attention tile; the reference has no counterpart (its kv-outer body gathers queries per
+ * cluster instead, semblo/vllm_plugin/kv_outer.py:254-329).
+ * workspace >= semblo_layout_workspace_bytes(n, heads). */
+int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key, int32_t* order,
+                        void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---- prefill attention ---------------------------------------------------------- */
 
@@ -137,6 +145,21 @@ int semblo_sparse_prefill(const void* q, int num_queries, int num_q_heads, int n
                           const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
                           int ordered_pos0, int local_start, float sm_scale, void* out, float* lse,
                           unsigned long long* attended, int32_t* status, void* stream);
+
+/* The sparse part of semblo/vllm_plugin/kv_outer.py:482-816 with row-granular reads: for every
+ * query, attention over rows [indptr[c], indptr[c] + causal_sizes[c]) of the clusters set in
+ * its qmask, gathered row by row from the cluster-ordered K/V (packed_k / packed_v
+ * [rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
+ * ([Hkv, Q], optional).  merge = 1: `out` / `lse` hold the window partial written by
+ * semblo_sparse_prefill (normalised output, natural-log LSE) and receive the LSE-merged
+ * result (kv_outer.py:203-227); merge = 0: the sparse result alone. */
+int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
+                                 int head_dim, const int32_t* q_order, const void* packed_k,
+                                 const void* packed_v, const int32_t* page_table,
+                                 const int32_t* qmask, const int32_t* causal_sizes,
+                                 const int32_t* indptr, int num_clusters, float sm_scale, int merge,
+                                 void* out, float* lse, unsigned long long* attended,
+                                 int32_t* status, void* stream);
 
 /* ---- decode ----------------------------------------------------------------------- */
 

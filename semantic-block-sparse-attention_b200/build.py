@@ -14,7 +14,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libsemblo_b200.so"
-SOURCES = ["host_common.cu", "index_build.cu", "select.cu", "prefill.cu", "decode.cu"]
+SOURCES = ["host_common.cu", "index_build.cu", "select.cu", "prefill.cu", "prefill_sparse.cu", "decode.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "--expt-relaxed-constexpr", "--extended-lambda", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

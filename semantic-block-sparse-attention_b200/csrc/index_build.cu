@@ -702,3 +702,15 @@ extern "C" int semblo_snapshot_advance(const int32_t* assign, int64_t head_strid
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
+
+extern "C" int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key,
+                                   int32_t* order, void* workspace, int64_t workspace_bytes,
+                                   void* stream) {
+  SEMBLO_REQUIRE(max_key > 0 && max_key <= 65536, "keys must be below 65536");
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, heads), "workspace too small");
+  if (n == 0) return 0;
+  int32_t* ws = (int32_t*)workspace;
+  const int64_t hn = (int64_t)heads * n;
+  return sort_by_cluster(keys, n, n, heads, max_key, order, ws, ws + hn, ws + 2 * hn, ws + 3 * hn,
+                         (cudaStream_t)stream);
+}

@@ -236,7 +236,8 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
                               float target_tokens, int iters, int force_sink,
                               int32_t* __restrict__ qmask,          // [Q, Hkv, C/32]
                               int32_t* __restrict__ counts,         // [Q, Hkv] or null
-                              int32_t* __restrict__ tokens) {       // [Q, Hkv] or null
+                              int32_t* __restrict__ tokens,         // [Q, Hkv] or null
+                              int32_t* __restrict__ top1) {         // [Hkv, Q] or null: best-scoring cluster
   extern __shared__ float sm[];
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -249,14 +250,24 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
   if (q >= num_queries) return;
   const float* row = score + ((int64_t)q * num_kv_heads + h) * num_clusters;
   float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  int arg = 0;
   for (int c = lane; c < num_clusters; c += 32) {
     const float s = row[c], n = s_size[c];
     s_score[c] = s;
+    if (s > mx) arg = c;
     mx = fmaxf(mx, s);
     mn = fminf(mn, n > 0.f ? s : 3.4e38f);
     tot += n > 0.f ? n : 0.f;
   }
   __syncwarp();
+  if (top1) {
+    // lowest cluster id among the maxima: a grouping key for the attention tiles
+    const float best = warp_max(mx);
+    int cand = mx == best ? arg : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+    if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
+  }
   float hi = warp_max(mx) + 1e-6f;
   float lo = warp_min(mn) - 1e-6f;
   lo = fminf(lo, hi - 1e-5f);
@@ -347,7 +358,7 @@ extern "C" int semblo_score_clusters(const void* vectors_bf16, int num_queries, 
 extern "C" int semblo_select_clusters(const float* score, const int32_t* select_sizes,
                                       int num_queries, int num_kv_heads, int num_clusters,
                                       int target_tokens, int iters, int force_sink, int32_t* qmask,
-                                      int32_t* counts, int32_t* tokens, void* stream) {
+                                      int32_t* counts, int32_t* tokens, int32_t* top1, void* stream) {
   SEMBLO_REQUIRE(num_clusters % 32 == 0, "cluster count %d must be a multiple of 32", num_clusters);
   if (num_queries == 0) return 0;
   int warps = 8;
@@ -358,7 +369,7 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   dim3 grid((unsigned)ceil_div(num_queries, warps), num_kv_heads);
   select_kernel<<<grid, warps * 32, smem, (cudaStream_t)stream>>>(
       score, select_sizes, num_queries, num_kv_heads, num_clusters, (float)target_tokens, iters,
-      force_sink, qmask, counts, tokens);
+      force_sink, qmask, counts, tokens, top1);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

@@ -50,7 +50,9 @@ _SIGNATURES = {
     "semblo_pack_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "semblo_snapshot_advance": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "semblo_score_clusters": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p]),
-    "semblo_select_clusters": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_select_clusters": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_argsort_keys": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p]),
+    "semblo_sparse_prefill_gather": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_sparse_prefill": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_decode_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int64, c_int]),
     "semblo_decode_workspace_offsets": (c_int, [c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p]),

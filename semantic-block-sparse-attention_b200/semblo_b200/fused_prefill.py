@@ -32,6 +32,7 @@ class CausalSnapshot:
         self.qmask = None
         self.score = None
         self.select_sizes = None
+        self.top1 = self.order = self.lse = self.sort_ws = None
 
     def advance(self, last_pos: int) -> torch.Tensor:
         hi = min(int(last_pos) + 1, self.length)
@@ -47,7 +48,7 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
                               temperature: float, beta: float, target_tokens: int, iters: int = 16,
                               qmask: torch.Tensor | None = None, score: torch.Tensor | None = None,
                               force_sink: bool = False, counts: torch.Tensor | None = None,
-                              tokens: torch.Tensor | None = None):
+                              tokens: torch.Tensor | None = None, top1: torch.Tensor | None = None):
     """Scores + bisected threshold -> per-query packed bitmask [Q, Hkv, C/32].
 
     vectors [Q, Hq, D] bf16 routing vectors; select_sizes [Hkv, C] int32 (one snapshot for
@@ -66,7 +67,7 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
                                       ptr(score), ptr(status.word), stream_ptr()))
     check(lib().semblo_select_clusters(ptr(score), ptr(select_sizes), q_count, num_kv_heads, num_clusters,
                                        int(target_tokens), int(iters), 1 if force_sink else 0, ptr(qmask),
-                                       ptr(counts), ptr(tokens), stream_ptr()))
+                                       ptr(counts), ptr(tokens), ptr(top1), stream_ptr()))
     return qmask, score
 
 
@@ -101,6 +102,38 @@ def sparse_prefill_attention(q: torch.Tensor, q_positions: torch.Tensor, *, pack
         ptr(pk), ptr(pv), packed_rows, ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr), num_clusters,
         ptr(ordered_k), ptr(ordered_v), 0 if ordered_k is None else int(ordered_k.shape[0]), int(ordered_pos0),
         int(local_start), float(sm_scale), ptr(out), ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
+    return out
+
+
+def argsort_keys(keys: torch.Tensor, max_key: int, *, out: torch.Tensor | None = None,
+                 workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Stable arg-sort of int32 keys [heads, n] in [0, max_key)."""
+    require_cuda(keys)
+    heads, n = keys.shape
+    if out is None:
+        out = torch.empty_like(keys)
+    need = int(lib().semblo_layout_workspace_bytes(n, heads))
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=keys.device)
+    check(lib().semblo_argsort_keys(ptr(keys), n, heads, int(max_key), ptr(out), ptr(workspace),
+                                    workspace.numel(), stream_ptr()))
+    return out
+
+
+def sparse_gather_attention(q: torch.Tensor, *, packed_kv: torch.Tensor, qmask: torch.Tensor,
+                            causal_sizes: torch.Tensor, indptr: torch.Tensor, sm_scale: float,
+                            out: torch.Tensor, lse: torch.Tensor | None, merge: bool, page_table=None,
+                            q_order=None, attended=None) -> torch.Tensor:
+    """One launch of the row-gather sparse kernel (semblo_sparse_prefill_gather)."""
+    require_cuda(q, packed_kv, qmask)
+    q_count, num_q_heads, head_dim = q.shape
+    q = q if q.is_contiguous() else q.contiguous()
+    status = _lib.status_for(q.device)
+    check(lib().semblo_sparse_prefill_gather(
+        ptr(q), q_count, num_q_heads, int(packed_kv.shape[2]), head_dim, ptr(q_order), ptr(packed_kv[0]),
+        ptr(packed_kv[1]), ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr),
+        int(causal_sizes.shape[1]), float(sm_scale), 1 if merge else 0, ptr(out), ptr(lse), ptr(attended),
+        ptr(status.word), stream_ptr()))
     return out
 
 
@@ -145,24 +178,40 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         select_sizes, select_target = base, int(target_tokens)
     vectors = query_state.vectors[0]
     vectors = vectors.reshape(vectors.shape[0], vectors.shape[1], -1)
-    q_count = q_chunk.shape[0]
+    q_count, num_q_heads = q_chunk.shape[0], q_chunk.shape[1]
     snap = snapshot_state
+    dev = q_chunk.device
     if snap.qmask is None or snap.qmask.shape[0] < q_count:
-        snap.qmask = torch.empty(q_count, index.num_kv_heads, index.num_buckets // 32, dtype=torch.int32,
-                                 device=q_chunk.device)
-        snap.score = torch.empty(q_count, index.num_kv_heads, index.num_buckets, dtype=torch.float32,
-                                 device=q_chunk.device)
+        hkv, c = index.num_kv_heads, index.num_buckets
+        snap.qmask = torch.empty(q_count, hkv, c // 32, dtype=torch.int32, device=dev)
+        snap.score = torch.empty(q_count, hkv, c, dtype=torch.float32, device=dev)
+        snap.top1 = torch.empty(hkv, q_count, dtype=torch.int32, device=dev)
+        snap.order = torch.empty(hkv, q_count, dtype=torch.int32, device=dev)
+        snap.lse = torch.empty(q_count, num_q_heads, dtype=torch.float32, device=dev)
+        snap.sort_ws = torch.empty(int(lib().semblo_layout_workspace_bytes(q_count, hkv)), dtype=torch.uint8,
+                                   device=dev)
+    full = q_count == snap.qmask.shape[0]
+    top1 = snap.top1 if full else torch.empty(index.num_kv_heads, q_count, dtype=torch.int32, device=dev)
+    order = snap.order if full else torch.empty_like(top1)
     qmask, _ = theta_select_bitmask_flat(vectors, index.codebooks, select_sizes, temperature=temperature,
                                          beta=beta, target_tokens=select_target, iters=iters,
                                          qmask=snap.qmask[:q_count], score=snap.score[:q_count],
-                                         force_sink=bool(sink))
+                                         force_sink=bool(sink), top1=top1)
+    # queries with the same best-scoring cluster select nearly the same clusters: tiles are
+    # formed in that order so a tile's union of selections stays close to a single selection
+    argsort_keys(top1, index.num_buckets, out=order, workspace=snap.sort_ws)
+    if out is None:
+        out = torch.empty_like(q_chunk)
+    lse = snap.lse[:q_count]
     if _timer:
         _timer("start")
-    res = sparse_prefill_attention(
-        q_chunk, q_positions, packed_kv=index.packed_kv, page_table=getattr(index, "kv_page_table", None),
-        qmask=qmask, causal_sizes=base, indptr=index.bucket_indptr, ordered_k=k_pos[wstart:chunk_end + 1],
-        ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart, sm_scale=sm_scale,
-        out=out, attended=attended)
+    # the exact window [wstart, q] in position order, then the selected clusters merged into it
+    sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[wstart:chunk_end + 1],
+                             ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart,
+                             sm_scale=sm_scale, out=out, lse=lse, attended=attended)
+    sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
+                            indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
+                            page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended)
     if _timer:
         _timer("stop")
-    return res
+    return out

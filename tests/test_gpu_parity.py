@@ -236,8 +236,10 @@ def test_scores_and_selection(dev, dim, hq, hkv, sink):
     tokens = torch.empty(333, hkv, dtype=torch.int32, device=dev)
     qmask, score = theta_select_bitmask_flat(vectors.to(dev), index.codebooks.to(dev), sel_sizes.to(dev),
                                              temperature=0.1, beta=0.25, target_tokens=sel_target,
-                                             force_sink=bool(sink), counts=counts, tokens=tokens)
+                                             force_sink=bool(sink), counts=counts, tokens=tokens,
+                                             top1=(top1 := torch.empty(hkv, 333, dtype=torch.int32, device=dev)))
     _status_ok(dev)
+    assert torch.equal(top1.cpu().long().t(), score.cpu().argmax(dim=-1))
     live = (sel_sizes > 0)[None].expand(333, -1, -1)
     err = (score.cpu().double() - score_ref)[live].abs()
     assert float(err.max()) < 5e-5, float(err.max())
@@ -328,6 +330,44 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
         ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev), ordered_v=data["v"][ws:ce + 1].contiguous().to(dev),
         ordered_pos0=ws, local_start=ws, sm_scale=sm_scale, q_order=order.to(dev))
     _close_attention(got_p, want, "sparse chunk, permuted tiles")
+    # the two-launch form: exact window first, then the row-gather sparse kernel merged into it
+    from semblo_b200.fused_prefill import sparse_gather_attention
+    for q_order in (None, order.to(dev)):
+        lse = torch.empty(500, hq, dtype=torch.float32, device=dev)
+        out2 = torch.empty(500, hq, dim, dtype=torch.bfloat16, device=dev)
+        att2 = torch.zeros(1, dtype=torch.int64, device=dev)
+        sparse_prefill_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev),
+                                 ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev),
+                                 ordered_v=data["v"][ws:ce + 1].contiguous().to(dev), ordered_pos0=ws, local_start=ws,
+                                 sm_scale=sm_scale, out=out2, lse=lse, attended=att2)
+        sparse_gather_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), packed_kv=packed,
+                                qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev),
+                                indptr=index.bucket_indptr.to(dev), sm_scale=sm_scale, out=out2, lse=lse, merge=True,
+                                page_table=table, q_order=q_order, attended=att2)
+        _status_ok(dev)
+        _close_attention(out2, want, "window + gathered clusters")
+        assert int(att2.item()) == int(natt.sum())
+    # the sparse part alone
+    empty_k = data["k_post"][ws:ws].contiguous()
+    want_s, _ = O.sparse_chunk_attention(data["q_post"][cs:ce + 1], index, sel, sizes, qpos, empty_k,
+                                         data["v"][ws:ws].contiguous(), ws, sm_scale)
+    out3 = torch.empty(500, hq, dim, dtype=torch.bfloat16, device=dev)
+    sparse_gather_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), packed_kv=packed,
+                            qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev),
+                            indptr=index.bucket_indptr.to(dev), sm_scale=sm_scale, out=out3, lse=None, merge=False,
+                            page_table=table)
+    _status_ok(dev)
+    _close_attention(out3, want_s, "gathered clusters alone")
+
+
+def test_argsort_and_top1_keys(dev):
+    from semblo_b200.fused_prefill import argsort_keys
+    g = torch.Generator().manual_seed(1)
+    for n, heads, mx in ((5000, 3, 2048), (333, 1, 200), (8192, 4, 16384)):
+        keys = torch.randint(0, mx, (heads, n), generator=g).int()
+        got = argsort_keys(keys.to(dev), mx).cpu().long()
+        want = torch.argsort(keys.long(), dim=1, stable=True)
+        assert torch.equal(got, want)
 
 
 def test_prefill_chunk_loop_end_to_end(dev):
