@@ -166,7 +166,7 @@ class PrefillStep:
     def _timer(self, phase):
         ev = torch.cuda.Event(enable_timing=True)
         ev.record()
-        self.attn_events.append(ev)
+        self.attn_events.append((phase, ev))
 
     def prepare(self):
         L = self.cfg["length"]
@@ -237,7 +237,7 @@ def kernel_launches(calls: dict, clusters: int) -> int:
     per_call = {"semblo_routing_normalize": 1, "semblo_gather_rows": 1, "semblo_assign_argmax": 1,
                 "semblo_cluster_counts": 2, "semblo_kmeans_update": 3 * passes + 1, "semblo_split_descriptor": 1,
                 "semblo_build_layout": 2 + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
-                "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_sparse_prefill": 1,
+                "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_window_prefill": 1, "semblo_sparse_prefill_gather": 1, "semblo_argsort_keys": 3 * passes,
                 "semblo_decode_step": 3}
     return sum(per_call.get(k, 0) * v for k, v in calls.items())
 
@@ -513,7 +513,17 @@ def main():
     launches = kernel_launches(calls, clusters) // args.steps
     attended = int(step.attended.item()) // args.steps
     evs = step.attn_events
-    attn_ms = sum(evs[i].elapsed_time(evs[i + 1]) for i in range(0, len(evs), 2)) / args.steps
+    attn_ms = window_ms = gather_ms = dense_ms = 0.0
+    for i, (phase, ev) in enumerate(evs):
+        if phase == "start":
+            nxt = evs[i + 1]
+            if nxt[0] == "stop":
+                dense_ms += ev.elapsed_time(nxt[1])
+            else:
+                window_ms += ev.elapsed_time(nxt[1])
+                gather_ms += nxt[1].elapsed_time(evs[i + 2][1])
+    dense_ms, window_ms, gather_ms = dense_ms / args.steps, window_ms / args.steps, gather_ms / args.steps
+    attn_ms = dense_ms + window_ms + gather_ms
     step.time_attention = False
     g = cfg["hq"] // cfg["hkv"]
     flops = 4.0 * cfg["dim"] * g * attended
@@ -559,10 +569,11 @@ def main():
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-        "roofline": {"bound": "tensor", "kernel": "sparse_prefill_kernel<256,4>", "achieved": flops / (attn_ms * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "window_prefill_kernel<256,4> + sparse_gather_prefill_kernel<256,4>", "achieved": flops / (attn_ms * 1e-3) / 1e12,
                      "peak": pk["tensor"], "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"],
                      "traffic": None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
-                     "kernel_ms_per_step": attn_ms, "attended_keys_per_step": attended,
+                     "kernel_ms_per_step": attn_ms, "dense_prefix_ms": dense_ms, "window_ms": window_ms,
+                     "gather_ms": gather_ms, "attended_keys_per_step": attended,
                      "flops_per_step": flops},
     }
     if world == 1 and not args.no_decode and not args.length:

@@ -126,24 +126,16 @@ int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key, 
 
 /* ---- prefill attention ---------------------------------------------------------- */
 
-/* semblo/vllm_plugin/kv_outer.py:482-816 (kv_outer_attention incl. the fused local window
- * and combine_partials) and semblo/vllm_plugin/fused_prefill.py:155-189
- * (_dense_chunk_attention).  For every query of the chunk: one softmax over
- *   { rows [indptr[c], indptr[c] + causal_sizes[c]) of the clusters c set in its qmask }
- *   U { positions [local_start, q_position] of the position-ordered K/V }.
- * q, out [Q, Hq, D] bf16; q_positions [Q]; q_order [Hkv, Q] optional permutation of the
- * chunk's queries (tiles are formed in this order); packed_k / packed_v [packed_rows, Hkv, D]
- * (page_table optional: packed row / 16 -> physical 16-row page); ordered_k / ordered_v
- * [ordered_rows, Hkv, D] hold positions ordered_pos0 ...; qmask == NULL gives the exact
- * dense causal attention, ordered_k == NULL the sparse part only.  lse [Q, Hq] (natural log)
- * and attended (sum over (query, KV head) of attended keys) may be NULL. */
-int semblo_sparse_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
-                          int head_dim, const int32_t* q_positions, const int32_t* q_order,
-                          const void* packed_k, const void* packed_v, int64_t packed_rows,
-                          const int32_t* page_table, const int32_t* qmask,
-                          const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
-                          const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
-                          int ordered_pos0, int local_start, float sm_scale, void* out, float* lse,
+/* semblo/vllm_plugin/fused_prefill.py:155-189 (_dense_chunk_attention) and the chunk's own
+ * causal window of semblo/vllm_plugin/kv_outer.py:661-676: every query attends positions
+ * [local_start, q_position] of the position-ordered K/V, exactly causally.
+ * q, out [Q, Hq, D] bf16 (consecutive queries); q_positions [Q]; ordered_k / ordered_v
+ * [ordered_rows, Hkv, D] hold positions ordered_pos0 ...; lse [Q, Hq] (natural log) and
+ * attended (sum over (query, KV head) of attended keys, accumulated) may be NULL. */
+int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
+                          int head_dim, const int32_t* q_positions, const void* ordered_k,
+                          const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
+                          int local_start, float sm_scale, void* out, float* lse,
                           unsigned long long* attended, int32_t* status, void* stream);
 
 /* The sparse part of semblo/vllm_plugin/kv_outer.py:482-816 with row-granular reads: for every
@@ -151,7 +143,7 @@ int semblo_sparse_prefill(const void* q, int num_queries, int num_q_heads, int n
  * its qmask, gathered row by row from the cluster-ordered K/V (packed_k / packed_v
  * [rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
  * ([Hkv, Q], optional).  merge = 1: `out` / `lse` hold the window partial written by
- * semblo_sparse_prefill (normalised output, natural-log LSE) and receive the LSE-merged
+ * semblo_window_prefill (normalised output, natural-log LSE) and receive the LSE-merged
  * result (kv_outer.py:203-227); merge = 0: the sparse result alone. */
 int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
                                  int head_dim, const int32_t* q_order, const void* packed_k,

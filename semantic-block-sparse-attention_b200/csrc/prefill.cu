@@ -1,25 +1,18 @@
-// Block-sparse paged prefill attention on tcgen05 / TMEM.
+// Exact causal window attention on tcgen05 / TMEM: the dense-prefix chunks and the
+// local window of every sparse chunk.
 //
-// One CTA owns a tile of QT = 128 / G queries of one KV head (128 rows: query-major,
-// the G heads of a query adjacent) and keeps the output accumulator O [128, D] in
-// TMEM for the whole pass.  K/V reach shared memory as 16-row pages through TMA:
-//
-//   sparse part : the producer warp walks the per-query cluster bitmasks of the
-//                 tile, and for every cluster any query selected it pushes the
-//                 cluster's causally visible pages (rows [indptr[c], indptr[c] + n_c))
-//                 from the cluster-ordered K/V (optionally through a 16-row page
-//                 table), tagged with the 32-bit set of queries that selected it;
-//   local part  : positions [local_start, max q_pos of the tile] from the
-//                 position-ordered K/V, masked exactly causally per row.
-//
-// Four pages make a 64-key tile: S = Q K^T (UMMA, fp32 in TMEM), the softmax warps
-// (one thread per row) apply the page masks, keep a lazily rescaled running max,
-// write P as bf16 into swizzled shared memory, and O += P V is a second UMMA with V
-// as an MN-major operand.  One softmax over the union, as the reference's LSE merge.
+// One CTA owns a tile of QT = 128 / G consecutive queries of one KV head (128 rows:
+// query-major, the G heads of a query adjacent) and keeps the output accumulator
+// O [128, D] in TMEM.  The producer streams positions [local_start, max q_pos of the
+// tile] of the position-ordered K/V through TMA in 64-row tiles; S = Q K^T (UMMA,
+// fp32 in TMEM), the softmax warps (one thread per row) apply the causal mask, keep a
+// lazily rescaled running max and write P as bf16 into swizzled shared memory, and
+// O += P V is a second UMMA with V as an MN-major operand.  The kernel writes the
+// normalised output and its log-sum-exp, which the sparse launch merges into.
 //
 // Reference behaviour restated here:
-//   semblo/vllm_plugin/kv_outer.py:482-816       attended set of the default prefill body
 //   semblo/vllm_plugin/fused_prefill.py:155-189  exact dense attention for short prefixes
+//   semblo/vllm_plugin/kv_outer.py:661-676       the chunk's own causal window
 //   semblo/vllm_plugin/fused_prefill.py:250-279  window start / dense-prefix rule (caller)
 #include <algorithm>
 
@@ -39,9 +32,10 @@ constexpr float LN2F = 0.6931471805599453f;
 constexpr float RESCALE_GAP = 8.0f;                // log2 units
 
 struct TileInfo {
-  int npages;          // 0 = end of stream
-  int pad[3];
-  int4 page[PAGES_PER_TILE];   // x: query bitmask, y: valid rows, z: position of row 0 (INT_MIN: no causal test)
+  int npages;          // 16-row groups in the tile, 0 = end of stream
+  int rows;            // valid rows
+  int kpos0;           // position of row 0
+  int pad;
 };
 
 template <int D>
@@ -68,15 +62,9 @@ struct PrefillArgs {
   int num_kv_heads;
   int num_clusters;
   const int32_t* q_positions;     // [Q]
-  const int32_t* q_order;         // [Hkv, Q] or null
-  const int32_t* qmask;           // [Q, Hkv, C/32] or null
-  const int32_t* causal_sizes;    // [Hkv, C]
-  const int32_t* indptr;          // [Hkv, C+1]
-  const int32_t* page_table;      // packed row / 16 -> physical page, or null
   int local_start;                // first position of the window (do_local)
   int local_pos0;                 // position held by row 0 of the position-ordered K/V
   int local_rows;                 // rows in the position-ordered K/V
-  int do_local;
   float scale_log2;               // sm_scale * log2(e)
   __nv_bfloat16* out;             // [Q, Hq, D]
   float* lse;                     // [Q, Hq] or null
@@ -89,9 +77,7 @@ enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMP
 
 template <int D, int G>
 __global__ void __launch_bounds__(192, 1)
-sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
-                      const __grid_constant__ CUtensorMap tmap_pk,
-                      const __grid_constant__ CUtensorMap tmap_pv,
+window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_ok,
                       const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
   using C = AttnCfg<D>;
@@ -120,7 +106,7 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 5);
+      mbar_init(bar(B_KVEMPTY + s), 5);     // four softmax warps + the UMMA commit
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -138,107 +124,41 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // ------------------------------------------------------------ producer
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
-    const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
-    const int qpos = qvalid ? a.q_positions[qi] : -1;
+    const int qpos = qvalid ? a.q_positions[slot] : -1;
     const unsigned vmask = __ballot_sync(0xffffffffu, qvalid);
+    int max_qpos = qpos;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) max_qpos = max(max_qpos, __shfl_xor_sync(0xffffffffu, max_qpos, o));
     if (lane == 0) {
       tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_pk);
-      tma_prefetch_desc(&tmap_pv);
       tma_prefetch_desc(&tmap_ok);
       tma_prefetch_desc(&tmap_ov);
-      mbar_arrive_expect_tx(bar(B_QFULL), (uint32_t)__popc(vmask) * G * D * 2);
-    }
-    for (int i = 0; i < QT; ++i) {
-      const int qsrc = __shfl_sync(0xffffffffu, qi, i);
-      if (lane == 0 && ((vmask >> i) & 1)) {
-        for (int sl = 0; sl < C::SLABS; ++sl)
-          tma_load_3d(smem_u32(smem + C::Q_OFF + sl * 128 * 128 + i * G * 128), &tmap_q, bar(B_QFULL),
-                      sl * 64, h * G, qsrc);
-      }
-    }
-
-    int tile = 0, fill = 0;
-    bool ok = true;
-    auto push_page = [&](const CUtensorMap* mk, const CUtensorMap* mv, int row, int nvalid, int mask,
-                         int kpos0) {
-      // warp-uniform arguments
-      const int s = tile % STAGES;
-      if (fill == 0) {
-        if (lane == 0)
-          ok = mbar_wait(bar(B_KVEMPTY + s), ((tile / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
-        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-        if (!ok) return;
-      }
-      if (lane == 0) {
-        const uint32_t koff = C::K_OFF + s * C::KV_BYTES + fill * PAGE * 128;
-        const uint32_t voff = C::V_OFF + s * C::KV_BYTES + fill * PAGE * 128;
-        for (int sl = 0; sl < C::SLABS; ++sl) {
-          tma_load_2d(smem_u32(smem + koff + sl * BLOCK_N * 128), mk, bar(B_KVFULL + s), h * D + sl * 64, row);
-          tma_load_2d(smem_u32(smem + voff + sl * BLOCK_N * 128), mv, bar(B_KVFULL + s), h * D + sl * 64, row);
-        }
-        info[s].page[fill] = make_int4(mask, nvalid, kpos0, 0);
-      }
-      ++fill;
-      if (fill == PAGES_PER_TILE) {
-        if (lane == 0) {
-          info[s].npages = fill;
-          mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)fill * PAGE * D * 2 * 2);
-        }
-        ++tile;
-        fill = 0;
-      }
-    };
-    auto flush_tile = [&]() {
-      if (fill > 0) {
-        const int s = tile % STAGES;
-        if (lane == 0) {
-          info[s].npages = fill;
-          mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)fill * PAGE * D * 2 * 2);
-        }
-        ++tile;
-        fill = 0;
-      }
-    };
-
-    if (a.qmask != nullptr) {
-      const int nwords = a.num_clusters >> 5;
-      const int32_t* qm = a.qmask + ((int64_t)qi * a.num_kv_heads + h) * nwords;
-      const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
-      const int32_t* ipt = a.indptr + (int64_t)h * (a.num_clusters + 1);
-      for (int w = 0; w < nwords && ok; ++w) {
-        const unsigned word = qvalid ? (unsigned)qm[w] : 0u;
-        unsigned any = __reduce_or_sync(0xffffffffu, word);
-        while (any && ok) {
-          const int bit = __ffs(any) - 1;
-          any &= any - 1;
-          const int c = w * 32 + bit;
-          const int n_c = csz[c];
-          if (n_c <= 0) continue;
-          const unsigned mask = __ballot_sync(0xffffffffu, (word >> bit) & 1u);
-          const int start = ipt[c];
-          for (int pg = 0; pg * PAGE < n_c && ok; ++pg) {
-            int row = start + pg * PAGE;
-            if (a.page_table) row = a.page_table[row >> 4] * PAGE;
-            push_page(&tmap_pk, &tmap_pv, row, min(PAGE, n_c - pg * PAGE), (int)mask, INT_MIN);
-          }
-        }
-      }
-      flush_tile();       // keep the masks of the two parts in separate tiles
-    }
-    if (a.do_local && ok) {
-      int max_qpos = qpos;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) max_qpos = max(max_qpos, __shfl_xor_sync(0xffffffffu, max_qpos, o));
+      (void)vmask;
+      mbar_arrive_expect_tx(bar(B_QFULL), (uint32_t)C::Q_BYTES);
+      // consecutive queries: one box per 64-column slab covers the whole tile
+      for (int sl = 0; sl < C::SLABS; ++sl)
+        tma_load_3d(smem_u32(smem + C::Q_OFF + sl * 128 * 128), &tmap_q, bar(B_QFULL), sl * 64, h * G, q_tile0);
       const int last = min(max_qpos, a.local_pos0 + a.local_rows - 1);
-      for (int p = a.local_start; p <= last && ok; p += PAGE)
-        push_page(&tmap_ok, &tmap_ov, p - a.local_pos0, min(PAGE, last - p + 1), -1, p);
-      flush_tile();
-    }
-    if (ok) {
-      // end marker
-      const int s = tile % STAGES;
-      if (lane == 0) {
+      int tile = 0;
+      bool ok = true;
+      for (int p = a.local_start; p <= last && ok; p += BLOCK_N, ++tile) {
+        const int s = tile % STAGES;
+        ok = mbar_wait(bar(B_KVEMPTY + s), ((tile / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
+        if (!ok) break;
+        const int rows = min(BLOCK_N, last - p + 1);
+        info[s].npages = (rows + PAGE - 1) / PAGE;
+        info[s].rows = rows;
+        info[s].kpos0 = p;
+        mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)BLOCK_N * D * 2 * 2);
+        for (int sl = 0; sl < C::SLABS; ++sl) {
+          tma_load_2d(smem_u32(smem + C::K_OFF + s * C::KV_BYTES + sl * BLOCK_N * 128), &tmap_ok,
+                      bar(B_KVFULL + s), h * D + sl * 64, p - a.local_pos0);
+          tma_load_2d(smem_u32(smem + C::V_OFF + s * C::KV_BYTES + sl * BLOCK_N * 128), &tmap_ov,
+                      bar(B_KVFULL + s), h * D + sl * 64, p - a.local_pos0);
+        }
+      }
+      if (ok) {
+        const int s = tile % STAGES;
         ok = mbar_wait(bar(B_KVEMPTY + s), ((tile / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
         if (ok) {
           info[s].npages = 0;
@@ -297,7 +217,7 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
     const bool qvalid = slot < a.num_queries;
-    const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
+    const int qi = qvalid ? slot : 0;
     const int qpos = qvalid ? a.q_positions[qi] : -1;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     float m_ref = -INFINITY, l_run = 0.f;
@@ -310,9 +230,7 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (!ok) break;
       const int np = info[s].npages;
       if (np == 0) break;
-      int4 pg[PAGES_PER_TILE];
-#pragma unroll
-      for (int p = 0; p < PAGES_PER_TILE; ++p) pg[p] = info[s].page[p];
+      const int rows = info[s].rows, kpos0 = info[s].kpos0;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
       ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
@@ -327,22 +245,17 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // masks, scaled logits, tile max
       float tmax = -INFINITY;
       int cnt = 0;
+      // keys of the tile at or before this row's position
+      const int lim = min(rows, qpos - kpos0 + 1);
 #pragma unroll
-      for (int p = 0; p < PAGES_PER_TILE; ++p) {
-        const bool page_on = p < np && ((pg[p].x >> qslot) & 1);
-        const int nv = pg[p].y;
-        const int kp0 = pg[p].z;
-#pragma unroll
-        for (int i = 0; i < PAGE; ++i) {
-          uint32_t& slot_r = p < 2 ? r0[p * PAGE + i] : r1[(p - 2) * PAGE + i];
-          const bool causal = kp0 == INT_MIN || kp0 + i <= qpos;
-          const bool allowed = page_on && i < nv && causal;
-          const float s2 = allowed ? __uint_as_float(slot_r) * a.scale_log2 : -INFINITY;
-          slot_r = __float_as_uint(s2);
-          tmax = fmaxf(tmax, s2);
-          cnt += allowed;
-        }
+      for (int col = 0; col < BLOCK_N; ++col) {
+        uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
+        const bool allowed = col < lim;
+        const float s2 = allowed ? __uint_as_float(slot_r) * a.scale_log2 : -INFINITY;
+        slot_r = __float_as_uint(s2);
+        tmax = fmaxf(tmax, s2);
       }
+      cnt = max(lim, 0);
       if (t == 0) att += cnt;
       // lazy rescale: only when the running reference falls more than 2^8 behind
       bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
@@ -446,81 +359,54 @@ sparse_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 template <int D, int G>
-int launch_prefill(const void* q, const void* packed_k, const void* packed_v, int64_t packed_rows,
-                   const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
+int launch_prefill(const void* q, const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
                    const PrefillArgs& a, cudaStream_t st) {
   using C = AttnCfg<D>;
   constexpr int QT = 128 / G;
-  CUtensorMap mq, mpk, mpv, mok, mov;
+  CUtensorMap mq, mok, mov;
   {
     uint64_t d[3] = {(uint64_t)D, (uint64_t)a.num_q_heads, (uint64_t)a.num_queries};
     uint64_t s[2] = {(uint64_t)D * 2, (uint64_t)a.num_q_heads * D * 2};
-    uint32_t b[3] = {64, (uint32_t)G, 1};
+    uint32_t b[3] = {64, (uint32_t)G, (uint32_t)QT};
     int rc = semblo::make_tensor_map_bf16(&mq, q, 3, d, s, b);
     if (rc) return rc;
   }
   const uint64_t row_bytes = (uint64_t)a.num_kv_heads * D * 2;
-  uint32_t box[2] = {64, PAGE};
-  const void* pk = packed_k ? packed_k : ordered_k;
-  const void* pv = packed_v ? packed_v : ordered_v;
-  const int64_t prow = packed_k ? packed_rows : ordered_rows;
-  const void* ok_ = ordered_k ? ordered_k : packed_k;
-  const void* ov_ = ordered_v ? ordered_v : packed_v;
-  const int64_t orow = ordered_k ? ordered_rows : packed_rows;
-  {
-    uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)prow};
-    int rc = semblo::make_tensor_map_bf16(&mpk, pk, 2, d, &row_bytes, box);
-    if (rc) return rc;
-    rc = semblo::make_tensor_map_bf16(&mpv, pv, 2, d, &row_bytes, box);
-    if (rc) return rc;
-  }
-  {
-    uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)orow};
-    int rc = semblo::make_tensor_map_bf16(&mok, ok_, 2, d, &row_bytes, box);
-    if (rc) return rc;
-    rc = semblo::make_tensor_map_bf16(&mov, ov_, 2, d, &row_bytes, box);
-    if (rc) return rc;
-  }
-  auto kern = sparse_prefill_kernel<D, G>;
+  uint32_t box[2] = {64, BLOCK_N};
+  uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)ordered_rows};
+  int rc = semblo::make_tensor_map_bf16(&mok, ordered_k, 2, d, &row_bytes, box);
+  if (rc) return rc;
+  rc = semblo::make_tensor_map_bf16(&mov, ordered_v, 2, d, &row_bytes, box);
+  if (rc) return rc;
+  auto kern = window_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 192, C::TOTAL, st>>>(mq, mpk, mpv, mok, mov, a);
+  kern<<<grid, 192, C::TOTAL, st>>>(mq, mok, mov, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
 
 }  // namespace
 
-extern "C" int semblo_sparse_prefill(
-    const void* q, int num_queries, int num_q_heads, int num_kv_heads, int head_dim,
-    const int32_t* q_positions, const int32_t* q_order,
-    const void* packed_k, const void* packed_v, int64_t packed_rows, const int32_t* page_table,
-    const int32_t* qmask, const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
-    const void* ordered_k, const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
-    int local_start, float sm_scale, void* out, float* lse, unsigned long long* attended,
-    int32_t* status, void* stream) {
+extern "C" int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
+                                     int head_dim, const int32_t* q_positions, const void* ordered_k,
+                                     const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
+                                     int local_start, float sm_scale, void* out, float* lse,
+                                     unsigned long long* attended, int32_t* status, void* stream) {
   SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
-  SEMBLO_REQUIRE(qmask != nullptr || ordered_k != nullptr, "nothing to attend: neither a selection nor a window");
-  SEMBLO_REQUIRE(qmask == nullptr || (packed_k && packed_v && causal_sizes && indptr && num_clusters % 32 == 0),
-                 "the sparse part needs packed K/V, sizes, indptr and a cluster count that is a multiple of 32");
-  SEMBLO_REQUIRE((ordered_k == nullptr) == (ordered_v == nullptr), "ordered K and V must be given together");
+  SEMBLO_REQUIRE(ordered_k != nullptr && ordered_v != nullptr && q_positions != nullptr, "K, V and positions are required");
+  SEMBLO_REQUIRE(local_start >= ordered_pos0, "the window starts before the first row of K/V");
   if (num_queries == 0) return 0;
   PrefillArgs a;
   a.num_queries = num_queries;
   a.num_q_heads = num_q_heads;
   a.num_kv_heads = num_kv_heads;
-  a.num_clusters = num_clusters;
+  a.num_clusters = 0;
   a.q_positions = q_positions;
-  a.q_order = q_order;
-  a.qmask = qmask;
-  a.causal_sizes = causal_sizes;
-  a.indptr = indptr;
-  a.page_table = page_table;
   a.local_start = local_start;
   a.local_pos0 = ordered_pos0;
   a.local_rows = (int)ordered_rows;
-  a.do_local = ordered_k != nullptr;
   a.scale_log2 = sm_scale * 1.4426950408889634f;
   a.out = (__nv_bfloat16*)out;
   a.lse = lse;
@@ -528,10 +414,8 @@ extern "C" int semblo_sparse_prefill(
   a.status = status;
   const int g = num_q_heads / num_kv_heads;
   cudaStream_t st = (cudaStream_t)stream;
-#define SEMBLO_PREFILL_CASE(DD, GG)                                                              \
-  if (head_dim == DD && g == GG)                                                                 \
-    return launch_prefill<DD, GG>(q, packed_k, packed_v, packed_rows, ordered_k, ordered_v,      \
-                                  ordered_rows, a, st);
+#define SEMBLO_PREFILL_CASE(DD, GG) \
+  if (head_dim == DD && g == GG) return launch_prefill<DD, GG>(q, ordered_k, ordered_v, ordered_rows, a, st);
   SEMBLO_PREFILL_CASE(256, 4)
   SEMBLO_PREFILL_CASE(128, 4)
   SEMBLO_PREFILL_CASE(256, 8)

@@ -71,37 +71,25 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
     return qmask, score
 
 
-def sparse_prefill_attention(q: torch.Tensor, q_positions: torch.Tensor, *, packed_kv=None, page_table=None,
-                             qmask=None, causal_sizes=None, indptr=None, ordered_k=None, ordered_v=None,
-                             ordered_pos0: int = 0, local_start: int = 0, sm_scale: float, out=None,
-                             lse=None, attended=None, q_order=None) -> torch.Tensor:
-    """One launch of the block-sparse prefill kernel (see include/semblo_b200.h)."""
-    require_cuda(q)
+def window_attention(q: torch.Tensor, q_positions: torch.Tensor, *, ordered_k: torch.Tensor,
+                     ordered_v: torch.Tensor, ordered_pos0: int = 0, local_start: int = 0, sm_scale: float,
+                     out=None, lse=None, attended=None) -> torch.Tensor:
+    """Exact causal attention of consecutive queries over positions [local_start, q_position]
+    of the position-ordered K/V (semblo_window_prefill)."""
+    require_cuda(q, ordered_k, ordered_v)
     q_count, num_q_heads, head_dim = q.shape
     if q.dtype != torch.bfloat16:
         raise ValueError("prefill attention takes bf16 queries")
     q = q if q.is_contiguous() else q.contiguous()
     if out is None:
         out = torch.empty_like(q)
-    num_clusters = 0
-    pk = pv = None
-    packed_rows = 0
-    num_kv_heads = None
-    if qmask is not None:
-        num_clusters = int(causal_sizes.shape[1])
-        pk, pv = packed_kv[0], packed_kv[1]
-        packed_rows = int(packed_kv.shape[1])
-        num_kv_heads = int(packed_kv.shape[2])
-    if ordered_k is not None:
-        num_kv_heads = int(ordered_k.shape[1])
-        ordered_k = ordered_k if ordered_k.is_contiguous() else ordered_k.contiguous()
-        ordered_v = ordered_v if ordered_v.is_contiguous() else ordered_v.contiguous()
+    ordered_k = ordered_k if ordered_k.is_contiguous() else ordered_k.contiguous()
+    ordered_v = ordered_v if ordered_v.is_contiguous() else ordered_v.contiguous()
     status = _lib.status_for(q.device)
-    check(lib().semblo_sparse_prefill(
-        ptr(q), q_count, num_q_heads, num_kv_heads, head_dim, ptr(q_positions), ptr(q_order),
-        ptr(pk), ptr(pv), packed_rows, ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr), num_clusters,
-        ptr(ordered_k), ptr(ordered_v), 0 if ordered_k is None else int(ordered_k.shape[0]), int(ordered_pos0),
-        int(local_start), float(sm_scale), ptr(out), ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
+    check(lib().semblo_window_prefill(
+        ptr(q), q_count, num_q_heads, int(ordered_k.shape[1]), head_dim, ptr(q_positions), ptr(ordered_k),
+        ptr(ordered_v), int(ordered_k.shape[0]), int(ordered_pos0), int(local_start), float(sm_scale), ptr(out),
+        ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
     return out
 
 
@@ -159,9 +147,9 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if wstart == 0:
         if _timer:
             _timer("start")
-        res = sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
-                                       ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
-                                       sm_scale=sm_scale, out=out, attended=attended)
+        res = window_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
+                               ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
+                               sm_scale=sm_scale, out=out, attended=attended)
         if _timer:
             _timer("stop")
         return res
@@ -206,9 +194,11 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if _timer:
         _timer("start")
     # the exact window [wstart, q] in position order, then the selected clusters merged into it
-    sparse_prefill_attention(q_chunk, q_positions, ordered_k=k_pos[wstart:chunk_end + 1],
-                             ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart,
-                             sm_scale=sm_scale, out=out, lse=lse, attended=attended)
+    window_attention(q_chunk, q_positions, ordered_k=k_pos[wstart:chunk_end + 1],
+                     ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart,
+                     sm_scale=sm_scale, out=out, lse=lse, attended=attended)
+    if _timer:
+        _timer("mid")
     sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
                             indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
                             page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended)

@@ -265,7 +265,7 @@ def test_scores_and_selection(dev, dim, hq, hkv, sink):
 # ---------------------------------------------------------------------- prefill attention
 @pytest.mark.parametrize("dim,hq,hkv", [(256, 8, 2), (128, 4, 1), (128, 16, 2)])
 def test_dense_causal_attention(dev, dim, hq, hkv):
-    from semblo_b200.fused_prefill import sparse_prefill_attention
+    from semblo_b200.fused_prefill import window_attention
     length = 700
     data = O.mixture_inputs(length=length, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=8, seed=3)
     sm_scale = dim ** -0.5
@@ -273,7 +273,7 @@ def test_dense_causal_attention(dev, dim, hq, hkv):
     want, lse_want = O.dense_causal_attention(data["q_post"], data["k_post"], data["v"], qpos, sm_scale)
     lse = torch.empty(length, hq, dtype=torch.float32, device=dev)
     att = torch.zeros(1, dtype=torch.int64, device=dev)
-    got = sparse_prefill_attention(data["q_post"].to(dev), qpos.int().to(dev), ordered_k=data["k_post"].to(dev),
+    got = window_attention(data["q_post"].to(dev), qpos.int().to(dev), ordered_k=data["k_post"].to(dev),
                                    ordered_v=data["v"].to(dev), sm_scale=sm_scale, lse=lse, attended=att)
     _status_ok(dev)
     _close_attention(got, want, "dense prefix")
@@ -283,7 +283,7 @@ def test_dense_causal_attention(dev, dim, hq, hkv):
     qs = slice(400, 700)
     want_w, _ = O.dense_causal_attention(data["q_post"][qs], data["k_post"][200:], data["v"][200:], qpos[qs],
                                          sm_scale, k_start=200)
-    got_w = sparse_prefill_attention(data["q_post"][qs].contiguous().to(dev), qpos[qs].int().to(dev),
+    got_w = window_attention(data["q_post"][qs].contiguous().to(dev), qpos[qs].int().to(dev),
                                      ordered_k=data["k_post"][200:].contiguous().to(dev),
                                      ordered_v=data["v"][200:].contiguous().to(dev), ordered_pos0=200,
                                      local_start=200, sm_scale=sm_scale)
@@ -292,7 +292,7 @@ def test_dense_causal_attention(dev, dim, hq, hkv):
 
 @pytest.mark.parametrize("dim,hq,hkv,sink,paged", [(256, 8, 2, 64, True), (128, 8, 2, 0, False)])
 def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, hq, hkv, sink, paged):
-    from semblo_b200.fused_prefill import sparse_prefill_attention
+    from semblo_b200.fused_prefill import window_attention
     length, target, local = 6144, 512, 128
     data, index = _small_problem(length, hq, hkv, dim, 24, 77 + dim, 32, 7, sink)
     cs, ce = 4096, 4096 + 499
@@ -313,33 +313,17 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
         pool[:, perm] = packed.view(2, n_pages, 16, hkv, dim)
         packed = pool.view(2, n_pages * 16, hkv, dim).contiguous()
         table = perm.to(torch.int32).to(dev)
-    att = torch.zeros(1, dtype=torch.int64, device=dev)
-    got = sparse_prefill_attention(
-        data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev), packed_kv=packed, page_table=table,
-        qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev), indptr=index.bucket_indptr.to(dev),
-        ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev), ordered_v=data["v"][ws:ce + 1].contiguous().to(dev),
-        ordered_pos0=ws, local_start=ws, sm_scale=sm_scale, attended=att)
-    _status_ok(dev)
-    _close_attention(got, want, "sparse chunk")
-    assert int(att.item()) == int(natt.sum())
-    # a permuted tile order gives the same rows
     order = torch.stack([torch.randperm(500, generator=torch.Generator().manual_seed(h)) for h in range(hkv)]).int()
-    got_p = sparse_prefill_attention(
-        data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev), packed_kv=packed, page_table=table,
-        qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev), indptr=index.bucket_indptr.to(dev),
-        ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev), ordered_v=data["v"][ws:ce + 1].contiguous().to(dev),
-        ordered_pos0=ws, local_start=ws, sm_scale=sm_scale, q_order=order.to(dev))
-    _close_attention(got_p, want, "sparse chunk, permuted tiles")
     # the two-launch form: exact window first, then the row-gather sparse kernel merged into it
     from semblo_b200.fused_prefill import sparse_gather_attention
     for q_order in (None, order.to(dev)):
         lse = torch.empty(500, hq, dtype=torch.float32, device=dev)
         out2 = torch.empty(500, hq, dim, dtype=torch.bfloat16, device=dev)
         att2 = torch.zeros(1, dtype=torch.int64, device=dev)
-        sparse_prefill_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev),
-                                 ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev),
-                                 ordered_v=data["v"][ws:ce + 1].contiguous().to(dev), ordered_pos0=ws, local_start=ws,
-                                 sm_scale=sm_scale, out=out2, lse=lse, attended=att2)
+        window_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), qpos.int().to(dev),
+                         ordered_k=data["k_post"][ws:ce + 1].contiguous().to(dev),
+                         ordered_v=data["v"][ws:ce + 1].contiguous().to(dev), ordered_pos0=ws, local_start=ws,
+                         sm_scale=sm_scale, out=out2, lse=lse, attended=att2)
         sparse_gather_attention(data["q_post"][cs:ce + 1].contiguous().to(dev), packed_kv=packed,
                                 qmask=O.pack_bits(sel).to(dev), causal_sizes=sizes.to(dev),
                                 indptr=index.bucket_indptr.to(dev), sm_scale=sm_scale, out=out2, lse=lse, merge=True,
