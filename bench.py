@@ -115,7 +115,7 @@ class PrefillStep:
         from semblo_b200 import _lib
         self.cfg, self.device, self.world = cfg, device, world
         self.page_table = None
-        self.attended = torch.zeros(1, dtype=torch.int64, device=device)
+        self.attended = torch.zeros(2, dtype=torch.int64, device=device)
         self.attn_events = []
         self.time_attention = False
         self.gathered = None
@@ -511,7 +511,8 @@ def main():
     calls = dict(_lib.CALLS)
     clusters = int(index.num_buckets)
     launches = kernel_launches(calls, clusters) // args.steps
-    attended = int(step.attended.item()) // args.steps
+    attended = int(step.attended[0].item()) // args.steps
+    gathered_rows = int(step.attended[1].item()) // args.steps
     evs = step.attn_events
     attn_ms = window_ms = gather_ms = dense_ms = 0.0
     for i, (phase, ev) in enumerate(evs):
@@ -573,7 +574,7 @@ def main():
                      "peak": pk["tensor"], "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"],
                      "traffic": None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
                      "kernel_ms_per_step": attn_ms, "dense_prefix_ms": dense_ms, "window_ms": window_ms,
-                     "gather_ms": gather_ms, "attended_keys_per_step": attended,
+                     "gather_ms": gather_ms, "attended_keys_per_step": attended, "gathered_rows_per_step": gathered_rows,
                      "flops_per_step": flops},
     }
     if world == 1 and not args.no_decode and not args.length:

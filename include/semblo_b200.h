@@ -144,7 +144,9 @@ int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int n
  * [rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
  * ([Hkv, Q], optional).  merge = 1: `out` / `lse` hold the window partial written by
  * semblo_window_prefill (normalised output, natural-log LSE) and receive the LSE-merged
- * result (kv_outer.py:203-227); merge = 0: the sparse result alone. */
+ * result (kv_outer.py:203-227); merge = 0: the sparse result alone.  attended (may be NULL)
+ * points at two counters: [0] += attended keys summed over (query, KV head), [1] += K/V rows
+ * gathered summed over tiles (the union each tile actually reads). */
 int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
                                  int head_dim, const int32_t* q_order, const void* packed_k,
                                  const void* packed_v, const int32_t* page_table,

@@ -159,6 +159,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
     const int32_t* ipt = a.indptr + (int64_t)h * (a.num_clusters + 1);
     int tile = 0, fill = 0;
+    long long gathered = 0;
     bool ok = true;
     auto acquire = [&]() {          // make plan stage of `tile` writable
       const int ps = tile % PLAN_STAGES;
@@ -173,6 +174,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         plan[ps].count = count;
         mbar_arrive(bar(B_PLANFULL + ps));
       }
+      gathered += count;
       ++tile;
       fill = 0;
     };
@@ -243,6 +245,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       publish(fill);
       acquire();
     }
+    if (a.attended && lane == 0 && gathered) atomicAdd(a.attended + 1, (unsigned long long)gathered);
     if (ok) {
       // end of stream, once per gather warp (they alternate tiles)
       publish(0);
