@@ -8,10 +8,11 @@
 //              starts fetched by 32 lanes in parallel), and expands the union of selected
 //              clusters into a stream of packed rows, each tagged with the 32-bit set of
 //              queries that selected its cluster; 64 rows make a tile
-//   warps 5-6  gather: alternate tiles; copy the K and V rows of a tile with 16-byte
+//   warps 5-8  gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
 //              cp.async into the 128-byte-swizzled UMMA layout (only visible rows are
-//              read: no page padding), then publish them to the async proxy
-//   warp  7    UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM
+//              read: no page padding), then published to the async proxy
+//   warp  9    UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
+//              whichever order their operands become ready
 // The epilogue merges the sparse partial with the window partial already stored in
 // `out` / `lse` by the dense launch, so each query sees one softmax over the union.
 //
@@ -55,7 +56,7 @@ struct GatherCfg {
   static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
   static constexpr int PLAN_OFF = P_OFF + 2 * P_BYTES;
   static constexpr int BAR_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (10 + 2 * STAGES + 2 * PLAN_STAGES);
+  static constexpr int MISC_OFF = BAR_OFF + 8 * (10 + 4 * STAGES + 2 * PLAN_STAGES);
   static constexpr int TOTAL = MISC_OFF + 16 + 1024;
   static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
   static constexpr int O_COL = 2 * BLOCK_N;
@@ -78,7 +79,7 @@ struct GatherArgs {
   int* status;
 };
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KVFULL = 10 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KFULL = 10 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -88,13 +89,15 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(320, 1)
 sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
   constexpr int STAGES = C::STAGES;
-  constexpr int B_KVEMPTY = B_KVFULL + STAGES;
-  constexpr int B_PLANFULL = B_KVEMPTY + STAGES;
+  constexpr int B_KEMPTY = B_KFULL + STAGES;
+  constexpr int B_VFULL = B_KEMPTY + STAGES;
+  constexpr int B_VEMPTY = B_VFULL + STAGES;
+  constexpr int B_PLANFULL = B_VEMPTY + STAGES;
   constexpr int B_PLANEMPTY = B_PLANFULL + PLAN_STAGES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -118,12 +121,14 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       mbar_init(bar(B_PEMPTY + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 1);
+      mbar_init(bar(B_KFULL + s), 1);
+      mbar_init(bar(B_KEMPTY + s), 1);
+      mbar_init(bar(B_VFULL + s), 1);
+      mbar_init(bar(B_VEMPTY + s), 1);
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 6);     // one gather warp, the UMMA thread, four softmax warps
+      mbar_init(bar(B_PLANEMPTY + s), 7);     // a K and a V gather warp, the UMMA thread, four softmax warps
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -179,61 +184,77 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       fill = 0;
     };
     acquire();
-    unsigned next_word = (qvalid && nwords > 0) ? (unsigned)qm[0] : 0u;
+    // software pipeline over the bitmask words: word w+2 and the sizes / starts of the clusters
+    // of word w+1 are in flight while word w is expanded
+    auto load_word = [&](int w) -> unsigned { return (qvalid && w < nwords) ? (unsigned)qm[w] : 0u; };
+    unsigned word1 = load_word(0), word2 = load_word(1);
+    unsigned any1 = __reduce_or_sync(0xffffffffu, word1);
+    int n1 = ((any1 >> lane) & 1) ? csz[lane] : 0;
+    int start1 = ((any1 >> lane) & 1) ? ipt[lane] : 0;
+    int pt1 = (a.page_table && ((any1 >> lane) & 1)) ? a.page_table[start1 >> 4] : 0;
     for (int w = 0; w < nwords && ok; ++w) {
-      const unsigned word = next_word;
-      if (w + 1 < nwords) next_word = qvalid ? (unsigned)qm[w + 1] : 0u;     // prefetch
-      const unsigned any = __reduce_or_sync(0xffffffffu, word);
-      if (any == 0) continue;
-      const int c = w * 32 + lane;
-      const bool has = (any >> lane) & 1;
-      int n_b = has ? csz[c] : 0;
-      n_b = max(n_b, 0);
-      const int start_b = has ? ipt[c] : 0;
-      // mask_b: the queries of the tile that selected cluster (w, lane)
-      unsigned mask_b = 0;
-      for (unsigned tmp = any; tmp; tmp &= tmp - 1) {
-        const int b = __ffs(tmp) - 1;
-        const unsigned m = __ballot_sync(0xffffffffu, (word >> b) & 1u);
-        if (lane == b) mask_b = m;
+      const unsigned word = word1, any = any1;
+      int n_b = max(n1, 0);
+      const int start_b = start1, pt_b = pt1;
+      // prefetch for the following words
+      word1 = word2;
+      word2 = load_word(w + 2);
+      any1 = __reduce_or_sync(0xffffffffu, word1);
+      {
+        const bool has1 = (w + 1 < nwords) && ((any1 >> lane) & 1);
+        const int c1 = (w + 1) * 32 + lane;
+        n1 = has1 ? csz[c1] : 0;
+        start1 = has1 ? ipt[c1] : 0;
       }
-      int pre = n_b;                               // inclusive scan over lanes
+      if (any != 0) {
+        // mask_b: the queries of the tile that selected cluster (w, lane)
+        unsigned mask_b = 0;
+        for (unsigned tmp = any; tmp; tmp &= tmp - 1) {
+          const int b = __ffs(tmp) - 1;
+          const unsigned m = __ballot_sync(0xffffffffu, (word >> b) & 1u);
+          if (lane == b) mask_b = m;
+        }
+        int pre = n_b;                               // inclusive scan over lanes
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, pre, o);
-        if (lane >= o) pre += v;
-      }
-      const int total = __shfl_sync(0xffffffffu, pre, 31);
-      const int excl = pre - n_b;
-      for (int j0 = 0; j0 < total && ok;) {
-        const int cnt = min(min(32, total - j0), BLOCK_N - fill);
-        const int j = j0 + lane;
-        // first lane whose inclusive prefix exceeds j
-        int lo = 0;
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, pre, o);
+          if (lane >= o) pre += v;
+        }
+        const int total = __shfl_sync(0xffffffffu, pre, 31);
+        const int excl = pre - n_b;
+        for (int j0 = 0; j0 < total && ok;) {
+          const int cnt = min(min(32, total - j0), BLOCK_N - fill);
+          const int j = j0 + lane;
+          // first lane whose inclusive prefix exceeds j
+          int lo = 0;
 #pragma unroll
-        for (int step = 16; step > 0; step >>= 1) {
-          const int probe = lo + step - 1;
-          const int v = __shfl_sync(0xffffffffu, pre, probe);
-          if (v <= j) lo += step;
-        }
-        lo = min(lo, 31);
-        const int sb = __shfl_sync(0xffffffffu, start_b, lo);
-        const int eb = __shfl_sync(0xffffffffu, excl, lo);
-        const unsigned mb = __shfl_sync(0xffffffffu, mask_b, lo);
-        if (lane < cnt) {
-          int row = sb + (j - eb);
-          if (a.page_table) row = a.page_table[row >> 4] * 16 + (row & 15);
-          const int ps = tile % PLAN_STAGES;
-          plan[ps].row[fill + lane] = row;
-          plan[ps].mask[fill + lane] = mb;
-        }
-        fill += cnt;
-        j0 += cnt;
-        if (fill == BLOCK_N) {
-          publish(BLOCK_N);
-          acquire();
+          for (int step = 16; step > 0; step >>= 1) {
+            const int v = __shfl_sync(0xffffffffu, pre, lo + step - 1);
+            if (v <= j) lo += step;
+          }
+          lo = min(lo, 31);
+          const int sb = __shfl_sync(0xffffffffu, start_b, lo);
+          const int eb = __shfl_sync(0xffffffffu, excl, lo);
+          const int pb = __shfl_sync(0xffffffffu, pt_b, lo);
+          const unsigned mb = __shfl_sync(0xffffffffu, mask_b, lo);
+          if (lane < cnt) {
+            const int off = j - eb;
+            int row = sb + off;
+            if (a.page_table) row = (off < 16 ? pb : a.page_table[row >> 4]) * 16 + (row & 15);
+            const int ps = tile % PLAN_STAGES;
+            plan[ps].row[fill + lane] = row;
+            plan[ps].mask[fill + lane] = mb;
+          }
+          fill += cnt;
+          j0 += cnt;
+          if (fill == BLOCK_N) {
+            publish(BLOCK_N);
+            acquire();
+          }
         }
       }
+      // the first page of every cluster of the next word (its start has arrived by now)
+      pt1 = (a.page_table && ((any1 >> lane) & 1) && w + 1 < nwords) ? a.page_table[start1 >> 4] : 0;
     }
     if (ok && fill > 0) {
       const int ps = tile % PLAN_STAGES;
@@ -252,84 +273,111 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       acquire();
       if (ok) publish(0);
     }
-  } else if (warp == 5 || warp == 6) {
-    // ------------------------------------------------------------ gather warps (alternate tiles)
+  } else if (warp >= 5 && warp <= 8) {
+    // ------------------------------------------------------------ gather warps
+    // warps 5/6 copy the K rows of even/odd tiles, warps 7/8 the V rows: consecutive tiles
+    // are in flight in different warps, so a tile's latency hides behind its neighbours'.
+    const bool is_v = warp >= 7;
+    const int par = (warp - 5) & 1;
+    const __nv_bfloat16* src_base = is_v ? a.packed_v : a.packed_k;
+    const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
     const int64_t row_elems = (int64_t)a.num_kv_heads * D;
     constexpr int LANES_PER_ROW = D / 8;           // 16-byte chunks per row: 32 (D=256) or 16 (D=128)
     constexpr int ROWS_PER_ITER = 32 / LANES_PER_ROW;
     const int sub = lane / LANES_PER_ROW, l_in = lane % LANES_PER_ROW;
     const int slab = l_in >> 3, chunk = l_in & 7;
-    for (int t = warp - 5;; t += 2) {
+    const int64_t lane_off = (int64_t)h * D + l_in * 8;
+    for (int t = par;; t += 2) {
       const int ps = t % PLAN_STAGES, s = t % STAGES;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       const int cnt = plan[ps].count;
       if (cnt == 0) break;
-      if (!mbar_wait(bar(B_KVEMPTY + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
-      const int n16 = (cnt + 15) & ~15;
-      const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-      const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
-      for (int j0 = 0; j0 < n16; j0 += ROWS_PER_ITER) {
-        const int j = j0 + sub;
-        const int row = plan[ps].row[j];
-        const int64_t off = ((int64_t)max(row, 0) * row_elems + (int64_t)h * D + l_in * 8);
-        const uint32_t dst = slab * (BLOCK_N * 128) + swz128(j, chunk);
-        const uint32_t bytes = row >= 0 ? 16u : 0u;
-        cp_async16(k_base + dst, a.packed_k + off, bytes);
-        cp_async16(v_base + dst, a.packed_v + off, bytes);
-      }
+      const int r_lo = plan[ps].row[lane], r_hi = plan[ps].row[lane + 32];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
+      if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      const int n16 = (cnt + 15) & ~15;
+      const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
+#pragma unroll 4
+      for (int j0 = 0; j0 < n16; j0 += ROWS_PER_ITER) {
+        const int j = j0 + sub;
+        const int row = __shfl_sync(0xffffffffu, j0 < 32 ? r_lo : r_hi, j & 31);
+        const int64_t off = (int64_t)max(row, 0) * row_elems + lane_off;
+        cp_async16(base + swz128(j, chunk), src_base + off, row >= 0 ? 16u : 0u);
+      }
       cp_async_wait_all();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_KVFULL + s));
+      if (lane == 0) mbar_arrive(bar(b_full + s));
     }
-  } else if (warp == 7) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
+    // S(j) = Q K(j)^T is issued as soon as K(j) has landed and the S buffer is free;
+    // O += P(j) V(j) as soon as the softmax warps have written P(j): whichever is ready first.
     if (elect_one()) {
       const uint32_t q_base = smem_u32(smem + C::Q_OFF);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
-      int np_prev = 0;
-      auto issue_pv = [&](int t, int np) -> bool {
-        const int b = t & 1, s = t % STAGES;
-        if (!mbar_wait(bar(B_PFULL + b), (t >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) return false;
-        tc_fence_after();
-        const uint32_t p_base = smem_u32(smem + C::P_OFF + b * C::P_BYTES);
-        const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
-        for (int kk = 0; kk < np; ++kk)
-          umma_ss(tmem_base + C::O_COL, make_smem_desc(p_base + kk * 32, 16, 1024),
-                  make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
-                  (t > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(B_KVEMPTY + s));
-        umma_commit(bar(B_PEMPTY + b));
-        return true;
-      };
-      int j = 0;
+      int next_qk = 0, next_pv = 0, end_tile = INT_MAX, plan_seen = -1, cnt_cur = 0;
+      int np_of[4] = {0, 0, 0, 0};                    // pages of the tiles in flight (index tile & 3)
+      unsigned long long t0 = globaltimer();
+      uint32_t idle = 0;
       while (ok) {
-        const int ps = j % PLAN_STAGES, s = j % STAGES, b = j & 1;
-        if (!mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
-        const int cnt = plan[ps].count;
-        mbar_arrive(bar(B_PLANEMPTY + ps));
-        if (cnt == 0) break;
-        const int np = (cnt + 15) >> 4;
-        if (!mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
-        if (!mbar_wait(bar(B_SEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-        const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
+        bool progress = false;
+        if (next_qk < end_tile && next_qk - next_pv < 2) {
+          const int j = next_qk, ps = j % PLAN_STAGES, s = j % STAGES, b = j & 1;
+          if (plan_seen < j && mbar_try_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1)) {
+            cnt_cur = plan[ps].count;
+            mbar_arrive(bar(B_PLANEMPTY + ps));
+            plan_seen = j;
+            if (cnt_cur == 0) end_tile = j;
+            progress = true;
+          }
+          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait(bar(B_KFULL + s), (j / STAGES) & 1) &&
+              mbar_try_wait(bar(B_SEMPTY + b), ((j >> 1) & 1) ^ 1)) {
+            tc_fence_after();
+            const int np = (cnt_cur + 15) >> 4;
+            np_of[j & 3] = np;
+            const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
+            const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-          umma_ss(tmem_base + b * BLOCK_N, make_smem_desc(q_base + sl * 128 * 128 + ko, 16, 1024),
-                  make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+              umma_ss(tmem_base + b * BLOCK_N, make_smem_desc(q_base + sl * 128 * 128 + ko, 16, 1024),
+                      make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(bar(B_KEMPTY + s));
+            umma_commit(bar(B_SFULL + b));
+            ++next_qk;
+            progress = true;
+          }
         }
-        umma_commit(bar(B_SFULL + b));
-        if (j > 0 && !issue_pv(j - 1, np_prev)) { ok = false; break; }
-        np_prev = np;
-        ++j;
+        if (next_pv < next_qk) {
+          const int t = next_pv, b = t & 1, s = t % STAGES;
+          if (mbar_try_wait(bar(B_PFULL + b), (t >> 1) & 1) && mbar_try_wait(bar(B_VFULL + s), (t / STAGES) & 1)) {
+            tc_fence_after();
+            const int np = np_of[t & 3];
+            const uint32_t p_base = smem_u32(smem + C::P_OFF + b * C::P_BYTES);
+            const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
+            for (int kk = 0; kk < np; ++kk)
+              umma_ss(tmem_base + C::O_COL, make_smem_desc(p_base + kk * 32, 16, 1024),
+                      make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
+                      (t > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar(B_VEMPTY + s));
+            umma_commit(bar(B_PEMPTY + b));
+            ++next_pv;
+            progress = true;
+          }
+        }
+        if (next_pv == end_tile) break;
+        if (progress) {
+          idle = 0;
+        } else if ((++idle & 0x3ff) == 0) {
+          if (idle == 0x400) t0 = globaltimer();
+          if (*abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; ok = false; }
+          else if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(a.status, 0, STATUS_TIMEOUT_MMA); ok = false; }
+        }
       }
-      if (ok && j > 0) ok = issue_pv(j - 1, np_prev);
       if (ok) umma_commit(bar(B_OREADY));
     }
   } else {
@@ -524,7 +572,7 @@ int launch_gather(const void* q, const GatherArgs& a, cudaStream_t st) {
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 256, C::TOTAL, st>>>(mq, a);
+  kern<<<grid, 320, C::TOTAL, st>>>(mq, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
