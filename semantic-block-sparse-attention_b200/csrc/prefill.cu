@@ -245,16 +245,23 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // masks, scaled logits, tile max
       float tmax = -INFINITY;
       int cnt = 0;
-      // keys of the tile at or before this row's position
+      // keys of the tile at or before this row's position; tiles wholly below the diagonal
+      // for every row of the warp need no mask (scaling is folded into the exponent below)
       const int lim = min(rows, qpos - kpos0 + 1);
+      if (__all_sync(0xffffffffu, lim >= BLOCK_N)) {
 #pragma unroll
-      for (int col = 0; col < BLOCK_N; ++col) {
-        uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
-        const bool allowed = col < lim;
-        const float s2 = allowed ? __uint_as_float(slot_r) * a.scale_log2 : -INFINITY;
-        slot_r = __float_as_uint(s2);
-        tmax = fmaxf(tmax, s2);
+        for (int col = 0; col < BLOCK_N; ++col)
+          tmax = fmaxf(tmax, __uint_as_float(col < 32 ? r0[col] : r1[col - 32]));
+      } else {
+#pragma unroll
+        for (int col = 0; col < BLOCK_N; ++col) {
+          uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
+          const float sraw = col < lim ? __uint_as_float(slot_r) : -INFINITY;
+          slot_r = __float_as_uint(sraw);
+          tmax = fmaxf(tmax, sraw);
+        }
       }
+      tmax *= a.scale_log2;
       cnt = max(lim, 0);
       if (t == 0) att += cnt;
       // lazy rescale: only when the running reference falls more than 2^8 behind
@@ -287,6 +294,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tc_fence_before();
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      const float neg_m = -m_use, sc = a.scale_log2;
       uint8_t* p_row = smem + C::P_OFF + b * C::P_BYTES;
       float add = 0.f;
 #pragma unroll
@@ -297,8 +305,8 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
           for (int i = 0; i < 8; ++i) {
             const uint32_t u0 = p < 2 ? r0[p * PAGE + 2 * i] : r1[(p - 2) * PAGE + 2 * i];
             const uint32_t u1 = p < 2 ? r0[p * PAGE + 2 * i + 1] : r1[(p - 2) * PAGE + 2 * i + 1];
-            const float e0 = exp2f(__uint_as_float(u0) - m_use);
-            const float e1 = exp2f(__uint_as_float(u1) - m_use);
+            const float e0 = fast_exp2(fmaf(__uint_as_float(u0), sc, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(u1), sc, neg_m));
             add += e0 + e1;
             __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
             packed[i] = *reinterpret_cast<uint32_t*>(&pr);

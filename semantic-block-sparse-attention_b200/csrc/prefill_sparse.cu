@@ -412,8 +412,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(bar(B_SEMPTY + b));
+      // masked raw logits (scaling is folded into the exponent below)
       float tmax = -INFINITY;
       int n_on = 0;
+      const uint32_t qbit = 1u << qslot;
       const uint4* mk = reinterpret_cast<const uint4*>(plan[ps].mask);
 #pragma unroll
       for (int g4 = 0; g4 < BLOCK_N / 4; ++g4) {
@@ -424,14 +426,15 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           for (int e = 0; e < 4; ++e) {
             const int col = g4 * 4 + e;
             uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
-            const bool allowed = (mm[e] >> qslot) & 1u;
-            const float s2 = allowed ? __uint_as_float(slot_r) * a.scale_log2 : -INFINITY;
-            slot_r = __float_as_uint(s2);
-            tmax = fmaxf(tmax, s2);
+            const bool allowed = (mm[e] & qbit) != 0u;
+            const float sraw = allowed ? __uint_as_float(slot_r) : -INFINITY;
+            slot_r = __float_as_uint(sraw);
+            tmax = fmaxf(tmax, sraw);
             n_on += allowed;
           }
         }
       }
+      tmax *= a.scale_log2;                      // scale > 0: the max commutes with it
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
       if (t == 0) att += n_on;
@@ -463,6 +466,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         tc_fence_before();
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      const float neg_m = -m_use, sc = a.scale_log2;
       uint8_t* p_row = smem + C::P_OFF + b * C::P_BYTES;
       float add = 0.f;
 #pragma unroll
@@ -473,8 +477,8 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           for (int i = 0; i < 8; ++i) {
             const uint32_t u0 = p < 2 ? r0[p * 16 + 2 * i] : r1[(p - 2) * 16 + 2 * i];
             const uint32_t u1 = p < 2 ? r0[p * 16 + 2 * i + 1] : r1[(p - 2) * 16 + 2 * i + 1];
-            const float e0 = exp2f(__uint_as_float(u0) - m_use);
-            const float e1 = exp2f(__uint_as_float(u1) - m_use);
+            const float e0 = fast_exp2(fmaf(__uint_as_float(u0), sc, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(u1), sc, neg_m));
             add += e0 + e1;
             __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
             packed[i] = *reinterpret_cast<uint32_t*>(&pr);

@@ -225,6 +225,13 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 2^x on the special-function unit (flushes denormals; -inf -> 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Byte offset of element (row, 16-byte chunk) inside a [rows][128 B] tile stored with
 // the 128-byte swizzle (what TMA writes and UMMA reads): chunk ^= row % 8.
 __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk) {
