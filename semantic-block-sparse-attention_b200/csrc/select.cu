@@ -151,53 +151,98 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
     // epilogue warps: thread = row (query i = row / G, head t = row % G)
     const int row = threadIdx.x;
     const int qi = q0 + row / G;
-    float m_run = -INFINITY, l_run = 0.f, lse2 = 0.f;
+    // Routing vectors and descriptors are unit vectors (up to bf16 rounding), so every logit is
+    // bounded by 1.01 * scale: with a moderate scale the log-sum-exp needs no running maximum.
+    const bool fixed_max = scale_log2 <= 60.f;
+    const float m_fixed = 1.01f * scale_log2;
+    float m_run = fixed_max ? m_fixed : -INFINITY, l_run = 0.f, lse2 = 0.f;
     const int32_t* sz = sizes + (int64_t)h * num_clusters;
+    // column offset of this lane's share after the head butterfly (depends on the lane only)
+    int col_off = 0;
+    {
+      int width = 32;
+#pragma unroll
+      for (int bit = 1; bit < G; bit <<= 1) {
+        width >>= 1;
+        col_off += (lane & bit) ? width : 0;
+      }
+    }
+    constexpr int OUT = 32 / G;                    // outputs per thread per 32 columns
     bool ok = true;
     for (int j = 0; j < total && ok; ++j) {
       const int b = j & 1;
+      const int pass = j / chunks;
+      const int c0 = (j % chunks) * SC_BN;
+      const bool full_chunk = c0 + SC_BN <= num_clusters;
+      // sizes of this thread's output clusters, fetched before the accumulator is awaited
+      int nsz[SC_BN / 32][OUT];
+      if (pass == 1) {
+#pragma unroll
+        for (int c4 = 0; c4 < SC_BN / 32; ++c4)
+#pragma unroll
+          for (int i = 0; i < OUT; ++i) {
+            const int c = c0 + c4 * 32 + col_off + i;
+            nsz[c4][i] = c < num_clusters ? sz[c] : 0;
+          }
+      }
       ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
-      const int pass = j / chunks;
-      const int c0 = (j % chunks) * SC_BN;
-      if (j == chunks) lse2 = m_run + log2f(l_run);
-#pragma unroll 1
+      if (j == chunks) lse2 = m_run + __log2f(l_run);
+      const float neg_ref = pass == 0 ? -m_run : -lse2;
+#pragma unroll
       for (int c4 = 0; c4 < SC_BN / 32; ++c4) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * SC_BN + c4 * 32, r);
         tmem_ld_wait();
         const int cbase = c0 + c4 * 32;
         if (pass == 0) {
-          float mx = m_run;
+          if (fixed_max) {
+            float add = 0.f;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float s2 = __uint_as_float(r[i]) * scale_log2;
-            s2 = (cbase + i < num_clusters) ? s2 : -INFINITY;
-            r[i] = __float_as_uint(s2);
-            mx = fmaxf(mx, s2);
+            for (int i = 0; i < 32; ++i) {
+              const float e = fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, neg_ref));
+              add += (full_chunk || cbase + i < num_clusters) ? e : 0.f;
+            }
+            l_run += add;
+          } else {
+            float mx = m_run;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float s2 = __uint_as_float(r[i]) * scale_log2;
+              s2 = (full_chunk || cbase + i < num_clusters) ? s2 : -INFINITY;
+              r[i] = __float_as_uint(s2);
+              mx = fmaxf(mx, s2);
+            }
+            float add = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) add += fast_exp2(__uint_as_float(r[i]) - mx);
+            l_run = l_run * fast_exp2(m_run - mx) + add;
+            m_run = mx;
           }
-          float add = 0.f;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) add += exp2f(__uint_as_float(r[i]) - mx);
-          l_run = l_run * exp2f(m_run - mx) + add;
-          m_run = mx;
         } else {
           float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = exp2f(__uint_as_float(r[i]) * scale_log2 - lse2);
-          const int col = head_butterfly<G>(v, lane);
+          for (int i = 0; i < 32; ++i) v[i] = fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, neg_ref));
+          head_butterfly<G>(v, lane);
           if (qi < num_queries) {
-            float* dst = score + ((int64_t)qi * num_kv_heads + h) * num_clusters;
+            float* dst = score + ((int64_t)qi * num_kv_heads + h) * num_clusters + cbase + col_off;
+            float o[OUT];
 #pragma unroll
-            for (int i = 0; i < 32 / G; ++i) {
-              const int c = cbase + col + i;
-              if (c < num_clusters) {
-                const float n = (float)sz[c];
-                float sc = log2f(fmaxf(v[i], 1e-38f)) * LN2;
-                if (beta != 0.f) sc -= beta * logf(1.0f + n);
-                dst[c] = n > 0.f ? sc : NEG_BIG;
-              }
+            for (int i = 0; i < OUT; ++i) {
+              const float n = (float)nsz[c4][i];
+              float sc = __log2f(fmaxf(v[i], 1e-38f)) * LN2;
+              if (beta != 0.f) sc -= beta * (__log2f(1.0f + n) * LN2);
+              o[i] = n > 0.f ? sc : NEG_BIG;
+            }
+            if (full_chunk && OUT % 4 == 0) {
+#pragma unroll
+              for (int i = 0; i < OUT; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < OUT; ++i)
+                if (cbase + col_off + i < num_clusters) dst[i] = o[i];
             }
           }
         }
@@ -301,6 +346,80 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
   }
 }
 
+// Register-resident form for C = 32 * PER <= 2048: the warp keeps the whole score row and the
+// sizes in registers, so each bisection step is a compare and a predicated add per cluster.
+template <int PER>
+__global__ void __launch_bounds__(256)
+select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
+                  int num_kv_heads, float target_tokens, int iters, int force_sink,
+                  int32_t* __restrict__ qmask, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ tokens, int32_t* __restrict__ top1) {
+  constexpr int C = PER * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y;
+  const int q = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (q >= num_queries) return;
+  const float* row = score + ((int64_t)q * num_kv_heads + h) * C;
+  const int32_t* sz = sizes + (int64_t)h * C;
+  float sc[PER], nn[PER];
+  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  int arg = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = i * 32 + lane;
+    sc[i] = row[c];
+    nn[i] = (float)sz[c];
+    if (sc[i] > mx) arg = c;
+    mx = fmaxf(mx, sc[i]);
+    mn = fminf(mn, nn[i] > 0.f ? sc[i] : 3.4e38f);
+    tot += nn[i] > 0.f ? nn[i] : 0.f;
+  }
+  const float best = warp_max(mx);
+  if (top1) {
+    int cand = mx == best ? arg : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+    if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
+  }
+  float hi = best + 1e-6f;
+  float lo = warp_min(mn) - 1e-6f;
+  lo = fminf(lo, hi - 1e-5f);
+  const bool all_fit = warp_sumf(tot) < target_tokens;
+  for (int it = 0; it < iters; ++it) {
+    const float mid = (lo + hi) * 0.5f;
+    float above = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) above += sc[i] >= mid ? nn[i] : 0.f;
+    above = warp_sumf(above);
+    const bool reach = above >= target_tokens;
+    lo = reach ? mid : lo;
+    hi = reach ? hi : mid;
+  }
+  const float theta = all_fit ? NEG_BIG : lo;
+  int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * PER;
+  int n_sel = 0;
+  float n_tok = 0.f;
+  unsigned mine = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const bool sel = nn[i] > 0.f && sc[i] >= theta;
+    unsigned bits = __ballot_sync(0xffffffffu, sel);
+    n_sel += __popc(bits);
+    n_tok += sel ? nn[i] : 0.f;
+    if (i == 0 && force_sink) bits |= 1u;
+    if ((i & 31) == lane) mine = bits;
+    if ((i & 31) == 31 || i == PER - 1) {
+      const int w = (i & ~31) + lane;
+      if (w <= i) qm[w] = (int32_t)mine;
+    }
+  }
+  n_tok = warp_sumf(n_tok);
+  if (lane == 0) {
+    if (counts) counts[(int64_t)q * num_kv_heads + h] = n_sel;
+    if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)n_tok;
+  }
+}
+
 template <int D, int G>
 int launch_score(const void* vectors, int num_queries, int num_q_heads, const void* codebooks,
                  int num_kv_heads, int num_clusters, const int32_t* sizes, float temperature,
@@ -361,6 +480,22 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
                                       int32_t* counts, int32_t* tokens, int32_t* top1, void* stream) {
   SEMBLO_REQUIRE(num_clusters % 32 == 0, "cluster count %d must be a multiple of 32", num_clusters);
   if (num_queries == 0) return 0;
+  cudaStream_t st_sel = (cudaStream_t)stream;
+#define SEMBLO_SELECT_REG(PER)                                                                      \
+  if (num_clusters == PER * 32) {                                                                   \
+    dim3 grid_r((unsigned)ceil_div(num_queries, 8), num_kv_heads);                                  \
+    select_kernel_reg<PER><<<grid_r, 256, 0, st_sel>>>(score, select_sizes, num_queries, num_kv_heads, \
+                                                      (float)target_tokens, iters, force_sink, qmask, \
+                                                      counts, tokens, top1);                        \
+    SEMBLO_LAUNCH_CHECK();                                                                          \
+    return 0;                                                                                       \
+  }
+  SEMBLO_SELECT_REG(4)
+  SEMBLO_SELECT_REG(8)
+  SEMBLO_SELECT_REG(16)
+  SEMBLO_SELECT_REG(32)
+  SEMBLO_SELECT_REG(64)
+#undef SEMBLO_SELECT_REG
   int warps = 8;
   while (warps > 1 && (size_t)(warps + 1) * num_clusters * 4 > 200 * 1024) warps >>= 1;
   const size_t smem = (size_t)(warps + 1) * num_clusters * 4;

@@ -468,3 +468,28 @@ def test_decode_steps_through_the_arena(dev, dim, hq, hkv, sink):
         assert torch.equal(arena.suffix_kpre.cpu().float(), ref.suffix_kpre.float())
     finally:
         os.environ.pop("SEMBLO_SINK_TOKENS", None)
+
+
+@pytest.mark.parametrize("clusters", [128, 2048, 4096])
+def test_threshold_selection_on_given_scores_is_exact(dev, clusters):
+    """Register-resident (C <= 2048) and shared-memory (larger C) selectors against the oracle's
+    float32 rule on identical scores: the result is a pure function of (scores, sizes)."""
+    from semblo_b200._lib import lib, ptr, check, stream_ptr
+    g = torch.Generator().manual_seed(clusters)
+    nq, hkv, target = 77, 3, 900
+    sizes = torch.randint(0, 40, (hkv, clusters), generator=g).int()
+    sizes[:, ::5] = 0
+    sizes[2] = (sizes[2] > 30).int()                      # everything fits for head 2
+    score = torch.randn(nq, hkv, clusters, generator=g) * 2
+    score = torch.where(sizes[None] > 0, score, torch.full_like(score, O.NEG_BIG))
+    want = O.theta_select(score, sizes[None], target, 16)
+    qmask = torch.empty(nq, hkv, clusters // 32, dtype=torch.int32, device=dev)
+    counts = torch.empty(nq, hkv, dtype=torch.int32, device=dev)
+    tokens = torch.empty(nq, hkv, dtype=torch.int32, device=dev)
+    top1 = torch.empty(hkv, nq, dtype=torch.int32, device=dev)
+    check(lib().semblo_select_clusters(ptr(score.to(dev)), ptr(sizes.to(dev)), nq, hkv, clusters, target, 16, 0,
+                                       ptr(qmask), ptr(counts), ptr(tokens), ptr(top1), stream_ptr()))
+    assert torch.equal(O.unpack_bits(qmask.cpu()), want)
+    assert torch.equal(counts.cpu(), want.sum(-1).int())
+    assert torch.equal(tokens.cpu(), (want * sizes[None]).sum(-1).int())
+    assert torch.equal(top1.cpu().long().t(), score.argmax(-1))
