@@ -98,6 +98,7 @@ def test_kmeans_update_with_empty_cluster_restart(dev):
     repl = torch.randperm(n, generator=g)
     want, _ = O.kmeans_update(sample, assign, clusters, repl)
     s_d, a_d = sample.to(dev), assign.to(torch.int32).to(dev)
+    repl_d = repl.to(dev)
     counts = torch.empty(clusters, dtype=torch.int32, device=dev)
     ip = torch.empty(clusters + 1, dtype=torch.int32, device=dev)
     er = torch.empty(clusters, dtype=torch.int32, device=dev)
@@ -109,13 +110,13 @@ def test_kmeans_update_with_empty_cluster_restart(dev):
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     cf = torch.empty(clusters, dim, dtype=torch.float32, device=dev)
     cb = torch.empty(clusters, dim, dtype=torch.bfloat16, device=dev)
-    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl.to(dev)),
+    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl_d),
                                      ptr(cf), ptr(cb), ptr(ws), ws_bytes, stream_ptr()))
     torch.testing.assert_close(cf.cpu(), want, atol=2e-6, rtol=0)
     assert torch.equal(cb.cpu().float(), cf.cpu().to(torch.bfloat16).float())
     # deterministic: a second run gives the same bytes
     cf2 = torch.empty_like(cf)
-    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl.to(dev)),
+    check(lib().semblo_kmeans_update(ptr(s_d), ptr(a_d), n, clusters, dim, ptr(ip), ptr(er), ptr(repl_d),
                                      ptr(cf2), ptr(cb), ptr(ws), ws_bytes, stream_ptr()))
     assert torch.equal(cf, cf2)
 
@@ -487,7 +488,8 @@ def test_threshold_selection_on_given_scores_is_exact(dev, clusters):
     counts = torch.empty(nq, hkv, dtype=torch.int32, device=dev)
     tokens = torch.empty(nq, hkv, dtype=torch.int32, device=dev)
     top1 = torch.empty(hkv, nq, dtype=torch.int32, device=dev)
-    check(lib().semblo_select_clusters(ptr(score.to(dev)), ptr(sizes.to(dev)), nq, hkv, clusters, target, 16, 0,
+    score_d, sizes_d = score.to(dev), sizes.to(dev)          # keep the device copies alive across the call
+    check(lib().semblo_select_clusters(ptr(score_d), ptr(sizes_d), nq, hkv, clusters, target, 16, 0,
                                        ptr(qmask), ptr(counts), ptr(tokens), ptr(top1), stream_ptr()))
     assert torch.equal(O.unpack_bits(qmask.cpu()), want)
     assert torch.equal(counts.cpu(), want.sum(-1).int())
