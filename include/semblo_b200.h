@@ -131,19 +131,22 @@ int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key, 
  * [local_start, q_position] of the position-ordered K/V, exactly causally.
  * q, out [Q, Hq, D] bf16 (consecutive queries); q_positions [Q]; ordered_k / ordered_v
  * [ordered_rows, Hkv, D] hold positions ordered_pos0 ...; lse [Q, Hq] (natural log) and
- * attended (sum over (query, KV head) of attended keys, accumulated) may be NULL. */
+ * attended (sum over (query, KV head) of attended keys, accumulated) may be NULL.
+ * partial_out [Q, Hq, D] fp32 (may be NULL): when given, the normalised result goes there
+ * instead of `out`, for semblo_sparse_prefill_gather to merge without a bf16 rounding. */
 int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
                           int head_dim, const int32_t* q_positions, const void* ordered_k,
                           const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
-                          int local_start, float sm_scale, void* out, float* lse,
+                          int local_start, float sm_scale, void* out, float* partial_out, float* lse,
                           unsigned long long* attended, int32_t* status, void* stream);
 
 /* The sparse part of semblo/vllm_plugin/kv_outer.py:482-816 with row-granular reads: for every
  * query, attention over rows [indptr[c], indptr[c] + causal_sizes[c]) of the clusters set in
  * its qmask, gathered row by row from the cluster-ordered K/V (packed_k / packed_v
  * [rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
- * ([Hkv, Q], optional).  merge = 1: `out` / `lse` hold the window partial written by
- * semblo_window_prefill (normalised output, natural-log LSE) and receive the LSE-merged
+ * ([Hkv, Q], optional).  merge = 1: partial_in (fp32; or `out` as bf16 when partial_in is
+ * NULL) and `lse` hold the window partial written by semblo_window_prefill (normalised
+ * output, natural-log LSE); `out` / `lse` receive the LSE-merged
  * result (kv_outer.py:203-227); merge = 0: the sparse result alone.  attended (may be NULL)
  * points at two counters: [0] += attended keys summed over (query, KV head), [1] += K/V rows
  * gathered summed over tiles (the union each tile actually reads). */
@@ -152,7 +155,8 @@ int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads
                                  const void* packed_v, const int32_t* page_table,
                                  const int32_t* qmask, const int32_t* causal_sizes,
                                  const int32_t* indptr, int num_clusters, float sm_scale, int merge,
-                                 void* out, float* lse, unsigned long long* attended,
+                                 const float* partial_in, void* out, float* lse,
+                                 unsigned long long* attended,
                                  int32_t* status, void* stream);
 
 /* ---- decode ----------------------------------------------------------------------- */

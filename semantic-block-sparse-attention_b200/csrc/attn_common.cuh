@@ -1,0 +1,199 @@
+// Softmax / epilogue code shared by the two prefill attention kernels.
+//
+// A tile is 128 rows x 64 keys.  Two warpgroups of 128 threads split the 64 columns of
+// S: thread (half, row) owns columns [32 half, 32 half + 32) of its row.  The row maximum
+// is exchanged through shared memory, the running reference maximum m_ref is kept
+// identical in both threads of a row, each thread keeps the partial sum of its own
+// columns, and each half rescales / finalises its own D/2 columns of O.
+#pragma once
+#include "sm100.cuh"
+
+namespace attn {
+
+using namespace sm100;
+
+constexpr float LN2F = 0.6931471805599453f;
+constexpr float LOG2EF = 1.4426950408889634f;
+constexpr float RESCALE_GAP = 8.0f;              // log2 units: rescale O only when the max moved by > 2^8
+
+// Rendezvous of the 256 softmax threads on an mbarrier (count 256).  Unlike bar.sync the wait
+// is bounded and observes the abort flag, so a role that gave up cannot strand its partners.
+__device__ __forceinline__ bool softmax_group_sync(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                   int* status) {
+  mbar_arrive(bar);
+  return mbar_wait(bar, parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX);
+}
+
+// One half-row of one tile.  r[] holds the 32 raw logits of this half with masked entries
+// already set to -inf; tmax_raw is their maximum.  my_pages = how many 16-column groups of
+// this half exist in the tile (0, 1 or 2).  Returns false after a wait timed out.
+template <int D, int O_COL, int BLOCK_N>
+__device__ __forceinline__ bool softmax_half_tile(
+    uint32_t (&r)[32], float tmax_raw, int my_pages, int j, int hf, int row, uint32_t lane_addr,
+    uint32_t tmem_base, uint8_t* p_buf, __nv_bfloat16* xchg /* [2][2][128] */, uint32_t bar_xchg0,
+    uint32_t bar_pempty_b,
+    uint32_t bar_pempty_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
+    float& l_rnd, volatile int* abort_flag, int* status) {
+  // Both threads of a row must agree on the reference exactly, so each publishes its maximum
+  // rounded UP to bf16 and both take the larger of the two rounded values (a reference slightly
+  // above the true maximum is harmless).  Double-buffered by tile parity: one barrier per tile.
+  __nv_bfloat16* xc = xchg + (j & 1) * 256;
+  const __nv_bfloat16 mine = __float2bfloat16_ru(tmax_raw);
+  xc[hf * 128 + row] = mine;
+  if (!softmax_group_sync(bar_xchg0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, status)) return false;
+  const float tmax = fmaxf(__bfloat162float(mine), __bfloat162float(xc[(hf ^ 1) * 128 + row])) * scale_log2;
+  // lazy rescale: only when the running reference falls more than 2^8 behind
+  const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
+  float alpha = 1.f;
+  if (need) {
+    alpha = fast_exp2(m_ref - tmax);
+    m_ref = tmax;
+    l_part *= alpha;
+    l_rnd *= alpha;
+  } else if (m_ref == -INFINITY) {
+    m_ref = tmax;
+  }
+  if (!mbar_wait(bar_pempty_b, ((j >> 1) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+  if (__any_sync(0xffffffffu, need)) {
+    // O must be quiescent: the previous tile's P V has to be complete
+    if (!mbar_wait(bar_pempty_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < D / 64; ++c) {
+      uint32_t o[32];
+      const uint32_t addr = tmem_base + lane_addr + O_COL + hf * (D / 2) + c * 32;
+      tmem_ld32(addr, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+      tmem_st32(addr, o);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+  }
+  const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+  float add = 0.f, add_rnd = 0.f;
+#pragma unroll
+  for (int p = 0; p < 2; ++p) {
+    if (p < my_pages) {
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float e0 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i]), scale_log2, neg_m));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i + 1]), scale_log2, neg_m));
+        __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+        packed[i] = *reinterpret_cast<uint32_t*>(&pr);
+        add += e0 + e1;
+        // O is normalised by the sum of the weights as the tensor core sees them, so the
+        // rounding of P perturbs the convex combination and not its scale; the exact sum
+        // gives the LSE
+        add_rnd += __uint_as_float(packed[i] << 16) + __uint_as_float(packed[i] & 0xffff0000u);
+      }
+      const int chunk = (hf * 2 + p) * 2;
+      *reinterpret_cast<uint4*>(p_buf + swz128(row, chunk)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(p_buf + swz128(row, chunk + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    }
+  }
+  l_part += add;
+  l_rnd += add_rnd;
+  fence_proxy_async_smem();
+  mbar_arrive(bar_pfull_b);
+  return true;
+}
+
+// Final write of this half's D/2 output columns.  merge != 0: another partial (normalised
+// output in prev_f32, or in `dst` as bf16 when prev_f32 is null; natural-log LSE in lse_ptr) is
+// LSE-merged with this one.  out_f32 != null: the result is written there in fp32 instead of
+// `dst` (a partial that a later launch merges without an intermediate bf16 rounding).
+template <int D, int O_COL>
+__device__ __forceinline__ void epilogue_half(bool have_tiles, int hf, int row, uint32_t lane_addr,
+                                              uint32_t tmem_base, float* xchg, uint32_t bar_epi, float m_ref,
+                                              float l_part, float l_rnd, bool qvalid, int merge,
+                                              __nv_bfloat16* dst /* row base */, const float* prev_f32,
+                                              float* out_f32, float* lse_ptr /* this row's slot or null */,
+                                              volatile int* abort_flag, int* status) {
+  xchg[hf * 128 + row] = l_part;
+  xchg[256 + hf * 128 + row] = l_rnd;
+  if (!softmax_group_sync(bar_epi, 0, abort_flag, status)) return;
+  const float l_run = l_part + xchg[(hf ^ 1) * 128 + row];
+  const float l_rnd_run = l_rnd + xchg[256 + (hf ^ 1) * 128 + row];
+  const float own = l_rnd_run > 0.f ? l_run / l_rnd_run : 0.f;   // O / l_rnd_run is the normalised partial
+  float wa = 0.f, wb = 1.f, denom = l_run, m_new = m_ref;
+  if (merge && qvalid) {
+    const float l2 = *lse_ptr * LOG2EF;                 // the other partial's LSE in log2 units
+    m_new = fmaxf(l2, m_ref);
+    if (m_new == -INFINITY) {
+      wa = 0.f; wb = 0.f; denom = 0.f;
+    } else {
+      wa = fast_exp2(l2 - m_new);
+      wb = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_new);
+      denom = wa + l_run * wb;
+    }
+  }
+  if (!softmax_group_sync(bar_epi, 1, abort_flag, status)) return;   // both halves have read the old LSE
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+#pragma unroll 1
+  for (int c = 0; c < D / 64; ++c) {
+    uint32_t o[32];
+    const int col0 = hf * (D / 2) + c * 32;
+    if (have_tiles) {
+      tmem_ld32(tmem_base + lane_addr + O_COL + col0, o);
+      tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = 0u;
+    }
+    if (qvalid) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst + col0);
+      float prev[32];
+      if (merge) {
+        if (prev_f32) {
+          const float4* p4 = reinterpret_cast<const float4*>(prev_f32 + col0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 v = p4[i];
+            prev[4 * i] = v.x; prev[4 * i + 1] = v.y; prev[4 * i + 2] = v.z; prev[4 * i + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint4 v = d4[i];
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[e]));
+              prev[8 * i + 2 * e] = pv.x;
+              prev[8 * i + 2 * e + 1] = pv.y;
+            }
+          }
+        }
+      }
+      float x[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float v = __uint_as_float(o[i]) * (wb * own);
+        if (merge) v += prev[i] * wa;
+        x[i] = v * inv;
+      }
+      if (out_f32) {
+        float4* o4 = reinterpret_cast<float4*>(out_f32 + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o4[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+      } else {
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          __nv_bfloat162 pr = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+        d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        d4[2] = make_uint4(w[8], w[9], w[10], w[11]);
+        d4[3] = make_uint4(w[12], w[13], w[14], w[15]);
+      }
+    }
+  }
+  if (qvalid && lse_ptr && hf == 0) *lse_ptr = denom > 0.f ? (m_new + __log2f(denom)) * LN2F : -INFINITY;
+}
+
+}  // namespace attn

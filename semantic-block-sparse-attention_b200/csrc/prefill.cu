@@ -18,6 +18,7 @@
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
+#include "attn_common.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -28,8 +29,6 @@ namespace {
 constexpr int PAGE = 16;
 constexpr int PAGES_PER_TILE = 4;
 constexpr int BLOCK_N = PAGE * PAGES_PER_TILE;     // 64 keys per tile
-constexpr float LN2F = 0.6931471805599453f;
-constexpr float RESCALE_GAP = 8.0f;                // log2 units
 
 struct TileInfo {
   int npages;          // 16-row groups in the tile, 0 = end of stream
@@ -49,9 +48,10 @@ struct AttnCfg {
   static constexpr int K_OFF = Q_OFF + Q_BYTES;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
-  static constexpr int BAR_OFF = P_OFF + 2 * P_BYTES;
+  static constexpr int XCHG_OFF = P_OFF + 2 * P_BYTES;        // bf16 [2][2][128]
+  static constexpr int BAR_OFF = XCHG_OFF + 1024;
   static constexpr int INFO_OFF = BAR_OFF + 256;
-  static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64 + 1024;
+  static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
   static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
   static constexpr int O_COL = 2 * BLOCK_N;
 };
@@ -68,24 +68,30 @@ struct PrefillArgs {
   float scale_log2;               // sm_scale * log2(e)
   __nv_bfloat16* out;             // [Q, Hq, D]
   float* lse;                     // [Q, Hq] or null
+  float* partial;                 // [Q, Hq, D] fp32: written instead of `out` when not null
   unsigned long long* attended;   // sum over (query, KV head) of attended keys, or null
   int* status;
 };
 
 // barrier slots
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KVFULL = 10, B_KVEMPTY = 14 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KVFULL = 10, B_KVEMPTY = 14,
+       B_XCHG = 18, B_EPI = 20 };
 
 template <int D, int G>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_ok,
                       const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
   using C = AttnCfg<D>;
   constexpr int QT = 128 / G;
   constexpr int STAGES = C::STAGES;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, STATUS_SMEM_ALIGN);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
+  __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::XCHG_OFF);
   TileInfo* info = reinterpret_cast<TileInfo*>(smem + C::INFO_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::INFO_OFF + STAGES * sizeof(TileInfo));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -98,15 +104,17 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 1);
     mbar_init(bar(B_OREADY), 1);
+    mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_SEMPTY + b), 128);
-      mbar_init(bar(B_PFULL + b), 128);
+      mbar_init(bar(B_SEMPTY + b), 256);
+      mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PEMPTY + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 5);     // four softmax warps + the UMMA commit
+      mbar_init(bar(B_KVEMPTY + s), 9);     // eight softmax warps + the UMMA commit
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -120,7 +128,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ producer
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
@@ -166,7 +174,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
     if (elect_one()) {
       const uint32_t q_base = smem_u32(smem + C::Q_OFF);
@@ -212,15 +220,17 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (ok) umma_commit(bar(B_OREADY));
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (thread = row)
-    const int row = threadIdx.x;
+    // ------------------------------------------------------------ softmax + epilogue
+    // warps 0-3: columns [0, 32) of every tile, warps 4-7: columns [32, 64); thread = row
+    const int hf = warp >> 2;
+    const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
     const bool qvalid = slot < a.num_queries;
     const int qi = qvalid ? slot : 0;
     const int qpos = qvalid ? a.q_positions[qi] : -1;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m_ref = -INFINITY, l_run = 0.f;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
     unsigned long long att = 0;
     bool ok = true;
     int j = 0;
@@ -233,131 +243,54 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
       const int rows = info[s].rows, kpos0 = info[s].kpos0;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
+      const int my_pages = min(max(np - 2 * hf, 0), 2);
       ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       tc_fence_after();
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tmem_base + lane_addr + b * BLOCK_N, r0);
-      if (np > 2) tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + 32, r1);
-      tmem_ld_wait();
+      uint32_t r[32];
+      if (my_pages > 0) {
+        tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + hf * 32, r);
+        tmem_ld_wait();
+      }
       tc_fence_before();
       mbar_arrive(bar(B_SEMPTY + b));
-      // masks, scaled logits, tile max
+      // keys of this half at or before the row's position; tiles wholly below the diagonal for
+      // every row of the warp need no mask (scaling is folded into the exponent)
+      const int lim = min(rows, qpos - kpos0 + 1) - hf * 32;
       float tmax = -INFINITY;
-      int cnt = 0;
-      // keys of the tile at or before this row's position; tiles wholly below the diagonal
-      // for every row of the warp need no mask (scaling is folded into the exponent below)
-      const int lim = min(rows, qpos - kpos0 + 1);
-      if (__all_sync(0xffffffffu, lim >= BLOCK_N)) {
+      if (my_pages > 0) {
+        if (__all_sync(0xffffffffu, lim >= 32)) {
 #pragma unroll
-        for (int col = 0; col < BLOCK_N; ++col)
-          tmax = fmaxf(tmax, __uint_as_float(col < 32 ? r0[col] : r1[col - 32]));
-      } else {
-#pragma unroll
-        for (int col = 0; col < BLOCK_N; ++col) {
-          uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
-          const float sraw = col < lim ? __uint_as_float(slot_r) : -INFINITY;
-          slot_r = __float_as_uint(sraw);
-          tmax = fmaxf(tmax, sraw);
-        }
-      }
-      tmax *= a.scale_log2;
-      cnt = max(lim, 0);
-      if (t == 0) att += cnt;
-      // lazy rescale: only when the running reference falls more than 2^8 behind
-      bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
-      float alpha = 1.f;
-      if (need) {
-        alpha = exp2f(m_ref - tmax);
-        m_ref = tmax;
-        l_run *= alpha;
-      } else if (m_ref == -INFINITY) {
-        m_ref = tmax;
-      }
-      ok = mbar_wait(bar(B_PEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-      if (!ok) break;
-      if (__any_sync(0xffffffffu, need)) {
-        // O must be quiescent: the previous tile's P V has to be complete
-        ok = mbar_wait(bar(B_PEMPTY + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-      }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      const float neg_m = -m_use, sc = a.scale_log2;
-      uint8_t* p_row = smem + C::P_OFF + b * C::P_BYTES;
-      float add = 0.f;
-#pragma unroll
-      for (int p = 0; p < PAGES_PER_TILE; ++p) {
-        if (p < np) {
-          uint32_t packed[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t u0 = p < 2 ? r0[p * PAGE + 2 * i] : r1[(p - 2) * PAGE + 2 * i];
-            const uint32_t u1 = p < 2 ? r0[p * PAGE + 2 * i + 1] : r1[(p - 2) * PAGE + 2 * i + 1];
-            const float e0 = fast_exp2(fmaf(__uint_as_float(u0), sc, neg_m));
-            const float e1 = fast_exp2(fmaf(__uint_as_float(u1), sc, neg_m));
-            add += e0 + e1;
-            __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-            packed[i] = *reinterpret_cast<uint32_t*>(&pr);
-          }
-          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        }
-      }
-      l_run += add;
-      fence_proxy_async_smem();
-      mbar_arrive(bar(B_PFULL + b));
-    }
-    // epilogue
-    if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
-    if (ok) {
-      tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = a.out + ((int64_t)qi * a.num_q_heads + h * G + t) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        if (j > 0) {
-          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-          tmem_ld_wait();
+          for (int col = 0; col < 32; ++col) tmax = fmaxf(tmax, __uint_as_float(r[col]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (qvalid) {
-          uint32_t w[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv,
-                                                      __uint_as_float(o[2 * i + 1]) * inv);
-            w[i] = *reinterpret_cast<uint32_t*>(&pr);
+          for (int col = 0; col < 32; ++col) {
+            const float sraw = col < lim ? __uint_as_float(r[col]) : -INFINITY;
+            r[col] = __float_as_uint(sraw);
+            tmax = fmaxf(tmax, sraw);
           }
-          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
-          d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          d4[2] = make_uint4(w[8], w[9], w[10], w[11]);
-          d4[3] = make_uint4(w[12], w[13], w[14], w[15]);
         }
       }
-      if (qvalid && a.lse)
-        a.lse[(int64_t)qi * a.num_q_heads + h * G + t] = l_run > 0.f ? (m_ref + log2f(l_run)) * LN2F : -INFINITY;
-      if (a.attended) {
-        if (!qvalid) att = 0;
+      if (t == 0) att += min(max(lim, 0), 32);
+      ok = attn::softmax_half_tile<D, C::O_COL, BLOCK_N>(
+          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, smem + C::P_OFF + b * C::P_BYTES, xchg,
+          bar(B_XCHG), bar(B_PEMPTY + b), bar(B_PEMPTY + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2,
+          m_ref, l_part, l_rnd, abort_flag, a.status);
+      if (!ok) break;
+    }
+    if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::P_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+                                     ok && qvalid, 0, a.out + hidx * D, nullptr,
+                                     a.partial ? a.partial + hidx * D : nullptr, a.lse ? a.lse + hidx : nullptr,
+                                     abort_flag, a.status);
+    if (ok && a.attended) {
+      if (!qvalid) att = 0;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
-        if (lane == 0 && att) atomicAdd(a.attended, att);
-      }
+      for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
+      if (lane == 0 && att) atomicAdd(a.attended, att);
     }
     tc_fence_before();
   }
@@ -389,7 +322,7 @@ int launch_prefill(const void* q, const void* ordered_k, const void* ordered_v, 
   auto kern = window_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 192, C::TOTAL, st>>>(mq, mok, mov, a);
+  kern<<<grid, 320, C::TOTAL, st>>>(mq, mok, mov, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
@@ -399,8 +332,9 @@ int launch_prefill(const void* q, const void* ordered_k, const void* ordered_v, 
 extern "C" int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
                                      int head_dim, const int32_t* q_positions, const void* ordered_k,
                                      const void* ordered_v, int64_t ordered_rows, int ordered_pos0,
-                                     int local_start, float sm_scale, void* out, float* lse,
-                                     unsigned long long* attended, int32_t* status, void* stream) {
+                                     int local_start, float sm_scale, void* out, float* partial_out,
+                                     float* lse, unsigned long long* attended, int32_t* status,
+                                     void* stream) {
   SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
   SEMBLO_REQUIRE(ordered_k != nullptr && ordered_v != nullptr && q_positions != nullptr, "K, V and positions are required");
@@ -418,6 +352,7 @@ extern "C" int semblo_window_prefill(const void* q, int num_queries, int num_q_h
   a.scale_log2 = sm_scale * 1.4426950408889634f;
   a.out = (__nv_bfloat16*)out;
   a.lse = lse;
+  a.partial = partial_out;
   a.attended = attended;
   a.status = status;
   const int g = num_q_heads / num_kv_heads;

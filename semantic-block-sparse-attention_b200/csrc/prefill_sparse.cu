@@ -3,15 +3,16 @@
 //
 // One CTA owns QT = 128 / G queries of one KV head, taken in the caller's tile order
 // (queries with similar selections are placed in the same tile).  Warp roles:
-//   warps 0-3  softmax + epilogue, one thread per row (TMEM lane)
-//   warp  4    planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
+//   warps 0-7  softmax + epilogue: two warpgroups split the 64 columns of a tile, one
+//              thread per (row, half)
+//   warp  8    planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
 //              starts fetched by 32 lanes in parallel), and expands the union of selected
 //              clusters into a stream of packed rows, each tagged with the 32-bit set of
 //              queries that selected its cluster; 64 rows make a tile
-//   warps 5-8  gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
+//   warps 9-12 gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
 //              cp.async into the 128-byte-swizzled UMMA layout (only visible rows are
 //              read: no page padding), then published to the async proxy
-//   warp  9    UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
+//   warp  13   UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
 //              whichever order their operands become ready
 // The epilogue merges the sparse partial with the window partial already stored in
 // `out` / `lse` by the dense launch, so each query sees one softmax over the union.
@@ -23,6 +24,7 @@
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
+#include "attn_common.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -32,14 +34,12 @@ namespace {
 
 constexpr int BLOCK_N = 64;
 constexpr int PLAN_STAGES = 3;
-constexpr float LN2F = 0.6931471805599453f;
 constexpr float LOG2EF = 1.4426950408889634f;
-constexpr float RESCALE_GAP = 8.0f;
 
 struct Plan {
   int count;             // rows in the tile (0 = end of stream)
   int pad[3];
-  int row[BLOCK_N];      // physical packed row, -1 = zero fill
+  int row[BLOCK_N];      // logical packed row (before the page table), -1 = zero fill
   uint32_t mask[BLOCK_N];
 };
 
@@ -55,9 +55,10 @@ struct GatherCfg {
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
   static constexpr int PLAN_OFF = P_OFF + 2 * P_BYTES;
-  static constexpr int BAR_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (10 + 4 * STAGES + 2 * PLAN_STAGES);
-  static constexpr int TOTAL = MISC_OFF + 16 + 1024;
+  static constexpr int XCHG_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);   // bf16 [2][2][128]
+  static constexpr int BAR_OFF = XCHG_OFF + 1024;
+  static constexpr int MISC_OFF = BAR_OFF + 8 * (13 + 4 * STAGES + 2 * PLAN_STAGES);
+  static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
   static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
   static constexpr int O_COL = 2 * BLOCK_N;
 };
@@ -74,12 +75,25 @@ struct GatherArgs {
   float scale_log2;
   __nv_bfloat16* out;           // [Q, Hq, D] in: window partial, out: merged
   float* lse;                   // [Q, Hq]    in: window lse,     out: merged (natural log)
+  const float* partial;         // [Q, Hq, D] fp32 window partial, or null: it is in `out` as bf16
   int merge;                    // 0: no window partial, write the sparse result alone
   unsigned long long* attended;
   int* status;
 };
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KFULL = 10 };
+// Optional wait accounting (build with -DSEMBLO_TRACE): every role adds the cycles it spends
+// in each phase to attended[8 + 8 * role + phase]; the buffer must then hold 48 counters.
+#ifdef SEMBLO_TRACE
+#define TR_DECL long long tr_last = clock64(); long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define TR(i) { const long long tr_now = clock64(); tr[i] += tr_now - tr_last; tr_last = tr_now; }
+#define TR_FLUSH(role) if (a.attended && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) if (tr[i_]) atomicAdd(a.attended + 8 + 8 * (role) + i_, (unsigned long long)tr[i_]); }
+#else
+#define TR_DECL
+#define TR(i)
+#define TR_FLUSH(role)
+#endif
+
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_XCHG = 10, B_EPI = 12, B_KFULL = 13 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -89,7 +103,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
@@ -99,9 +113,13 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   constexpr int B_VEMPTY = B_VFULL + STAGES;
   constexpr int B_PLANFULL = B_VEMPTY + STAGES;
   constexpr int B_PLANEMPTY = B_PLANFULL + PLAN_STAGES;
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, STATUS_SMEM_ALIGN);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
+  __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::XCHG_OFF);
   Plan* plan = reinterpret_cast<Plan*>(smem + C::PLAN_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -114,10 +132,12 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 1);
     mbar_init(bar(B_OREADY), 1);
+    mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_SEMPTY + b), 128);
-      mbar_init(bar(B_PFULL + b), 128);
+      mbar_init(bar(B_SEMPTY + b), 256);
+      mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PEMPTY + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
@@ -128,7 +148,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 7);     // a K and a V gather warp, the UMMA thread, four softmax warps
+      mbar_init(bar(B_PLANEMPTY + s), 11);    // a K and a V gather warp, the UMMA thread, eight softmax warps
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -142,7 +162,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ planner (+ Q load)
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
@@ -166,11 +186,14 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     int tile = 0, fill = 0;
     long long gathered = 0;
     bool ok = true;
+    TR_DECL
     auto acquire = [&]() {          // make plan stage of `tile` writable
       const int ps = tile % PLAN_STAGES;
+      TR(1)
       if (lane == 0)
         ok = mbar_wait(bar(B_PLANEMPTY + ps), ((tile / PLAN_STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
       ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      TR(0)
     };
     auto publish = [&](int count) {
       const int ps = tile % PLAN_STAGES;
@@ -191,11 +214,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     unsigned any1 = __reduce_or_sync(0xffffffffu, word1);
     int n1 = ((any1 >> lane) & 1) ? csz[lane] : 0;
     int start1 = ((any1 >> lane) & 1) ? ipt[lane] : 0;
-    int pt1 = (a.page_table && ((any1 >> lane) & 1)) ? a.page_table[start1 >> 4] : 0;
     for (int w = 0; w < nwords && ok; ++w) {
       const unsigned word = word1, any = any1;
       int n_b = max(n1, 0);
-      const int start_b = start1, pt_b = pt1;
+      const int start_b = start1;
       // prefetch for the following words
       word1 = word2;
       word2 = load_word(w + 2);
@@ -235,14 +257,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           lo = min(lo, 31);
           const int sb = __shfl_sync(0xffffffffu, start_b, lo);
           const int eb = __shfl_sync(0xffffffffu, excl, lo);
-          const int pb = __shfl_sync(0xffffffffu, pt_b, lo);
           const unsigned mb = __shfl_sync(0xffffffffu, mask_b, lo);
           if (lane < cnt) {
-            const int off = j - eb;
-            int row = sb + off;
-            if (a.page_table) row = (off < 16 ? pb : a.page_table[row >> 4]) * 16 + (row & 15);
             const int ps = tile % PLAN_STAGES;
-            plan[ps].row[fill + lane] = row;
+            plan[ps].row[fill + lane] = sb + (j - eb);       // logical packed row; the gather warps translate pages
             plan[ps].mask[fill + lane] = mb;
           }
           fill += cnt;
@@ -253,8 +271,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           }
         }
       }
-      // the first page of every cluster of the next word (its start has arrived by now)
-      pt1 = (a.page_table && ((any1 >> lane) & 1) && w + 1 < nwords) ? a.page_table[start1 >> 4] : 0;
     }
     if (ok && fill > 0) {
       const int ps = tile % PLAN_STAGES;
@@ -267,18 +283,20 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       acquire();
     }
     if (a.attended && lane == 0 && gathered) atomicAdd(a.attended + 1, (unsigned long long)gathered);
+    TR(1)
+    TR_FLUSH(0)
     if (ok) {
       // end of stream, once per gather warp (they alternate tiles)
       publish(0);
       acquire();
       if (ok) publish(0);
     }
-  } else if (warp >= 5 && warp <= 8) {
+  } else if (warp >= 9 && warp <= 12) {
     // ------------------------------------------------------------ gather warps
-    // warps 5/6 copy the K rows of even/odd tiles, warps 7/8 the V rows: consecutive tiles
+    // warps 9/10 copy the K rows of even/odd tiles, warps 11/12 the V rows: consecutive tiles
     // are in flight in different warps, so a tile's latency hides behind its neighbours'.
-    const bool is_v = warp >= 7;
-    const int par = (warp - 5) & 1;
+    const bool is_v = warp >= 11;
+    const int par = (warp - 9) & 1;
     const __nv_bfloat16* src_base = is_v ? a.packed_v : a.packed_k;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
     const int64_t row_elems = (int64_t)a.num_kv_heads * D;
@@ -287,30 +305,51 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     const int sub = lane / LANES_PER_ROW, l_in = lane % LANES_PER_ROW;
     const int slab = l_in >> 3, chunk = l_in & 7;
     const int64_t lane_off = (int64_t)h * D + l_in * 8;
+    TR_DECL
     for (int t = par;; t += 2) {
       const int ps = t % PLAN_STAGES, s = t % STAGES;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      TR(0)
       const int cnt = plan[ps].count;
       if (cnt == 0) break;
-      const int r_lo = plan[ps].row[lane], r_hi = plan[ps].row[lane + 32];
+      int r_lo = plan[ps].row[lane], r_hi = plan[ps].row[lane + 32];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-      if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       const int n16 = (cnt + 15) & ~15;
-      const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
-#pragma unroll 4
-      for (int j0 = 0; j0 < n16; j0 += ROWS_PER_ITER) {
-        const int j = j0 + sub;
-        const int row = __shfl_sync(0xffffffffu, j0 < 32 ? r_lo : r_hi, j & 31);
-        const int64_t off = (int64_t)max(row, 0) * row_elems + lane_off;
-        cp_async16(base + swz128(j, chunk), src_base + off, row >= 0 ? 16u : 0u);
+      if (a.page_table) {
+        // logical row -> physical row of the paged pool: 64 independent lookups in flight
+        if (lane < n16 && r_lo >= 0) r_lo = a.page_table[r_lo >> 4] * 16 + (r_lo & 15);
+        if (lane + 32 < n16 && r_hi >= 0) r_hi = a.page_table[r_hi >> 4] * 16 + (r_hi & 15);
       }
+      if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      TR(1)
+      const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
+      // 8 copies per step: the row indices are fetched first so the shuffles overlap
+      constexpr int GROUP = 8;
+      for (int j0 = 0; j0 < n16; j0 += GROUP * ROWS_PER_ITER) {
+        int rows[GROUP];
+#pragma unroll
+        for (int u = 0; u < GROUP; ++u) {
+          const int j = j0 + u * ROWS_PER_ITER + sub;
+          rows[u] = __shfl_sync(0xffffffffu, j0 < 32 ? r_lo : r_hi, j & 31);
+        }
+#pragma unroll
+        for (int u = 0; u < GROUP; ++u) {
+          const int j = j0 + u * ROWS_PER_ITER + sub;
+          const int64_t off = (int64_t)max(rows[u], 0) * row_elems + lane_off;
+          cp_async16(base + swz128(j, chunk), src_base + off, rows[u] >= 0 ? 16u : 0u);
+        }
+      }
+      TR(2)
       cp_async_wait_all();
+      TR(3)
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(b_full + s));
+      TR(4)
     }
-  } else if (warp == 9) {
+    TR_FLUSH(is_v ? 2 : 1)
+  } else if (warp == 13) {
     // ------------------------------------------------------------ UMMA issuer
     // S(j) = Q K(j)^T is issued as soon as K(j) has landed and the S buffer is free;
     // O += P(j) V(j) as soon as the softmax warps have written P(j): whichever is ready first.
@@ -322,6 +361,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       int np_of[4] = {0, 0, 0, 0};                    // pages of the tiles in flight (index tile & 3)
       unsigned long long t0 = globaltimer();
       uint32_t idle = 0;
+      TR_DECL
       while (ok) {
         bool progress = false;
         if (next_qk < end_tile && next_qk - next_pv < 2) {
@@ -370,6 +410,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           }
         }
         if (next_pv == end_tile) break;
+        if (progress) { TR(1) } else { TR(0) }
         if (progress) {
           idle = 0;
         } else if ((++idle & 0x3ff) == 0) {
@@ -379,23 +420,30 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         }
       }
       if (ok) umma_commit(bar(B_OREADY));
+      { const int lane = 0; (void)lane; TR_FLUSH(3) }
     }
   } else {
-    // ------------------------------------------------------------ softmax + epilogue (thread = row)
-    const int row = threadIdx.x;
+    // ------------------------------------------------------------ softmax + epilogue
+    // warps 0-3: columns [0, 32) of every tile, warps 4-7: columns [32, 64); thread = row
+    const int hf = warp >> 2;
+    const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
     const bool qvalid = slot < a.num_queries;
     const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m_ref = -INFINITY, l_run = 0.f;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t qbit = 1u << qslot;
+    float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
     unsigned long long att = 0;
     bool ok = true;
     int j = 0;
+    TR_DECL
     for (;; ++j) {
       const int ps = j % PLAN_STAGES, b = j & 1;
+      TR(5)
       ok = mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
+      TR(0)
       const int cnt = plan[ps].count;
       if (cnt == 0) {
         __syncwarp();
@@ -403,158 +451,63 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         break;
       }
       const int np = (cnt + 15) >> 4;
+      const int my_pages = min(max(np - 2 * hf, 0), 2);
       ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
+      TR(1)
       tc_fence_after();
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tmem_base + lane_addr + b * BLOCK_N, r0);
-      if (np > 2) tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + 32, r1);
-      tmem_ld_wait();
+      uint32_t r[32];
+      if (my_pages > 0) {
+        tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + hf * 32, r);
+        tmem_ld_wait();
+      }
       tc_fence_before();
       mbar_arrive(bar(B_SEMPTY + b));
-      // masked raw logits (scaling is folded into the exponent below)
+      // masked raw logits of this half (scaling is folded into the exponent)
       float tmax = -INFINITY;
       int n_on = 0;
-      const uint32_t qbit = 1u << qslot;
-      const uint4* mk = reinterpret_cast<const uint4*>(plan[ps].mask);
+      const uint4* mk = reinterpret_cast<const uint4*>(plan[ps].mask + hf * 32);
 #pragma unroll
-      for (int g4 = 0; g4 < BLOCK_N / 4; ++g4) {
-        if (g4 * 4 < np * 16) {
+      for (int g4 = 0; g4 < 8; ++g4) {
+        if (g4 * 4 < my_pages * 16) {
           const uint4 m4 = mk[g4];
           const uint32_t mm[4] = {m4.x, m4.y, m4.z, m4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int col = g4 * 4 + e;
-            uint32_t& slot_r = col < 32 ? r0[col] : r1[col - 32];
             const bool allowed = (mm[e] & qbit) != 0u;
-            const float sraw = allowed ? __uint_as_float(slot_r) : -INFINITY;
-            slot_r = __float_as_uint(sraw);
+            const float sraw = allowed ? __uint_as_float(r[col]) : -INFINITY;
+            r[col] = __float_as_uint(sraw);
             tmax = fmaxf(tmax, sraw);
             n_on += allowed;
           }
         }
       }
-      tmax *= a.scale_log2;                      // scale > 0: the max commutes with it
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
       if (t == 0) att += n_on;
-      bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
-      float alpha = 1.f;
-      if (need) {
-        alpha = exp2f(m_ref - tmax);
-        m_ref = tmax;
-        l_run *= alpha;
-      } else if (m_ref == -INFINITY) {
-        m_ref = tmax;
-      }
-      ok = mbar_wait(bar(B_PEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      TR(2)
+      ok = attn::softmax_half_tile<D, C::O_COL, BLOCK_N>(
+          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, smem + C::P_OFF + b * C::P_BYTES, xchg,
+          bar(B_XCHG), bar(B_PEMPTY + b), bar(B_PEMPTY + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd,
+          abort_flag, a.status);
       if (!ok) break;
-      if (__any_sync(0xffffffffu, need)) {
-        ok = mbar_wait(bar(B_PEMPTY + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-      }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      const float neg_m = -m_use, sc = a.scale_log2;
-      uint8_t* p_row = smem + C::P_OFF + b * C::P_BYTES;
-      float add = 0.f;
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        if (p < np) {
-          uint32_t packed[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t u0 = p < 2 ? r0[p * 16 + 2 * i] : r1[(p - 2) * 16 + 2 * i];
-            const uint32_t u1 = p < 2 ? r0[p * 16 + 2 * i + 1] : r1[(p - 2) * 16 + 2 * i + 1];
-            const float e0 = fast_exp2(fmaf(__uint_as_float(u0), sc, neg_m));
-            const float e1 = fast_exp2(fmaf(__uint_as_float(u1), sc, neg_m));
-            add += e0 + e1;
-            __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-            packed[i] = *reinterpret_cast<uint32_t*>(&pr);
-          }
-          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(p_row + swz128(row, 2 * p + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        }
-      }
-      l_run += add;
-      fence_proxy_async_smem();
-      mbar_arrive(bar(B_PFULL + b));
+      TR(4)
     }
+    if (warp == 0) { TR_FLUSH(4) }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
-    if (ok) {
-      tc_fence_after();
-      // merge with the window partial (out holds its normalised output, lse its natural-log LSE)
-      const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
-      float wa = 0.f, wb = 1.f, denom = l_run, m_new = m_ref;
-      if (a.merge && qvalid) {
-        const float l2 = a.lse[hidx] * LOG2EF;                 // window LSE in log2 units
-        m_new = fmaxf(l2, m_ref);
-        if (m_new == -INFINITY) {
-          wa = 0.f; wb = 0.f; denom = 0.f;
-        } else {
-          wa = exp2f(l2 - m_new);
-          wb = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);
-          denom = wa + l_run * wb;
-        }
-      }
-      const float inv = denom > 0.f ? 1.f / denom : 0.f;
-      __nv_bfloat16* dst = a.out + hidx * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        if (j > 0) {
-          tmem_ld32(tmem_base + lane_addr + C::O_COL + c * 32, o);
-          tmem_ld_wait();
-        } else {
+    tc_fence_after();
+    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::P_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+                                     ok && qvalid, a.merge, a.out + hidx * D,
+                                     a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
+                                     abort_flag, a.status);
+    if (ok && a.attended) {
+      if (!qvalid) att = 0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (qvalid) {
-          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
-          uint32_t prev[16];
-          if (a.merge) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint4 v = d4[i];
-              prev[4 * i] = v.x; prev[4 * i + 1] = v.y; prev[4 * i + 2] = v.z; prev[4 * i + 3] = v.w;
-            }
-          }
-          uint32_t w[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x0 = __uint_as_float(o[2 * i]) * wb, x1 = __uint_as_float(o[2 * i + 1]) * wb;
-            if (a.merge) {
-              const float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&prev[i]));
-              x0 += pv.x * wa;
-              x1 += pv.y * wa;
-            }
-            __nv_bfloat162 pr = __floats2bfloat162_rn(x0 * inv, x1 * inv);
-            w[i] = *reinterpret_cast<uint32_t*>(&pr);
-          }
-          d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          d4[2] = make_uint4(w[8], w[9], w[10], w[11]);
-          d4[3] = make_uint4(w[12], w[13], w[14], w[15]);
-        }
-      }
-      if (qvalid && a.lse) a.lse[hidx] = denom > 0.f ? (m_new + log2f(denom)) * LN2F : -INFINITY;
-      if (a.attended) {
-        if (!qvalid) att = 0;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
-        if (lane == 0 && att) atomicAdd(a.attended, att);
-      }
+      for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
+      if (lane == 0 && att) atomicAdd(a.attended, att);
     }
     tc_fence_before();
   }
@@ -576,7 +529,7 @@ int launch_gather(const void* q, const GatherArgs& a, cudaStream_t st) {
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 320, C::TOTAL, st>>>(mq, a);
+  kern<<<grid, 448, C::TOTAL, st>>>(mq, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
@@ -587,8 +540,8 @@ extern "C" int semblo_sparse_prefill_gather(
     const void* q, int num_queries, int num_q_heads, int num_kv_heads, int head_dim,
     const int32_t* q_order, const void* packed_k, const void* packed_v, const int32_t* page_table,
     const int32_t* qmask, const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
-    float sm_scale, int merge, void* out, float* lse, unsigned long long* attended,
-    int32_t* status, void* stream) {
+    float sm_scale, int merge, const float* partial_in, void* out, float* lse,
+    unsigned long long* attended, int32_t* status, void* stream) {
   SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
   SEMBLO_REQUIRE(qmask && packed_k && packed_v && causal_sizes && indptr, "selection, packed K/V, sizes and indptr are required");
@@ -602,7 +555,7 @@ extern "C" int semblo_sparse_prefill_gather(
   a.num_clusters = num_clusters; a.q_order = q_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
   a.indptr = indptr; a.page_table = page_table;
   a.packed_k = (const __nv_bfloat16*)packed_k; a.packed_v = (const __nv_bfloat16*)packed_v;
-  a.scale_log2 = sm_scale * LOG2EF; a.out = (__nv_bfloat16*)out; a.lse = lse; a.merge = merge;
+  a.scale_log2 = sm_scale * LOG2EF; a.out = (__nv_bfloat16*)out; a.lse = lse; a.merge = merge; a.partial = partial_in;
   a.attended = attended; a.status = status;
   const int g = num_q_heads / num_kv_heads;
   cudaStream_t st = (cudaStream_t)stream;

@@ -23,6 +23,7 @@ enum Status : int {
   STATUS_TIMEOUT_SOFTMAX = 103,
   STATUS_TIMEOUT_EPILOGUE = 104,
   STATUS_OVERFLOW = 201,
+  STATUS_SMEM_ALIGN = 202,       // dynamic shared memory did not start on a 1024-byte boundary
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

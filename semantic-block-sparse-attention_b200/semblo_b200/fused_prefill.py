@@ -32,7 +32,7 @@ class CausalSnapshot:
         self.qmask = None
         self.score = None
         self.select_sizes = None
-        self.top1 = self.order = self.lse = self.sort_ws = None
+        self.top1 = self.order = self.lse = self.sort_ws = self.partial = None
 
     def advance(self, last_pos: int) -> torch.Tensor:
         hi = min(int(last_pos) + 1, self.length)
@@ -73,7 +73,7 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
 
 def window_attention(q: torch.Tensor, q_positions: torch.Tensor, *, ordered_k: torch.Tensor,
                      ordered_v: torch.Tensor, ordered_pos0: int = 0, local_start: int = 0, sm_scale: float,
-                     out=None, lse=None, attended=None) -> torch.Tensor:
+                     out=None, lse=None, attended=None, partial=None) -> torch.Tensor:
     """Exact causal attention of consecutive queries over positions [local_start, q_position]
     of the position-ordered K/V (semblo_window_prefill)."""
     require_cuda(q, ordered_k, ordered_v)
@@ -89,7 +89,7 @@ def window_attention(q: torch.Tensor, q_positions: torch.Tensor, *, ordered_k: t
     check(lib().semblo_window_prefill(
         ptr(q), q_count, num_q_heads, int(ordered_k.shape[1]), head_dim, ptr(q_positions), ptr(ordered_k),
         ptr(ordered_v), int(ordered_k.shape[0]), int(ordered_pos0), int(local_start), float(sm_scale), ptr(out),
-        ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
+        ptr(partial), ptr(lse), ptr(attended), ptr(status.word), stream_ptr()))
     return out
 
 
@@ -111,7 +111,7 @@ def argsort_keys(keys: torch.Tensor, max_key: int, *, out: torch.Tensor | None =
 def sparse_gather_attention(q: torch.Tensor, *, packed_kv: torch.Tensor, qmask: torch.Tensor,
                             causal_sizes: torch.Tensor, indptr: torch.Tensor, sm_scale: float,
                             out: torch.Tensor, lse: torch.Tensor | None, merge: bool, page_table=None,
-                            q_order=None, attended=None) -> torch.Tensor:
+                            q_order=None, attended=None, partial=None) -> torch.Tensor:
     """One launch of the row-gather sparse kernel (semblo_sparse_prefill_gather)."""
     require_cuda(q, packed_kv, qmask)
     q_count, num_q_heads, head_dim = q.shape
@@ -120,7 +120,8 @@ def sparse_gather_attention(q: torch.Tensor, *, packed_kv: torch.Tensor, qmask: 
     check(lib().semblo_sparse_prefill_gather(
         ptr(q), q_count, num_q_heads, int(packed_kv.shape[2]), head_dim, ptr(q_order), ptr(packed_kv[0]),
         ptr(packed_kv[1]), ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr),
-        int(causal_sizes.shape[1]), float(sm_scale), 1 if merge else 0, ptr(out), ptr(lse), ptr(attended),
+        int(causal_sizes.shape[1]), float(sm_scale), 1 if merge else 0, ptr(partial), ptr(out), ptr(lse),
+        ptr(attended),
         ptr(status.word), stream_ptr()))
     return out
 
@@ -176,6 +177,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         snap.top1 = torch.empty(hkv, q_count, dtype=torch.int32, device=dev)
         snap.order = torch.empty(hkv, q_count, dtype=torch.int32, device=dev)
         snap.lse = torch.empty(q_count, num_q_heads, dtype=torch.float32, device=dev)
+        snap.partial = torch.empty(q_count, num_q_heads, q_chunk.shape[2], dtype=torch.float32, device=dev)
         snap.sort_ws = torch.empty(int(lib().semblo_layout_workspace_bytes(q_count, hkv)), dtype=torch.uint8,
                                    device=dev)
     full = q_count == snap.qmask.shape[0]
@@ -191,17 +193,19 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if out is None:
         out = torch.empty_like(q_chunk)
     lse = snap.lse[:q_count]
+    partial = snap.partial[:q_count]
     if _timer:
         _timer("start")
     # the exact window [wstart, q] in position order, then the selected clusters merged into it
     window_attention(q_chunk, q_positions, ordered_k=k_pos[wstart:chunk_end + 1],
                      ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart,
-                     sm_scale=sm_scale, out=out, lse=lse, attended=attended)
+                     sm_scale=sm_scale, out=out, lse=lse, attended=attended, partial=partial)
     if _timer:
         _timer("mid")
     sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
                             indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
-                            page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended)
+                            page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended,
+                            partial=partial)
     if _timer:
         _timer("stop")
     return out
