@@ -124,6 +124,20 @@ int semblo_select_clusters(const float* score, const int32_t* select_sizes, int 
 int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key, int32_t* order,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* semblo_argsort_keys without a workspace and without any allocation: the scratch is a fixed
+ * array inside the library image, looked up once per device.  No counterpart in the reference.
+ * For callers that must not allocate at the point of the call (inside a serving loop that has
+ * frozen its memory pool, or under an allocator they do not own).  Limits: heads * n <=
+ * semblo_argsort_keys_static_max_keys() (65536) and heads <= 64; larger inputs are refused
+ * with an error and belong to semblo_argsort_keys.  The first call on a device, with that
+ * device current, resolves the array's address (this may load the module): make it before any
+ * stream capture begins.  All calls on a device share the one array, so two calls whose kernels
+ * can overlap (different streams or threads) race; order them on one stream.  Nothing in the
+ * array has to be cleared between calls. */
+int64_t semblo_argsort_keys_static_max_keys(void);
+int semblo_argsort_keys_static(const int32_t* keys, int64_t n, int heads, int max_key,
+                               int32_t* order, void* stream);
+
 /* ---- prefill attention ---------------------------------------------------------- */
 
 /* semblo/vllm_plugin/fused_prefill.py:155-189 (_dense_chunk_attention) and the chunk's own

@@ -11,6 +11,7 @@
 //   semblo/vllm_plugin/state.py:44-84, 850-914   posting order, page alignment, inverse map
 //   semblo/vllm_plugin/state.py:950-997          pack_prompt_kv
 #include <cuda_bf16.h>
+#include <mutex>
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
@@ -710,6 +711,61 @@ extern "C" int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, in
   SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, heads), "workspace too small");
   if (n == 0) return 0;
   int32_t* ws = (int32_t*)workspace;
+  const int64_t hn = (int64_t)heads * n;
+  return sort_by_cluster(keys, n, n, heads, max_key, order, ws, ws + hn, ws + 2 * hn, ws + 3 * hn,
+                         (cudaStream_t)stream);
+}
+
+// ====================================================================== no-allocation arg-sort
+//
+// semblo_argsort_keys with its scratch in a fixed array inside the library image instead of a
+// caller-provided workspace.  Every scratch word is written by the sort before it is read, so
+// nothing has to start at zero; all calls on a device share the one array.
+namespace {
+
+constexpr int64_t STATIC_SORT_MAX_KEYS = 65536;     // heads * n
+constexpr int STATIC_SORT_MAX_HEADS = 64;
+constexpr int64_t STATIC_SORT_HIST_WORDS = 256 * (STATIC_SORT_MAX_KEYS / SORT_TILE + STATIC_SORT_MAX_HEADS);
+constexpr int64_t STATIC_SORT_WORDS = 4 * STATIC_SORT_MAX_KEYS + STATIC_SORT_HIST_WORDS;
+
+static __device__ __align__(256) int32_t g_static_sort_scratch[STATIC_SORT_WORDS];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+int32_t* g_static_sort_ptr[STATIC_MAX_DEVICES] = {};
+std::mutex g_static_sort_mutex;
+
+// Address of the scratch array on the current device, looked up once per device.
+int static_sort_scratch(int32_t** out) {
+  int dev = -1;
+  SEMBLO_CUDA(cudaGetDevice(&dev));
+  SEMBLO_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_sort_mutex);
+  if (!g_static_sort_ptr[dev]) {
+    int32_t* p = nullptr;
+    SEMBLO_CUDA(cudaGetSymbolAddress((void**)&p, g_static_sort_scratch));
+    SEMBLO_REQUIRE(p != nullptr, "the scratch array has no address on device %d", dev);
+    g_static_sort_ptr[dev] = p;
+  }
+  *out = g_static_sort_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int64_t semblo_argsort_keys_static_max_keys(void) { return STATIC_SORT_MAX_KEYS; }
+
+extern "C" int semblo_argsort_keys_static(const int32_t* keys, int64_t n, int heads, int max_key,
+                                          int32_t* order, void* stream) {
+  SEMBLO_REQUIRE(max_key > 0 && max_key <= 65536, "keys must be below 65536");
+  SEMBLO_REQUIRE(n >= 0 && heads > 0 && heads <= STATIC_SORT_MAX_HEADS,
+                 "heads %d outside [1, %d] of the fixed scratch", heads, STATIC_SORT_MAX_HEADS);
+  SEMBLO_REQUIRE((int64_t)heads * n <= STATIC_SORT_MAX_KEYS,
+                 "heads * n = %lld keys exceed the fixed scratch of %lld keys; use semblo_argsort_keys "
+                 "with a workspace", (long long)((int64_t)heads * n), (long long)STATIC_SORT_MAX_KEYS);
+  int32_t* ws = nullptr;
+  int rc = static_sort_scratch(&ws);
+  if (rc) return rc;
+  if (n == 0) return 0;
   const int64_t hn = (int64_t)heads * n;
   return sort_by_cluster(keys, n, n, heads, max_key, order, ws, ws + hn, ws + 2 * hn, ws + 3 * hn,
                          (cudaStream_t)stream);
