@@ -5,6 +5,12 @@
 // is exchanged through shared memory, the running reference maximum m_ref is kept
 // identical in both threads of a row, each thread keeps the partial sum of its own
 // columns, and each half rescales / finalises its own D/2 columns of O.
+//
+// Both A operands live in tensor memory, so shared memory holds K / V stages only:
+//   Q  [128 x D]  bf16, two elements per 32-bit column, written once per CTA (stage_q_half);
+//   P  [128 x 64] bf16 in the first 32 columns of the S buffer it was computed from (the
+//      S values are in registers by then), read by O += P V as a TMEM operand.
+// An S buffer therefore becomes free when the P V product of its tile has completed.
 #pragma once
 #include "sm100.cuh"
 
@@ -24,23 +30,51 @@ __device__ __forceinline__ bool softmax_group_sync(uint32_t bar, uint32_t parity
   return mbar_wait(bar, parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX);
 }
 
+// Copies this thread's half of its query row (D/2 bf16 from qrow_half, or zeros when null) into
+// the Q operand columns and arrives on bar_qfull (count: all softmax threads).
+template <int D, int Q_COL>
+__device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int hf, uint32_t lane_addr,
+                                             uint32_t tmem_base, uint32_t bar_qfull) {
+#pragma unroll 1
+  for (int c = 0; c < D / 128; ++c) {
+    uint32_t w[32];
+    if (qrow_half) {
+      const uint4* src = reinterpret_cast<const uint4*>(qrow_half + c * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 v = __ldg(src + i);
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) w[i] = 0u;
+    }
+    tmem_st32(tmem_base + lane_addr + Q_COL + hf * (D / 4) + c * 32, w);
+  }
+  tmem_st_wait();
+  tc_fence_before();
+  mbar_arrive(bar_qfull);
+}
+
 // One half-row of one tile.  r[] holds the 32 raw logits of this half with masked entries
 // already set to -inf; tmax_raw is their maximum.  my_pages = how many 16-column groups of
-// this half exist in the tile (0, 1 or 2).  Returns false after a wait timed out.
-template <int D, int O_COL, int BLOCK_N>
+// this half exist in the tile (0, 1 or 2).  s_col = first TMEM column of the tile's S buffer,
+// which receives P.  Returns false after a wait timed out.
+template <int D, int O_COL>
 __device__ __forceinline__ bool softmax_half_tile(
     uint32_t (&r)[32], float tmax_raw, int my_pages, int j, int hf, int row, uint32_t lane_addr,
-    uint32_t tmem_base, uint8_t* p_buf, __nv_bfloat16* xchg /* [2][2][128] */, uint32_t bar_xchg0,
-    uint32_t bar_pempty_b,
-    uint32_t bar_pempty_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
+    uint32_t tmem_base, uint32_t s_col, __nv_bfloat16* xchg /* [2][2][128] */, uint32_t bar_xchg0,
+    uint32_t bar_pvdone_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
     float& l_rnd, volatile int* abort_flag, int* status) {
   // Both threads of a row must agree on the reference exactly, so each publishes its maximum
   // rounded UP to bf16 and both take the larger of the two rounded values (a reference slightly
   // above the true maximum is harmless).  Double-buffered by tile parity: one barrier per tile.
+  // Past this barrier both halves hold their S values in registers, so P may overwrite S.
   __nv_bfloat16* xc = xchg + (j & 1) * 256;
   const __nv_bfloat16 mine = __float2bfloat16_ru(tmax_raw);
   xc[hf * 128 + row] = mine;
   if (!softmax_group_sync(bar_xchg0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, status)) return false;
+  tc_fence_after();
   const float tmax = fmaxf(__bfloat162float(mine), __bfloat162float(xc[(hf ^ 1) * 128 + row])) * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
   const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
@@ -53,10 +87,9 @@ __device__ __forceinline__ bool softmax_half_tile(
   } else if (m_ref == -INFINITY) {
     m_ref = tmax;
   }
-  if (!mbar_wait(bar_pempty_b, ((j >> 1) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
   if (__any_sync(0xffffffffu, need)) {
     // O must be quiescent: the previous tile's P V has to be complete
-    if (!mbar_wait(bar_pempty_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+    if (!mbar_wait(bar_pvdone_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
     tc_fence_after();
 #pragma unroll 1
     for (int c = 0; c < D / 64; ++c) {
@@ -68,35 +101,39 @@ __device__ __forceinline__ bool softmax_half_tile(
       for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
       tmem_st32(addr, o);
     }
-    tmem_st_wait();
-    tc_fence_before();
   }
   const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
   float add = 0.f, add_rnd = 0.f;
+  if (my_pages > 0) {
+    uint32_t packed[16];
 #pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    if (p < my_pages) {
-      uint32_t packed[8];
+    for (int p = 0; p < 2; ++p) {
+      if (p < my_pages) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float e0 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i]), scale_log2, neg_m));
-        const float e1 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i + 1]), scale_log2, neg_m));
-        __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-        packed[i] = *reinterpret_cast<uint32_t*>(&pr);
-        add += e0 + e1;
-        // O is normalised by the sum of the weights as the tensor core sees them, so the
-        // rounding of P perturbs the convex combination and not its scale; the exact sum
-        // gives the LSE
-        add_rnd += __uint_as_float(packed[i] << 16) + __uint_as_float(packed[i] & 0xffff0000u);
+        for (int i = 0; i < 8; ++i) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i]), scale_log2, neg_m));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i + 1]), scale_log2, neg_m));
+          __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+          const uint32_t w = *reinterpret_cast<uint32_t*>(&pr);
+          packed[p * 8 + i] = w;
+          add += e0 + e1;
+          // O is normalised by the sum of the weights as the tensor core sees them, so the
+          // rounding of P perturbs the convex combination and not its scale; the exact sum
+          // gives the LSE
+          add_rnd += __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) packed[p * 8 + i] = 0u;
       }
-      const int chunk = (hf * 2 + p) * 2;
-      *reinterpret_cast<uint4*>(p_buf + swz128(row, chunk)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      *reinterpret_cast<uint4*>(p_buf + swz128(row, chunk + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
     }
+    // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 16 hf + i of the P operand
+    tmem_st16(tmem_base + lane_addr + s_col + hf * 16, packed);
   }
   l_part += add;
   l_rnd += add_rnd;
-  fence_proxy_async_smem();
+  tmem_st_wait();
+  tc_fence_before();
   mbar_arrive(bar_pfull_b);
   return true;
 }

@@ -2,12 +2,13 @@
 // local window of every sparse chunk.
 //
 // One CTA owns a tile of QT = 128 / G consecutive queries of one KV head (128 rows:
-// query-major, the G heads of a query adjacent) and keeps the output accumulator
-// O [128, D] in TMEM.  The producer streams positions [local_start, max q_pos of the
-// tile] of the position-ordered K/V through TMA in 64-row tiles; S = Q K^T (UMMA,
-// fp32 in TMEM), the softmax warps (one thread per row) apply the causal mask, keep a
-// lazily rescaled running max and write P as bf16 into swizzled shared memory, and
-// O += P V is a second UMMA with V as an MN-major operand.  The kernel writes the
+// query-major, the G heads of a query adjacent).  The output accumulator O [128, D], the
+// query operand Q [128, D] and the probabilities P all live in TMEM, so shared memory is
+// K / V stages only.  The producer streams positions [local_start, max q_pos of the
+// tile] of the position-ordered K/V through TMA in 64-row tiles; S = Q K^T (UMMA, Q read
+// from TMEM, fp32 result in TMEM), the softmax warps (two threads per row) apply the causal
+// mask, keep a lazily rescaled running max and store P as bf16 over S, and O += P V is a
+// second UMMA with P read from TMEM and V as an MN-major operand.  The kernel writes the
 // normalised output and its log-sum-exp, which the sparse launch merges into.
 //
 // Reference behaviour restated here:
@@ -15,6 +16,7 @@
 //   semblo/vllm_plugin/kv_outer.py:661-676       the chunk's own causal window
 //   semblo/vllm_plugin/fused_prefill.py:250-279  window start / dense-prefix rule (caller)
 #include <algorithm>
+#include <climits>
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
@@ -39,21 +41,19 @@ struct TileInfo {
 
 template <int D>
 struct AttnCfg {
-  static constexpr int STAGES = D >= 256 ? 2 : 4;
-  static constexpr int SLABS = D / 64;
-  static constexpr int Q_BYTES = 128 * D * 2;
+  static constexpr int STAGES = D >= 256 ? 3 : 6;
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
-  static constexpr int P_BYTES = 128 * BLOCK_N * 2;
-  static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = Q_OFF + Q_BYTES;
+  static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-  static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
-  static constexpr int XCHG_OFF = P_OFF + 2 * P_BYTES;        // bf16 [2][2][128]
+  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][2][128]
+  static constexpr int XCHG_OFF = EPI_OFF + 2048;             // bf16 [2][2][128]
   static constexpr int BAR_OFF = XCHG_OFF + 1024;
   static constexpr int INFO_OFF = BAR_OFF + 256;
   static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
-  static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
-  static constexpr int O_COL = 2 * BLOCK_N;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int O_COL = 2 * BLOCK_N;                    // S/P buffers, then O, then Q
+  static constexpr int Q_COL = O_COL + D;
+  static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory budget");
 };
 
 struct PrefillArgs {
@@ -61,6 +61,7 @@ struct PrefillArgs {
   int num_q_heads;
   int num_kv_heads;
   int num_clusters;
+  const __nv_bfloat16* q;         // [Q, Hq, D]
   const int32_t* q_positions;     // [Q]
   int local_start;                // first position of the window (do_local)
   int local_pos0;                 // position held by row 0 of the position-ordered K/V
@@ -74,17 +75,17 @@ struct PrefillArgs {
 };
 
 // barrier slots
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_KVFULL = 10, B_KVEMPTY = 14,
-       B_XCHG = 18, B_EPI = 20 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 10, B_KVFULL = 11 };
 
 template <int D, int G>
 __global__ void __launch_bounds__(320, 1)
-window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
-                      const __grid_constant__ CUtensorMap tmap_ok,
+window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
                       const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
   using C = AttnCfg<D>;
   constexpr int QT = 128 / G;
   constexpr int STAGES = C::STAGES;
+  constexpr int B_KVEMPTY = B_KVFULL + STAGES;
+  static_assert(8 * (B_KVEMPTY + STAGES) <= 256, "barrier area");
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(a.status, 0, STATUS_SMEM_ALIGN);
@@ -102,15 +103,14 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int q_tile0 = blockIdx.x * QT;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(B_QFULL), 1);
+    mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_SEMPTY + b), 256);
       mbar_init(bar(B_PFULL + b), 256);
-      mbar_init(bar(B_PEMPTY + b), 1);
+      mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
@@ -133,19 +133,12 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
     const int qpos = qvalid ? a.q_positions[slot] : -1;
-    const unsigned vmask = __ballot_sync(0xffffffffu, qvalid);
     int max_qpos = qpos;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) max_qpos = max(max_qpos, __shfl_xor_sync(0xffffffffu, max_qpos, o));
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_ok);
       tma_prefetch_desc(&tmap_ov);
-      (void)vmask;
-      mbar_arrive_expect_tx(bar(B_QFULL), (uint32_t)C::Q_BYTES);
-      // consecutive queries: one box per 64-column slab covers the whole tile
-      for (int sl = 0; sl < C::SLABS; ++sl)
-        tma_load_3d(smem_u32(smem + C::Q_OFF + sl * 128 * 128), &tmap_q, bar(B_QFULL), sl * 64, h * G, q_tile0);
       const int last = min(max_qpos, a.local_pos0 + a.local_rows - 1);
       int tile = 0;
       bool ok = true;
@@ -158,7 +151,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         info[s].rows = rows;
         info[s].kpos0 = p;
         mbar_arrive_expect_tx(bar(B_KVFULL + s), (uint32_t)BLOCK_N * D * 2 * 2);
-        for (int sl = 0; sl < C::SLABS; ++sl) {
+        for (int sl = 0; sl < D / 64; ++sl) {
           tma_load_2d(smem_u32(smem + C::K_OFF + s * C::KV_BYTES + sl * BLOCK_N * 128), &tmap_ok,
                       bar(B_KVFULL + s), h * D + sl * 64, p - a.local_pos0);
           tma_load_2d(smem_u32(smem + C::V_OFF + s * C::KV_BYTES + sl * BLOCK_N * 128), &tmap_ov,
@@ -176,47 +169,67 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
+    // S(j) = Q K(j)^T goes out as soon as K(j) has landed and P V(j-2), which reads the same
+    // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
+    // as soon as the softmax warps have stored P(j): whichever is ready first.
     if (elect_one()) {
-      const uint32_t q_base = smem_u32(smem + C::Q_OFF);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
-      int np_prev = 0;
-      auto issue_pv = [&](int t, int np) -> bool {
-        const int b = t & 1, s = t % STAGES;
-        if (!mbar_wait(bar(B_PFULL + b), (t >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) return false;
-        tc_fence_after();
-        const uint32_t p_base = smem_u32(smem + C::P_OFF + b * C::P_BYTES);
-        const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
-        for (int kk = 0; kk < np; ++kk)
-          umma_ss(tmem_base + C::O_COL, make_smem_desc(p_base + kk * 32, 16, 1024),
-                  make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
-                  (t > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(B_KVEMPTY + s));
-        umma_commit(bar(B_PEMPTY + b));
-        return true;
-      };
-      int j = 0;
+      tc_fence_after();
+      int next_qk = 0, next_pv = 0, end_tile = INT_MAX;
+      int np_of[4] = {0, 0, 0, 0};
+      unsigned long long t0 = globaltimer();
+      uint32_t idle = 0;
       while (ok) {
-        const int s = j % STAGES, b = j & 1;
-        if (!mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
-        const int np = info[s].npages;
-        if (np == 0) break;
-        if (!mbar_wait(bar(B_SEMPTY + b), ((j >> 1) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-        const uint32_t idesc_qk = make_idesc_bf16(128, np * PAGE, false, false);
+        bool progress = false;
+        if (next_qk < end_tile && next_qk - next_pv < 2) {
+          const int j = next_qk, s = j % STAGES, b = j & 1;
+          if (mbar_try_wait(bar(B_KVFULL + s), (j / STAGES) & 1)) {
+            const int np = info[s].npages;
+            if (np == 0) {
+              end_tile = j;
+            } else {
+              tc_fence_after();
+              np_of[j & 3] = np;
+              const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
+              const uint32_t idesc_qk = make_idesc_bf16(128, np * PAGE, false, false);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-          umma_ss(tmem_base + b * BLOCK_N, make_smem_desc(q_base + sl * 128 * 128 + ko, 16, 1024),
-                  make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+                umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8,
+                        make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+              }
+              umma_commit(bar(B_SFULL + b));
+              ++next_qk;
+            }
+            progress = true;
+          }
         }
-        umma_commit(bar(B_SFULL + b));
-        if (j > 0 && !issue_pv(j - 1, np_prev)) { ok = false; break; }
-        np_prev = np;
-        ++j;
+        if (next_pv < next_qk) {
+          const int t = next_pv, b = t & 1, s = t % STAGES;
+          if (mbar_try_wait(bar(B_PFULL + b), (t >> 1) & 1)) {
+            tc_fence_after();
+            const int np = np_of[t & 3];
+            const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
+            for (int kk = 0; kk < np; ++kk)
+              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + kk * 8,
+                      make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
+                      (t > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(bar(B_KVEMPTY + s));
+            umma_commit(bar(B_PVDONE + b));
+            ++next_pv;
+            progress = true;
+          }
+        }
+        if (next_pv == end_tile) break;
+        if (progress) {
+          idle = 0;
+        } else if ((++idle & 0x3ff) == 0) {
+          if (idle == 0x400) t0 = globaltimer();
+          if (*abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; ok = false; }
+          else if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(a.status, 0, STATUS_TIMEOUT_MMA); ok = false; }
+        }
       }
-      if (ok && j > 0) ok = issue_pv(j - 1, np_prev);
       if (ok) umma_commit(bar(B_OREADY));
     }
   } else {
@@ -230,6 +243,9 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int qi = qvalid ? slot : 0;
     const int qpos = qvalid ? a.q_positions[qi] : -1;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
+    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+                                    bar(B_QFULL));
     float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
     unsigned long long att = 0;
     bool ok = true;
@@ -253,7 +269,6 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tmem_ld_wait();
       }
       tc_fence_before();
-      mbar_arrive(bar(B_SEMPTY + b));
       // keys of this half at or before the row's position; tiles wholly below the diagonal for
       // every row of the warp need no mask (scaling is folded into the exponent)
       const int lim = min(rows, qpos - kpos0 + 1) - hf * 32;
@@ -272,17 +287,15 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
       }
       if (t == 0) att += min(max(lim, 0), 32);
-      ok = attn::softmax_half_tile<D, C::O_COL, BLOCK_N>(
-          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, smem + C::P_OFF + b * C::P_BYTES, xchg,
-          bar(B_XCHG), bar(B_PEMPTY + b), bar(B_PEMPTY + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2,
-          m_ref, l_part, l_rnd, abort_flag, a.status);
+      ok = attn::softmax_half_tile<D, C::O_COL>(
+          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
+          bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd, abort_flag, a.status);
       if (!ok) break;
     }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
     attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::P_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
                                      ok && qvalid, 0, a.out + hidx * D, nullptr,
                                      a.partial ? a.partial + hidx * D : nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);
@@ -300,18 +313,11 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 template <int D, int G>
-int launch_prefill(const void* q, const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
+int launch_prefill(const void* ordered_k, const void* ordered_v, int64_t ordered_rows,
                    const PrefillArgs& a, cudaStream_t st) {
   using C = AttnCfg<D>;
   constexpr int QT = 128 / G;
-  CUtensorMap mq, mok, mov;
-  {
-    uint64_t d[3] = {(uint64_t)D, (uint64_t)a.num_q_heads, (uint64_t)a.num_queries};
-    uint64_t s[2] = {(uint64_t)D * 2, (uint64_t)a.num_q_heads * D * 2};
-    uint32_t b[3] = {64, (uint32_t)G, (uint32_t)QT};
-    int rc = semblo::make_tensor_map_bf16(&mq, q, 3, d, s, b);
-    if (rc) return rc;
-  }
+  CUtensorMap mok, mov;
   const uint64_t row_bytes = (uint64_t)a.num_kv_heads * D * 2;
   uint32_t box[2] = {64, BLOCK_N};
   uint64_t d[2] = {(uint64_t)a.num_kv_heads * D, (uint64_t)ordered_rows};
@@ -322,7 +328,7 @@ int launch_prefill(const void* q, const void* ordered_k, const void* ordered_v, 
   auto kern = window_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 320, C::TOTAL, st>>>(mq, mok, mov, a);
+  kern<<<grid, 320, C::TOTAL, st>>>(mok, mov, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
@@ -339,12 +345,14 @@ extern "C" int semblo_window_prefill(const void* q, int num_queries, int num_q_h
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
   SEMBLO_REQUIRE(ordered_k != nullptr && ordered_v != nullptr && q_positions != nullptr, "K, V and positions are required");
   SEMBLO_REQUIRE(local_start >= ordered_pos0, "the window starts before the first row of K/V");
+  SEMBLO_REQUIRE(q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15) == 0, "q must be 16-byte aligned");
   if (num_queries == 0) return 0;
   PrefillArgs a;
   a.num_queries = num_queries;
   a.num_q_heads = num_q_heads;
   a.num_kv_heads = num_kv_heads;
   a.num_clusters = 0;
+  a.q = (const __nv_bfloat16*)q;
   a.q_positions = q_positions;
   a.local_start = local_start;
   a.local_pos0 = ordered_pos0;
@@ -358,7 +366,7 @@ extern "C" int semblo_window_prefill(const void* q, int num_queries, int num_q_h
   const int g = num_q_heads / num_kv_heads;
   cudaStream_t st = (cudaStream_t)stream;
 #define SEMBLO_PREFILL_CASE(DD, GG) \
-  if (head_dim == DD && g == GG) return launch_prefill<DD, GG>(q, ordered_k, ordered_v, ordered_rows, a, st);
+  if (head_dim == DD && g == GG) return launch_prefill<DD, GG>(ordered_k, ordered_v, ordered_rows, a, st);
   SEMBLO_PREFILL_CASE(256, 4)
   SEMBLO_PREFILL_CASE(128, 4)
   SEMBLO_PREFILL_CASE(256, 8)

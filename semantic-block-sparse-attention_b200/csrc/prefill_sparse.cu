@@ -33,7 +33,7 @@ using semblo::ceil_div;
 namespace {
 
 constexpr int BLOCK_N = 64;
-constexpr int PLAN_STAGES = 3;
+constexpr int PLAN_STAGES = 8;
 constexpr float LOG2EF = 1.4426950408889634f;
 
 struct Plan {
@@ -45,26 +45,27 @@ struct Plan {
 
 template <int D>
 struct GatherCfg {
-  static constexpr int STAGES = D >= 256 ? 2 : 4;
+  static constexpr int STAGES = D >= 256 ? 3 : 6;
   static constexpr int SLABS = D / 64;
-  static constexpr int Q_BYTES = 128 * D * 2;
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
-  static constexpr int P_BYTES = 128 * BLOCK_N * 2;
-  static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = Q_OFF + Q_BYTES;
+  static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-  static constexpr int P_OFF = V_OFF + STAGES * KV_BYTES;
-  static constexpr int PLAN_OFF = P_OFF + 2 * P_BYTES;
+  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][2][128]
+  static constexpr int PLAN_OFF = EPI_OFF + 2048;
   static constexpr int XCHG_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);   // bf16 [2][2][128]
   static constexpr int BAR_OFF = XCHG_OFF + 1024;
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (13 + 4 * STAGES + 2 * PLAN_STAGES);
+  static constexpr int MISC_OFF = BAR_OFF + 8 * (11 + 4 * STAGES + 2 * PLAN_STAGES);
   static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
-  static constexpr int TMEM_COLS = D >= 256 ? 512 : 256;
-  static constexpr int O_COL = 2 * BLOCK_N;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int O_COL = 2 * BLOCK_N;        // S/P buffers, then O, then Q
+  static constexpr int Q_COL = O_COL + D;
+  static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory budget");
+  static_assert(TOTAL <= 232448, "shared memory budget");
 };
 
 struct GatherArgs {
   int num_queries, num_q_heads, num_kv_heads, num_clusters;
+  const __nv_bfloat16* q;       // [Q, Hq, D]
   const int32_t* q_order;       // [Hkv, Q] tile order, or null
   const int32_t* qmask;         // [Q, Hkv, C/32]
   const int32_t* causal_sizes;  // [Hkv, C]
@@ -93,7 +94,7 @@ struct GatherArgs {
 #define TR_FLUSH(role)
 #endif
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_SEMPTY = 4, B_PFULL = 6, B_PEMPTY = 8, B_XCHG = 10, B_EPI = 12, B_KFULL = 13 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 10, B_KFULL = 11 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -104,7 +105,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 
 template <int D, int G>
 __global__ void __launch_bounds__(448, 1)
-sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const GatherArgs a) {
+sparse_gather_prefill_kernel(const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
   constexpr int STAGES = C::STAGES;
@@ -130,15 +131,14 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   const int q_tile0 = blockIdx.x * QT;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(B_QFULL), 1);
+    mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_SEMPTY + b), 256);
       mbar_init(bar(B_PFULL + b), 256);
-      mbar_init(bar(B_PEMPTY + b), 1);
+      mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KFULL + s), 1);
@@ -163,22 +163,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
-    // ------------------------------------------------------------ planner (+ Q load)
+    // ------------------------------------------------------------ planner
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
     const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
-    const unsigned vmask = __ballot_sync(0xffffffffu, qvalid);
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_q);
-      mbar_arrive_expect_tx(bar(B_QFULL), (uint32_t)__popc(vmask) * G * D * 2);
-    }
-    for (int i = 0; i < QT; ++i) {
-      const int qsrc = __shfl_sync(0xffffffffu, qi, i);
-      if (lane == 0 && ((vmask >> i) & 1))
-        for (int sl = 0; sl < C::SLABS; ++sl)
-          tma_load_3d(smem_u32(smem + C::Q_OFF + sl * 128 * 128 + i * G * 128), &tmap_q, bar(B_QFULL),
-                      sl * 64, h * G, qsrc);
-    }
     const int nwords = a.num_clusters >> 5;
     const int32_t* qm = a.qmask + ((int64_t)qi * a.num_kv_heads + h) * nwords;
     const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
@@ -351,12 +339,13 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     TR_FLUSH(is_v ? 2 : 1)
   } else if (warp == 13) {
     // ------------------------------------------------------------ UMMA issuer
-    // S(j) = Q K(j)^T is issued as soon as K(j) has landed and the S buffer is free;
-    // O += P(j) V(j) as soon as the softmax warps have written P(j): whichever is ready first.
+    // S(j) = Q K(j)^T is issued as soon as K(j) has landed and P V(j-2), which reads the same
+    // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
+    // as soon as the softmax warps have stored P(j): whichever is ready first.
     if (elect_one()) {
-      const uint32_t q_base = smem_u32(smem + C::Q_OFF);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+      tc_fence_after();
       int next_qk = 0, next_pv = 0, end_tile = INT_MAX, plan_seen = -1, cnt_cur = 0;
       int np_of[4] = {0, 0, 0, 0};                    // pages of the tiles in flight (index tile & 3)
       unsigned long long t0 = globaltimer();
@@ -373,8 +362,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
             if (cnt_cur == 0) end_tile = j;
             progress = true;
           }
-          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait(bar(B_KFULL + s), (j / STAGES) & 1) &&
-              mbar_try_wait(bar(B_SEMPTY + b), ((j >> 1) & 1) ^ 1)) {
+          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait(bar(B_KFULL + s), (j / STAGES) & 1)) {
             tc_fence_after();
             const int np = (cnt_cur + 15) >> 4;
             np_of[j & 3] = np;
@@ -383,7 +371,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-              umma_ss(tmem_base + b * BLOCK_N, make_smem_desc(q_base + sl * 128 * 128 + ko, 16, 1024),
+              umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8,
                       make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
             }
             umma_commit(bar(B_KEMPTY + s));
@@ -397,14 +385,13 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           if (mbar_try_wait(bar(B_PFULL + b), (t >> 1) & 1) && mbar_try_wait(bar(B_VFULL + s), (t / STAGES) & 1)) {
             tc_fence_after();
             const int np = np_of[t & 3];
-            const uint32_t p_base = smem_u32(smem + C::P_OFF + b * C::P_BYTES);
             const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
             for (int kk = 0; kk < np; ++kk)
-              umma_ss(tmem_base + C::O_COL, make_smem_desc(p_base + kk * 32, 16, 1024),
+              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + kk * 8,
                       make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
                       (t > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar(B_VEMPTY + s));
-            umma_commit(bar(B_PEMPTY + b));
+            umma_commit(bar(B_PVDONE + b));
             ++next_pv;
             progress = true;
           }
@@ -433,6 +420,9 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t qbit = 1u << qslot;
+    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
+    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+                                    bar(B_QFULL));
     float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
     unsigned long long att = 0;
     bool ok = true;
@@ -462,7 +452,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         tmem_ld_wait();
       }
       tc_fence_before();
-      mbar_arrive(bar(B_SEMPTY + b));
       // masked raw logits of this half (scaling is folded into the exponent)
       float tmax = -INFINITY;
       int n_on = 0;
@@ -487,19 +476,17 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
       if (t == 0) att += n_on;
       TR(2)
-      ok = attn::softmax_half_tile<D, C::O_COL, BLOCK_N>(
-          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, smem + C::P_OFF + b * C::P_BYTES, xchg,
-          bar(B_XCHG), bar(B_PEMPTY + b), bar(B_PEMPTY + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd,
-          abort_flag, a.status);
+      ok = attn::softmax_half_tile<D, C::O_COL>(
+          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
+          bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd, abort_flag, a.status);
       if (!ok) break;
       TR(4)
     }
     if (warp == 0) { TR_FLUSH(4) }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
     attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::P_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
                                      ok && qvalid, a.merge, a.out + hidx * D,
                                      a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);
@@ -517,19 +504,13 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
 }
 
 template <int D, int G>
-int launch_gather(const void* q, const GatherArgs& a, cudaStream_t st) {
+int launch_gather(const GatherArgs& a, cudaStream_t st) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
-  CUtensorMap mq;
-  uint64_t d[3] = {(uint64_t)D, (uint64_t)a.num_q_heads, (uint64_t)a.num_queries};
-  uint64_t s[2] = {(uint64_t)D * 2, (uint64_t)a.num_q_heads * D * 2};
-  uint32_t b[3] = {64, (uint32_t)G, 1};
-  int rc = semblo::make_tensor_map_bf16(&mq, q, 3, d, s, b);
-  if (rc) return rc;
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 448, C::TOTAL, st>>>(mq, a);
+  kern<<<grid, 448, C::TOTAL, st>>>(a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
@@ -549,10 +530,11 @@ extern "C" int semblo_sparse_prefill_gather(
   SEMBLO_REQUIRE(!merge || lse != nullptr, "merging needs the window's log-sum-exp");
   SEMBLO_REQUIRE((reinterpret_cast<uintptr_t>(packed_k) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_v) & 15) == 0,
                  "packed K/V must be 16-byte aligned");
+  SEMBLO_REQUIRE(q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15) == 0, "q must be 16-byte aligned");
   if (num_queries == 0) return 0;
   GatherArgs a;
   a.num_queries = num_queries; a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads;
-  a.num_clusters = num_clusters; a.q_order = q_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
+  a.num_clusters = num_clusters; a.q = (const __nv_bfloat16*)q; a.q_order = q_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
   a.indptr = indptr; a.page_table = page_table;
   a.packed_k = (const __nv_bfloat16*)packed_k; a.packed_v = (const __nv_bfloat16*)packed_v;
   a.scale_log2 = sm_scale * LOG2EF; a.out = (__nv_bfloat16*)out; a.lse = lse; a.merge = merge; a.partial = partial_in;
@@ -560,7 +542,7 @@ extern "C" int semblo_sparse_prefill_gather(
   const int g = num_q_heads / num_kv_heads;
   cudaStream_t st = (cudaStream_t)stream;
 #define SEMBLO_GATHER_CASE(DD, GG) \
-  if (head_dim == DD && g == GG) return launch_gather<DD, GG>(q, a, st);
+  if (head_dim == DD && g == GG) return launch_gather<DD, GG>(a, st);
   SEMBLO_GATHER_CASE(256, 4)
   SEMBLO_GATHER_CASE(128, 4)
   SEMBLO_GATHER_CASE(256, 8)
