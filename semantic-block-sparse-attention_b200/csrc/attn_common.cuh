@@ -20,6 +20,9 @@ using namespace sm100;
 
 constexpr float LN2F = 0.6931471805599453f;
 constexpr float LOG2EF = 1.4426950408889634f;
+// true: O is normalised by the sum of the bf16-rounded weights the tensor core multiplies
+// (two more integer operations per pair of keys); false: by the exact sum, as the LSE is.
+constexpr bool ROUNDED_NORMALISER = false;
 constexpr float RESCALE_GAP = 8.0f;              // log2 units: rescale O only when the max moved by > 2^8
 
 // Rendezvous of the 256 softmax threads on an mbarrier (count 256).  Unlike bar.sync the wait
@@ -63,19 +66,17 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
 template <int D, int O_COL>
 __device__ __forceinline__ bool softmax_half_tile(
     uint32_t (&r)[32], float tmax_raw, int my_pages, int j, int hf, int row, uint32_t lane_addr,
-    uint32_t tmem_base, uint32_t s_col, __nv_bfloat16* xchg /* [2][2][128] */, uint32_t bar_xchg0,
+    uint32_t tmem_base, uint32_t s_col, float* xchg /* [2][2][128] */, uint32_t bar_xchg0,
     uint32_t bar_pvdone_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
     float& l_rnd, volatile int* abort_flag, int* status) {
-  // Both threads of a row must agree on the reference exactly, so each publishes its maximum
-  // rounded UP to bf16 and both take the larger of the two rounded values (a reference slightly
-  // above the true maximum is harmless).  Double-buffered by tile parity: one barrier per tile.
-  // Past this barrier both halves hold their S values in registers, so P may overwrite S.
-  __nv_bfloat16* xc = xchg + (j & 1) * 256;
-  const __nv_bfloat16 mine = __float2bfloat16_ru(tmax_raw);
-  xc[hf * 128 + row] = mine;
+  // Both threads of a row exchange their maxima and take the larger, so they agree on the
+  // reference exactly.  Double-buffered by tile parity: one barrier per tile.  Past this
+  // barrier both halves hold their S values in registers, so P may overwrite S.
+  float* xc = xchg + (j & 1) * 256;
+  xc[hf * 128 + row] = tmax_raw;
   if (!softmax_group_sync(bar_xchg0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, status)) return false;
   tc_fence_after();
-  const float tmax = fmaxf(__bfloat162float(mine), __bfloat162float(xc[(hf ^ 1) * 128 + row])) * scale_log2;
+  const float tmax = fmaxf(tmax_raw, xc[(hf ^ 1) * 128 + row]) * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
   const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
   float alpha = 1.f;
@@ -117,10 +118,8 @@ __device__ __forceinline__ bool softmax_half_tile(
           const uint32_t w = *reinterpret_cast<uint32_t*>(&pr);
           packed[p * 8 + i] = w;
           add += e0 + e1;
-          // O is normalised by the sum of the weights as the tensor core sees them, so the
-          // rounding of P perturbs the convex combination and not its scale; the exact sum
-          // gives the LSE
-          add_rnd += __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
+          if constexpr (ROUNDED_NORMALISER)
+            add_rnd += __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
         }
       } else {
 #pragma unroll
@@ -154,7 +153,8 @@ __device__ __forceinline__ void epilogue_half(bool have_tiles, int hf, int row, 
   if (!softmax_group_sync(bar_epi, 0, abort_flag, status)) return;
   const float l_run = l_part + xchg[(hf ^ 1) * 128 + row];
   const float l_rnd_run = l_rnd + xchg[256 + (hf ^ 1) * 128 + row];
-  const float own = l_rnd_run > 0.f ? l_run / l_rnd_run : 0.f;   // O / l_rnd_run is the normalised partial
+  // O / l_rnd_run is the normalised partial when the rounded sum is kept
+  const float own = !ROUNDED_NORMALISER ? 1.f : (l_rnd_run > 0.f ? l_run / l_rnd_run : 0.f);
   float wa = 0.f, wb = 1.f, denom = l_run, m_new = m_ref;
   if (merge && qvalid) {
     const float l2 = *lse_ptr * LOG2EF;                 // the other partial's LSE in log2 units

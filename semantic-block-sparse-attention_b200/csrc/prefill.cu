@@ -46,8 +46,8 @@ struct AttnCfg {
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][2][128]
-  static constexpr int XCHG_OFF = EPI_OFF + 2048;             // bf16 [2][2][128]
-  static constexpr int BAR_OFF = XCHG_OFF + 1024;
+  static constexpr int XCHG_OFF = EPI_OFF + 2048;             // float [2][2][128]
+  static constexpr int BAR_OFF = XCHG_OFF + 2048;
   static constexpr int INFO_OFF = BAR_OFF + 256;
   static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
   static constexpr int TMEM_COLS = 512;
@@ -92,7 +92,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::XCHG_OFF);
+  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
   TileInfo* info = reinterpret_cast<TileInfo*>(smem + C::INFO_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::INFO_OFF + STAGES * sizeof(TileInfo));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);

@@ -39,7 +39,7 @@ constexpr float LOG2EF = 1.4426950408889634f;
 struct Plan {
   int count;             // rows in the tile (0 = end of stream)
   int pad[3];
-  int row[BLOCK_N];      // logical packed row (before the page table), -1 = zero fill
+  int row[BLOCK_N];      // logical packed row (before the page table); padding rows have mask 0
   uint32_t mask[BLOCK_N];
 };
 
@@ -52,8 +52,8 @@ struct GatherCfg {
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][2][128]
   static constexpr int PLAN_OFF = EPI_OFF + 2048;
-  static constexpr int XCHG_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);   // bf16 [2][2][128]
-  static constexpr int BAR_OFF = XCHG_OFF + 1024;
+  static constexpr int XCHG_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);   // float [2][2][128]
+  static constexpr int BAR_OFF = XCHG_OFF + 2048;
   static constexpr int MISC_OFF = BAR_OFF + 8 * (11 + 4 * STAGES + 2 * PLAN_STAGES);
   static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
   static constexpr int TMEM_COLS = 512;
@@ -96,8 +96,8 @@ struct GatherArgs {
 
 enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 10, B_KFULL = 11 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
@@ -120,7 +120,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  __nv_bfloat16* xchg = reinterpret_cast<__nv_bfloat16*>(smem + C::XCHG_OFF);
+  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
   Plan* plan = reinterpret_cast<Plan*>(smem + C::PLAN_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -172,7 +172,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
     const int32_t* ipt = a.indptr + (int64_t)h * (a.num_clusters + 1);
     int tile = 0, fill = 0;
-    long long gathered = 0;
+    long long gathered = 0, pairs = 0;
     bool ok = true;
     TR_DECL
     auto acquire = [&]() {          // make plan stage of `tile` writable
@@ -224,6 +224,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
           const unsigned m = __ballot_sync(0xffffffffu, (word >> b) & 1u);
           if (lane == b) mask_b = m;
         }
+        pairs += (long long)n_b * __popc(mask_b);    // (query, key) pairs this cluster contributes
         int pre = n_b;                               // inclusive scan over lanes
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -264,13 +265,18 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       const int ps = tile % PLAN_STAGES;
       const int padded = (fill + 15) & ~15;
       for (int i = fill + lane; i < padded; i += 32) {
-        plan[ps].row[i] = -1;
+        plan[ps].row[i] = 0;                           // any valid row: no query attends to it
         plan[ps].mask[i] = 0u;
       }
       publish(fill);
       acquire();
     }
-    if (a.attended && lane == 0 && gathered) atomicAdd(a.attended + 1, (unsigned long long)gathered);
+    if (a.attended) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) pairs += __shfl_xor_sync(0xffffffffu, pairs, o);
+      if (lane == 0 && pairs) atomicAdd(a.attended, (unsigned long long)pairs);
+      if (lane == 0 && gathered) atomicAdd(a.attended + 1, (unsigned long long)gathered);
+    }
     TR(1)
     TR_FLUSH(0)
     if (ok) {
@@ -292,7 +298,12 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     constexpr int ROWS_PER_ITER = 32 / LANES_PER_ROW;
     const int sub = lane / LANES_PER_ROW, l_in = lane % LANES_PER_ROW;
     const int slab = l_in >> 3, chunk = l_in & 7;
-    const int64_t lane_off = (int64_t)h * D + l_in * 8;
+    const __nv_bfloat16* src_lane = src_base + (int64_t)h * D + l_in * 8;
+    // destination of copy u of a group, relative to the group's first row (128-byte swizzle)
+    constexpr int GROUP = 8;
+    uint32_t dst_off[GROUP];
+#pragma unroll
+    for (int u = 0; u < GROUP; ++u) dst_off[u] = swz128(u * ROWS_PER_ITER + sub, chunk);
     TR_DECL
     for (int t = par;; t += 2) {
       const int ps = t % PLAN_STAGES, s = t % STAGES;
@@ -306,27 +317,24 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       const int n16 = (cnt + 15) & ~15;
       if (a.page_table) {
         // logical row -> physical row of the paged pool: 64 independent lookups in flight
-        if (lane < n16 && r_lo >= 0) r_lo = a.page_table[r_lo >> 4] * 16 + (r_lo & 15);
-        if (lane + 32 < n16 && r_hi >= 0) r_hi = a.page_table[r_hi >> 4] * 16 + (r_hi & 15);
+        if (lane < n16) r_lo = a.page_table[r_lo >> 4] * 16 + (r_lo & 15);
+        if (lane + 32 < n16) r_hi = a.page_table[r_hi >> 4] * 16 + (r_hi & 15);
       }
       if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(1)
       const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
       // 8 copies per step: the row indices are fetched first so the shuffles overlap
-      constexpr int GROUP = 8;
+#ifdef SEMBLO_SKIP_COPY
+      if (false)
+#endif
       for (int j0 = 0; j0 < n16; j0 += GROUP * ROWS_PER_ITER) {
         int rows[GROUP];
 #pragma unroll
-        for (int u = 0; u < GROUP; ++u) {
-          const int j = j0 + u * ROWS_PER_ITER + sub;
-          rows[u] = __shfl_sync(0xffffffffu, j0 < 32 ? r_lo : r_hi, j & 31);
-        }
+        for (int u = 0; u < GROUP; ++u)
+          rows[u] = __shfl_sync(0xffffffffu, j0 < 32 ? r_lo : r_hi, (j0 + u * ROWS_PER_ITER + sub) & 31);
 #pragma unroll
-        for (int u = 0; u < GROUP; ++u) {
-          const int j = j0 + u * ROWS_PER_ITER + sub;
-          const int64_t off = (int64_t)max(rows[u], 0) * row_elems + lane_off;
-          cp_async16(base + swz128(j, chunk), src_base + off, rows[u] >= 0 ? 16u : 0u);
-        }
+        for (int u = 0; u < GROUP; ++u)
+          cp_async16(base + j0 * 128 + dst_off[u], src_lane + (int64_t)rows[u] * row_elems);
       }
       TR(2)
       cp_async_wait_all();
@@ -424,7 +432,6 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
                                     bar(B_QFULL));
     float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
-    unsigned long long att = 0;
     bool ok = true;
     int j = 0;
     TR_DECL
@@ -452,9 +459,14 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
         tmem_ld_wait();
       }
       tc_fence_before();
+#ifdef SEMBLO_SKIP_SOFTMAX
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
+      mbar_arrive(bar(B_PFULL + b));
+      continue;
+#endif
       // masked raw logits of this half (scaling is folded into the exponent)
       float tmax = -INFINITY;
-      int n_on = 0;
       const uint4* mk = reinterpret_cast<const uint4*>(plan[ps].mask + hf * 32);
 #pragma unroll
       for (int g4 = 0; g4 < 8; ++g4) {
@@ -468,13 +480,11 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
             const float sraw = allowed ? __uint_as_float(r[col]) : -INFINITY;
             r[col] = __float_as_uint(sraw);
             tmax = fmaxf(tmax, sraw);
-            n_on += allowed;
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-      if (t == 0) att += n_on;
       TR(2)
       ok = attn::softmax_half_tile<D, C::O_COL>(
           r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
@@ -490,12 +500,6 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
                                      ok && qvalid, a.merge, a.out + hidx * D,
                                      a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);
-    if (ok && a.attended) {
-      if (!qvalid) att = 0;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) att += __shfl_xor_sync(0xffffffffu, att, o);
-      if (lane == 0 && att) atomicAdd(a.attended, att);
-    }
     tc_fence_before();
   }
   __syncthreads();
