@@ -25,7 +25,7 @@ constexpr float LOG2EF = 1.4426950408889634f;
 constexpr bool ROUNDED_NORMALISER = false;
 constexpr float RESCALE_GAP = 8.0f;              // log2 units: rescale O only when the max moved by > 2^8
 
-// Rendezvous of the 256 softmax threads on an mbarrier (count 256).  Unlike bar.sync the wait
+// Rendezvous of softmax threads on an mbarrier (count = the threads that meet).  Unlike bar.sync the wait
 // is bounded and observes the abort flag, so a role that gave up cannot strand its partners.
 __device__ __forceinline__ bool softmax_group_sync(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                    int* status) {
@@ -70,11 +70,12 @@ __device__ __forceinline__ bool softmax_half_tile(
     uint32_t bar_pvdone_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
     float& l_rnd, volatile int* abort_flag, int* status) {
   // Both threads of a row exchange their maxima and take the larger, so they agree on the
-  // reference exactly.  Double-buffered by tile parity: one barrier per tile.  Past this
-  // barrier both halves hold their S values in registers, so P may overwrite S.
+  // reference exactly.  The two warps that share 32 rows meet on a barrier of their own (count
+  // 64; double-buffered by tile parity), so the four warp pairs do not wait for one another.
+  // Past this barrier both threads hold their S values in registers, so P may overwrite S.
   float* xc = xchg + (j & 1) * 256;
   xc[hf * 128 + row] = tmax_raw;
-  if (!softmax_group_sync(bar_xchg0 + 8 * (j & 1), (j >> 1) & 1, abort_flag, status)) return false;
+  if (!softmax_group_sync(bar_xchg0 + 8 * ((j & 1) * 4 + (row >> 5)), (j >> 1) & 1, abort_flag, status)) return false;
   tc_fence_after();
   const float tmax = fmaxf(tmax_raw, xc[(hf ^ 1) * 128 + row]) * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
@@ -104,7 +105,7 @@ __device__ __forceinline__ bool softmax_half_tile(
     }
   }
   const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-  float add = 0.f, add_rnd = 0.f;
+  float add = 0.f, add2 = 0.f, add_rnd = 0.f;
   if (my_pages > 0) {
     uint32_t packed[16];
 #pragma unroll
@@ -117,7 +118,7 @@ __device__ __forceinline__ bool softmax_half_tile(
           __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
           const uint32_t w = *reinterpret_cast<uint32_t*>(&pr);
           packed[p * 8 + i] = w;
-          add += e0 + e1;
+          if (i & 1) add2 += e0 + e1; else add += e0 + e1;
           if constexpr (ROUNDED_NORMALISER)
             add_rnd += __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
         }
@@ -129,7 +130,7 @@ __device__ __forceinline__ bool softmax_half_tile(
     // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 16 hf + i of the P operand
     tmem_st16(tmem_base + lane_addr + s_col + hf * 16, packed);
   }
-  l_part += add;
+  l_part += add + add2;
   l_rnd += add_rnd;
   tmem_st_wait();
   tc_fence_before();

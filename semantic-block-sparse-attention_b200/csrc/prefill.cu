@@ -31,6 +31,7 @@ namespace {
 constexpr int PAGE = 16;
 constexpr int PAGES_PER_TILE = 4;
 constexpr int BLOCK_N = PAGE * PAGES_PER_TILE;     // 64 keys per tile
+constexpr uint32_t POLL_NS = 50;      // how long the UMMA thread sleeps on one barrier before it looks at the other
 
 struct TileInfo {
   int npages;          // 16-row groups in the tile, 0 = end of stream
@@ -75,7 +76,7 @@ struct PrefillArgs {
 };
 
 // barrier slots
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 10, B_KVFULL = 11 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 16, B_KVFULL = 17 };
 
 template <int D, int G>
 __global__ void __launch_bounds__(320, 1)
@@ -106,8 +107,8 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
+    for (int i = 0; i < 8; ++i) mbar_init(bar(B_XCHG + i), 64);     // [tile parity][warp pair]
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
       mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
@@ -184,7 +185,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         bool progress = false;
         if (next_qk < end_tile && next_qk - next_pv < 2) {
           const int j = next_qk, s = j % STAGES, b = j & 1;
-          if (mbar_try_wait(bar(B_KVFULL + s), (j / STAGES) & 1)) {
+          if (mbar_try_wait_for(bar(B_KVFULL + s), (j / STAGES) & 1, POLL_NS)) {
             const int np = info[s].npages;
             if (np == 0) {
               end_tile = j;
@@ -207,7 +208,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         }
         if (next_pv < next_qk) {
           const int t = next_pv, b = t & 1, s = t % STAGES;
-          if (mbar_try_wait(bar(B_PFULL + b), (t >> 1) & 1)) {
+          if (mbar_try_wait_for(bar(B_PFULL + b), (t >> 1) & 1, POLL_NS)) {
             tc_fence_after();
             const int np = np_of[t & 3];
             const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
@@ -274,17 +275,19 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
       const int lim = min(rows, qpos - kpos0 + 1) - hf * 32;
       float tmax = -INFINITY;
       if (my_pages > 0) {
+        float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four short chains
         if (__all_sync(0xffffffffu, lim >= 32)) {
 #pragma unroll
-          for (int col = 0; col < 32; ++col) tmax = fmaxf(tmax, __uint_as_float(r[col]));
+          for (int col = 0; col < 32; ++col) tm[col & 3] = fmaxf(tm[col & 3], __uint_as_float(r[col]));
         } else {
 #pragma unroll
           for (int col = 0; col < 32; ++col) {
             const float sraw = col < lim ? __uint_as_float(r[col]) : -INFINITY;
             r[col] = __float_as_uint(sraw);
-            tmax = fmaxf(tmax, sraw);
+            tm[col & 3] = fmaxf(tm[col & 3], sraw);
           }
         }
+        tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
       }
       if (t == 0) att += min(max(lim, 0), 32);
       ok = attn::softmax_half_tile<D, C::O_COL>(

@@ -33,15 +33,18 @@ using semblo::ceil_div;
 namespace {
 
 constexpr int BLOCK_N = 64;
+constexpr uint32_t POLL_NS = 50;      // how long the UMMA thread sleeps on one barrier before it looks at the other
 constexpr int PLAN_STAGES = 8;
 constexpr float LOG2EF = 1.4426950408889634f;
 
+// The plan ring: stream position p lives at entry p % (PLAN_STAGES * BLOCK_N); tile T is slot
+// T % PLAN_STAGES, i.e. entries [64 slot, 64 slot + 64).
 struct Plan {
-  int count;             // rows in the tile (0 = end of stream)
-  int pad[3];
-  int row[BLOCK_N];      // logical packed row (before the page table); padding rows have mask 0
-  uint32_t mask[BLOCK_N];
+  int row[PLAN_STAGES * BLOCK_N];        // logical packed row (before the page table); padding rows have mask 0
+  uint32_t mask[PLAN_STAGES * BLOCK_N];  // the queries of the tile that attend to the row
+  int count[PLAN_STAGES];                // rows in the tile (0 = end of stream)
 };
+static_assert((PLAN_STAGES & (PLAN_STAGES - 1)) == 0, "the ring index is a mask");
 
 template <int D>
 struct GatherCfg {
@@ -52,9 +55,9 @@ struct GatherCfg {
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][2][128]
   static constexpr int PLAN_OFF = EPI_OFF + 2048;
-  static constexpr int XCHG_OFF = PLAN_OFF + PLAN_STAGES * (int)sizeof(Plan);   // float [2][2][128]
+  static constexpr int XCHG_OFF = PLAN_OFF + (int)sizeof(Plan);   // float [2][2][128]
   static constexpr int BAR_OFF = XCHG_OFF + 2048;
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (11 + 4 * STAGES + 2 * PLAN_STAGES);
+  static constexpr int MISC_OFF = BAR_OFF + 8 * (17 + 4 * STAGES + 2 * PLAN_STAGES);
   static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL = 2 * BLOCK_N;        // S/P buffers, then O, then Q
@@ -88,13 +91,16 @@ struct GatherArgs {
 #define TR_DECL long long tr_last = clock64(); long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #define TR(i) { const long long tr_now = clock64(); tr[i] += tr_now - tr_last; tr_last = tr_now; }
 #define TR_FLUSH(role) if (a.attended && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) if (tr[i_]) atomicAdd(a.attended + 8 + 8 * (role) + i_, (unsigned long long)tr[i_]); }
+// timeline of one CTA: event e of tile T at attended[64 + 256 e + T]
+#define EV(e, T) if (a.attended && blockIdx.x == 5 && blockIdx.y == 0 && (T) < 256) a.attended[64 + 256 * (e) + (T)] = (unsigned long long)clock64();
 #else
 #define TR_DECL
 #define TR(i)
 #define TR_FLUSH(role)
+#define EV(e, T)
 #endif
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 10, B_KFULL = 11 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 16, B_KFULL = 17 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -134,8 +140,8 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
+    for (int i = 0; i < 8; ++i) mbar_init(bar(B_XCHG + i), 64);     // [tile parity][warp pair]
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(B_XCHG + b), 256);
       mbar_init(bar(B_SFULL + b), 1);
       mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
@@ -171,30 +177,39 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     const int32_t* qm = a.qmask + ((int64_t)qi * a.num_kv_heads + h) * nwords;
     const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
     const int32_t* ipt = a.indptr + (int64_t)h * (a.num_clusters + 1);
-    int tile = 0, fill = 0;
-    long long gathered = 0, pairs = 0;
+    // The selected clusters' visible rows form one stream; 64 consecutive stream positions
+    // are a tile, and tile T lives in plan slot T % PLAN_STAGES.
+    int pos = 0;                 // stream position of the next row
+    int acq = 0, pub = 0;        // tiles made writable / published so far
+    long long pairs = 0;
     bool ok = true;
     TR_DECL
-    auto acquire = [&]() {          // make plan stage of `tile` writable
-      const int ps = tile % PLAN_STAGES;
+    auto acquire_to = [&](int upto) {          // make tiles [acq, upto) writable
       TR(1)
-      if (lane == 0)
-        ok = mbar_wait(bar(B_PLANEMPTY + ps), ((tile / PLAN_STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD);
-      ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+      while (ok && acq < upto) {
+        if (lane == 0)
+          ok = mbar_wait(bar(B_PLANEMPTY + acq % PLAN_STAGES), ((acq / PLAN_STAGES) & 1) ^ 1, abort_flag, a.status,
+                         STATUS_TIMEOUT_LOAD);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        ++acq;
+      }
       TR(0)
     };
-    auto publish = [&](int count) {
-      const int ps = tile % PLAN_STAGES;
+    auto publish_to = [&](int upto, int last_count) {   // publish tiles [pub, upto), the last with last_count rows
       __syncwarp();
-      if (lane == 0) {
-        plan[ps].count = count;
-        mbar_arrive(bar(B_PLANFULL + ps));
-      }
-      gathered += count;
-      ++tile;
-      fill = 0;
+      if (lane == 0)
+        for (int t = pub; t < upto; ++t) {
+          plan->count[t % PLAN_STAGES] = t == upto - 1 ? last_count : BLOCK_N;
+          mbar_arrive(bar(B_PLANFULL + t % PLAN_STAGES));
+          EV(0, t)
+        }
+      pub = max(pub, upto);
     };
-    acquire();
+    auto put = [&](int p, int row, unsigned mask) {
+      const int e = p & (PLAN_STAGES * BLOCK_N - 1);
+      plan->row[e] = row;
+      plan->mask[e] = mask;
+    };
     // software pipeline over the bitmask words: word w+2 and the sizes / starts of the clusters
     // of word w+1 are in flight while word w is expanded
     auto load_word = [&](int w) -> unsigned { return (qvalid && w < nwords) ? (unsigned)qm[w] : 0u; };
@@ -202,9 +217,10 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     unsigned any1 = __reduce_or_sync(0xffffffffu, word1);
     int n1 = ((any1 >> lane) & 1) ? csz[lane] : 0;
     int start1 = ((any1 >> lane) & 1) ? ipt[lane] : 0;
+    constexpr int SELF_MAX = 16;     // longer runs are written by the whole warp
     for (int w = 0; w < nwords && ok; ++w) {
       const unsigned word = word1, any = any1;
-      int n_b = max(n1, 0);
+      const int n_b = max(n1, 0);
       const int start_b = start1;
       // prefetch for the following words
       word1 = word2;
@@ -216,74 +232,76 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
         n1 = has1 ? csz[c1] : 0;
         start1 = has1 ? ipt[c1] : 0;
       }
-      if (any != 0) {
-        // mask_b: the queries of the tile that selected cluster (w, lane)
-        unsigned mask_b = 0;
-        for (unsigned tmp = any; tmp; tmp &= tmp - 1) {
-          const int b = __ffs(tmp) - 1;
-          const unsigned m = __ballot_sync(0xffffffffu, (word >> b) & 1u);
-          if (lane == b) mask_b = m;
-        }
-        pairs += (long long)n_b * __popc(mask_b);    // (query, key) pairs this cluster contributes
-        int pre = n_b;                               // inclusive scan over lanes
+      if (any == 0) continue;
+      TR(1)
+      // mask_b: the queries of the tile that selected cluster (w, lane) -- the 32 x 32 bit
+      // matrix (query lane, cluster bit) transposed across the warp in five exchange steps
+      unsigned mask_b = word;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int v = __shfl_up_sync(0xffffffffu, pre, o);
-          if (lane >= o) pre += v;
-        }
-        const int total = __shfl_sync(0xffffffffu, pre, 31);
-        const int excl = pre - n_b;
-        for (int j0 = 0; j0 < total && ok;) {
-          const int cnt = min(min(32, total - j0), BLOCK_N - fill);
-          const int j = j0 + lane;
-          // first lane whose inclusive prefix exceeds j
-          int lo = 0;
-#pragma unroll
-          for (int step = 16; step > 0; step >>= 1) {
-            const int v = __shfl_sync(0xffffffffu, pre, lo + step - 1);
-            if (v <= j) lo += step;
-          }
-          lo = min(lo, 31);
-          const int sb = __shfl_sync(0xffffffffu, start_b, lo);
-          const int eb = __shfl_sync(0xffffffffu, excl, lo);
-          const unsigned mb = __shfl_sync(0xffffffffu, mask_b, lo);
-          if (lane < cnt) {
-            const int ps = tile % PLAN_STAGES;
-            plan[ps].row[fill + lane] = sb + (j - eb);       // logical packed row; the gather warps translate pages
-            plan[ps].mask[fill + lane] = mb;
-          }
-          fill += cnt;
-          j0 += cnt;
-          if (fill == BLOCK_N) {
-            publish(BLOCK_N);
-            acquire();
-          }
-        }
+      for (int d = 16; d > 0; d >>= 1) {
+        const unsigned m = d == 16 ? 0x0000ffffu : d == 8 ? 0x00ff00ffu : d == 4 ? 0x0f0f0f0fu
+                         : d == 2 ? 0x33333333u : 0x55555555u;             // columns whose bit d is clear
+        const unsigned y = __shfl_xor_sync(0xffffffffu, mask_b, d);
+        mask_b = (lane & d) ? (((y & ~m) >> d) | (mask_b & ~m)) : ((mask_b & m) | ((y & m) << d));
       }
+      TR(2)
+      pairs += (long long)n_b * __popc(mask_b);      // (query, key) pairs this cluster contributes
+      int pre = n_b;                                 // inclusive scan over lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, pre, o);
+        if (lane >= o) pre += v;
+      }
+      const int total = __shfl_sync(0xffffffffu, pre, 31);
+      if (total == 0) continue;
+      // lane b owns stream positions [a_b, e_b): its cluster's rows start_b, start_b + 1, ...
+      const int a_b = pos + pre - n_b, e_b = pos + pre, end = pos + total;
+      const int row_minus_pos = start_b - a_b;
+      int wlo = pos;
+      TR(3)
+      while (wlo < end && ok) {
+        // a wave: as far as the plan ring reaches beyond the oldest unpublished tile
+        const int whi = min(end, (pub + PLAN_STAGES) * BLOCK_N);
+        acquire_to((whi + BLOCK_N - 1) / BLOCK_N);
+        if (!ok) break;
+        const int lo = max(a_b, wlo), hi = min(e_b, whi);
+        const bool big = hi - lo > SELF_MAX;
+        if (!big)
+          for (int p = lo; p < hi; ++p) put(p, row_minus_pos + p, mask_b);
+        TR(4)
+        for (unsigned bigs = __ballot_sync(0xffffffffu, big); bigs; bigs &= bigs - 1) {
+          const int bb = __ffs(bigs) - 1;
+          const int blo = __shfl_sync(0xffffffffu, lo, bb), bhi = __shfl_sync(0xffffffffu, hi, bb);
+          const int brow = __shfl_sync(0xffffffffu, row_minus_pos, bb);
+          const unsigned bmask = __shfl_sync(0xffffffffu, mask_b, bb);
+          for (int p = blo + lane; p < bhi; p += 32) put(p, brow + p, bmask);
+        }
+        TR(5)
+        publish_to(whi / BLOCK_N, BLOCK_N);
+        wlo = whi;
+        TR(6)
+      }
+      pos = end;
     }
+    const int fill = pos % BLOCK_N;
     if (ok && fill > 0) {
-      const int ps = tile % PLAN_STAGES;
+      // the open tile: pad to whole 16-row groups with a valid row that no query attends to
       const int padded = (fill + 15) & ~15;
-      for (int i = fill + lane; i < padded; i += 32) {
-        plan[ps].row[i] = 0;                           // any valid row: no query attends to it
-        plan[ps].mask[i] = 0u;
-      }
-      publish(fill);
-      acquire();
+      for (int i = fill + lane; i < padded; i += 32) put(pos - fill + i, 0, 0u);
+      publish_to(pub + 1, fill);
     }
     if (a.attended) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) pairs += __shfl_xor_sync(0xffffffffu, pairs, o);
       if (lane == 0 && pairs) atomicAdd(a.attended, (unsigned long long)pairs);
-      if (lane == 0 && gathered) atomicAdd(a.attended + 1, (unsigned long long)gathered);
+      if (lane == 0 && pos) atomicAdd(a.attended + 1, (unsigned long long)pos);
     }
     TR(1)
     TR_FLUSH(0)
-    if (ok) {
-      // end of stream, once per gather warp (they alternate tiles)
-      publish(0);
-      acquire();
-      if (ok) publish(0);
+    // end of stream, once per gather warp (they alternate tiles)
+    for (int e = 0; e < 2 && ok; ++e) {
+      acquire_to(pub + 1);
+      if (ok) publish_to(pub + 1, 0);
     }
   } else if (warp >= 9 && warp <= 12) {
     // ------------------------------------------------------------ gather warps
@@ -309,9 +327,10 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       const int ps = t % PLAN_STAGES, s = t % STAGES;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(0)
-      const int cnt = plan[ps].count;
+      if (lane == 0) { EV(is_v ? 9 : 1, t) }
+      const int cnt = plan->count[ps];
       if (cnt == 0) break;
-      int r_lo = plan[ps].row[lane], r_hi = plan[ps].row[lane + 32];
+      int r_lo = plan->row[ps * BLOCK_N + lane], r_hi = plan->row[ps * BLOCK_N + lane + 32];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
       const int n16 = (cnt + 15) & ~15;
@@ -322,6 +341,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       }
       if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(1)
+      if (lane == 0) { EV(is_v ? 10 : 2, t) }
       const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
       // 8 copies per step: the row indices are fetched first so the shuffles overlap
 #ifdef SEMBLO_SKIP_COPY
@@ -342,6 +362,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(b_full + s));
+      if (lane == 0) { EV(is_v ? 4 : 3, t) }
       TR(4)
     }
     TR_FLUSH(is_v ? 2 : 1)
@@ -363,15 +384,16 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
         bool progress = false;
         if (next_qk < end_tile && next_qk - next_pv < 2) {
           const int j = next_qk, ps = j % PLAN_STAGES, s = j % STAGES, b = j & 1;
-          if (plan_seen < j && mbar_try_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1)) {
-            cnt_cur = plan[ps].count;
+          if (plan_seen < j && mbar_try_wait_for(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, POLL_NS)) {
+            cnt_cur = plan->count[ps];
             mbar_arrive(bar(B_PLANEMPTY + ps));
             plan_seen = j;
             if (cnt_cur == 0) end_tile = j;
             progress = true;
           }
-          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait(bar(B_KFULL + s), (j / STAGES) & 1)) {
+          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait_for(bar(B_KFULL + s), (j / STAGES) & 1, POLL_NS)) {
             tc_fence_after();
+            TR(1)
             const int np = (cnt_cur + 15) >> 4;
             np_of[j & 3] = np;
             const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
@@ -384,14 +406,17 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
             }
             umma_commit(bar(B_KEMPTY + s));
             umma_commit(bar(B_SFULL + b));
+            TR(2)
+            EV(5, j)
             ++next_qk;
             progress = true;
           }
         }
         if (next_pv < next_qk) {
           const int t = next_pv, b = t & 1, s = t % STAGES;
-          if (mbar_try_wait(bar(B_PFULL + b), (t >> 1) & 1) && mbar_try_wait(bar(B_VFULL + s), (t / STAGES) & 1)) {
+          if (mbar_try_wait_for(bar(B_PFULL + b), (t >> 1) & 1, POLL_NS) && mbar_try_wait_for(bar(B_VFULL + s), (t / STAGES) & 1, POLL_NS)) {
             tc_fence_after();
+            TR(1)
             const int np = np_of[t & 3];
             const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
             for (int kk = 0; kk < np; ++kk)
@@ -400,6 +425,8 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
                       (t > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar(B_VEMPTY + s));
             umma_commit(bar(B_PVDONE + b));
+            TR(3)
+            EV(6, t)
             ++next_pv;
             progress = true;
           }
@@ -441,7 +468,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       ok = mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       TR(0)
-      const int cnt = plan[ps].count;
+      const int cnt = plan->count[ps];
       if (cnt == 0) {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
@@ -452,6 +479,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       TR(1)
+      if (threadIdx.x == 0) { EV(7, j) }
       tc_fence_after();
       uint32_t r[32];
       if (my_pages > 0) {
@@ -466,8 +494,8 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       continue;
 #endif
       // masked raw logits of this half (scaling is folded into the exponent)
-      float tmax = -INFINITY;
-      const uint4* mk = reinterpret_cast<const uint4*>(plan[ps].mask + hf * 32);
+      float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
+      const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hf * 32);
 #pragma unroll
       for (int g4 = 0; g4 < 8; ++g4) {
         if (g4 * 4 < my_pages * 16) {
@@ -479,10 +507,11 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
             const bool allowed = (mm[e] & qbit) != 0u;
             const float sraw = allowed ? __uint_as_float(r[col]) : -INFINITY;
             r[col] = __float_as_uint(sraw);
-            tmax = fmaxf(tmax, sraw);
+            tm[e] = fmaxf(tm[e], sraw);
           }
         }
       }
+      const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
       TR(2)
@@ -490,6 +519,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
           r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
           bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd, abort_flag, a.status);
       if (!ok) break;
+      if (threadIdx.x == 0) { EV(8, j) }
       TR(4)
     }
     if (warp == 0) { TR_FLUSH(4) }
