@@ -1,15 +1,21 @@
 // Softmax / epilogue code shared by the two prefill attention kernels.
 //
-// A tile is 128 rows x 64 keys.  Two warpgroups of 128 threads split the 64 columns of
-// S: thread (half, row) owns columns [32 half, 32 half + 32) of its row.  The row maximum
-// is exchanged through shared memory, the running reference maximum m_ref is kept
-// identical in both threads of a row, each thread keeps the partial sum of its own
-// columns, and each half rescales / finalises its own D/2 columns of O.
+// A tile is 128 rows x 64 keys.  The softmax of a tile is a two-stage pipeline over two
+// warpgroups of 128 threads, one thread per row in each:
+//   mask warps (warps 0-3)  read S from tensor memory, replace the entries the row may not
+//                           attend to by -inf, take the row maximum and write the masked
+//                           logits back over S (kernel-specific code; integer / compare work);
+//   exp warps  (warps 4-7)  read the masked logits, keep the lazily rescaled running maximum
+//                           and the row sum, and write P = exp2(scale * s - m) as bf16 over the
+//                           first 32 columns of the same buffer (exp_tile below; special-
+//                           function-unit work).
+// The two stages work on consecutive tiles at the same time, on different execution pipes of
+// the same scheduler, and a row never needs a cross-thread reduction.
 //
 // Both A operands live in tensor memory, so shared memory holds K / V stages only:
 //   Q  [128 x D]  bf16, two elements per 32-bit column, written once per CTA (stage_q_half);
-//   P  [128 x 64] bf16 in the first 32 columns of the S buffer it was computed from (the
-//      S values are in registers by then), read by O += P V as a TMEM operand.
+//   P  [128 x 64] bf16 in the first 32 columns of the S buffer it was computed from,
+//      read by O += P V as a TMEM operand.
 // An S buffer therefore becomes free when the P V product of its tile has completed.
 #pragma once
 #include "sm100.cuh"
@@ -20,9 +26,6 @@ using namespace sm100;
 
 constexpr float LN2F = 0.6931471805599453f;
 constexpr float LOG2EF = 1.4426950408889634f;
-// true: O is normalised by the sum of the bf16-rounded weights the tensor core multiplies
-// (two more integer operations per pair of keys); false: by the exact sum, as the LSE is.
-constexpr bool ROUNDED_NORMALISER = false;
 constexpr float RESCALE_GAP = 8.0f;              // log2 units: rescale O only when the max moved by > 2^8
 
 // Rendezvous of softmax threads on an mbarrier (count = the threads that meet).  Unlike bar.sync the wait
@@ -59,33 +62,30 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
   mbar_arrive(bar_qfull);
 }
 
-// One half-row of one tile.  r[] holds the 32 raw logits of this half with masked entries
-// already set to -inf; tmax_raw is their maximum.  my_pages = how many 16-column groups of
-// this half exist in the tile (0, 1 or 2).  s_col = first TMEM column of the tile's S buffer,
-// which receives P.  Returns false after a wait timed out.
+// What the mask warps hand to the exp warps for tile j (slot j & 1), besides the masked logits
+// in tensor memory.
+struct TileNote {
+  float row_max[128];    // maximum of the row's masked raw logits (-inf: nothing to attend to)
+  int pages;             // 16-key groups in the tile; 0 = end of the stream
+  int pad[3];
+};
+
+// The exp stage of one tile for one row.  The masked raw logits are in TMEM columns
+// [s_col, s_col + 16 pages); P goes to columns [s_col, s_col + 8 pages).  Returns false after
+// a wait timed out.
 template <int D, int O_COL>
-__device__ __forceinline__ bool softmax_half_tile(
-    uint32_t (&r)[32], float tmax_raw, int my_pages, int j, int hf, int row, uint32_t lane_addr,
-    uint32_t tmem_base, uint32_t s_col, float* xchg /* [2][2][128] */, uint32_t bar_xchg0,
-    uint32_t bar_pvdone_prev, uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
-    float& l_rnd, volatile int* abort_flag, int* status) {
-  // Both threads of a row exchange their maxima and take the larger, so they agree on the
-  // reference exactly.  The two warps that share 32 rows meet on a barrier of their own (count
-  // 64; double-buffered by tile parity), so the four warp pairs do not wait for one another.
-  // Past this barrier both threads hold their S values in registers, so P may overwrite S.
-  float* xc = xchg + (j & 1) * 256;
-  xc[hf * 128 + row] = tmax_raw;
-  if (!softmax_group_sync(bar_xchg0 + 8 * ((j & 1) * 4 + (row >> 5)), (j >> 1) & 1, abort_flag, status)) return false;
-  tc_fence_after();
-  const float tmax = fmaxf(tmax_raw, xc[(hf ^ 1) * 128 + row]) * scale_log2;
+__device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint32_t lane_addr,
+                                         uint32_t tmem_base, uint32_t s_col, uint32_t bar_pvdone_prev,
+                                         uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_run,
+                                         volatile int* abort_flag, int* status) {
+  const float tmax = tmax_raw * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
   const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
   float alpha = 1.f;
   if (need) {
     alpha = fast_exp2(m_ref - tmax);
     m_ref = tmax;
-    l_part *= alpha;
-    l_rnd *= alpha;
+    l_run *= alpha;
   } else if (m_ref == -INFINITY) {
     m_ref = tmax;
   }
@@ -94,9 +94,9 @@ __device__ __forceinline__ bool softmax_half_tile(
     if (!mbar_wait(bar_pvdone_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
     tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < D / 64; ++c) {
+    for (int c = 0; c < D / 32; ++c) {
       uint32_t o[32];
-      const uint32_t addr = tmem_base + lane_addr + O_COL + hf * (D / 2) + c * 32;
+      const uint32_t addr = tmem_base + lane_addr + O_COL + c * 32;
       tmem_ld32(addr, o);
       tmem_ld_wait();
 #pragma unroll
@@ -105,57 +105,55 @@ __device__ __forceinline__ bool softmax_half_tile(
     }
   }
   const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-  float add = 0.f, add2 = 0.f, add_rnd = 0.f;
-  if (my_pages > 0) {
-    uint32_t packed[16];
+  uint32_t plo[16], phi[16];
+  float add0 = 0.f, add1 = 0.f;
+  auto half = [&](int h, uint32_t (&packed)[16]) {
+    uint32_t x[32];
+    tmem_ld32(tmem_base + lane_addr + s_col + h * 32, x);
+    tmem_ld_wait();
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      if (p < my_pages) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i]), scale_log2, neg_m));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(r[p * 16 + 2 * i + 1]), scale_log2, neg_m));
-          __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-          const uint32_t w = *reinterpret_cast<uint32_t*>(&pr);
-          packed[p * 8 + i] = w;
-          if (i & 1) add2 += e0 + e1; else add += e0 + e1;
-          if constexpr (ROUNDED_NORMALISER)
-            add_rnd += __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) packed[p * 8 + i] = 0u;
-      }
+    for (int i = 0; i < 16; ++i) {
+      const float e0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), scale_log2, neg_m));
+      const float e1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), scale_log2, neg_m));
+      __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+      packed[i] = *reinterpret_cast<uint32_t*>(&pr);
+      if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
     }
-    // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 16 hf + i of the P operand
-    tmem_st16(tmem_base + lane_addr + s_col + hf * 16, packed);
-  }
-  l_part += add + add2;
-  l_rnd += add_rnd;
+  };
+  half(0, plo);
+  if (pages > 2) half(1, phi);
+  l_run += add0 + add1;
+  // keys 2 i, 2 i + 1 of the row share column i of the P operand; every load of the masked
+  // logits has completed, so P may overwrite them
+  tmem_st16(tmem_base + lane_addr + s_col, plo);
+  if (pages > 2) tmem_st16(tmem_base + lane_addr + s_col + 16, phi);
   tmem_st_wait();
   tc_fence_before();
   mbar_arrive(bar_pfull_b);
   return true;
 }
 
-// Final write of this half's D/2 output columns.  merge != 0: another partial (normalised
-// output in prev_f32, or in `dst` as bf16 when prev_f32 is null; natural-log LSE in lse_ptr) is
-// LSE-merged with this one.  out_f32 != null: the result is written there in fp32 instead of
-// `dst` (a partial that a later launch merges without an intermediate bf16 rounding).
+// Final write of D/2 output columns by each of the two threads of a row (hf 0: the mask
+// thread, hf 1: the exp thread, which owns the row's running maximum and sum and passes them
+// through xchg).  merge != 0: another partial (normalised output in prev_f32, or in `dst` as
+// bf16 when prev_f32 is null; natural-log LSE in lse_ptr) is LSE-merged with this one.
+// out_f32 != null: the result is written there in fp32 instead of `dst` (a partial that a
+// later launch merges without an intermediate bf16 rounding).
 template <int D, int O_COL>
 __device__ __forceinline__ void epilogue_half(bool have_tiles, int hf, int row, uint32_t lane_addr,
-                                              uint32_t tmem_base, float* xchg, uint32_t bar_epi, float m_ref,
-                                              float l_part, float l_rnd, bool qvalid, int merge,
+                                              uint32_t tmem_base, float* xchg /* [2][128] */, uint32_t bar_epi,
+                                              float m_ref_own, float l_own, bool qvalid, int merge,
                                               __nv_bfloat16* dst /* row base */, const float* prev_f32,
                                               float* out_f32, float* lse_ptr /* this row's slot or null */,
                                               volatile int* abort_flag, int* status) {
-  xchg[hf * 128 + row] = l_part;
-  xchg[256 + hf * 128 + row] = l_rnd;
+  if (hf == 1) {
+    xchg[row] = l_own;
+    xchg[128 + row] = m_ref_own;
+  }
   if (!softmax_group_sync(bar_epi, 0, abort_flag, status)) return;
-  const float l_run = l_part + xchg[(hf ^ 1) * 128 + row];
-  const float l_rnd_run = l_rnd + xchg[256 + (hf ^ 1) * 128 + row];
-  // O / l_rnd_run is the normalised partial when the rounded sum is kept
-  const float own = !ROUNDED_NORMALISER ? 1.f : (l_rnd_run > 0.f ? l_run / l_rnd_run : 0.f);
+  const float l_run = xchg[row];
+  const float m_ref = xchg[128 + row];
+  constexpr float own = 1.f;
   float wa = 0.f, wb = 1.f, denom = l_run, m_new = m_ref;
   if (merge && qvalid) {
     const float l2 = *lse_ptr * LOG2EF;                 // the other partial's LSE in log2 units

@@ -46,9 +46,9 @@ struct AttnCfg {
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][2][128]
-  static constexpr int XCHG_OFF = EPI_OFF + 2048;             // float [2][2][128]
-  static constexpr int BAR_OFF = XCHG_OFF + 2048;
+  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][128]
+  static constexpr int NOTE_OFF = EPI_OFF + 2048;             // attn::TileNote [2]
+  static constexpr int BAR_OFF = NOTE_OFF + 2 * (int)sizeof(attn::TileNote);
   static constexpr int INFO_OFF = BAR_OFF + 256;
   static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
   static constexpr int TMEM_COLS = 512;
@@ -76,7 +76,7 @@ struct PrefillArgs {
 };
 
 // barrier slots
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 16, B_KVFULL = 17 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XFULL = 8, B_EPI = 10, B_KVFULL = 11 };
 
 template <int D, int G>
 __global__ void __launch_bounds__(320, 1)
@@ -93,7 +93,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
+  attn::TileNote* note = reinterpret_cast<attn::TileNote*>(smem + C::NOTE_OFF);
   TileInfo* info = reinterpret_cast<TileInfo*>(smem + C::INFO_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::INFO_OFF + STAGES * sizeof(TileInfo));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -107,15 +107,15 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
-    for (int i = 0; i < 8; ++i) mbar_init(bar(B_XCHG + i), 64);     // [tile parity][warp pair]
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_PFULL + b), 256);
+      mbar_init(bar(B_XFULL + b), 128);
+      mbar_init(bar(B_PFULL + b), 128);
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 9);     // eight softmax warps + the UMMA commit
+      mbar_init(bar(B_KVEMPTY + s), 5);     // four mask warps + the UMMA commit
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -235,8 +235,8 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-3: columns [0, 32) of every tile, warps 4-7: columns [32, 64); thread = row
-    const int hf = warp >> 2;
+    // warps 0-3: mask stage, warps 4-7: exp stage; thread = row in both
+    const int stage = warp >> 2;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
@@ -245,60 +245,84 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     const int qpos = qvalid ? a.q_positions[qi] : -1;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
-    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + stage * (D / 2) : nullptr, stage, lane_addr, tmem_base,
                                     bar(B_QFULL));
-    float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;
     unsigned long long att = 0;
     bool ok = true;
     int j = 0;
-    for (;; ++j) {
-      const int s = j % STAGES, b = j & 1;
-      ok = mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-      if (!ok) break;
-      const int np = info[s].npages;
-      if (np == 0) break;
-      const int rows = info[s].rows, kpos0 = info[s].kpos0;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
-      const int my_pages = min(max(np - 2 * hf, 0), 2);
-      ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t r[32];
-      if (my_pages > 0) {
-        tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + hf * 32, r);
-        tmem_ld_wait();
-      }
-      tc_fence_before();
-      // keys of this half at or before the row's position; tiles wholly below the diagonal for
-      // every row of the warp need no mask (scaling is folded into the exponent)
-      const int lim = min(rows, qpos - kpos0 + 1) - hf * 32;
-      float tmax = -INFINITY;
-      if (my_pages > 0) {
+    if (stage == 0) {
+      for (;; ++j) {
+        const int s = j % STAGES, b = j & 1;
+        ok = mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        const int np = info[s].npages;
+        const int rows = info[s].rows, kpos0 = info[s].kpos0;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
+        if (np == 0) {
+          // end of the stream: the note slot is free once P V of tile j - 2 has been issued
+          if (j >= 2) ok = mbar_wait(bar(B_PVDONE + b), ((j - 2) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+          if (threadIdx.x == 0) note[b].pages = 0;
+          mbar_arrive(bar(B_XFULL + b));
+          break;
+        }
+        ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        tc_fence_after();
+        // keys at or before the row's position; halves wholly below the diagonal for every row
+        // of the warp need no mask and are left as they are
+        const int lim = min(rows, qpos - kpos0 + 1);
         float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four short chains
-        if (__all_sync(0xffffffffu, lim >= 32)) {
 #pragma unroll
-          for (int col = 0; col < 32; ++col) tm[col & 3] = fmaxf(tm[col & 3], __uint_as_float(r[col]));
-        } else {
+        for (int hh = 0; hh < 2; ++hh) {
+          if (2 * hh < np) {
+            uint32_t r[32];
+            const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hh * 32;
+            tmem_ld32(addr, r);
+            tmem_ld_wait();
+            if (__all_sync(0xffffffffu, lim >= 32 * hh + 32)) {
 #pragma unroll
-          for (int col = 0; col < 32; ++col) {
-            const float sraw = col < lim ? __uint_as_float(r[col]) : -INFINITY;
-            r[col] = __float_as_uint(sraw);
-            tm[col & 3] = fmaxf(tm[col & 3], sraw);
+              for (int col = 0; col < 32; col += 2)
+                tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], __uint_as_float(r[col]), __uint_as_float(r[col + 1]));
+            } else {
+#pragma unroll
+              for (int col = 0; col < 32; col += 2) {
+                const float s0 = 32 * hh + col < lim ? __uint_as_float(r[col]) : -INFINITY;
+                const float s1 = 32 * hh + col + 1 < lim ? __uint_as_float(r[col + 1]) : -INFINITY;
+                r[col] = __float_as_uint(s0);
+                r[col + 1] = __float_as_uint(s1);
+                tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], s0, s1);
+              }
+              tmem_st32(addr, r);
+            }
           }
         }
-        tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+        if (t == 0) att += max(lim, 0);
+        note[b].row_max[row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+        if (threadIdx.x == 0) note[b].pages = np;
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(B_XFULL + b));
       }
-      if (t == 0) att += min(max(lim, 0), 32);
-      ok = attn::softmax_half_tile<D, C::O_COL>(
-          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
-          bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd, abort_flag, a.status);
-      if (!ok) break;
+    } else {
+      for (;; ++j) {
+        const int b = j & 1;
+        ok = mbar_wait(bar(B_XFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        const int np = note[b].pages;
+        if (np == 0) break;
+        tc_fence_after();
+        ok = attn::exp_tile<D, C::O_COL>(np, note[b].row_max[row], j, lane_addr, tmem_base, b * BLOCK_N,
+                                         bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_run,
+                                         abort_flag, a.status);
+        if (!ok) break;
+      }
     }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, stage, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_run,
                                      ok && qvalid, 0, a.out + hidx * D, nullptr,
                                      a.partial ? a.partial + hidx * D : nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);

@@ -3,8 +3,10 @@
 //
 // One CTA owns QT = 128 / G queries of one KV head, taken in the caller's tile order
 // (queries with similar selections are placed in the same tile).  Warp roles:
-//   warps 0-7  softmax + epilogue: two warpgroups split the 64 columns of a tile, one
-//              thread per (row, half)
+//   warps 0-3  mask stage of the softmax: per row, keep the logits of the keys whose cluster
+//              the row's query selected, take the row maximum
+//   warps 4-7  exp stage of the softmax: running maximum and sum, P as bf16 into TMEM; both
+//              stages write the output in the epilogue
 //   warp  8    planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
 //              starts fetched by 32 lanes in parallel), and expands the union of selected
 //              clusters into a stream of packed rows, each tagged with the 32-bit set of
@@ -53,11 +55,11 @@ struct GatherCfg {
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][2][128]
+  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][128]
   static constexpr int PLAN_OFF = EPI_OFF + 2048;
-  static constexpr int XCHG_OFF = PLAN_OFF + (int)sizeof(Plan);   // float [2][2][128]
-  static constexpr int BAR_OFF = XCHG_OFF + 2048;
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (17 + 4 * STAGES + 2 * PLAN_STAGES);
+  static constexpr int NOTE_OFF = PLAN_OFF + (int)sizeof(Plan);   // attn::TileNote [2]
+  static constexpr int BAR_OFF = NOTE_OFF + 2 * (int)sizeof(attn::TileNote);
+  static constexpr int MISC_OFF = BAR_OFF + 8 * (11 + 4 * STAGES + 2 * PLAN_STAGES);
   static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL = 2 * BLOCK_N;        // S/P buffers, then O, then Q
@@ -100,7 +102,7 @@ struct GatherArgs {
 #define EV(e, T)
 #endif
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XCHG = 8, B_EPI = 16, B_KFULL = 17 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XFULL = 8, B_EPI = 10, B_KFULL = 11 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -126,7 +128,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  float* xchg = reinterpret_cast<float*>(smem + C::XCHG_OFF);
+  attn::TileNote* note = reinterpret_cast<attn::TileNote*>(smem + C::NOTE_OFF);
   Plan* plan = reinterpret_cast<Plan*>(smem + C::PLAN_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -140,10 +142,10 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
-    for (int i = 0; i < 8; ++i) mbar_init(bar(B_XCHG + i), 64);     // [tile parity][warp pair]
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_PFULL + b), 256);
+      mbar_init(bar(B_XFULL + b), 128);
+      mbar_init(bar(B_PFULL + b), 128);
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
@@ -154,7 +156,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 11);    // a K and a V gather warp, the UMMA thread, eight softmax warps
+      mbar_init(bar(B_PLANEMPTY + s), 7);     // a K and a V gather warp, the UMMA thread, four mask warps
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -285,9 +287,9 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     }
     const int fill = pos % BLOCK_N;
     if (ok && fill > 0) {
-      // the open tile: pad to whole 16-row groups with a valid row that no query attends to
-      const int padded = (fill + 15) & ~15;
-      for (int i = fill + lane; i < padded; i += 32) put(pos - fill + i, 0, 0u);
+      // the open tile: the rest of it is a valid row that no query attends to (the copies stop
+      // at the next 16-row group, the masks are cleared to the end of the tile)
+      for (int i = fill + lane; i < BLOCK_N; i += 32) put(pos - fill + i, 0, 0u);
       publish_to(pub + 1, fill);
     }
     if (a.attended) {
@@ -446,8 +448,8 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-3: columns [0, 32) of every tile, warps 4-7: columns [32, 64); thread = row
-    const int hf = warp >> 2;
+    // warps 0-3: mask stage, warps 4-7: exp stage; thread = row in both
+    const int stage = warp >> 2;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
@@ -456,77 +458,102 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t qbit = 1u << qslot;
     const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
-    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + stage * (D / 2) : nullptr, stage, lane_addr, tmem_base,
                                     bar(B_QFULL));
-    float m_ref = -INFINITY, l_part = 0.f, l_rnd = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
     int j = 0;
     TR_DECL
-    for (;; ++j) {
-      const int ps = j % PLAN_STAGES, b = j & 1;
-      TR(5)
-      ok = mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-      if (!ok) break;
-      TR(0)
-      const int cnt = plan->count[ps];
-      if (cnt == 0) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-        break;
-      }
-      const int np = (cnt + 15) >> 4;
-      const int my_pages = min(max(np - 2 * hf, 0), 2);
-      ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-      if (!ok) break;
-      TR(1)
-      if (threadIdx.x == 0) { EV(7, j) }
-      tc_fence_after();
-      uint32_t r[32];
-      if (my_pages > 0) {
-        tmem_ld32(tmem_base + lane_addr + b * BLOCK_N + hf * 32, r);
-        tmem_ld_wait();
-      }
-      tc_fence_before();
-#ifdef SEMBLO_SKIP_SOFTMAX
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-      mbar_arrive(bar(B_PFULL + b));
-      continue;
-#endif
-      // masked raw logits of this half (scaling is folded into the exponent)
-      float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
-      const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hf * 32);
+    if (stage == 0) {
+      for (;; ++j) {
+        const int ps = j % PLAN_STAGES, b = j & 1;
+        TR(5)
+        ok = mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        TR(0)
+        const int cnt = plan->count[ps];
+        if (cnt == 0) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
+          // end of the stream: the note slot is free once P V of tile j - 2 has been issued
+          if (j >= 2) ok = mbar_wait(bar(B_PVDONE + b), ((j - 2) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+          if (threadIdx.x == 0) note[b].pages = 0;
+          mbar_arrive(bar(B_XFULL + b));
+          break;
+        }
+        const int np = (cnt + 15) >> 4;
+        ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        TR(1)
+        if (threadIdx.x == 0) { EV(7, j) }
+        tc_fence_after();
+        // a key counts for this row only if the row's query selected the key's cluster
+        float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
 #pragma unroll
-      for (int g4 = 0; g4 < 8; ++g4) {
-        if (g4 * 4 < my_pages * 16) {
-          const uint4 m4 = mk[g4];
-          const uint32_t mm[4] = {m4.x, m4.y, m4.z, m4.w};
+        for (int hh = 0; hh < 2; ++hh) {
+          if (2 * hh < np) {
+            uint32_t r[32];
+            const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hh * 32;
+            tmem_ld32(addr, r);
+            const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hh * 32);
+            uint4 m4[8];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = g4 * 4 + e;
-            const bool allowed = (mm[e] & qbit) != 0u;
-            const float sraw = allowed ? __uint_as_float(r[col]) : -INFINITY;
-            r[col] = __float_as_uint(sraw);
-            tm[e] = fmaxf(tm[e], sraw);
+            for (int g4 = 0; g4 < 8; ++g4) m4[g4] = mk[g4];
+            tmem_ld_wait();
+            // (keys past the tile's last row carry an empty mask: the planner clears them)
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              const uint32_t mm[4] = {m4[g4].x, m4[g4].y, m4[g4].z, m4[g4].w};
+              float sv[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                sv[e] = (mm[e] & qbit) != 0u ? __uint_as_float(r[g4 * 4 + e]) : -INFINITY;
+                r[g4 * 4 + e] = __float_as_uint(sv[e]);
+              }
+              tm[g4 & 1] = fmax3(tm[g4 & 1], sv[0], sv[1]);
+              tm[2 + (g4 & 1)] = fmax3(tm[2 + (g4 & 1)], sv[2], sv[3]);
+            }
+            tmem_st32(addr, r);
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
+        note[b].row_max[row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+        if (threadIdx.x == 0) note[b].pages = np;
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar(B_XFULL + b));
+        if (threadIdx.x == 0) { EV(11, j) }
+        TR(2)
       }
-      const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-      TR(2)
-      ok = attn::softmax_half_tile<D, C::O_COL>(
-          r, tmax, my_pages, j, hf, row, lane_addr, tmem_base, b * BLOCK_N, xchg, bar(B_XCHG),
-          bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_part, l_rnd, abort_flag, a.status);
-      if (!ok) break;
-      if (threadIdx.x == 0) { EV(8, j) }
-      TR(4)
+    } else {
+      for (;; ++j) {
+        const int b = j & 1;
+        TR(5)
+        ok = mbar_wait(bar(B_XFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+        if (!ok) break;
+        TR(1)
+        const int np = note[b].pages;
+        if (np == 0) break;
+        tc_fence_after();
+        ok = attn::exp_tile<D, C::O_COL>(np, note[b].row_max[row], j, lane_addr, tmem_base, b * BLOCK_N,
+                                         bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_run,
+                                         abort_flag, a.status);
+        if (!ok) break;
+        if (lane == 0) { EV(warp == 4 ? 8 : 8 + warp - 1, j) }
+        TR(4)
+      }
     }
-    if (warp == 0) { TR_FLUSH(4) }
+#ifndef SEMBLO_TRACE_WARP
+#define SEMBLO_TRACE_WARP 0
+#endif
+    if (warp == SEMBLO_TRACE_WARP) { TR_FLUSH(4) }
+    if (warp == SEMBLO_TRACE_WARP + 4) { TR_FLUSH(5) }
+
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part, l_rnd,
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, stage, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_run,
                                      ok && qvalid, a.merge, a.out + hidx * D,
                                      a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);

@@ -84,15 +84,18 @@ __device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity,
   return ok != 0;
 }
 
-// Bounded wait.  `abort_flag` lives in shared memory, `status` in global memory.
+// Bounded wait.  `abort_flag` lives in shared memory, `status` in global memory.  Each try
+// may sleep in hardware for SLEEP_NS (it returns as soon as the phase completes), so a waiting
+// warp leaves the issue slots to the warps that have work.
+constexpr uint32_t SLEEP_NS = 20000;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = globaltimer();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xff) == 0) {
+    if (mbar_try_wait_for(bar, parity, SLEEP_NS)) return true;
+    if ((++spins & 0x7) == 0) {
       if (*abort_flag) return false;
       if (*reinterpret_cast<volatile int*>(status) != 0) {
         *abort_flag = 1;
@@ -247,6 +250,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// max(a, b, c) in one instruction.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
 // 2^x on the special-function unit (flushes denormals; -inf -> 0).
