@@ -41,7 +41,7 @@ import torch  # noqa: E402
 PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_log2=7, target=4096,
                sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
 DECODE = dict(length=524288, hq=16, hkv=4, dim=256, centres=512, unit=64, min_log2=7, target=4096,
-              sink=128, reserve=1024, steps=256, temperature=0.1, beta=0.25, splits=74)
+              sink=128, reserve=1024, steps=256, temperature=0.1, beta=0.25, splits=37)
 
 
 def peaks():
@@ -322,23 +322,28 @@ def decode_measure(device, pk):
     torch.cuda.synchronize()
     _lib.status_for(device).raise_if_set()
     graph_us = sorted(a.elapsed_time(b) * 1e3 for a, b in gev)
-    # attend kernel alone (stage mask 4) for its own roofline
-    aev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(64)]
-    for a, b in aev:
-        flush.zero_()
-        a.record()
-        fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t, k_post=None,
-                          v_states=None, k_pre=None, output=out, temperature=cfg["temperature"], beta=cfg["beta"],
-                          target_tokens=cfg["target"], sm_scale=sm_scale, num_splits=cfg["splits"], stage_mask=4)
-        b.record()
-    torch.cuda.synchronize()
-    attend_us = sorted(a.elapsed_time(b) * 1e3 for a, b in aev)
+    # each kernel alone (stage masks 1, 2, 4): the attend kernel has its own roofline
+    stage_us = {}
+    for name, mask in (("score", 1), ("select", 2), ("attend", 4)):
+        aev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(64)]
+        for a, b in aev:
+            flush.zero_()
+            a.record()
+            fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t, k_post=None,
+                              v_states=None, k_pre=None, output=out, temperature=cfg["temperature"],
+                              beta=cfg["beta"], target_tokens=cfg["target"], sm_scale=sm_scale,
+                              num_splits=cfg["splits"], stage_mask=mask)
+            b.record()
+        torch.cuda.synchronize()
+        stage_us[name] = sorted(a.elapsed_time(b) * 1e3 for a, b in aev)
+    attend_us = stage_us["attend"]
     med = lambda v: v[len(v) // 2]
     gathered = (n_rows + n_suffix) * dim * 2 * 2 + n_rows * 4
     codebook = hkv * clusters * dim * 2 + hkv * clusters * 8
     return {
         "metric": "decode_us_per_step", "context": L, "clusters": clusters, "steps": steps,
         "eager_us": med(eager_us), "graph_us": med(graph_us), "attend_kernel_us": med(attend_us),
+        "score_kernel_us": med(stage_us["score"]), "select_kernel_us": med(stage_us["select"]),
         "selected_rows": n_rows, "gathered_bytes": gathered, "codebook_bytes": codebook,
         "roofline_attend": {"bound": "hbm", "achieved": gathered / (med(attend_us) * 1e-6) / 1e9, "peak": pk["hbm"],
                             "unit": "GB/s", "frac": gathered / (med(attend_us) * 1e-6) / 1e9 / pk["hbm"],
@@ -457,6 +462,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--length", type=int, default=0, help="override the prompt length (profiling on a small case)")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the decode measurement and print its record (profiling the decode kernels)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -472,6 +479,9 @@ def main():
     from semblo_b200 import _lib
     _lib.lib()
     pk = peaks()
+    if args.decode_only:
+        print(json.dumps(decode_measure(device, pk)))
+        return
     cfg = dict(PREFILL)
     if args.length:
         cfg["length"] = args.length

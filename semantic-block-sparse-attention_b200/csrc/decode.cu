@@ -6,8 +6,9 @@
 // plain coalesced 16-byte loads spread over the whole GPU:
 //   decode_score_kernel   grid [Hkv, blocks]: suffix write (block 0,0), router, logits of a
 //                         slice of the codebook and the slice's (max, sum-exp) per head
-//   decode_select_kernel  grid [Hkv]: log-sum-exp, cluster probabilities, penalised score,
-//                         bisection, CSR (start, len, cum) and the flat list of selected rows
+//   decode_penalise_kernel grid [Hkv, C / 256]: log-sum-exp, cluster probabilities, penalised score
+//   decode_select_kernel  grid [Hkv]: bisection, CSR (start, len, cum) and the flat list of
+//                         selected rows
 //   decode_attend_kernel  grid [Hkv, splits]: each half-warp streams whole K/V rows
 //                         (16 lanes x 16 B = one 256-B request per row and tensor); the last
 //                         CTA of a head merges the splits and writes the output
@@ -81,14 +82,52 @@ __device__ __forceinline__ double warp_sumd(double v) {
 }
 
 // ------------------------------------------------------------------ score
-__global__ void __launch_bounds__(256)
+// Sum of G per-lane values over the LPR lanes that share a codebook row, as a reduce-scatter:
+// while more than one value is left, each exchange step halves the values a lane carries, so
+// G = 4 over 32 lanes costs 6 shuffles instead of 20.  On return v[0] of lane l is the total
+// of head head_of_lane(l).
+template <int G, int LPR>
+__device__ __forceinline__ void reduce_heads(float (&v)[G], int lane_in_row) {
+  int n = G;
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) {
+    if (n > 1) {
+      const bool upper = (lane_in_row & o) != 0;
+      const int hn = n / 2;
+#pragma unroll
+      for (int i = 0; i < G / 2; ++i) {
+        if (i < hn) {
+          const float send = upper ? v[i] : v[i + hn];          // the half this lane gives away
+          const float keep = upper ? v[i + hn] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+      }
+      n = hn;
+    } else {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+    }
+  }
+}
+// The head whose total reduce_heads leaves in a lane: one bit per halving step, highest first.
+template <int G, int LPR>
+__device__ __forceinline__ int head_of_lane(int lane_in_row) {
+  int t = 0, n = G;
+#pragma unroll
+  for (int o = LPR / 2; o > 0 && n > 1; o >>= 1) {
+    n /= 2;
+    if (lane_in_row & o) t += n;
+  }
+  return t;
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(256, 2)
 decode_score_kernel(const DecodeArgs a) {
-  extern __shared__ float smf[];
-  float* qv = smf;                                   // [G][D] routing vectors as fp32
-  float* red = smf + a.group * a.head_dim;           // [8 warps][G][2]
+  __shared__ float qv[G * D];                        // routing vectors as fp32
+  __shared__ float red[8][G][2];
   const int h = blockIdx.x, blk = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int D = a.head_dim, G = a.group, C = a.num_clusters;
+  const int C = a.num_clusters;
 
   if (h == 0 && blk == 0 && a.k_post != nullptr) {
     // the token's K/V (and pre-RoPE key) into the suffix store
@@ -111,108 +150,103 @@ decode_score_kernel(const DecodeArgs a) {
   // router: normalise in fp32, round to bf16, normalise again, round again
   for (int t = warp; t < G; t += 8) {
     const __nv_bfloat16* src = a.q_pre + (int64_t)(h * G + t) * D;
-    float v[8];
+    float v[D / 32];
     double ss = 0.0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int d = lane + 32 * i;
-      v[i] = d < D ? __bfloat162float(src[d]) : 0.f;
+    for (int i = 0; i < D / 32; ++i) {
+      v[i] = __bfloat162float(src[lane + 32 * i]);
       ss += (double)v[i] * v[i];
     }
     const float n1 = fmaxf((float)sqrt(warp_sumd(ss)), 1e-12f);
     double ss2 = 0.0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < D / 32; ++i) {
       v[i] = __bfloat162float(__float2bfloat16_rn(v[i] / n1));
       ss2 += (double)v[i] * v[i];
     }
     const float n2 = fmaxf((float)sqrt(warp_sumd(ss2)), 1e-12f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < D / 32; ++i) {
       const int d = lane + 32 * i;
-      if (d < D) {
-        const __nv_bfloat16 r = __float2bfloat16_rn(v[i] / n2);
-        qv[t * D + d] = __bfloat162float(r);
-        if (blk == 0) a.vectors[(int64_t)(h * G + t) * D + d] = r;
-      }
+      const __nv_bfloat16 r = __float2bfloat16_rn(v[i] / n2);
+      qv[t * D + d] = __bfloat162float(r);
+      if (blk == 0) a.vectors[(int64_t)(h * G + t) * D + d] = r;
     }
   }
   __syncthreads();
 
-  // logits of this block's centroid slice.  Lanes [0, hl) read half 0, [hl, 2 hl) half 1.
-  const int half = D / 2;
-  const int lanes_per_half = half / 8;               // 16-byte chunks per half
-  const int lanes_per_row = 2 * lanes_per_half;      // 32 (D = 256) or 16 (D = 128)
-  const int rows_per_warp = 32 / lanes_per_row;
-  const int sub = lane / lanes_per_row, l_in = lane % lanes_per_row;
-  const int f = l_in / lanes_per_half, chunk = l_in % lanes_per_half;
+  // logits of this block's centroid slice.  A row (both halves of the codebook) is read by LPR
+  // lanes, 16 bytes each: lanes [0, LPR/2) take half 0, the rest half 1.
+  constexpr int HALF = D / 2;
+  constexpr int LPR = D / 8;                          // 32 (D = 256) or 16 (D = 128)
+  constexpr int RPW = 32 / LPR;                       // rows per warp and step
+  const int sub = lane / LPR, l_in = lane % LPR;
+  const int f = l_in / (LPR / 2), chunk = l_in % (LPR / 2);
   const int per_block = (int)ceil_div(C, gridDim.y);
   const int c_lo = blk * per_block, c_hi = min(C, c_lo + per_block);
-  const int d0 = f * half + chunk * 8;
-  float qreg[MAX_G][8];
+  const int d0 = f * HALF + chunk * 8;
+  float qreg[G][8];
 #pragma unroll
-  for (int t = 0; t < MAX_G; ++t)
-    if (t < G)
+  for (int t = 0; t < G; ++t)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) qreg[t][e] = qv[t * D + d0 + e];
-  float m_run[MAX_G], l_run[MAX_G];
+    for (int e = 0; e < 8; ++e) qreg[t][e] = qv[t * D + d0 + e];
+  // after the reduction a lane keeps the logits of one head only
+  const int my_t = head_of_lane<G, LPR>(l_in);
+  const bool writer = (l_in & (LPR / G - 1)) == 0;    // one lane per (row, head)
+  float m_run = -INFINITY, l_run = 0.f;
+  float* logit_out = a.ws_logit + ((int64_t)h * G + my_t) * C;
+  const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * HALF + chunk * 8;
+  // four codebook rows per lane group are requested before the first is used
+  constexpr int SU = 4;
+  for (int cw = c_lo + warp * RPW; cw < c_hi; cw += 8 * RPW * SU) {
+    uint4 raw[SU];
 #pragma unroll
-  for (int t = 0; t < MAX_G; ++t) { m_run[t] = -INFINITY; l_run[t] = 0.f; }
-  const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * half + chunk * 8;
-  for (int cw = c_lo + warp * rows_per_warp; cw < c_hi; cw += 8 * rows_per_warp) {
-    const int c = cw + sub;
-    const bool live = c < c_hi;                       // the trip count is warp-uniform
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = *reinterpret_cast<const uint4*>(cb + (int64_t)c * half);
-    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float x[8];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f2 = __bfloat1622float2(p2[e]);
-      x[2 * e] = f2.x;
-      x[2 * e + 1] = f2.y;
+    for (int u = 0; u < SU; ++u) {
+      const int c = cw + u * 8 * RPW + sub;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (c < c_hi) raw[u] = __ldg(reinterpret_cast<const uint4*>(cb + (int64_t)c * HALF));
     }
 #pragma unroll
-    for (int t = 0; t < MAX_G; ++t) {
-      if (t < G) {
-        float dot = 0.f;
+    for (int u = 0; u < SU; ++u) {
+      const int c = cw + u * 8 * RPW + sub;
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+      float x[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qreg[t][e], x[e], dot);
-        for (int o = lanes_per_row >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (live) {
-          const float s2 = dot * a.scale_log2_router;
-          if (l_in == 0) a.ws_logit[((int64_t)h * G + t) * C + c] = s2;
-          const float mx = fmaxf(m_run[t], s2);
-          l_run[t] = l_run[t] * exp2f(m_run[t] - mx) + exp2f(s2 - mx);
-          m_run[t] = mx;
-        }
+      for (int e = 0; e < 4; ++e) {
+        const float2 f2 = __bfloat1622float2(p2[e]);
+        x[2 * e] = f2.x;
+        x[2 * e + 1] = f2.y;
+      }
+      float dot[G];
+#pragma unroll
+      for (int t = 0; t < G; ++t) {
+        dot[t] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dot[t] = fmaf(qreg[t][e], x[e], dot[t]);
+      }
+      reduce_heads<G, LPR>(dot, l_in);
+      if (c < c_hi) {
+        const float s2 = dot[0] * a.scale_log2_router;
+        if (writer) logit_out[c] = s2;
+        const float mx = fmaxf(m_run, s2);
+        l_run = l_run * sm100::fast_exp2(m_run - mx) + sm100::fast_exp2(s2 - mx);
+        m_run = mx;
       }
     }
   }
-  // combine the (max, sum) of the block: lanes with l_in == 0 of each sub-row hold them
-#pragma unroll
-  for (int t = 0; t < MAX_G; ++t) {
-    if (t < G) {
-      float m = m_run[t], l = l_run[t];
-      if (rows_per_warp == 2) {
-        const float m_o = __shfl_xor_sync(0xffffffffu, m, 16), l_o = __shfl_xor_sync(0xffffffffu, l, 16);
-        const float mx = fmaxf(m, m_o);
-        l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
-        m = mx;
-      }
-      if (lane == 0) { red[(warp * G + t) * 2] = m; red[(warp * G + t) * 2 + 1] = l; }
-    }
-  }
+  // combine the (max, sum) of the block: the writer lanes of every sub-row hold a head's pair
+  auto merge = [](float& m, float& l, float m_o, float l_o) {
+    const float mx = fmaxf(m, m_o);
+    l = (m == -INFINITY ? 0.f : l * sm100::fast_exp2(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * sm100::fast_exp2(m_o - mx));
+    m = mx;
+  };
+  if (RPW == 2) merge(m_run, l_run, __shfl_xor_sync(0xffffffffu, m_run, 16), __shfl_xor_sync(0xffffffffu, l_run, 16));
+  if (sub == 0 && writer) { red[warp][my_t][0] = m_run; red[warp][my_t][1] = l_run; }
   __syncthreads();
   if (threadIdx.x < G) {
     const int t = threadIdx.x;
     float m = -INFINITY, l = 0.f;
-    for (int w = 0; w < 8; ++w) {
-      const float m_o = red[(w * G + t) * 2], l_o = red[(w * G + t) * 2 + 1];
-      const float mx = fmaxf(m, m_o);
-      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
-      m = mx;
-    }
+    for (int w = 0; w < 8; ++w) merge(m, l, red[w][t][0], red[w][t][1]);
     float* dst = a.ws_ml + (((int64_t)h * gridDim.y + blk) * G + t) * 2;
     dst[0] = m;
     dst[1] = l;
@@ -220,88 +254,120 @@ decode_score_kernel(const DecodeArgs a) {
 }
 
 // ------------------------------------------------------------------ select
-template <typename T, typename Op>
-__device__ __forceinline__ T block_reduce(T v, Op op, T* scratch /* [33] */) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
-  __syncthreads();
-  if (lane == 0) scratch[warp] = v;
-  __syncthreads();
-  if (warp == 0) {
-    T w = lane < nw ? scratch[lane] : scratch[0];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) w = op(w, __shfl_xor_sync(0xffffffffu, w, o));
-    if (lane == 0) scratch[32] = w;
-  }
-  __syncthreads();
-  return scratch[32];
-}
-
 constexpr int SEL_THREADS = 1024;
 constexpr int SEL_MAX_PER = 16;        // clusters per thread: C <= 16384
+constexpr int SEL_CSR_SMEM = 2048;     // selected clusters whose (start, cum) are searched in shared memory
+constexpr int PEN_THREADS = 256;
 
-__global__ void __launch_bounds__(SEL_THREADS)
-decode_select_kernel(const DecodeArgs a) {
-  __shared__ float fscr[33];
+// Penalised score of every cluster: grid [Hkv, C / 256], one cluster per thread.  The head's
+// log-sum-exp is rebuilt from the score kernel's block partials by one warp per query head
+// (the partials of a head are read in parallel and merged with shuffles).
+__global__ void __launch_bounds__(PEN_THREADS)
+decode_penalise_kernel(const DecodeArgs a) {
   __shared__ float lse2[MAX_G];
-  __shared__ int scan_a[SEL_THREADS], scan_b[SEL_THREADS];
   const int h = blockIdx.x;
   const int C = a.num_clusters, G = a.group;
-  // per-head log-sum-exp from the block partials
-  if (threadIdx.x < G) {
-    const int t = threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < G) {
+    const int t = warp;
     float m = -INFINITY, l = 0.f;
-    for (int b = 0; b < a.score_blocks; ++b) {
-      const float* src = a.ws_ml + (((int64_t)h * a.score_blocks + b) * G + t) * 2;
-      const float m_o = src[0], l_o = src[1];
+    for (int b = lane; b < a.score_blocks; b += 32) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (((int64_t)h * a.score_blocks + b) * G + t) * 2));
+      const float mx = fmaxf(m, ml.x);
+      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (ml.x == -INFINITY ? 0.f : ml.y * exp2f(ml.x - mx));
+      m = mx;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m, o), l_o = __shfl_xor_sync(0xffffffffu, l, o);
       const float mx = fmaxf(m, m_o);
       l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
       m = mx;
     }
-    lse2[t] = m + log2f(l);
+    if (lane == 0) lse2[t] = m + log2f(l);
   }
   __syncthreads();
-  const int per = (C + SEL_THREADS - 1) / SEL_THREADS;        // consecutive clusters per thread
-  const int c0 = threadIdx.x * per;
-  float score[SEL_MAX_PER];
-  int real[SEL_MAX_PER];
-  const float budget = (float)max(a.target_tokens - a.sink_tokens, 0);
-  const bool has_sink = a.sink_tokens > 0;
-  auto seen_size = [&](int i) { return (has_sink && c0 + i == 0) ? 0.f : (float)real[i]; };
-  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  const int c = blockIdx.y * PEN_THREADS + threadIdx.x;
+  if (c >= C) return;
+  float lg[MAX_G];
 #pragma unroll
-  for (int i = 0; i < SEL_MAX_PER; ++i) {
-    const int c = c0 + i;
-    score[i] = NEG_BIG;
-    real[i] = 0;
-    if (i < per && c < C) {
-      float prob = 0.f;
-      for (int t = 0; t < G; ++t) prob += exp2f(a.ws_logit[((int64_t)h * G + t) * C + c] - lse2[t]);
-      real[i] = a.sizes[(int64_t)h * C + c];
-      const float n = seen_size(i);
-      float sc = log2f(fmaxf(prob, 1e-38f)) * LN2;
-      if (a.beta != 0.f) sc -= a.beta * logf(1.0f + n);
-      score[i] = n > 0.f ? sc : NEG_BIG;
-      a.ws_score[(int64_t)h * C + c] = score[i];
-      mx = fmaxf(mx, score[i]);
-      mn = fminf(mn, n > 0.f ? score[i] : 3.4e38f);
-      tot += n > 0.f ? n : 0.f;
+  for (int t = 0; t < MAX_G; ++t)
+    if (t < G) lg[t] = __ldcg(a.ws_logit + ((int64_t)h * G + t) * C + c);
+  const int size = __ldg(a.sizes + (int64_t)h * C + c);
+  float prob = 0.f;
+#pragma unroll
+  for (int t = 0; t < MAX_G; ++t)
+    if (t < G) prob += exp2f(lg[t] - lse2[t]);
+  const float n = (a.sink_tokens > 0 && c == 0) ? 0.f : (float)size;
+  float sc = log2f(fmaxf(prob, 1e-38f)) * LN2;
+  if (a.beta != 0.f) sc -= a.beta * logf(1.0f + n);
+  a.ws_score[(int64_t)h * C + c] = n > 0.f ? sc : NEG_BIG;
+}
+
+// Threshold bisection, selection, CSR in cluster order and the flat row list: grid [Hkv].
+// A thread owns PER consecutive clusters (PER * 1024 >= C, C a multiple of 4).
+template <int PER>
+__global__ void __launch_bounds__(SEL_THREADS)
+decode_select_kernel(const DecodeArgs a) {
+  __shared__ float fred[2][32];
+  __shared__ int isum[2][32];
+  __shared__ int wsum_a[32], wsum_b[32];
+  __shared__ int csr_start[SEL_CSR_SMEM], csr_cum[SEL_CSR_SMEM];
+  const int h = blockIdx.x;
+  const int C = a.num_clusters;
+  const int lane_s = threadIdx.x & 31, warp_s = threadIdx.x >> 5;
+  const int c0 = threadIdx.x * PER;
+  const bool has_sink = a.sink_tokens > 0;
+  float score[PER];
+  int real[PER], seen[PER];          // cluster size, and the size the budget sees (0 for the sink cluster)
+#pragma unroll
+  for (int i4 = 0; i4 < PER; i4 += 4) {
+    float4 sc = make_float4(NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG);
+    int4 sz = make_int4(0, 0, 0, 0);
+    if (c0 + i4 < C) {
+      sc = __ldcg(reinterpret_cast<const float4*>(a.ws_score + (int64_t)h * C + c0 + i4));
+      sz = __ldg(reinterpret_cast<const int4*>(a.sizes + (int64_t)h * C + c0 + i4));
     }
+    score[i4] = sc.x; score[i4 + 1] = sc.y; score[i4 + 2] = sc.z; score[i4 + 3] = sc.w;
+    real[i4] = sz.x; real[i4 + 1] = sz.y; real[i4 + 2] = sz.z; real[i4 + 3] = sz.w;
   }
-  auto fmax_op = [](float x, float y) { return fmaxf(x, y); };
-  auto fmin_op = [](float x, float y) { return fminf(x, y); };
-  auto fadd_op = [](float x, float y) { return x + y; };
-  float hi = block_reduce(mx, fmax_op, fscr) + 1e-6f;
-  float lo = block_reduce(mn, fmin_op, fscr) - 1e-6f;
-  lo = fminf(lo, hi - 1e-5f);
-  const bool all_fit = block_reduce(tot, fadd_op, fscr) < budget;
+  float mx = -INFINITY, mn = 3.4e38f;
+  int tot = 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    seen[i] = (has_sink && c0 + i == 0) ? 0 : real[i];
+    if (c0 + i < C) mx = fmaxf(mx, score[i]);
+    if (seen[i] > 0) { mn = fminf(mn, score[i]); tot += seen[i]; }
+  }
+  // block reductions with one barrier each: warp results go to one of two buffers (alternating,
+  // so a fast warp's next write cannot overtake a slow warp's read), then every warp folds the 32
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  tot = __reduce_add_sync(0xffffffffu, tot);
+  if (lane_s == 0) { fred[0][warp_s] = mx; fred[1][warp_s] = mn; isum[1][warp_s] = tot; }
+  __syncthreads();
+  mx = fred[0][lane_s]; mn = fred[1][lane_s];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+  }
+  const int budget = max(a.target_tokens - a.sink_tokens, 0);
+  const bool all_fit = __reduce_add_sync(0xffffffffu, isum[1][lane_s]) < budget;
+  float hi = mx + 1e-6f;
+  float lo = fminf(mn - 1e-6f, hi - 1e-5f);
   for (int it = 0; it < a.iters; ++it) {
     const float mid = (lo + hi) * 0.5f;
-    float above = 0.f;
+    int above = 0;
 #pragma unroll
-    for (int i = 0; i < SEL_MAX_PER; ++i) above += score[i] >= mid ? seen_size(i) : 0.f;
-    above = block_reduce(above, fadd_op, fscr);
+    for (int i = 0; i < PER; ++i) above += score[i] >= mid ? seen[i] : 0;
+    above = __reduce_add_sync(0xffffffffu, above);
+    if (lane_s == 0) isum[it & 1][warp_s] = above;
+    __syncthreads();
+    above = __reduce_add_sync(0xffffffffu, isum[it & 1][lane_s]);
     const bool reach = above >= budget;
     lo = reach ? mid : lo;
     hi = reach ? hi : mid;
@@ -311,38 +377,47 @@ decode_select_kernel(const DecodeArgs a) {
   int n_sel = 0, n_tok = 0;
   unsigned sel_bits = 0;
 #pragma unroll
-  for (int i = 0; i < SEL_MAX_PER; ++i) {
+  for (int i = 0; i < PER; ++i) {
     const int c = c0 + i;
     const bool is_sink = has_sink && c == 0;
-    const bool s = (i < per && c < C) &&
-                   ((seen_size(i) > 0.f && score[i] >= theta) || (is_sink && real[i] > 0));
+    const bool s = c < C && ((seen[i] > 0 && score[i] >= theta) || (is_sink && real[i] > 0));
     sel_bits |= s ? (1u << i) : 0u;
     n_sel += s;
     n_tok += s ? real[i] : 0;
   }
-  scan_a[threadIdx.x] = n_sel;
-  scan_b[threadIdx.x] = n_tok;
-  __syncthreads();
-  // Hillis-Steele inclusive scan
-  for (int off = 1; off < SEL_THREADS; off <<= 1) {
-    int va = 0, vb = 0;
-    if ((int)threadIdx.x >= off) { va = scan_a[threadIdx.x - off]; vb = scan_b[threadIdx.x - off]; }
-    __syncthreads();
-    scan_a[threadIdx.x] += va;
-    scan_b[threadIdx.x] += vb;
-    __syncthreads();
+  // block-wide exclusive scan of (clusters, tokens): warp scans, then a scan of the warp totals
+  int inc_a = n_sel, inc_b = n_tok;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int va = __shfl_up_sync(0xffffffffu, inc_a, o), vb = __shfl_up_sync(0xffffffffu, inc_b, o);
+    if (lane_s >= o) { inc_a += va; inc_b += vb; }
   }
-  int pos = scan_a[threadIdx.x] - n_sel, cum = scan_b[threadIdx.x] - n_tok;
-  const int total_sel = scan_a[SEL_THREADS - 1], total_tok = scan_b[SEL_THREADS - 1];
+  if (lane_s == 31) { wsum_a[warp_s] = inc_a; wsum_b[warp_s] = inc_b; }
+  __syncthreads();
+  int wa = wsum_a[lane_s], wb = wsum_b[lane_s];      // 32 warps exactly
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int va = __shfl_up_sync(0xffffffffu, wa, o), vb = __shfl_up_sync(0xffffffffu, wb, o);
+    if (lane_s >= o) { wa += va; wb += vb; }
+  }
+  const int total_sel = __shfl_sync(0xffffffffu, wa, 31), total_tok = __shfl_sync(0xffffffffu, wb, 31);
+  const int base_a = __shfl_sync(0xffffffffu, wa, warp_s) - wsum_a[warp_s];
+  const int base_b = __shfl_sync(0xffffffffu, wb, warp_s) - wsum_b[warp_s];
+  int pos = base_a + inc_a - n_sel, cum = base_b + inc_b - n_tok;
   int32_t* rs = a.rstart + (int64_t)h * C;
   int32_t* rl = a.rlen + (int64_t)h * C;
   int32_t* rc = a.rcum + (int64_t)h * C;
+  int starts[PER];
 #pragma unroll
-  for (int i = 0; i < SEL_MAX_PER; ++i) {
+  for (int i = 0; i < PER; ++i)
+    starts[i] = ((sel_bits >> i) & 1) ? __ldg(a.indptr + (int64_t)h * (C + 1) + c0 + i) : 0;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
     if ((sel_bits >> i) & 1) {
-      rs[pos] = a.indptr[(int64_t)h * (C + 1) + c0 + i];
+      rs[pos] = starts[i];
       rl[pos] = real[i];
       rc[pos] = cum;
+      if (pos < SEL_CSR_SMEM) { csr_start[pos] = starts[i]; csr_cum[pos] = cum; }
       ++pos;
       cum += real[i];
     }
@@ -354,18 +429,28 @@ decode_select_kernel(const DecodeArgs a) {
   }
   __threadfence_block();
   __syncthreads();
-  // flat list of selected packed rows: slot -> cluster by binary search over rcum
+  // flat list of selected packed rows: slot -> cluster by binary search over the cumulative sizes
   const int limit = min(total_tok, (int)a.packed_width);
   int32_t* rows = a.rows + (int64_t)h * a.packed_width;
-  for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
-    int lo_r = 0, hi_r = total_sel;                 // last r with rcum[r] <= o
-    while (hi_r - lo_r > 1) {
-      const int mid = (lo_r + hi_r) >> 1;
-      if (rc[mid] <= o) lo_r = mid; else hi_r = mid;
+  if (total_sel <= SEL_CSR_SMEM) {
+    for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
+      int lo_r = 0, hi_r = total_sel;                 // last r with cum[r] <= o
+      while (hi_r - lo_r > 1) {
+        const int mid = (lo_r + hi_r) >> 1;
+        if (csr_cum[mid] <= o) lo_r = mid; else hi_r = mid;
+      }
+      rows[o] = csr_start[lo_r] + (o - csr_cum[lo_r]);
     }
-    rows[o] = rs[lo_r] + (o - rc[lo_r]);
+  } else {
+    for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
+      int lo_r = 0, hi_r = total_sel;
+      while (hi_r - lo_r > 1) {
+        const int mid = (lo_r + hi_r) >> 1;
+        if (rc[mid] <= o) lo_r = mid; else hi_r = mid;
+      }
+      rows[o] = rs[lo_r] + (o - rc[lo_r]);
+    }
   }
-
 }
 
 // ------------------------------------------------------------------ attend + merge
@@ -416,81 +501,105 @@ decode_attend_kernel(const DecodeArgs a) {
   const int64_t pk_plane = a.packed_width * (int64_t)a.num_kv_heads * D;
   const int64_t sf_plane = (int64_t)a.suffix_blocks * a.suffix_block * a.num_kv_heads * D;
 
-  for (int base = lo + warp * 2; base < hi; base += 16) {
-    const int o = base + hw;
-    const bool live = o < hi;
-    const __nv_bfloat16* kp = a.packed_kv;
-    int64_t voff = pk_plane;
-    bool keep = false;
-    if (live) {
-      if (o < n_prompt) {
-        const int r = rows[o];
-        kp = a.packed_kv + ((int64_t)r * a.num_kv_heads + h) * D;
-        keep = posting[r] <= q_pos;
-      } else {
-        const long long pos = (long long)plen + (o - n_prompt);
-        const long long block = pos / a.suffix_block;
-        const long long phys = block < a.table_len ? a.suffix_table[block] : 0;
+  // Each half-warp takes U rows per step.  The row indices of the next step, then all K / V
+  // rows of this step, are in flight before any arithmetic, so a half-warp keeps U kilobyte-
+  // sized requests outstanding instead of one.
+  constexpr int U = 4;
+  auto row_source = [&](int o, const __nv_bfloat16*& kp, int64_t& voff, int& post_row, bool& in_range) {
+    // o: slot in [lo, hi); prompt slots come from the selected-row list, the rest from the suffix store
+    kp = a.packed_kv;
+    voff = pk_plane;
+    post_row = -1;
+    in_range = false;
+    if (o >= hi) return;
+    if (o < n_prompt) {
+      const int r = rows[o];
+      kp = a.packed_kv + ((int64_t)r * a.num_kv_heads + h) * D;
+      post_row = r;
+      in_range = true;
+    } else {
+      const long long pos = (long long)plen + (o - n_prompt);
+      const long long block = pos / a.suffix_block;
+      if (pos <= q_pos && block < a.table_len) {
+        const long long phys = a.suffix_table[block];
         kp = a.suffix_kv + (((phys * a.suffix_block + (pos - block * a.suffix_block)) * a.num_kv_heads) + h) * D;
         voff = sf_plane;
-        keep = pos <= q_pos && block < a.table_len;
+        in_range = true;
       }
     }
-    uint4 kraw[CH], vraw[CH];
+  };
+  for (int base = lo + warp * 2; base < hi; base += 16 * U) {
+    const __nv_bfloat16* kp[U];
+    int64_t voff[U];
+    int post_row[U];
+    bool keep[U];
 #pragma unroll
-    for (int ch = 0; ch < CH; ++ch) {
-      kraw[ch] = make_uint4(0, 0, 0, 0);
-      vraw[ch] = make_uint4(0, 0, 0, 0);
-      if (keep) {
-        kraw[ch] = *reinterpret_cast<const uint4*>(kp + ch * 128 + l16 * 8);
-        vraw[ch] = *reinterpret_cast<const uint4*>(kp + voff + ch * 128 + l16 * 8);
-      }
-    }
-    float s2[G];
+    for (int u = 0; u < U; ++u) row_source(base + 16 * u + hw, kp[u], voff[u], post_row[u], keep[u]);
+    uint4 kraw[U][CH], vraw[U][CH];
+    int post[U];
 #pragma unroll
-    for (int t = 0; t < G; ++t) s2[t] = 0.f;
-#pragma unroll
-    for (int ch = 0; ch < CH; ++ch) {
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[ch]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f2 = __bfloat1622float2(p2[e]);
-#pragma unroll
-        for (int t = 0; t < G; ++t) {
-          s2[t] = fmaf(q[t][ch * 8 + 2 * e], f2.x, s2[t]);
-          s2[t] = fmaf(q[t][ch * 8 + 2 * e + 1], f2.y, s2[t]);
-        }
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < G; ++t) {
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) s2[t] += __shfl_xor_sync(0xffffffffu, s2[t], off);
-    }
-    if (keep) {
-      float p[G];
-#pragma unroll
-      for (int t = 0; t < G; ++t) {
-        const float mx = fmaxf(m_run[t], s2[t]);
-        const float alpha = exp2f(m_run[t] - mx);       // 0 on the first row (m_run = -inf)
-        p[t] = exp2f(s2[t] - mx);
-        l_run[t] = l_run[t] * alpha + p[t];
-        m_run[t] = mx;
-        if (alpha != 1.f) {
-#pragma unroll
-          for (int d = 0; d < DPL; ++d) acc[t][d] *= alpha;
-        }
-      }
+    for (int u = 0; u < U; ++u) {
+      post[u] = INT_MIN;
+      if (keep[u] && post_row[u] >= 0) post[u] = __ldg(posting + post_row[u]);
 #pragma unroll
       for (int ch = 0; ch < CH; ++ch) {
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[ch]);
+        kraw[u][ch] = make_uint4(0, 0, 0, 0);
+        vraw[u][ch] = make_uint4(0, 0, 0, 0);
+        if (keep[u]) {
+          kraw[u][ch] = __ldg(reinterpret_cast<const uint4*>(kp[u] + ch * 128 + l16 * 8));
+          vraw[u][ch] = __ldg(reinterpret_cast<const uint4*>(kp[u] + voff[u] + ch * 128 + l16 * 8));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float s2[G];
+#pragma unroll
+      for (int t = 0; t < G; ++t) s2[t] = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < CH; ++ch) {
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[u][ch]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f2 = __bfloat1622float2(p2[e]);
 #pragma unroll
           for (int t = 0; t < G; ++t) {
-            acc[t][ch * 8 + 2 * e] = fmaf(p[t], f2.x, acc[t][ch * 8 + 2 * e]);
-            acc[t][ch * 8 + 2 * e + 1] = fmaf(p[t], f2.y, acc[t][ch * 8 + 2 * e + 1]);
+            s2[t] = fmaf(q[t][ch * 8 + 2 * e], f2.x, s2[t]);
+            s2[t] = fmaf(q[t][ch * 8 + 2 * e + 1], f2.y, s2[t]);
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < G; ++t) {
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) s2[t] += __shfl_xor_sync(0xffffffffu, s2[t], off);
+      }
+      // a prompt row counts only if its token is at or before the query's position
+      if (keep[u] && (long long)post[u] <= q_pos) {
+        float p[G];
+#pragma unroll
+        for (int t = 0; t < G; ++t) {
+          const float mx = fmaxf(m_run[t], s2[t]);
+          const float alpha = exp2f(m_run[t] - mx);       // 0 on the first row (m_run = -inf)
+          p[t] = exp2f(s2[t] - mx);
+          l_run[t] = l_run[t] * alpha + p[t];
+          m_run[t] = mx;
+          if (alpha != 1.f) {
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[t][d] *= alpha;
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[u][ch]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f2 = __bfloat1622float2(p2[e]);
+#pragma unroll
+            for (int t = 0; t < G; ++t) {
+              acc[t][ch * 8 + 2 * e] = fmaf(p[t], f2.x, acc[t][ch * 8 + 2 * e]);
+              acc[t][ch * 8 + 2 * e + 1] = fmaf(p[t], f2.y, acc[t][ch * 8 + 2 * e + 1]);
+            }
           }
         }
       }
@@ -550,19 +659,46 @@ decode_attend_kernel(const DecodeArgs a) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int t = idx / D, d = idx % D;
+  // Final merge by the head's last CTA.  The split weights are computed once into shared
+  // memory; then every thread owns four consecutive output columns and reads one float4 per
+  // split, all independent, so the loads overlap instead of queueing behind one another.
+  float* s_w = &s_acc[0][0][0];                       // [G][nsplit] weights, then [G] denominators
+  for (int t = warp; t < G; t += 8) {
     const float* ml = a.pml + (int64_t)(h * G + t) * nsplit * 2;
     float mx = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, __ldcg(ml + 2 * s));
-    float num = 0.f, den = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
+    for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, __ldcg(ml + 2 * s));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float den = 0.f;
+    for (int s = lane; s < nsplit; s += 32) {
       const float m_s = __ldcg(ml + 2 * s);
       const float sc = m_s == -INFINITY ? 0.f : exp2f(m_s - mx);
-      num += __ldcg(a.pacc + ((int64_t)(h * G + t) * nsplit + s) * D + d) * sc;
+      s_w[t * nsplit + s] = sc;
       den += __ldcg(ml + 2 * s + 1) * sc;
     }
-    a.out[(int64_t)(h * G + t) * D + d] = __float2bfloat16_rn(den == 0.f ? 0.f : num / den);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+    if (lane == 0) s_w[G * nsplit + t] = den;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D / 4; idx += blockDim.x) {
+    const int t = idx / (D / 4), d = (idx % (D / 4)) * 4;
+    const float4* src = reinterpret_cast<const float4*>(a.pacc + (int64_t)(h * G + t) * nsplit * D + d);
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s = 0; s < nsplit; ++s) {
+      const float4 v = __ldcg(src + (int64_t)s * (D / 4));
+      const float sc = s_w[t * nsplit + s];
+      num.x += v.x * sc; num.y += v.y * sc; num.z += v.z * sc; num.w += v.w * sc;
+    }
+    const float den = s_w[G * nsplit + t];
+    const float inv = den == 0.f ? 0.f : 1.f / den;
+    __nv_bfloat162 o01 = __floats2bfloat162_rn(num.x * inv, num.y * inv);
+    __nv_bfloat162 o23 = __floats2bfloat162_rn(num.z * inv, num.w * inv);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&o01);
+    packed.y = *reinterpret_cast<uint32_t*>(&o23);
+    *reinterpret_cast<uint2*>(a.out + (int64_t)(h * G + t) * D + d) = packed;
   }
 }
 
@@ -668,10 +804,18 @@ extern "C" int semblo_decode_step(
   a.out = (__nv_bfloat16*)output; a.status = status;
   cudaStream_t st = (cudaStream_t)stream;
   if (stage_mask & 1) {
-    const size_t smem = (size_t)(g * head_dim + 8 * g * 2) * sizeof(float);
-    decode_score_kernel<<<dim3(num_kv_heads, sblocks), 256, smem, st>>>(a);
+    const dim3 sgrid(num_kv_heads, sblocks);
+    if (head_dim == 256 && g == 4) decode_score_kernel<256, 4><<<sgrid, 256, 0, st>>>(a);
+    else if (head_dim == 128 && g == 4) decode_score_kernel<128, 4><<<sgrid, 256, 0, st>>>(a);
+    else if (head_dim == 128 && g == 8) decode_score_kernel<128, 8><<<sgrid, 256, 0, st>>>(a);
+    else return semblo::fail(semblo::SEMBLO_EINVAL, "decode scoring supports head_dim 256 with 4, or 128 with 4 or 8, query heads per KV head (got %d, %d)", head_dim, g);
   }
-  if (stage_mask & 2) decode_select_kernel<<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+  if (stage_mask & 2) {
+    decode_penalise_kernel<<<dim3(num_kv_heads, (unsigned)ceil_div(num_clusters, PEN_THREADS)), PEN_THREADS, 0, st>>>(a);
+    if (num_clusters <= SEL_THREADS * 4) decode_select_kernel<4><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+    else if (num_clusters <= SEL_THREADS * 8) decode_select_kernel<8><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+    else decode_select_kernel<16><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+  }
   if (stage_mask & 4) {
     dim3 grid(num_kv_heads, num_splits);
 #define SEMBLO_DECODE_CASE(DD, GG) \
