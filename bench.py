@@ -238,7 +238,7 @@ def kernel_launches(calls: dict, clusters: int) -> int:
                 "semblo_cluster_counts": 2, "semblo_kmeans_update": 3 * passes + 1, "semblo_split_descriptor": 1,
                 "semblo_build_layout": 2 + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
                 "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_window_prefill": 1, "semblo_sparse_prefill_gather": 1, "semblo_argsort_keys": 3 * passes,
-                "semblo_decode_step": 3}
+                "semblo_decode_step": 4}
     return sum(per_call.get(k, 0) * v for k, v in calls.items())
 
 
@@ -456,7 +456,7 @@ def workload_config(world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-decode", action="store_true")
@@ -511,11 +511,15 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
+    marks = [e0]
     for _ in range(args.steps):
         index = step.run(x, out)
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[-1].record()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
+    step_ms = [round(marks[i].elapsed_time(marks[i + 1]), 2) for i in range(args.steps)]
     clocks = sampler.stop()
     _lib.status_for(device).raise_if_set()
     calls = dict(_lib.CALLS)
@@ -575,7 +579,8 @@ def main():
     tokens = cfg["length"] * world
     line = {
         "metric": "sparse_prefill_tok_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "step_ms": step_ms,
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,

@@ -147,6 +147,29 @@ decode_score_kernel(const DecodeArgs a) {
       atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
     }
   }
+  // A row (both halves of the codebook) is read by LPR lanes, 16 bytes each: lanes [0, LPR/2)
+  // take half 0, the rest half 1.  The first SU rows of every lane group are requested before
+  // anything else, so the codebook is on its way while the router runs.
+  constexpr int HALF = D / 2;
+  constexpr int LPR = D / 8;                          // 32 (D = 256) or 16 (D = 128)
+  constexpr int RPW = 32 / LPR;                       // rows per warp and step
+  constexpr int SU = 16;
+  const int sub = lane / LPR, l_in = lane % LPR;
+  const int f = l_in / (LPR / 2), chunk = l_in % (LPR / 2);
+  const int per_block = (int)ceil_div(C, gridDim.y);
+  const int c_lo = blk * per_block, c_hi = min(C, c_lo + per_block);
+  const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * HALF + chunk * 8;
+  uint4 raw[SU];
+  auto fetch = [&](int cw) {
+#pragma unroll
+    for (int u = 0; u < SU; ++u) {
+      const int c = cw + u * 8 * RPW + sub;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (c < c_hi) raw[u] = __ldg(reinterpret_cast<const uint4*>(cb + (int64_t)c * HALF));
+    }
+  };
+  fetch(c_lo + warp * RPW);
+
   // router: normalise in fp32, round to bf16, normalise again, round again
   for (int t = warp; t < G; t += 8) {
     const __nv_bfloat16* src = a.q_pre + (int64_t)(h * G + t) * D;
@@ -175,15 +198,6 @@ decode_score_kernel(const DecodeArgs a) {
   }
   __syncthreads();
 
-  // logits of this block's centroid slice.  A row (both halves of the codebook) is read by LPR
-  // lanes, 16 bytes each: lanes [0, LPR/2) take half 0, the rest half 1.
-  constexpr int HALF = D / 2;
-  constexpr int LPR = D / 8;                          // 32 (D = 256) or 16 (D = 128)
-  constexpr int RPW = 32 / LPR;                       // rows per warp and step
-  const int sub = lane / LPR, l_in = lane % LPR;
-  const int f = l_in / (LPR / 2), chunk = l_in % (LPR / 2);
-  const int per_block = (int)ceil_div(C, gridDim.y);
-  const int c_lo = blk * per_block, c_hi = min(C, c_lo + per_block);
   const int d0 = f * HALF + chunk * 8;
   float qreg[G][8];
 #pragma unroll
@@ -195,20 +209,12 @@ decode_score_kernel(const DecodeArgs a) {
   const bool writer = (l_in & (LPR / G - 1)) == 0;    // one lane per (row, head)
   float m_run = -INFINITY, l_run = 0.f;
   float* logit_out = a.ws_logit + ((int64_t)h * G + my_t) * C;
-  const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * HALF + chunk * 8;
-  // four codebook rows per lane group are requested before the first is used
-  constexpr int SU = 4;
   for (int cw = c_lo + warp * RPW; cw < c_hi; cw += 8 * RPW * SU) {
-    uint4 raw[SU];
+    if (cw != c_lo + warp * RPW) fetch(cw);
 #pragma unroll
     for (int u = 0; u < SU; ++u) {
       const int c = cw + u * 8 * RPW + sub;
-      raw[u] = make_uint4(0, 0, 0, 0);
-      if (c < c_hi) raw[u] = __ldg(reinterpret_cast<const uint4*>(cb + (int64_t)c * HALF));
-    }
-#pragma unroll
-    for (int u = 0; u < SU; ++u) {
-      const int c = cw + u * 8 * RPW + sub;
+      if (cw + u * 8 * RPW >= c_hi) break;           // warp-uniform
       const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
       float x[8];
 #pragma unroll
@@ -305,10 +311,12 @@ decode_penalise_kernel(const DecodeArgs a) {
 }
 
 // Threshold bisection, selection, CSR in cluster order and the flat row list: grid [Hkv].
-// A thread owns PER consecutive clusters (PER * 1024 >= C, C a multiple of 4).
-template <int PER>
-__global__ void __launch_bounds__(SEL_THREADS)
+// A thread owns PER consecutive clusters (PER * T >= C, C a multiple of 4).  Few threads with
+// many clusters each: the per-warp cost of the 16 block-wide sums dominates otherwise.
+template <int PER, int T>
+__global__ void __launch_bounds__(T)
 decode_select_kernel(const DecodeArgs a) {
+  constexpr int NW = T / 32;
   __shared__ float fred[2][32];
   __shared__ int isum[2][32];
   __shared__ int wsum_a[32], wsum_b[32];
@@ -349,14 +357,15 @@ decode_select_kernel(const DecodeArgs a) {
   tot = __reduce_add_sync(0xffffffffu, tot);
   if (lane_s == 0) { fred[0][warp_s] = mx; fred[1][warp_s] = mn; isum[1][warp_s] = tot; }
   __syncthreads();
-  mx = fred[0][lane_s]; mn = fred[1][lane_s];
+  mx = lane_s < NW ? fred[0][lane_s] : -INFINITY;
+  mn = lane_s < NW ? fred[1][lane_s] : 3.4e38f;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
   }
   const int budget = max(a.target_tokens - a.sink_tokens, 0);
-  const bool all_fit = __reduce_add_sync(0xffffffffu, isum[1][lane_s]) < budget;
+  const bool all_fit = __reduce_add_sync(0xffffffffu, lane_s < NW ? isum[1][lane_s] : 0) < budget;
   float hi = mx + 1e-6f;
   float lo = fminf(mn - 1e-6f, hi - 1e-5f);
   for (int it = 0; it < a.iters; ++it) {
@@ -367,7 +376,7 @@ decode_select_kernel(const DecodeArgs a) {
     above = __reduce_add_sync(0xffffffffu, above);
     if (lane_s == 0) isum[it & 1][warp_s] = above;
     __syncthreads();
-    above = __reduce_add_sync(0xffffffffu, isum[it & 1][lane_s]);
+    above = __reduce_add_sync(0xffffffffu, lane_s < NW ? isum[it & 1][lane_s] : 0);
     const bool reach = above >= budget;
     lo = reach ? mid : lo;
     hi = reach ? hi : mid;
@@ -394,13 +403,13 @@ decode_select_kernel(const DecodeArgs a) {
   }
   if (lane_s == 31) { wsum_a[warp_s] = inc_a; wsum_b[warp_s] = inc_b; }
   __syncthreads();
-  int wa = wsum_a[lane_s], wb = wsum_b[lane_s];      // 32 warps exactly
+  int wa = lane_s < NW ? wsum_a[lane_s] : 0, wb = lane_s < NW ? wsum_b[lane_s] : 0;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int va = __shfl_up_sync(0xffffffffu, wa, o), vb = __shfl_up_sync(0xffffffffu, wb, o);
     if (lane_s >= o) { wa += va; wb += vb; }
   }
-  const int total_sel = __shfl_sync(0xffffffffu, wa, 31), total_tok = __shfl_sync(0xffffffffu, wb, 31);
+  const int total_sel = __shfl_sync(0xffffffffu, wa, NW - 1), total_tok = __shfl_sync(0xffffffffu, wb, NW - 1);
   const int base_a = __shfl_sync(0xffffffffu, wa, warp_s) - wsum_a[warp_s];
   const int base_b = __shfl_sync(0xffffffffu, wb, warp_s) - wsum_b[warp_s];
   int pos = base_a + inc_a - n_sel, cum = base_b + inc_b - n_tok;
@@ -433,7 +442,7 @@ decode_select_kernel(const DecodeArgs a) {
   const int limit = min(total_tok, (int)a.packed_width);
   int32_t* rows = a.rows + (int64_t)h * a.packed_width;
   if (total_sel <= SEL_CSR_SMEM) {
-    for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
+    for (int o = threadIdx.x; o < limit; o += T) {
       int lo_r = 0, hi_r = total_sel;                 // last r with cum[r] <= o
       while (hi_r - lo_r > 1) {
         const int mid = (lo_r + hi_r) >> 1;
@@ -442,7 +451,7 @@ decode_select_kernel(const DecodeArgs a) {
       rows[o] = csr_start[lo_r] + (o - csr_cum[lo_r]);
     }
   } else {
-    for (int o = threadIdx.x; o < limit; o += SEL_THREADS) {
+    for (int o = threadIdx.x; o < limit; o += T) {
       int lo_r = 0, hi_r = total_sel;
       while (hi_r - lo_r > 1) {
         const int mid = (lo_r + hi_r) >> 1;
@@ -685,11 +694,17 @@ decode_attend_kernel(const DecodeArgs a) {
     const int t = idx / (D / 4), d = (idx % (D / 4)) * 4;
     const float4* src = reinterpret_cast<const float4*>(a.pacc + (int64_t)(h * G + t) * nsplit * D + d);
     float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) {
-      const float4 v = __ldcg(src + (int64_t)s * (D / 4));
-      const float sc = s_w[t * nsplit + s];
-      num.x += v.x * sc; num.y += v.y * sc; num.z += v.z * sc; num.w += v.w * sc;
+    constexpr int MB = 16;                              // splits whose partials are in flight together
+    for (int s0 = 0; s0 < nsplit; s0 += MB) {
+      float4 v[MB];
+#pragma unroll
+      for (int i = 0; i < MB; ++i)
+        v[i] = s0 + i < nsplit ? __ldcg(src + (int64_t)(s0 + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const float sc = s0 + i < nsplit ? s_w[t * nsplit + s0 + i] : 0.f;
+        num.x += v[i].x * sc; num.y += v[i].y * sc; num.z += v[i].z * sc; num.w += v[i].w * sc;
+      }
     }
     const float den = s_w[G * nsplit + t];
     const float inv = den == 0.f ? 0.f : 1.f / den;
@@ -812,9 +827,9 @@ extern "C" int semblo_decode_step(
   }
   if (stage_mask & 2) {
     decode_penalise_kernel<<<dim3(num_kv_heads, (unsigned)ceil_div(num_clusters, PEN_THREADS)), PEN_THREADS, 0, st>>>(a);
-    if (num_clusters <= SEL_THREADS * 4) decode_select_kernel<4><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
-    else if (num_clusters <= SEL_THREADS * 8) decode_select_kernel<8><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
-    else decode_select_kernel<16><<<num_kv_heads, SEL_THREADS, 0, st>>>(a);
+    if (num_clusters <= 2048) decode_select_kernel<4, 512><<<num_kv_heads, 512, 0, st>>>(a);
+    else if (num_clusters <= 8192) decode_select_kernel<16, 512><<<num_kv_heads, 512, 0, st>>>(a);
+    else decode_select_kernel<16, 1024><<<num_kv_heads, 1024, 0, st>>>(a);
   }
   if (stage_mask & 4) {
     dim3 grid(num_kv_heads, num_splits);
