@@ -155,12 +155,14 @@ class PrefillStep:
                                   sm_scale=sm_scale, out=out[cs:ce + 1], attended=self.attended,
                                   _timer=self._timer if self.time_attention else None)
             if self.world > 1:
-                import torch.distributed as dist
+                # the one collective of the path: per-head outputs of the chunk to every rank
                 if self.gathered is None:
-                    self.gathered = torch.empty(self.world, chunk, hq, dim, dtype=torch.bfloat16, device=dev)
+                    from semblo_b200.head_parallel import HeadGather
+                    self.gathered = HeadGather()
+                    self.full_out = torch.empty(chunk, hq * self.world, dim, dtype=torch.bfloat16, device=dev)
                 if n != chunk:
                     raise RuntimeError("the prompt length must be a multiple of the query chunk")
-                dist.all_gather_into_tensor(self.gathered, out[cs:ce + 1])
+                self.gathered(out[cs:ce + 1], self.full_out)
         return index
 
     def _timer(self, phase):
