@@ -22,6 +22,7 @@ reference path (torch on the host cores) on a bounded sample of the same workloa
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -511,6 +512,8 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gc.collect()
+    gc.disable()                     # no collector pause inside the timed region
     barrier()
     e0.record()
     marks = [e0]
@@ -520,6 +523,7 @@ def main():
         marks[-1].record()
     e1.record()
     barrier()
+    gc.enable()
     ms = e0.elapsed_time(e1) / args.steps
     step_ms = [round(marks[i].elapsed_time(marks[i + 1]), 2) for i in range(args.steps)]
     clocks = sampler.stop()
@@ -604,7 +608,12 @@ def main():
     if world == 1 and not args.no_cpu:
         v, text = cpu_reference_sample(PREFILL, os.cpu_count() or 1)
         line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port", "sample": text}
-    print(json.dumps(line))
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
