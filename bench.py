@@ -41,6 +41,10 @@ import torch  # noqa: E402
 
 PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_log2=7, target=4096,
                sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of sparse_gather_prefill_kernel on the 131072-token
+# step, from a one-pass ncu capture of this file's own command (summary: profiles/prefill_128k_dram_traffic.md)
+GATHER_DRAM_BYTES_PER_LAUNCH = 1.307e9
+
 DECODE = dict(length=524288, hq=16, hkv=4, dim=256, centres=512, unit=64, min_log2=7, target=4096,
               sink=128, reserve=1024, steps=256, temperature=0.1, beta=0.25, splits=37)
 
@@ -593,7 +597,7 @@ def main():
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "roofline": {"bound": "tensor", "kernel": "window_prefill_kernel<256,4> + sparse_gather_prefill_kernel<256,4>", "achieved": flops / (attn_ms * 1e-3) / 1e12,
                      "peak": pk["tensor"], "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"],
-                     "traffic": None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
+                     "traffic": GATHER_DRAM_BYTES_PER_LAUNCH if not args.length else None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
                      "kernel_ms_per_step": attn_ms, "dense_prefix_ms": dense_ms, "window_ms": window_ms,
                      "gather_ms": gather_ms, "attended_keys_per_step": attended, "gathered_rows_per_step": gathered_rows,
                      "flops_per_step": flops},
