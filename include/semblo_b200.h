@@ -124,6 +124,60 @@ int semblo_select_clusters(const float* score, const int32_t* select_sizes, int 
 int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, int max_key, int32_t* order,
                         void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- keys that arrive after the index was fitted: token-order streamed prefill and suffix flush ---- */
+
+/* _nearest_cluster (semblo/vllm_plugin/suffix_flush.py:154-169, used by
+ * token_outer_prefill.py:343-347): for every key of keys [n, Hkv, D] (bf16, unit-normalised
+ * routing keys) the cluster whose unit descriptor has the largest fp32 cosine, lowest id on
+ * ties; descriptors that are all zero (the sink cluster) are never chosen.  codebooks
+ * [Hkv, 2, C, D/2] bf16; ids [Hkv, n]; dead_bits_scratch [Hkv, C/32] u32. */
+int semblo_nearest_cluster(const void* keys_bf16, int64_t n, int num_kv_heads, int head_dim,
+                           const void* codebooks, int num_clusters, int32_t* ids_out,
+                           uint32_t* dead_bits_scratch, int32_t* status, void* stream);
+
+/* append_rows (token_outer_prefill.py:66-87): ids [heads, n] in position order ->
+ * rows[h, i] = indptr[h, id] + sizes[h, id] + (earlier keys of the slice with the same id) and
+ * counts [heads, C].  workspace >= semblo_layout_workspace_bytes(n, heads) + heads * (C + 1) * 4. */
+int semblo_append_rows(const int32_t* ids, int64_t n, int heads, int num_clusters, const int32_t* indptr,
+                       const int32_t* sizes, int32_t* rows, int32_t* counts, void* workspace,
+                       int64_t workspace_bytes, void* stream);
+
+/* The index_copy_ calls of _append / _fit_and_pack (token_outer_prefill.py:296-309, 354-358):
+ * k, v [n, Hkv, D] of consecutive tokens go to rows[h, i] of packed [2, packed_rows, Hkv, D]
+ * (through page_table when given), posting[h, row] = positions[i], inverse[h, inverse_offset + i]
+ * = row; posting / inverse may be NULL.  A row outside the store sets status 201 and is skipped. */
+int semblo_scatter_kv(const void* k, const void* v, const int32_t* positions, int64_t n, int num_kv_heads,
+                      int head_dim, const int32_t* rows, int64_t rows_stride, void* packed,
+                      int64_t packed_rows, int64_t kv_stride_elems, int32_t* posting, int64_t posting_stride,
+                      int32_t* inverse, int64_t inverse_stride, int64_t inverse_offset,
+                      const int32_t* page_table, int32_t* status, void* stream);
+
+/* The opposite direction (reads through the inverse map: the local window and the dense start
+ * of the streamed mode, fused_prefill.py:155-189; the clone in _repack, token_outer_prefill.py:381):
+ * out_k / out_v [n, Hkv, D] = packed rows rows[h, i]. */
+int semblo_gather_kv(const void* packed, int64_t kv_stride_elems, const int32_t* rows, int64_t rows_stride,
+                     int64_t n, int num_kv_heads, int head_dim, void* out_k, void* out_v,
+                     const int32_t* page_table, void* stream);
+
+/* Rows after the cluster runs moved (token_outer_prefill.py:282-287, 375-379):
+ * new[h, i] = old[h, i] - old_indptr[h, b] + new_indptr[h, b] with b = bucket[h, i]. */
+int semblo_relayout_rows(const int32_t* rows_old, const int32_t* bucket, int64_t n, int64_t stride, int heads,
+                         const int32_t* old_indptr, const int32_t* new_indptr, int num_clusters,
+                         int32_t* rows_new, void* stream);
+
+/* repack_apply (suffix_flush.py:97-133) for all heads: n flushed tokens (flushed_k / flushed_v
+ * [n, Hkv, D], positions, assign [Hkv, n] in position order) follow each cluster's old rows, every
+ * cluster is re-padded to `align`, padding rows repeat the old row 0; packed, posting, sizes and
+ * indptr are rewritten in place.  old_packed_copy [2, packed_rows, Hkv, D] and old_posting_copy
+ * [Hkv, packed_rows] are scratch for the old store (posting_stride must equal packed_rows). */
+int64_t semblo_flush_workspace_bytes(int64_t n, int heads, int num_clusters);
+int semblo_flush_repack(void* packed, int64_t kv_stride_elems, int64_t packed_rows, int32_t* posting,
+                        int64_t posting_stride, int32_t* sizes, int32_t* indptr, int num_clusters,
+                        int num_kv_heads, int head_dim, int align, const void* flushed_k,
+                        const void* flushed_v, const int32_t* flushed_pos, const int32_t* assign, int64_t n,
+                        void* old_packed_copy, int32_t* old_posting_copy, void* workspace,
+                        int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* semblo_argsort_keys without a workspace and without any allocation: the scratch is a fixed
  * array inside the library image, looked up once per device.  No counterpart in the reference.
  * For callers that must not allocate at the point of the call (inside a serving loop that has

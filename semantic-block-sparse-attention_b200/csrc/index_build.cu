@@ -119,15 +119,20 @@ struct AssignSmem {
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
 };
 
-template <int D>
+// SPLIT: the centroids are a descriptor pair [2][C][D/2] (3-D map: column in the half, row,
+// half) instead of [C][D], the similarity is compared in fp32 as it comes out of the tensor
+// core (no bf16 rounding), and centroids whose bit is set in dead_bits are never chosen.
+template <int D, bool SPLIT>
 __global__ void __launch_bounds__(192, 1)
 assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
                      const __grid_constant__ CUtensorMap tmap_c, int64_t n, int num_centroids,
-                     int32_t* __restrict__ assign_out, int id_offset, int* __restrict__ status) {
+                     int32_t* __restrict__ assign_out, int id_offset,
+                     const uint32_t* __restrict__ dead_bits, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = AssignSmem<D>;
   constexpr int SLABS = D / 64;
+  constexpr int HALF_SLABS = SLABS >= 2 ? SLABS / 2 : 1;
   uint8_t* a_smem = smem;
   uint8_t* b_smem = smem + L::A_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -172,9 +177,13 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
                        STATUS_TIMEOUT_LOAD))
           break;
         mbar_arrive_expect_tx(smem_u32(&bars[1 + s]), L::B_BYTES);
-        for (int sl = 0; sl < SLABS; ++sl)
-          tma_load_2d(smem_u32(b_smem + s * L::B_BYTES + sl * ASG_BN * 128), &tmap_c,
-                      smem_u32(&bars[1 + s]), sl * 64, j * ASG_BN);
+        for (int sl = 0; sl < SLABS; ++sl) {
+          const uint32_t dst = smem_u32(b_smem + s * L::B_BYTES + sl * ASG_BN * 128);
+          if (SPLIT)
+            tma_load_3d(dst, &tmap_c, smem_u32(&bars[1 + s]), (sl % HALF_SLABS) * 64, j * ASG_BN, sl / HALF_SLABS);
+          else
+            tma_load_2d(dst, &tmap_c, smem_u32(&bars[1 + s]), sl * 64, j * ASG_BN);
+        }
       }
     }
   } else if (warp == 5) {
@@ -217,11 +226,13 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
         tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * ASG_BN + c4 * 32, r);
         tmem_ld_wait();
         const int cbase = j * ASG_BN + c4 * 32;
+        uint32_t dead = 0u;
+        if (SPLIT && dead_bits != nullptr && cbase < num_centroids) dead = __ldg(dead_bits + (cbase >> 5));
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           // the reference's bf16 matmul output: fp32 accumulate, round to nearest even
-          float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
-          bool take = (cbase + i < num_centroids) && (v > best);
+          float v = SPLIT ? __uint_as_float(r[i]) : __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+          bool take = (cbase + i < num_centroids) && !((dead >> i) & 1u) && (v > best);
           best = take ? v : best;
           best_id = take ? cbase + i : best_id;
         }
@@ -535,22 +546,46 @@ int sort_by_cluster(const int32_t* keys, int64_t n, int64_t head_stride, int hea
   return 0;
 }
 
-template <int D>
-int launch_assign(const void* x, int64_t n, const void* cent, int num_centroids, int32_t* out,
-                  int id_offset, int* status, cudaStream_t st) {
+template <int D, bool SPLIT>
+int launch_assign(const void* x, int64_t n, int64_t x_stride_elems, const void* cent, int num_centroids, int32_t* out,
+                  int id_offset, const uint32_t* dead_bits, int* status, cudaStream_t st) {
   CUtensorMap mx, mc;
-  uint64_t dx[2] = {(uint64_t)D, (uint64_t)n}, sx[1] = {(uint64_t)D * 2};
-  uint64_t dc[2] = {(uint64_t)D, (uint64_t)num_centroids};
+  uint64_t dx[2] = {(uint64_t)D, (uint64_t)n}, sx[1] = {(uint64_t)x_stride_elems * 2};
   uint32_t box[2] = {64, 128};
   int rc = semblo::make_tensor_map_bf16(&mx, x, 2, dx, sx, box);
   if (rc) return rc;
-  rc = semblo::make_tensor_map_bf16(&mc, cent, 2, dc, sx, box);
+  if (SPLIT) {
+    uint64_t dc[3] = {(uint64_t)D / 2, (uint64_t)num_centroids, 2};
+    uint64_t sc[2] = {(uint64_t)D, (uint64_t)num_centroids * D};          // bytes: row, half
+    uint32_t bc[3] = {64, 128, 1};
+    rc = semblo::make_tensor_map_bf16(&mc, cent, 3, dc, sc, bc);
+  } else {
+    uint64_t dc[2] = {(uint64_t)D, (uint64_t)num_centroids}, sc[1] = {(uint64_t)D * 2};
+    rc = semblo::make_tensor_map_bf16(&mc, cent, 2, dc, sc, box);
+  }
   if (rc) return rc;
-  auto kern = assign_argmax_kernel<D>;
+  auto kern = assign_argmax_kernel<D, SPLIT>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AssignSmem<D>::TOTAL));
-  kern<<<(unsigned)ceil_div(n, 128), 192, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset, status);
+  kern<<<(unsigned)ceil_div(n, 128), 192, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset,
+                                                                    dead_bits, status);
   SEMBLO_LAUNCH_CHECK();
   return 0;
+}
+
+// one warp per centroid of a descriptor pair [2][C][half]: bit set when every element is zero
+__global__ void dead_descriptor_kernel(const __nv_bfloat16* __restrict__ cb, int num_centroids, int half,
+                                       uint32_t* __restrict__ dead_bits) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int c = warp;
+  bool nonzero = false;
+  if (c < num_centroids) {
+    for (int f = 0; f < 2; ++f)
+      for (int d = lane; d < half; d += 32)
+        nonzero |= (__bfloat16_as_ushort(cb[((int64_t)f * num_centroids + c) * half + d]) & 0x7fffu) != 0;
+  }
+  const bool any = __any_sync(0xffffffffu, nonzero);
+  // clusters are consecutive per warp, 32 warps of 32 centroids share a word: set bits atomically
+  if (lane == 0 && c < num_centroids && !any) atomicOr(dead_bits + (c >> 5), 1u << (c & 31));
 }
 
 }  // namespace
@@ -595,11 +630,37 @@ extern "C" int semblo_assign_argmax(const void* x_bf16, int64_t n, const void* c
   if (n == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dim) {
-    case 64: return launch_assign<64>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
-    case 128: return launch_assign<128>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
-    case 256: return launch_assign<256>(x_bf16, n, cent_bf16, num_centroids, assign_out, id_offset, status, st);
+    case 64: return launch_assign<64, false>(x_bf16, n, 64, cent_bf16, num_centroids, assign_out, id_offset, nullptr, status, st);
+    case 128: return launch_assign<128, false>(x_bf16, n, 128, cent_bf16, num_centroids, assign_out, id_offset, nullptr, status, st);
+    case 256: return launch_assign<256, false>(x_bf16, n, 256, cent_bf16, num_centroids, assign_out, id_offset, nullptr, status, st);
     default: return semblo::fail(semblo::SEMBLO_EINVAL, "routing dim %d is not 64, 128 or 256", dim);
   }
+}
+
+extern "C" int semblo_nearest_cluster(const void* keys_bf16, int64_t n, int num_kv_heads, int head_dim,
+                                      const void* codebooks, int num_clusters, int32_t* ids_out,
+                                      uint32_t* dead_bits_scratch, int32_t* status, void* stream) {
+  SEMBLO_REQUIRE(num_clusters > 0 && num_clusters % 32 == 0, "cluster count %d must be a positive multiple of 32", num_clusters);
+  SEMBLO_REQUIRE(status != nullptr && dead_bits_scratch != nullptr, "status word and scratch are required");
+  SEMBLO_REQUIRE(head_dim == 128 || head_dim == 256, "head_dim %d must be 128 or 256", head_dim);
+  if (n == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int words = num_clusters / 32;
+  SEMBLO_CUDA(cudaMemsetAsync(dead_bits_scratch, 0, sizeof(uint32_t) * (size_t)num_kv_heads * words, st));
+  for (int h = 0; h < num_kv_heads; ++h) {
+    const __nv_bfloat16* cb = (const __nv_bfloat16*)codebooks + (int64_t)h * 2 * num_clusters * (head_dim / 2);
+    uint32_t* dead = dead_bits_scratch + (int64_t)h * words;
+    dead_descriptor_kernel<<<(unsigned)ceil_div(num_clusters, 8), 256, 0, st>>>(cb, num_clusters, head_dim / 2, dead);
+    const __nv_bfloat16* x = (const __nv_bfloat16*)keys_bf16 + (int64_t)h * head_dim;
+    int rc;
+    if (head_dim == 256)
+      rc = launch_assign<256, true>(x, n, (int64_t)num_kv_heads * 256, cb, num_clusters, ids_out + (int64_t)h * n, 0, dead, status, st);
+    else
+      rc = launch_assign<128, true>(x, n, (int64_t)num_kv_heads * 128, cb, num_clusters, ids_out + (int64_t)h * n, 0, dead, status, st);
+    if (rc) return rc;
+  }
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
 }
 
 extern "C" int64_t semblo_layout_workspace_bytes(int64_t n, int heads) {
@@ -714,6 +775,304 @@ extern "C" int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, in
   const int64_t hn = (int64_t)heads * n;
   return sort_by_cluster(keys, n, n, heads, max_key, order, ws, ws + hn, ws + 2 * hn, ws + 3 * hn,
                          (cudaStream_t)stream);
+}
+
+// ====================================================================== streamed updates
+// Keys that arrive after the index was fitted (token-order streamed prefill, suffix flush):
+// nearest-centroid ids come from semblo_nearest_cluster; the kernels below turn them into packed
+// rows and move K/V rows.  Reference behaviour restated here:
+//   semblo/vllm_plugin/token_outer_prefill.py:66-87    append_rows (destination rows, counts)
+//   semblo/vllm_plugin/token_outer_prefill.py:339-392  _append, _repack (row moves)
+//   semblo/vllm_plugin/suffix_flush.py:56-133          repack_plan / repack_apply
+namespace {
+
+// sorted slot j of head h -> destination row of the key it holds
+__global__ void append_rank_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
+                                   const int32_t* __restrict__ starts /* [H, C+1] */,
+                                   const int32_t* __restrict__ indptr, const int32_t* __restrict__ sizes,
+                                   int64_t n, int num_clusters, int32_t* __restrict__ rows) {
+  const int h = blockIdx.y;
+  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (int64_t)gridDim.x * blockDim.x) {
+    const int t = order[h * n + j];
+    const int c = ids[h * n + t];
+    const int rank = (int)j - starts[(int64_t)h * (num_clusters + 1) + c];
+    rows[h * n + t] = indptr[(int64_t)h * (num_clusters + 1) + c] + sizes[(int64_t)h * num_clusters + c] + rank;
+  }
+}
+
+// one warp per (token, head): K/V row into the packed store, position and inverse entry
+__global__ void scatter_kv_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                  const int32_t* __restrict__ positions, int64_t n, int num_kv_heads, int head_dim,
+                                  const int32_t* __restrict__ rows, int64_t rows_stride,
+                                  __nv_bfloat16* __restrict__ packed, int64_t kv_stride_elems,
+                                  int32_t* __restrict__ posting, int64_t posting_stride,
+                                  int32_t* __restrict__ inverse, int64_t inverse_stride, int64_t inverse_offset,
+                                  const int32_t* __restrict__ page_table, int64_t packed_rows,
+                                  int32_t* __restrict__ status) {
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n * num_kv_heads) return;
+  const int64_t i = item / num_kv_heads;
+  const int h = (int)(item % num_kv_heads);
+  if (*reinterpret_cast<const volatile int32_t*>(status) != 0) return;   // an earlier stage refused
+  const int row = rows[h * rows_stride + i];
+  if (row < 0 || row >= packed_rows) {               // the store is full: refuse, never write outside it
+    if (lane == 0) atomicCAS(status, 0, STATUS_OVERFLOW);
+    return;
+  }
+  const int64_t phys = page_table ? (int64_t)page_table[row >> 4] * 16 + (row & 15) : row;
+  const uint4* ks = reinterpret_cast<const uint4*>(k + (i * num_kv_heads + h) * head_dim);
+  const uint4* vs = reinterpret_cast<const uint4*>(v + (i * num_kv_heads + h) * head_dim);
+  uint4* kd = reinterpret_cast<uint4*>(packed + (phys * num_kv_heads + h) * head_dim);
+  uint4* vd = reinterpret_cast<uint4*>(packed + kv_stride_elems + (phys * num_kv_heads + h) * head_dim);
+  for (int c = lane; c < head_dim / 8; c += 32) {
+    kd[c] = ks[c];
+    vd[c] = vs[c];
+  }
+  if (lane == 0) {
+    if (posting) posting[h * posting_stride + row] = positions[i];
+    if (inverse) inverse[h * inverse_stride + inverse_offset + i] = row;
+  }
+}
+
+// one warp per (token, head): packed rows back into [n, Hkv, D]
+__global__ void gather_kv_kernel(const __nv_bfloat16* __restrict__ packed, int64_t kv_stride_elems,
+                                 const int32_t* __restrict__ rows, int64_t rows_stride, int64_t n, int num_kv_heads,
+                                 int head_dim, __nv_bfloat16* __restrict__ out_k, __nv_bfloat16* __restrict__ out_v,
+                                 const int32_t* __restrict__ page_table) {
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n * num_kv_heads) return;
+  const int64_t i = item / num_kv_heads;
+  const int h = (int)(item % num_kv_heads);
+  const int row = rows[h * rows_stride + i];
+  const int64_t phys = page_table ? (int64_t)page_table[row >> 4] * 16 + (row & 15) : row;
+  const uint4* ks = reinterpret_cast<const uint4*>(packed + (phys * num_kv_heads + h) * head_dim);
+  const uint4* vs = reinterpret_cast<const uint4*>(packed + kv_stride_elems + (phys * num_kv_heads + h) * head_dim);
+  uint4* kd = reinterpret_cast<uint4*>(out_k + (i * num_kv_heads + h) * head_dim);
+  uint4* vd = reinterpret_cast<uint4*>(out_v + (i * num_kv_heads + h) * head_dim);
+  for (int c = lane; c < head_dim / 8; c += 32) {
+    kd[c] = ks[c];
+    vd[c] = vs[c];
+  }
+}
+
+__global__ void relayout_rows_kernel(const int32_t* __restrict__ rows_old, const int32_t* __restrict__ bucket,
+                                     int64_t n, int64_t stride, const int32_t* __restrict__ old_indptr,
+                                     const int32_t* __restrict__ new_indptr, int num_clusters,
+                                     int32_t* __restrict__ rows_new) {
+  const int h = blockIdx.y;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int b = bucket[h * stride + i];
+    rows_new[h * stride + i] = rows_old[h * stride + i] - old_indptr[(int64_t)h * (num_clusters + 1) + b] +
+                               new_indptr[(int64_t)h * (num_clusters + 1) + b];
+  }
+}
+
+// Suffix flush: new sizes and 16-aligned starts of every cluster
+__global__ void flush_layout_kernel(const int32_t* __restrict__ old_sizes, const int32_t* __restrict__ added,
+                                    int num_clusters, int align, int32_t* __restrict__ new_sizes,
+                                    int32_t* __restrict__ new_indptr /* [H, C+1] */, int64_t packed_rows,
+                                    int32_t* __restrict__ status) {
+  __shared__ int s_part[1024];
+  const int h = blockIdx.x;
+  const int per = (num_clusters + blockDim.x - 1) / blockDim.x;
+  const int lo = min(num_clusters, (int)threadIdx.x * per), hi = min(num_clusters, lo + per);
+  int sum = 0;
+  for (int c = lo; c < hi; ++c) {
+    const int v = old_sizes[(int64_t)h * num_clusters + c] + added[(int64_t)h * num_clusters + c];
+    sum += ((v + align - 1) / align) * align;
+  }
+  s_part[threadIdx.x] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) { const int v = s_part[t]; s_part[t] = run; run += v; }
+    new_indptr[(int64_t)h * (num_clusters + 1) + num_clusters] = run;
+    if (run > packed_rows) atomicCAS(status, 0, STATUS_OVERFLOW);   // the re-packed store does not fit: nothing moves
+  }
+  __syncthreads();
+  int run = s_part[threadIdx.x];
+  for (int c = lo; c < hi; ++c) {
+    const int v = old_sizes[(int64_t)h * num_clusters + c] + added[(int64_t)h * num_clusters + c];
+    new_sizes[(int64_t)h * num_clusters + c] = v;
+    new_indptr[(int64_t)h * (num_clusters + 1) + c] = run;
+    run += ((v + align - 1) / align) * align;
+  }
+}
+
+// Suffix flush: the new sizes and starts replace the old ones unless the flush was refused.
+__global__ void flush_commit_kernel(const int32_t* __restrict__ new_sizes, const int32_t* __restrict__ new_indptr,
+                                    int64_t n_sizes, int64_t n_indptr, int32_t* __restrict__ sizes,
+                                    int32_t* __restrict__ indptr, const int32_t* __restrict__ status) {
+  if (*reinterpret_cast<const volatile int32_t*>(status) != 0) return;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_indptr; i += (int64_t)gridDim.x * blockDim.x) {
+    if (i < n_sizes) sizes[i] = new_sizes[i];
+    indptr[i] = new_indptr[i];
+  }
+}
+
+// Suffix flush: one warp per (new row, head).  Old rows move from the copy of the old store,
+// padding rows repeat the old row 0 (K/V and position); rows of flushed tokens are left to
+// the scatter that follows.
+__global__ void flush_move_kernel(const __nv_bfloat16* __restrict__ old_packed, const int32_t* __restrict__ old_posting,
+                                  int64_t old_kv_stride_elems, int64_t posting_stride,
+                                  const int32_t* __restrict__ old_sizes, const int32_t* __restrict__ old_indptr,
+                                  const int32_t* __restrict__ new_sizes, const int32_t* __restrict__ new_indptr,
+                                  int num_clusters, int num_kv_heads, int head_dim, int64_t max_rows,
+                                  __nv_bfloat16* __restrict__ packed, int64_t kv_stride_elems,
+                                  int32_t* __restrict__ posting, const int32_t* __restrict__ status) {
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= max_rows * num_kv_heads) return;
+  if (*reinterpret_cast<const volatile int32_t*>(status) != 0) return;
+  const int64_t r = item / num_kv_heads;
+  const int h = (int)(item % num_kv_heads);
+  const int32_t* nip = new_indptr + (int64_t)h * (num_clusters + 1);
+  if (r >= nip[num_clusters]) return;
+  int lo = 0, hi = num_clusters;                      // last c with nip[c] <= r
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (nip[mid] <= r) lo = mid; else hi = mid;
+  }
+  const int c = lo;
+  const int off = (int)r - nip[c];
+  const int osz = old_sizes[(int64_t)h * num_clusters + c];
+  int64_t src;
+  if (off < osz) src = old_indptr[(int64_t)h * (num_clusters + 1) + c] + off;
+  else if (off < new_sizes[(int64_t)h * num_clusters + c]) return;      // a flushed token's row
+  else src = 0;
+  const uint4* ks = reinterpret_cast<const uint4*>(old_packed + (src * num_kv_heads + h) * head_dim);
+  const uint4* vs = reinterpret_cast<const uint4*>(old_packed + old_kv_stride_elems + (src * num_kv_heads + h) * head_dim);
+  uint4* kd = reinterpret_cast<uint4*>(packed + (r * num_kv_heads + h) * head_dim);
+  uint4* vd = reinterpret_cast<uint4*>(packed + kv_stride_elems + (r * num_kv_heads + h) * head_dim);
+  for (int ch = lane; ch < head_dim / 8; ch += 32) {
+    kd[ch] = ks[ch];
+    vd[ch] = vs[ch];
+  }
+  if (lane == 0) posting[h * posting_stride + r] = old_posting[h * posting_stride + src];
+}
+
+}  // namespace
+
+extern "C" int semblo_append_rows(const int32_t* ids, int64_t n, int heads, int num_clusters,
+                                  const int32_t* indptr, const int32_t* sizes, int32_t* rows, int32_t* counts,
+                                  void* workspace, int64_t workspace_bytes, void* stream) {
+  SEMBLO_REQUIRE(num_clusters > 0 && num_clusters <= 65536 && heads > 0, "bad cluster or head count");
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, heads) + (int64_t)heads * (num_clusters + 1) * 4,
+                 "workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n == 0) {
+    SEMBLO_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (size_t)heads * num_clusters, st));
+    return 0;
+  }
+  int32_t* ws = (int32_t*)workspace;
+  const int64_t hn = (int64_t)heads * n;
+  int32_t *order = ws, *tk = ws + hn, *tv = ws + 2 * hn, *tk2 = ws + 3 * hn, *th = ws + 4 * hn;
+  int32_t* starts = th + (int64_t)heads * 256 * ceil_div(n, SORT_TILE);
+  int rc = semblo_cluster_counts(ids, n, n, heads, num_clusters, 1, counts, starts, nullptr, nullptr, nullptr, stream);
+  if (rc) return rc;
+  rc = sort_by_cluster(ids, n, n, heads, num_clusters, order, tk, tv, tk2, th, st);
+  if (rc) return rc;
+  dim3 grid((unsigned)std::min<int64_t>(ceil_div(n, 256), 1184), heads);
+  append_rank_kernel<<<grid, 256, 0, st>>>(ids, order, starts, indptr, sizes, n, num_clusters, rows);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_scatter_kv(const void* k, const void* v, const int32_t* positions, int64_t n,
+                                 int num_kv_heads, int head_dim, const int32_t* rows, int64_t rows_stride,
+                                 void* packed, int64_t packed_rows, int64_t kv_stride_elems, int32_t* posting,
+                                 int64_t posting_stride, int32_t* inverse, int64_t inverse_stride,
+                                 int64_t inverse_offset, const int32_t* page_table, int32_t* status, void* stream) {
+  SEMBLO_REQUIRE(head_dim % 8 == 0, "head_dim %d must be a multiple of 8", head_dim);
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  SEMBLO_REQUIRE(posting == nullptr || positions != nullptr, "positions are needed to fill the posting list");
+  const int64_t items = n * num_kv_heads;
+  if (items == 0) return 0;
+  scatter_kv_kernel<<<(unsigned)ceil_div(items, 8), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, positions, n, num_kv_heads, head_dim, rows, rows_stride,
+      (__nv_bfloat16*)packed, kv_stride_elems, posting, posting_stride, inverse, inverse_stride, inverse_offset,
+      page_table, packed_rows, status);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_gather_kv(const void* packed, int64_t kv_stride_elems, const int32_t* rows,
+                                int64_t rows_stride, int64_t n, int num_kv_heads, int head_dim, void* out_k,
+                                void* out_v, const int32_t* page_table, void* stream) {
+  SEMBLO_REQUIRE(head_dim % 8 == 0, "head_dim %d must be a multiple of 8", head_dim);
+  const int64_t items = n * num_kv_heads;
+  if (items == 0) return 0;
+  gather_kv_kernel<<<(unsigned)ceil_div(items, 8), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)packed, kv_stride_elems, rows, rows_stride, n, num_kv_heads, head_dim,
+      (__nv_bfloat16*)out_k, (__nv_bfloat16*)out_v, page_table);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int semblo_relayout_rows(const int32_t* rows_old, const int32_t* bucket, int64_t n, int64_t stride,
+                                    int heads, const int32_t* old_indptr, const int32_t* new_indptr,
+                                    int num_clusters, int32_t* rows_new, void* stream) {
+  if (n == 0) return 0;
+  dim3 grid((unsigned)std::min<int64_t>(ceil_div(n, 256), 1184), heads);
+  relayout_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(rows_old, bucket, n, stride, old_indptr, new_indptr,
+                                                              num_clusters, rows_new);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int64_t semblo_flush_workspace_bytes(int64_t n, int heads, int num_clusters) {
+  // append_rows workspace, then added [H, C], new_sizes [H, C], new_indptr [H, C+1], rows [H, n]
+  return semblo_layout_workspace_bytes(n, heads) + (int64_t)heads * (num_clusters + 1) * 4 +
+         ((int64_t)heads * (3 * (int64_t)num_clusters + 1) + (int64_t)heads * n) * 4 + 1024;
+}
+
+extern "C" int semblo_flush_repack(void* packed, int64_t kv_stride_elems, int64_t packed_rows, int32_t* posting,
+                                   int64_t posting_stride, int32_t* sizes, int32_t* indptr, int num_clusters,
+                                   int num_kv_heads, int head_dim, int align, const void* flushed_k,
+                                   const void* flushed_v, const int32_t* flushed_pos, const int32_t* assign,
+                                   int64_t n, void* old_packed_copy, int32_t* old_posting_copy, void* workspace,
+                                   int64_t workspace_bytes, int32_t* status, void* stream) {
+  SEMBLO_REQUIRE(align >= 1 && head_dim % 8 == 0, "bad alignment or head_dim");
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_flush_workspace_bytes(n, num_kv_heads, num_clusters), "workspace too small");
+  SEMBLO_REQUIRE(old_packed_copy != nullptr && old_posting_copy != nullptr, "a copy of the old store is required");
+  SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  if (n == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int H = num_kv_heads, C = num_clusters;
+  uint8_t* wsb = (uint8_t*)workspace;
+  const int64_t append_bytes = semblo_layout_workspace_bytes(n, H) + (int64_t)H * (C + 1) * 4;
+  int32_t* added = (int32_t*)(wsb + ((append_bytes + 255) / 256) * 256);
+  int32_t* new_sizes = added + (int64_t)H * C;
+  int32_t* new_indptr = new_sizes + (int64_t)H * C;
+  int32_t* rows = new_indptr + (int64_t)H * (C + 1);
+  // the old store, to read from while the live one is rewritten
+  const size_t plane_bytes = (size_t)packed_rows * H * head_dim * 2;
+  SEMBLO_CUDA(cudaMemcpyAsync(old_packed_copy, packed, plane_bytes, cudaMemcpyDeviceToDevice, st));
+  SEMBLO_CUDA(cudaMemcpyAsync((__nv_bfloat16*)old_packed_copy + (int64_t)packed_rows * H * head_dim,
+                              (const __nv_bfloat16*)packed + kv_stride_elems, plane_bytes, cudaMemcpyDeviceToDevice, st));
+  SEMBLO_CUDA(cudaMemcpy2DAsync(old_posting_copy, (size_t)packed_rows * 4, posting, (size_t)posting_stride * 4,
+                                (size_t)packed_rows * 4, H, cudaMemcpyDeviceToDevice, st));
+  // counts of the flushed tokens, the new layout, then the flushed tokens' rows in it
+  int rc = semblo_cluster_counts(assign, n, n, H, C, 1, added, new_indptr /* scratch, rewritten below */, nullptr,
+                                 nullptr, nullptr, stream);
+  if (rc) return rc;
+  flush_layout_kernel<<<H, 1024, 0, st>>>(sizes, added, C, align, new_sizes, new_indptr, packed_rows, status);
+  rc = semblo_append_rows(assign, n, H, C, new_indptr, sizes, rows, added, workspace, append_bytes, stream);
+  if (rc) return rc;
+  // (old_posting_copy rows are packed_rows apart; the kernel indexes both postings with one stride)
+  SEMBLO_REQUIRE(posting_stride == packed_rows, "the posting list and the packed store must have the same row count");
+  flush_move_kernel<<<(unsigned)ceil_div(packed_rows * H, 8), 256, 0, st>>>(
+      (const __nv_bfloat16*)old_packed_copy, old_posting_copy, (int64_t)packed_rows * H * head_dim, posting_stride,
+      sizes, indptr, new_sizes, new_indptr, C, H, head_dim, packed_rows, (__nv_bfloat16*)packed, kv_stride_elems,
+      posting, status);
+  rc = semblo_scatter_kv(flushed_k, flushed_v, flushed_pos, n, H, head_dim, rows, n, packed, packed_rows,
+                         kv_stride_elems, posting, posting_stride, nullptr, 0, 0, nullptr, status, stream);
+  if (rc) return rc;
+  flush_commit_kernel<<<32, 256, 0, st>>>(new_sizes, new_indptr, (int64_t)H * C, (int64_t)H * (C + 1), sizes, indptr, status);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
 }
 
 // ====================================================================== no-allocation arg-sort

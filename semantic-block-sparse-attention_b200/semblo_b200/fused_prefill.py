@@ -130,26 +130,39 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                           snapshot_state: CausalSnapshot, chunk_start: int, chunk_end: int, *,
                           temperature: float, beta: float, target_tokens: int, queries_per_block: int = 32,
                           sm_scale: float, iters: int = 16, dense_prefix_x: int = 4, out=None,
-                          attended=None, _timer=None, **unused) -> torch.Tensor:
+                          attended=None, local_kv=None, _timer=None, **unused) -> torch.Tensor:
     """Attention of one query chunk (fused_prefill.py:219-482, default path).
 
     ``query_state.vectors`` [1, Q, Hq, 1, D] routing vectors; ``index.original_kv`` must hold
-    the position-ordered (k_post, v) of the prompt: the exact window is read from it."""
+    the position-ordered (k_post, v) of the prompt: the exact window is read from it.
+    ``local_kv`` = (k, v, first_position) replaces it for this call (the streamed mode, which
+    keeps no prompt-order copy, hands over the rows of the window it has gathered)."""
     import semblo_b200
     semblo_b200.SPARSE_ATTENTION_CALLS += 1
     cap = int(os.environ.get("SEMBLO_FA3_DENSE_PREFIX_X", str(dense_prefix_x))) * target_tokens
     local = int(os.environ.get("SEMBLO_FA3_LOCAL", "0"))
     wstart = 0 if chunk_start <= cap else max(0, chunk_start - local)
-    original_kv = getattr(index, "original_kv", None)
-    if original_kv is None:
-        raise RuntimeError("the prefill body reads the chunk's exact window from the position-ordered K/V "
-                           "(index.original_kv)")
-    k_pos, v_pos = original_kv
+    if local_kv is not None:
+        k_loc, v_loc, pos0 = local_kv
+        if pos0 > wstart or pos0 + k_loc.shape[0] <= chunk_end:
+            raise RuntimeError(f"the window [{wstart}, {chunk_end}] is not inside the rows handed over "
+                               f"([{pos0}, {pos0 + k_loc.shape[0] - 1}])")
+    else:
+        original_kv = getattr(index, "original_kv", None)
+        if original_kv is None:
+            raise RuntimeError("the prefill body reads the chunk's exact window from the position-ordered K/V "
+                               "(index.original_kv)")
+        k_loc, v_loc = original_kv
+        pos0 = 0
+
+    def window_rows(first):
+        return k_loc[first - pos0:chunk_end + 1 - pos0], v_loc[first - pos0:chunk_end + 1 - pos0]
+
     if wstart == 0:
         if _timer:
             _timer("start")
-        res = window_attention(q_chunk, q_positions, ordered_k=k_pos[:chunk_end + 1],
-                               ordered_v=v_pos[:chunk_end + 1], ordered_pos0=0, local_start=0,
+        k_w, v_w = window_rows(0)
+        res = window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=0, local_start=0,
                                sm_scale=sm_scale, out=out, attended=attended)
         if _timer:
             _timer("stop")
@@ -197,8 +210,8 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if _timer:
         _timer("start")
     # the exact window [wstart, q] in position order, then the selected clusters merged into it
-    window_attention(q_chunk, q_positions, ordered_k=k_pos[wstart:chunk_end + 1],
-                     ordered_v=v_pos[wstart:chunk_end + 1], ordered_pos0=wstart, local_start=wstart,
+    k_w, v_w = window_rows(wstart)
+    window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=wstart, local_start=wstart,
                      sm_scale=sm_scale, out=out, lse=lse, attended=attended, partial=partial)
     if _timer:
         _timer("mid")

@@ -1,0 +1,62 @@
+"""Suffix flush: move the older part of the exact generated suffix into the clusters.
+
+Mirrors semblo/vllm_plugin/suffix_flush.py (flush_range 140-151, flush_layer 172-208 with the
+identity routing map, repack_apply 97-133) on a DecodeArena.  It runs between decode steps,
+eagerly, on the arena's own buffers."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, ptr, stream_ptr
+from .flat_index import routing_normalize
+from .token_outer import nearest_cluster
+
+
+def flush_range(prompt_len: int, written: int, plen_cur: int, keep: int, every: int):
+    """suffix_flush.py:140-151: the positions [frm, to) to move now, or None."""
+    live = prompt_len + written - plen_cur
+    if live >= keep + every:
+        return plen_cur, prompt_len + written - keep
+    return None
+
+
+def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
+    """Move suffix positions [frm, to) into their nearest clusters (suffix_flush.py:172-208).
+
+    Reads the rows from the suffix store, assigns each to a cluster per KV head, re-packs the
+    arena's store in place, advances the prompt length and extends the ring table.  Returns the
+    widest packed length after the flush (one host read, as the reference's own return value)."""
+    n = int(to) - int(frm)
+    if n <= 0:
+        return 0
+    if arena.suffix_kpre is None:
+        raise RuntimeError("the flush assigns by the pre-RoPE keys: build the arena with keep_kpre=True")
+    dev = arena.packed_kv.device
+    align = arena.page_align if align is None else max(int(align), 1)
+    pos = torch.arange(frm, to, device=dev)
+    blk = pos // arena.suffix_block
+    phys = arena.suffix_table[0, blk].long()
+    off = pos - blk * arena.suffix_block
+    kpre = arena.suffix_kpre[phys, off].contiguous()                    # [n, Hkv, D]
+    k = arena.suffix_kv[0, phys, off].contiguous()
+    v = arena.suffix_kv[1, phys, off].contiguous()
+    product = routing_normalize(kpre)
+    assign = nearest_cluster(product, arena.codebooks)                   # [Hkv, n]
+    hkv, c = int(arena.sizes.shape[0]), int(arena.sizes.shape[1])
+    d = int(arena.packed_kv.shape[-1])
+    width = int(arena.packed_kv.shape[1])
+    ws_bytes = int(lib().semblo_flush_workspace_bytes(n, hkv, c))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    old_packed = torch.empty_like(arena.packed_kv)
+    old_posting = torch.empty_like(arena.posting)
+    status = _lib.status_for(dev)
+    check(lib().semblo_flush_repack(ptr(arena.packed_kv), arena.packed_kv.stride(0), width, ptr(arena.posting),
+                                    arena.posting.stride(0), ptr(arena.sizes), ptr(arena.indptr), c, hkv, d, align,
+                                    ptr(k), ptr(v), ptr(pos.to(torch.int32)), ptr(assign), n, ptr(old_packed),
+                                    ptr(old_posting), ptr(ws), ws_bytes, ptr(status.word), stream_ptr()))
+    arena.prompt_length_t.fill_(int(to))
+    arena.extend_suffix_table(int(to) + arena.reserve - 1)
+    widest = int(arena.indptr[:, -1].max().item())
+    status.raise_if_set()
+    return widest
