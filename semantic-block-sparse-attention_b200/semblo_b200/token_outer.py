@@ -271,6 +271,13 @@ class TokenOuterPrefillSession:
         if bool((sizes.to(torch.int64) + counts > self.reserve).any()):       # one host read, as the reference
             self._repack(start)
             rows, counts = append_rows(ids, index.bucket_indptr, sizes)
+            if bool((sizes.to(torch.int64) + counts > self.reserve).any()):
+                # The reference stops here (token_outer_prefill.py:350-352) and a cluster that the
+                # slice pushes past its fresh reservation would run into its neighbour's rows.  Lay
+                # the store out once more from the sizes that include the slice: every run then
+                # holds its cluster by construction.
+                self._repack(start, incoming=counts, n_incoming=stop - start)
+                rows, counts = append_rows(ids, index.bucket_indptr, sizes)
         scatter_kv(k3, v3, self.positions32[start:stop], rows, index.packed_kv, index.posting_positions,
                    index._inverse_positions, inverse_offset=start)
         index.orig_bucket[:, start:stop] = ids
@@ -279,12 +286,14 @@ class TokenOuterPrefillSession:
         self.snapshot.chunk_start = start
         sizes += counts
 
-    def _repack(self, n_so_far: int) -> None:
-        """Lay the runs out again from the current proportions, in place (token_outer_prefill.py:366-392)."""
+    def _repack(self, n_so_far: int, incoming: torch.Tensor | None = None, n_incoming: int = 0) -> None:
+        """Lay the runs out again from the current proportions, in place (token_outer_prefill.py:366-392).
+        ``incoming`` [Hkv, C] adds a slice's counts to the proportions (see _append)."""
         index = self.index
         align = max(int(index.page_align), 1)
         width = int(index.packed_kv.shape[1])
-        reserve = reserved_layout(index.bucket_sizes, n_so_far, self.tokens, width, align)
+        basis = index.bucket_sizes if incoming is None else index.bucket_sizes + incoming
+        reserve = reserved_layout(basis, n_so_far + n_incoming, self.tokens, width, align)
         new_ip = torch.zeros_like(index.bucket_indptr)
         new_ip[:, 1:] = torch.cumsum(reserve, 1).to(torch.int32)
         rows_old = index._inverse_positions

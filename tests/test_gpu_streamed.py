@@ -170,10 +170,11 @@ def test_token_outer_session_against_the_oracle(dev):
                 ref = dict(packed=ix.packed_kv.cpu().clone(), posting=ix.posting_positions.cpu().clone(),
                            indptr=want_ip.clone(), sizes=sizes_fit.clone(), inverse=ix._inverse_positions.cpu().clone(),
                            codebooks=ix.codebooks.cpu().clone(), reserve=reserve.clone(), repacks=0)
-            def oracle_repack(n_so_far):
+            def oracle_repack(n_so_far, incoming=None, n_incoming=0):
                 """token_outer_prefill.py:366-392 on the oracle's copy of the store."""
                 old_ip = ref["indptr"].clone()
-                new_res = O.reserved_layout(ref["sizes"], n_so_far, total, int(ref["packed"].shape[1]), align)
+                basis = ref["sizes"] if incoming is None else (ref["sizes"].long() + incoming).int()
+                new_res = O.reserved_layout(basis, n_so_far + n_incoming, total, int(ref["packed"].shape[1]), align)
                 new_ip = torch.zeros_like(old_ip)
                 new_ip[:, 1:] = new_res.cumsum(1).int()
                 rows_new = O.relayout_rows(ref["inverse"][:, :n_so_far], old_ip, new_ip)
@@ -208,6 +209,9 @@ def test_token_outer_session_against_the_oracle(dev):
             if bool((ref["sizes"].long() + counts > ref["reserve"]).any()):     # a cluster outgrew its reservation
                 oracle_repack(start)
                 rows_want, counts = O.append_rows(ids, ref["indptr"], ref["sizes"])
+                if bool((ref["sizes"].long() + counts > ref["reserve"]).any()):  # still too small: include the slice
+                    oracle_repack(start, counts, chunk)
+                    rows_want, counts = O.append_rows(ids, ref["indptr"], ref["sizes"])
             assert torch.equal(sess.index.bucket_indptr.cpu(), ref["indptr"])
             assert torch.equal(sess.index._inverse_positions[:, sl].cpu().long(), rows_want)
             sizes_before = ref["sizes"].clone()
