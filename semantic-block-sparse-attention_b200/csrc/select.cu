@@ -35,7 +35,8 @@ struct ScoreSmem {
   static constexpr int A_BYTES = 128 * D * 2;
   static constexpr int B_BYTES = SC_BN * D * 2;
   static constexpr int BAR_OFF = A_BYTES + SC_STAGES * B_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int XCHG_OFF = BAR_OFF + 256;               // float [2][128][2]: (max, sum) of a half-row
+  static constexpr int TOTAL = XCHG_OFF + 2048 + 1024;
 };
 
 // Sum v[] over the G adjacent lanes that hold the G heads of one query; afterwards
@@ -63,7 +64,7 @@ __device__ __forceinline__ int head_butterfly(float (&v)[32], int lane) {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D] bf16, box (64, G, 128/G)
              const __grid_constant__ CUtensorMap tmap_cb,   // codebooks [Hkv*2, C, D/2] bf16, box (64, 128, 1)
              int num_queries, int num_clusters, const int32_t* __restrict__ sizes,   // [Hkv, C]
@@ -81,6 +82,8 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);
+  // bars: 0 a_full, 1..2 b_full, 3..4 b_empty, 5..6 acc_full, 7..8 acc_empty, 9 epilogue rendezvous
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -94,8 +97,9 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
       mbar_init(smem_u32(&bars[5 + s]), 1);
-      mbar_init(smem_u32(&bars[7 + s]), 128);
+      mbar_init(smem_u32(&bars[7 + s]), 256);
     }
+    mbar_init(smem_u32(&bars[9]), 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -108,7 +112,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (elect_one()) {
       tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_cb);
@@ -126,7 +130,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
                       smem_u32(&bars[1 + s]), (sl % SLABS_PER_HALF) * 64, c0, h * 2 + sl / SLABS_PER_HALF);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_bf16(128, SC_BN, false, false);
       bool ok = mbar_wait(smem_u32(&bars[0]), 0, abort_flag, status, STATUS_TIMEOUT_MMA);
@@ -148,8 +152,10 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
       }
     }
   } else {
-    // epilogue warps: thread = row (query i = row / G, head t = row % G)
-    const int row = threadIdx.x;
+    // epilogue warps 0-7: thread = (half, row); query i = row / G, head t = row % G.  The two
+    // warps that share 32 rows split every 128-cluster chunk: half 0 takes its first 64 columns.
+    const int hf = warp >> 2;
+    const int row = threadIdx.x & 127;
     const int qi = q0 + row / G;
     // Routing vectors and descriptors are unit vectors (up to bf16 rounding), so every logit is
     // bounded by 1.01 * scale: with a moderate scale the log-sum-exp needs no running maximum.
@@ -175,25 +181,38 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
       const int c0 = (j % chunks) * SC_BN;
       const bool full_chunk = c0 + SC_BN <= num_clusters;
       // sizes of this thread's output clusters, fetched before the accumulator is awaited
-      int nsz[SC_BN / 32][OUT];
+      int nsz[2][OUT];
       if (pass == 1) {
 #pragma unroll
-        for (int c4 = 0; c4 < SC_BN / 32; ++c4)
+        for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
           for (int i = 0; i < OUT; ++i) {
-            const int c = c0 + c4 * 32 + col_off + i;
-            nsz[c4][i] = c < num_clusters ? sz[c] : 0;
+            const int c = c0 + (2 * hf + cc) * 32 + col_off + i;
+            nsz[cc][i] = c < num_clusters ? sz[c] : 0;
           }
       }
       ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
-      if (j == chunks) lse2 = m_run + __log2f(l_run);
+      if (j == chunks) {
+        // both halves of a row combine their (max, sum) before the second pass
+        xchg[(hf * 128 + row) * 2] = m_run;
+        xchg[(hf * 128 + row) * 2 + 1] = l_run;
+        mbar_arrive(smem_u32(&bars[9]));
+        ok = mbar_wait(smem_u32(&bars[9]), 0, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+        if (!ok) break;
+        const float m_o = xchg[((hf ^ 1) * 128 + row) * 2], l_o = xchg[((hf ^ 1) * 128 + row) * 2 + 1];
+        const float mx = fmaxf(m_run, m_o);
+        const float l_all = (m_run == -INFINITY ? 0.f : l_run * fast_exp2(m_run - mx)) +
+                            (m_o == -INFINITY ? 0.f : l_o * fast_exp2(m_o - mx));
+        lse2 = mx + __log2f(l_all);
+      }
       const float neg_ref = pass == 0 ? -m_run : -lse2;
 #pragma unroll
-      for (int c4 = 0; c4 < SC_BN / 32; ++c4) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c4 = 2 * hf + cc;
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * SC_BN + c4 * 32, r);
+        tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + b * SC_BN + c4 * 32, r);
         tmem_ld_wait();
         const int cbase = c0 + c4 * 32;
         if (pass == 0) {
@@ -230,7 +249,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
             float o[OUT];
 #pragma unroll
             for (int i = 0; i < OUT; ++i) {
-              const float n = (float)nsz[c4][i];
+              const float n = (float)nsz[cc][i];
               float sc = __log2f(fmaxf(v[i], 1e-38f)) * LN2;
               if (beta != 0.f) sc -= beta * (__log2f(1.0f + n) * LN2);
               o[i] = n > 0.f ? sc : NEG_BIG;
@@ -439,7 +458,7 @@ int launch_score(const void* vectors, int num_queries, int num_q_heads, const vo
   auto kern = score_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScoreSmem<D>::TOTAL));
   dim3 grid((unsigned)ceil_div(num_queries, QT), num_kv_heads);
-  kern<<<grid, 192, ScoreSmem<D>::TOTAL, st>>>(mq, mc, num_queries, num_clusters, sizes,
+  kern<<<grid, 320, ScoreSmem<D>::TOTAL, st>>>(mq, mc, num_queries, num_clusters, sizes,
                                                LOG2E / temperature, beta, score, num_kv_heads, status);
   SEMBLO_LAUNCH_CHECK();
   return 0;
