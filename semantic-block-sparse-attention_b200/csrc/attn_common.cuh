@@ -1,16 +1,17 @@
 // Softmax / epilogue code shared by the two prefill attention kernels.
 //
-// A tile is 128 rows x 64 keys.  The softmax of a tile is a two-stage pipeline over two
-// warpgroups of 128 threads, one thread per row in each:
-//   mask warps (warps 0-3)  read S from tensor memory, replace the entries the row may not
-//                           attend to by -inf, take the row maximum and write the masked
-//                           logits back over S (kernel-specific code; integer / compare work);
-//   exp warps  (warps 4-7)  read the masked logits, keep the lazily rescaled running maximum
-//                           and the row sum, and write P = exp2(scale * s - m) as bf16 over the
-//                           first 32 columns of the same buffer (exp_tile below; special-
-//                           function-unit work).
+// A tile is 128 rows x 64 keys.  The softmax of a tile is a two-stage pipeline; each stage has
+// two threads per row, one for columns [0, 32) and one for columns [32, 64) (half 0 / half 1):
+//   mask warps (8)  read S from tensor memory, replace the entries the row may not attend to
+//                   by -inf, take the maximum of their half-row and write the masked logits
+//                   back over S (kernel-specific code; integer / compare work);
+//   exp warps  (8)  read the masked logits of their half-row, keep the lazily rescaled running
+//                   maximum (the same in both halves: it is a function of the two half maxima
+//                   the mask warps publish) and their half of the row sum, and write P =
+//                   exp2(scale * s - m) as bf16 over the first 16 columns of their own half
+//                   (exp_tile below; special-function-unit work).
 // The two stages work on consecutive tiles at the same time, on different execution pipes of
-// the same scheduler, and a row never needs a cross-thread reduction.
+// the same schedulers, and no thread waits for another thread of its own stage.
 //
 // Both A operands live in tensor memory, so shared memory holds K / V stages only:
 //   Q  [128 x D]  bf16, two elements per 32-bit column, written once per CTA (stage_q_half);
@@ -65,18 +66,19 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
 // What the mask warps hand to the exp warps for tile j (slot j & 1), besides the masked logits
 // in tensor memory.
 struct TileNote {
-  float row_max[128];    // maximum of the row's masked raw logits (-inf: nothing to attend to)
+  float row_max[256];    // [half][row]: maximum of the half-row's masked raw logits (-inf: nothing to attend to)
   int pages;             // 16-key groups in the tile; 0 = end of the stream
   int pad[3];
 };
 
-// The exp stage of one tile for one row.  The masked raw logits are in TMEM columns
-// [s_col, s_col + 16 pages); P goes to columns [s_col, s_col + 8 pages).  Returns false after
-// a wait timed out.
+// The exp stage of one tile for one half-row (hf: columns [32 hf, 32 hf + 32) of the tile, and
+// columns [hf D/2, (hf + 1) D/2) of O when the accumulator has to be rescaled).  The masked raw
+// logits are in TMEM columns [s_col, s_col + 16 pages); P goes over the first 16 columns of each half.
+// tmax_raw: the larger of the two half maxima.  Returns false after a wait timed out.
 template <int D, int O_COL>
-__device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint32_t lane_addr,
+__device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int hf, uint32_t lane_addr,
                                          uint32_t tmem_base, uint32_t s_col, uint32_t bar_pvdone_prev,
-                                         uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_run,
+                                         uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
                                          volatile int* abort_flag, int* status) {
   const float tmax = tmax_raw * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
@@ -85,7 +87,7 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint3
   if (need) {
     alpha = fast_exp2(m_ref - tmax);
     m_ref = tmax;
-    l_run *= alpha;
+    l_part *= alpha;
   } else if (m_ref == -INFINITY) {
     m_ref = tmax;
   }
@@ -94,9 +96,9 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint3
     if (!mbar_wait(bar_pvdone_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
     tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
       uint32_t o[32];
-      const uint32_t addr = tmem_base + lane_addr + O_COL + c * 32;
+      const uint32_t addr = tmem_base + lane_addr + O_COL + hf * (D / 2) + c * 32;
       tmem_ld32(addr, o);
       tmem_ld_wait();
 #pragma unroll
@@ -104,13 +106,12 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint3
       tmem_st32(addr, o);
     }
   }
-  const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-  uint32_t plo[16], phi[16];
-  float add0 = 0.f, add1 = 0.f;
-  auto half = [&](int h, uint32_t (&packed)[16]) {
-    uint32_t x[32];
-    tmem_ld32(tmem_base + lane_addr + s_col + h * 32, x);
+  if (pages > 2 * hf) {
+    const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+    uint32_t x[32], packed[16];
+    tmem_ld32(tmem_base + lane_addr + s_col + hf * 32, x);
     tmem_ld_wait();
+    float add0 = 0.f, add1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float e0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), scale_log2, neg_m));
@@ -119,40 +120,33 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, uint3
       packed[i] = *reinterpret_cast<uint32_t*>(&pr);
       if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
     }
-  };
-  half(0, plo);
-  if (pages > 2) half(1, phi);
-  l_run += add0 + add1;
-  // keys 2 i, 2 i + 1 of the row share column i of the P operand; every load of the masked
-  // logits has completed, so P may overwrite them
-  tmem_st16(tmem_base + lane_addr + s_col, plo);
-  if (pages > 2) tmem_st16(tmem_base + lane_addr + s_col + 16, phi);
+    l_part += add0 + add1;
+    // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
+    // half's own logits only, so nothing the other half still has to read is overwritten.  The
+    // P V product takes its 16-key operand slices from columns 0, 8, 32 and 40 of the buffer.
+    tmem_st16(tmem_base + lane_addr + s_col + hf * 32, packed);
+  }
   tmem_st_wait();
   tc_fence_before();
   mbar_arrive(bar_pfull_b);
   return true;
 }
 
-// Final write of D/2 output columns by each of the two threads of a row (hf 0: the mask
-// thread, hf 1: the exp thread, which owns the row's running maximum and sum and passes them
-// through xchg).  merge != 0: another partial (normalised output in prev_f32, or in `dst` as
-// bf16 when prev_f32 is null; natural-log LSE in lse_ptr) is LSE-merged with this one.
-// out_f32 != null: the result is written there in fp32 instead of `dst` (a partial that a
-// later launch merges without an intermediate bf16 rounding).
+// Final write of D/2 output columns by each of the two exp threads of a row (they hold the same
+// running maximum and one half of the row sum each, exchanged through xchg).  merge != 0: another
+// partial (normalised output in prev_f32, or in `dst` as bf16 when prev_f32 is null; natural-log
+// LSE in lse_ptr) is LSE-merged with this one.  out_f32 != null: the result is written there in
+// fp32 instead of `dst` (a partial that a later launch merges without an intermediate bf16 rounding).
 template <int D, int O_COL>
 __device__ __forceinline__ void epilogue_half(bool have_tiles, int hf, int row, uint32_t lane_addr,
                                               uint32_t tmem_base, float* xchg /* [2][128] */, uint32_t bar_epi,
-                                              float m_ref_own, float l_own, bool qvalid, int merge,
+                                              float m_ref, float l_part, bool qvalid, int merge,
                                               __nv_bfloat16* dst /* row base */, const float* prev_f32,
                                               float* out_f32, float* lse_ptr /* this row's slot or null */,
                                               volatile int* abort_flag, int* status) {
-  if (hf == 1) {
-    xchg[row] = l_own;
-    xchg[128 + row] = m_ref_own;
-  }
+  xchg[hf * 128 + row] = l_part;
   if (!softmax_group_sync(bar_epi, 0, abort_flag, status)) return;
-  const float l_run = xchg[row];
-  const float m_ref = xchg[128 + row];
+  const float l_run = l_part + xchg[(hf ^ 1) * 128 + row];
   constexpr float own = 1.f;
   float wa = 0.f, wb = 1.f, denom = l_run, m_new = m_ref;
   if (merge && qvalid) {

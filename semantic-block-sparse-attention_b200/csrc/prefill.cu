@@ -79,7 +79,7 @@ struct PrefillArgs {
 enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XFULL = 8, B_EPI = 10, B_KVFULL = 11 };
 
 template <int D, int G>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
 window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
                       const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
   using C = AttnCfg<D>;
@@ -109,13 +109,13 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_XFULL + b), 128);
-      mbar_init(bar(B_PFULL + b), 128);
+      mbar_init(bar(B_XFULL + b), 256);
+      mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 5);     // four mask warps + the UMMA commit
+      mbar_init(bar(B_KVEMPTY + s), 9);     // eight mask warps + the UMMA commit
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -129,7 +129,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------ producer
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
@@ -168,7 +168,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ------------------------------------------------------------ UMMA issuer
     // S(j) = Q K(j)^T goes out as soon as K(j) has landed and P V(j-2), which reads the same
     // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
@@ -213,7 +213,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
             const int np = np_of[t & 3];
             const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
             for (int kk = 0; kk < np; ++kk)
-              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + kk * 8,
+              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
                       make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
                       (t > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar(B_KVEMPTY + s));
@@ -235,8 +235,10 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-3: mask stage, warps 4-7: exp stage; thread = row in both
-    const int stage = warp >> 2;
+    // warps 0-7: mask stage, warps 8-15: exp stage; in both, warps 0-3 of the stage take columns
+    // [0, 32) of every tile and warps 4-7 columns [32, 64); thread = row
+    const int stage = warp >> 3;
+    const int hf = (warp >> 2) & 1;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
@@ -245,13 +247,13 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     const int qpos = qvalid ? a.q_positions[qi] : -1;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
-    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + stage * (D / 2) : nullptr, stage, lane_addr, tmem_base,
-                                    bar(B_QFULL));
-    float m_ref = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_part = 0.f;
     unsigned long long att = 0;
     bool ok = true;
     int j = 0;
     if (stage == 0) {
+      attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+                                      bar(B_QFULL));
       for (;; ++j) {
         const int s = j % STAGES, b = j & 1;
         ok = mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
@@ -270,36 +272,33 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
         tc_fence_after();
-        // keys at or before the row's position; halves wholly below the diagonal for every row
-        // of the warp need no mask and are left as they are
+        // keys at or before the row's position; a half wholly below the diagonal for every row of
+        // the warp needs no mask and is left as it is
         const int lim = min(rows, qpos - kpos0 + 1);
         float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four short chains
+        if (2 * hf < np) {
+          uint32_t r[32];
+          const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hf * 32;
+          tmem_ld32(addr, r);
+          tmem_ld_wait();
+          if (__all_sync(0xffffffffu, lim >= 32 * hf + 32)) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          if (2 * hh < np) {
-            uint32_t r[32];
-            const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hh * 32;
-            tmem_ld32(addr, r);
-            tmem_ld_wait();
-            if (__all_sync(0xffffffffu, lim >= 32 * hh + 32)) {
+            for (int col = 0; col < 32; col += 2)
+              tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], __uint_as_float(r[col]), __uint_as_float(r[col + 1]));
+          } else {
 #pragma unroll
-              for (int col = 0; col < 32; col += 2)
-                tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], __uint_as_float(r[col]), __uint_as_float(r[col + 1]));
-            } else {
-#pragma unroll
-              for (int col = 0; col < 32; col += 2) {
-                const float s0 = 32 * hh + col < lim ? __uint_as_float(r[col]) : -INFINITY;
-                const float s1 = 32 * hh + col + 1 < lim ? __uint_as_float(r[col + 1]) : -INFINITY;
-                r[col] = __float_as_uint(s0);
-                r[col + 1] = __float_as_uint(s1);
-                tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], s0, s1);
-              }
-              tmem_st32(addr, r);
+            for (int col = 0; col < 32; col += 2) {
+              const float s0 = 32 * hf + col < lim ? __uint_as_float(r[col]) : -INFINITY;
+              const float s1 = 32 * hf + col + 1 < lim ? __uint_as_float(r[col + 1]) : -INFINITY;
+              r[col] = __float_as_uint(s0);
+              r[col + 1] = __float_as_uint(s1);
+              tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], s0, s1);
             }
+            tmem_st32(addr, r);
           }
         }
-        if (t == 0) att += max(lim, 0);
-        note[b].row_max[row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+        if (t == 0 && hf == 0) att += max(lim, 0);
+        note[b].row_max[hf * 128 + row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
         if (threadIdx.x == 0) note[b].pages = np;
         tmem_st_wait();
         tc_fence_before();
@@ -313,19 +312,21 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         const int np = note[b].pages;
         if (np == 0) break;
         tc_fence_after();
-        ok = attn::exp_tile<D, C::O_COL>(np, note[b].row_max[row], j, lane_addr, tmem_base, b * BLOCK_N,
-                                         bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_run,
-                                         abort_flag, a.status);
+        ok = attn::exp_tile<D, C::O_COL>(np, fmaxf(note[b].row_max[row], note[b].row_max[128 + row]), j, hf, lane_addr,
+                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b),
+                                         a.scale_log2, m_ref, l_part, abort_flag, a.status);
         if (!ok) break;
       }
     }
+    if (stage == 1) {
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    attn::epilogue_half<D, C::O_COL>(ok && j > 0, stage, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_run,
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
                                      ok && qvalid, 0, a.out + hidx * D, nullptr,
                                      a.partial ? a.partial + hidx * D : nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);
+    }
     if (ok && a.attended) {
       if (!qvalid) att = 0;
 #pragma unroll
@@ -355,7 +356,7 @@ int launch_prefill(const void* ordered_k, const void* ordered_v, int64_t ordered
   auto kern = window_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 320, C::TOTAL, st>>>(mok, mov, a);
+  kern<<<grid, 576, C::TOTAL, st>>>(mok, mov, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

@@ -3,18 +3,18 @@
 //
 // One CTA owns QT = 128 / G queries of one KV head, taken in the caller's tile order
 // (queries with similar selections are placed in the same tile).  Warp roles:
-//   warps 0-3  mask stage of the softmax: per row, keep the logits of the keys whose cluster
-//              the row's query selected, take the row maximum
-//   warps 4-7  exp stage of the softmax: running maximum and sum, P as bf16 into TMEM; both
-//              stages write the output in the epilogue
-//   warp  8    planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
+//   warps 0-7  mask stage of the softmax (two threads per row, 32 columns each): keep the
+//              logits of the keys whose cluster the row's query selected, take the maximum
+//   warps 8-15 exp stage of the softmax (two threads per row): running maximum and sum, P as
+//              bf16 into TMEM; they also write the output in the epilogue
+//   warp  16   planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
 //              starts fetched by 32 lanes in parallel), and expands the union of selected
 //              clusters into a stream of packed rows, each tagged with the 32-bit set of
 //              queries that selected its cluster; 64 rows make a tile
-//   warps 9-12 gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
+//   warps 17-20 gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
 //              cp.async into the 128-byte-swizzled UMMA layout (only visible rows are
 //              read: no page padding), then published to the async proxy
-//   warp  13   UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
+//   warp  21   UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
 //              whichever order their operands become ready
 // The epilogue merges the sparse partial with the window partial already stored in
 // `out` / `lse` by the dense launch, so each query sees one softmax over the union.
@@ -112,7 +112,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(704, 1)
 sparse_gather_prefill_kernel(const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
@@ -144,8 +144,8 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     mbar_init(bar(B_EPI), 256);
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_XFULL + b), 128);
-      mbar_init(bar(B_PFULL + b), 128);
+      mbar_init(bar(B_XFULL + b), 256);
+      mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
@@ -156,7 +156,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 7);     // a K and a V gather warp, the UMMA thread, four mask warps
+      mbar_init(bar(B_PLANEMPTY + s), 11);    // a K and a V gather warp, the UMMA thread, eight mask warps
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -170,7 +170,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------ planner
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
@@ -305,12 +305,12 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       acquire_to(pub + 1);
       if (ok) publish_to(pub + 1, 0);
     }
-  } else if (warp >= 9 && warp <= 12) {
+  } else if (warp >= 17 && warp <= 20) {
     // ------------------------------------------------------------ gather warps
     // warps 9/10 copy the K rows of even/odd tiles, warps 11/12 the V rows: consecutive tiles
     // are in flight in different warps, so a tile's latency hides behind its neighbours'.
-    const bool is_v = warp >= 11;
-    const int par = (warp - 9) & 1;
+    const bool is_v = warp >= 19;
+    const int par = (warp - 17) & 1;
     const __nv_bfloat16* src_base = is_v ? a.packed_v : a.packed_k;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
     const int64_t row_elems = (int64_t)a.num_kv_heads * D;
@@ -368,7 +368,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       TR(4)
     }
     TR_FLUSH(is_v ? 2 : 1)
-  } else if (warp == 13) {
+  } else if (warp == 21) {
     // ------------------------------------------------------------ UMMA issuer
     // S(j) = Q K(j)^T is issued as soon as K(j) has landed and P V(j-2), which reads the same
     // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
@@ -422,7 +422,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
             const int np = np_of[t & 3];
             const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
             for (int kk = 0; kk < np; ++kk)
-              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + kk * 8,
+              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
                       make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
                       (t > 0 || kk > 0) ? 1u : 0u);
             umma_commit(bar(B_VEMPTY + s));
@@ -448,8 +448,10 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-3: mask stage, warps 4-7: exp stage; thread = row in both
-    const int stage = warp >> 2;
+    // warps 0-7: mask stage, warps 8-15: exp stage; in both, warps 0-3 of the stage take columns
+    // [0, 32) of every tile and warps 4-7 columns [32, 64); thread = row
+    const int stage = warp >> 3;
+    const int hf = (warp >> 2) & 1;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
     const int slot = q_tile0 + qslot;
@@ -458,13 +460,13 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t qbit = 1u << qslot;
     const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
-    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + stage * (D / 2) : nullptr, stage, lane_addr, tmem_base,
-                                    bar(B_QFULL));
-    float m_ref = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY, l_part = 0.f;
     bool ok = true;
     int j = 0;
     TR_DECL
     if (stage == 0) {
+      attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+                                      bar(B_QFULL));
       for (;; ++j) {
         const int ps = j % PLAN_STAGES, b = j & 1;
         TR(5)
@@ -482,43 +484,41 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
           break;
         }
         const int np = (cnt + 15) >> 4;
+        // the masks of this half are fetched while the accumulator is awaited
+        const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hf * 32);
+        uint4 m4[8];
+#pragma unroll
+        for (int g4 = 0; g4 < 8; ++g4) m4[g4] = mk[g4];
         ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
         TR(1)
         if (threadIdx.x == 0) { EV(7, j) }
         tc_fence_after();
         // a key counts for this row only if the row's query selected the key's cluster
+        // (keys past the tile's last row carry an empty mask: the planner clears them)
         float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
+        if (2 * hf < np) {
+          uint32_t r[32];
+          const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hf * 32;
+          tmem_ld32(addr, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          if (2 * hh < np) {
-            uint32_t r[32];
-            const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hh * 32;
-            tmem_ld32(addr, r);
-            const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hh * 32);
-            uint4 m4[8];
+          for (int g4 = 0; g4 < 8; ++g4) {
+            const uint32_t mm[4] = {m4[g4].x, m4[g4].y, m4[g4].z, m4[g4].w};
+            float sv[4];
 #pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) m4[g4] = mk[g4];
-            tmem_ld_wait();
-            // (keys past the tile's last row carry an empty mask: the planner clears them)
-#pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) {
-              const uint32_t mm[4] = {m4[g4].x, m4[g4].y, m4[g4].z, m4[g4].w};
-              float sv[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                sv[e] = (mm[e] & qbit) != 0u ? __uint_as_float(r[g4 * 4 + e]) : -INFINITY;
-                r[g4 * 4 + e] = __float_as_uint(sv[e]);
-              }
-              tm[g4 & 1] = fmax3(tm[g4 & 1], sv[0], sv[1]);
-              tm[2 + (g4 & 1)] = fmax3(tm[2 + (g4 & 1)], sv[2], sv[3]);
+            for (int e = 0; e < 4; ++e) {
+              sv[e] = (mm[e] & qbit) != 0u ? __uint_as_float(r[g4 * 4 + e]) : -INFINITY;
+              r[g4 * 4 + e] = __float_as_uint(sv[e]);
             }
-            tmem_st32(addr, r);
+            tm[g4 & 1] = fmax3(tm[g4 & 1], sv[0], sv[1]);
+            tm[2 + (g4 & 1)] = fmax3(tm[2 + (g4 & 1)], sv[2], sv[3]);
           }
+          tmem_st32(addr, r);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-        note[b].row_max[row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+        note[b].row_max[hf * 128 + row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
         if (threadIdx.x == 0) note[b].pages = np;
         tmem_st_wait();
         tc_fence_before();
@@ -536,11 +536,11 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
         const int np = note[b].pages;
         if (np == 0) break;
         tc_fence_after();
-        ok = attn::exp_tile<D, C::O_COL>(np, note[b].row_max[row], j, lane_addr, tmem_base, b * BLOCK_N,
-                                         bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b), a.scale_log2, m_ref, l_run,
-                                         abort_flag, a.status);
+        ok = attn::exp_tile<D, C::O_COL>(np, fmaxf(note[b].row_max[row], note[b].row_max[128 + row]), j, hf, lane_addr,
+                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b),
+                                         a.scale_log2, m_ref, l_part, abort_flag, a.status);
         if (!ok) break;
-        if (lane == 0) { EV(warp == 4 ? 8 : 8 + warp - 1, j) }
+        if (lane == 0) { EV(warp == 8 ? 8 : 8 + (warp & 3), j) }
         TR(4)
       }
     }
@@ -548,15 +548,17 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
 #define SEMBLO_TRACE_WARP 0
 #endif
     if (warp == SEMBLO_TRACE_WARP) { TR_FLUSH(4) }
-    if (warp == SEMBLO_TRACE_WARP + 4) { TR_FLUSH(5) }
+    if (warp == SEMBLO_TRACE_WARP + 8) { TR_FLUSH(5) }
 
-    if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
-    tc_fence_after();
-    attn::epilogue_half<D, C::O_COL>(ok && j > 0, stage, row, lane_addr, tmem_base,
-                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_run,
-                                     ok && qvalid, a.merge, a.out + hidx * D,
-                                     a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
-                                     abort_flag, a.status);
+    if (stage == 1) {
+      if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
+      tc_fence_after();
+      attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
+                                       reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
+                                       ok && qvalid, a.merge, a.out + hidx * D,
+                                       a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
+                                       abort_flag, a.status);
+    }
     tc_fence_before();
   }
   __syncthreads();
@@ -571,7 +573,7 @@ int launch_gather(const GatherArgs& a, cudaStream_t st) {
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 448, C::TOTAL, st>>>(a);
+  kern<<<grid, 704, C::TOTAL, st>>>(a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
