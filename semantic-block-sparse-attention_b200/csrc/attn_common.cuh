@@ -106,7 +106,11 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int h
       tmem_st32(addr, o);
     }
   }
+#ifdef SEMBLO_SKIP_SOFTMAX
+  if (false) {
+#else
   if (pages > 2 * hf) {
+#endif
     const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
     uint32_t x[32], packed[16];
     tmem_ld32(tmem_base + lane_addr + s_col + hf * 32, x);
