@@ -1,4 +1,4 @@
-"""BASELINE.json's full sizes through properties that do not depend on the size: sampled
+"""The benchmark configurations' full sizes through properties that do not depend on the size: sampled
 queries of the 131072-token prefill against the oracle's per-query gather on the kernel's own
 selection, determinism of a whole step, and the store invariants of the 262144-token
 token-order streamed prefill (every key sits where the inverse map says, in position order
