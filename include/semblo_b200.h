@@ -211,7 +211,7 @@ int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int n
 /* The sparse part of semblo/vllm_plugin/kv_outer.py:482-816 with row-granular reads: for every
  * query, attention over rows [indptr[c], indptr[c] + causal_sizes[c]) of the clusters set in
  * its qmask, gathered row by row from the cluster-ordered K/V (packed_k / packed_v
- * [rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
+ * [packed_rows, Hkv, D]; page_table optional).  Tiles of 128 / G queries are formed in q_order
  * ([Hkv, Q], optional).  merge = 1: partial_in (fp32; or `out` as bf16 when partial_in is
  * NULL) and `lse` hold the window partial written by semblo_window_prefill (normalised
  * output, natural-log LSE); `out` / `lse` receive the LSE-merged
@@ -220,7 +220,7 @@ int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int n
  * gathered summed over tiles (the union each tile actually reads). */
 int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
                                  int head_dim, const int32_t* q_order, const void* packed_k,
-                                 const void* packed_v, const int32_t* page_table,
+                                 const void* packed_v, int64_t packed_rows, const int32_t* page_table,
                                  const int32_t* qmask, const int32_t* causal_sizes,
                                  const int32_t* indptr, int num_clusters, float sm_scale, int merge,
                                  const float* partial_in, void* out, float* lse,

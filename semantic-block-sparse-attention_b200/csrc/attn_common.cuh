@@ -37,8 +37,8 @@ __device__ __forceinline__ bool softmax_group_sync(uint32_t bar, uint32_t parity
   return mbar_wait(bar, parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX);
 }
 
-// Copies this thread's half of its query row (D/2 bf16 from qrow_half, or zeros when null) into
-// the Q operand columns and arrives on bar_qfull (count: all softmax threads).
+// Copies this thread's half of the first D dims of its query row (D/2 bf16 from qrow_half, or
+// zeros when null) into the Q operand columns and arrives on bar_qfull (count: the mask threads).
 template <int D, int Q_COL>
 __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int hf, uint32_t lane_addr,
                                              uint32_t tmem_base, uint32_t bar_qfull) {
@@ -63,7 +63,7 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
   mbar_arrive(bar_qfull);
 }
 
-// What the mask warps hand to the exp warps for tile j (slot j & 1), besides the masked logits
+// What the mask warps hand to the exp warps for a tile (one slot per S buffer), besides the masked logits
 // in tensor memory.
 struct TileNote {
   float row_max[256];    // [half][row]: maximum of the half-row's masked raw logits (-inf: nothing to attend to)
@@ -78,7 +78,8 @@ struct TileNote {
 template <int D, int O_COL>
 __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int hf, uint32_t lane_addr,
                                          uint32_t tmem_base, uint32_t s_col, uint32_t bar_pvdone_prev,
-                                         uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
+                                         uint32_t pvdone_prev_parity, uint32_t bar_pfull_b, float scale_log2,
+                                         float& m_ref, float& l_part,
                                          volatile int* abort_flag, int* status) {
   const float tmax = tmax_raw * scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
@@ -93,7 +94,7 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int h
   }
   if (__any_sync(0xffffffffu, need)) {
     // O must be quiescent: the previous tile's P V has to be complete
-    if (!mbar_wait(bar_pvdone_prev, ((j - 1) >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+    if (!mbar_wait(bar_pvdone_prev, pvdone_prev_parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
     tc_fence_after();
 #pragma unroll 1
     for (int c = 0; c < D / 64; ++c) {

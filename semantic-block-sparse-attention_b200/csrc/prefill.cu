@@ -313,7 +313,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         if (np == 0) break;
         tc_fence_after();
         ok = attn::exp_tile<D, C::O_COL>(np, fmaxf(note[b].row_max[row], note[b].row_max[128 + row]), j, hf, lane_addr,
-                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b),
+                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, bar(B_PFULL + b),
                                          a.scale_log2, m_ref, l_part, abort_flag, a.status);
         if (!ok) break;
       }

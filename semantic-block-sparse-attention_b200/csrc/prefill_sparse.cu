@@ -48,24 +48,44 @@ struct Plan {
 };
 static_assert((PLAN_STAGES & (PLAN_STAGES - 1)) == 0, "the ring index is a mask");
 
+constexpr int NSB = 3;                 // S buffers: tiles between Q K^T and the end of their softmax
+constexpr int BIAS_BYTES = BLOCK_N * 64;     // per tile: 64 keys x 32 query slots, bf16
+constexpr uint32_t BIAS_OFF_BITS = 0xF180u;  // bf16 -2^100: the logit of a key the row's query did not select
+
+// The selection enters the logits through the tensor cores: S = [Q | E] [K | B]^T, where row
+// r of E is the one-hot vector of the row's query slot (32 slots) and B[key][slot] is 0 if
+// the slot's query selected the key's cluster and -2^100 otherwise.  Adding 0 leaves a
+// selected logit bit-exact; a rejected one becomes about -2^100, whose exponential is 0.
+//
+// At D = 256 tensor memory holds three S buffers (192 columns), O (256) and the first 128 dims
+// of Q (64); the other 128 dims of Q are a shared-memory operand.  At D = 128 all of Q fits.
 template <int D>
 struct GatherCfg {
-  static constexpr int STAGES = D >= 256 ? 3 : 6;
+  static constexpr int K_STAGES = D >= 256 ? 3 : 5;
+  static constexpr int V_STAGES = D >= 256 ? 2 : 5;
+  static constexpr int Q_TMEM_DIMS = D >= 256 ? 128 : D;
+  static constexpr int Q_SMEM_DIMS = D - Q_TMEM_DIMS;
   static constexpr int SLABS = D / 64;
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
-  static constexpr int K_OFF = 0;
-  static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
-  static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;     // float [2][128]
+  static constexpr int QHI_BYTES = 128 * Q_SMEM_DIMS * 2;
+  static constexpr int QHI_OFF = 0;
+  static constexpr int K_OFF = QHI_OFF + QHI_BYTES;
+  static constexpr int V_OFF = K_OFF + K_STAGES * KV_BYTES;
+  static constexpr int ONEHOT_OFF = V_OFF + V_STAGES * KV_BYTES;   // E: 128 rows x 64 bytes, 64-byte swizzle
+  static constexpr int BIAS_OFF = ONEHOT_OFF + 128 * 64;           // B: one tile per K stage
+  static constexpr int LUT_OFF = BIAS_OFF + K_STAGES * BIAS_BYTES; // uint4 [256]: 8 selection bits -> 8 bf16
+  static constexpr int EPI_OFF = LUT_OFF + 4096;                   // float [2][128]
   static constexpr int PLAN_OFF = EPI_OFF + 2048;
-  static constexpr int NOTE_OFF = PLAN_OFF + (int)sizeof(Plan);   // attn::TileNote [2]
-  static constexpr int BAR_OFF = NOTE_OFF + 2 * (int)sizeof(attn::TileNote);
-  static constexpr int MISC_OFF = BAR_OFF + 8 * (11 + 4 * STAGES + 2 * PLAN_STAGES);
-  static constexpr int TOTAL = MISC_OFF + 16;      // the dynamic segment must start 1024-byte aligned
+  static constexpr int BAR_OFF = PLAN_OFF + (int)sizeof(Plan);
+  static constexpr int NUM_BARS = 8 + 3 * NSB + 2 * K_STAGES + 2 * V_STAGES + 2 * PLAN_STAGES;
+  static constexpr int MISC_OFF = BAR_OFF + 8 * NUM_BARS;          // tmem slot, abort flag, pages [NSB]
+  static constexpr int TOTAL = MISC_OFF + 32;      // the dynamic segment must start 1024-byte aligned
   static constexpr int TMEM_COLS = 512;
-  static constexpr int O_COL = 2 * BLOCK_N;        // S/P buffers, then O, then Q
+  static constexpr int O_COL = NSB * BLOCK_N;      // S/P buffers, then O, then Q
   static constexpr int Q_COL = O_COL + D;
-  static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory budget");
+  static_assert(Q_COL + Q_TMEM_DIMS / 2 <= TMEM_COLS, "tensor memory budget");
   static_assert(TOTAL <= 232448, "shared memory budget");
+  static_assert(ONEHOT_OFF % 1024 == 0, "swizzled operands start on the swizzle period");
 };
 
 struct GatherArgs {
@@ -78,6 +98,7 @@ struct GatherArgs {
   const int32_t* page_table;    // or null
   const __nv_bfloat16* packed_k;
   const __nv_bfloat16* packed_v;
+  int64_t packed_rows;          // rows of the pools
   float scale_log2;
   __nv_bfloat16* out;           // [Q, Hq, D] in: window partial, out: merged
   float* lse;                   // [Q, Hq]    in: window lse,     out: merged (natural log)
@@ -102,7 +123,24 @@ struct GatherArgs {
 #define EV(e, T)
 #endif
 
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XFULL = 8, B_EPI = 10, B_KFULL = 11 };
+enum { B_QFULL = 0, B_OREADY = 1, B_EPI = 2, B_QHI = 3, B_PAIR = 4, B_SFULL = 8, B_PFULL = 8 + NSB,
+       B_PVDONE = 8 + 2 * NSB, B_KFULL = 8 + 3 * NSB };
+
+// Shared-memory descriptor of a K-major operand whose rows are 64 bytes (64-byte swizzle,
+// eight-row groups 512 bytes apart).
+__device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= 1ull << 46;            // descriptor version (Blackwell)
+  d |= 4ull << 61;            // SWIZZLE_64B
+  return d;
+}
+// Byte offset of 16-byte chunk c of row r in such an operand.
+__device__ __forceinline__ uint32_t sw64_off(int r, int c) {
+  return (uint32_t)((r >> 3) * 512 + (r & 7) * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -112,15 +150,15 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(704, 1)
-sparse_gather_prefill_kernel(const GatherArgs a) {
+__global__ void __launch_bounds__(512, 1)
+sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
-  constexpr int STAGES = C::STAGES;
-  constexpr int B_KEMPTY = B_KFULL + STAGES;
-  constexpr int B_VFULL = B_KEMPTY + STAGES;
-  constexpr int B_VEMPTY = B_VFULL + STAGES;
-  constexpr int B_PLANFULL = B_VEMPTY + STAGES;
+  constexpr int K_STAGES = C::K_STAGES, V_STAGES = C::V_STAGES;
+  constexpr int B_KEMPTY = B_KFULL + K_STAGES;
+  constexpr int B_VFULL = B_KEMPTY + K_STAGES;
+  constexpr int B_VEMPTY = B_VFULL + V_STAGES;
+  constexpr int B_PLANFULL = B_VEMPTY + V_STAGES;
   constexpr int B_PLANEMPTY = B_PLANFULL + PLAN_STAGES;
   extern __shared__ __align__(1024) uint8_t smem[];
   if (smem_u32(smem) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
@@ -128,10 +166,10 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  attn::TileNote* note = reinterpret_cast<attn::TileNote*>(smem + C::NOTE_OFF);
   Plan* plan = reinterpret_cast<Plan*>(smem + C::PLAN_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::MISC_OFF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* tile_pages = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [NSB]; 0 ends the stream
   auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -142,21 +180,24 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_XFULL + b), 256);
+    mbar_init(bar(B_QHI), 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 64);   // the two warps that share 32 rows
+    for (int b = 0; b < NSB; ++b) {
+      mbar_init(bar(B_SFULL + b), 2);          // the issuer's own arrival (after the page count) + its commit
       mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
     }
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar(B_KFULL + s), 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(bar(B_KFULL + s), 2);          // the K rows and the tile's selection operand
       mbar_init(bar(B_KEMPTY + s), 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
       mbar_init(bar(B_VFULL + s), 1);
       mbar_init(bar(B_VEMPTY + s), 1);
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 11);    // a K and a V gather warp, the UMMA thread, eight mask warps
+      mbar_init(bar(B_PLANEMPTY + s), 4);     // a K and a V gather warp, the S = Q K^T issuer, the selection warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -165,16 +206,50 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
+  {
+    // table: 8 selection bits -> 8 bf16 (0 where the bit is set); E: one-hot query slot of every row
+    uint4* lut = reinterpret_cast<uint4*>(smem + C::LUT_OFF);
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+      const uint32_t n = ~(uint32_t)i;
+      uint32_t w[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        w[k] = (((n >> (2 * k)) & 1u) | (((n >> (2 * k + 1)) & 1u) << 16)) * BIAS_OFF_BITS;
+      lut[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    for (int i = threadIdx.x; i < 128 * 4; i += blockDim.x) {
+      const int r = i >> 2, c = i & 3, qs = r / G;
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+      if ((qs >> 3) == c) w[(qs & 7) >> 1] = 0x3F80u << (16 * (qs & 1));
+      *reinterpret_cast<uint4*>(smem + C::ONEHOT_OFF + sw64_off(r, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_proxy_async_smem();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 16) {
+  if (warp == 8) {
     // ------------------------------------------------------------ planner
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
     const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
+    if (C::Q_SMEM_DIMS > 0) {
+      // the dims of Q that stay in shared memory: one box (64 dims, G heads) per query and slab
+      const unsigned vmask = __ballot_sync(0xffffffffu, qvalid);
+      if (lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        mbar_arrive_expect_tx(bar(B_QHI), (uint32_t)__popc(vmask) * G * C::Q_SMEM_DIMS * 2);
+      }
+      for (int i = 0; i < QT; ++i) {
+        const int qsrc = __shfl_sync(0xffffffffu, qi, i);
+        if (lane == 0 && ((vmask >> i) & 1))
+          for (int sl = 0; sl < C::Q_SMEM_DIMS / 64; ++sl)
+            tma_load_3d(smem_u32(smem + C::QHI_OFF + sl * 128 * 128 + i * G * 128), &tmap_q, bar(B_QHI),
+                        C::Q_TMEM_DIMS + sl * 64, h * G, qsrc);
+      }
+    }
     const int nwords = a.num_clusters >> 5;
     const int32_t* qm = a.qmask + ((int64_t)qi * a.num_kv_heads + h) * nwords;
     const int32_t* csz = a.causal_sizes + (int64_t)h * a.num_clusters;
@@ -305,14 +380,15 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       acquire_to(pub + 1);
       if (ok) publish_to(pub + 1, 0);
     }
-  } else if (warp >= 17 && warp <= 20) {
+  } else if (warp >= 9 && warp <= 12) {
     // ------------------------------------------------------------ gather warps
     // warps 9/10 copy the K rows of even/odd tiles, warps 11/12 the V rows: consecutive tiles
     // are in flight in different warps, so a tile's latency hides behind its neighbours'.
-    const bool is_v = warp >= 19;
-    const int par = (warp - 17) & 1;
+    const bool is_v = warp >= 11;
+    const int par = (warp - 9) & 1;
     const __nv_bfloat16* src_base = is_v ? a.packed_v : a.packed_k;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
+    const int stages = is_v ? V_STAGES : K_STAGES;
     const int64_t row_elems = (int64_t)a.num_kv_heads * D;
     constexpr int LANES_PER_ROW = D / 8;           // 16-byte chunks per row: 32 (D=256) or 16 (D=128)
     constexpr int ROWS_PER_ITER = 32 / LANES_PER_ROW;
@@ -326,7 +402,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     for (int u = 0; u < GROUP; ++u) dst_off[u] = swz128(u * ROWS_PER_ITER + sub, chunk);
     TR_DECL
     for (int t = par;; t += 2) {
-      const int ps = t % PLAN_STAGES, s = t % STAGES;
+      const int ps = t % PLAN_STAGES, s = t % stages;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(0)
       if (lane == 0) { EV(is_v ? 9 : 1, t) }
@@ -341,7 +417,7 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
         if (lane < n16) r_lo = a.page_table[r_lo >> 4] * 16 + (r_lo & 15);
         if (lane + 32 < n16) r_hi = a.page_table[r_hi >> 4] * 16 + (r_hi & 15);
       }
-      if (!mbar_wait(bar(b_empty + s), ((t / STAGES) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      if (!mbar_wait(bar(b_empty + s), ((t / stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(1)
       if (lane == 0) { EV(is_v ? 10 : 2, t) }
       const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
@@ -368,89 +444,132 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
       TR(4)
     }
     TR_FLUSH(is_v ? 2 : 1)
-  } else if (warp == 21) {
-    // ------------------------------------------------------------ UMMA issuer
-    // S(j) = Q K(j)^T is issued as soon as K(j) has landed and P V(j-2), which reads the same
-    // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
-    // as soon as the softmax warps have stored P(j): whichever is ready first.
+  } else if (warp == 13) {
+    // ------------------------------------------------------------ UMMA issuer of S = [Q | E] [K | B]^T
+    // Two threads issue the UMMAs, one per product, so that the waits and bookkeeping of one
+    // overlap the tensor work of the other.  S(j) goes into buffer j % NSB once P V(j - NSB),
+    // which read P from that buffer, is complete.  The tile's page count travels with the
+    // buffer: it is stored before this thread's own arrival on the buffer's barrier.
     if (elect_one()) {
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+      if (ok && C::Q_SMEM_DIMS > 0) ok = mbar_wait(bar(B_QHI), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       tc_fence_after();
-      int next_qk = 0, next_pv = 0, end_tile = INT_MAX, plan_seen = -1, cnt_cur = 0;
-      int np_of[4] = {0, 0, 0, 0};                    // pages of the tiles in flight (index tile & 3)
-      unsigned long long t0 = globaltimer();
-      uint32_t idle = 0;
+      const uint32_t qhi_base = smem_u32(smem + C::QHI_OFF);
+      const uint32_t onehot_base = smem_u32(smem + C::ONEHOT_OFF);
+      int ps = 0, s = 0, b = 0;                       // ring slots of tile j
+      uint32_t plan_par = 0, k_par = 0, pv_par = 0;   // pv_par: parity of P V(j - NSB), first used at j = NSB
       TR_DECL
-      while (ok) {
-        bool progress = false;
-        if (next_qk < end_tile && next_qk - next_pv < 2) {
-          const int j = next_qk, ps = j % PLAN_STAGES, s = j % STAGES, b = j & 1;
-          if (plan_seen < j && mbar_try_wait_for(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, POLL_NS)) {
-            cnt_cur = plan->count[ps];
-            mbar_arrive(bar(B_PLANEMPTY + ps));
-            plan_seen = j;
-            if (cnt_cur == 0) end_tile = j;
-            progress = true;
-          }
-          if (plan_seen == j && cnt_cur > 0 && mbar_try_wait_for(bar(B_KFULL + s), (j / STAGES) & 1, POLL_NS)) {
-            tc_fence_after();
-            TR(1)
-            const int np = (cnt_cur + 15) >> 4;
-            np_of[j & 3] = np;
-            const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-            const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
+      for (int j = 0; ok; ++j) {
+        ok = mbar_wait(bar(B_PLANFULL + ps), plan_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        const int cnt = plan->count[ps];
+        mbar_arrive(bar(B_PLANEMPTY + ps));
+        if (j >= NSB) ok = mbar_wait(bar(B_PVDONE + b), pv_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        if (cnt == 0) {                               // end of the stream
+          tile_pages[b] = 0;
+          mbar_arrive(bar(B_SFULL + b));
+          mbar_arrive(bar(B_SFULL + b));
+          break;
+        }
+        const int np = (cnt + 15) >> 4;
+        tile_pages[b] = np;
+        mbar_arrive(bar(B_SFULL + b));
+        ok = mbar_wait(bar(B_KFULL + s), k_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        TR(1)
+        EV(12, j)
+        const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
+        const uint32_t bias_base = smem_u32(smem + C::BIAS_OFF + s * BIAS_BYTES);
+        const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-              umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8,
-                      make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
-            }
-            umma_commit(bar(B_KEMPTY + s));
-            umma_commit(bar(B_SFULL + b));
-            TR(2)
-            EV(5, j)
-            ++next_qk;
-            progress = true;
-          }
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+          const uint64_t kd = make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024);
+          if (kk < C::Q_TMEM_DIMS / 16)
+            umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8, kd, idesc_qk, kk > 0 ? 1u : 0u);
+          else                        // the dims of Q that live in shared memory
+            umma_ss(tmem_base + b * BLOCK_N,
+                    make_smem_desc(qhi_base + (sl - C::Q_TMEM_DIMS / 64) * 128 * 128 + ko, 16, 1024), kd, idesc_qk, 1u);
         }
-        if (next_pv < next_qk) {
-          const int t = next_pv, b = t & 1, s = t % STAGES;
-          if (mbar_try_wait_for(bar(B_PFULL + b), (t >> 1) & 1, POLL_NS) && mbar_try_wait_for(bar(B_VFULL + s), (t / STAGES) & 1, POLL_NS)) {
-            tc_fence_after();
-            TR(1)
-            const int np = np_of[t & 3];
-            const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
-            for (int kk = 0; kk < np; ++kk)
-              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
-                      make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
-                      (t > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(bar(B_VEMPTY + s));
-            umma_commit(bar(B_PVDONE + b));
-            TR(3)
-            EV(6, t)
-            ++next_pv;
-            progress = true;
-          }
-        }
-        if (next_pv == end_tile) break;
-        if (progress) { TR(1) } else { TR(0) }
-        if (progress) {
-          idle = 0;
-        } else if ((++idle & 0x3ff) == 0) {
-          if (idle == 0x400) t0 = globaltimer();
-          if (*abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; ok = false; }
-          else if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(a.status, 0, STATUS_TIMEOUT_MMA); ok = false; }
-        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)  // the selection: 32 query slots
+          umma_ss(tmem_base + b * BLOCK_N, make_smem_desc_sw64(onehot_base + kk * 32),
+                  make_smem_desc_sw64(bias_base + kk * 32), idesc_qk, 1u);
+        umma_commit(bar(B_KEMPTY + s));
+        umma_commit(bar(B_SFULL + b));
+        TR(2)
+        EV(5, j)
+        if (++ps == PLAN_STAGES) { ps = 0; plan_par ^= 1; }
+        if (++s == K_STAGES) { s = 0; k_par ^= 1; }
+        if (++b == NSB) { b = 0; if (j >= NSB) pv_par ^= 1; }
       }
-      if (ok) umma_commit(bar(B_OREADY));
       { const int lane = 0; (void)lane; TR_FLUSH(3) }
     }
-  } else {
+  } else if (warp == 14) {
+    // ------------------------------------------------------------ UMMA issuer of O += P V
+    if (elect_one()) {
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
+      bool ok = true;
+      // the page count of tile t comes with P(t) (0 after the last tile): the softmax warps
+      // pass the barrier on
+      int s = 0, b = 0;
+      uint32_t v_par = 0, p_par = 0;
+      for (int t = 0; ok; ++t) {
+        ok = mbar_wait(bar(B_PFULL + b), p_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        const int np = tile_pages[b];
+        if (np == 0) break;
+        ok = mbar_wait(bar(B_VFULL + s), v_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        EV(13, t)
+        const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
+        for (int kk = 0; kk < np; ++kk)
+          umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
+                  make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
+                  (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(B_VEMPTY + s));
+        umma_commit(bar(B_PVDONE + b));
+        EV(6, t)
+        if (++s == V_STAGES) { s = 0; v_par ^= 1; }
+        if (++b == NSB) { b = 0; p_par ^= 1; }
+      }
+      if (ok) umma_commit(bar(B_OREADY));
+    }
+  } else if (warp == 15) {
+    // ------------------------------------------------------------ selection operand B
+    // B[key][slot] of a tile from the planner's per-key slot masks: lane = (key & 7, 8-slot
+    // group), eight keys per pass; one table lookup turns 8 mask bits into 8 bf16.
+    const uint4* lut = reinterpret_cast<const uint4*>(smem + C::LUT_OFF);
+    const int r0 = lane >> 2, c = lane & 3;
+    int ps = 0, s = 0;
+    uint32_t plan_par = 0, empty_par = 1;
+    for (int t = 0;; ++t) {
+      if (!mbar_wait(bar(B_PLANFULL + ps), plan_par, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      if (plan->count[ps] == 0) break;
+      uint32_t m[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) m[it] = plan->mask[ps * BLOCK_N + it * 8 + r0];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
+      if (!mbar_wait(bar(B_KEMPTY + s), empty_par, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
+      uint8_t* dst = smem + C::BIAS_OFF + s * BIAS_BYTES;
+#pragma unroll
+      for (int it = 0; it < 8; ++it)
+        *reinterpret_cast<uint4*>(dst + sw64_off(it * 8 + r0, c)) = lut[(m[it] >> (8 * c)) & 0xFFu];
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_KFULL + s));
+      if (++ps == PLAN_STAGES) { ps = 0; plan_par ^= 1; }
+      if (++s == K_STAGES) { s = 0; empty_par ^= 1; }
+    }
+  } else if (warp < 8) {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-7: mask stage, warps 8-15: exp stage; in both, warps 0-3 of the stage take columns
-    // [0, 32) of every tile and warps 4-7 columns [32, 64); thread = row
-    const int stage = warp >> 3;
+    // Two threads per row: warps 0-3 take columns [0, 32) of every tile, warps 4-7 columns
+    // [32, 64).  Both read all 64 logits for the row maximum, so they agree on it without
+    // talking to each other; each turns its own half into P.
     const int hf = (warp >> 2) & 1;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
@@ -458,107 +577,135 @@ sparse_gather_prefill_kernel(const GatherArgs a) {
     const bool qvalid = slot < a.num_queries;
     const int qi = qvalid ? (a.q_order ? a.q_order[(int64_t)h * a.num_queries + slot] : slot) : 0;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t qbit = 1u << qslot;
     const int64_t hidx = (int64_t)qi * a.num_q_heads + h * G + t;
     float m_ref = -INFINITY, l_part = 0.f;
     bool ok = true;
-    int j = 0;
+    int j = 0, b = 0;
+    uint32_t s_par = 0, pv_prev_par = 0;             // pv_prev_par: parity of P V(j - 1) on its buffer
     TR_DECL
-    if (stage == 0) {
-      attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
-                                      bar(B_QFULL));
-      for (;; ++j) {
-        const int ps = j % PLAN_STAGES, b = j & 1;
-        TR(5)
-        ok = mbar_wait(bar(B_PLANFULL + ps), (j / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        TR(0)
-        const int cnt = plan->count[ps];
-        if (cnt == 0) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-          // end of the stream: the note slot is free once P V of tile j - 2 has been issued
-          if (j >= 2) ok = mbar_wait(bar(B_PVDONE + b), ((j - 2) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-          if (threadIdx.x == 0) note[b].pages = 0;
-          mbar_arrive(bar(B_XFULL + b));
-          break;
-        }
-        const int np = (cnt + 15) >> 4;
-        // the masks of this half are fetched while the accumulator is awaited
-        const uint4* mk = reinterpret_cast<const uint4*>(plan->mask + ps * BLOCK_N + hf * 32);
-        uint4 m4[8];
+    attn::stage_q_half<C::Q_TMEM_DIMS, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (C::Q_TMEM_DIMS / 2) : nullptr, hf,
+                                                 lane_addr, tmem_base, bar(B_QFULL));
+    for (;; ++j) {
+      TR(5)
+      ok = mbar_wait(bar(B_SFULL + b), s_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      TR(1)
+      const int np = tile_pages[b];
+      if (np == 0) {                        // end of the stream: tell the P V issuer
+        mbar_arrive(bar(B_PFULL + b));
+        break;
+      }
+      if (threadIdx.x == 0) { EV(7, j) }
+      tc_fence_after();
+      const uint32_t s_addr = tmem_base + lane_addr + b * BLOCK_N;
+      uint32_t x[32], y[32];
+      tmem_ld32(s_addr + hf * 32, x);
+      tmem_ld32(s_addr + (hf ^ 1) * 32, y);
+      tmem_ld_wait();
+      // the row's other thread writes P over its half of the logits: tell it this thread has
+      // read them (it waits for that just before its store)
+      tc_fence_before();
+      mbar_arrive(bar(B_PAIR + (warp & 3)));
+      // columns past the tile's pages were not written by this tile's product
+      {
+        const int own = np - 2 * hf, oth = np - 2 * (hf ^ 1);      // 16-column groups present in each half
+        if (own < 2) {
 #pragma unroll
-        for (int g4 = 0; g4 < 8; ++g4) m4[g4] = mk[g4];
-        ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+          for (int i = 16; i < 32; ++i) x[i] = 0xff800000u;
+          if (own < 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = 0xff800000u;
+          }
+        }
+        if (oth < 2) {
+#pragma unroll
+          for (int i = 16; i < 32; ++i) y[i] = 0xff800000u;
+          if (oth < 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = 0xff800000u;
+          }
+        }
+      }
+      float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        tm[0] = fmax3(tm[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+        tm[1] = fmax3(tm[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+        tm[2] = fmax3(tm[2], __uint_as_float(y[i]), __uint_as_float(y[i + 1]));
+        tm[3] = fmax3(tm[3], __uint_as_float(y[i + 2]), __uint_as_float(y[i + 3]));
+      }
+      float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+      if (tmax < -1e29f) tmax = -INFINITY;             // nothing selected for this row in the tile
+      tmax *= a.scale_log2;
+      // lazy rescale: only when the running reference falls more than 2^8 behind
+      const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + attn::RESCALE_GAP;
+      float alpha = 1.f;
+      if (need) {
+        alpha = fast_exp2(m_ref - tmax);
+        m_ref = tmax;
+        l_part *= alpha;
+      } else if (m_ref == -INFINITY) {
+        m_ref = tmax;
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        // O must be quiescent: the previous tile's P V has to be complete
+        ok = mbar_wait(bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)), pv_prev_par, abort_flag, a.status,
+                       STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
-        TR(1)
-        if (threadIdx.x == 0) { EV(7, j) }
         tc_fence_after();
-        // a key counts for this row only if the row's query selected the key's cluster
-        // (keys past the tile's last row carry an empty mask: the planner clears them)
-        float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
-        if (2 * hf < np) {
-          uint32_t r[32];
-          const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hf * 32;
-          tmem_ld32(addr, r);
+#pragma unroll 1
+        for (int cc = 0; cc < D / 64; ++cc) {
+          uint32_t o[32];
+          const uint32_t addr = tmem_base + lane_addr + C::O_COL + hf * (D / 2) + cc * 32;
+          tmem_ld32(addr, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int g4 = 0; g4 < 8; ++g4) {
-            const uint32_t mm[4] = {m4[g4].x, m4[g4].y, m4[g4].z, m4[g4].w};
-            float sv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              sv[e] = (mm[e] & qbit) != 0u ? __uint_as_float(r[g4 * 4 + e]) : -INFINITY;
-              r[g4 * 4 + e] = __float_as_uint(sv[e]);
-            }
-            tm[g4 & 1] = fmax3(tm[g4 & 1], sv[0], sv[1]);
-            tm[2 + (g4 & 1)] = fmax3(tm[2 + (g4 & 1)], sv[2], sv[3]);
-          }
-          tmem_st32(addr, r);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(addr, o);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_PLANEMPTY + ps));
-        note[b].row_max[hf * 128 + row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
-        if (threadIdx.x == 0) note[b].pages = np;
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(bar(B_XFULL + b));
-        if (threadIdx.x == 0) { EV(11, j) }
-        TR(2)
       }
-    } else {
-      for (;; ++j) {
-        const int b = j & 1;
-        TR(5)
-        ok = mbar_wait(bar(B_XFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (np > 2 * hf) {
+        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+        uint32_t packed[16];
+        float add0 = 0.f, add1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), a.scale_log2, neg_m));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), a.scale_log2, neg_m));
+          __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
+          packed[i] = *reinterpret_cast<uint32_t*>(&pr);
+          if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
+        }
+        l_part += add0 + add1;
+        ok = mbar_wait(bar(B_PAIR + (warp & 3)), (uint32_t)(j & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
-        TR(1)
-        const int np = note[b].pages;
-        if (np == 0) break;
         tc_fence_after();
-        ok = attn::exp_tile<D, C::O_COL>(np, fmaxf(note[b].row_max[row], note[b].row_max[128 + row]), j, hf, lane_addr,
-                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), bar(B_PFULL + b),
-                                         a.scale_log2, m_ref, l_part, abort_flag, a.status);
-        if (!ok) break;
-        if (lane == 0) { EV(warp == 8 ? 8 : 8 + (warp & 3), j) }
-        TR(4)
+        // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
+        // half's own logits only.  The P V product takes its 16-key operand slices from columns
+        // 0, 8, 32 and 40 of the buffer.
+        tmem_st16(s_addr + hf * 32, packed);
       }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bar(B_PFULL + b));
+      if (lane == 0) { EV(8, j) }
+      TR(4)
+      if (++b == NSB) { b = 0; s_par ^= 1; }
+      // P V(j) of the tile just finished lives on buffer (j % NSB) with parity (j / NSB) & 1
+      pv_prev_par = (uint32_t)((j / NSB) & 1);
     }
 #ifndef SEMBLO_TRACE_WARP
 #define SEMBLO_TRACE_WARP 0
 #endif
     if (warp == SEMBLO_TRACE_WARP) { TR_FLUSH(4) }
-    if (warp == SEMBLO_TRACE_WARP + 8) { TR_FLUSH(5) }
 
-    if (stage == 1) {
-      if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
-      tc_fence_after();
-      attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
-                                       reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
-                                       ok && qvalid, a.merge, a.out + hidx * D,
-                                       a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
-                                       abort_flag, a.status);
-    }
+    if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
+    tc_fence_after();
+    attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
+                                     reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
+                                     ok && qvalid, a.merge, a.out + hidx * D,
+                                     a.partial ? a.partial + hidx * D : nullptr, nullptr, a.lse ? a.lse + hidx : nullptr,
+                                     abort_flag, a.status);
     tc_fence_before();
   }
   __syncthreads();
@@ -570,10 +717,18 @@ template <int D, int G>
 int launch_gather(const GatherArgs& a, cudaStream_t st) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
+  CUtensorMap mq;
+  {
+    uint64_t d[3] = {(uint64_t)D, (uint64_t)a.num_q_heads, (uint64_t)a.num_queries};
+    uint64_t st2[2] = {(uint64_t)D * 2, (uint64_t)a.num_q_heads * D * 2};
+    uint32_t bx[3] = {64, (uint32_t)G, 1};
+    int rc = semblo::make_tensor_map_bf16(&mq, a.q, 3, d, st2, bx);
+    if (rc) return rc;
+  }
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 704, C::TOTAL, st>>>(a);
+  kern<<<grid, 512, C::TOTAL, st>>>(mq, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
@@ -582,7 +737,8 @@ int launch_gather(const GatherArgs& a, cudaStream_t st) {
 
 extern "C" int semblo_sparse_prefill_gather(
     const void* q, int num_queries, int num_q_heads, int num_kv_heads, int head_dim,
-    const int32_t* q_order, const void* packed_k, const void* packed_v, const int32_t* page_table,
+    const int32_t* q_order, const void* packed_k, const void* packed_v, int64_t packed_rows,
+    const int32_t* page_table,
     const int32_t* qmask, const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
     float sm_scale, int merge, const float* partial_in, void* out, float* lse,
     unsigned long long* attended, int32_t* status, void* stream) {
@@ -594,12 +750,14 @@ extern "C" int semblo_sparse_prefill_gather(
   SEMBLO_REQUIRE((reinterpret_cast<uintptr_t>(packed_k) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed_v) & 15) == 0,
                  "packed K/V must be 16-byte aligned");
   SEMBLO_REQUIRE(q != nullptr && (reinterpret_cast<uintptr_t>(q) & 15) == 0, "q must be 16-byte aligned");
+  SEMBLO_REQUIRE(packed_rows > 0 && packed_rows < (int64_t)1 << 31, "packed_rows %lld is out of range", (long long)packed_rows);
   if (num_queries == 0) return 0;
   GatherArgs a;
   a.num_queries = num_queries; a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads;
   a.num_clusters = num_clusters; a.q = (const __nv_bfloat16*)q; a.q_order = q_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
   a.indptr = indptr; a.page_table = page_table;
   a.packed_k = (const __nv_bfloat16*)packed_k; a.packed_v = (const __nv_bfloat16*)packed_v;
+  a.packed_rows = packed_rows;
   a.scale_log2 = sm_scale * LOG2EF; a.out = (__nv_bfloat16*)out; a.lse = lse; a.merge = merge; a.partial = partial_in;
   a.attended = attended; a.status = status;
   const int g = num_q_heads / num_kv_heads;

@@ -119,7 +119,7 @@ def sparse_gather_attention(q: torch.Tensor, *, packed_kv: torch.Tensor, qmask: 
     status = _lib.status_for(q.device)
     check(lib().semblo_sparse_prefill_gather(
         ptr(q), q_count, num_q_heads, int(packed_kv.shape[2]), head_dim, ptr(q_order), ptr(packed_kv[0]),
-        ptr(packed_kv[1]), ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr),
+        ptr(packed_kv[1]), int(packed_kv.shape[1]), ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr),
         int(causal_sizes.shape[1]), float(sm_scale), 1 if merge else 0, ptr(partial), ptr(out), ptr(lse),
         ptr(attended),
         ptr(status.word), stream_ptr()))
