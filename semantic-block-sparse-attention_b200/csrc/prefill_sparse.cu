@@ -48,7 +48,16 @@ struct Plan {
 };
 static_assert((PLAN_STAGES & (PLAN_STAGES - 1)) == 0, "the ring index is a mask");
 
-constexpr int NSB = 3;                 // S buffers: tiles between Q K^T and the end of their softmax
+#ifndef SEMBLO_GATHER_WARPS
+#define SEMBLO_GATHER_WARPS 3
+#endif
+constexpr int GW = SEMBLO_GATHER_WARPS;     // gather warps per operand; warp w of them takes tiles t = w (mod GW)
+constexpr int W_GATHER = 9, W_QK = W_GATHER + 2 * GW, W_PV = W_QK + 1, W_BIAS = W_PV + 1;
+constexpr int GATHER_THREADS = 32 * (W_BIAS + 1);
+#ifndef SEMBLO_NSB
+#define SEMBLO_NSB 2
+#endif
+constexpr int NSB = SEMBLO_NSB;       // S buffers: tiles between Q K^T and the end of their softmax
 constexpr int BIAS_BYTES = BLOCK_N * 64;     // per tile: 64 keys x 32 query slots, bf16
 constexpr uint32_t BIAS_OFF_BITS = 0xF180u;  // bf16 -2^100: the logit of a key the row's query did not select
 
@@ -57,13 +66,14 @@ constexpr uint32_t BIAS_OFF_BITS = 0xF180u;  // bf16 -2^100: the logit of a key 
 // the slot's query selected the key's cluster and -2^100 otherwise.  Adding 0 leaves a
 // selected logit bit-exact; a rejected one becomes about -2^100, whose exponential is 0.
 //
-// At D = 256 tensor memory holds three S buffers (192 columns), O (256) and the first 128 dims
-// of Q (64); the other 128 dims of Q are a shared-memory operand.  At D = 128 all of Q fits.
+// Tensor memory (512 columns) holds NSB S buffers of 64 columns, O (D columns) and Q (D / 2).
+// With two S buffers everything fits at D = 256; a third one (SEMBLO_NSB = 3) moves the last
+// 128 dims of Q into shared memory and leaves room for two V stages only.
 template <int D>
 struct GatherCfg {
   static constexpr int K_STAGES = D >= 256 ? 3 : 5;
-  static constexpr int V_STAGES = D >= 256 ? 2 : 5;
-  static constexpr int Q_TMEM_DIMS = D >= 256 ? 128 : D;
+  static constexpr int V_STAGES = D >= 256 ? (NSB >= 3 ? 2 : 3) : 5;
+  static constexpr int Q_TMEM_DIMS = (D >= 256 && NSB >= 3) ? 128 : D;
   static constexpr int Q_SMEM_DIMS = D - Q_TMEM_DIMS;
   static constexpr int SLABS = D / 64;
   static constexpr int KV_BYTES = BLOCK_N * D * 2;
@@ -85,6 +95,9 @@ struct GatherCfg {
   static constexpr int Q_COL = O_COL + D;
   static_assert(Q_COL + Q_TMEM_DIMS / 2 <= TMEM_COLS, "tensor memory budget");
   static_assert(TOTAL <= 232448, "shared memory budget");
+  // a gather warp waits on a stage by phase parity, which only tells neighbouring phases apart:
+  // no warp may run a whole ring ahead of another
+  static_assert(GW <= K_STAGES && GW <= V_STAGES, "more gather warps than stages");
   static_assert(ONEHOT_OFF % 1024 == 0, "swizzled operands start on the swizzle period");
 };
 
@@ -150,7 +163,7 @@ __device__ __forceinline__ void cp_async_wait_all() {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(GATHER_THREADS, 1)
 sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const GatherArgs a) {
   using C = GatherCfg<D>;
   constexpr int QT = 128 / G;
@@ -375,17 +388,18 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     }
     TR(1)
     TR_FLUSH(0)
-    // end of stream, once per gather warp (they alternate tiles)
-    for (int e = 0; e < 2 && ok; ++e) {
+    // end of stream, once per gather warp of an operand (they take tiles in turn)
+    for (int e = 0; e < GW && ok; ++e) {
       acquire_to(pub + 1);
       if (ok) publish_to(pub + 1, 0);
     }
-  } else if (warp >= 9 && warp <= 12) {
+  } else if (warp >= W_GATHER && warp < W_QK) {
     // ------------------------------------------------------------ gather warps
-    // warps 9/10 copy the K rows of even/odd tiles, warps 11/12 the V rows: consecutive tiles
-    // are in flight in different warps, so a tile's latency hides behind its neighbours'.
-    const bool is_v = warp >= 11;
-    const int par = (warp - 9) & 1;
+    // GW warps copy the K rows and GW warps the V rows, tile t in warp t mod GW of its operand:
+    // consecutive tiles are in flight in different warps, so a tile's latency hides behind its
+    // neighbours'.
+    const bool is_v = warp >= W_GATHER + GW;
+    const int par = (warp - W_GATHER) % GW;
     const __nv_bfloat16* src_base = is_v ? a.packed_v : a.packed_k;
     const int b_full = is_v ? B_VFULL : B_KFULL, b_empty = is_v ? B_VEMPTY : B_KEMPTY;
     const int stages = is_v ? V_STAGES : K_STAGES;
@@ -401,7 +415,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
 #pragma unroll
     for (int u = 0; u < GROUP; ++u) dst_off[u] = swz128(u * ROWS_PER_ITER + sub, chunk);
     TR_DECL
-    for (int t = par;; t += 2) {
+    for (int t = par;; t += GW) {
       const int ps = t % PLAN_STAGES, s = t % stages;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
       TR(0)
@@ -444,7 +458,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       TR(4)
     }
     TR_FLUSH(is_v ? 2 : 1)
-  } else if (warp == 13) {
+  } else if (warp == W_QK) {
     // ------------------------------------------------------------ UMMA issuer of S = [Q | E] [K | B]^T
     // Two threads issue the UMMAs, one per product, so that the waits and bookkeeping of one
     // overlap the tensor work of the other.  S(j) goes into buffer j % NSB once P V(j - NSB),
@@ -507,7 +521,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       }
       { const int lane = 0; (void)lane; TR_FLUSH(3) }
     }
-  } else if (warp == 14) {
+  } else if (warp == W_PV) {
     // ------------------------------------------------------------ UMMA issuer of O += P V
     if (elect_one()) {
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
@@ -538,7 +552,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       }
       if (ok) umma_commit(bar(B_OREADY));
     }
-  } else if (warp == 15) {
+  } else if (warp == W_BIAS) {
     // ------------------------------------------------------------ selection operand B
     // B[key][slot] of a tile from the planner's per-key slot masks: lane = (key & 7, 8-slot
     // group), eight keys per pass; one table lookup turns 8 mask bits into 8 bf16.
@@ -728,7 +742,7 @@ int launch_gather(const GatherArgs& a, cudaStream_t st) {
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 512, C::TOTAL, st>>>(mq, a);
+  kern<<<grid, GATHER_THREADS, C::TOTAL, st>>>(mq, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }
