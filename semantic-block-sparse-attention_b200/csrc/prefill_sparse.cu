@@ -188,6 +188,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
   const int q_tile0 = blockIdx.x * QT;
+  if (threadIdx.x == 0) { EV(14, 0) }
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 256);
@@ -241,6 +242,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0) { EV(14, 1) }
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
@@ -616,6 +618,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       tmem_ld32(s_addr + hf * 32, x);
       tmem_ld32(s_addr + (hf ^ 1) * 32, y);
       tmem_ld_wait();
+      TR(2)
       // the row's other thread writes P over its half of the logits: tell it this thread has
       // read them (it waits for that just before its store)
       tc_fence_before();
@@ -662,6 +665,9 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         m_ref = tmax;
       }
       if (__any_sync(0xffffffffu, need)) {
+#ifdef SEMBLO_TRACE
+        tr[0] += 1000;
+#endif
         // O must be quiescent: the previous tile's P V has to be complete
         ok = mbar_wait(bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)), pv_prev_par, abort_flag, a.status,
                        STATUS_TIMEOUT_SOFTMAX);
@@ -678,6 +684,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           tmem_st32(addr, o);
         }
       }
+      TR(3)
       if (np > 2 * hf) {
         const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
         uint32_t packed[16];
@@ -691,9 +698,11 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
         }
         l_part += add0 + add1;
+        TR(6)
         ok = mbar_wait(bar(B_PAIR + (warp & 3)), (uint32_t)(j & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
         tc_fence_after();
+        TR(7)
         // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
         // half's own logits only.  The P V product takes its 16-key operand slices from columns
         // 0, 8, 32 and 40 of the buffer.
@@ -713,8 +722,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
 #endif
     if (warp == SEMBLO_TRACE_WARP) { TR_FLUSH(4) }
 
+    if (threadIdx.x == 0) { EV(14, 2) }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
+    if (threadIdx.x == 0) { EV(14, 3) }
     attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
                                      reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
                                      ok && qvalid, a.merge, a.out + hidx * D,
@@ -723,6 +734,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     tc_fence_before();
   }
   __syncthreads();
+  if (threadIdx.x == 0) { EV(14, 4) }
   if (*abort_flag) __nanosleep(50000);
   if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
