@@ -291,7 +291,8 @@ def test_dense_causal_attention(dev, dim, hq, hkv):
     _close_attention(got_w, want_w, "window")
 
 
-@pytest.mark.parametrize("dim,hq,hkv,sink,paged", [(256, 8, 2, 64, True), (128, 8, 2, 0, False)])
+@pytest.mark.parametrize("dim,hq,hkv,sink,paged", [(256, 8, 2, 64, True), (128, 8, 2, 0, False),
+                                                   (128, 16, 2, 0, True), (256, 16, 1, 64, False)])
 def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, hq, hkv, sink, paged):
     from semblo_b200.fused_prefill import window_attention
     length, target, local = 6144, 512, 128
@@ -302,6 +303,13 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
     qpos = torch.arange(cs, ce + 1)
     vectors = O.trivial_router_vectors(data["q_pre"][cs:ce + 1])
     sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=0.1, beta=0.25, target_tokens=target, sink=sink)
+    # a few queries with nothing selected on head 0 (the sparse part alone must then give zeros),
+    # and one that selects a single cluster
+    sel[3, 0] = False
+    sel[250, 0] = False
+    sel[499, 0] = False
+    sel[100, 0] = False
+    sel[100, 0, int(sizes[0].argmax())] = True
     sm_scale = dim ** -0.5
     want, natt = O.sparse_chunk_attention(data["q_post"][cs:ce + 1], index, sel, sizes, qpos,
                                           data["k_post"][ws:ce + 1], data["v"][ws:ce + 1], ws, sm_scale)
@@ -344,6 +352,9 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
                             page_table=table)
     _status_ok(dev)
     _close_attention(out3, want_s, "gathered clusters alone")
+    group = hq // hkv
+    for qi in (3, 250, 499):
+        assert float(out3[qi, :group].float().abs().max()) == 0.0, "a query with an empty selection must give zeros"
 
 
 def test_argsort_and_top1_keys(dev):
