@@ -640,6 +640,9 @@ def main():
     d2h = out_host.numel() * out_host.element_size()
     del host, dev_in, dev_sets, out_host
     if rank != 0:
+        import torch.distributed as dist
+        dist.barrier()                                # rank 0 joins it after printing the line
+        dist.destroy_process_group()
         return
     tokens = cfg["length"] * world
     line = {
