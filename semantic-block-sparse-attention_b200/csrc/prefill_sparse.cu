@@ -52,7 +52,7 @@ static_assert((PLAN_STAGES & (PLAN_STAGES - 1)) == 0, "the ring index is a mask"
 #define SEMBLO_GATHER_WARPS 3
 #endif
 constexpr int GW = SEMBLO_GATHER_WARPS;     // gather warps per operand; warp w of them takes tiles t = w (mod GW)
-constexpr int W_GATHER = 9, W_QK = W_GATHER + 2 * GW, W_PV = W_QK + 1, W_BIAS = W_PV + 1;
+constexpr int W_GATHER = 9, W_MMA = W_GATHER + 2 * GW, W_BIAS = W_MMA + 1;
 constexpr int GATHER_THREADS = 32 * (W_BIAS + 1);
 #ifndef SEMBLO_NSB
 #define SEMBLO_NSB 2
@@ -211,7 +211,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     }
     for (int s = 0; s < PLAN_STAGES; ++s) {
       mbar_init(bar(B_PLANFULL + s), 1);
-      mbar_init(bar(B_PLANEMPTY + s), 4);     // a K and a V gather warp, the S = Q K^T issuer, the selection warp
+      mbar_init(bar(B_PLANEMPTY + s), 4);     // a K and a V gather warp, the UMMA issuer, the selection warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -395,7 +395,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       acquire_to(pub + 1);
       if (ok) publish_to(pub + 1, 0);
     }
-  } else if (warp >= W_GATHER && warp < W_QK) {
+  } else if (warp >= W_GATHER && warp < W_MMA) {
     // ------------------------------------------------------------ gather warps
     // GW warps copy the K rows and GW warps the V rows, tile t in warp t mod GW of its operand:
     // consecutive tiles are in flight in different warps, so a tile's latency hides behind its
@@ -460,99 +460,98 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       TR(4)
     }
     TR_FLUSH(is_v ? 2 : 1)
-  } else if (warp == W_QK) {
-    // ------------------------------------------------------------ UMMA issuer of S = [Q | E] [K | B]^T
-    // Two threads issue the UMMAs, one per product, so that the waits and bookkeeping of one
-    // overlap the tensor work of the other.  S(j) goes into buffer j % NSB once P V(j - NSB),
-    // which read P from that buffer, is complete.  The tile's page count travels with the
-    // buffer: it is stored before this thread's own arrival on the buffer's barrier.
+  } else if (warp == W_MMA) {
+    // ------------------------------------------------------------ UMMA issuer
+    // One thread issues S(j) = [Q | E] [K(j) | B(j)]^T and O += P(t) V(t) in the fixed order
+    // S(0) .. S(NSB-1), then P V(t), S(t + NSB) for t = 0, 1, ...  UMMAs of one thread execute in
+    // issue order, so S(t + NSB) may follow P V(t), which reads P from the same buffer, without
+    // waiting for it to complete.  The tile's page count travels with the buffer: it is stored
+    // before this thread's own arrival on the buffer's barrier (0 ends the stream).
     if (elect_one()) {
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       if (ok && C::Q_SMEM_DIMS > 0) ok = mbar_wait(bar(B_QHI), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       tc_fence_after();
       const uint32_t qhi_base = smem_u32(smem + C::QHI_OFF);
       const uint32_t onehot_base = smem_u32(smem + C::ONEHOT_OFF);
-      int ps = 0, s = 0, b = 0;                       // ring slots of tile j
-      uint32_t plan_par = 0, k_par = 0, pv_par = 0;   // pv_par: parity of P V(j - NSB), first used at j = NSB
+      int ps = 0, ks = 0, qb = 0;                     // ring slots of the next S product
+      uint32_t plan_par = 0, k_par = 0;
+      bool ended = false;
       TR_DECL
-      for (int j = 0; ok; ++j) {
+      auto issue_s = [&](int j) {
         ok = mbar_wait(bar(B_PLANFULL + ps), plan_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
-        if (!ok) break;
+        if (!ok) return;
         const int cnt = plan->count[ps];
         mbar_arrive(bar(B_PLANEMPTY + ps));
-        if (j >= NSB) ok = mbar_wait(bar(B_PVDONE + b), pv_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
-        if (!ok) break;
         if (cnt == 0) {                               // end of the stream
-          tile_pages[b] = 0;
-          mbar_arrive(bar(B_SFULL + b));
-          mbar_arrive(bar(B_SFULL + b));
-          break;
+          tile_pages[qb] = 0;
+          mbar_arrive(bar(B_SFULL + qb));
+          mbar_arrive(bar(B_SFULL + qb));
+          ended = true;
+          return;
         }
         const int np = (cnt + 15) >> 4;
-        tile_pages[b] = np;
-        mbar_arrive(bar(B_SFULL + b));
-        ok = mbar_wait(bar(B_KFULL + s), k_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
-        if (!ok) break;
+        tile_pages[qb] = np;
+        mbar_arrive(bar(B_SFULL + qb));
+        ok = mbar_wait(bar(B_KFULL + ks), k_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) return;
         tc_fence_after();
         TR(1)
         EV(12, j)
-        const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-        const uint32_t bias_base = smem_u32(smem + C::BIAS_OFF + s * BIAS_BYTES);
+        const uint32_t k_base = smem_u32(smem + C::K_OFF + ks * C::KV_BYTES);
+        const uint32_t bias_base = smem_u32(smem + C::BIAS_OFF + ks * BIAS_BYTES);
         const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
           const uint64_t kd = make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024);
           if (kk < C::Q_TMEM_DIMS / 16)
-            umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8, kd, idesc_qk, kk > 0 ? 1u : 0u);
+            umma_ts(tmem_base + qb * BLOCK_N, tmem_base + C::Q_COL + kk * 8, kd, idesc_qk, kk > 0 ? 1u : 0u);
           else                        // the dims of Q that live in shared memory
-            umma_ss(tmem_base + b * BLOCK_N,
+            umma_ss(tmem_base + qb * BLOCK_N,
                     make_smem_desc(qhi_base + (sl - C::Q_TMEM_DIMS / 64) * 128 * 128 + ko, 16, 1024), kd, idesc_qk, 1u);
         }
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk)  // the selection: 32 query slots
-          umma_ss(tmem_base + b * BLOCK_N, make_smem_desc_sw64(onehot_base + kk * 32),
+          umma_ss(tmem_base + qb * BLOCK_N, make_smem_desc_sw64(onehot_base + kk * 32),
                   make_smem_desc_sw64(bias_base + kk * 32), idesc_qk, 1u);
-        umma_commit(bar(B_KEMPTY + s));
-        umma_commit(bar(B_SFULL + b));
+        umma_commit(bar(B_KEMPTY + ks));
+        umma_commit(bar(B_SFULL + qb));
         TR(2)
         EV(5, j)
         if (++ps == PLAN_STAGES) { ps = 0; plan_par ^= 1; }
-        if (++s == K_STAGES) { s = 0; k_par ^= 1; }
-        if (++b == NSB) { b = 0; if (j >= NSB) pv_par ^= 1; }
-      }
-      { const int lane = 0; (void)lane; TR_FLUSH(3) }
-    }
-  } else if (warp == W_PV) {
-    // ------------------------------------------------------------ UMMA issuer of O += P V
-    if (elect_one()) {
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
-      bool ok = true;
-      // the page count of tile t comes with P(t) (0 after the last tile): the softmax warps
-      // pass the barrier on
-      int s = 0, b = 0;
+        if (++ks == K_STAGES) { ks = 0; k_par ^= 1; }
+        if (++qb == NSB) qb = 0;
+      };
+      int next_s = 0;
+      for (; next_s < NSB && ok && !ended; ++next_s) issue_s(next_s);
+      int vs = 0, pb = 0;
       uint32_t v_par = 0, p_par = 0;
       for (int t = 0; ok; ++t) {
-        ok = mbar_wait(bar(B_PFULL + b), p_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        ok = mbar_wait(bar(B_PFULL + pb), p_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
-        const int np = tile_pages[b];
+        const int np = tile_pages[pb];
         if (np == 0) break;
-        ok = mbar_wait(bar(B_VFULL + s), v_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        ok = mbar_wait(bar(B_VFULL + vs), v_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
+        TR(1)
         EV(13, t)
-        const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
+        const uint32_t v_base = smem_u32(smem + C::V_OFF + vs * C::KV_BYTES);
         for (int kk = 0; kk < np; ++kk)
-          umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
+          umma_ts(tmem_base + C::O_COL, tmem_base + pb * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
                   make_smem_desc(v_base + kk * 16 * 128, BLOCK_N * 128, 1024), idesc_pv,
                   (t > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar(B_VEMPTY + s));
-        umma_commit(bar(B_PVDONE + b));
+        umma_commit(bar(B_VEMPTY + vs));
+        umma_commit(bar(B_PVDONE + pb));
+        TR(3)
         EV(6, t)
-        if (++s == V_STAGES) { s = 0; v_par ^= 1; }
-        if (++b == NSB) { b = 0; p_par ^= 1; }
+        if (++vs == V_STAGES) { vs = 0; v_par ^= 1; }
+        if (++pb == NSB) { pb = 0; p_par ^= 1; }
+        if (!ended) { issue_s(next_s); ++next_s; }
       }
       if (ok) umma_commit(bar(B_OREADY));
+      { const int lane = 0; (void)lane; TR_FLUSH(3) }
     }
   } else if (warp == W_BIAS) {
     // ------------------------------------------------------------ selection operand B
