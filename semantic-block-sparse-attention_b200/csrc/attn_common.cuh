@@ -1,22 +1,17 @@
 // Softmax / epilogue code shared by the two prefill attention kernels.
 //
-// A tile is 128 rows x 64 keys.  The softmax of a tile is a two-stage pipeline; each stage has
-// two threads per row, one for columns [0, 32) and one for columns [32, 64) (half 0 / half 1):
-//   mask warps (8)  read S from tensor memory, replace the entries the row may not attend to
-//                   by -inf, take the maximum of their half-row and write the masked logits
-//                   back over S (kernel-specific code; integer / compare work);
-//   exp warps  (8)  read the masked logits of their half-row, keep the lazily rescaled running
-//                   maximum (the same in both halves: it is a function of the two half maxima
-//                   the mask warps publish) and their half of the row sum, and write P =
-//                   exp2(scale * s - m) as bf16 over the first 16 columns of their own half
-//                   (exp_tile below; special-function-unit work).
-// The two stages work on consecutive tiles at the same time, on different execution pipes of
-// the same schedulers, and no thread waits for another thread of its own stage.
+// A tile is 128 rows x 64 keys.  Its softmax is one stage run by eight warps, two threads per
+// row: one for columns [0, 32) and one for columns [32, 64) (half 0 / half 1).  Both threads
+// read all 64 logits of the row from tensor memory, so they find the same row maximum without
+// exchanging anything; each keeps the lazily rescaled running maximum (identical in the two)
+// and its half of the row sum, and writes P = exp2(scale * s - m) as bf16 over the first 16
+// columns of its own half (softmax_tile below).  Since the partner reads those columns for its
+// maximum, a thread stores P only after the pair's barrier says both have loaded the row.
 //
 // Both A operands live in tensor memory, so shared memory holds K / V stages only:
 //   Q  [128 x D]  bf16, two elements per 32-bit column, written once per CTA (stage_q_half);
-//   P  [128 x 64] bf16 in the first 32 columns of the S buffer it was computed from,
-//      read by O += P V as a TMEM operand.
+//   P  [128 x 64] bf16 in the first 16 columns of each half of the S buffer it was computed
+//      from, read by O += P V as a TMEM operand.
 // An S buffer therefore becomes free when the P V product of its tile has completed.
 #pragma once
 #include "sm100.cuh"
@@ -38,7 +33,7 @@ __device__ __forceinline__ bool softmax_group_sync(uint32_t bar, uint32_t parity
 }
 
 // Copies this thread's half of the first D dims of its query row (D/2 bf16 from qrow_half, or
-// zeros when null) into the Q operand columns and arrives on bar_qfull (count: the mask threads).
+// zeros when null) into the Q operand columns and arrives on bar_qfull (count: the softmax threads).
 template <int D, int Q_COL>
 __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int hf, uint32_t lane_addr,
                                              uint32_t tmem_base, uint32_t bar_qfull) {
@@ -63,25 +58,47 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
   mbar_arrive(bar_qfull);
 }
 
-// What the mask warps hand to the exp warps for a tile (one slot per S buffer), besides the masked logits
-// in tensor memory.
-struct TileNote {
-  float row_max[256];    // [half][row]: maximum of the half-row's masked raw logits (-inf: nothing to attend to)
-  int pages;             // 16-key groups in the tile; 0 = end of the stream
-  int pad[3];
-};
-
-// The exp stage of one tile for one half-row (hf: columns [32 hf, 32 hf + 32) of the tile, and
-// columns [hf D/2, (hf + 1) D/2) of O when the accumulator has to be rescaled).  The masked raw
-// logits are in TMEM columns [s_col, s_col + 16 pages); P goes over the first 16 columns of each half.
-// tmax_raw: the larger of the two half maxima.  Returns false after a wait timed out.
+// The softmax of one tile for one half-row (hf: columns [32 hf, 32 hf + 32) of the tile, and
+// columns [hf D/2, (hf + 1) D/2) of O when the accumulator has to be rescaled).  The raw logits
+// are in TMEM columns [s_col, s_col + 64); `lim` is the number of leading columns this row may
+// attend to (64: all; columns from `lim` on, which include those of pages the product did not
+// write, count as -inf).  `pages` is the tile's count of 16-key groups.  bar_pair: the barrier
+// of the two warps that share these 32 rows (count 64), in phase j.  Arrives on bar_pfull_b when
+// P is stored.  Returns false after a wait timed out.
 template <int D, int O_COL>
-__device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int hf, uint32_t lane_addr,
-                                         uint32_t tmem_base, uint32_t s_col, uint32_t bar_pvdone_prev,
-                                         uint32_t pvdone_prev_parity, uint32_t bar_pfull_b, float scale_log2,
-                                         float& m_ref, float& l_part,
-                                         volatile int* abort_flag, int* status) {
-  const float tmax = tmax_raw * scale_log2;
+__device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, uint32_t lane_addr,
+                                             uint32_t tmem_base, uint32_t s_col, uint32_t bar_pair,
+                                             uint32_t bar_pvdone_prev, uint32_t pvdone_prev_parity,
+                                             uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
+                                             volatile int* abort_flag, int* status) {
+  const uint32_t s_addr = tmem_base + lane_addr + s_col;
+  uint32_t x[32], y[32];
+  tmem_ld32(s_addr + hf * 32, x);
+  tmem_ld32(s_addr + (hf ^ 1) * 32, y);
+  tmem_ld_wait();
+  // the row's other thread writes P over its half of the logits: tell it this thread has read
+  // them (it waits for that just before its store)
+  tc_fence_before();
+  mbar_arrive(bar_pair);
+  if (!__all_sync(0xffffffffu, lim >= 64)) {
+    const int lx = lim - 32 * hf, ly = lim - 32 * (hf ^ 1);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i >= lx) x[i] = 0xff800000u;
+      if (i >= ly) y[i] = 0xff800000u;
+    }
+  }
+  float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    tm[0] = fmax3(tm[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+    tm[1] = fmax3(tm[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+    tm[2] = fmax3(tm[2], __uint_as_float(y[i]), __uint_as_float(y[i + 1]));
+    tm[3] = fmax3(tm[3], __uint_as_float(y[i + 2]), __uint_as_float(y[i + 3]));
+  }
+  float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+  if (tmax < -1e29f) tmax = -INFINITY;               // only keys rejected through the selection operand
+  tmax *= scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
   const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + RESCALE_GAP;
   float alpha = 1.f;
@@ -107,15 +124,9 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int h
       tmem_st32(addr, o);
     }
   }
-#ifdef SEMBLO_SKIP_SOFTMAX
-  if (false) {
-#else
   if (pages > 2 * hf) {
-#endif
     const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-    uint32_t x[32], packed[16];
-    tmem_ld32(tmem_base + lane_addr + s_col + hf * 32, x);
-    tmem_ld_wait();
+    uint32_t packed[16];
     float add0 = 0.f, add1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -126,10 +137,12 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int h
       if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
     }
     l_part += add0 + add1;
+    if (!mbar_wait(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+    tc_fence_after();
     // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
-    // half's own logits only, so nothing the other half still has to read is overwritten.  The
-    // P V product takes its 16-key operand slices from columns 0, 8, 32 and 40 of the buffer.
-    tmem_st16(tmem_base + lane_addr + s_col + hf * 32, packed);
+    // half's own logits only.  The P V product takes its 16-key operand slices from columns
+    // 0, 8, 32 and 40 of the buffer.
+    tmem_st16(s_addr + hf * 32, packed);
   }
   tmem_st_wait();
   tc_fence_before();
@@ -137,7 +150,7 @@ __device__ __forceinline__ bool exp_tile(int pages, float tmax_raw, int j, int h
   return true;
 }
 
-// Final write of D/2 output columns by each of the two exp threads of a row (they hold the same
+// Final write of D/2 output columns by each of the two softmax threads of a row (they hold the same
 // running maximum and one half of the row sum each, exchanged through xchg).  merge != 0: another
 // partial (normalised output in prev_f32, or in `dst` as bf16 when prev_f32 is null; natural-log
 // LSE in lse_ptr) is LSE-merged with this one.  out_f32 != null: the result is written there in

@@ -31,7 +31,6 @@ namespace {
 constexpr int PAGE = 16;
 constexpr int PAGES_PER_TILE = 4;
 constexpr int BLOCK_N = PAGE * PAGES_PER_TILE;     // 64 keys per tile
-constexpr uint32_t POLL_NS = 50;      // how long the UMMA thread sleeps on one barrier before it looks at the other
 
 struct TileInfo {
   int npages;          // 16-row groups in the tile, 0 = end of stream
@@ -47,8 +46,7 @@ struct AttnCfg {
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][128]
-  static constexpr int NOTE_OFF = EPI_OFF + 2048;             // attn::TileNote [2]
-  static constexpr int BAR_OFF = NOTE_OFF + 2 * (int)sizeof(attn::TileNote);
+  static constexpr int BAR_OFF = EPI_OFF + 2048;
   static constexpr int INFO_OFF = BAR_OFF + 256;
   static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
   static constexpr int TMEM_COLS = 512;
@@ -76,10 +74,10 @@ struct PrefillArgs {
 };
 
 // barrier slots
-enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_XFULL = 8, B_EPI = 10, B_KVFULL = 11 };
+enum { B_QFULL = 0, B_OREADY = 1, B_SFULL = 2, B_PFULL = 4, B_PVDONE = 6, B_EPI = 8, B_PAIR = 9, B_KVFULL = 13 };
 
 template <int D, int G>
-__global__ void __launch_bounds__(576, 1)
+__global__ void __launch_bounds__(320, 1)
 window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
                       const __grid_constant__ CUtensorMap tmap_ov, const PrefillArgs a) {
   using C = AttnCfg<D>;
@@ -93,7 +91,6 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFF);
-  attn::TileNote* note = reinterpret_cast<attn::TileNote*>(smem + C::NOTE_OFF);
   TileInfo* info = reinterpret_cast<TileInfo*>(smem + C::INFO_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::INFO_OFF + STAGES * sizeof(TileInfo));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -107,15 +104,15 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 64);   // the two warps that share 32 rows
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_XFULL + b), 256);
       mbar_init(bar(B_PFULL + b), 256);
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(B_KVFULL + s), 1);
-      mbar_init(bar(B_KVEMPTY + s), 9);     // eight mask warps + the UMMA commit
+      mbar_init(bar(B_KVEMPTY + s), 9);     // eight softmax warps + the UMMA commit
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -129,7 +126,7 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 16) {
+  if (warp == 8) {
     // ------------------------------------------------------------ producer
     const int slot = q_tile0 + lane;
     const bool qvalid = lane < QT && slot < a.num_queries;
@@ -168,76 +165,59 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
         }
       }
     }
-  } else if (warp == 17) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
-    // S(j) = Q K(j)^T goes out as soon as K(j) has landed and P V(j-2), which reads the same
-    // S/P buffer, has been issued (UMMAs of one thread execute in issue order); O += P(j) V(j)
-    // as soon as the softmax warps have stored P(j): whichever is ready first.
+    // One thread issues S(j) = Q K(j)^T and O += P(t) V(t) in the fixed order S(0), S(1), then
+    // P V(t), S(t + 2) for t = 0, 1, ...  UMMAs of one thread execute in issue order, so S(t + 2)
+    // may follow P V(t), which reads P from the same buffer, without waiting for it to complete.
     if (elect_one()) {
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       tc_fence_after();
-      int next_qk = 0, next_pv = 0, end_tile = INT_MAX;
-      int np_of[4] = {0, 0, 0, 0};
-      unsigned long long t0 = globaltimer();
-      uint32_t idle = 0;
-      while (ok) {
-        bool progress = false;
-        if (next_qk < end_tile && next_qk - next_pv < 2) {
-          const int j = next_qk, s = j % STAGES, b = j & 1;
-          if (mbar_try_wait_for(bar(B_KVFULL + s), (j / STAGES) & 1, POLL_NS)) {
-            const int np = info[s].npages;
-            if (np == 0) {
-              end_tile = j;
-            } else {
-              tc_fence_after();
-              np_of[j & 3] = np;
-              const uint32_t k_base = smem_u32(smem + C::K_OFF + s * C::KV_BYTES);
-              const uint32_t idesc_qk = make_idesc_bf16(128, np * PAGE, false, false);
+      int end_tile = INT_MAX;
+      int qs = 0;                                      // stage of the next S product
+      uint32_t q_par = 0;
+      auto issue_s = [&](int j) {
+        ok = mbar_wait(bar(B_KVFULL + qs), q_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) return;
+        const int np = info[qs].npages;
+        if (np == 0) { end_tile = j; return; }
+        tc_fence_after();
+        const int b = j & 1;
+        const uint32_t k_base = smem_u32(smem + C::K_OFF + qs * C::KV_BYTES);
+        const uint32_t idesc_qk = make_idesc_bf16(128, np * PAGE, false, false);
 #pragma unroll
-              for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-                umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8,
-                        make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
-              }
-              umma_commit(bar(B_SFULL + b));
-              ++next_qk;
-            }
-            progress = true;
-          }
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
+          umma_ts(tmem_base + b * BLOCK_N, tmem_base + C::Q_COL + kk * 8,
+                  make_smem_desc(k_base + sl * BLOCK_N * 128 + ko, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
-        if (next_pv < next_qk) {
-          const int t = next_pv, b = t & 1, s = t % STAGES;
-          if (mbar_try_wait_for(bar(B_PFULL + b), (t >> 1) & 1, POLL_NS)) {
-            tc_fence_after();
-            const int np = np_of[t & 3];
-            const uint32_t v_base = smem_u32(smem + C::V_OFF + s * C::KV_BYTES);
-            for (int kk = 0; kk < np; ++kk)
-              umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
-                      make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
-                      (t > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(bar(B_KVEMPTY + s));
-            umma_commit(bar(B_PVDONE + b));
-            ++next_pv;
-            progress = true;
-          }
-        }
-        if (next_pv == end_tile) break;
-        if (progress) {
-          idle = 0;
-        } else if ((++idle & 0x3ff) == 0) {
-          if (idle == 0x400) t0 = globaltimer();
-          if (*abort_flag || *reinterpret_cast<volatile int*>(a.status) != 0) { *abort_flag = 1; ok = false; }
-          else if (globaltimer() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(a.status, 0, STATUS_TIMEOUT_MMA); ok = false; }
-        }
+        umma_commit(bar(B_SFULL + b));
+        if (++qs == STAGES) { qs = 0; q_par ^= 1; }
+      };
+      for (int j = 0; j < 2 && ok && end_tile == INT_MAX; ++j) issue_s(j);
+      int vs = 0;
+      for (int t = 0; ok && t < end_tile; ++t) {
+        const int b = t & 1;
+        ok = mbar_wait(bar(B_PFULL + b), (uint32_t)((t >> 1) & 1), abort_flag, a.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after();
+        const int np = info[vs].npages;                // the stage is held until this product's commit
+        const uint32_t v_base = smem_u32(smem + C::V_OFF + vs * C::KV_BYTES);
+        for (int kk = 0; kk < np; ++kk)
+          umma_ts(tmem_base + C::O_COL, tmem_base + b * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
+                  make_smem_desc(v_base + kk * PAGE * 128, BLOCK_N * 128, 1024), idesc_pv,
+                  (t > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar(B_KVEMPTY + vs));
+        umma_commit(bar(B_PVDONE + b));
+        if (++vs == STAGES) vs = 0;
+        if (end_tile == INT_MAX) issue_s(t + 2);
       }
       if (ok) umma_commit(bar(B_OREADY));
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue
-    // warps 0-7: mask stage, warps 8-15: exp stage; in both, warps 0-3 of the stage take columns
-    // [0, 32) of every tile and warps 4-7 columns [32, 64); thread = row
-    const int stage = warp >> 3;
+    // warps 0-3 take columns [0, 32) of every tile and warps 4-7 columns [32, 64); thread = row
     const int hf = (warp >> 2) & 1;
     const int row = threadIdx.x & 127;
     const int qslot = row / G, t = row % G;
@@ -250,75 +230,32 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     float m_ref = -INFINITY, l_part = 0.f;
     unsigned long long att = 0;
     bool ok = true;
-    int j = 0;
-    if (stage == 0) {
-      attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
-                                      bar(B_QFULL));
-      for (;; ++j) {
-        const int s = j % STAGES, b = j & 1;
-        ok = mbar_wait(bar(B_KVFULL + s), (j / STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        const int np = info[s].npages;
-        const int rows = info[s].rows, kpos0 = info[s].kpos0;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
-        if (np == 0) {
-          // end of the stream: the note slot is free once P V of tile j - 2 has been issued
-          if (j >= 2) ok = mbar_wait(bar(B_PVDONE + b), ((j - 2) >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-          if (threadIdx.x == 0) note[b].pages = 0;
-          mbar_arrive(bar(B_XFULL + b));
-          break;
-        }
-        ok = mbar_wait(bar(B_SFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-        // keys at or before the row's position; a half wholly below the diagonal for every row of
-        // the warp needs no mask and is left as it is
-        const int lim = min(rows, qpos - kpos0 + 1);
-        float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};    // four short chains
-        if (2 * hf < np) {
-          uint32_t r[32];
-          const uint32_t addr = tmem_base + lane_addr + b * BLOCK_N + hf * 32;
-          tmem_ld32(addr, r);
-          tmem_ld_wait();
-          if (__all_sync(0xffffffffu, lim >= 32 * hf + 32)) {
-#pragma unroll
-            for (int col = 0; col < 32; col += 2)
-              tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], __uint_as_float(r[col]), __uint_as_float(r[col + 1]));
-          } else {
-#pragma unroll
-            for (int col = 0; col < 32; col += 2) {
-              const float s0 = 32 * hf + col < lim ? __uint_as_float(r[col]) : -INFINITY;
-              const float s1 = 32 * hf + col + 1 < lim ? __uint_as_float(r[col + 1]) : -INFINITY;
-              r[col] = __float_as_uint(s0);
-              r[col + 1] = __float_as_uint(s1);
-              tm[(col >> 1) & 3] = fmax3(tm[(col >> 1) & 3], s0, s1);
-            }
-            tmem_st32(addr, r);
-          }
-        }
-        if (t == 0 && hf == 0) att += max(lim, 0);
-        note[b].row_max[hf * 128 + row] = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
-        if (threadIdx.x == 0) note[b].pages = np;
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(bar(B_XFULL + b));
-      }
-    } else {
-      for (;; ++j) {
-        const int b = j & 1;
-        ok = mbar_wait(bar(B_XFULL + b), (j >> 1) & 1, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        const int np = note[b].pages;
-        if (np == 0) break;
-        tc_fence_after();
-        ok = attn::exp_tile<D, C::O_COL>(np, fmaxf(note[b].row_max[row], note[b].row_max[128 + row]), j, hf, lane_addr,
-                                         tmem_base, b * BLOCK_N, bar(B_PVDONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, bar(B_PFULL + b),
-                                         a.scale_log2, m_ref, l_part, abort_flag, a.status);
-        if (!ok) break;
-      }
+    int j = 0, s = 0;
+    uint32_t kv_par = 0;
+    attn::stage_q_half<D, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (D / 2) : nullptr, hf, lane_addr, tmem_base,
+                                    bar(B_QFULL));
+    for (;; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(bar(B_KVFULL + s), kv_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      const int np = info[s].npages;
+      const int rows = info[s].rows, kpos0 = info[s].kpos0;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
+      if (np == 0) break;                              // end of the stream
+      ok = mbar_wait(bar(B_SFULL + b), (uint32_t)((j >> 1) & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      if (!ok) break;
+      tc_fence_after();
+      // keys at or before the row's position; a tile wholly below the diagonal for every row of
+      // the warp needs no mask
+      const int lim = min(rows, qpos - kpos0 + 1);
+      if (t == 0 && hf == 0) att += max(lim, 0);
+      ok = attn::softmax_tile<D, C::O_COL>(np, lim, j, hf, lane_addr, tmem_base, b * BLOCK_N, bar(B_PAIR + (warp & 3)),
+                                           bar(B_PVDONE + ((j - 1) & 1)), (uint32_t)(((j - 1) >> 1) & 1),
+                                           bar(B_PFULL + b), a.scale_log2, m_ref, l_part, abort_flag, a.status);
+      if (!ok) break;
+      if (++s == STAGES) { s = 0; kv_par ^= 1; }
     }
-    if (stage == 1) {
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
     attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
@@ -326,7 +263,6 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
                                      ok && qvalid, 0, a.out + hidx * D, nullptr,
                                      a.partial ? a.partial + hidx * D : nullptr, a.lse ? a.lse + hidx : nullptr,
                                      abort_flag, a.status);
-    }
     if (ok && a.attended) {
       if (!qvalid) att = 0;
 #pragma unroll
@@ -356,7 +292,7 @@ int launch_prefill(const void* ordered_k, const void* ordered_v, int64_t ordered
   auto kern = window_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
-  kern<<<grid, 576, C::TOTAL, st>>>(mok, mov, a);
+  kern<<<grid, 320, C::TOTAL, st>>>(mok, mov, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

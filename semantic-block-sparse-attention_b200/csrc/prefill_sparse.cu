@@ -612,104 +612,12 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       }
       if (threadIdx.x == 0) { EV(7, j) }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + lane_addr + b * BLOCK_N;
-      uint32_t x[32], y[32];
-      tmem_ld32(s_addr + hf * 32, x);
-      tmem_ld32(s_addr + (hf ^ 1) * 32, y);
-      tmem_ld_wait();
-      TR(2)
-      // the row's other thread writes P over its half of the logits: tell it this thread has
-      // read them (it waits for that just before its store)
-      tc_fence_before();
-      mbar_arrive(bar(B_PAIR + (warp & 3)));
-      // columns past the tile's pages were not written by this tile's product
-      {
-        const int own = np - 2 * hf, oth = np - 2 * (hf ^ 1);      // 16-column groups present in each half
-        if (own < 2) {
-#pragma unroll
-          for (int i = 16; i < 32; ++i) x[i] = 0xff800000u;
-          if (own < 1) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) x[i] = 0xff800000u;
-          }
-        }
-        if (oth < 2) {
-#pragma unroll
-          for (int i = 16; i < 32; ++i) y[i] = 0xff800000u;
-          if (oth < 1) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = 0xff800000u;
-          }
-        }
-      }
-      float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
-#pragma unroll
-      for (int i = 0; i < 32; i += 4) {
-        tm[0] = fmax3(tm[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
-        tm[1] = fmax3(tm[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
-        tm[2] = fmax3(tm[2], __uint_as_float(y[i]), __uint_as_float(y[i + 1]));
-        tm[3] = fmax3(tm[3], __uint_as_float(y[i + 2]), __uint_as_float(y[i + 3]));
-      }
-      float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
-      if (tmax < -1e29f) tmax = -INFINITY;             // nothing selected for this row in the tile
-      tmax *= a.scale_log2;
-      // lazy rescale: only when the running reference falls more than 2^8 behind
-      const bool need = j > 0 && m_ref != -INFINITY && tmax > m_ref + attn::RESCALE_GAP;
-      float alpha = 1.f;
-      if (need) {
-        alpha = fast_exp2(m_ref - tmax);
-        m_ref = tmax;
-        l_part *= alpha;
-      } else if (m_ref == -INFINITY) {
-        m_ref = tmax;
-      }
-      if (__any_sync(0xffffffffu, need)) {
-#ifdef SEMBLO_TRACE
-        tr[0] += 1000;
-#endif
-        // O must be quiescent: the previous tile's P V has to be complete
-        ok = mbar_wait(bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)), pv_prev_par, abort_flag, a.status,
-                       STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < D / 64; ++cc) {
-          uint32_t o[32];
-          const uint32_t addr = tmem_base + lane_addr + C::O_COL + hf * (D / 2) + cc * 32;
-          tmem_ld32(addr, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(addr, o);
-        }
-      }
-      TR(3)
-      if (np > 2 * hf) {
-        const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-        uint32_t packed[16];
-        float add0 = 0.f, add1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(x[2 * i]), a.scale_log2, neg_m));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(x[2 * i + 1]), a.scale_log2, neg_m));
-          __nv_bfloat162 pr = __floats2bfloat162_rn(e0, e1);
-          packed[i] = *reinterpret_cast<uint32_t*>(&pr);
-          if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
-        }
-        l_part += add0 + add1;
-        TR(6)
-        ok = mbar_wait(bar(B_PAIR + (warp & 3)), (uint32_t)(j & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-        TR(7)
-        // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
-        // half's own logits only.  The P V product takes its 16-key operand slices from columns
-        // 0, 8, 32 and 40 of the buffer.
-        tmem_st16(s_addr + hf * 32, packed);
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(bar(B_PFULL + b));
+      // columns past the tile's pages were not written by this tile's product: lim = 16 np
+      ok = attn::softmax_tile<D, C::O_COL>(np, np * 16, j, hf, lane_addr, tmem_base, b * BLOCK_N,
+                                           bar(B_PAIR + (warp & 3)), bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)),
+                                           pv_prev_par, bar(B_PFULL + b), a.scale_log2, m_ref, l_part, abort_flag,
+                                           a.status);
+      if (!ok) break;
       if (lane == 0) { EV(8, j) }
       TR(4)
       if (++b == NSB) { b = 0; s_par ^= 1; }
