@@ -1,12 +1,11 @@
 // Softmax / epilogue code shared by the two prefill attention kernels.
 //
 // A tile is 128 rows x 64 keys.  Its softmax is one stage run by eight warps, two threads per
-// row: one for columns [0, 32) and one for columns [32, 64) (half 0 / half 1).  Both threads
-// read all 64 logits of the row from tensor memory, so they find the same row maximum without
-// exchanging anything; each keeps the lazily rescaled running maximum (identical in the two)
-// and its half of the row sum, and writes P = exp2(scale * s - m) as bf16 over the first 16
-// columns of its own half (softmax_tile below).  Since the partner reads those columns for its
-// maximum, a thread stores P only after the pair's barrier says both have loaded the row.
+// row: one for columns [0, 32) and one for columns [32, 64) (half 0 / half 1).  Each thread
+// reads its 32 logits from tensor memory once; the two half maxima of a row meet in shared
+// memory at a barrier of the two warps involved.  Each thread keeps the lazily rescaled running
+// maximum (identical in the two) and its half of the row sum, and writes P = exp2(scale * s - m)
+// as bf16 over the first 16 columns of its own half (softmax_tile below).
 //
 // Both A operands live in tensor memory, so shared memory holds K / V stages only:
 //   Q  [128 x D]  bf16, two elements per 32-bit column, written once per CTA (stage_q_half);
@@ -62,41 +61,42 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
 // columns [hf D/2, (hf + 1) D/2) of O when the accumulator has to be rescaled).  The raw logits
 // are in TMEM columns [s_col, s_col + 64); `lim` is the number of leading columns this row may
 // attend to (64: all; columns from `lim` on, which include those of pages the product did not
-// write, count as -inf).  `pages` is the tile's count of 16-key groups.  bar_pair: the barrier
-// of the two warps that share these 32 rows (count 64), in phase j.  Arrives on bar_pfull_b when
-// P is stored.  Returns false after a wait timed out.
+// write, count as -inf).  `pages` is the tile's count of 16-key groups.  The two threads of a row
+// exchange their half maxima through mx (float [2][2][128]: tile parity, half, row) and
+// bar_pair, the barrier of the two warps that share these 32 rows (count 64), in phase j.
+// Arrives on bar_pfull_b when P is stored.  Returns false after a wait timed out.
 template <int D, int O_COL>
-__device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, uint32_t lane_addr,
-                                             uint32_t tmem_base, uint32_t s_col, uint32_t bar_pair,
+__device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, int row, uint32_t lane_addr,
+                                             uint32_t tmem_base, uint32_t s_col, float* mx, uint32_t bar_pair,
                                              uint32_t bar_pvdone_prev, uint32_t pvdone_prev_parity,
                                              uint32_t bar_pfull_b, float scale_log2, float& m_ref, float& l_part,
                                              volatile int* abort_flag, int* status) {
-  const uint32_t s_addr = tmem_base + lane_addr + s_col;
-  uint32_t x[32], y[32];
-  tmem_ld32(s_addr + hf * 32, x);
-  tmem_ld32(s_addr + (hf ^ 1) * 32, y);
-  tmem_ld_wait();
-  // the row's other thread writes P over its half of the logits: tell it this thread has read
-  // them (it waits for that just before its store)
-  tc_fence_before();
-  mbar_arrive(bar_pair);
-  if (!__all_sync(0xffffffffu, lim >= 64)) {
-    const int lx = lim - 32 * hf, ly = lim - 32 * (hf ^ 1);
+  const uint32_t s_addr = tmem_base + lane_addr + s_col + hf * 32;
+  const bool active = pages > 2 * hf;                  // the product wrote at least one page of this half
+  uint32_t x[32];
+  float hm = -INFINITY;
+  if (active) {
+    tmem_ld32(s_addr, x);
+    tmem_ld_wait();
+    const int lx = lim - 32 * hf;
+    if (!__all_sync(0xffffffffu, lx >= 32)) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (i >= lx) x[i] = 0xff800000u;
-      if (i >= ly) y[i] = 0xff800000u;
+      for (int i = 0; i < 32; ++i)
+        if (i >= lx) x[i] = 0xff800000u;
     }
-  }
-  float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four short chains
+    float tm[2] = {-INFINITY, -INFINITY};              // two short chains
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    tm[0] = fmax3(tm[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
-    tm[1] = fmax3(tm[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
-    tm[2] = fmax3(tm[2], __uint_as_float(y[i]), __uint_as_float(y[i + 1]));
-    tm[3] = fmax3(tm[3], __uint_as_float(y[i + 2]), __uint_as_float(y[i + 3]));
+    for (int i = 0; i < 32; i += 4) {
+      tm[0] = fmax3(tm[0], __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+      tm[1] = fmax3(tm[1], __uint_as_float(x[i + 2]), __uint_as_float(x[i + 3]));
+    }
+    hm = fmaxf(tm[0], tm[1]);
   }
-  float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+  float* slot = mx + (j & 1) * 256;
+  slot[hf * 128 + row] = hm;
+  mbar_arrive(bar_pair);
+  if (!mbar_wait(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+  float tmax = fmaxf(hm, slot[(hf ^ 1) * 128 + row]);
   if (tmax < -1e29f) tmax = -INFINITY;               // only keys rejected through the selection operand
   tmax *= scale_log2;
   // lazy rescale: only when the running reference falls more than 2^8 behind
@@ -124,7 +124,7 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
       tmem_st32(addr, o);
     }
   }
-  if (pages > 2 * hf) {
+  if (active) {
     const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
     uint32_t packed[16];
     float add0 = 0.f, add1 = 0.f;
@@ -137,12 +137,10 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
       if (i & 1) add1 += e0 + e1; else add0 += e0 + e1;
     }
     l_part += add0 + add1;
-    if (!mbar_wait(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
-    tc_fence_after();
     // keys 32 hf + 2 i, 32 hf + 2 i + 1 of the row share column 32 hf + i: P lies over this
-    // half's own logits only.  The P V product takes its 16-key operand slices from columns
-    // 0, 8, 32 and 40 of the buffer.
-    tmem_st16(s_addr + hf * 32, packed);
+    // half's own logits only (nobody else reads them).  The P V product takes its 16-key operand
+    // slices from columns 0, 8, 32 and 40 of the buffer.
+    tmem_st16(s_addr, packed);
   }
   tmem_st_wait();
   tc_fence_before();

@@ -46,7 +46,8 @@ struct AttnCfg {
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
   static constexpr int EPI_OFF = V_OFF + STAGES * KV_BYTES;   // float [2][128]
-  static constexpr int BAR_OFF = EPI_OFF + 2048;
+  static constexpr int MX_OFF = EPI_OFF + 2048;               // float [2][2][128]: half-row maxima
+  static constexpr int BAR_OFF = MX_OFF + 2048;
   static constexpr int INFO_OFF = BAR_OFF + 256;
   static constexpr int TOTAL = INFO_OFF + STAGES * (int)sizeof(TileInfo) + 64;   // 1024-byte aligned base
   static constexpr int TMEM_COLS = 512;
@@ -250,7 +251,8 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
       // the warp needs no mask
       const int lim = min(rows, qpos - kpos0 + 1);
       if (t == 0 && hf == 0) att += max(lim, 0);
-      ok = attn::softmax_tile<D, C::O_COL>(np, lim, j, hf, lane_addr, tmem_base, b * BLOCK_N, bar(B_PAIR + (warp & 3)),
+      ok = attn::softmax_tile<D, C::O_COL>(np, lim, j, hf, row, lane_addr, tmem_base, b * BLOCK_N,
+                                           reinterpret_cast<float*>(smem + C::MX_OFF), bar(B_PAIR + (warp & 3)),
                                            bar(B_PVDONE + ((j - 1) & 1)), (uint32_t)(((j - 1) >> 1) & 1),
                                            bar(B_PFULL + b), a.scale_log2, m_ref, l_part, abort_flag, a.status);
       if (!ok) break;

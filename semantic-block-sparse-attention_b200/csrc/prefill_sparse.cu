@@ -84,7 +84,8 @@ struct GatherCfg {
   static constexpr int ONEHOT_OFF = V_OFF + V_STAGES * KV_BYTES;   // E: 128 rows x 64 bytes, 64-byte swizzle
   static constexpr int BIAS_OFF = ONEHOT_OFF + 128 * 64;           // B: one tile per K stage
   static constexpr int LUT_OFF = BIAS_OFF + K_STAGES * BIAS_BYTES; // uint4 [256]: 8 selection bits -> 8 bf16
-  static constexpr int EPI_OFF = LUT_OFF + 4096;                   // float [2][128]
+  static constexpr int MX_OFF = LUT_OFF + 4096;                    // float [2][2][128]: half-row maxima
+  static constexpr int EPI_OFF = MX_OFF + 2048;                    // float [2][128]
   static constexpr int PLAN_OFF = EPI_OFF + 2048;
   static constexpr int BAR_OFF = PLAN_OFF + (int)sizeof(Plan);
   static constexpr int NUM_BARS = 8 + 3 * NSB + 2 * K_STAGES + 2 * V_STAGES + 2 * PLAN_STAGES;
@@ -613,8 +614,8 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       if (threadIdx.x == 0) { EV(7, j) }
       tc_fence_after();
       // columns past the tile's pages were not written by this tile's product: lim = 16 np
-      ok = attn::softmax_tile<D, C::O_COL>(np, np * 16, j, hf, lane_addr, tmem_base, b * BLOCK_N,
-                                           bar(B_PAIR + (warp & 3)), bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)),
+      ok = attn::softmax_tile<D, C::O_COL>(np, np * 16, j, hf, row, lane_addr, tmem_base, b * BLOCK_N,
+                                           reinterpret_cast<float*>(smem + C::MX_OFF), bar(B_PAIR + (warp & 3)), bar(B_PVDONE + (b == 0 ? NSB - 1 : b - 1)),
                                            pv_prev_par, bar(B_PFULL + b), a.scale_log2, m_ref, l_part, abort_flag,
                                            a.status);
       if (!ok) break;
