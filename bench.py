@@ -71,7 +71,8 @@ def mixture_inputs_device(cfg, seed, device, length=None):
     cent = torch.randn(hkv, cfg["centres"], dim, generator=g, device=device)
     z = torch.randint(0, cfg["centres"], (length,), generator=g, device=device)
     base = cent[:, z].permute(1, 0, 2)                                   # [L, Hkv, D]
-    k_pre = base + 0.3 * torch.randn(length, hkv, dim, generator=g, device=device)
+    # contiguous [L, Hkv, D] like a model's projection output (the sum inherits the permuted strides of `base`)
+    k_pre = (base + 0.3 * torch.randn(length, hkv, dim, generator=g, device=device)).contiguous()
     v = torch.randn(length, hkv, dim, generator=g, device=device).to(torch.bfloat16)
     pos = torch.arange(length, device=device)
 
