@@ -116,14 +116,15 @@ struct AssignSmem {
   static constexpr int A_BYTES = 128 * D * 2;
   static constexpr int B_BYTES = ASG_BN * D * 2;
   static constexpr int BAR_OFF = A_BYTES + ASG_STAGES * B_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // barriers + alignment slack
+  static constexpr int XCHG_OFF = BAR_OFF + 256;       // (value, id) of the upper-half epilogue threads: [128] float + [128] int
+  static constexpr int TOTAL = XCHG_OFF + 1024 + 1024; // + alignment slack
 };
 
 // SPLIT: the centroids are a descriptor pair [2][C][D/2] (3-D map: column in the half, row,
 // half) instead of [C][D], the similarity is compared in fp32 as it comes out of the tensor
 // core (no bf16 rounding), and centroids whose bit is set in dead_bits are never chosen.
 template <int D, bool SPLIT>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
                      const __grid_constant__ CUtensorMap tmap_c, int64_t n, int num_centroids,
                      int32_t* __restrict__ assign_out, int id_offset,
@@ -150,7 +151,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
       mbar_init(smem_u32(&bars[5 + s]), 1);
-      mbar_init(smem_u32(&bars[7 + s]), 128);
+      mbar_init(smem_u32(&bars[7 + s]), 256);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -164,6 +165,9 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  float epi_best = 0.f;
+  int epi_id = 0, epi_row = 0, epi_hf = -1;      // set by the epilogue threads
+  bool epi_ok = false;
   if (warp == 4) {
     if (elect_one()) {
       tma_prefetch_desc(&tmap_x);
@@ -210,37 +214,64 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
     }
   } else {
-    // epilogue: thread = row (TMEM lane), scan the centroids in ascending order
-    const int row = threadIdx.x;           // 0..127
+    // epilogue: eight warps, two threads per row (TMEM lane).  Warps 0-3 scan columns [0, 64) of
+    // every 128-centroid chunk, warps 6-9 columns [64, 128), each in ascending order; the two
+    // partial results of a row are combined after the loop (larger value, then smaller id).
+    const int hf = warp >= 6 ? 1 : 0;
+    const int row = (warp & 3) * 32 + (threadIdx.x & 31);
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     float best = -INFINITY;
     int best_id = 0;
     bool ok = true;
+    const bool full = (num_centroids % ASG_BN) == 0;
     for (int j = 0; j < num_chunks && ok; ++j) {
       const int b = j & 1;
       ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c4 = 0; c4 < ASG_BN / 32; ++c4) {
+      for (int c4 = 0; c4 < ASG_BN / 64; ++c4) {
         uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * ASG_BN + c4 * 32, r);
+        tmem_ld32(tmem_base + lane_addr + b * ASG_BN + hf * 64 + c4 * 32, r);
         tmem_ld_wait();
-        const int cbase = j * ASG_BN + c4 * 32;
+        const int cbase = j * ASG_BN + hf * 64 + c4 * 32;
         uint32_t dead = 0u;
         if (SPLIT && dead_bits != nullptr && cbase < num_centroids) dead = __ldg(dead_bits + (cbase >> 5));
+        if (full && dead == 0u) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          // the reference's bf16 matmul output: fp32 accumulate, round to nearest even
-          float v = SPLIT ? __uint_as_float(r[i]) : __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
-          bool take = (cbase + i < num_centroids) && !((dead >> i) & 1u) && (v > best);
-          best = take ? v : best;
-          best_id = take ? cbase + i : best_id;
+          for (int i = 0; i < 32; ++i) {
+            // the reference's bf16 matmul output: fp32 accumulate, round to nearest even
+            float v = SPLIT ? __uint_as_float(r[i]) : __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+            const bool take = v > best;
+            best = take ? v : best;
+            best_id = take ? cbase + i : best_id;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = SPLIT ? __uint_as_float(r[i]) : __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+            const bool take = (cbase + i < num_centroids) && !((dead >> i) & 1u) && (v > best);
+            best = take ? v : best;
+            best_id = take ? cbase + i : best_id;
+          }
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&bars[7 + b]));
     }
-    if (ok && row0 + row < n) assign_out[row0 + row] = best_id + id_offset;
+    float* xv = reinterpret_cast<float*>(smem + L::XCHG_OFF);
+    int* xi = reinterpret_cast<int*>(smem + L::XCHG_OFF + 512);
+    if (hf == 1) { xv[row] = ok ? best : NAN; xi[row] = best_id; }
+    epi_best = best; epi_id = best_id; epi_ok = ok; epi_row = row; epi_hf = hf;
+  }
+  __syncthreads();
+  if (epi_hf == 0) {
+    const float ov = reinterpret_cast<const float*>(smem + L::XCHG_OFF)[epi_row];
+    const int oi = reinterpret_cast<const int*>(smem + L::XCHG_OFF + 512)[epi_row];
+    if (epi_ok && ov == ov && row0 + epi_row < n) {
+      const bool take = ov > epi_best || (ov == epi_best && oi < epi_id);
+      assign_out[row0 + epi_row] = (take ? oi : epi_id) + id_offset;
+    }
   }
   __syncthreads();
   if (*abort_flag) __nanosleep(50000);
@@ -566,7 +597,7 @@ int launch_assign(const void* x, int64_t n, int64_t x_stride_elems, const void* 
   if (rc) return rc;
   auto kern = assign_argmax_kernel<D, SPLIT>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AssignSmem<D>::TOTAL));
-  kern<<<(unsigned)ceil_div(n, 128), 192, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset,
+  kern<<<(unsigned)ceil_div(n, 128), 320, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset,
                                                                     dead_bits, status);
   SEMBLO_LAUNCH_CHECK();
   return 0;
