@@ -473,6 +473,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       if (ok && C::Q_SMEM_DIMS > 0) ok = mbar_wait(bar(B_QHI), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       tc_fence_after();
+      EV(14, 5)
       const uint32_t qhi_base = smem_u32(smem + C::QHI_OFF);
       const uint32_t onehot_base = smem_u32(smem + C::ONEHOT_OFF);
       int ps = 0, ks = 0, qb = 0;                     // ring slots of the next S product
