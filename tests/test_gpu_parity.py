@@ -264,7 +264,7 @@ def test_scores_and_selection(dev, dim, hq, hkv, sink):
 
 
 # ---------------------------------------------------------------------- prefill attention
-@pytest.mark.parametrize("dim,hq,hkv", [(256, 8, 2), (128, 4, 1), (128, 16, 2)])
+@pytest.mark.parametrize("dim,hq,hkv", [(256, 8, 2), (128, 4, 1), (128, 16, 2), (256, 16, 1)])
 def test_dense_causal_attention(dev, dim, hq, hkv):
     from semblo_b200.fused_prefill import window_attention
     length = 700
