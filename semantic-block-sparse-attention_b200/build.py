@@ -51,7 +51,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         log.append(f"==== {src}\n{out}")
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
-    subprocess.run([_nvcc(), "-shared", "-o", str(LIB), *objs, "-lcudart"], check=True)
+    subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(LIB), *objs, "-lcudart"],
+                   check=True)
     (HERE / "build.log").write_text("\n".join(log))
     if verbose:
         print("\n".join(log))
