@@ -99,7 +99,8 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
-  const int q_tile0 = blockIdx.x * QT;
+  // later queries see more keys: the longest tiles start first, so the launch ends evenly
+  const int q_tile0 = (int)(gridDim.x - 1 - blockIdx.x) * QT;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 256);
