@@ -217,15 +217,28 @@ int semblo_window_prefill(const void* q, int num_queries, int num_q_heads, int n
  * output, natural-log LSE); `out` / `lse` receive the LSE-merged
  * result (kv_outer.py:203-227); merge = 0: the sparse result alone.  attended (may be NULL)
  * points at two counters: [0] += attended keys summed over (query, KV head), [1] += K/V rows
- * gathered summed over tiles (the union each tile actually reads). */
+ * gathered summed over tiles (the union each tile actually reads).  cta_order (optional,
+ * [tiles * Hkv] from semblo_gather_launch_order): the (tile, head) pairs in the order their
+ * CTAs should start; it changes the schedule only, not the result. */
 int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads, int num_kv_heads,
-                                 int head_dim, const int32_t* q_order, const void* packed_k,
-                                 const void* packed_v, int64_t packed_rows, const int32_t* page_table,
+                                 int head_dim, const int32_t* q_order, const int32_t* cta_order,
+                                 const void* packed_k, const void* packed_v, int64_t packed_rows,
+                                 const int32_t* page_table,
                                  const int32_t* qmask, const int32_t* causal_sizes,
                                  const int32_t* indptr, int num_clusters, float sm_scale, int merge,
                                  const float* partial_in, void* out, float* lse,
                                  unsigned long long* attended,
                                  int32_t* status, void* stream);
+
+/* Launch order for semblo_sparse_prefill_gather: the rows each (tile, head) will gather (the
+ * union of the tile's selections; tiles of 128 / G queries in q_order) go to work
+ * [tiles * Hkv], and order_out [tiles * Hkv] lists tile * Hkv + head by descending work, so
+ * that the longest CTAs start first and the launch ends evenly.  No reference counterpart (the
+ * reference's kernels are scheduled by Triton's grid order). */
+int semblo_gather_launch_order(const int32_t* q_order, const int32_t* qmask,
+                               const int32_t* causal_sizes, int num_queries, int num_q_heads,
+                               int num_kv_heads, int num_clusters, int32_t* work,
+                               int32_t* order_out, void* stream);
 
 /* ---- decode ----------------------------------------------------------------------- */
 

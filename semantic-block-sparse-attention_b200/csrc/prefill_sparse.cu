@@ -106,6 +106,7 @@ struct GatherArgs {
   int num_queries, num_q_heads, num_kv_heads, num_clusters;
   const __nv_bfloat16* q;       // [Q, Hq, D]
   const int32_t* q_order;       // [Hkv, Q] tile order, or null
+  const int32_t* cta_order;     // [tiles * Hkv] (tile * Hkv + head) in launch order, or null
   const int32_t* qmask;         // [Q, Hkv, C/32]
   const int32_t* causal_sizes;  // [Hkv, C]
   const int32_t* indptr;        // [Hkv, C+1]
@@ -187,8 +188,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y;
-  const int q_tile0 = blockIdx.x * QT;
+  // with a launch order the grid is one-dimensional and entry i names the (tile, head) of CTA i
+  const int cta_id = a.cta_order ? a.cta_order[blockIdx.x] : -1;
+  const int h = cta_id >= 0 ? cta_id % a.num_kv_heads : (int)blockIdx.y;
+  const int q_tile0 = (cta_id >= 0 ? cta_id / a.num_kv_heads : (int)blockIdx.x) * QT;
   if (threadIdx.x == 0) { EV(14, 0) }
 
   if (threadIdx.x == 0) {
@@ -648,6 +651,82 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ------------------------------------------------------------------ launch order
+// work[tile * Hkv + h] = rows in the union of the tile's selections (what the tile's CTA gathers).
+// One warp per (tile, head): lanes take the bitmask words in turn.
+__global__ void tile_work_kernel(const int32_t* __restrict__ q_order, const int32_t* __restrict__ qmask,
+                                 const int32_t* __restrict__ causal_sizes, int num_queries, int num_kv_heads,
+                                 int num_clusters, int qt, int num_tiles, int32_t* __restrict__ work) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= num_tiles * num_kv_heads) return;
+  const int tile = item / num_kv_heads, h = item % num_kv_heads;
+  const int nwords = num_clusters >> 5;
+  const int32_t* csz = causal_sizes + (int64_t)h * num_clusters;
+  // lane i holds the query of slot i (qt <= 32); -1 past the end
+  const int my_slot = tile * qt + lane;
+  const int my_q = (lane < qt && my_slot < num_queries)
+                       ? (q_order ? q_order[(int64_t)h * num_queries + my_slot] : my_slot) : -1;
+  int total = 0;
+  for (int w0 = 0; w0 < nwords; w0 += 32) {
+    const int w = w0 + lane;
+    uint32_t u = 0u;
+#pragma unroll 8
+    for (int i = 0; i < qt; ++i) {
+      const int qi = __shfl_sync(0xffffffffu, my_q, i);
+      if (qi >= 0 && w < nwords) u |= (uint32_t)__ldg(qmask + ((int64_t)qi * num_kv_heads + h) * nwords + w);
+    }
+    if (u) {
+      // the word's 32 sizes in eight independent 16-byte loads
+      const int4* c4 = reinterpret_cast<const int4*>(csz + w * 32);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int4 v = __ldg(c4 + k);
+        const uint32_t nib = (u >> (4 * k)) & 0xFu;
+        total += ((nib & 1u) ? v.x : 0) + ((nib & 2u) ? v.y : 0) + ((nib & 4u) ? v.z : 0) + ((nib & 8u) ? v.w : 0);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+  if (lane == 0) work[item] = total;
+}
+
+// order[] = the items by descending work, in 256 classes of equal width (one block).
+__global__ void tile_order_kernel(const int32_t* __restrict__ work, int n, int32_t* __restrict__ order) {
+  __shared__ int s_max;
+  __shared__ int s_hist[256];
+  if (threadIdx.x == 0) s_max = 0;
+  if (threadIdx.x < 256) s_hist[threadIdx.x] = 0;
+  __syncthreads();
+  int m = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) m = max(m, work[i]);
+  atomicMax(&s_max, m);
+  __syncthreads();
+  const long long top = (long long)s_max + 1;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    atomicAdd(&s_hist[255 - (int)((long long)work[i] * 256 / top)], 1);
+  __syncthreads();
+  if (threadIdx.x < 32) {                 // exclusive scan of the 256 classes: eight per lane
+    const int lane = threadIdx.x;
+    int c[8], sum = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { c[k] = s_hist[lane * 8 + k]; sum += c[k]; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { s_hist[lane * 8 + k] = run; run += c[k]; }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    order[atomicAdd(&s_hist[255 - (int)((long long)work[i] * 256 / top)], 1)] = i;
+}
+
 template <int D, int G>
 int launch_gather(const GatherArgs& a, cudaStream_t st) {
   using C = GatherCfg<D>;
@@ -663,6 +742,7 @@ int launch_gather(const GatherArgs& a, cudaStream_t st) {
   auto kern = sparse_gather_prefill_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
   dim3 grid((unsigned)ceil_div(a.num_queries, QT), a.num_kv_heads);
+  if (a.cta_order) grid = dim3(grid.x * grid.y, 1);
   kern<<<grid, GATHER_THREADS, C::TOTAL, st>>>(mq, a);
   SEMBLO_LAUNCH_CHECK();
   return 0;
@@ -672,8 +752,8 @@ int launch_gather(const GatherArgs& a, cudaStream_t st) {
 
 extern "C" int semblo_sparse_prefill_gather(
     const void* q, int num_queries, int num_q_heads, int num_kv_heads, int head_dim,
-    const int32_t* q_order, const void* packed_k, const void* packed_v, int64_t packed_rows,
-    const int32_t* page_table,
+    const int32_t* q_order, const int32_t* cta_order, const void* packed_k, const void* packed_v,
+    int64_t packed_rows, const int32_t* page_table,
     const int32_t* qmask, const int32_t* causal_sizes, const int32_t* indptr, int num_clusters,
     float sm_scale, int merge, const float* partial_in, void* out, float* lse,
     unsigned long long* attended, int32_t* status, void* stream) {
@@ -689,7 +769,7 @@ extern "C" int semblo_sparse_prefill_gather(
   if (num_queries == 0) return 0;
   GatherArgs a;
   a.num_queries = num_queries; a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads;
-  a.num_clusters = num_clusters; a.q = (const __nv_bfloat16*)q; a.q_order = q_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
+  a.num_clusters = num_clusters; a.q = (const __nv_bfloat16*)q; a.q_order = q_order; a.cta_order = cta_order; a.qmask = qmask; a.causal_sizes = causal_sizes;
   a.indptr = indptr; a.page_table = page_table;
   a.packed_k = (const __nv_bfloat16*)packed_k; a.packed_v = (const __nv_bfloat16*)packed_v;
   a.packed_rows = packed_rows;
@@ -709,4 +789,24 @@ extern "C" int semblo_sparse_prefill_gather(
   return semblo::fail(semblo::SEMBLO_EINVAL,
                       "sparse prefill supports head_dim 128/256 with 4, 8 or 16 query heads per KV head "
                       "(got head_dim %d, group %d)", head_dim, g);
+}
+
+extern "C" int semblo_gather_launch_order(const int32_t* q_order, const int32_t* qmask, const int32_t* causal_sizes,
+                                          int num_queries, int num_q_heads, int num_kv_heads, int num_clusters,
+                                          int32_t* work, int32_t* order_out, void* stream) {
+  SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
+  SEMBLO_REQUIRE(qmask && causal_sizes && work && order_out, "selection, sizes and the two outputs are required");
+  SEMBLO_REQUIRE(num_clusters % 32 == 0, "cluster count %d must be a multiple of 32", num_clusters);
+  const int g = num_q_heads / num_kv_heads;
+  SEMBLO_REQUIRE(g == 4 || g == 8 || g == 16, "4, 8 or 16 query heads per KV head (got %d)", g);
+  if (num_queries == 0) return 0;
+  const int qt = 128 / g;
+  const int tiles = (num_queries + qt - 1) / qt;
+  const int n = tiles * num_kv_heads;
+  cudaStream_t st = (cudaStream_t)stream;
+  tile_work_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, st>>>(q_order, qmask, causal_sizes, num_queries, num_kv_heads,
+                                                             num_clusters, qt, tiles, work);
+  tile_order_kernel<<<1, 1024, 0, st>>>(work, n, order_out);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
 }

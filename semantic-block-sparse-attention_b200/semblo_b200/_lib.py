@@ -61,7 +61,8 @@ _SIGNATURES = {
     "semblo_flush_repack": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "semblo_argsort_keys_static_max_keys": (c_int64, []),
     "semblo_argsort_keys_static": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
-    "semblo_sparse_prefill_gather": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_gather_launch_order": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "semblo_sparse_prefill_gather": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_window_prefill": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_decode_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int64, c_int]),
     "semblo_decode_workspace_offsets": (c_int, [c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p]),

@@ -111,19 +111,36 @@ def argsort_keys(keys: torch.Tensor, max_key: int, *, out: torch.Tensor | None =
 def sparse_gather_attention(q: torch.Tensor, *, packed_kv: torch.Tensor, qmask: torch.Tensor,
                             causal_sizes: torch.Tensor, indptr: torch.Tensor, sm_scale: float,
                             out: torch.Tensor, lse: torch.Tensor | None, merge: bool, page_table=None,
-                            q_order=None, attended=None, partial=None) -> torch.Tensor:
+                            q_order=None, attended=None, partial=None, cta_order=None) -> torch.Tensor:
     """One launch of the row-gather sparse kernel (semblo_sparse_prefill_gather)."""
     require_cuda(q, packed_kv, qmask)
     q_count, num_q_heads, head_dim = q.shape
     q = q if q.is_contiguous() else q.contiguous()
     status = _lib.status_for(q.device)
     check(lib().semblo_sparse_prefill_gather(
-        ptr(q), q_count, num_q_heads, int(packed_kv.shape[2]), head_dim, ptr(q_order), ptr(packed_kv[0]),
+        ptr(q), q_count, num_q_heads, int(packed_kv.shape[2]), head_dim, ptr(q_order), ptr(cta_order),
+        ptr(packed_kv[0]),
         ptr(packed_kv[1]), int(packed_kv.shape[1]), ptr(page_table), ptr(qmask), ptr(causal_sizes), ptr(indptr),
         int(causal_sizes.shape[1]), float(sm_scale), 1 if merge else 0, ptr(partial), ptr(out), ptr(lse),
         ptr(attended),
         ptr(status.word), stream_ptr()))
     return out
+
+
+def gather_launch_order(q_order, qmask: torch.Tensor, causal_sizes: torch.Tensor, num_q_heads: int, *,
+                        work: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """(tile, head) pairs of a sparse launch by descending gathered rows (semblo_gather_launch_order)."""
+    require_cuda(qmask, causal_sizes)
+    q_count, hkv = int(qmask.shape[0]), int(qmask.shape[1])
+    qt = 128 // (num_q_heads // hkv)
+    n = ((q_count + qt - 1) // qt) * hkv
+    if work is None:
+        work = torch.empty(n, dtype=torch.int32, device=qmask.device)
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=qmask.device)
+    check(lib().semblo_gather_launch_order(ptr(q_order), ptr(qmask), ptr(causal_sizes), q_count, num_q_heads, hkv,
+                                           int(causal_sizes.shape[1]), ptr(work), ptr(out), stream_ptr()))
+    return out[:n]
 
 
 def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions: torch.Tensor,
@@ -203,6 +220,13 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     # queries with the same best-scoring cluster select nearly the same clusters: tiles are
     # formed in that order so a tile's union of selections stays close to a single selection
     argsort_keys(top1, index.num_buckets, out=order, workspace=snap.sort_ws)
+    # the CTAs with the most rows to gather start first
+    n_cta = ((q_count + 128 // (num_q_heads // index.num_kv_heads) - 1) // (128 // (num_q_heads // index.num_kv_heads))) * index.num_kv_heads
+    if getattr(snap, "cta_work", None) is None or snap.cta_work.numel() < n_cta:
+        snap.cta_work = torch.empty(n_cta, dtype=torch.int32, device=dev)
+        snap.cta_order = torch.empty(n_cta, dtype=torch.int32, device=dev)
+    cta_order = gather_launch_order(order, qmask, base, num_q_heads, work=snap.cta_work[:n_cta],
+                                    out=snap.cta_order[:n_cta])
     if out is None:
         out = torch.empty_like(q_chunk)
     lse = snap.lse[:q_count]
@@ -218,7 +242,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
                             indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
                             page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended,
-                            partial=partial)
+                            partial=partial, cta_order=cta_order)
     if _timer:
         _timer("stop")
     return out

@@ -357,6 +357,38 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
         assert float(out3[qi, :group].float().abs().max()) == 0.0, "a query with an empty selection must give zeros"
 
 
+def test_gather_launch_order_counts_union_rows(dev):
+    """work[tile, head] = rows in the union of the tile's selections; the order is a permutation of
+    the (tile, head) pairs by descending work class (256 classes of equal width)."""
+    from semblo_b200.fused_prefill import gather_launch_order
+    q_count, hkv, clusters, hq = 1000, 2, 256, 8             # G = 4: tiles of 32 queries, the last one ragged
+    g = torch.Generator().manual_seed(11)
+    sel = torch.rand(q_count, hkv, clusters, generator=g) < 0.1
+    sizes = torch.randint(0, 90, (hkv, clusters), generator=g, dtype=torch.int32)
+    order = torch.stack([torch.randperm(q_count, generator=g) for _ in range(hkv)]).int()
+    tiles = (q_count + 31) // 32
+    got = gather_launch_order(order.to(dev), O.pack_bits(sel).to(dev), sizes.to(dev), hq)
+    # a second call that also returns the work counts
+    work = torch.empty(tiles * hkv, dtype=torch.int32, device=dev)
+    got2 = gather_launch_order(order.to(dev), O.pack_bits(sel).to(dev), sizes.to(dev), hq, work=work)
+    want = torch.zeros(tiles, hkv, dtype=torch.int64)
+    for h in range(hkv):
+        rows = sel[order[h].long(), h]
+        for t in range(tiles):
+            want[t, h] = int((rows[32 * t:32 * t + 32].any(0).long() * sizes[h].long()).sum())
+    assert torch.equal(work.cpu().long().view(tiles, hkv), want)
+    for o in (got.cpu().long(), got2.cpu().long()):
+        assert sorted(o.tolist()) == list(range(tiles * hkv))
+        cls = want.view(-1)[o] * 256 // (int(want.max()) + 1)
+        assert bool((cls[:-1] >= cls[1:]).all())
+    # without a tile order the tiles are consecutive queries
+    got3 = gather_launch_order(None, O.pack_bits(sel).to(dev), sizes.to(dev), hq, work=work)
+    want3 = torch.stack([torch.stack([(sel[32 * t:32 * t + 32, h].any(0).long() * sizes[h].long()).sum()
+                                      for h in range(hkv)]) for t in range(tiles)])
+    assert torch.equal(work.cpu().long().view(tiles, hkv), want3)
+    assert sorted(got3.cpu().tolist()) == list(range(tiles * hkv))
+
+
 def test_argsort_and_top1_keys(dev):
     from semblo_b200.fused_prefill import argsort_keys
     g = torch.Generator().manual_seed(1)
