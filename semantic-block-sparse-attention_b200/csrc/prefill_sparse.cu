@@ -2,20 +2,21 @@
 // clusters' visible rows, tcgen05 / TMEM attention, LSE merge with the window partial.
 //
 // One CTA owns QT = 128 / G queries of one KV head, taken in the caller's tile order
-// (queries with similar selections are placed in the same tile).  Warp roles:
-//   warps 0-7  mask stage of the softmax (two threads per row, 32 columns each): keep the
-//              logits of the keys whose cluster the row's query selected, take the maximum
-//   warps 8-15 exp stage of the softmax (two threads per row): running maximum and sum, P as
-//              bf16 into TMEM; they also write the output in the epilogue
-//   warp  16   planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
+// (queries with similar selections are placed in the same tile).  Warp roles (GW = 3):
+//   warps 0-7  softmax, two threads per row with 32 columns each (attn::softmax_tile): running
+//              maximum and sum, P as bf16 into TMEM; they also write the output in the epilogue
+//   warp  8    planner: walks the tile's cluster bitmasks 32 clusters at a time (sizes and
 //              starts fetched by 32 lanes in parallel), and expands the union of selected
 //              clusters into a stream of packed rows, each tagged with the 32-bit set of
-//              queries that selected its cluster; 64 rows make a tile
-//   warps 17-20 gather: K rows of even / odd tiles, V rows of even / odd tiles; 16-byte
-//              cp.async into the 128-byte-swizzled UMMA layout (only visible rows are
-//              read: no page padding), then published to the async proxy
-//   warp  21   UMMA issuer: S = Q K^T and O += P V, accumulators in TMEM, issued in
-//              whichever order their operands become ready
+//              query slots that selected its cluster; 64 rows make a tile
+//   warps 9 .. 8 + 2 GW  gather: GW warps for the K rows and GW for the V rows, tile t in warp
+//              t mod GW; 16-byte cp.async into the 128-byte-swizzled UMMA layout (only visible
+//              rows are read: no page padding), then published to the async proxy
+//   next warp  UMMA issuer: S = [Q | E] [K | B]^T and O += P V, accumulators in TMEM, in the
+//              fixed order P V(t), S(t + 2)
+//   last warp  selection operand B of every tile from the planner's slot masks
+// The selection itself is applied by the S product (see the comment above GatherCfg): the
+// softmax warps never look at a mask.
 // The epilogue merges the sparse partial with the window partial already stored in
 // `out` / `lse` by the dense launch, so each query sees one softmax over the union.
 //
@@ -35,7 +36,6 @@ using semblo::ceil_div;
 namespace {
 
 constexpr int BLOCK_N = 64;
-constexpr uint32_t POLL_NS = 50;      // how long the UMMA thread sleeps on one barrier before it looks at the other
 constexpr int PLAN_STAGES = 8;
 constexpr float LOG2EF = 1.4426950408889634f;
 
