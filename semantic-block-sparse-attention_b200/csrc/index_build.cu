@@ -91,6 +91,70 @@ __global__ void normalize_rows_kernel(const T* __restrict__ x, int64_t n_rows, i
   }
 }
 
+// The same computation for bf16 rows with 16-byte accesses: lane l holds elements [8 l, 8 l + 8)
+// of the row (dim a multiple of 8, at most 256; rows and outputs 16-byte aligned).
+__global__ void normalize_rows_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int64_t n_rows, int dim,
+                                             int64_t row_stride, __nv_bfloat16* __restrict__ out,
+                                             float* __restrict__ space_f32,
+                                             __nv_bfloat16* __restrict__ space_bf16, int second_round) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const bool have = lane * 8 < dim;
+  float v[8];
+  double ss = 0.0;
+  {
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (have) raw = __ldg(reinterpret_cast<const uint4*>(x + row * row_stride) + lane);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += (double)v[i] * (double)v[i];
+  }
+  ss = warp_sum_d(ss);
+  const float nrm = fmaxf((float)sqrt(ss), 1e-12f);
+  double ss2 = 0.0;
+  if (second_round == 2) {
+    ss2 = ss;                                        // the input is already the routed (stage-1) vector
+  } else {
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat16 r0 = __float2bfloat16_rn(v[2 * i] / nrm), r1 = __float2bfloat16_rn(v[2 * i + 1] / nrm);
+      v[2 * i] = __bfloat162float(r0); v[2 * i + 1] = __bfloat162float(r1);
+      packed[i] = (uint32_t)__bfloat16_as_ushort(r0) | ((uint32_t)__bfloat16_as_ushort(r1) << 16);
+      ss2 += (double)v[2 * i] * (double)v[2 * i] + (double)v[2 * i + 1] * (double)v[2 * i + 1];
+    }
+    if (out && have)
+      reinterpret_cast<uint4*>(out + row * (int64_t)dim)[lane] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+  if (!space_f32 && !space_bf16) return;
+  if (second_round != 2) ss2 = warp_sum_d(ss2);
+  const float nrm2 = fmaxf((float)sqrt(ss2), 1e-12f);
+  float sv[8];
+  uint32_t sp[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float s0 = v[2 * i] / nrm2, s1 = v[2 * i + 1] / nrm2;
+    const __nv_bfloat16 b0 = __float2bfloat16_rn(s0), b1 = __float2bfloat16_rn(s1);
+    sp[i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+    // query router (second_round == 1): the second normalisation is rounded to the storage dtype too
+    sv[2 * i] = second_round == 1 ? __bfloat162float(b0) : s0;
+    sv[2 * i + 1] = second_round == 1 ? __bfloat162float(b1) : s1;
+  }
+  if (!have) return;
+  if (space_bf16) reinterpret_cast<uint4*>(space_bf16 + row * (int64_t)dim)[lane] = make_uint4(sp[0], sp[1], sp[2], sp[3]);
+  if (space_f32) {
+    float4* o = reinterpret_cast<float4*>(space_f32 + row * (int64_t)dim) + 2 * lane;
+    o[0] = make_float4(sv[0], sv[1], sv[2], sv[3]);
+    o[1] = make_float4(sv[4], sv[5], sv[6], sv[7]);
+  }
+}
+
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int64_t* __restrict__ idx,
                                    int64_t m, int dim, float* __restrict__ dst_f32,
                                    __nv_bfloat16* __restrict__ dst_bf16) {
@@ -632,7 +696,15 @@ extern "C" int semblo_routing_normalize(const void* x, int dtype, int64_t n_rows
   cudaStream_t st = (cudaStream_t)stream;
   const int wpb = 8;
   dim3 grid((unsigned)ceil_div(n_rows, wpb));
-  if (dtype == SEMBLO_BF16)
+  const bool vec = dtype == SEMBLO_BF16 && dim % 8 == 0 && dim <= 256 && row_stride % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(space_f32) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(space_bf16) & 15) == 0;
+  if (vec)
+    normalize_rows_bf16x8_kernel<<<grid, wpb * 32, 0, st>>>((const __nv_bfloat16*)x, n_rows, dim, row_stride,
+                                                          (__nv_bfloat16*)out, space_f32,
+                                                          (__nv_bfloat16*)space_bf16, query_mode);
+  else if (dtype == SEMBLO_BF16)
     normalize_rows_kernel<__nv_bfloat16, 256><<<grid, wpb * 32, 0, st>>>(
         (const __nv_bfloat16*)x, n_rows, dim, row_stride, (__nv_bfloat16*)out, space_f32,
         (__nv_bfloat16*)space_bf16, query_mode);
