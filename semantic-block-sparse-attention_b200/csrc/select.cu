@@ -17,6 +17,7 @@
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
+#include "attn_common.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -32,9 +33,11 @@ constexpr float LN2 = 0.6931471805599453f;
 
 template <int D>
 struct ScoreSmem {
-  static constexpr int A_BYTES = 128 * D * 2;
   static constexpr int B_BYTES = SC_BN * D * 2;
-  static constexpr int BAR_OFF = A_BYTES + SC_STAGES * B_BYTES;
+  static constexpr int BAR_OFF = SC_STAGES * B_BYTES;
+  static constexpr int Q_COL = 2 * SC_BN;            // TMEM: two accumulators, then the routing vectors (D / 2 columns)
+  static constexpr int TMEM_COLS = 512;              // allocation (a power of two >= Q_COL + D / 2)
+  static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory budget");
   static constexpr int XCHG_OFF = BAR_OFF + 256;               // float [2][128][2]: (max, sum) of a half-row
   static constexpr int TOTAL = XCHG_OFF + 2048 + 1024;
 };
@@ -65,7 +68,7 @@ __device__ __forceinline__ int head_butterfly(float (&v)[32], int lane) {
 
 template <int D, int G>
 __global__ void __launch_bounds__(320, 1)
-score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D] bf16, box (64, G, 128/G)
+score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
              const __grid_constant__ CUtensorMap tmap_cb,   // codebooks [Hkv*2, C, D/2] bf16, box (64, 128, 1)
              int num_queries, int num_clusters, const int32_t* __restrict__ sizes,   // [Hkv, C]
              float scale_log2,                     // log2(e) / temperature
@@ -77,13 +80,12 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
   constexpr int SLABS = D / 64;
   constexpr int SLABS_PER_HALF = SLABS / 2;
   constexpr int QT = 128 / G;
-  uint8_t* a_smem = smem;
-  uint8_t* b_smem = smem + L::A_BYTES;
+  uint8_t* b_smem = smem;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xchg = reinterpret_cast<float*>(smem + L::XCHG_OFF);
-  // bars: 0 a_full, 1..2 b_full, 3..4 b_empty, 5..6 acc_full, 7..8 acc_empty, 9 epilogue rendezvous
+  // bars: 0 a_full (the routing vectors are in tensor memory), 1..2 b_full, 3..4 b_empty, 5..6 acc_full, 7..8 acc_empty, 9 epilogue rendezvous
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -92,7 +94,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
   const int total = 2 * chunks;                    // two passes over the codebook
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[0]), 256);
     for (int s = 0; s < SC_STAGES; ++s) {
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
@@ -104,7 +106,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_alloc(smem_u32(tmem_slot), L::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -114,11 +116,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
 
   if (warp == 8) {
     if (elect_one()) {
-      tma_prefetch_desc(&tmap_q);
       tma_prefetch_desc(&tmap_cb);
-      mbar_arrive_expect_tx(smem_u32(&bars[0]), L::A_BYTES);
-      for (int sl = 0; sl < SLABS; ++sl)
-        tma_load_3d(smem_u32(a_smem + sl * 128 * 128), &tmap_q, smem_u32(&bars[0]), sl * 64, h * G, q0);
       for (int j = 0; j < total; ++j) {
         const int s = j % SC_STAGES;
         if (!mbar_wait(smem_u32(&bars[3 + s]), ((j / SC_STAGES) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_LOAD))
@@ -139,12 +137,11 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
         if (!mbar_wait(smem_u32(&bars[1 + s]), (j / SC_STAGES) & 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
         if (!mbar_wait(smem_u32(&bars[7 + b]), ((j >> 1) & 1) ^ 1, abort_flag, status, STATUS_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint32_t a_base = smem_u32(a_smem);
         const uint32_t b_base = smem_u32(b_smem + s * L::B_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-          umma_ss(tmem_base + b * SC_BN, make_smem_desc(a_base + sl * 128 * 128 + ko, 16, 1024),
+          umma_ts(tmem_base + b * SC_BN, tmem_base + L::Q_COL + kk * 8,
                   make_smem_desc(b_base + sl * SC_BN * 128 + ko, 16, 1024), idesc, kk > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&bars[3 + s]));
@@ -157,6 +154,11 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
     const int hf = warp >> 2;
     const int row = threadIdx.x & 127;
     const int qi = q0 + row / G;
+    // the routing vectors go to tensor memory once: each of the two threads of a row copies half
+    // of its dims (rows past the last query are zero)
+    attn::stage_q_half<D, L::Q_COL>(
+        qi < num_queries ? vectors + ((int64_t)qi * (num_kv_heads * G) + h * G + row % G) * D + hf * (D / 2) : nullptr, hf,
+        (uint32_t)((warp & 3) * 32) << 16, tmem_base, smem_u32(&bars[0]));
     // Routing vectors and descriptors are unit vectors (up to bf16 rounding), so every logit is
     // bounded by 1.01 * scale: with a moderate scale the log-sum-exp needs no running maximum.
     const bool fixed_max = scale_log2 <= 60.f;
@@ -272,7 +274,7 @@ score_kernel(const __grid_constant__ CUtensorMap tmap_q,    // vectors [Q, Hq, D
   }
   __syncthreads();
   if (*abort_flag) __nanosleep(50000);
-  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (warp == 0) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------- threshold selection
@@ -444,12 +446,10 @@ int launch_score(const void* vectors, int num_queries, int num_q_heads, const vo
                  int num_kv_heads, int num_clusters, const int32_t* sizes, float temperature,
                  float beta, float* score, int* status, cudaStream_t st) {
   constexpr int QT = 128 / G;
-  CUtensorMap mq, mc;
-  uint64_t dq[3] = {(uint64_t)D, (uint64_t)num_q_heads, (uint64_t)num_queries};
-  uint64_t sq[2] = {(uint64_t)D * 2, (uint64_t)num_q_heads * D * 2};
-  uint32_t bq[3] = {64, (uint32_t)G, (uint32_t)QT};
-  int rc = semblo::make_tensor_map_bf16(&mq, vectors, 3, dq, sq, bq);
-  if (rc) return rc;
+  CUtensorMap mc;
+  if (reinterpret_cast<uintptr_t>(vectors) & 15)
+    return semblo::fail(semblo::SEMBLO_EINVAL, "routing vectors %p are not 16-byte aligned", vectors);
+  int rc;
   uint64_t dc[3] = {(uint64_t)D / 2, (uint64_t)num_clusters, (uint64_t)num_kv_heads * 2};
   uint64_t sc[2] = {(uint64_t)D, (uint64_t)num_clusters * D};
   uint32_t bc[3] = {64, (uint32_t)SC_BN, 1};
@@ -458,7 +458,7 @@ int launch_score(const void* vectors, int num_queries, int num_q_heads, const vo
   auto kern = score_kernel<D, G>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ScoreSmem<D>::TOTAL));
   dim3 grid((unsigned)ceil_div(num_queries, QT), num_kv_heads);
-  kern<<<grid, 320, ScoreSmem<D>::TOTAL, st>>>(mq, mc, num_queries, num_clusters, sizes,
+  kern<<<grid, 320, ScoreSmem<D>::TOTAL, st>>>((const __nv_bfloat16*)vectors, mc, num_queries, num_clusters, sizes,
                                                LOG2E / temperature, beta, score, num_kv_heads, status);
   SEMBLO_LAUNCH_CHECK();
   return 0;
