@@ -512,6 +512,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler starts before the warm-up: the start-up of its nvidia-smi process (a second
+    # client of the driver) then falls into the untimed steps; it samples until the timed region ends
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step.run(x, out)
     barrier()
@@ -521,8 +525,6 @@ def main():
     step.attended.zero_()
     step.time_attention = True
     step.attn_events = []
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gc.collect()
     gc.disable()                     # no collector pause inside the timed region

@@ -15,6 +15,7 @@
 
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
+#include "attn_common.cuh"
 #include "sm100.cuh"
 
 using namespace sm100;
@@ -177,9 +178,12 @@ constexpr int ASG_STAGES = 2;
 
 template <int D>
 struct AssignSmem {
-  static constexpr int A_BYTES = 128 * D * 2;
+  static constexpr bool A_TMEM = D >= 128;           // the key tile is a tensor-memory operand (D / 2 columns)
+  static constexpr int A_BYTES = A_TMEM ? 0 : 128 * D * 2;
   static constexpr int B_BYTES = ASG_BN * D * 2;
   static constexpr int BAR_OFF = A_BYTES + ASG_STAGES * B_BYTES;
+  static constexpr int X_COL = 2 * ASG_BN;           // TMEM: two accumulators, then the keys
+  static constexpr int TMEM_COLS = A_TMEM ? 512 : 256;
   static constexpr int XCHG_OFF = BAR_OFF + 256;       // (value, id) of the upper-half epilogue threads: [128] float + [128] int
   static constexpr int TOTAL = XCHG_OFF + 1024 + 1024; // + alignment slack
 };
@@ -189,7 +193,8 @@ struct AssignSmem {
 // core (no bf16 rounding), and centroids whose bit is set in dead_bits are never chosen.
 template <int D, bool SPLIT>
 __global__ void __launch_bounds__(320, 1)
-assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
+assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bfloat16* __restrict__ x,
+                     int64_t x_stride,
                      const __grid_constant__ CUtensorMap tmap_c, int64_t n, int num_centroids,
                      int32_t* __restrict__ assign_out, int id_offset,
                      const uint32_t* __restrict__ dead_bits, int* __restrict__ status) {
@@ -210,7 +215,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int64_t row0 = (int64_t)blockIdx.x * 128;
 
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[0]), L::A_TMEM ? 256 : 1);
     for (int s = 0; s < ASG_STAGES; ++s) {
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
@@ -221,7 +226,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 256);
+    tmem_alloc(smem_u32(tmem_slot), L::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -234,11 +239,13 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
   bool epi_ok = false;
   if (warp == 4) {
     if (elect_one()) {
-      tma_prefetch_desc(&tmap_x);
       tma_prefetch_desc(&tmap_c);
-      mbar_arrive_expect_tx(smem_u32(&bars[0]), L::A_BYTES);
-      for (int sl = 0; sl < SLABS; ++sl)
-        tma_load_2d(smem_u32(a_smem + sl * 128 * 128), &tmap_x, smem_u32(&bars[0]), sl * 64, (int)row0);
+      if (!L::A_TMEM) {
+        tma_prefetch_desc(&tmap_x);
+        mbar_arrive_expect_tx(smem_u32(&bars[0]), L::A_BYTES);
+        for (int sl = 0; sl < SLABS; ++sl)
+          tma_load_2d(smem_u32(a_smem + sl * 128 * 128), &tmap_x, smem_u32(&bars[0]), sl * 64, (int)row0);
+      }
       for (int j = 0; j < num_chunks; ++j) {
         const int s = j % ASG_STAGES;
         if (!mbar_wait(smem_u32(&bars[3 + s]), ((j / ASG_STAGES) & 1) ^ 1, abort_flag, status,
@@ -269,9 +276,12 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t sl = kk >> 2, ko = (kk & 3) * 32;
-          uint64_t ad = make_smem_desc(a_base + sl * 128 * 128 + ko, 16, 1024);
           uint64_t bd = make_smem_desc(b_base + sl * ASG_BN * 128 + ko, 16, 1024);
-          umma_ss(tmem_base + b * ASG_BN, ad, bd, idesc, kk > 0 ? 1u : 0u);
+          if (L::A_TMEM)
+            umma_ts(tmem_base + b * ASG_BN, tmem_base + L::X_COL + kk * 8, bd, idesc, kk > 0 ? 1u : 0u);
+          else
+            umma_ss(tmem_base + b * ASG_BN, make_smem_desc(a_base + sl * 128 * 128 + ko, 16, 1024), bd, idesc,
+                    kk > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&bars[3 + s]));
         umma_commit(smem_u32(&bars[5 + b]));
@@ -284,6 +294,12 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int hf = warp >= 6 ? 1 : 0;
     const int row = (warp & 3) * 32 + (threadIdx.x & 31);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    if constexpr (L::A_TMEM) {
+      // the key tile goes to tensor memory once: each of the two threads of a row copies half of it
+      // (rows past the last key are zero)
+      attn::stage_q_half<D, L::X_COL>(row0 + row < n ? x + (row0 + row) * x_stride + hf * (D / 2) : nullptr, hf,
+                                      lane_addr, tmem_base, smem_u32(&bars[0]));
+    }
     float best = -INFINITY;
     int best_id = 0;
     bool ok = true;
@@ -339,7 +355,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x,
   }
   __syncthreads();
   if (*abort_flag) __nanosleep(50000);
-  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (warp == 0) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------ counts
@@ -661,7 +677,8 @@ int launch_assign(const void* x, int64_t n, int64_t x_stride_elems, const void* 
   if (rc) return rc;
   auto kern = assign_argmax_kernel<D, SPLIT>;
   SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AssignSmem<D>::TOTAL));
-  kern<<<(unsigned)ceil_div(n, 128), 320, AssignSmem<D>::TOTAL, st>>>(mx, mc, n, num_centroids, out, id_offset,
+  kern<<<(unsigned)ceil_div(n, 128), 320, AssignSmem<D>::TOTAL, st>>>(mx, (const __nv_bfloat16*)x, x_stride_elems, mc, n,
+                                                                    num_centroids, out, id_offset,
                                                                     dead_bits, status);
   SEMBLO_LAUNCH_CHECK();
   return 0;
