@@ -110,11 +110,15 @@ int semblo_score_clusters(const void* vectors_bf16, int num_queries, int num_q_h
 
 /* semblo/vllm_plugin/fused_select.py:604-647 (_streaming_select_kernel) plus
  * fused_prefill.py:212-216 (_force_sink_bit): the bisected threshold and the packed
- * per-query bitmask qmask [Q, Hkv, C/32]; counts / tokens [Q, Hkv] may be NULL. */
+ * per-query bitmask qmask [Q, Hkv, C/32]; counts / tokens [Q, Hkv] may be NULL.
+ * top1 (no reference counterpart) receives arg max_c of score + tile_key_beta log(1 + n_c), lowest
+ * id on ties: with tile_key_beta = the penalty's beta the cluster of the largest mixture
+ * probability, with 0 the best-scoring cluster.  The caller sorts queries by it to form tiles. */
 int semblo_select_clusters(const float* score, const int32_t* select_sizes, int num_queries,
                            int num_kv_heads, int num_clusters, int target_tokens, int iters,
                            int force_sink, int32_t* qmask, int32_t* counts, int32_t* tokens,
-                           int32_t* top1 /* [Hkv, Q] best-scoring cluster, or NULL */, void* stream);
+                           int32_t* top1 /* [Hkv, Q] tile-order key, or NULL */, float tile_key_beta,
+                           void* stream);
 
 /* Stable arg-sort of small integer keys (keys [heads, n] in [0, max_key), max_key <= 65536):
  * order [heads, n].  Used to put queries with the same best-scoring cluster into the same

@@ -1158,6 +1158,8 @@ extern "C" int semblo_flush_repack(void* packed, int64_t kv_stride_elems, int64_
   SEMBLO_REQUIRE(workspace_bytes >= semblo_flush_workspace_bytes(n, num_kv_heads, num_clusters), "workspace too small");
   SEMBLO_REQUIRE(old_packed_copy != nullptr && old_posting_copy != nullptr, "a copy of the old store is required");
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
+  // old_posting_copy rows are packed_rows apart and the move kernel indexes both postings with one stride
+  SEMBLO_REQUIRE(posting_stride == packed_rows, "the posting list and the packed store must have the same row count");
   if (n == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int H = num_kv_heads, C = num_clusters;
@@ -1181,8 +1183,6 @@ extern "C" int semblo_flush_repack(void* packed, int64_t kv_stride_elems, int64_
   flush_layout_kernel<<<H, 1024, 0, st>>>(sizes, added, C, align, new_sizes, new_indptr, packed_rows, status);
   rc = semblo_append_rows(assign, n, H, C, new_indptr, sizes, rows, added, workspace, append_bytes, stream);
   if (rc) return rc;
-  // (old_posting_copy rows are packed_rows apart; the kernel indexes both postings with one stride)
-  SEMBLO_REQUIRE(posting_stride == packed_rows, "the posting list and the packed store must have the same row count");
   flush_move_kernel<<<(unsigned)ceil_div(packed_rows * H, 8), 256, 0, st>>>(
       (const __nv_bfloat16*)old_packed_copy, old_posting_copy, (int64_t)packed_rows * H * head_dim, posting_stride,
       sizes, indptr, new_sizes, new_indptr, C, H, head_dim, packed_rows, (__nv_bfloat16*)packed, kv_stride_elems,

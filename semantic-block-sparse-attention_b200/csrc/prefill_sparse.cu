@@ -48,16 +48,10 @@ struct Plan {
 };
 static_assert((PLAN_STAGES & (PLAN_STAGES - 1)) == 0, "the ring index is a mask");
 
-#ifndef SEMBLO_GATHER_WARPS
-#define SEMBLO_GATHER_WARPS 3
-#endif
-constexpr int GW = SEMBLO_GATHER_WARPS;     // gather warps per operand; warp w of them takes tiles t = w (mod GW)
+constexpr int GW = 3;     // gather warps per operand; warp w of them takes tiles t = w (mod GW)
 constexpr int W_GATHER = 9, W_MMA = W_GATHER + 2 * GW, W_BIAS = W_MMA + 1;
 constexpr int GATHER_THREADS = 32 * (W_BIAS + 1);
-#ifndef SEMBLO_NSB
-#define SEMBLO_NSB 2
-#endif
-constexpr int NSB = SEMBLO_NSB;       // S buffers: tiles between Q K^T and the end of their softmax
+constexpr int NSB = 2;       // S buffers: tiles between Q K^T and the end of their softmax
 constexpr int BIAS_BYTES = BLOCK_N * 64;     // per tile: 64 keys x 32 query slots, bf16
 constexpr uint32_t BIAS_OFF_BITS = 0xF180u;  // bf16 -2^100: the logit of a key the row's query did not select
 
@@ -67,7 +61,7 @@ constexpr uint32_t BIAS_OFF_BITS = 0xF180u;  // bf16 -2^100: the logit of a key 
 // selected logit bit-exact; a rejected one becomes about -2^100, whose exponential is 0.
 //
 // Tensor memory (512 columns) holds NSB S buffers of 64 columns, O (D columns) and Q (D / 2).
-// With two S buffers everything fits at D = 256; a third one (SEMBLO_NSB = 3) moves the last
+// With two S buffers everything fits at D = 256; a third one (NSB = 3) moves the last
 // 128 dims of Q into shared memory and leaves room for two V stages only.
 template <int D>
 struct GatherCfg {
@@ -123,21 +117,6 @@ struct GatherArgs {
   int* status;
 };
 
-// Optional wait accounting (build with -DSEMBLO_TRACE): every role adds the cycles it spends
-// in each phase to attended[8 + 8 * role + phase]; the buffer must then hold 48 counters.
-#ifdef SEMBLO_TRACE
-#define TR_DECL long long tr_last = clock64(); long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define TR(i) { const long long tr_now = clock64(); tr[i] += tr_now - tr_last; tr_last = tr_now; }
-#define TR_FLUSH(role) if (a.attended && lane == 0) { for (int i_ = 0; i_ < 8; ++i_) if (tr[i_]) atomicAdd(a.attended + 8 + 8 * (role) + i_, (unsigned long long)tr[i_]); }
-// timeline of one CTA: event e of tile T at attended[64 + 256 e + T]
-#define EV(e, T) if (a.attended && blockIdx.x == 5 && blockIdx.y == 0 && (T) < 256) a.attended[64 + 256 * (e) + (T)] = (unsigned long long)clock64();
-#else
-#define TR_DECL
-#define TR(i)
-#define TR_FLUSH(role)
-#define EV(e, T)
-#endif
-
 enum { B_QFULL = 0, B_OREADY = 1, B_EPI = 2, B_QHI = 3, B_PAIR = 4, B_SFULL = 8, B_PFULL = 8 + NSB,
        B_PVDONE = 8 + 2 * NSB, B_KFULL = 8 + 3 * NSB };
 
@@ -192,7 +171,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   const int cta_id = a.cta_order ? a.cta_order[blockIdx.x] : -1;
   const int h = cta_id >= 0 ? cta_id % a.num_kv_heads : (int)blockIdx.y;
   const int q_tile0 = (cta_id >= 0 ? cta_id / a.num_kv_heads : (int)blockIdx.x) * QT;
-  if (threadIdx.x == 0) { EV(14, 0) }
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QFULL), 256);
@@ -246,7 +224,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (threadIdx.x == 0) { EV(14, 1) }
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
@@ -279,9 +256,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     int acq = 0, pub = 0;        // tiles made writable / published so far
     long long pairs = 0;
     bool ok = true;
-    TR_DECL
     auto acquire_to = [&](int upto) {          // make tiles [acq, upto) writable
-      TR(1)
       while (ok && acq < upto) {
         if (lane == 0)
           ok = mbar_wait(bar(B_PLANEMPTY + acq % PLAN_STAGES), ((acq / PLAN_STAGES) & 1) ^ 1, abort_flag, a.status,
@@ -289,7 +264,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
         ++acq;
       }
-      TR(0)
     };
     auto publish_to = [&](int upto, int last_count) {   // publish tiles [pub, upto), the last with last_count rows
       __syncwarp();
@@ -297,7 +271,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         for (int t = pub; t < upto; ++t) {
           plan->count[t % PLAN_STAGES] = t == upto - 1 ? last_count : BLOCK_N;
           mbar_arrive(bar(B_PLANFULL + t % PLAN_STAGES));
-          EV(0, t)
         }
       pub = max(pub, upto);
     };
@@ -329,7 +302,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         start1 = has1 ? ipt[c1] : 0;
       }
       if (any == 0) continue;
-      TR(1)
       // mask_b: the queries of the tile that selected cluster (w, lane) -- the 32 x 32 bit
       // matrix (query lane, cluster bit) transposed across the warp in five exchange steps
       unsigned mask_b = word;
@@ -340,7 +312,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         const unsigned y = __shfl_xor_sync(0xffffffffu, mask_b, d);
         mask_b = (lane & d) ? (((y & ~m) >> d) | (mask_b & ~m)) : ((mask_b & m) | ((y & m) << d));
       }
-      TR(2)
       pairs += (long long)n_b * __popc(mask_b);      // (query, key) pairs this cluster contributes
       int pre = n_b;                                 // inclusive scan over lanes
 #pragma unroll
@@ -354,7 +325,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       const int a_b = pos + pre - n_b, e_b = pos + pre, end = pos + total;
       const int row_minus_pos = start_b - a_b;
       int wlo = pos;
-      TR(3)
       while (wlo < end && ok) {
         // a wave: as far as the plan ring reaches beyond the oldest unpublished tile
         const int whi = min(end, (pub + PLAN_STAGES) * BLOCK_N);
@@ -364,7 +334,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         const bool big = hi - lo > SELF_MAX;
         if (!big)
           for (int p = lo; p < hi; ++p) put(p, row_minus_pos + p, mask_b);
-        TR(4)
         for (unsigned bigs = __ballot_sync(0xffffffffu, big); bigs; bigs &= bigs - 1) {
           const int bb = __ffs(bigs) - 1;
           const int blo = __shfl_sync(0xffffffffu, lo, bb), bhi = __shfl_sync(0xffffffffu, hi, bb);
@@ -372,10 +341,8 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
           const unsigned bmask = __shfl_sync(0xffffffffu, mask_b, bb);
           for (int p = blo + lane; p < bhi; p += 32) put(p, brow + p, bmask);
         }
-        TR(5)
         publish_to(whi / BLOCK_N, BLOCK_N);
         wlo = whi;
-        TR(6)
       }
       pos = end;
     }
@@ -392,8 +359,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       if (lane == 0 && pairs) atomicAdd(a.attended, (unsigned long long)pairs);
       if (lane == 0 && pos) atomicAdd(a.attended + 1, (unsigned long long)pos);
     }
-    TR(1)
-    TR_FLUSH(0)
     // end of stream, once per gather warp of an operand (they take tiles in turn)
     for (int e = 0; e < GW && ok; ++e) {
       acquire_to(pub + 1);
@@ -420,12 +385,9 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     uint32_t dst_off[GROUP];
 #pragma unroll
     for (int u = 0; u < GROUP; ++u) dst_off[u] = swz128(u * ROWS_PER_ITER + sub, chunk);
-    TR_DECL
     for (int t = par;; t += GW) {
       const int ps = t % PLAN_STAGES, s = t % stages;
       if (!mbar_wait(bar(B_PLANFULL + ps), (t / PLAN_STAGES) & 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
-      TR(0)
-      if (lane == 0) { EV(is_v ? 9 : 1, t) }
       const int cnt = plan->count[ps];
       if (cnt == 0) break;
       int r_lo = plan->row[ps * BLOCK_N + lane], r_hi = plan->row[ps * BLOCK_N + lane + 32];
@@ -438,13 +400,8 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         if (lane + 32 < n16) r_hi = a.page_table[r_hi >> 4] * 16 + (r_hi & 15);
       }
       if (!mbar_wait(bar(b_empty + s), ((t / stages) & 1) ^ 1, abort_flag, a.status, STATUS_TIMEOUT_LOAD)) break;
-      TR(1)
-      if (lane == 0) { EV(is_v ? 10 : 2, t) }
       const uint32_t base = smem_u32(smem + (is_v ? C::V_OFF : C::K_OFF) + s * C::KV_BYTES) + slab * (BLOCK_N * 128);
       // 8 copies per step: the row indices are fetched first so the shuffles overlap
-#ifdef SEMBLO_SKIP_COPY
-      if (false)
-#endif
       for (int j0 = 0; j0 < n16; j0 += GROUP * ROWS_PER_ITER) {
         int rows[GROUP];
 #pragma unroll
@@ -454,16 +411,11 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         for (int u = 0; u < GROUP; ++u)
           cp_async16(base + j0 * 128 + dst_off[u], src_lane + (int64_t)rows[u] * row_elems);
       }
-      TR(2)
       cp_async_wait_all();
-      TR(3)
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(b_full + s));
-      if (lane == 0) { EV(is_v ? 4 : 3, t) }
-      TR(4)
     }
-    TR_FLUSH(is_v ? 2 : 1)
   } else if (warp == W_MMA) {
     // ------------------------------------------------------------ UMMA issuer
     // One thread issues S(j) = [Q | E] [K(j) | B(j)]^T and O += P(t) V(t) in the fixed order
@@ -476,13 +428,11 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       if (ok && C::Q_SMEM_DIMS > 0) ok = mbar_wait(bar(B_QHI), 0, abort_flag, a.status, STATUS_TIMEOUT_MMA);
       tc_fence_after();
-      EV(14, 5)
       const uint32_t qhi_base = smem_u32(smem + C::QHI_OFF);
       const uint32_t onehot_base = smem_u32(smem + C::ONEHOT_OFF);
       int ps = 0, ks = 0, qb = 0;                     // ring slots of the next S product
       uint32_t plan_par = 0, k_par = 0;
       bool ended = false;
-      TR_DECL
       auto issue_s = [&](int j) {
         ok = mbar_wait(bar(B_PLANFULL + ps), plan_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
         if (!ok) return;
@@ -501,8 +451,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         ok = mbar_wait(bar(B_KFULL + ks), k_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
         if (!ok) return;
         tc_fence_after();
-        TR(1)
-        EV(12, j)
         const uint32_t k_base = smem_u32(smem + C::K_OFF + ks * C::KV_BYTES);
         const uint32_t bias_base = smem_u32(smem + C::BIAS_OFF + ks * BIAS_BYTES);
         const uint32_t idesc_qk = make_idesc_bf16(128, np * 16, false, false);
@@ -522,8 +470,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
                   make_smem_desc_sw64(bias_base + kk * 32), idesc_qk, 1u);
         umma_commit(bar(B_KEMPTY + ks));
         umma_commit(bar(B_SFULL + qb));
-        TR(2)
-        EV(5, j)
         if (++ps == PLAN_STAGES) { ps = 0; plan_par ^= 1; }
         if (++ks == K_STAGES) { ks = 0; k_par ^= 1; }
         if (++qb == NSB) qb = 0;
@@ -540,8 +486,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
         ok = mbar_wait(bar(B_VFULL + vs), v_par, abort_flag, a.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after();
-        TR(1)
-        EV(13, t)
         const uint32_t v_base = smem_u32(smem + C::V_OFF + vs * C::KV_BYTES);
         for (int kk = 0; kk < np; ++kk)
           umma_ts(tmem_base + C::O_COL, tmem_base + pb * BLOCK_N + (kk >> 1) * 32 + (kk & 1) * 8,
@@ -549,14 +493,11 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
                   (t > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar(B_VEMPTY + vs));
         umma_commit(bar(B_PVDONE + pb));
-        TR(3)
-        EV(6, t)
         if (++vs == V_STAGES) { vs = 0; v_par ^= 1; }
         if (++pb == NSB) { pb = 0; p_par ^= 1; }
         if (!ended) { issue_s(next_s); ++next_s; }
       }
       if (ok) umma_commit(bar(B_OREADY));
-      { const int lane = 0; (void)lane; TR_FLUSH(3) }
     }
   } else if (warp == W_BIAS) {
     // ------------------------------------------------------------ selection operand B
@@ -602,20 +543,16 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     bool ok = true;
     int j = 0, b = 0;
     uint32_t s_par = 0, pv_prev_par = 0;             // pv_prev_par: parity of P V(j - 1) on its buffer
-    TR_DECL
     attn::stage_q_half<C::Q_TMEM_DIMS, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (C::Q_TMEM_DIMS / 2) : nullptr, hf,
                                                  lane_addr, tmem_base, bar(B_QFULL));
     for (;; ++j) {
-      TR(5)
       ok = mbar_wait(bar(B_SFULL + b), s_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
-      TR(1)
       const int np = tile_pages[b];
       if (np == 0) {                        // end of the stream: tell the P V issuer
         mbar_arrive(bar(B_PFULL + b));
         break;
       }
-      if (threadIdx.x == 0) { EV(7, j) }
       tc_fence_after();
       // columns past the tile's pages were not written by this tile's product: lim = 16 np
       ok = attn::softmax_tile<D, C::O_COL>(np, np * 16, j, hf, row, lane_addr, tmem_base, b * BLOCK_N,
@@ -623,21 +560,12 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
                                            pv_prev_par, bar(B_PFULL + b), a.scale_log2, m_ref, l_part, abort_flag,
                                            a.status);
       if (!ok) break;
-      if (lane == 0) { EV(8, j) }
-      TR(4)
       if (++b == NSB) { b = 0; s_par ^= 1; }
       // P V(j) of the tile just finished lives on buffer (j % NSB) with parity (j / NSB) & 1
       pv_prev_par = (uint32_t)((j / NSB) & 1);
     }
-#ifndef SEMBLO_TRACE_WARP
-#define SEMBLO_TRACE_WARP 0
-#endif
-    if (warp == SEMBLO_TRACE_WARP) { TR_FLUSH(4) }
-
-    if (threadIdx.x == 0) { EV(14, 2) }
     if (ok) ok = mbar_wait(bar(B_OREADY), 0, abort_flag, a.status, STATUS_TIMEOUT_EPILOGUE);
     tc_fence_after();
-    if (threadIdx.x == 0) { EV(14, 3) }
     attn::epilogue_half<D, C::O_COL>(ok && j > 0, hf, row, lane_addr, tmem_base,
                                      reinterpret_cast<float*>(smem + C::EPI_OFF), bar(B_EPI), m_ref, l_part,
                                      ok && qvalid, a.merge, a.out + hidx * D,
@@ -646,7 +574,6 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     tc_fence_before();
   }
   __syncthreads();
-  if (threadIdx.x == 0) { EV(14, 4) }
   if (*abort_flag) __nanosleep(50000);
   if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }

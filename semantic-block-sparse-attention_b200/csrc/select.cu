@@ -294,16 +294,24 @@ __device__ __forceinline__ float warp_sumf(float v) {
   return v;
 }
 
+// The key whose arg-max orders the attention tiles: the score with `key_beta` log(1 + n) added back.
+// With key_beta = the penalty's beta that is the cluster of the largest mixture probability, which
+// groups queries by where they point and not by which small cluster the size penalty favours;
+// key_beta = 0 is the arg-max of the score itself.
+__device__ __forceinline__ float tile_key(float score, float n, float key_beta) {
+  return key_beta != 0.f && n > 0.f ? score + key_beta * __logf(1.0f + n) : score;
+}
+
 // One warp per (query, KV head).  Dynamic smem: sizes of the head [C] floats, then one
 // [C] float score row per warp.
 __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, C]
                               const int32_t* __restrict__ sizes,    // [Hkv, C] (sink held out)
                               int num_queries, int num_kv_heads, int num_clusters,
-                              float target_tokens, int iters, int force_sink,
+                              float target_tokens, int iters, int force_sink, float key_beta,
                               int32_t* __restrict__ qmask,          // [Q, Hkv, C/32]
                               int32_t* __restrict__ counts,         // [Q, Hkv] or null
                               int32_t* __restrict__ tokens,         // [Q, Hkv] or null
-                              int32_t* __restrict__ top1) {         // [Hkv, Q] or null: best-scoring cluster
+                              int32_t* __restrict__ top1) {         // [Hkv, Q] or null: the tile-order key
   extern __shared__ float sm[];
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -315,21 +323,22 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
   const int q = blockIdx.x * warps + warp;
   if (q >= num_queries) return;
   const float* row = score + ((int64_t)q * num_kv_heads + h) * num_clusters;
-  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f, kmx = -INFINITY;
   int arg = 0;
   for (int c = lane; c < num_clusters; c += 32) {
     const float s = row[c], n = s_size[c];
     s_score[c] = s;
-    if (s > mx) arg = c;
+    const float key = tile_key(s, n, key_beta);
+    if (key > kmx) { kmx = key; arg = c; }
     mx = fmaxf(mx, s);
     mn = fminf(mn, n > 0.f ? s : 3.4e38f);
     tot += n > 0.f ? n : 0.f;
   }
   __syncwarp();
   if (top1) {
-    // lowest cluster id among the maxima: a grouping key for the attention tiles
-    const float best = warp_max(mx);
-    int cand = mx == best ? arg : 0x7fffffff;
+    // lowest cluster id among the maxima of the key: a grouping key for the attention tiles
+    const float best = warp_max(kmx);
+    int cand = kmx == best ? arg : 0x7fffffff;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
     if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
@@ -372,7 +381,7 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
 template <int PER>
 __global__ void __launch_bounds__(256)
 select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
-                  int num_kv_heads, float target_tokens, int iters, int force_sink,
+                  int num_kv_heads, float target_tokens, int iters, int force_sink, float key_beta,
                   int32_t* __restrict__ qmask, int32_t* __restrict__ counts,
                   int32_t* __restrict__ tokens, int32_t* __restrict__ top1) {
   constexpr int C = PER * 32;
@@ -383,21 +392,23 @@ select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ s
   const float* row = score + ((int64_t)q * num_kv_heads + h) * C;
   const int32_t* sz = sizes + (int64_t)h * C;
   float sc[PER], nn[PER];
-  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f;
+  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f, kmx = -INFINITY;
   int arg = 0;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int c = i * 32 + lane;
     sc[i] = row[c];
     nn[i] = (float)sz[c];
-    if (sc[i] > mx) arg = c;
+    const float key = tile_key(sc[i], nn[i], key_beta);
+    if (key > kmx) { kmx = key; arg = c; }
     mx = fmaxf(mx, sc[i]);
     mn = fminf(mn, nn[i] > 0.f ? sc[i] : 3.4e38f);
     tot += nn[i] > 0.f ? nn[i] : 0.f;
   }
   const float best = warp_max(mx);
   if (top1) {
-    int cand = mx == best ? arg : 0x7fffffff;
+    const float kbest = warp_max(kmx);
+    int cand = kmx == kbest ? arg : 0x7fffffff;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
     if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
@@ -496,7 +507,8 @@ extern "C" int semblo_score_clusters(const void* vectors_bf16, int num_queries, 
 extern "C" int semblo_select_clusters(const float* score, const int32_t* select_sizes,
                                       int num_queries, int num_kv_heads, int num_clusters,
                                       int target_tokens, int iters, int force_sink, int32_t* qmask,
-                                      int32_t* counts, int32_t* tokens, int32_t* top1, void* stream) {
+                                      int32_t* counts, int32_t* tokens, int32_t* top1, float tile_key_beta,
+                                      void* stream) {
   SEMBLO_REQUIRE(num_clusters % 32 == 0, "cluster count %d must be a multiple of 32", num_clusters);
   if (num_queries == 0) return 0;
   cudaStream_t st_sel = (cudaStream_t)stream;
@@ -504,8 +516,8 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   if (num_clusters == PER * 32) {                                                                   \
     dim3 grid_r((unsigned)ceil_div(num_queries, 8), num_kv_heads);                                  \
     select_kernel_reg<PER><<<grid_r, 256, 0, st_sel>>>(score, select_sizes, num_queries, num_kv_heads, \
-                                                      (float)target_tokens, iters, force_sink, qmask, \
-                                                      counts, tokens, top1);                        \
+                                                      (float)target_tokens, iters, force_sink,      \
+                                                      tile_key_beta, qmask, counts, tokens, top1);  \
     SEMBLO_LAUNCH_CHECK();                                                                          \
     return 0;                                                                                       \
   }
@@ -523,7 +535,7 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   dim3 grid((unsigned)ceil_div(num_queries, warps), num_kv_heads);
   select_kernel<<<grid, warps * 32, smem, (cudaStream_t)stream>>>(
       score, select_sizes, num_queries, num_kv_heads, num_clusters, (float)target_tokens, iters,
-      force_sink, qmask, counts, tokens, top1);
+      force_sink, tile_key_beta, qmask, counts, tokens, top1);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

@@ -100,10 +100,7 @@ __device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity,
 // Bounded wait.  `abort_flag` lives in shared memory, `status` in global memory.  Each try
 // may sleep in hardware for SLEEP_NS (it returns as soon as the phase completes), so a waiting
 // warp leaves the issue slots to the warps that have work.
-#ifndef SEMBLO_SLEEP_NS
-#define SEMBLO_SLEEP_NS 20000
-#endif
-constexpr uint32_t SLEEP_NS = SEMBLO_SLEEP_NS;
+constexpr uint32_t SLEEP_NS = 20000;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;

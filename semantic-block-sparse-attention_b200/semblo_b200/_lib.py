@@ -50,7 +50,7 @@ _SIGNATURES = {
     "semblo_pack_kv": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "semblo_snapshot_advance": (c_int, [c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "semblo_score_clusters": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p]),
-    "semblo_select_clusters": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_select_clusters": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "semblo_argsort_keys": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p]),
     "semblo_nearest_cluster": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_append_rows": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
@@ -123,23 +123,53 @@ STATUS_TEXT = {0: "ok", 101: "load wait timed out", 102: "mma wait timed out", 1
 
 
 class DeviceStatus:
-    """The int32 status word kernels report device-side conditions into."""
+    """The int32 status word kernels report device-side conditions into.
+
+    Kernels that change a store refuse to run while the word is non-zero, so the word has to be
+    looked at: :meth:`raise_if_set` reads it now (one host synchronisation); :meth:`poll` never
+    blocks - it raises what an earlier poll's copy has brought back and queues the next copy, so
+    a loop that polls once per chunk or per step learns of a device-side condition one call late."""
 
     def __init__(self, device) -> None:
         self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self._host = None
+        self._event = None
+
+    def _raise(self, code: int) -> None:
+        self.word.zero_()
+        raise RuntimeError(f"semblo_b200 kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
 
     def raise_if_set(self) -> None:
+        self._event = None
         code = int(self.word.item())
         if code:
-            self.word.zero_()
-            raise RuntimeError(f"semblo_b200 kernel status {code}: {STATUS_TEXT.get(code, 'unknown')}")
+            self._raise(code)
+
+    def poll(self) -> None:
+        if torch.cuda.is_current_stream_capturing():
+            return
+        if self._event is not None:
+            if not self._event.query():
+                return
+            self._event = None
+            code = int(self._host[0])
+            if code:
+                self._raise(code)
+        if self._host is None:
+            self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._host.copy_(self.word, non_blocking=True)
+        self._event = torch.cuda.Event()
+        self._event.record()
 
 
 _STATUS: dict = {}
 
 
 def status_for(device) -> DeviceStatus:
-    key = torch.device(device).index or 0
+    """The status word shared by the calls on ``device`` (a device given without an index means the
+    current one)."""
+    index = torch.device(device).index
+    key = torch.cuda.current_device() if index is None else index
     if key not in _STATUS:
-        _STATUS[key] = DeviceStatus(device)
+        _STATUS[key] = DeviceStatus(torch.device("cuda", key))
     return _STATUS[key]

@@ -94,3 +94,4 @@ def fused_decode_step(layer, arena, *, q_post: torch.Tensor, q_pre: torch.Tensor
         ptr(arena.prompt_length_t), hq, hkv, d, c, float(temperature), float(beta), int(target_tokens), sink,
         int(iters), float(sm_scale), splits, ptr(ws.buffer), ws.bytes, ptr(output), ptr(status.word),
         int(stage_mask), stream_ptr()))
+    status.poll()          # non-blocking; a step learns of the previous step's device-side condition

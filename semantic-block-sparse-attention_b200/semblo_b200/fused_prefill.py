@@ -48,11 +48,13 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
                               temperature: float, beta: float, target_tokens: int, iters: int = 16,
                               qmask: torch.Tensor | None = None, score: torch.Tensor | None = None,
                               force_sink: bool = False, counts: torch.Tensor | None = None,
-                              tokens: torch.Tensor | None = None, top1: torch.Tensor | None = None):
+                              tokens: torch.Tensor | None = None, top1: torch.Tensor | None = None,
+                              tile_key_beta: float = 0.0):
     """Scores + bisected threshold -> per-query packed bitmask [Q, Hkv, C/32].
 
     vectors [Q, Hq, D] bf16 routing vectors; select_sizes [Hkv, C] int32 (one snapshot for
-    the whole chunk, the sink cluster already held out).  Returns (qmask, score)."""
+    the whole chunk, the sink cluster already held out).  ``top1`` [Hkv, Q] receives the tile-order
+    key: arg max of score + tile_key_beta log(1 + n).  Returns (qmask, score)."""
     require_cuda(vectors, codebooks, select_sizes)
     q_count, num_q_heads, dim = vectors.shape
     num_kv_heads, _, num_clusters, _ = codebooks.shape
@@ -67,7 +69,7 @@ def theta_select_bitmask_flat(vectors: torch.Tensor, codebooks: torch.Tensor, se
                                       ptr(score), ptr(status.word), stream_ptr()))
     check(lib().semblo_select_clusters(ptr(score), ptr(select_sizes), q_count, num_kv_heads, num_clusters,
                                        int(target_tokens), int(iters), 1 if force_sink else 0, ptr(qmask),
-                                       ptr(counts), ptr(tokens), ptr(top1), stream_ptr()))
+                                       ptr(counts), ptr(tokens), ptr(top1), float(tile_key_beta), stream_ptr()))
     return qmask, score
 
 
@@ -185,6 +187,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
             _timer("stop")
         return res
     base = snapshot_state.advance(wstart - 1)
+    status = _lib.status_for(q_chunk.device)
     sink = _fitted_sink_tokens()
     if sink:
         if snapshot_state.select_sizes is None:
@@ -216,9 +219,9 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     qmask, _ = theta_select_bitmask_flat(vectors, index.codebooks, select_sizes, temperature=temperature,
                                          beta=beta, target_tokens=select_target, iters=iters,
                                          qmask=snap.qmask[:q_count], score=snap.score[:q_count],
-                                         force_sink=bool(sink), top1=top1)
-    # queries with the same best-scoring cluster select nearly the same clusters: tiles are
-    # formed in that order so a tile's union of selections stays close to a single selection
+                                         force_sink=bool(sink), top1=top1, tile_key_beta=beta)
+    # queries whose largest mixture probability falls on the same cluster select nearly the same
+    # clusters: tiles are formed in that order so a tile's union of selections stays small
     argsort_keys(top1, index.num_buckets, out=order, workspace=snap.sort_ws)
     # the CTAs with the most rows to gather start first
     n_cta = ((q_count + 128 // (num_q_heads // index.num_kv_heads) - 1) // (128 // (num_q_heads // index.num_kv_heads))) * index.num_kv_heads
@@ -245,4 +248,5 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                             partial=partial, cta_order=cta_order)
     if _timer:
         _timer("stop")
+    status.poll()
     return out

@@ -14,6 +14,7 @@ from . import flat_index
 from ._lib import check, lib, ptr, require_cuda, stream_ptr
 
 _PACK_ALIGN = 256          # state.py:17
+HEAD_SEED_STRIDE = 1000003
 
 
 def _sink_tokens() -> int:
@@ -81,11 +82,17 @@ class ProductPostingIndex:
     def build(cls, product_keys: torch.Tensor, positions: torch.Tensor, *, num_centroids: int = 0,
               kmeans_iters: int = 4, kmeans_sample_size: int = 8192, codebook_seed: int | None = None,
               flat_unit_tokens: int = 0, flat_min_clusters_log2: int = 9, page_align: int = 0,
-              layer_idx: int | None = None, centroids: list | None = None, **unused) -> "ProductPostingIndex":
+              layer_idx: int | None = None, centroids: list | None = None, num_clusters: int = 0,
+              per_head_seed: bool = False, head_offset: int = 0, **unused) -> "ProductPostingIndex":
         """Fit the per-prompt partition and lay out the posting lists (state.py:476-948).
 
         ``product_keys`` [L, Hkv, I] is the key router's output.  ``centroids`` (one
-        fp32 [C or C-1, I] tensor per head) skips the fit: assignment and layout only."""
+        fp32 [C or C-1, I] tensor per head) skips the fit: assignment and layout only.
+        ``num_clusters`` > 0 fixes the cluster count (as SEMBLO_FLAT_CLUSTERS does).
+        ``per_head_seed`` (not a reference mode: the reference draws all heads from one generator in
+        order, state.py:520-523, 648) re-seeds the generator for head h with ``codebook_seed +
+        HEAD_SEED_STRIDE (head_offset + h)``, so the partition of a head does not depend on which other
+        heads this process holds: a KV-head shard then equals the same heads of an unsharded build."""
         require_cuda(product_keys)
         if product_keys.ndim != 3:
             raise ValueError("product_keys must have shape [L,Hkv,I]")
@@ -104,7 +111,8 @@ class ProductPostingIndex:
         if codebook_seed is not None:
             generator = torch.Generator(device=device)
             generator.manual_seed(int(codebook_seed))
-        num_clusters = flat_num_clusters(length, flat_target, flat_min_clusters_log2)
+        num_clusters = int(num_clusters) if num_clusters > 0 else flat_num_clusters(length, flat_target,
+                                                                                    flat_min_clusters_log2)
         per_centroid = int(os.environ.get("SEMBLO_FLAT_FIT_PER_C", "32"))
         fit_sample = min(length, max(int(kmeans_sample_size), per_centroid * num_clusters))
         fit_iters = int(os.environ.get("SEMBLO_FLAT_FIT_ITERS", "8"))
@@ -118,7 +126,11 @@ class ProductPostingIndex:
         half = index_dim // 2
         codebooks = torch.empty(num_kv_heads, 2, num_clusters, half, dtype=torch.bfloat16, device=device)
         assign = torch.empty(num_kv_heads, length, dtype=torch.int32, device=device)
+        if per_head_seed and codebook_seed is None:
+            raise ValueError("per_head_seed needs a codebook_seed")
         for h in range(num_kv_heads):
+            if per_head_seed:
+                generator.manual_seed(int(codebook_seed) + HEAD_SEED_STRIDE * (int(head_offset) + h))
             keys = product_keys[:, h]
             _, space_f32, space_bf16 = flat_index._normalize_space(keys)
             if sink:

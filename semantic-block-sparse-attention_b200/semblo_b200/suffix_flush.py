@@ -50,13 +50,15 @@ def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     old_packed = torch.empty_like(arena.packed_kv)
     old_posting = torch.empty_like(arena.posting)
-    status = _lib.status_for(dev)
+    # the flush has a status word of its own: a stale code of another call cannot gate it, and the
+    # host-side state below is committed only after the device has accepted the new layout
+    status = _lib.DeviceStatus(dev)
     check(lib().semblo_flush_repack(ptr(arena.packed_kv), arena.packed_kv.stride(0), width, ptr(arena.posting),
                                     arena.posting.stride(0), ptr(arena.sizes), ptr(arena.indptr), c, hkv, d, align,
                                     ptr(k), ptr(v), ptr(pos.to(torch.int32)), ptr(assign), n, ptr(old_packed),
                                     ptr(old_posting), ptr(ws), ws_bytes, ptr(status.word), stream_ptr()))
+    status.raise_if_set()        # refused (the result would not fit): the store is unchanged, as after the
+                                 # reference's repack_apply, which raises before it moves anything
     arena.prompt_length_t.fill_(int(to))
     arena.extend_suffix_table(int(to) + arena.reserve - 1)
-    widest = int(arena.indptr[:, -1].max().item())
-    status.raise_if_set()
-    return widest
+    return int(arena.indptr[:, -1].max().item())

@@ -203,6 +203,8 @@ class TokenOuterPrefillSession:
         if self.index is None:
             self.fit_at = self.tokens              # the prompt ended before the fit point: fit on all of it
             self._fit_and_pack()
+        # the store kernels refuse to run after a device-side condition: the end of the prompt reads the word
+        _lib.status_for(self.device).raise_if_set()
 
     # -- dense start ---------------------------------------------------------------------
     def _stage(self, k3, v3, kp3, start, stop) -> None:
@@ -220,13 +222,11 @@ class TokenOuterPrefillSession:
         p = self.fit_at
         clusters = flat_num_clusters(self.tokens, self.unit, self.min_log2)
         product = routing_normalize(self.stage_kpre[:p])
-        os.environ["SEMBLO_FLAT_CLUSTERS"] = str(clusters)      # the count the whole prompt would get
-        try:
-            index = ProductPostingIndex.build(product, self.positions[:p], kmeans_sample_size=self.sample,
-                                              codebook_seed=self.seed, flat_unit_tokens=self.unit,
-                                              flat_min_clusters_log2=self.min_log2, page_align=self.align)
-        finally:
-            del os.environ["SEMBLO_FLAT_CLUSTERS"]
+        # the count the whole prompt would get (the reference passes it through SEMBLO_FLAT_CLUSTERS)
+        index = ProductPostingIndex.build(product, self.positions[:p], kmeans_sample_size=self.sample,
+                                          codebook_seed=self.seed, flat_unit_tokens=self.unit,
+                                          flat_min_clusters_log2=self.min_log2, page_align=self.align,
+                                          num_clusters=clusters)
         del product
         align = max(int(index.page_align), 1)
         width = self.tokens + int(index.num_buckets) * align

@@ -533,7 +533,7 @@ def test_threshold_selection_on_given_scores_is_exact(dev, clusters):
     top1 = torch.empty(hkv, nq, dtype=torch.int32, device=dev)
     score_d, sizes_d = score.to(dev), sizes.to(dev)          # keep the device copies alive across the call
     check(lib().semblo_select_clusters(ptr(score_d), ptr(sizes_d), nq, hkv, clusters, target, 16, 0,
-                                       ptr(qmask), ptr(counts), ptr(tokens), ptr(top1), stream_ptr()))
+                                       ptr(qmask), ptr(counts), ptr(tokens), ptr(top1), 0.0, stream_ptr()))
     assert torch.equal(O.unpack_bits(qmask.cpu()), want)
     assert torch.equal(counts.cpu(), want.sum(-1).int())
     assert torch.equal(tokens.cpu(), (want * sizes[None]).sum(-1).int())
