@@ -253,7 +253,7 @@ def kernel_launches(calls: dict, clusters: int) -> int:
                 "semblo_build_layout": 2 + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
                 "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_window_prefill": 1, "semblo_sparse_prefill_gather": 1, "semblo_gather_launch_order": 2,
                 "semblo_argsort_keys": 3 * passes,
-                "semblo_decode_step": 4}
+                "semblo_decode_step": 3}
     return sum(per_call.get(k, 0) * v for k, v in calls.items())
 
 
@@ -337,27 +337,58 @@ def decode_measure(device, pk):
     torch.cuda.synchronize()
     _lib.status_for(device).raise_if_set()
     graph_us = sorted(a.elapsed_time(b) * 1e3 for a, b in gev)
-    # each kernel alone (stage masks 1, 2, 4): the attend kernel has its own roofline
-    stage_us = {}
-    for name, mask in (("score", 1), ("select", 2), ("attend", 4)):
-        aev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(64)]
-        for a, b in aev:
-            flush.zero_()
+    # sixteen steps back to back in one graph (same query, so the codebook and the rows stay in L2):
+    # what a step costs without the launch of a graph around it
+    g16 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g16):
+        for _ in range(16):
+            step()
+    b2b = []
+    for _ in range(16):
+        a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a_ev.record()
+        g16.replay()
+        b_ev.record()
+        b2b.append((a_ev, b_ev))
+    torch.cuda.synchronize()
+    back_to_back_us = sorted(a.elapsed_time(b) * 1e3 / 16 for a, b in b2b)
+    # Each kernel alone (stage masks 1, 2, 4).  A graph of one small kernel between two events already
+    # measures about 6 us on this part, so a stage is timed as the difference of two graphs: L2 flush +
+    # stage, and the L2 flush alone - what the kernel adds to a stream that is already running.
+    def graph_of(fn):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g
+
+    def timed(g, n=48):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for a, b in evs:
             a.record()
-            fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t, k_post=None,
-                              v_states=None, k_pre=None, output=out, temperature=cfg["temperature"],
-                              beta=cfg["beta"], target_tokens=cfg["target"], sm_scale=sm_scale,
-                              num_splits=cfg["splits"], stage_mask=mask)
+            g.replay()
             b.record()
         torch.cuda.synchronize()
-        stage_us[name] = sorted(a.elapsed_time(b) * 1e3 for a, b in aev)
-    attend_us = stage_us["attend"]
+        return sorted(a.elapsed_time(b) * 1e3 for a, b in evs)
+
+    def stage(mask):
+        fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t, k_post=None,
+                          v_states=None, k_pre=None, output=out, temperature=cfg["temperature"],
+                          beta=cfg["beta"], target_tokens=cfg["target"], sm_scale=sm_scale,
+                          num_splits=cfg["splits"], stage_mask=mask)
+
     med = lambda v: v[len(v) // 2]
+    flush_only = med(timed(graph_of(lambda: flush.zero_())))
+    stage_us = {}
+    for name, mask in (("score", 1), ("select", 2), ("attend", 4)):
+        g = graph_of(lambda mask=mask: (flush.zero_(), stage(mask)))
+        stage_us[name] = [max(0.0, v - flush_only) for v in timed(g)]
+    attend_us = stage_us["attend"]
     gathered = (n_rows + n_suffix) * dim * 2 * 2 + n_rows * 4
     codebook = hkv * clusters * dim * 2 + hkv * clusters * 8
     return {
         "metric": "decode_us_per_step", "context": L, "clusters": clusters, "steps": steps,
-        "eager_us": med(eager_us), "graph_us": med(graph_us), "attend_kernel_us": med(attend_us),
+        "eager_us": med(eager_us), "graph_us": med(graph_us), "graph_back_to_back_warm_us": med(back_to_back_us),
+        "stage_timing": "graph(L2 flush + stage) - graph(L2 flush)", "attend_kernel_us": med(attend_us),
         "score_kernel_us": med(stage_us["score"]), "select_kernel_us": med(stage_us["select"]),
         "selected_rows": n_rows, "gathered_bytes": gathered, "codebook_bytes": codebook,
         "roofline_attend": {"bound": "hbm", "achieved": gathered / (med(attend_us) * 1e-6) / 1e9, "peak": pk["hbm"],

@@ -250,12 +250,13 @@ int64_t semblo_decode_workspace_bytes(int num_q_heads, int num_kv_heads, int hea
                                       int num_clusters, int64_t packed_width, int num_splits);
 
 /* Byte offsets of the workspace members, in order: tickets, logit [Hkv, G, C] f32,
- * block (max, sum) partials, score [Hkv, C] f32, rstart, rlen, rcum [Hkv, C] i32,
- * rcount, rtokens [Hkv] i32, rows [Hkv, packed_width] i32, pacc, pml, vectors [Hq, D] bf16.
- * The workspace must be zeroed once before its first use. */
+ * block (max, sum) partials, split records [Hkv, splits, 4] i32 (CSR entry, offset inside it, selected
+ * rows, selected clusters),
+ * rstart, rlen, rcum [Hkv, C] i32 (the CSR of fused_decode.py:189-199), rcount, rtokens [Hkv] i32,
+ * pacc, pml, vectors [Hq, D] bf16.  The workspace must be zeroed once before its first use. */
 int semblo_decode_workspace_offsets(int num_q_heads, int num_kv_heads, int head_dim,
                                     int num_clusters, int64_t packed_width, int num_splits,
-                                    int64_t* offsets /* host, [13] */);
+                                    int64_t* offsets /* host, [12] */);
 
 /* semblo/vllm_plugin/fused_decode.py:393-521 (fused_decode_step): the whole decode step of
  * one layer over the decode arena (semblo/vllm_plugin/arena.py:66-253): suffix write at
@@ -263,7 +264,11 @@ int semblo_decode_workspace_offsets(int num_q_heads, int num_kv_heads, int head_
  * the sink rule, attention over the selected rows with posting <= position plus the
  * suffix positions [prompt_length, position], merged into output [Hq * D] bf16.
  * k_post / v_new / k_pre [Hkv, D] may be NULL (layers sharing another layer's K/V).
- * stage_mask: bit 0 score + suffix write, bit 1 select, bit 2 attend + merge (7 = all). */
+ * stage_mask: bit 0 score + suffix write, bit 1 select, bit 2 attend + merge (7 = all); bit 3
+ * set: every stage is launched strictly after the one before it (without it the select and
+ * attend kernels are programmatic dependent launches that start while their predecessor drains
+ * and wait for it before reading its results).  1 <= iters <= 16, num_clusters a multiple of 32
+ * up to 16384. */
 int semblo_decode_step(const void* q_post, const void* q_pre, const void* k_post, const void* v_new,
                        const void* k_pre, const void* positions, int pos_is_int64,
                        const void* codebooks, const int32_t* sizes, const int32_t* indptr,

@@ -4,14 +4,20 @@
 //
 // The step is HBM-bound (codebook read + gathered K/V rows), so the kernels are
 // plain coalesced 16-byte loads spread over the whole GPU:
-//   decode_score_kernel   grid [Hkv, blocks]: suffix write (block 0,0), router, logits of a
-//                         slice of the codebook and the slice's (max, sum-exp) per head
-//   decode_penalise_kernel grid [Hkv, C / 256]: log-sum-exp, cluster probabilities, penalised score
-//   decode_select_kernel  grid [Hkv]: bisection, CSR (start, len, cum) and the flat list of
-//                         selected rows
-//   decode_attend_kernel  grid [Hkv, splits]: each half-warp streams whole K/V rows
-//                         (16 lanes x 16 B = one 256-B request per row and tensor); the last
-//                         CTA of a head merges the splits and writes the output
+//   decode_score_kernel   grid [Hkv, blocks + 1]: router, logits of a slice of the codebook and the
+//                         slice's (max, sum-exp) per head; the extra block row writes the
+//                         token's K/V into the suffix store
+//   decode_select_kernel  grid [8, Hkv], one thread-block cluster per head: log-sum-exp,
+//                         penalised scores, the bisected threshold as a radix select over the
+//                         clusters' paths through the tree of midpoints (histograms summed
+//                         through distributed shared memory), CSR (start, len, cum) in cluster
+//                         order and the CSR position where every attention split starts
+//   decode_attend_kernel  grid [Hkv, splits]: expands its own slice of the CSR, brings all its
+//                         K/V rows into shared memory with 16-byte asynchronous copies in one
+//                         go, then one warp per row; the last CTA of a head merges the splits
+//                         and writes the output
+// The select and attend kernels are launched as programmatic dependents: they start while the
+// kernel before them drains and wait (griddepcontrol.wait) before they touch its results.
 // No host reads, no allocations, fixed addresses: the step can be captured in a CUDA graph.
 //
 // Reference behaviour restated here:
@@ -26,7 +32,12 @@
 #include "host_common.h"
 #include "sm100.cuh"
 
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 using semblo::ceil_div;
+using sm100::pdl_launch_dependents;
+using sm100::pdl_wait;
 
 namespace {
 
@@ -58,10 +69,9 @@ struct DecodeArgs {
   // workspace
   float* ws_logit;      // [Hkv, G, C]
   float* ws_ml;         // [Hkv, score_blocks, G, 2]
-  float* ws_score;      // [Hkv, C]
   int32_t *rstart, *rlen, *rcum;   // [Hkv, C]
   int32_t *rcount, *rtokens;       // [Hkv]
-  int32_t* rows;        // [Hkv, packed_width]
+  int32_t* split_start; // [Hkv, splits, 4] per split: CSR entry and offset inside it where its rows begin, selected rows, selected clusters
   float* pacc;          // [Hq, splits, D]
   float* pml;           // [Hq, splits, 2]
   int32_t* tickets;     // [Hkv]
@@ -128,9 +138,12 @@ decode_score_kernel(const DecodeArgs a) {
   const int h = blockIdx.x, blk = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int C = a.num_clusters;
+  pdl_launch_dependents();            // the select kernel may take its seats; it waits for this grid to finish
 
-  if (h == 0 && blk == 0 && a.k_post != nullptr) {
-    // the token's K/V (and pre-RoPE key) into the suffix store
+  if (blk == gridDim.y - 1) {
+    // The extra block row: head 0's CTA writes the token's K/V (and pre-RoPE key) into the suffix
+    // store and does nothing else, so no scoring CTA carries that chain of dependent loads.
+    if (h != 0 || a.k_post == nullptr) return;
     const long long pos = load_pos(a);
     const long long block = pos / a.suffix_block;
     if (block >= 0 && block < a.table_len) {
@@ -138,14 +151,16 @@ decode_score_kernel(const DecodeArgs a) {
       const long long off = pos - block * a.suffix_block;
       const int64_t plane = (int64_t)a.suffix_blocks * a.suffix_block * a.num_kv_heads * D;
       const int64_t dst = (phys * a.suffix_block + off) * a.num_kv_heads * D;
-      for (int i = threadIdx.x; i < a.num_kv_heads * D; i += blockDim.x) {
-        a.suffix_kv[dst + i] = a.k_post[i];
-        a.suffix_kv[plane + dst + i] = a.v_new[i];
-        if (a.suffix_kpre && a.k_pre) a.suffix_kpre[dst + i] = a.k_pre[i];
+      for (int i = threadIdx.x * 8; i < a.num_kv_heads * D; i += blockDim.x * 8) {
+        *reinterpret_cast<uint4*>(a.suffix_kv + dst + i) = *reinterpret_cast<const uint4*>(a.k_post + i);
+        *reinterpret_cast<uint4*>(a.suffix_kv + plane + dst + i) = *reinterpret_cast<const uint4*>(a.v_new + i);
+        if (a.suffix_kpre && a.k_pre)
+          *reinterpret_cast<uint4*>(a.suffix_kpre + dst + i) = *reinterpret_cast<const uint4*>(a.k_pre + i);
       }
     } else if (threadIdx.x == 0) {
       atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
     }
+    return;
   }
   // A row (both halves of the codebook) is read by LPR lanes, 16 bytes each: lanes [0, LPR/2)
   // take half 0, the rest half 1.  The first SU rows of every lane group are requested before
@@ -156,7 +171,8 @@ decode_score_kernel(const DecodeArgs a) {
   constexpr int SU = 16;
   const int sub = lane / LPR, l_in = lane % LPR;
   const int f = l_in / (LPR / 2), chunk = l_in % (LPR / 2);
-  const int per_block = (int)ceil_div(C, gridDim.y);
+  const int nblk = gridDim.y - 1;                     // scoring blocks (the last block row is the suffix write)
+  const int per_block = (int)ceil_div(C, nblk);
   const int c_lo = blk * per_block, c_hi = min(C, c_lo + per_block);
   const __nv_bfloat16* cb = a.codebooks + ((int64_t)(h * 2 + f) * C) * HALF + chunk * 8;
   uint4 raw[SU];
@@ -253,403 +269,628 @@ decode_score_kernel(const DecodeArgs a) {
     const int t = threadIdx.x;
     float m = -INFINITY, l = 0.f;
     for (int w = 0; w < 8; ++w) merge(m, l, red[w][t][0], red[w][t][1]);
-    float* dst = a.ws_ml + (((int64_t)h * gridDim.y + blk) * G + t) * 2;
+    float* dst = a.ws_ml + (((int64_t)h * nblk + blk) * G + t) * 2;
     dst[0] = m;
     dst[1] = l;
   }
 }
 
 // ------------------------------------------------------------------ select
-constexpr int SEL_THREADS = 1024;
-constexpr int SEL_MAX_PER = 16;        // clusters per thread: C <= 16384
-constexpr int SEL_CSR_SMEM = 2048;     // selected clusters whose (start, cum) are searched in shared memory
-constexpr int PEN_THREADS = 256;
+// One thread-block cluster of SEL_CL CTAs per KV head.  A thread owns SEL_PER consecutive
+// clusters; CTA r of the head owns clusters [r C / SEL_CL, (r + 1) C / SEL_CL).
+constexpr int SEL_CL = 8;
+constexpr int SEL_THREADS = 512;
+constexpr int SEL_PER = 4;
+constexpr int SEL_MAX_CLUSTERS = SEL_CL * SEL_THREADS * SEL_PER;     // 16384
+constexpr int SEL_WARPS = SEL_THREADS / 32;
 
-// Penalised score of every cluster: grid [Hkv, C / 256], one cluster per thread.  The head's
-// log-sum-exp is rebuilt from the score kernel's block partials by one warp per query head
-// (the partials of a head are read in parallel and merged with shuffles).
-__global__ void __launch_bounds__(PEN_THREADS)
-decode_penalise_kernel(const DecodeArgs a) {
-  __shared__ float lse2[MAX_G];
-  const int h = blockIdx.x;
-  const int C = a.num_clusters, G = a.group;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp < G) {
-    const int t = warp;
-    float m = -INFINITY, l = 0.f;
-    for (int b = lane; b < a.score_blocks; b += 32) {
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (((int64_t)h * a.score_blocks + b) * G + t) * 2));
-      const float mx = fmaxf(m, ml.x);
-      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (ml.x == -INFINITY ? 0.f : ml.y * exp2f(ml.x - mx));
-      m = mx;
-    }
+// What the CTAs of a head exchange through distributed shared memory.
+struct SelectShared {
+  float lse2[MAX_G];
+  float w_mx[SEL_WARPS], w_mn[SEL_WARPS];
+  int w_tot[SEL_WARPS], w_sel[SEL_WARPS], w_tok[SEL_WARPS];
+  float cta_mx, cta_mn;          // read by the other CTAs of the head
+  int cta_tot, cta_sel, cta_tok;
+  int hist1[256], hist2[256];    // read by the other CTAs of the head
+  int total[256];
+  float all_mx, all_mn;
+  int all_tot, byte_found, byte_above, base_sel, base_tok, sum_sel, sum_tok;
+};
+
+// Largest bin b whose suffix sum total[b] + total[b + 1] + ... reaches `budget` (255 when the
+// budget is not positive, 0 when nothing reaches it), and the sum of the bins above it.  Warp 0.
+__device__ __forceinline__ void find_threshold_bin(const int* total, int budget, int lane, int* found, int* above) {
+  int mine[8], s = 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float m_o = __shfl_xor_sync(0xffffffffu, m, o), l_o = __shfl_xor_sync(0xffffffffu, l, o);
-      const float mx = fmaxf(m, m_o);
-      l = (m == -INFINITY ? 0.f : l * exp2f(m - mx)) + (m_o == -INFINITY ? 0.f : l_o * exp2f(m_o - mx));
-      m = mx;
-    }
-    if (lane == 0) lse2[t] = m + log2f(l);
+  for (int k = 0; k < 8; ++k) { mine[k] = total[lane * 8 + k]; s += mine[k]; }
+  int suf = s;                                         // sum over lanes >= this one
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_down_sync(0xffffffffu, suf, o);
+    if (lane + o < 32) suf += v;
   }
-  __syncthreads();
-  const int c = blockIdx.y * PEN_THREADS + threadIdx.x;
-  if (c >= C) return;
-  float lg[MAX_G];
+  const unsigned reach = __ballot_sync(0xffffffffu, suf >= budget);
+  if (reach == 0u) {
+    if (lane == 0) { *found = 0; *above = 0; }
+    return;
+  }
+  const int top = 31 - __clz(reach);
+  if (lane == top) {
+    int run = suf - s;                                 // the bins of the lanes above
+    int b = 0, ab = 0;
 #pragma unroll
-  for (int t = 0; t < MAX_G; ++t)
-    if (t < G) lg[t] = __ldcg(a.ws_logit + ((int64_t)h * G + t) * C + c);
-  const int size = __ldg(a.sizes + (int64_t)h * C + c);
-  float prob = 0.f;
-#pragma unroll
-  for (int t = 0; t < MAX_G; ++t)
-    if (t < G) prob += exp2f(lg[t] - lse2[t]);
-  const float n = (a.sink_tokens > 0 && c == 0) ? 0.f : (float)size;
-  float sc = log2f(fmaxf(prob, 1e-38f)) * LN2;
-  if (a.beta != 0.f) sc -= a.beta * logf(1.0f + n);
-  a.ws_score[(int64_t)h * C + c] = n > 0.f ? sc : NEG_BIG;
+    for (int k = 7; k >= 0; --k) {
+      if (run + mine[k] >= budget) { b = lane * 8 + k; ab = run; break; }
+      run += mine[k];
+    }
+    *found = b;
+    *above = ab;
+  }
 }
 
-// Threshold bisection, selection, CSR in cluster order and the flat row list: grid [Hkv].
-// A thread owns PER consecutive clusters (PER * T >= C, C a multiple of 4).  Few threads with
-// many clusters each: the per-warp cost of the 16 block-wide sums dominates otherwise.
-template <int PER, int T>
-__global__ void __launch_bounds__(T)
+// Selection of one decode query: penalised scores, the bisected threshold, CSR of the selected
+// clusters in cluster order, and where every attention split starts in it.
+//
+// The 16-step bisection of fused_decode.py:159-187 is evaluated without its 16 dependent sweeps.
+// The midpoints it can visit form a fixed binary tree over [lo0, hi0].  Every cluster walks that
+// tree with its own score (bit k = score >= midpoint at depth k, then lo / hi move exactly as in
+// the reference, in fp32), which gives it a 16-bit code; codes order the clusters as the midpoints
+// do.  On the bisection's own path the step at depth k asks whether the sizes of the clusters
+// with score >= m_k reach the budget; a cluster that left the path earlier sits wholly above or
+// below every later midpoint of the path, so that sum is the sum over codes >= (path so far, 1,
+// 0 ...).  The path is therefore the largest 16-bit value T whose suffix sum reaches the budget,
+// found with two 256-bin histograms, and `score >= theta` is `code >= T`, bit for bit.
+__global__ void __cluster_dims__(SEL_CL, 1, 1) __launch_bounds__(SEL_THREADS)
 decode_select_kernel(const DecodeArgs a) {
-  constexpr int NW = T / 32;
-  __shared__ float fred[2][32];
-  __shared__ int isum[2][32];
-  __shared__ int wsum_a[32], wsum_b[32];
-  __shared__ int csr_start[SEL_CSR_SMEM], csr_cum[SEL_CSR_SMEM];
-  const int h = blockIdx.x;
-  const int C = a.num_clusters;
-  const int lane_s = threadIdx.x & 31, warp_s = threadIdx.x >> 5;
-  const int c0 = threadIdx.x * PER;
-  const bool has_sink = a.sink_tokens > 0;
-  float score[PER];
-  int real[PER], seen[PER];          // cluster size, and the size the budget sees (0 for the sink cluster)
+  __shared__ SelectShared sh;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int h = blockIdx.y;
+  const int C = a.num_clusters, G = a.group;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  if (tid < 256) { sh.hist1[tid] = 0; sh.hist2[tid] = 0; }
+  pdl_wait();                                          // the score kernel's logits and partials are complete
+  // this thread's logits, sizes and cluster starts are requested before the log-sum-exp is built
+  const int per_cta = C / SEL_CL;                      // C is a multiple of 32
+  const int c0 = rank * per_cta + tid * SEL_PER;
+  const bool active = tid * SEL_PER < per_cta;
+  float4 lg[MAX_G];
+  int4 sz = make_int4(0, 0, 0, 0);
+  int starts[SEL_PER] = {0, 0, 0, 0};
+  if (active) {
 #pragma unroll
-  for (int i4 = 0; i4 < PER; i4 += 4) {
-    float4 sc = make_float4(NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG);
-    int4 sz = make_int4(0, 0, 0, 0);
-    if (c0 + i4 < C) {
-      sc = __ldcg(reinterpret_cast<const float4*>(a.ws_score + (int64_t)h * C + c0 + i4));
-      sz = __ldg(reinterpret_cast<const int4*>(a.sizes + (int64_t)h * C + c0 + i4));
-    }
-    score[i4] = sc.x; score[i4 + 1] = sc.y; score[i4 + 2] = sc.z; score[i4 + 3] = sc.w;
-    real[i4] = sz.x; real[i4 + 1] = sz.y; real[i4 + 2] = sz.z; real[i4 + 3] = sz.w;
+    for (int t = 0; t < MAX_G; ++t)
+      if (t < G) lg[t] = __ldcg(reinterpret_cast<const float4*>(a.ws_logit + ((int64_t)h * G + t) * C + c0));
+    sz = __ldg(reinterpret_cast<const int4*>(a.sizes + (int64_t)h * C + c0));
+#pragma unroll
+    for (int i = 0; i < SEL_PER; ++i) starts[i] = __ldg(a.indptr + (int64_t)h * (C + 1) + c0 + i);
   }
+  if (warp < G) {
+    // log-sum-exp of a query head from the score kernel's block partials: the maximum first, then
+    // one pass of weighted sums
+    const int t = warp;
+    float2 part[4];
+    float m = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int b = lane + 32 * k;
+      part[k] = b < a.score_blocks
+                    ? __ldcg(reinterpret_cast<const float2*>(a.ws_ml + (((int64_t)h * a.score_blocks + b) * G + t) * 2))
+                    : make_float2(-INFINITY, 0.f);
+      m = fmaxf(m, part[k].x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) l += part[k].x == -INFINITY ? 0.f : part[k].y * exp2f(part[k].x - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) sh.lse2[t] = m + log2f(l);
+  }
+  __syncthreads();
+
+  // penalised scores of this thread's clusters
+  const bool has_sink = a.sink_tokens > 0;
+  float score[SEL_PER];
+  int real[SEL_PER], seen[SEL_PER];
+#pragma unroll
+  for (int i = 0; i < SEL_PER; ++i) { score[i] = NEG_BIG; real[i] = 0; seen[i] = 0; }
+  if (active) {
+    float prob[SEL_PER] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int t = 0; t < MAX_G; ++t) {
+      if (t < G) {
+        const float ls = sh.lse2[t];
+        prob[0] += exp2f(lg[t].x - ls); prob[1] += exp2f(lg[t].y - ls);
+        prob[2] += exp2f(lg[t].z - ls); prob[3] += exp2f(lg[t].w - ls);
+      }
+    }
+    real[0] = sz.x; real[1] = sz.y; real[2] = sz.z; real[3] = sz.w;
+#pragma unroll
+    for (int i = 0; i < SEL_PER; ++i) {
+      seen[i] = (has_sink && c0 + i == 0) ? 0 : real[i];      // the budget does not see the sink cluster
+      const float n = (float)seen[i];
+      float sc = log2f(fmaxf(prob[i], 1e-38f)) * LN2;
+      if (a.beta != 0.f) sc -= a.beta * logf(1.0f + n);
+      score[i] = n > 0.f ? sc : NEG_BIG;
+    }
+  }
+  // maximum over all clusters, minimum over the live ones, live tokens: warp, CTA, head
   float mx = -INFINITY, mn = 3.4e38f;
   int tot = 0;
+  if (active) {
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    seen[i] = (has_sink && c0 + i == 0) ? 0 : real[i];
-    if (c0 + i < C) mx = fmaxf(mx, score[i]);
-    if (seen[i] > 0) { mn = fminf(mn, score[i]); tot += seen[i]; }
+    for (int i = 0; i < SEL_PER; ++i) {
+      mx = fmaxf(mx, score[i]);
+      if (seen[i] > 0) { mn = fminf(mn, score[i]); tot += seen[i]; }
+    }
   }
-  // block reductions with one barrier each: warp results go to one of two buffers (alternating,
-  // so a fast warp's next write cannot overtake a slow warp's read), then every warp folds the 32
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
   }
   tot = __reduce_add_sync(0xffffffffu, tot);
-  if (lane_s == 0) { fred[0][warp_s] = mx; fred[1][warp_s] = mn; isum[1][warp_s] = tot; }
+  if (lane == 0) { sh.w_mx[warp] = mx; sh.w_mn[warp] = mn; sh.w_tot[warp] = tot; }
   __syncthreads();
-  mx = lane_s < NW ? fred[0][lane_s] : -INFINITY;
-  mn = lane_s < NW ? fred[1][lane_s] : 3.4e38f;
+  if (warp == 0) {
+    mx = lane < SEL_WARPS ? sh.w_mx[lane] : -INFINITY;
+    mn = lane < SEL_WARPS ? sh.w_mn[lane] : 3.4e38f;
+    tot = lane < SEL_WARPS ? sh.w_tot[lane] : 0;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    }
+    tot = __reduce_add_sync(0xffffffffu, tot);
+    if (lane == 0) { sh.cta_mx = mx; sh.cta_mn = mn; sh.cta_tot = tot; }
   }
+  cluster.sync();
+  if (warp == 0) {
+    mx = -INFINITY; mn = 3.4e38f; tot = 0;
+    if (lane < SEL_CL) {
+      const SelectShared* peer = cluster.map_shared_rank(&sh, lane);
+      mx = peer->cta_mx; mn = peer->cta_mn; tot = peer->cta_tot;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    }
+    tot = __reduce_add_sync(0xffffffffu, tot);
+    if (lane == 0) { sh.all_mx = mx; sh.all_mn = mn; sh.all_tot = tot; }
+  }
+  __syncthreads();
   const int budget = max(a.target_tokens - a.sink_tokens, 0);
-  const bool all_fit = __reduce_add_sync(0xffffffffu, lane_s < NW ? isum[1][lane_s] : 0) < budget;
-  float hi = mx + 1e-6f;
-  float lo = fminf(mn - 1e-6f, hi - 1e-5f);
-  for (int it = 0; it < a.iters; ++it) {
-    const float mid = (lo + hi) * 0.5f;
-    int above = 0;
+  const bool all_fit = sh.all_tot < budget;
+  const float hi0 = sh.all_mx + 1e-6f;
+  const float lo0 = fminf(sh.all_mn - 1e-6f, hi0 - 1e-5f);
+
+  // every cluster's path through the tree of midpoints
+  unsigned code[SEL_PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) above += score[i] >= mid ? seen[i] : 0;
-    above = __reduce_add_sync(0xffffffffu, above);
-    if (lane_s == 0) isum[it & 1][warp_s] = above;
-    __syncthreads();
-    above = __reduce_add_sync(0xffffffffu, lane_s < NW ? isum[it & 1][lane_s] : 0);
-    const bool reach = above >= budget;
-    lo = reach ? mid : lo;
-    hi = reach ? hi : mid;
+  for (int i = 0; i < SEL_PER; ++i) {
+    float lo = lo0, hi = hi0;
+    unsigned cd = 0;
+    for (int it = 0; it < a.iters; ++it) {
+      const float mid = (lo + hi) * 0.5f;
+      const bool up = score[i] >= mid;
+      cd = (cd << 1) | (up ? 1u : 0u);
+      lo = up ? mid : lo;
+      hi = up ? hi : mid;
+    }
+    code[i] = cd << (16 - a.iters);
+    if (seen[i] > 0) atomicAdd(&sh.hist1[code[i] >> 8], seen[i]);
   }
-  const float theta = all_fit ? NEG_BIG : lo;
-  // selection flags, CSR positions (block scan over threads; clusters of a thread are consecutive)
+  cluster.sync();
+  if (tid < 256) {
+    int s = 0;
+#pragma unroll
+    for (int r = 0; r < SEL_CL; ++r) s += cluster.map_shared_rank(&sh, r)->hist1[tid];
+    sh.total[tid] = s;
+  }
+  __syncthreads();
+  if (warp == 0) find_threshold_bin(sh.total, budget, lane, &sh.byte_found, &sh.byte_above);
+  __syncthreads();
+  const unsigned top_byte = (unsigned)sh.byte_found;
+  const int budget2 = budget - sh.byte_above;
+#pragma unroll
+  for (int i = 0; i < SEL_PER; ++i)
+    if (seen[i] > 0 && (code[i] >> 8) == top_byte) atomicAdd(&sh.hist2[code[i] & 255u], seen[i]);
+  cluster.sync();
+  if (tid < 256) {
+    int s = 0;
+#pragma unroll
+    for (int r = 0; r < SEL_CL; ++r) s += cluster.map_shared_rank(&sh, r)->hist2[tid];
+    sh.total[tid] = s;
+  }
+  __syncthreads();
+  if (warp == 0) find_threshold_bin(sh.total, budget2, lane, &sh.byte_found, &sh.byte_above);
+  __syncthreads();
+  const unsigned threshold = (top_byte << 8) | (unsigned)sh.byte_found;
+
+  // selection flags; CSR positions by a scan over the threads of the head in cluster order
   int n_sel = 0, n_tok = 0;
   unsigned sel_bits = 0;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int c = c0 + i;
-    const bool is_sink = has_sink && c == 0;
-    const bool s = c < C && ((seen[i] > 0 && score[i] >= theta) || (is_sink && real[i] > 0));
+  for (int i = 0; i < SEL_PER; ++i) {
+    const bool is_sink = has_sink && c0 + i == 0;
+    const bool s = active && ((seen[i] > 0 && (all_fit || code[i] >= threshold)) || (is_sink && real[i] > 0));
     sel_bits |= s ? (1u << i) : 0u;
     n_sel += s;
     n_tok += s ? real[i] : 0;
   }
-  // block-wide exclusive scan of (clusters, tokens): warp scans, then a scan of the warp totals
   int inc_a = n_sel, inc_b = n_tok;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int va = __shfl_up_sync(0xffffffffu, inc_a, o), vb = __shfl_up_sync(0xffffffffu, inc_b, o);
-    if (lane_s >= o) { inc_a += va; inc_b += vb; }
+    if (lane >= o) { inc_a += va; inc_b += vb; }
   }
-  if (lane_s == 31) { wsum_a[warp_s] = inc_a; wsum_b[warp_s] = inc_b; }
+  if (lane == 31) { sh.w_sel[warp] = inc_a; sh.w_tok[warp] = inc_b; }
   __syncthreads();
-  int wa = lane_s < NW ? wsum_a[lane_s] : 0, wb = lane_s < NW ? wsum_b[lane_s] : 0;
+  int wa = lane < SEL_WARPS ? sh.w_sel[lane] : 0, wb = lane < SEL_WARPS ? sh.w_tok[lane] : 0;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int va = __shfl_up_sync(0xffffffffu, wa, o), vb = __shfl_up_sync(0xffffffffu, wb, o);
-    if (lane_s >= o) { wa += va; wb += vb; }
+    if (lane >= o) { wa += va; wb += vb; }
   }
-  const int total_sel = __shfl_sync(0xffffffffu, wa, NW - 1), total_tok = __shfl_sync(0xffffffffu, wb, NW - 1);
-  const int base_a = __shfl_sync(0xffffffffu, wa, warp_s) - wsum_a[warp_s];
-  const int base_b = __shfl_sync(0xffffffffu, wb, warp_s) - wsum_b[warp_s];
-  int pos = base_a + inc_a - n_sel, cum = base_b + inc_b - n_tok;
+  const int cta_sel = __shfl_sync(0xffffffffu, wa, SEL_WARPS - 1), cta_tok = __shfl_sync(0xffffffffu, wb, SEL_WARPS - 1);
+  const int warp_base_a = __shfl_sync(0xffffffffu, wa, warp) - sh.w_sel[warp];
+  const int warp_base_b = __shfl_sync(0xffffffffu, wb, warp) - sh.w_tok[warp];
+  if (tid == 0) { sh.cta_sel = cta_sel; sh.cta_tok = cta_tok; }
+  cluster.sync();
+  if (warp == 0) {
+    int ps = 0, pt = 0;
+    if (lane < SEL_CL) {
+      const SelectShared* peer = cluster.map_shared_rank(&sh, lane);
+      ps = peer->cta_sel; pt = peer->cta_tok;
+    }
+    const int before_s = __reduce_add_sync(0xffffffffu, lane < rank ? ps : 0);
+    const int before_t = __reduce_add_sync(0xffffffffu, lane < rank ? pt : 0);
+    const int all_s = __reduce_add_sync(0xffffffffu, ps), all_t = __reduce_add_sync(0xffffffffu, pt);
+    if (lane == 0) { sh.base_sel = before_s; sh.base_tok = before_t; sh.sum_sel = all_s; sh.sum_tok = all_t; }
+  }
+  __syncthreads();
+  const int total_sel = sh.sum_sel, total_tok = sh.sum_tok;
+  int pos = sh.base_sel + warp_base_a + inc_a - n_sel;
+  int cum = sh.base_tok + warp_base_b + inc_b - n_tok;
+  // the attention splits divide the selected rows and the live suffix evenly (the attend kernel
+  // computes the same numbers); a CSR entry records every split that starts inside it
+  const long long q_pos = load_pos(a);
+  const int plen = *a.prompt_length;
+  const int n_prompt = min(total_tok, (int)a.packed_width);
+  const int n_suffix = (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
+  const int per_split = max(1, (int)ceil_div(n_prompt + n_suffix, a.num_splits));
   int32_t* rs = a.rstart + (int64_t)h * C;
   int32_t* rl = a.rlen + (int64_t)h * C;
   int32_t* rc = a.rcum + (int64_t)h * C;
-  int starts[PER];
+  // per split {CSR entry, offset inside it, selected rows, selected clusters}: the first two by the
+  // thread whose entry holds the split's first row, the totals by the head's first CTA
+  int4* split = reinterpret_cast<int4*>(a.split_start) + (int64_t)h * a.num_splits;
+  if (sel_bits) {
 #pragma unroll
-  for (int i = 0; i < PER; ++i)
-    starts[i] = ((sel_bits >> i) & 1) ? __ldg(a.indptr + (int64_t)h * (C + 1) + c0 + i) : 0;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    if ((sel_bits >> i) & 1) {
-      rs[pos] = starts[i];
-      rl[pos] = real[i];
-      rc[pos] = cum;
-      if (pos < SEL_CSR_SMEM) { csr_start[pos] = starts[i]; csr_cum[pos] = cum; }
-      ++pos;
-      cum += real[i];
-    }
-  }
-  if (threadIdx.x == 0) {
-    a.rcount[h] = total_sel;
-    a.rtokens[h] = total_tok;
-    if (total_tok > a.packed_width) atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
-  }
-  __threadfence_block();
-  __syncthreads();
-  // flat list of selected packed rows: slot -> cluster by binary search over the cumulative sizes
-  const int limit = min(total_tok, (int)a.packed_width);
-  int32_t* rows = a.rows + (int64_t)h * a.packed_width;
-  if (total_sel <= SEL_CSR_SMEM) {
-    for (int o = threadIdx.x; o < limit; o += T) {
-      int lo_r = 0, hi_r = total_sel;                 // last r with cum[r] <= o
-      while (hi_r - lo_r > 1) {
-        const int mid = (lo_r + hi_r) >> 1;
-        if (csr_cum[mid] <= o) lo_r = mid; else hi_r = mid;
+    for (int i = 0; i < SEL_PER; ++i) {
+      if ((sel_bits >> i) & 1) {
+        const int len = real[i];
+        rs[pos] = starts[i];
+        rl[pos] = len;
+        rc[pos] = cum;
+        for (int s = (int)ceil_div(cum, per_split); s < a.num_splits && s * per_split < cum + len; ++s)
+          *reinterpret_cast<int2*>(&split[s]) = make_int2(pos, s * per_split - cum);
+        ++pos;
+        cum += len;
       }
-      rows[o] = csr_start[lo_r] + (o - csr_cum[lo_r]);
-    }
-  } else {
-    for (int o = threadIdx.x; o < limit; o += T) {
-      int lo_r = 0, hi_r = total_sel;
-      while (hi_r - lo_r > 1) {
-        const int mid = (lo_r + hi_r) >> 1;
-        if (rc[mid] <= o) lo_r = mid; else hi_r = mid;
-      }
-      rows[o] = rs[lo_r] + (o - rc[lo_r]);
     }
   }
+  if (rank == 0) {
+    for (int s = tid; s < a.num_splits; s += SEL_THREADS)
+      *(reinterpret_cast<int2*>(&split[s]) + 1) = make_int2(total_tok, total_sel);
+    if (tid == 0) {
+      a.rcount[h] = total_sel;
+      a.rtokens[h] = total_tok;
+      if (total_tok > a.packed_width) atomicCAS(a.status, 0, sm100::STATUS_OVERFLOW);
+    }
+  }
+  cluster.sync();                 // no CTA of the head leaves while a peer may still read its shared memory
 }
 
 // ------------------------------------------------------------------ attend + merge
+// A CTA takes the slots [lo, hi) of its head's rows (selected prompt rows in CSR order, then the
+// live suffix positions).  All of its rows are brought into shared memory at once with 16-byte
+// asynchronous copies, so the bytes in flight cost no registers.  The arithmetic runs on the
+// tensor cores with the G query heads of the KV head as one operand dimension (warp-level
+// mma.sync m16n8k16; a single query has no 64-row tile to offer tcgen05): warp w takes rows
+// [16 w, 16 w + 16) of the chunk,
+//   S^T [heads x rows] = Q [heads (padded to 16) x D] K^T,   O^T [D x heads] += V^T [D x rows] P [rows x heads],
+// and the accumulator layout of S^T is the operand layout P needs, so P never leaves registers.
+constexpr int ATT_CHUNK = 128;           // rows resident at a time (one 16-row tile per warp)
+constexpr int ATT_ENTRIES = 256;         // CSR entries looked at per chunk (each holds at least one row)
+
+template <int D, int G>
+struct AttendSmem {
+  static constexpr int K_OFF = 0;                                    // [CHUNK][D] bf16, 16-byte chunks swizzled by row
+  static constexpr int V_OFF = K_OFF + ATT_CHUNK * D * 2;
+  static constexpr int ACC_OFF = V_OFF + ATT_CHUNK * D * 2;          // float [8][G][D]
+  static constexpr int ML_OFF = ACC_OFF + 8 * G * D * 4;             // float [8][G][2]
+  static constexpr int KP_OFF = ML_OFF + 8 * G * 2 * 4;              // const bf16* [CHUNK]
+  static constexpr int VP_OFF = KP_OFF + ATT_CHUNK * 8;
+  static constexpr int OK_OFF = VP_OFF + ATT_CHUNK * 8;              // int [CHUNK]
+  static constexpr int ES_OFF = OK_OFF + ATT_CHUNK * 4;              // int [ENTRIES]
+  static constexpr int EC_OFF = ES_OFF + ATT_ENTRIES * 4;            // int [ENTRIES + 1]
+  static constexpr int WS_OFF = EC_OFF + (ATT_ENTRIES + 1) * 4 + 12; // int [8] warp sums (16-byte aligned)
+  static constexpr int MISC_OFF = WS_OFF + 32;                       // int [4]
+  static constexpr int TOTAL = MISC_OFF + 16;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sm100::smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sm100::smem_u32(smem_row)));
+}
+// D (16 x 8, fp32) += A (16 x 16, bf16, row-major) B (16 x 8, bf16, column-major)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(256)
 decode_attend_kernel(const DecodeArgs a) {
-  constexpr int DPL = D / 16;                  // dims per lane (a half-warp covers a row)
-  constexpr int CH = DPL / 8;                  // 16-byte chunks per lane
-  __shared__ float s_acc[8][G][D];             // per-warp partial outputs
-  __shared__ float s_ml[8][G][2];
-  __shared__ int s_last;
+  using S = AttendSmem<D, G>;
+  constexpr int LPR = D / 8;                   // 16-byte chunks per row
+  constexpr int RPW = 32 / LPR;                // rows a warp copies per instruction
+  constexpr int KSTEPS = D / 16;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16* s_k = reinterpret_cast<__nv_bfloat16*>(smem + S::K_OFF);
+  __nv_bfloat16* s_v = reinterpret_cast<__nv_bfloat16*>(smem + S::V_OFF);
+  float* s_acc = reinterpret_cast<float*>(smem + S::ACC_OFF);
+  float* s_ml = reinterpret_cast<float*>(smem + S::ML_OFF);
+  const __nv_bfloat16** s_kp = reinterpret_cast<const __nv_bfloat16**>(smem + S::KP_OFF);
+  const __nv_bfloat16** s_vp = reinterpret_cast<const __nv_bfloat16**>(smem + S::VP_OFF);
+  int* s_ok = reinterpret_cast<int*>(smem + S::OK_OFF);
+  int* e_start = reinterpret_cast<int*>(smem + S::ES_OFF);
+  int* e_cum = reinterpret_cast<int*>(smem + S::EC_OFF);
+  int* s_wsum = reinterpret_cast<int*>(smem + S::WS_OFF);
+  int* s_misc = reinterpret_cast<int*>(smem + S::MISC_OFF);        // [0] last-CTA flag, [1] entry cursor, [2] offset in it
   const int h = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hw = lane >> 4, l16 = lane & 15;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sub = lane / LPR, l_in = lane % LPR;
+  const int g = lane >> 2, t4 = lane & 3;      // fragment coordinates of the lane
+
+  // everything that does not depend on the selection comes before the wait
   const long long q_pos = load_pos(a);
   const int plen = *a.prompt_length;
-  const int n_prompt = min(a.rtokens[h], (int)a.packed_width);
-  const int n_suffix = (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
-  const int total = n_prompt + n_suffix;
-  const int per_split = (int)ceil_div(total, nsplit);
-  const int lo = split * per_split, hi = min(total, lo + per_split);
-
-  // q fragment: lane owns dims {ch * 128 + l16 * 8 + e}
-  float q[G][DPL];
+  // Q as the 16 x 16 row-major operand of every 16-dim step: rows = query heads (rows >= G are zero)
+  uint32_t qa[KSTEPS][2];
 #pragma unroll
-  for (int t = 0; t < G; ++t)
-#pragma unroll
-    for (int ch = 0; ch < CH; ++ch) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(a.q_post + (int64_t)(h * G + t) * D + ch * 128 + l16 * 8);
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f2 = __bfloat1622float2(p2[e]);
-        q[t][ch * 8 + 2 * e] = f2.x * a.sm_scale_log2;
-        q[t][ch * 8 + 2 * e + 1] = f2.y * a.sm_scale_log2;
-      }
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    qa[kk][0] = 0u;
+    qa[kk][1] = 0u;
+    if (g < G) {
+      const __nv_bfloat16* qrow = a.q_post + (int64_t)(h * G + g) * D + kk * 16 + t4 * 2;
+      qa[kk][0] = *reinterpret_cast<const uint32_t*>(qrow);
+      qa[kk][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
     }
-  float acc[G][DPL], m_run[G], l_run[G];
-#pragma unroll
-  for (int t = 0; t < G; ++t) {
-    m_run[t] = -INFINITY;
-    l_run[t] = 0.f;
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) acc[t][d] = 0.f;
   }
-  const int32_t* rows = a.rows + (int64_t)h * a.packed_width;
-  const int32_t* posting = a.posting + (int64_t)h * a.packed_width;
+  float o[KSTEPS][4];                          // O^T: tile nn holds dims 16 nn + g (+ 8), heads 2 t4 (+ 1)
+#pragma unroll
+  for (int nn = 0; nn < KSTEPS; ++nn)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nn][e] = 0.f;
+  float m_run = -INFINITY, l_part = 0.f;       // of head g (lanes with g < G); l_part: this lane's share of the row sum
   const int64_t pk_plane = a.packed_width * (int64_t)a.num_kv_heads * D;
   const int64_t sf_plane = (int64_t)a.suffix_blocks * a.suffix_block * a.num_kv_heads * D;
+  const int32_t* posting = a.posting + (int64_t)h * a.packed_width;
+  pdl_wait();                                          // the selection is complete
 
-  // Each half-warp takes U rows per step.  The row indices of the next step, then all K / V
-  // rows of this step, are in flight before any arithmetic, so a half-warp keeps U kilobyte-
-  // sized requests outstanding instead of one.
-  constexpr int U = 4;
-  auto row_source = [&](int o, const __nv_bfloat16*& kp, int64_t& voff, int& post_row, bool& in_range) {
-    // o: slot in [lo, hi); prompt slots come from the selected-row list, the rest from the suffix store
-    kp = a.packed_kv;
-    voff = pk_plane;
-    post_row = -1;
-    in_range = false;
-    if (o >= hi) return;
-    if (o < n_prompt) {
-      const int r = rows[o];
-      kp = a.packed_kv + ((int64_t)r * a.num_kv_heads + h) * D;
-      post_row = r;
-      in_range = true;
-    } else {
-      const long long pos = (long long)plen + (o - n_prompt);
-      const long long block = pos / a.suffix_block;
-      if (pos <= q_pos && block < a.table_len) {
-        const long long phys = a.suffix_table[block];
-        kp = a.suffix_kv + (((phys * a.suffix_block + (pos - block * a.suffix_block)) * a.num_kv_heads) + h) * D;
-        voff = sf_plane;
-        in_range = true;
-      }
-    }
-  };
-  for (int base = lo + warp * 2; base < hi; base += 16 * U) {
-    const __nv_bfloat16* kp[U];
-    int64_t voff[U];
-    int post_row[U];
-    bool keep[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) row_source(base + 16 * u + hw, kp[u], voff[u], post_row[u], keep[u]);
-    uint4 kraw[U][CH], vraw[U][CH];
-    int post[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      post[u] = INT_MIN;
-      if (keep[u] && post_row[u] >= 0) post[u] = __ldg(posting + post_row[u]);
-#pragma unroll
-      for (int ch = 0; ch < CH; ++ch) {
-        kraw[u][ch] = make_uint4(0, 0, 0, 0);
-        vraw[u][ch] = make_uint4(0, 0, 0, 0);
-        if (keep[u]) {
-          kraw[u][ch] = __ldg(reinterpret_cast<const uint4*>(kp[u] + ch * 128 + l16 * 8));
-          vraw[u][ch] = __ldg(reinterpret_cast<const uint4*>(kp[u] + voff[u] + ch * 128 + l16 * 8));
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float s2[G];
-#pragma unroll
-      for (int t = 0; t < G; ++t) s2[t] = 0.f;
-#pragma unroll
-      for (int ch = 0; ch < CH; ++ch) {
-        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&kraw[u][ch]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f2 = __bfloat1622float2(p2[e]);
-#pragma unroll
-          for (int t = 0; t < G; ++t) {
-            s2[t] = fmaf(q[t][ch * 8 + 2 * e], f2.x, s2[t]);
-            s2[t] = fmaf(q[t][ch * 8 + 2 * e + 1], f2.y, s2[t]);
-          }
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < G; ++t) {
-#pragma unroll
-        for (int off = 8; off > 0; off >>= 1) s2[t] += __shfl_xor_sync(0xffffffffu, s2[t], off);
-      }
-      // a prompt row counts only if its token is at or before the query's position
-      if (keep[u] && (long long)post[u] <= q_pos) {
-        float p[G];
-#pragma unroll
-        for (int t = 0; t < G; ++t) {
-          const float mx = fmaxf(m_run[t], s2[t]);
-          const float alpha = exp2f(m_run[t] - mx);       // 0 on the first row (m_run = -inf)
-          p[t] = exp2f(s2[t] - mx);
-          l_run[t] = l_run[t] * alpha + p[t];
-          m_run[t] = mx;
-          if (alpha != 1.f) {
-#pragma unroll
-            for (int d = 0; d < DPL; ++d) acc[t][d] *= alpha;
-          }
-        }
-#pragma unroll
-        for (int ch = 0; ch < CH; ++ch) {
-          const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&vraw[u][ch]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f2 = __bfloat1622float2(p2[e]);
-#pragma unroll
-            for (int t = 0; t < G; ++t) {
-              acc[t][ch * 8 + 2 * e] = fmaf(p[t], f2.x, acc[t][ch * 8 + 2 * e]);
-              acc[t][ch * 8 + 2 * e + 1] = fmaf(p[t], f2.y, acc[t][ch * 8 + 2 * e + 1]);
-            }
-          }
-        }
-      }
-    }
-  }
-  // merge the two half-warps, then the 8 warps, into the split's partial
-#pragma unroll
-  for (int t = 0; t < G; ++t) {
-    const float m_o = __shfl_xor_sync(0xffffffffu, m_run[t], 16);
-    const float l_o = __shfl_xor_sync(0xffffffffu, l_run[t], 16);
-    const float mx = fmaxf(m_run[t], m_o);
-    const float w_s = m_run[t] == -INFINITY ? 0.f : exp2f(m_run[t] - mx);
-    const float w_o = m_o == -INFINITY ? 0.f : exp2f(m_o - mx);
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) {
-      const float other = __shfl_xor_sync(0xffffffffu, acc[t][d], 16);
-      acc[t][d] = acc[t][d] * w_s + other * w_o;
-    }
-    l_run[t] = l_run[t] * w_s + l_o * w_o;
-    m_run[t] = mx;
-    if (hw == 0) {
-#pragma unroll
-      for (int ch = 0; ch < CH; ++ch)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) s_acc[warp][t][ch * 128 + l16 * 8 + e] = acc[t][ch * 8 + e];
-      if (l16 == 0) { s_ml[warp][t][0] = m_run[t]; s_ml[warp][t][1] = l_run[t]; }
-    }
+  const int4 rec = __ldcg(reinterpret_cast<const int4*>(a.split_start) + (int64_t)h * nsplit + split);
+  const int n_prompt = min(rec.z, (int)a.packed_width);
+  const int n_entries = rec.w;
+  const int n_suffix = (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
+  const int total = n_prompt + n_suffix;
+  const int per_split = max(1, (int)ceil_div(total, nsplit));
+  const int lo = split * per_split, hi = min(total, lo + per_split);
+  const int32_t* rs = a.rstart + (int64_t)h * a.num_clusters;
+  const int32_t* rl = a.rlen + (int64_t)h * a.num_clusters;
+  if (tid == 0) {
+    const bool has_prompt = lo < min(hi, n_prompt);
+    s_misc[1] = has_prompt ? rec.x : 0;
+    s_misc[2] = has_prompt ? rec.y : 0;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+
+  for (int base = lo; base < hi; base += ATT_CHUNK) {
+    const int n = min(ATT_CHUNK, hi - base);
+    const int n16 = (n + 15) & ~15;
+    const int np = max(0, min(n, n_prompt - base));     // prompt slots of this chunk, the rest is suffix
+    const int e_first = s_misc[1], e_off = s_misc[2];
+    if (np > 0) {
+      // ATT_ENTRIES entries from the cursor on: starts, and the running count of their rows
+      const int e = e_first + tid;
+      int st = 0, ln = 0;
+      if (e < n_entries) {
+        st = __ldcg(rs + e);
+        ln = __ldcg(rl + e);
+        if (tid == 0) { st += e_off; ln -= e_off; }
+      }
+      int inc = ln;
+#pragma unroll
+      for (int o2 = 1; o2 < 32; o2 <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o2);
+        if (lane >= o2) inc += v;
+      }
+      if (lane == 31) s_wsum[warp] = inc;
+      __syncthreads();
+      int wpre = 0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) wpre += w < warp ? s_wsum[w] : 0;
+      e_start[tid] = st;
+      e_cum[tid + 1] = wpre + inc;
+      if (tid == 0) e_cum[0] = 0;
+    }
+    __syncthreads();
+    int post = INT_MIN;
+    bool is_prompt = false;
+    if (tid < n16) {
+      const __nv_bfloat16* kp = nullptr;
+      const __nv_bfloat16* vp = nullptr;
+      if (tid < np) {
+        int lo_e = 0, hi_e = ATT_ENTRIES;               // last entry whose first row is at or before this slot
+        while (hi_e - lo_e > 1) {
+          const int mid = (lo_e + hi_e) >> 1;
+          if (e_cum[mid] <= tid) lo_e = mid; else hi_e = mid;
+        }
+        const int row = e_start[lo_e] + (tid - e_cum[lo_e]);
+        kp = a.packed_kv + ((int64_t)row * a.num_kv_heads + h) * D;
+        vp = kp + pk_plane;
+        post = __ldg(posting + row);
+        is_prompt = true;
+      } else if (tid < n) {
+        const long long pos = (long long)plen + (base + tid - n_prompt);
+        const long long block = pos / a.suffix_block;
+        if (pos <= q_pos && block < a.table_len) {
+          const long long phys = a.suffix_table[block];
+          kp = a.suffix_kv + (((phys * a.suffix_block + (pos - block * a.suffix_block)) * a.num_kv_heads) + h) * D;
+          vp = kp + sf_plane;
+        }
+      }
+      s_kp[tid] = kp;
+      s_vp[tid] = vp;
+    }
+    if (tid == 0 && base + ATT_CHUNK < hi && np == n) {
+      // the cursor for the next chunk: the entry that holds slot `n` of this one
+      int lo_e = 0, hi_e = ATT_ENTRIES;
+      while (hi_e - lo_e > 1) {
+        const int mid = (lo_e + hi_e) >> 1;
+        if (e_cum[mid] <= n) lo_e = mid; else hi_e = mid;
+      }
+      s_misc[1] = e_first + lo_e;
+      s_misc[2] = (lo_e == 0 ? e_off : 0) + (n - e_cum[lo_e]);
+    }
+    __syncthreads();
+    // all rows of the chunk in one go; rows without a source (masked, or padding up to the 16-row
+    // tile) are zeroed so that a zero weight times stale shared memory cannot make a NaN
+    for (int i = warp * RPW + sub; i < n16; i += 8 * RPW) {
+      const __nv_bfloat16* kp = s_kp[i];
+      const int off = i * D + ((l_in ^ (i & 7)) << 3);
+      if (kp) {
+        cp_async16(s_k + off, kp + l_in * 8);
+        cp_async16(s_v + off, s_vp[i] + l_in * 8);
+      } else {
+        *reinterpret_cast<uint4*>(s_k + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(s_v + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    cp_async_wait_all();
+    // a prompt row counts only if its token is at or before the query's position (the position's
+    // load has been in flight beside the row copies)
+    if (tid < n16) s_ok[tid] = s_kp[tid] != nullptr && (!is_prompt || (long long)post <= q_pos);
+    __syncthreads();
+    for (int r0 = warp * 16; r0 < n16; r0 += 8 * 16) {
+      // S^T = Q K^T for the tile's two 8-row groups
+      float sc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
+        const int row = r0 + 8 * j + (lane & 7);
+        const __nv_bfloat16* krow = s_k + row * D;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; kk += 2) {
+          uint32_t b[4];
+          ldmatrix_x4(b, krow + (((2 * kk + (lane >> 3)) ^ (row & 7)) << 3));
+          mma_bf16_16816(sc[j], qa[kk][0], 0u, qa[kk][1], 0u, b[0], b[1]);
+          mma_bf16_16816(sc[j], qa[kk + 1][0], 0u, qa[kk + 1][1], 0u, b[2], b[3]);
+        }
+      }
+      // lane (g, t4) holds head g, rows r0 + 8 j + 2 t4 (+ 1)
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool ok = s_ok[r0 + 8 * j + 2 * t4 + e] != 0;
+          sc[j][e] = ok ? sc[j][e] * a.sm_scale_log2 : -INFINITY;
+          tmax = fmaxf(tmax, sc[j][e]);
+        }
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      const float m_new = fmaxf(m_run, tmax);
+      const float alpha = (m_new == -INFINITY || m_run == m_new) ? 1.f
+                          : (m_run == -INFINITY ? 0.f : sm100::fast_exp2(m_run - m_new));
+      float p[2][2], psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          p[j][e] = m_new == -INFINITY ? 0.f : sm100::fast_exp2(sc[j][e] - m_new);
+          psum += p[j][e];
+        }
+      l_part = l_part * alpha + psum;
+      m_run = m_new;
+      __nv_bfloat162 pb0 = __floats2bfloat162_rn(p[0][0], p[0][1]);
+      __nv_bfloat162 pb1 = __floats2bfloat162_rn(p[1][0], p[1][1]);
+      const uint32_t b0 = *reinterpret_cast<uint32_t*>(&pb0), b1 = *reinterpret_cast<uint32_t*>(&pb1);
+      // the accumulator holds heads 2 t4 and 2 t4 + 1: their factors live in lanes 8 t4 and 8 t4 + 4
+      const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * t4), al1 = __shfl_sync(0xffffffffu, alpha, 8 * t4 + 4);
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int nn = 0; nn < KSTEPS; ++nn) {
+          o[nn][0] *= al0; o[nn][1] *= al1; o[nn][2] *= al0; o[nn][3] *= al1;
+        }
+      }
+      // O^T += V^T P: V^T tiles come out of the row-major rows through the transposing load
+      const int vrow = r0 + ((lane >> 4) << 3) + (lane & 7);
+      const __nv_bfloat16* vbase = s_v + vrow * D;
+#pragma unroll
+      for (int nn = 0; nn < KSTEPS; ++nn) {
+        uint32_t av[4];
+        ldmatrix_x4_trans(av, vbase + (((2 * nn + ((lane >> 3) & 1)) ^ (vrow & 7)) << 3));
+        mma_bf16_16816(o[nn], av[0], av[1], av[2], av[3], b0, b1);
+      }
+    }
+    __syncthreads();                                    // the rows are consumed before the next chunk overwrites them
+  }
+  // this warp's partial: row sums over the four lanes of a head, then O^T into shared memory
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
+  if (g < G && t4 == 0) { s_ml[(warp * G + g) * 2] = m_run; s_ml[(warp * G + g) * 2 + 1] = l_part; }
+#pragma unroll
+  for (int nn = 0; nn < KSTEPS; ++nn)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int head = 2 * t4 + e;
+      if (head < G) {
+        s_acc[(warp * G + head) * D + 16 * nn + g] = o[nn][e];
+        s_acc[(warp * G + head) * D + 16 * nn + g + 8] = o[nn][2 + e];
+      }
+    }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += blockDim.x) {
     const int t = idx / D, d = idx % D;
     float mx = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) mx = fmaxf(mx, s_ml[w][t][0]);
+    for (int w = 0; w < 8; ++w) mx = fmaxf(mx, s_ml[(w * G + t) * 2]);
     float num = 0.f, den = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-      const float m_w = s_ml[w][t][0];
+      const float m_w = s_ml[(w * G + t) * 2];
       const float sc = m_w == -INFINITY ? 0.f : exp2f(m_w - mx);
-      num += s_acc[w][t][d] * sc;
-      den += s_ml[w][t][1] * sc;
+      num += s_acc[(w * G + t) * D + d] * sc;
+      den += s_ml[(w * G + t) * 2 + 1] * sc;
     }
     a.pacc[((int64_t)(h * G + t) * nsplit + split) * D + d] = num;
     if (d == 0) {
@@ -660,70 +901,80 @@ decode_attend_kernel(const DecodeArgs a) {
   // the last CTA of the head merges every split (no waiting: a ticket counter)
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     const int ticket = atomicAdd(&a.tickets[h], 1);
-    s_last = ticket == nsplit - 1;
-    if (s_last) a.tickets[h] = 0;                   // ready for the next step / graph replay
+    s_misc[0] = ticket == nsplit - 1;
+    if (s_misc[0]) a.tickets[h] = 0;                  // ready for the next step / graph replay
   }
   __syncthreads();
-  if (!s_last) return;
+  if (!s_misc[0]) return;
   __threadfence();
-  // Final merge by the head's last CTA.  The split weights are computed once into shared
-  // memory; then every thread owns four consecutive output columns and reads one float4 per
-  // split, all independent, so the loads overlap instead of queueing behind one another.
-  float* s_w = &s_acc[0][0][0];                       // [G][nsplit] weights, then [G] denominators
-  for (int t = warp; t < G; t += 8) {
-    const float* ml = a.pml + (int64_t)(h * G + t) * nsplit * 2;
-    float mx = -INFINITY;
-    for (int s = lane; s < nsplit; s += 32) mx = fmaxf(mx, __ldcg(ml + 2 * s));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float den = 0.f;
-    for (int s = lane; s < nsplit; s += 32) {
-      const float m_s = __ldcg(ml + 2 * s);
-      const float sc = m_s == -INFINITY ? 0.f : exp2f(m_s - mx);
-      s_w[t * nsplit + s] = sc;
-      den += __ldcg(ml + 2 * s + 1) * sc;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-    if (lane == 0) s_w[G * nsplit + t] = den;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D / 4; idx += blockDim.x) {
-    const int t = idx / (D / 4), d = (idx % (D / 4)) * 4;
+  // Final merge by the head's last CTA.  Every thread owns four consecutive output columns of one
+  // query head and has that column group of up to MERGE_SPLITS splits in flight at once; while those
+  // loads travel, the splits' (max, sum) pairs are turned into weights in shared memory.
+  constexpr int MERGE_SPLITS = 40;
+  float* s_w = s_acc;                                  // [G][nsplit] weights, then [G] denominators
+  float* s_mx = s_ml;                                  // [G] maxima
+  for (int idx0 = 0; idx0 < G * D / 4; idx0 += blockDim.x) {
+    const int idx = idx0 + tid;
+    const bool live = idx < G * D / 4;
+    const int t = live ? idx / (D / 4) : 0, d = live ? (idx % (D / 4)) * 4 : 0;
     const float4* src = reinterpret_cast<const float4*>(a.pacc + (int64_t)(h * G + t) * nsplit * D + d);
     float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-    constexpr int MB = 16;                              // splits whose partials are in flight together
-    for (int s0 = 0; s0 < nsplit; s0 += MB) {
-      float4 v[MB];
+    for (int s0 = 0; s0 < nsplit; s0 += MERGE_SPLITS) {
+      float4 v[MERGE_SPLITS];
 #pragma unroll
-      for (int i = 0; i < MB; ++i)
-        v[i] = s0 + i < nsplit ? __ldcg(src + (int64_t)(s0 + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int i = 0; i < MERGE_SPLITS; ++i)
+        v[i] = (live && s0 + i < nsplit) ? __ldcg(src + (int64_t)(s0 + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (idx0 == 0 && s0 == 0) {
+        // weights of every (head, split), once
+        for (int i = tid; i < G * nsplit; i += blockDim.x) s_w[i] = __ldcg(a.pml + ((int64_t)h * G * nsplit + i) * 2);
+        __syncthreads();
+        if (tid < G) {
+          float mx = -INFINITY;
+          for (int s2 = 0; s2 < nsplit; ++s2) mx = fmaxf(mx, s_w[tid * nsplit + s2]);
+          s_mx[tid] = mx;
+        }
+        __syncthreads();
+        for (int i = tid; i < G * nsplit; i += blockDim.x) {
+          const float m_s = s_w[i], mx = s_mx[i / nsplit];
+          s_w[i] = m_s == -INFINITY ? 0.f : exp2f(m_s - mx);
+        }
+        __syncthreads();
+        if (tid < G) {
+          float den = 0.f;
+          for (int s2 = 0; s2 < nsplit; ++s2)
+            den += __ldcg(a.pml + ((int64_t)(h * G + tid) * nsplit + s2) * 2 + 1) * s_w[tid * nsplit + s2];
+          s_w[G * nsplit + tid] = den;
+        }
+        __syncthreads();
+      }
 #pragma unroll
-      for (int i = 0; i < MB; ++i) {
+      for (int i = 0; i < MERGE_SPLITS; ++i) {
         const float sc = s0 + i < nsplit ? s_w[t * nsplit + s0 + i] : 0.f;
         num.x += v[i].x * sc; num.y += v[i].y * sc; num.z += v[i].z * sc; num.w += v[i].w * sc;
       }
     }
-    const float den = s_w[G * nsplit + t];
-    const float inv = den == 0.f ? 0.f : 1.f / den;
-    __nv_bfloat162 o01 = __floats2bfloat162_rn(num.x * inv, num.y * inv);
-    __nv_bfloat162 o23 = __floats2bfloat162_rn(num.z * inv, num.w * inv);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&o01);
-    packed.y = *reinterpret_cast<uint32_t*>(&o23);
-    *reinterpret_cast<uint2*>(a.out + (int64_t)(h * G + t) * D + d) = packed;
+    if (live) {
+      const float den = s_w[G * nsplit + t];
+      const float inv = den == 0.f ? 0.f : 1.f / den;
+      __nv_bfloat162 o01 = __floats2bfloat162_rn(num.x * inv, num.y * inv);
+      __nv_bfloat162 o23 = __floats2bfloat162_rn(num.z * inv, num.w * inv);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&o01);
+      packed.y = *reinterpret_cast<uint32_t*>(&o23);
+      *reinterpret_cast<uint2*>(a.out + (int64_t)(h * G + t) * D + d) = packed;
+    }
   }
 }
 
 int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 struct WsLayout {
-  int64_t logit, ml, score, rstart, rlen, rcum, rcount, rtokens, rows, pacc, pml, tickets, vectors, total;
+  int64_t logit, ml, split, rstart, rlen, rcum, rcount, rtokens, pacc, pml, tickets, vectors, total;
 };
 
-WsLayout ws_layout(int hq, int hkv, int d, int c, int64_t width, int splits, int score_blocks) {
+WsLayout ws_layout(int hq, int hkv, int d, int c, int splits, int score_blocks) {
   const int g = hq / hkv;
   WsLayout w;
   int64_t off = 0;
@@ -731,13 +982,12 @@ WsLayout ws_layout(int hq, int hkv, int d, int c, int64_t width, int splits, int
   w.tickets = take((int64_t)hkv * 4);
   w.logit = take((int64_t)hkv * g * c * 4);
   w.ml = take((int64_t)hkv * score_blocks * g * 2 * 4);
-  w.score = take((int64_t)hkv * c * 4);
+  w.split = take((int64_t)hkv * splits * 4 * 4);
   w.rstart = take((int64_t)hkv * c * 4);
   w.rlen = take((int64_t)hkv * c * 4);
   w.rcum = take((int64_t)hkv * c * 4);
   w.rcount = take((int64_t)hkv * 4);
   w.rtokens = take((int64_t)hkv * 4);
-  w.rows = take((int64_t)hkv * width * 4);
   w.pacc = take((int64_t)hq * splits * d * 4);
   w.pml = take((int64_t)hq * splits * 2 * 4);
   w.vectors = take((int64_t)hq * d * 2);
@@ -747,8 +997,36 @@ WsLayout ws_layout(int hq, int hkv, int d, int c, int64_t width, int splits, int
 
 int score_blocks_for(int hkv, int c) {
   int b = std::max(1, SCORE_BLOCKS_TARGET / std::max(hkv, 1));
+  b = std::min(b, 128);                       // the select kernel folds the block partials four per lane
   b = std::min(b, std::max(1, c / 32));
   return b;
+}
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may start while its
+// predecessor in the stream is still running, and its griddepcontrol.wait holds it until the
+// predecessor has completed.  `overlap` = 0 gives the plain stream-ordered launch.
+template <typename Kernel>
+int launch_decode_kernel(Kernel kern, dim3 grid, int threads, size_t smem, cudaStream_t st, int overlap,
+                         const DecodeArgs& a) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  SEMBLO_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  return 0;
+}
+
+template <int D, int G>
+int launch_attend(const DecodeArgs& a, dim3 grid, cudaStream_t st, int overlap) {
+  auto kern = decode_attend_kernel<D, G>;
+  SEMBLO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttendSmem<D, G>::TOTAL));
+  return launch_decode_kernel(kern, grid, 256, AttendSmem<D, G>::TOTAL, st, overlap, a);
 }
 
 }  // namespace
@@ -756,18 +1034,20 @@ int score_blocks_for(int hkv, int c) {
 extern "C" int64_t semblo_decode_workspace_bytes(int num_q_heads, int num_kv_heads, int head_dim,
                                                  int num_clusters, int64_t packed_width,
                                                  int num_splits) {
-  return ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width, num_splits,
+  (void)packed_width;
+  return ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, num_splits,
                    score_blocks_for(num_kv_heads, num_clusters)).total;
 }
 
 extern "C" int semblo_decode_workspace_offsets(int num_q_heads, int num_kv_heads, int head_dim,
                                                int num_clusters, int64_t packed_width,
-                                               int num_splits, int64_t* offsets /* [13] */) {
-  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width,
-                               num_splits, score_blocks_for(num_kv_heads, num_clusters));
-  const int64_t v[13] = {w.tickets, w.logit, w.ml, w.score, w.rstart, w.rlen, w.rcum,
-                         w.rcount, w.rtokens, w.rows, w.pacc, w.pml, w.vectors};
-  for (int i = 0; i < 13; ++i) offsets[i] = v[i];
+                                               int num_splits, int64_t* offsets /* [12] */) {
+  (void)packed_width;
+  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, num_splits,
+                               score_blocks_for(num_kv_heads, num_clusters));
+  const int64_t v[12] = {w.tickets, w.logit, w.ml, w.split, w.rstart, w.rlen, w.rcum,
+                         w.rcount, w.rtokens, w.pacc, w.pml, w.vectors};
+  for (int i = 0; i < 12; ++i) offsets[i] = v[i];
   return 0;
 }
 
@@ -786,13 +1066,19 @@ extern "C" int semblo_decode_step(
   const int g = num_q_heads / num_kv_heads;
   SEMBLO_REQUIRE(g <= MAX_G, "at most %d query heads per KV head", MAX_G);
   SEMBLO_REQUIRE(head_dim == 128 || head_dim == 256, "head_dim %d must be 128 or 256", head_dim);
-  SEMBLO_REQUIRE(num_clusters >= 32 && num_clusters <= SEL_THREADS * SEL_MAX_PER,
-                 "cluster count %d outside [32, %d]", num_clusters, SEL_THREADS * SEL_MAX_PER);
+  SEMBLO_REQUIRE(num_clusters >= 32 && num_clusters % 32 == 0 && num_clusters <= SEL_MAX_CLUSTERS,
+                 "cluster count %d must be a multiple of 32 in [32, %d]", num_clusters, SEL_MAX_CLUSTERS);
+  SEMBLO_REQUIRE(iters >= 1 && iters <= 16, "bisection steps %d outside [1, 16]", iters);
   SEMBLO_REQUIRE(temperature > 0.f && num_splits > 0, "temperature and split count must be positive");
   SEMBLO_REQUIRE((k_post == nullptr) == (v_new == nullptr), "key and value of the new token go together");
+  SEMBLO_REQUIRE(((reinterpret_cast<uintptr_t>(k_post) | reinterpret_cast<uintptr_t>(v_new) |
+                   reinterpret_cast<uintptr_t>(k_pre) | reinterpret_cast<uintptr_t>(q_post) |
+                   reinterpret_cast<uintptr_t>(suffix_kv) | reinterpret_cast<uintptr_t>(suffix_kpre) |
+                   reinterpret_cast<uintptr_t>(packed_kv)) & 15) == 0,
+                 "the step's tensors and the stores must be 16-byte aligned");
   SEMBLO_REQUIRE(status != nullptr, "status word is required");
   const int sblocks = score_blocks_for(num_kv_heads, num_clusters);
-  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, packed_width, num_splits, sblocks);
+  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, num_clusters, num_splits, sblocks);
   SEMBLO_REQUIRE(workspace_bytes >= w.total, "decode workspace has %lld bytes, %lld needed",
                  (long long)workspace_bytes, (long long)w.total);
   uint8_t* ws = (uint8_t*)workspace;
@@ -811,35 +1097,39 @@ extern "C" int semblo_decode_step(
   a.scale_log2_router = LOG2E / temperature; a.beta = beta; a.sm_scale_log2 = sm_scale * LOG2E;
   a.target_tokens = target_tokens; a.sink_tokens = sink_tokens; a.iters = iters;
   a.num_splits = num_splits; a.score_blocks = sblocks;
-  a.ws_logit = (float*)(ws + w.logit); a.ws_ml = (float*)(ws + w.ml); a.ws_score = (float*)(ws + w.score);
+  a.ws_logit = (float*)(ws + w.logit); a.ws_ml = (float*)(ws + w.ml);
+  a.split_start = (int32_t*)(ws + w.split);
   a.rstart = (int32_t*)(ws + w.rstart); a.rlen = (int32_t*)(ws + w.rlen); a.rcum = (int32_t*)(ws + w.rcum);
   a.rcount = (int32_t*)(ws + w.rcount); a.rtokens = (int32_t*)(ws + w.rtokens);
-  a.rows = (int32_t*)(ws + w.rows); a.pacc = (float*)(ws + w.pacc); a.pml = (float*)(ws + w.pml);
+  a.pacc = (float*)(ws + w.pacc); a.pml = (float*)(ws + w.pml);
   a.tickets = (int32_t*)(ws + w.tickets); a.vectors = (__nv_bfloat16*)(ws + w.vectors);
   a.out = (__nv_bfloat16*)output; a.status = status;
   cudaStream_t st = (cudaStream_t)stream;
+  // bit 3 of the stage mask turns the overlapped (programmatic dependent) launches off; a stage
+  // launched alone has no predecessor of this step to overlap with
+  const int overlap = (stage_mask & 8) ? 0 : 1;
   if (stage_mask & 1) {
-    const dim3 sgrid(num_kv_heads, sblocks);
+    const dim3 sgrid(num_kv_heads, sblocks + 1);
     if (head_dim == 256 && g == 4) decode_score_kernel<256, 4><<<sgrid, 256, 0, st>>>(a);
     else if (head_dim == 128 && g == 4) decode_score_kernel<128, 4><<<sgrid, 256, 0, st>>>(a);
     else if (head_dim == 128 && g == 8) decode_score_kernel<128, 8><<<sgrid, 256, 0, st>>>(a);
     else return semblo::fail(semblo::SEMBLO_EINVAL, "decode scoring supports head_dim 256 with 4, or 128 with 4 or 8, query heads per KV head (got %d, %d)", head_dim, g);
+    SEMBLO_LAUNCH_CHECK();
   }
   if (stage_mask & 2) {
-    decode_penalise_kernel<<<dim3(num_kv_heads, (unsigned)ceil_div(num_clusters, PEN_THREADS)), PEN_THREADS, 0, st>>>(a);
-    if (num_clusters <= 2048) decode_select_kernel<4, 512><<<num_kv_heads, 512, 0, st>>>(a);
-    else if (num_clusters <= 8192) decode_select_kernel<16, 512><<<num_kv_heads, 512, 0, st>>>(a);
-    else decode_select_kernel<16, 1024><<<num_kv_heads, 1024, 0, st>>>(a);
+    int rc = launch_decode_kernel(decode_select_kernel, dim3(SEL_CL, num_kv_heads), SEL_THREADS, 0, st,
+                                  overlap && (stage_mask & 1), a);
+    if (rc) return rc;
   }
   if (stage_mask & 4) {
-    dim3 grid(num_kv_heads, num_splits);
-#define SEMBLO_DECODE_CASE(DD, GG) \
-  if (head_dim == DD && g == GG) decode_attend_kernel<DD, GG><<<grid, 256, 0, st>>>(a); else
-    SEMBLO_DECODE_CASE(256, 4)
-    SEMBLO_DECODE_CASE(128, 4)
-    SEMBLO_DECODE_CASE(128, 8)
-#undef SEMBLO_DECODE_CASE
-    return semblo::fail(semblo::SEMBLO_EINVAL, "decode attention supports 4 or 8 query heads per KV head (got %d)", g);
+    const dim3 grid(num_kv_heads, num_splits);
+    const int ov = overlap && (stage_mask & 2);
+    int rc;
+    if (head_dim == 256 && g == 4) rc = launch_attend<256, 4>(a, grid, st, ov);
+    else if (head_dim == 128 && g == 4) rc = launch_attend<128, 4>(a, grid, st, ov);
+    else if (head_dim == 128 && g == 8) rc = launch_attend<128, 8>(a, grid, st, ov);
+    else return semblo::fail(semblo::SEMBLO_EINVAL, "decode attention supports head_dim 256 with 4, or 128 with 4 or 8, query heads per KV head (got %d, %d)", head_dim, g);
+    if (rc) return rc;
   }
   SEMBLO_LAUNCH_CHECK();
   return 0;

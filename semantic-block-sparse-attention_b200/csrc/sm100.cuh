@@ -123,6 +123,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---------------------------------------------------------------- dependent launches
+// In a kernel launched as a programmatic dependent: wait until the preceding kernel of the stream
+// has completed and its writes are visible (a no-op in a plain launch).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Allow the next kernel of the stream, if it was launched as a programmatic dependent, to start.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -1,8 +1,8 @@
 """The decode step of one sparse layer (mirror of semblo/vllm_plugin/fused_decode.py:393-521).
 
 Three launches on the current stream (score + suffix write, select + CSR, attend +
-merge), no host reads and no allocation after the workspace exists, so a CUDA graph
-can capture the step."""
+merge; the last two start while their predecessor drains), no host reads and no
+allocation after the workspace exists, so a CUDA graph can capture the step."""
 from __future__ import annotations
 
 import ctypes
@@ -21,7 +21,7 @@ def _pow2_at_least(n: int, floor: int = 16) -> int:
 class FusedDecodeWorkspace:
     """Fixed-address scratch of the step (fused_decode.py:365-385)."""
 
-    NAMES = ("tickets", "logit", "ml", "score", "rstart", "rlen", "rcum", "rcount", "rtokens", "rows",
+    NAMES = ("tickets", "logit", "ml", "split", "rstart", "rlen", "rcum", "rcount", "rtokens",
              "pacc", "pml", "vectors")
 
     def __init__(self, *, num_q_heads: int, num_kv_heads: int, head_dim: int, num_clusters: int,
@@ -31,7 +31,7 @@ class FusedDecodeWorkspace:
         self.bytes = int(lib().semblo_decode_workspace_bytes(num_q_heads, num_kv_heads, head_dim, num_clusters,
                                                              packed_width, num_splits))
         self.buffer = torch.zeros(self.bytes, dtype=torch.uint8, device=device)
-        offs = (ctypes.c_int64 * 13)()
+        offs = (ctypes.c_int64 * len(self.NAMES))()
         check(lib().semblo_decode_workspace_offsets(num_q_heads, num_kv_heads, head_dim, num_clusters,
                                                     packed_width, num_splits, ctypes.cast(offs, ctypes.c_void_p)))
         self.offsets = dict(zip(self.NAMES, [int(o) for o in offs]))
@@ -47,13 +47,12 @@ class FusedDecodeWorkspace:
             return self.buffer[o:o + n * item].view(dtype).view(*shape)
 
         self.logit = view("logit", torch.float32, (num_kv_heads, g, c))
-        self.score = view("score", torch.float32, (num_kv_heads, c))
+        self.split = view("split", torch.int32, (num_kv_heads, num_splits, 4))
         self.rstart = view("rstart", torch.int32, (num_kv_heads, c))
         self.rlen = view("rlen", torch.int32, (num_kv_heads, c))
         self.rcum = view("rcum", torch.int32, (num_kv_heads, c))
         self.rcount = view("rcount", torch.int32, (num_kv_heads,))
         self.rtokens = view("rtokens", torch.int32, (num_kv_heads,))
-        self.rows = view("rows", torch.int32, (num_kv_heads, packed_width))
         self.vectors = view("vectors", torch.bfloat16, (num_q_heads, head_dim))
 
 
@@ -65,7 +64,9 @@ def fused_decode_step(layer, arena, *, q_post: torch.Tensor, q_pre: torch.Tensor
     """The whole decode step of one layer over ``arena`` into ``output`` [1, Hq * D].
 
     ``layer`` needs ``num_heads``, ``num_kv_heads`` and ``head_dim``.  The sink rule follows
-    SEMBLO_SINK_TOKENS as in the reference (fused_prefill._fitted_sink_tokens)."""
+    SEMBLO_SINK_TOKENS as in the reference (fused_prefill._fitted_sink_tokens).  ``stage_mask``:
+    1 score, 2 select, 4 attend (7 = the whole step); adding 8 launches the stages strictly one
+    after the other instead of overlapping each with the end of its predecessor."""
     require_cuda(q_post, q_pre, output)
     hq, hkv, d = int(layer.num_heads), int(layer.num_kv_heads), int(layer.head_dim)
     sink = int(os.environ.get("SEMBLO_SINK_TOKENS", "0") or "0")
