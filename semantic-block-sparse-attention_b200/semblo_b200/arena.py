@@ -3,6 +3,8 @@ capacity-shaped index buffers, the suffix store addressed by absolute position t
 block table, and the adoption of a request's freshly built index."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .flat_index import flat_cluster_count
@@ -16,38 +18,83 @@ def arena_cluster_count(capacity: int, unit_tokens: int, min_clusters_log2: int)
     return int(min(num_clusters, 1 << (int(capacity).bit_length() - 1)))
 
 
+def full_graph_decode_enabled() -> bool:
+    """arena.py:38-39."""
+    return os.environ.get("SEMBLO_FULL_GRAPH_DECODE") == "1"
+
+
+def suffix_reserve(room: int | None = None) -> int:
+    """arena.py:50-63: positions reserved for the generated suffix."""
+    env = os.environ.get("SEMBLO_SUFFIX_RESERVE")
+    if env is not None:
+        return int(env)
+    if room is not None:
+        return max(1, min(65536, int(room)))
+    return 65536
+
+
 class DecodeArena:
-    def __init__(self, *, capacity: int, num_kv_heads: int, head_dim: int, num_clusters: int, page_align: int,
-                 device, reserve: int, suffix_block: int = 256, packed_capacity: int | None = None,
+    """Capacity-shaped buffers for one source layer and an index object over them
+    (arena.py:66-140).  ``state`` (a SembloRuntimeState, or None) supplies engine-lifetime
+    buffers through ``pooled_buffer`` so that every request of a layer sees the same
+    addresses; without it the arena owns its tensors."""
+
+    def __init__(self, state=None, layer: int = 0, *, capacity: int, num_kv_heads: int, head_dim: int,
+                 index_dim: int | None = None, num_clusters: int, page_align: int,
+                 kv_dtype: torch.dtype = torch.bfloat16, desc_dtype: torch.dtype | None = None, device,
+                 suffix_block: int = 256, packed_capacity: int | None = None,
                  table_positions: int | None = None, keep_kpre: bool = False,
-                 kv_dtype=torch.bfloat16) -> None:
+                 reserve: int | None = None) -> None:
+        self.state = state
+        self.layer = int(layer)
         self.capacity = int(capacity)
         self.num_clusters = int(num_clusters)
-        self.reserve = int(reserve)
+        self.reserve = int(reserve) if reserve is not None else suffix_reserve()
         self.suffix_block = int(suffix_block)
         self.packed_capacity = int(packed_capacity if packed_capacity is not None else capacity)
         self.page_align = max(int(page_align), 1)
+        index_dim = int(head_dim if index_dim is None else index_dim)
+        desc_dtype = kv_dtype if desc_dtype is None else desc_dtype
+        if kv_dtype != torch.bfloat16 or desc_dtype != torch.bfloat16:
+            raise ValueError("the decode arena holds bf16 K/V and bf16 descriptors")
         width = self.packed_capacity + self.num_clusters * self.page_align
         self.width = width + (-width) % _PACK_ALIGN
-        i32 = dict(dtype=torch.int32, device=device)
-        self.posting = torch.zeros(num_kv_heads, self.width, **i32)
-        self.sizes = torch.zeros(num_kv_heads, self.num_clusters, **i32)
-        self.indptr = torch.zeros(num_kv_heads, self.num_clusters + 1, **i32)
-        self.codebooks = torch.zeros(num_kv_heads, 2, self.num_clusters, head_dim // 2, dtype=kv_dtype, device=device)
-        self.packed_kv = torch.zeros(2, self.width, num_kv_heads, head_dim, dtype=kv_dtype, device=device)
-        # the one-token warm-up index (arena.py:102-113)
-        self.sizes[:, 0] = 1
-        self.indptr[:, 1:] = 1
-        self.prompt_length_t = torch.full((1,), self.capacity, **i32)
+        device = torch.device(device)
+        fresh = [True]
+
+        def buf(name, shape, dtype, shared=False):
+            if state is None:
+                return torch.zeros(*shape, dtype=dtype, device=device)
+            key = f"arena:{name}" if shared else f"arena:{self.layer}:{name}"
+            known = key in state.index_buffers
+            t = state.pooled_buffer(key, shape, dtype, device)
+            if not known:
+                t.zero_()
+            else:
+                fresh[0] = False
+            return t
+
+        i32 = torch.int32
+        self.posting = buf("posting_positions", (num_kv_heads, self.width), i32)
+        self.sizes = buf("bucket_sizes", (num_kv_heads, self.num_clusters), i32)
+        self.indptr = buf("bucket_indptr", (num_kv_heads, self.num_clusters + 1), i32)
+        self.codebooks = buf("codebooks", (num_kv_heads, 2, self.num_clusters, index_dim // 2), desc_dtype)
+        self.packed_kv = buf("packed_kv", (2, self.width, num_kv_heads, head_dim), kv_dtype)
+        self.prompt_length_t = buf("prompt_length", (1,), i32)
         self.suffix_blocks = self.reserve // self.suffix_block + 1
-        self.suffix_kv = torch.zeros(2, self.suffix_blocks, self.suffix_block, num_kv_heads, head_dim,
-                                     dtype=kv_dtype, device=device)
+        self.suffix_kv = buf("suffix_kv", (2, self.suffix_blocks, self.suffix_block, num_kv_heads, head_dim), kv_dtype)
         span = int(table_positions if table_positions is not None else self.capacity + self.reserve)
-        self.suffix_table = torch.zeros(1, -(-span // self.suffix_block) + 1, **i32)
-        self.suffix_kpre = (torch.zeros(self.suffix_blocks, self.suffix_block, num_kv_heads, head_dim,
-                                        dtype=kv_dtype, device=device) if keep_kpre else None)
+        self.suffix_table = buf("suffix_block_table", (1, -(-span // self.suffix_block) + 1), i32, shared=True)
+        self.suffix_kpre = (buf("suffix_kpre", (self.suffix_blocks, self.suffix_block, num_kv_heads, head_dim), kv_dtype)
+                            if keep_kpre else None)
+        if fresh[0]:
+            # the one-token warm-up index (arena.py:102-113): cluster 0 of every head holds position 0
+            self.sizes[:, 0] = 1
+            self.indptr[:, 1:] = 1
+            self.prompt_length_t.fill_(self.capacity)
         self.suffix_base = -1
         self.table_filled = 0
+        self.adopted_epoch = None
         self.fused_decode_ws = None
         self.index = ProductPostingIndex(codebooks=self.codebooks, posting_positions=self.posting,
                                          bucket_indptr=self.indptr, bucket_sizes=self.sizes,
@@ -78,8 +125,11 @@ class DecodeArena:
             table[0, self.table_filled:last + 1] = ((blocks - self.suffix_base) % self.suffix_blocks).to(torch.int32)
             self.table_filled = last + 1
 
-    def adopt(self, index: ProductPostingIndex) -> ProductPostingIndex:
-        """arena.py:216-253: copy a request's index into the fixed-address buffers."""
+    def adopt(self, index: ProductPostingIndex, epoch: int | None = None) -> ProductPostingIndex:
+        """arena.py:216-253: copy a request's index into the fixed-address buffers (once per
+        ``epoch`` when one is given)."""
+        if epoch is not None and self.adopted_epoch == epoch:
+            return self.index
         length = int(index.prompt_length)
         clusters = int(index.num_buckets)
         width = int(index.posting_positions.shape[1])
@@ -106,4 +156,25 @@ class DecodeArena:
         self.index.max_position = length
         self.prompt_length_t.fill_(length)
         self.install_suffix_store(length)
+        self.adopted_epoch = epoch
         return self.index
+
+
+def arena_for(state, layer: int, *, capacity: int, unit_tokens: int, min_clusters_log2: int,
+              num_kv_heads: int, head_dim: int, index_dim: int, page_align: int,
+              kv_dtype: torch.dtype, desc_dtype: torch.dtype, device,
+              packed_capacity: int | None = None, table_positions: int | None = None,
+              keep_kpre: bool = False, reserve: int | None = None) -> DecodeArena:
+    """The layer's arena, made on first use (arena.py:256-274)."""
+    key = ("arena", int(layer))
+    arena = state.index_buffers.get(key)
+    if arena is None:
+        arena = DecodeArena(state, layer, capacity=capacity, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                            index_dim=index_dim,
+                            num_clusters=arena_cluster_count(capacity, unit_tokens, min_clusters_log2),
+                            page_align=page_align, kv_dtype=kv_dtype, desc_dtype=desc_dtype, device=device,
+                            suffix_block=int(getattr(state, "suffix_block_size", 256)),
+                            packed_capacity=packed_capacity, table_positions=table_positions,
+                            keep_kpre=keep_kpre, reserve=reserve)
+        state.index_buffers[key] = arena
+    return arena

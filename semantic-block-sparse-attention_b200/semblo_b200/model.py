@@ -1,0 +1,238 @@
+"""The sparse-attention layer body behind the ``semblo::attention`` operator.
+
+Mirror of the hot-path half of semblo/vllm_plugin/model.py (SembloAttention):
+``_init_semblo_runtime`` 302-354, ``_fit_index`` / ``_build_or_append_index`` 378-430,
+``_query_state`` 432-489, ``_arena`` 618-661, ``_adopt_into_arena`` 663-676,
+``_full_graph_decode_step`` 708-747, ``_run_product_attention`` 856-1008,
+``_sparse_layer_forward`` 1130-1167, ``attention_forward`` 1169-1269 and
+``_ingest_prompt_kv`` 1301-1382, for the configuration the kernels serve: flat partition,
+identity routing map with whole-vector normalisation, the layer's own cluster-ordered prompt
+copy (own_prompt_cache), the fused decode step over the decode arena.  The model-specific
+subclass sets ``num_heads / num_kv_heads / head_dim / scaling / is_kv_shared_layer`` and
+``attn.layer_name``, implements ``_project_qkv`` and ``_finish_output``, and calls
+``_init_semblo_runtime``; everything that differs from the served configuration raises."""
+from __future__ import annotations
+
+import os
+from types import SimpleNamespace
+
+import torch
+from torch import nn
+
+import semblo_b200
+
+from . import _lib
+from . import arena as _arena
+from . import fused_decode as _fused_decode
+from . import fused_prefill as _fused_prefill
+from .attention_op import register_layer, sparse_attention_op
+from .config import SembloVllmConfig
+from .flat_index import routing_normalize
+from .state import ProductPostingIndex, SembloRuntimeState
+from .trivial_router import trivial_router_vectors
+
+
+class SembloAttention(nn.Module):
+    """Sparse attention for one full-attention layer."""
+
+    def _init_semblo_runtime(self, *, runtime_config: SembloVllmConfig, runtime_state: SembloRuntimeState,
+                             layer_idx: int, source_layer_idx: int, uses_sparse_attention: bool = True,
+                             builds_product_index: bool = True,
+                             attention_logits_soft_cap: float | None = None) -> None:
+        """Requires ``num_heads / num_kv_heads / head_dim / scaling`` to be set already."""
+        runtime_config.validate()
+        if attention_logits_soft_cap:
+            raise RuntimeError("the fused sparse path has no logit soft cap")
+        if int(runtime_config.index_dim) != int(self.head_dim):
+            raise RuntimeError("the routing map is the identity: index_dim must equal head_dim")
+        self.layer_idx = int(layer_idx)
+        self.source_layer_idx = int(source_layer_idx)
+        self.uses_sparse_attention = bool(uses_sparse_attention)
+        self.builds_product_index = bool(builds_product_index)
+        self.runtime_config = runtime_config
+        self.runtime_state = runtime_state
+        self.attention_logits_soft_cap = attention_logits_soft_cap
+        self.layer_target_tokens = runtime_config.layer_target_tokens.get(self.layer_idx, runtime_config.target_tokens)
+        self.layer_decode_target_tokens = (
+            self.layer_target_tokens
+            if self.layer_idx in runtime_config.layer_target_tokens or not runtime_config.decode_target_tokens
+            else runtime_config.decode_target_tokens)
+        self._effective_target = self.layer_target_tokens
+        if not hasattr(self, "is_kv_shared_layer"):
+            self.is_kv_shared_layer = False
+        if self.builds_product_index:
+            runtime_state.register_source_module(self.layer_idx, self)
+        layer_name = getattr(getattr(self, "attn", None), "layer_name", None)
+        if layer_name is not None:
+            register_layer(layer_name, self)
+
+    # ---- the traced side -----------------------------------------------------------------
+    def _positions_for_runtime(self, positions: torch.Tensor):
+        return positions, positions
+
+    def _sparse_layer_forward(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
+        rope_positions, positions = self._positions_for_runtime(positions)
+        q_post, k_post, v_states, q_pre, k_pre, gate = self._project_qkv(rope_positions, hidden_states)
+        attn_output = torch.empty_like(q_post)
+        sparse_attention_op(positions, hidden_states, q_post, k_post, v_states, q_pre, k_pre, attn_output,
+                            self.attn.layer_name)
+        return self._finish_output(attn_output, gate)
+
+    # ---- index ---------------------------------------------------------------------------
+    def _source_module(self) -> "SembloAttention":
+        return self.runtime_state.get_source_module(self.source_layer_idx)
+
+    def _fit_index(self, product, positions) -> ProductPostingIndex:
+        if positions.numel() < 128:
+            raise ValueError("sparse prefill requires at least 128 prompt tokens after chat formatting")
+        cfg = self.runtime_config
+        return ProductPostingIndex.build(
+            product, positions, num_centroids=cfg.num_centroids, kmeans_iters=cfg.kmeans_iters,
+            kmeans_sample_size=cfg.kmeans_sample_size, codebook_seed=cfg.codebook_seed + self.source_layer_idx,
+            layer_idx=self.source_layer_idx, flat_unit_tokens=cfg.flat_unit_tokens,
+            flat_min_clusters_log2=cfg.flat_min_clusters_log2, page_align=cfg.fa3_page_align)
+
+    def _build_or_append_index(self, k_pre_rope: torch.Tensor, positions: torch.Tensor) -> ProductPostingIndex:
+        if not self.builds_product_index:
+            raise RuntimeError("only layers with their own K/V can build an index")
+        if self.runtime_state.step_first_position != 0:
+            return self.runtime_state.get(self.source_layer_idx)
+        # SembloKeyRouter with the identity map: unit-normalise the whole key (routing_map.py:35-94)
+        product = routing_normalize(k_pre_rope.view(-1, self.num_kv_heads, self.head_dim))
+        index = self._fit_index(product, positions)
+        self.runtime_state.put(self.source_layer_idx, index)
+        return index
+
+    def _query_state(self, q_pre_rope: torch.Tensor, source: "SembloAttention"):
+        """Routing vectors of [Q, Hq, D] pre-RoPE queries: one per head, uniform mixture."""
+        if (os.environ.get("SEMBLO_ROUTING_NORMALIZE", "whole") or "whole") != "whole":
+            raise RuntimeError("only SEMBLO_ROUTING_NORMALIZE=whole is implemented")
+        queries, heads, dim = q_pre_rope.shape
+        vectors = trivial_router_vectors(q_pre_rope).view(1, queries, heads, 1, dim)
+        return SimpleNamespace(vectors=vectors, mixture_weights=None)
+
+    # ---- arena ---------------------------------------------------------------------------
+    def _arena(self, like: torch.Tensor):
+        cfg = self.runtime_config
+        unit_tokens = int(os.environ.get("SEMBLO_FLAT_UNIT_TOKENS", cfg.flat_unit_tokens))
+        if unit_tokens <= 0:
+            raise RuntimeError("the decode arena needs the flat index (flat_unit_tokens > 0)")
+        from . import suffix_flush as _flush
+        room = int(self.runtime_state.max_model_len) - int(cfg.token_capacity)
+        reserve = _arena.suffix_reserve(room)
+        extra = dict(reserve=reserve)
+        if _flush.enabled():
+            if _flush.keep_exact() + _flush.flush_every() > reserve:
+                raise RuntimeError("SEMBLO_SUFFIX_KEEP_EXACT + SEMBLO_SUFFIX_FLUSH_EVERY must not exceed the "
+                                   f"suffix reserve ({reserve})")
+            extra.update(packed_capacity=int(self.runtime_state.max_model_len),
+                         table_positions=int(self.runtime_state.max_model_len) + reserve, keep_kpre=True)
+        elif room > reserve:
+            raise RuntimeError(f"the arena reserves {reserve} generated positions but max_model_len "
+                               f"{self.runtime_state.max_model_len} minus the token capacity "
+                               f"{cfg.token_capacity} allows {room}")
+        return _arena.arena_for(
+            self.runtime_state, self.source_layer_idx, capacity=int(cfg.token_capacity), unit_tokens=unit_tokens,
+            min_clusters_log2=max(3, int(os.environ.get("SEMBLO_FLAT_MIN_CLUSTERS_LOG2", cfg.flat_min_clusters_log2))),
+            num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, index_dim=int(cfg.index_dim),
+            page_align=int(os.environ.get("SEMBLO_FA3_ALIGN", cfg.fa3_page_align)), kv_dtype=like.dtype,
+            desc_dtype=like.dtype, device=like.device, **extra)
+
+    def _adopt_into_arena(self) -> None:
+        """After a request's prefill: its index moves into the layer's arena."""
+        index = self.runtime_state.source_indexes.get(self.source_layer_idx)
+        if index is None or index.packed_kv is None:
+            return
+        self._arena(index.packed_kv).adopt(index, self.runtime_state.prompt_epoch)
+
+    def _target_for_step(self, is_decode: bool) -> int:
+        return self.layer_decode_target_tokens if is_decode else self.layer_target_tokens
+
+    def _full_graph_decode_step(self, positions, q_post, k_post, v_states, q_pre, output, k_pre=None) -> None:
+        """One generated token: the fused step over the layer's fixed-address arena.  No host
+        state, so the caller may be capturing a CUDA graph."""
+        arena = self._source_module()._arena(q_post)
+        if not self.is_kv_shared_layer and (k_post is None or v_states is None):
+            raise RuntimeError("physical sparse layers must produce K/V")
+        self._effective_target = self._target_for_step(True)
+        shared = self.is_kv_shared_layer
+        _fused_decode.fused_decode_step(
+            self, arena, q_post=q_post, q_pre=q_pre, positions=positions,
+            k_post=None if shared else k_post.view(-1, self.num_kv_heads, self.head_dim),
+            v_states=None if shared else v_states.view(-1, self.num_kv_heads, self.head_dim),
+            k_pre=None if shared or k_pre is None else k_pre.view(-1, self.num_kv_heads, self.head_dim),
+            output=output, temperature=self.runtime_config.selection_temperature,
+            beta=self.runtime_config.bucket_size_penalty, target_tokens=int(self._effective_target),
+            sm_scale=self.scaling, num_splits=self.runtime_config.packed_decode_num_splits * 2)
+
+    # ---- prompt --------------------------------------------------------------------------
+    def _ingest_prompt_kv(self, k_post, v_states, k_pre, positions, *, prompt_order_views: bool = True) -> None:
+        """Build the index from the pre-RoPE keys and pack the prompt's post-RoPE K/V in cluster
+        order.  ``prompt_order_views`` leaves views of this call's K/V on the index: the chunk loop
+        reads each chunk's exact local window from them."""
+        if self.is_kv_shared_layer:
+            return
+        if k_post is None or v_states is None:
+            raise RuntimeError("physical sparse layers must produce K/V")
+        if not self.builds_product_index:
+            return
+        if k_pre is None:
+            raise RuntimeError("a product-index source must produce pre-RoPE keys")
+        index = self._build_or_append_index(k_pre, positions)
+        if index.packed_kv is None:
+            k3 = k_post.view(-1, self.num_kv_heads, self.head_dim)
+            v3 = v_states.view(-1, self.num_kv_heads, self.head_dim)
+            index.pack_prompt_kv(k3, v3)
+            if prompt_order_views:
+                index.original_kv = (k3, v3)
+            if _arena.full_graph_decode_enabled():
+                self._arena(k_post).install_suffix_store(int(index.prompt_length))
+
+    def _run_product_attention(self, q_post_rope, q_pre_rope, positions, out=None, query_offset: int = 0):
+        """Sparse attention for the given prompt queries, written into ``out`` if given.
+        ``query_offset`` is where these queries start in the prompt."""
+        semblo_b200.SPARSE_ATTENTION_CALLS += 1
+        source = self._source_module()
+        index = self.runtime_state.get(self.source_layer_idx)
+        q = q_post_rope.view(-1, self.num_heads, self.head_dim)
+        q_pre = q_pre_rope.view(-1, self.num_heads, self.head_dim)
+        if self.runtime_state.step_first_position >= int(index.prompt_length):
+            raise RuntimeError("generated tokens go through the decode arena (SEMBLO_FULL_GRAPH_DECODE=1)")
+        self._effective_target = self._target_for_step(False)
+        output = out.view(-1, self.num_heads, self.head_dim) if out is not None else torch.empty_like(q)
+        step = self.runtime_config.query_chunk_size
+        n_queries = positions.numel()
+        fused_snapshot = None
+        for start in range(0, n_queries, step):
+            end = min(n_queries, start + step)
+            q_positions = positions[start:end].to(torch.int32)
+            query_state = self._query_state(q_pre[start:end], source)
+            if fused_snapshot is None:
+                fused_snapshot = getattr(index, "_token_outer_snapshot", None) or _fused_prefill.CausalSnapshot(index)
+            _fused_prefill.fused_chunk_attention(
+                q[start:end], query_state, index, q_positions, fused_snapshot, start + query_offset,
+                end - 1 + query_offset, temperature=self.runtime_config.selection_temperature,
+                beta=self.runtime_config.bucket_size_penalty, target_tokens=int(self._effective_target),
+                queries_per_block=self.runtime_config.fused_select_block_queries, sm_scale=self.scaling,
+                dense_prefix_x=4, out=output[start:end])
+        if getattr(index, "original_kv", None) is not None:
+            index.original_kv = None                  # the views are dropped once the prompt has been attended
+        _lib.status_for(q.device).poll()
+        return output.flatten(-2, -1)
+
+    def attention_forward(self, positions, hidden_states, q_post, k_post, v_states, q_pre, k_pre, output) -> None:
+        """The attention core, reached only through the operator; the result goes into ``output``."""
+        if _arena.full_graph_decode_enabled() and positions.numel() == 1:
+            self._full_graph_decode_step(positions, q_post, k_post, v_states, q_pre, output, k_pre=k_pre)
+            return
+        self.runtime_state.maybe_begin_prompt(self.layer_idx, positions,
+                                              engage_above_tokens=self.runtime_config.engage_above_tokens)
+        if self.runtime_state.dense_request or not self.uses_sparse_attention:
+            raise RuntimeError("this layer serves the sparse path only: the stock attention of a dense request "
+                               "stays with the model's own attention layer")
+        self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
+        sparse_output = self._run_product_attention(q_post, q_pre, positions, out=output)
+        if sparse_output.data_ptr() != output.data_ptr():
+            output.copy_(sparse_output.view(output.shape))
+        if _arena.full_graph_decode_enabled() and positions.numel() > 1:
+            self._adopt_into_arena()

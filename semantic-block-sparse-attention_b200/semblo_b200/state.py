@@ -200,3 +200,75 @@ class ProductPostingIndex:
 
     def inverse_positions(self) -> torch.Tensor:
         return self._inverse_positions
+
+
+class SembloRuntimeState:
+    """Request-local state shared by the sparse layers of one model: the prompt's indexes by
+    source layer, engine-lifetime buffers, and the position bookkeeping of
+    semblo/vllm_plugin/state.py (SembloRuntimeState: pooled_buffer 1286-1300, reset 1322-1329,
+    maybe_begin_prompt 1417-1477, put/get 1479-1494).  One request at a time."""
+
+    def __init__(self, max_model_len: int, reset_layer_idx: int | None = None) -> None:
+        self.max_model_len = int(max_model_len)
+        self.reset_layer_idx = reset_layer_idx
+        self.source_indexes: dict = {}
+        self.index_buffers: dict = {}
+        self.source_modules: dict = {}
+        self.step_first_position = 0
+        self.expected_next_position = 0
+        self.prompt_epoch = 0
+        self.dense_request = False
+        self.suffix_block_size = 256
+
+    def register_source_module(self, layer_idx: int, module) -> None:
+        self.source_modules[int(layer_idx)] = module
+        if self.reset_layer_idx is None or int(layer_idx) < int(self.reset_layer_idx):
+            self.reset_layer_idx = int(layer_idx)          # the earliest sparse layer begins a prompt
+
+    def get_source_module(self, layer_idx: int):
+        return self.source_modules[int(layer_idx)]
+
+    def pooled_buffer(self, key, shape, dtype, device) -> torch.Tensor:
+        signature = (tuple(shape), dtype, torch.device(device))
+        buffer = self.index_buffers.get(key)
+        if buffer is None or self.index_buffers.get((key, "sig")) != signature:
+            buffer = torch.empty(*shape, dtype=dtype, device=device)
+            self.index_buffers[key] = buffer
+            self.index_buffers[(key, "sig")] = signature
+        return buffer
+
+    def reset(self) -> None:
+        self.dense_request = False
+        self.source_indexes.clear()
+        self.prompt_epoch += 1
+
+    def maybe_begin_prompt(self, layer_idx: int, positions: torch.Tensor, engage_above_tokens: int = 0) -> None:
+        """Reset the request-local indexes exactly once at a new prompt.  A decode step that follows
+        the previous call by one position is tracked on the host; anything else reads
+        ``positions[0]`` (one synchronisation, as in the reference)."""
+        if self.reset_layer_idx is None or int(layer_idx) != int(self.reset_layer_idx):
+            return
+        if positions.ndim != 1 or positions.numel() == 0:
+            raise ValueError("positions must be a non-empty one-dimensional tensor")
+        if positions.numel() == 1 and self.expected_next_position > 0:
+            self.step_first_position = self.expected_next_position
+        else:
+            self.step_first_position = int(positions[0].item())
+        self.expected_next_position = self.step_first_position + positions.numel()
+        if self.step_first_position == 0:
+            expected = torch.arange(positions.numel(), device=positions.device, dtype=positions.dtype)
+            if not torch.equal(positions, expected):
+                raise RuntimeError("the full prompt must arrive in one contiguous prefill call")
+            self.reset()
+            self.dense_request = 0 < engage_above_tokens and positions.numel() <= engage_above_tokens
+
+    def put(self, source_layer_idx: int, index: ProductPostingIndex) -> None:
+        if int(source_layer_idx) in self.source_indexes:
+            raise RuntimeError(f"semblo prompt index for source layer {source_layer_idx} was built more than once")
+        self.source_indexes[int(source_layer_idx)] = index
+
+    def get(self, source_layer_idx: int) -> ProductPostingIndex:
+        try:
+            return self.source_indexes[int(source_layer_idx)]
+        except KeyError as exc:
+            raise RuntimeError(f"semblo index for source layer {source_layer_idx} is unavailable") from exc

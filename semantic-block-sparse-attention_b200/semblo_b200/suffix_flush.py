@@ -5,12 +5,28 @@ identity routing map, repack_apply 97-133) on a DecodeArena.  It runs between de
 eagerly, on the arena's own buffers."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
 from ._lib import check, lib, ptr, stream_ptr
 from .flat_index import routing_normalize
 from .token_outer import nearest_cluster
+
+
+def flush_every() -> int:
+    """suffix_flush.py:29-30."""
+    return int(os.environ.get("SEMBLO_SUFFIX_FLUSH_EVERY", "0") or 0)
+
+
+def keep_exact() -> int:
+    """suffix_flush.py:33-34."""
+    return int(os.environ.get("SEMBLO_SUFFIX_KEEP_EXACT", "1024") or 1024)
+
+
+def enabled() -> bool:
+    return flush_every() > 0
 
 
 def flush_range(prompt_len: int, written: int, plen_cur: int, keep: int, every: int):

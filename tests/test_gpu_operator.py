@@ -1,0 +1,151 @@
+"""The operator boundary: a layer subclass with fixed projections is driven through
+``torch.ops.semblo.attention`` for a whole prompt (index build, packing, the query-chunk loop),
+the adoption into the decode arena and a few generated tokens, as the reference's model hooks
+drive it (semblo/vllm_plugin/model.py:1130-1269)."""
+from __future__ import annotations
+
+import os
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from oracle import semblo_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from semblo_b200 import _lib
+    _lib.lib()
+    return torch.device("cuda:0")
+
+
+def _make_layer(data, dev, *, hq, hkv, dim, cfg, state, name):
+    from semblo_b200.model import SembloAttention
+
+    class Layer(SembloAttention):
+        """The model-specific half: projections are lookups into the synthetic tensors."""
+
+        def __init__(self):
+            super().__init__()
+            self.num_heads, self.num_kv_heads, self.head_dim = hq, hkv, dim
+            self.scaling = dim ** -0.5
+            self.is_kv_shared_layer = False
+            self.attn = SimpleNamespace(layer_name=name)
+            self._init_semblo_runtime(runtime_config=cfg, runtime_state=state, layer_idx=0, source_layer_idx=0,
+                                      uses_sparse_attention=True, builds_product_index=True,
+                                      attention_logits_soft_cap=None)
+
+        def _project_qkv(self, positions, hidden_states):
+            idx = positions.long()
+            d = {k: v[idx] for k, v in data.items()}
+            n = idx.numel()
+            return (d["q_post"].reshape(n, hq * dim), d["k_post"].reshape(n, hkv * dim), d["v"], d["q_pre"],
+                    d["k_pre"], None)
+
+        def _finish_output(self, attn_output, gate):
+            return attn_output
+
+    return Layer()
+
+
+def test_prompt_and_decode_through_the_operator(dev):
+    from semblo_b200 import _lib
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.fused_prefill import CausalSnapshot, fused_chunk_attention
+    from semblo_b200.state import SembloRuntimeState
+    from semblo_b200.trivial_router import trivial_router_vectors
+    import semblo_b200
+    dim, hq, hkv, sink, length, target, local, chunk, steps = 128, 8, 2, 64, 5120, 256, 128, 1024, 5
+    cpu = O.mixture_inputs(length=length + steps, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=5)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4)
+    state = SembloRuntimeState(max_model_len=8192 + 512)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL=str(local), SEMBLO_FULL_GRAPH_DECODE="1",
+               SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16")
+    os.environ.update(env)
+    try:
+        layer = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=state, name="model.layers.0.self_attn.attn")
+        calls = semblo_b200.SPARSE_ATTENTION_CALLS
+        positions = torch.arange(length, device=dev)
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        out = layer._sparse_layer_forward(positions, hidden).view(length, hq, dim)
+        torch.cuda.synchronize()
+        _lib.status_for(dev).raise_if_set()
+        assert semblo_b200.SPARSE_ATTENTION_CALLS > calls          # the sparse path ran
+        index = state.get(0)
+        assert index.original_kv is None                            # the prompt-order views were dropped
+        arena = layer._arena(data["q_post"])
+        assert arena.adopted_epoch == state.prompt_epoch
+        assert int(arena.prompt_length_t.item()) == length
+        # the same chunk loop by hand over the same index: identical bytes
+        index.original_kv = (data["k_post"][:length], data["v"][:length])
+        snap = CausalSnapshot(index)
+        want = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=dev)
+        selections = {}
+        for cs in range(0, length, chunk):
+            ce = cs + chunk - 1
+            qv = trivial_router_vectors(data["q_pre"][cs:ce + 1])
+            fused_chunk_attention(data["q_post"][cs:ce + 1], SimpleNamespace(vectors=qv.view(1, chunk, hq, 1, dim)),
+                                  index, torch.arange(cs, ce + 1, dtype=torch.int32, device=dev), snap, cs, ce,
+                                  temperature=0.1, beta=0.25, target_tokens=target, sm_scale=dim ** -0.5,
+                                  out=want[cs:ce + 1])
+            if O.chunk_plan(cs, target, local) > 0:
+                selections[cs] = O.unpack_bits(snap.qmask[:chunk].cpu())
+        assert torch.equal(out, want)
+        # and the oracle on the kernel's own selections
+        oidx = O.FlatIndex(codebooks=index.codebooks.cpu(), posting_positions=index.posting_positions.cpu(),
+                           bucket_indptr=index.bucket_indptr.cpu(), bucket_sizes=index.bucket_sizes.cpu(),
+                           inverse_positions=index.inverse_positions().cpu(), assign=index.orig_bucket.cpu().long(),
+                           prompt_length=length, page_align=16, packed_kv=index.packed_kv.cpu())
+        ref = O.prefill_attention(cpu["q_post"][:length], cpu["q_pre"][:length], cpu["k_post"][:length],
+                                  cpu["v"][:length], oidx, temperature=0.1, beta=0.25, target_tokens=target, sink=sink,
+                                  local=local, sm_scale=dim ** -0.5, chunk=chunk, selections=dict(selections))
+        diff = (out.cpu().double() - ref).abs()
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 1e-3
+        # generated tokens: one position per call through the same operator
+        aref = O.make_arena(capacity=8192, num_clusters=arena.num_clusters, num_kv_heads=hkv, head_dim=dim,
+                            page_align=16, reserve=arena.reserve, kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16)
+        O.arena_adopt(aref, oidx)
+        for s in range(steps):
+            pos = length + s
+            o = layer._sparse_layer_forward(torch.tensor([pos], device=dev), hidden[:1]).view(hq, dim)
+            _lib.status_for(dev).raise_if_set()
+            ws = arena.fused_decode_ws
+            sel = torch.zeros(hkv, arena.num_clusters, dtype=torch.bool)
+            for h in range(hkv):
+                n = int(ws.rcount[h])
+                ids = torch.searchsorted(aref.indptr[h].contiguous(), ws.rstart[h, :n].cpu(), right=True) - 1
+                sel[h, ids] = True
+            wd, _, _ = O.decode_step(aref, q_post=cpu["q_post"][pos], q_pre=cpu["q_pre"][pos], pos=pos,
+                                     k_post=cpu["k_post"][pos], v=cpu["v"][pos], temperature=0.1, beta=0.25,
+                                     target_tokens=target, sink=sink, sm_scale=dim ** -0.5, sel=sel)
+            d = (o.cpu().double() - wd).abs()
+            assert float(d.max()) <= 2e-2 and float(d.mean()) <= 1e-3, (s, float(d.max()))
+        # a second prompt reuses the arena's buffers (same addresses) under a new epoch
+        ptr_before = arena.packed_kv.data_ptr()
+        out2 = layer._sparse_layer_forward(positions, hidden).view(length, hq, dim)
+        torch.cuda.synchronize()
+        assert layer._arena(data["q_post"]).packed_kv.data_ptr() == ptr_before
+        assert torch.equal(out2, out)
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
+def test_operator_refuses_what_it_does_not_serve(dev):
+    from semblo_b200.attention_op import registered_layer
+    from semblo_b200.config import SembloVllmConfig
+    with pytest.raises(RuntimeError):
+        registered_layer("no.such.layer")
+    with pytest.raises(ValueError):
+        SembloVllmConfig(token_capacity=1024, target_tokens=64, flat_unit_tokens=32, index_dim=128,
+                         own_prompt_cache=False).validate()
+    with pytest.raises(ValueError):
+        SembloVllmConfig(token_capacity=1024, target_tokens=64, flat_unit_tokens=0, index_dim=128).validate()
