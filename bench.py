@@ -12,12 +12,20 @@ Workload at N = 1: 131072-token prompt, 16 query / 4 KV heads, head_dim 256, bf1
 RoPE on 25 % of the dims, keys from a 256-centre Gaussian mixture per head, 64-token blocks,
 budget 4096 tokens + 128-token sink + 512-token local window, 16-token pages behind a seeded
 random page permutation.  At N > 1 every rank runs that step for its own 4-KV-head shard of a
-layer with 4 N KV heads and the per-head outputs are all-gathered with NCCL after each chunk
-(head-parallel, weak scaling); the value then counts token-shards per second.
+layer with 4 N KV heads and the per-head outputs are all-gathered with NCCL, chunk by chunk on a
+communication stream while the next chunk computes (head-parallel, weak scaling); the value
+then counts token-shards per second.
 
-The JSON line also carries the decode figure (microseconds per step at 524288 tokens) and the
-roofline of the dominant kernel of each.  ``--impl reference`` times the CPU restatement of the
-reference path (torch on the host cores) on a bounded sample of the same workload.
+The JSON line also carries
+  * ``decode``: microseconds per step at 524288 tokens and the roofline of its kernels;
+  * ``head_sharded``: the head-sharded configuration as written - one 1048576-token layer with
+    32 query / 8 KV heads of head_dim 128, 16384 clusters, budget 8192, its KV heads split
+    8 / 4 / 2 / 1 per GPU on 1 / 2 / 4 / 8 GPUs (strong scaling), then 128 decode steps, every
+    output gathered over NVLink;
+  * ``roofline``: the sparse kernel's own fraction first, then every attention launch kind.
+``--impl reference`` times the reference path on the host cores (the reference's own torch
+functions where they run on a CPU and are present, the CPU restatement for the rest) on a
+bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -41,9 +49,13 @@ import torch  # noqa: E402
 
 PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_log2=7, target=4096,
                sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of sparse_gather_prefill_kernel on the 131072-token
-# step, from a one-pass ncu capture of this file's own command (summary: profiles/prefill_128k_dram_traffic.md)
-GATHER_DRAM_BYTES_PER_LAUNCH = 1.307e9
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
+# command, keyed by (kernel, prompt length): a record of a past capture, not something a run produces
+DRAM_TRAFFIC_PER_LAUNCH = {("sparse_gather_prefill_kernel<256,4>", 131072): 1.307e9}
+
+HEAD_SHARDED = dict(length=1048576, hq=32, hkv=8, dim=128, centres=1024, unit=64, min_log2=7, target=8192,
+                    sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16, reserve=1024,
+                    decode_steps=128)
 
 DECODE = dict(length=524288, hq=16, hkv=4, dim=256, centres=512, unit=64, min_log2=7, target=4096,
               sink=128, reserve=1024, steps=256, temperature=0.1, beta=0.25, splits=37)
@@ -59,72 +71,73 @@ def peaks():
 
 
 # ------------------------------------------------------------------------- synthetic inputs
-def mixture_inputs_device(cfg, seed, device, length=None):
+def mixture_inputs_device(cfg, seed, device, length=None, heads=None):
     """Seeded Gaussian-mixture keys/queries (sigma 0.3 around N(0,1) centres), N(0,1) values,
-    partial RoPE (theta 1e7) on the first quarter of the dims.  Same recipe as the oracle's
-    ``mixture_inputs``, generated on the device."""
+    partial RoPE (theta 1e7) on the first quarter of the dims: the recipe of the oracle's
+    ``mixture_inputs``, generated on the device.  Every KV head has a generator of its own
+    (seed + 7919 * global head id; the cluster label of a token is shared), so a rank that holds
+    the heads ``heads`` of a layer gets exactly those heads of the unsharded tensors."""
     length = length or cfg["length"]
     hq, hkv, dim = cfg["hq"], cfg["hkv"], cfg["dim"]
+    group = hq // hkv
+    heads = range(hkv) if heads is None else heads
+    nh = len(heads)
     g = torch.Generator(device=device)
     g.manual_seed(seed)
-    group = hq // hkv
-    cent = torch.randn(hkv, cfg["centres"], dim, generator=g, device=device)
     z = torch.randint(0, cfg["centres"], (length,), generator=g, device=device)
-    base = cent[:, z].permute(1, 0, 2)                                   # [L, Hkv, D]
-    # contiguous [L, Hkv, D] like a model's projection output (the sum inherits the permuted strides of `base`)
-    k_pre = (base + 0.3 * torch.randn(length, hkv, dim, generator=g, device=device)).contiguous()
-    v = torch.randn(length, hkv, dim, generator=g, device=device).to(torch.bfloat16)
     pos = torch.arange(length, device=device)
+    r = dim // 4
+    half = r // 2
+    inv = 1e7 ** (-torch.arange(half, device=device, dtype=torch.float64) / half)
+    k_pre = torch.empty(length, nh, dim, dtype=torch.bfloat16, device=device)
+    k_post = torch.empty_like(k_pre)
+    v = torch.empty_like(k_pre)
+    q_pre = torch.empty(length, nh * group, dim, dtype=torch.bfloat16, device=device)
+    q_post = torch.empty_like(q_pre)
 
-    def rope(x):
-        r = dim // 4
-        half = r // 2
-        inv = 1e7 ** (-torch.arange(half, device=device, dtype=torch.float64) / half)
-        ang = pos.double()[:, None] * inv[None]
-        cos, sin = ang.cos().float(), ang.sin().float()
-        shape = [length] + [1] * (x.ndim - 2) + [half]
-        cos, sin = cos.view(shape), sin.view(shape)
+    def rope(x, lo, hi):
+        ang = pos[lo:hi].double()[:, None] * inv[None]
+        shape = [hi - lo] + [1] * (x.ndim - 2) + [half]
+        cos, sin = ang.cos().float().view(shape), ang.sin().float().view(shape)
         out = x.clone()
-        x1, x2 = x[..., :half], x[..., half:r]
-        out[..., :half] = x1 * cos - x2 * sin
-        out[..., half:r] = x2 * cos + x1 * sin
+        out[..., :half] = x[..., :half] * cos - x[..., half:r] * sin
+        out[..., half:r] = x[..., half:r] * cos + x[..., :half] * sin
         return out
 
-    k_post = rope(k_pre).to(torch.bfloat16)
-    k_pre = k_pre.to(torch.bfloat16)
-    q_pre = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=device)
-    q_post = torch.empty(length, hq, dim, dtype=torch.bfloat16, device=device)
-    step = 16384
-    for lo in range(0, length, step):
-        hi = min(length, lo + step)
-        qf = base[lo:hi, :, None, :] + 0.3 * torch.randn(hi - lo, hkv, group, dim, generator=g, device=device)
-        qf = qf.reshape(hi - lo, hq, dim)
-        q_pre[lo:hi] = qf.to(torch.bfloat16)
-        r = dim // 4
-        half = r // 2
-        inv = 1e7 ** (-torch.arange(half, device=device, dtype=torch.float64) / half)
-        ang = pos[lo:hi].double()[:, None] * inv[None]
-        cos, sin = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
-        out = qf.clone()
-        out[..., :half] = qf[..., :half] * cos - qf[..., half:r] * sin
-        out[..., half:r] = qf[..., half:r] * cos + qf[..., :half] * sin
-        q_post[lo:hi] = out.to(torch.bfloat16)
+    step = 65536
+    for j, h in enumerate(heads):
+        g.manual_seed(seed + 7919 * (h + 1))
+        cent = torch.randn(cfg["centres"], dim, generator=g, device=device)
+        for lo in range(0, length, step):
+            hi = min(length, lo + step)
+            base = cent[z[lo:hi]]                                            # [n, D]
+            kf = base + 0.3 * torch.randn(hi - lo, dim, generator=g, device=device)
+            k_pre[lo:hi, j] = kf.to(torch.bfloat16)
+            k_post[lo:hi, j] = rope(kf, lo, hi).to(torch.bfloat16)
+            v[lo:hi, j] = torch.randn(hi - lo, dim, generator=g, device=device).to(torch.bfloat16)
+            qf = base[:, None, :] + 0.3 * torch.randn(hi - lo, group, dim, generator=g, device=device)
+            q_pre[lo:hi, j * group:(j + 1) * group] = qf.to(torch.bfloat16)
+            q_post[lo:hi, j * group:(j + 1) * group] = rope(qf, lo, hi).to(torch.bfloat16)
     return dict(q_pre=q_pre, q_post=q_post, k_pre=k_pre, k_post=k_post, v=v)
 
 
 # ------------------------------------------------------------------------- the prefill step
 class PrefillStep:
     """The reference's prompt forward of one sparse layer (model.py:1169-1269: ingest, then the
-    query-chunk loop of _run_product_attention 856-1008) on the mirrored entry points."""
+    query-chunk loop of _run_product_attention 856-1008) on the mirrored entry points, for the KV
+    heads this rank holds (``hkv_local`` of them, starting at global head ``head_offset``)."""
 
-    def __init__(self, cfg, device, world=1):
+    def __init__(self, cfg, device, world=1, hkv_local=None, head_offset=0, per_head_seed=False):
         from semblo_b200 import _lib
         self.cfg, self.device, self.world = cfg, device, world
+        self.hkv = cfg["hkv"] if hkv_local is None else hkv_local
+        self.hq = self.hkv * (cfg["hq"] // cfg["hkv"])
+        self.head_offset, self.per_head_seed = head_offset, per_head_seed
         self.page_table = None
-        self.attended = torch.zeros(2, dtype=torch.int64, device=device)
+        self.attended = torch.zeros(4, dtype=torch.int64, device=device)    # window pairs, -, sparse pairs, gathered rows
         self.attn_events = []
         self.time_attention = False
-        self.gathered = None
+        self.gather = None
         self._lib = _lib
 
     def run(self, x, out, before_chunk=None, after_chunk=None):
@@ -135,11 +148,13 @@ class PrefillStep:
         from semblo_b200.state import ProductPostingIndex
         from semblo_b200.trivial_router import trivial_router_vectors
         cfg, dev = self.cfg, self.device
-        length, hq, dim, chunk = cfg["length"], cfg["hq"], cfg["dim"], cfg["chunk"]
+        length, hq, dim, chunk = cfg["length"], self.hq, cfg["dim"], cfg["chunk"]
         product = routing_normalize(x["k_pre"])
         index = ProductPostingIndex.build(product, self.positions, kmeans_sample_size=8192, codebook_seed=0,
                                           flat_unit_tokens=cfg["unit"], flat_min_clusters_log2=cfg["min_log2"],
-                                          page_align=cfg["page"])
+                                          page_align=cfg["page"], per_head_seed=self.per_head_seed,
+                                          head_offset=self.head_offset)
+        del product
         width = int(index.posting_positions.shape[1])
         n_pages = (width + (-width) % 256) // 16
         if self.page_table is None or self.page_table.numel() != n_pages:
@@ -157,24 +172,25 @@ class PrefillStep:
                 before_chunk(cs, ce)
             qv = trivial_router_vectors(x["q_pre"][cs:ce + 1])
             state = SimpleNamespace(vectors=qv.view(1, n, hq, 1, dim))
-            if self.time_attention:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                self._pending = (e0, e1)
             fused_chunk_attention(x["q_post"][cs:ce + 1], state, index, self.positions32[cs:ce + 1], snap, cs, ce,
                                   temperature=cfg["temperature"], beta=cfg["beta"], target_tokens=cfg["target"],
                                   sm_scale=sm_scale, out=out[cs:ce + 1], attended=self.attended,
                                   _timer=self._timer if self.time_attention else None)
             if self.world > 1:
-                # the one collective of the path: per-head outputs of the chunk to every rank
-                if self.gathered is None:
+                # The one collective of the path: the chunk's per-head outputs to every rank.  It runs on a
+                # communication stream behind this chunk's kernels while the next chunk computes; two
+                # receive buffers alternate, and the step ends when the last gather has landed.
+                if self.gather is None:
                     from semblo_b200.head_parallel import HeadGather
-                    self.gathered = HeadGather()
-                    self.full_out = torch.empty(chunk, hq * self.world, dim, dtype=torch.bfloat16, device=dev)
+                    self.gather = HeadGather()
+                    self.full_out = torch.empty(2, self.world, chunk, hq, dim, dtype=torch.bfloat16, device=dev)
                 if n != chunk:
                     raise RuntimeError("the prompt length must be a multiple of the query chunk")
-                self.gathered(out[cs:ce + 1], self.full_out)
+                self.gather.issue(out[cs:ce + 1], self.full_out[(cs // chunk) % 2])
             if after_chunk is not None:
                 after_chunk(cs, ce)
+        if self.gather is not None:
+            self.gather.wait()
         return index
 
     def _timer(self, phase):
@@ -400,6 +416,152 @@ def decode_measure(device, pk):
     }
 
 
+# ------------------------------------------------------------------------- head-sharded configuration
+def head_sharded_measure(device, rank, world, pk, steps=2, warmup=1, length=None):
+    """The head-sharded configuration as written: one layer of HEAD_SHARDED['length'] tokens with 8 KV heads,
+    this rank holding 8 / world of them (reference rule: num_kv_heads % tp == 0, no KV-head replication,
+    semblo/vllm_plugin/config.py:464-479), strong scaling.  Prefill steps with every chunk's output
+    all-gathered behind the next chunk's compute, then decode steps whose outputs are gathered too.
+    Times are device times, the maximum over the ranks.  Every KV head draws its k-means randomness
+    from a generator of its own, so a shard equals the same heads of the unsharded layer; that is
+    checked here on a small prompt (the gathered output against the whole layer computed locally)."""
+    import torch.distributed as dist
+    from semblo_b200 import _lib
+    from semblo_b200.arena import DecodeArena
+    from semblo_b200.fused_decode import fused_decode_step
+    from semblo_b200.head_parallel import HeadGather, kv_head_shard
+    from semblo_b200.state import flat_num_clusters
+    cfg = dict(HEAD_SHARDED)
+    if length:
+        cfg["length"] = length
+    set_env(cfg)
+    heads = kv_head_shard(cfg["hkv"], rank, world)
+    hkv_l = len(heads)
+    group = cfg["hq"] // cfg["hkv"]
+    hq_l, dim, L = hkv_l * group, cfg["dim"], cfg["length"]
+
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- shard check on a small prompt: sharded + gathered == unsharded, bit for bit
+    small = dict(cfg, length=16384, centres=64, target=1024)      # budget 1024: the second chunk is sparse
+    xs_all = mixture_inputs_device(small, 4100, device)
+    full = PrefillStep(small, device, 1, per_head_seed=True)
+    full.prepare()
+    want = torch.empty(small["length"], small["hq"], dim, dtype=torch.bfloat16, device=device)
+    full.run(xs_all, want)
+    xs = mixture_inputs_device(small, 4100, device, heads=heads)
+    part = PrefillStep(small, device, 1, hkv_local=hkv_l, head_offset=heads.start, per_head_seed=True)
+    part.prepare()
+    mine = torch.empty(small["length"], hq_l, dim, dtype=torch.bfloat16, device=device)
+    part.run(xs, mine)
+    gathered = torch.empty(world, small["length"], hq_l, dim, dtype=torch.bfloat16, device=device)
+    hg = HeadGather()
+    hg.issue(mine, gathered)
+    hg.wait()
+    torch.cuda.synchronize()
+    same = bool(torch.equal(HeadGather.as_heads(gathered), want))
+    if world > 1:
+        t = torch.tensor([1 if same else 0], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        same = bool(t.item())
+    del xs_all, xs, full, part, want, mine, gathered
+    torch.cuda.empty_cache()
+
+    # ---- prefill, strong scaling
+    x = mixture_inputs_device(cfg, 5000, device, length=L + cfg["decode_steps"], heads=heads)
+    xp = {k: v[:L] for k, v in x.items()}
+    step = PrefillStep(cfg, device, world, hkv_local=hkv_l, head_offset=heads.start, per_head_seed=True)
+    step.prepare()
+    out = torch.empty(L, hq_l, dim, dtype=torch.bfloat16, device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        step.run(xp, out)
+    barrier()
+    _lib.status_for(device).raise_if_set()
+    step.attended.zero_()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        index = step.run(xp, out)
+    e1.record()
+    barrier()
+    _lib.status_for(device).raise_if_set()
+    prefill_ms = reduce_max(e0.elapsed_time(e1) / steps)
+    counts = [int(v) // steps for v in step.attended.tolist()]
+
+    # ---- decode: the request's index moves into the arena, then one token per step
+    clusters = flat_num_clusters(L, cfg["unit"], cfg["min_log2"])
+    arena = DecodeArena(capacity=L, num_kv_heads=hkv_l, head_dim=dim, num_clusters=clusters, page_align=16,
+                        device=device, reserve=cfg["reserve"], keep_kpre=True)
+    if index.kv_page_table is not None:
+        # the arena reads the cluster-ordered copy in logical order: pack once more without the page table
+        index.pack_prompt_kv(xp["k_post"], xp["v"])
+    arena.adopt(index)
+    del index, out
+    layer = SimpleNamespace(num_heads=hq_l, num_kv_heads=hkv_l, head_dim=dim)
+    o_local = torch.empty(1, hq_l * dim, dtype=torch.bfloat16, device=device)
+    o_full = torch.empty(world, 1, hq_l * dim, dtype=torch.bfloat16, device=device)
+    pos_t = torch.zeros(1, dtype=torch.int64, device=device)
+    bufs = {k: torch.empty(1, *x[k].shape[1:], dtype=torch.bfloat16, device=device) for k in x}
+    splits = max(1, 148 // hkv_l)
+    dsteps = cfg["decode_steps"]
+
+    def decode_step():
+        fused_decode_step(layer, arena, q_post=bufs["q_post"], q_pre=bufs["q_pre"], positions=pos_t,
+                          k_post=bufs["k_post"], v_states=bufs["v"], k_pre=bufs["k_pre"], output=o_local,
+                          temperature=cfg["temperature"], beta=cfg["beta"], target_tokens=cfg["target"],
+                          sm_scale=dim ** -0.5, num_splits=splits)
+        if world > 1:
+            dist.all_gather_into_tensor(o_full.flatten(0, 1), o_local)     # 8 KiB per rank, on the compute stream
+
+    def load(s_):
+        for k in bufs:
+            bufs[k].copy_(x[k][L + s_:L + s_ + 1])
+        pos_t.fill_(L + s_)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for s_ in range(3):
+        load(s_)
+        decode_step()
+    barrier()
+    _lib.status_for(device).raise_if_set()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(dsteps)]
+    for s_ in range(dsteps):
+        load(s_)
+        flush.zero_()
+        ev[s_][0].record()
+        decode_step()
+        ev[s_][1].record()
+    barrier()
+    _lib.status_for(device).raise_if_set()
+    us = sorted(a.elapsed_time(b) * 1e3 for a, b in ev)
+    decode_us = reduce_max(us[len(us) // 2])
+    per_pair = 4.0 * dim * group
+    return {
+        "workload": f"{L}-token layer, GQA {cfg['hq']}q/{cfg['hkv']}kv, head_dim {dim}, {clusters} clusters, budget "
+                    f"{cfg['target']} + sink {cfg['sink']} + local window {cfg['local']}, KV heads {cfg['hkv']} split "
+                    f"{hkv_l} per GPU, outputs all-gathered with NCCL; then {dsteps} decode steps",
+        "scaling": "strong", "n_gpus": world, "kv_heads_per_gpu": hkv_l,
+        "prefill_tok_per_s": L / (prefill_ms * 1e-3), "prefill_ms_per_step": prefill_ms, "prefill_steps": steps,
+        "attended_pairs_per_step_this_rank": counts[0] + counts[2],
+        "prefill_tflops_this_rank": per_pair * (counts[0] + counts[2]) / (prefill_ms * 1e-3) / 1e12,
+        "decode_us_per_step": decode_us, "decode_steps": dsteps, "decode_timing": "eager launches incl. the all-gather, "
+        "L2 flushed before every step, median, max over ranks",
+        "gather_bytes_per_chunk_per_rank": cfg["chunk"] * hq_l * dim * 2,
+        "shards_equal_unsharded_layer": same,
+    }
+
+
 # ------------------------------------------------------------------------- CPU baseline
 def cpu_reference_sample(cfg, threads=None):
     """The CPU restatement of the reference path on a bounded sample of the prefill workload,
@@ -507,6 +669,9 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-head-sharded", action="store_true")
+    ap.add_argument("--head-sharded-only", action="store_true",
+                    help="run only the head-sharded configuration (optionally with --length) and print its record")
     ap.add_argument("--length", type=int, default=0, help="override the prompt length (profiling on a small case)")
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the decode measurement and print its record (profiling the decode kernels)")
@@ -528,11 +693,20 @@ def main():
     if args.decode_only:
         print(json.dumps(decode_measure(device, pk)))
         return
+    if args.head_sharded_only:
+        rec = head_sharded_measure(device, rank, world, pk, length=args.length or None)
+        if rank == 0:
+            print(json.dumps(rec))
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     cfg = dict(PREFILL)
     if args.length:
         cfg["length"] = args.length
     set_env(cfg)
-    x = mixture_inputs_device(cfg, 2000 + rank, device)
+    x = mixture_inputs_device(cfg, 2000, device, heads=range(rank * cfg["hkv"], (rank + 1) * cfg["hkv"]))
     step = PrefillStep(cfg, device, world)
     step.prepare()
     out = torch.empty(cfg["length"], cfg["hq"], cfg["dim"], dtype=torch.bfloat16, device=device)
@@ -576,8 +750,9 @@ def main():
     calls = dict(_lib.CALLS)
     clusters = int(index.num_buckets)
     launches = kernel_launches(calls, clusters) // args.steps
-    attended = int(step.attended[0].item()) // args.steps
-    gathered_rows = int(step.attended[1].item()) // args.steps
+    counts = [int(v) // args.steps for v in step.attended.tolist()]
+    attended = counts[0] + counts[2]                       # dense prefix + windows, selected clusters
+    sparse_pairs, gathered_rows = counts[2], counts[3]
     evs = step.attn_events
     attn_ms = window_ms = gather_ms = dense_ms = 0.0
     for i, (phase, ev) in enumerate(evs):
@@ -674,12 +849,53 @@ def main():
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
     del host, dev_in, dev_sets, out_host
+    head_sharded = None
+    if not args.length and not args.no_head_sharded:
+        del x, out
+        x = out = None
+        torch.cuda.empty_cache()
+        try:
+            head_sharded = head_sharded_measure(device, rank, world, pk)
+        except Exception as exc:                      # keep the headline if the second workload fails
+            head_sharded = {"error": repr(exc)}
+        set_env(cfg)
     if rank != 0:
         import torch.distributed as dist
         dist.barrier()                                # rank 0 joins it after printing the line
         dist.destroy_process_group()
         return
     tokens = cfg["length"] * world
+    # attended pairs by launch kind: dense-prefix chunks count their full causal triangle, the window
+    # launches of the sparse chunks the rest of counter 0, the sparse launches their own counter
+    cap = 4 * cfg["target"]
+    dense_pairs = sum((cs + min(cfg["length"], cs + cfg["chunk"]) + 1) * (min(cfg["length"], cs + cfg["chunk"]) - cs) // 2
+                      for cs in range(0, cfg["length"], cfg["chunk"]) if cs <= cap) * cfg["hkv"]
+    window_pairs = counts[0] - dense_pairs
+    per_pair = 4.0 * cfg["dim"] * g
+    dims = f"<{cfg['dim']},{g}>"
+
+    def kern(name, pairs, ms):
+        tf = per_pair * pairs / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+        return {"kernel": name, "attended_pairs_per_step": pairs, "flops_per_step": per_pair * pairs,
+                "ms_per_step": ms, "achieved": tf, "frac": tf / pk["tensor"]}
+
+    sparse = kern("sparse_gather_prefill_kernel" + dims, sparse_pairs, gather_ms)
+    roofline = {
+        "bound": "tensor", "kernel": sparse["kernel"], "achieved": sparse["achieved"], "peak": pk["tensor"],
+        "unit": "TFLOP/s", "frac": sparse["frac"],
+        "traffic": DRAM_TRAFFIC_PER_LAUNCH.get((sparse["kernel"], cfg["length"])),
+        "peak_source": pk["source"] + " (sustained bf16 GEMM)",
+        "what": "selected-cluster pairs x 4 D G flop / summed CUDA-event time of the sparse launches",
+        "gathered_rows_per_step": gathered_rows,
+        "executed_flops_per_step": 4.0 * cfg["dim"] * 128 * gathered_rows,
+        "launches": {"dense_prefix": kern("window_prefill_kernel" + dims, dense_pairs, dense_ms),
+                     "window": kern("window_prefill_kernel" + dims, window_pairs, window_ms),
+                     "sparse": sparse},
+        "all_attention": {"attended_pairs_per_step": attended, "flops_per_step": flops, "ms_per_step": attn_ms,
+                          "achieved": flops / (attn_ms * 1e-3) / 1e12,
+                          "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"]},
+        "step": {"flops_per_step": flops, "ms_per_step": ms, "frac": flops / (ms * 1e-3) / 1e12 / pk["tensor"]},
+    }
     line = {
         "metric": "sparse_prefill_tok_per_s", "value": tokens / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "step_ms": step_ms,
@@ -688,13 +904,10 @@ def main():
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-        "roofline": {"bound": "tensor", "kernel": "window_prefill_kernel<256,4> + sparse_gather_prefill_kernel<256,4>", "achieved": flops / (attn_ms * 1e-3) / 1e12,
-                     "peak": pk["tensor"], "unit": "TFLOP/s", "frac": flops / (attn_ms * 1e-3) / 1e12 / pk["tensor"],
-                     "traffic": GATHER_DRAM_BYTES_PER_LAUNCH if not args.length else None, "peak_source": pk["source"] + " (sustained bf16 GEMM)",
-                     "kernel_ms_per_step": attn_ms, "dense_prefix_ms": dense_ms, "window_ms": window_ms,
-                     "gather_ms": gather_ms, "attended_keys_per_step": attended, "gathered_rows_per_step": gathered_rows,
-                     "flops_per_step": flops},
+        "roofline": roofline,
     }
+    if head_sharded is not None:
+        line["head_sharded"] = head_sharded
     if world == 1 and not args.no_decode and not args.length:
         del x, out, step, index
         torch.cuda.empty_cache()

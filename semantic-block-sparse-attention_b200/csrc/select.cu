@@ -452,6 +452,145 @@ select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ s
   }
 }
 
+// Block-per-row form for C = 256 * PER (4096, 8192, 16384 clusters): the 256 threads of a CTA hold
+// one (query, head) score row in registers (PER scores each, four consecutive clusters per 16-byte
+// load), the head's sizes sit in shared memory, and every bisection step is PER predicated adds per
+// thread and one block-wide sum with a single barrier.  A CTA walks ROWS_PER_CTA consecutive queries
+// of one head, so the sizes are staged once.  Same arithmetic as select_kernel: the sums are sums of
+// integers below 2^24 in fp32, exact in any order.
+constexpr int SELECT_CTA_ROWS = 8;
+
+template <int PER>
+__global__ void __launch_bounds__(256, 2)
+select_kernel_cta(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
+                  int num_kv_heads, float target_tokens, int iters, int force_sink, float key_beta,
+                  int32_t* __restrict__ qmask, int32_t* __restrict__ counts, int32_t* __restrict__ tokens,
+                  int32_t* __restrict__ top1) {
+  constexpr int C = PER * 256;
+  extern __shared__ float s_size[];                       // [C]
+  __shared__ float red_f[2][3][8];                        // alternating buffers: a fast warp's next write
+  __shared__ int red_i[2][8];                             // cannot overtake a slow warp's read
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y;
+  for (int c = tid; c < C; c += 256) s_size[c] = (float)sizes[(int64_t)h * C + c];
+  __syncthreads();
+  int flip = 0;
+  for (int r = 0; r < SELECT_CTA_ROWS; ++r) {
+    const int q = blockIdx.x * SELECT_CTA_ROWS + r;
+    if (q >= num_queries) break;                          // uniform over the CTA
+    const float4* row = reinterpret_cast<const float4*>(score + ((int64_t)q * num_kv_heads + h) * C);
+    float sc[PER];
+#pragma unroll
+    for (int j = 0; j < PER / 4; ++j) {
+      const float4 v = __ldcs(row + j * 256 + tid);       // clusters j * 1024 + 4 tid .. + 3, read once
+      sc[4 * j] = v.x; sc[4 * j + 1] = v.y; sc[4 * j + 2] = v.z; sc[4 * j + 3] = v.w;
+    }
+    float mx = -INFINITY, mn = 3.4e38f, tot = 0.f, kmx = -INFINITY;
+    int arg = 0;
+#pragma unroll
+    for (int j = 0; j < PER / 4; ++j) {
+      const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
+      const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float s = sc[4 * j + e], n = nn[e];
+        const float key = tile_key(s, n, key_beta);
+        if (key > kmx) { kmx = key; arg = j * 1024 + tid * 4 + e; }     // ascending ids: the first maximum stays
+        mx = fmaxf(mx, s);
+        mn = fminf(mn, n > 0.f ? s : 3.4e38f);
+        tot += n > 0.f ? n : 0.f;
+      }
+    }
+    // block statistics with one barrier
+    mx = warp_max(mx); mn = warp_min(mn); tot = warp_sumf(tot);
+    {
+      const float kbest = warp_max(kmx);
+      int cand = kmx == kbest ? arg : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+      if (lane == 0) { red_f[flip][0][warp] = mx; red_f[flip][1][warp] = mn; red_f[flip][2][warp] = tot;
+                       red_i[flip][warp] = cand; s_size[C + 8 * flip + warp] = kbest; }
+    }
+    __syncthreads();
+    {
+      float a = lane < 8 ? red_f[flip][0][lane] : -INFINITY, b = lane < 8 ? red_f[flip][1][lane] : 3.4e38f;
+      float c2 = lane < 8 ? red_f[flip][2][lane] : 0.f;
+      mx = warp_max(a); mn = warp_min(b); tot = warp_sumf(c2);
+      if (top1 && warp == 0) {
+        const float kb = lane < 8 ? s_size[C + 8 * flip + lane] : -INFINITY;
+        const float kbest = warp_max(kb);
+        int cand = (lane < 8 && kb == kbest) ? red_i[flip][lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+        if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
+      }
+    }
+    flip ^= 1;
+    float hi = mx + 1e-6f;
+    float lo = fminf(mn - 1e-6f, hi - 1e-5f);
+    const bool all_fit = tot < target_tokens;
+    for (int it = 0; it < iters; ++it) {
+      const float mid = (lo + hi) * 0.5f;
+      float above = 0.f;
+#pragma unroll
+      for (int j = 0; j < PER / 4; ++j) {
+        const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
+        above += sc[4 * j] >= mid ? n4.x : 0.f;
+        above += sc[4 * j + 1] >= mid ? n4.y : 0.f;
+        above += sc[4 * j + 2] >= mid ? n4.z : 0.f;
+        above += sc[4 * j + 3] >= mid ? n4.w : 0.f;
+      }
+      above = warp_sumf(above);
+      if (lane == 0) red_f[flip][0][warp] = above;
+      __syncthreads();
+      above = warp_sumf(lane < 8 ? red_f[flip][0][lane] : 0.f);
+      flip ^= 1;
+      const bool reach = above >= target_tokens;
+      lo = reach ? mid : lo;
+      hi = reach ? hi : mid;
+    }
+    const float theta = all_fit ? NEG_BIG : lo;
+    int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * (C / 32);
+    int n_sel = 0;
+    float n_tok = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER / 4; ++j) {
+      const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
+      const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+      unsigned nib = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const bool sel = nn[e] > 0.f && sc[4 * j + e] >= theta;
+        nib |= sel ? (1u << e) : 0u;
+        n_sel += sel;
+        n_tok += sel ? nn[e] : 0.f;
+      }
+      // a 32-bit word holds the nibbles of eight consecutive threads
+      unsigned word = nib << (4 * (lane & 7));
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 2);
+      word |= __shfl_xor_sync(0xffffffffu, word, 4);
+      if (j == 0 && tid == 0 && force_sink) word |= 1u;
+      if ((lane & 7) == 0) qm[j * 32 + (tid >> 3)] = (int32_t)word;
+    }
+    if (counts || tokens) {
+      n_sel = __reduce_add_sync(0xffffffffu, n_sel);
+      n_tok = warp_sumf(n_tok);
+      if (lane == 0) { red_i[flip][warp] = n_sel; red_f[flip][0][warp] = n_tok; }
+      __syncthreads();
+      if (warp == 0) {
+        const int ns = __reduce_add_sync(0xffffffffu, lane < 8 ? red_i[flip][lane] : 0);
+        const float nt = warp_sumf(lane < 8 ? red_f[flip][0][lane] : 0.f);
+        if (lane == 0) {
+          if (counts) counts[(int64_t)q * num_kv_heads + h] = ns;
+          if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)nt;
+        }
+      }
+      flip ^= 1;
+    }
+  }
+}
+
 template <int D, int G>
 int launch_score(const void* vectors, int num_queries, int num_q_heads, const void* codebooks,
                  int num_kv_heads, int num_clusters, const int32_t* sizes, float temperature,
@@ -527,6 +666,21 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   SEMBLO_SELECT_REG(32)
   SEMBLO_SELECT_REG(64)
 #undef SEMBLO_SELECT_REG
+#define SEMBLO_SELECT_CTA(PER)                                                                      \
+  if (num_clusters == PER * 256) {                                                                  \
+    const size_t smem_c = (size_t)(PER * 256 + 16) * 4;                                             \
+    SEMBLO_CUDA(cudaFuncSetAttribute(select_kernel_cta<PER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c)); \
+    dim3 grid_c((unsigned)ceil_div(num_queries, SELECT_CTA_ROWS), num_kv_heads);                    \
+    select_kernel_cta<PER><<<grid_c, 256, smem_c, st_sel>>>(score, select_sizes, num_queries, num_kv_heads, \
+                                                          (float)target_tokens, iters, force_sink,  \
+                                                          tile_key_beta, qmask, counts, tokens, top1); \
+    SEMBLO_LAUNCH_CHECK();                                                                          \
+    return 0;                                                                                       \
+  }
+  SEMBLO_SELECT_CTA(16)
+  SEMBLO_SELECT_CTA(32)
+  SEMBLO_SELECT_CTA(64)
+#undef SEMBLO_SELECT_CTA
   int warps = 8;
   while (warps > 1 && (size_t)(warps + 1) * num_clusters * 4 > 200 * 1024) warps >>= 1;
   const size_t smem = (size_t)(warps + 1) * num_clusters * 4;

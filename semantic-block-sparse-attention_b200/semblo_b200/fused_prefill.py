@@ -155,7 +155,10 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     ``query_state.vectors`` [1, Q, Hq, 1, D] routing vectors; ``index.original_kv`` must hold
     the position-ordered (k_post, v) of the prompt: the exact window is read from it.
     ``local_kv`` = (k, v, first_position) replaces it for this call (the streamed mode, which
-    keeps no prompt-order copy, hands over the rows of the window it has gathered)."""
+    keeps no prompt-order copy, hands over the rows of the window it has gathered).
+    ``attended`` (int64, optional) accumulates the attended (query, key) pairs of the dense / window
+    launch in [0]; with four or more elements the sparse launch counts its pairs in [2] and the rows
+    it gathered in [3], otherwise in [0] and [1]."""
     import semblo_b200
     semblo_b200.SPARSE_ATTENTION_CALLS += 1
     cap = int(os.environ.get("SEMBLO_FA3_DENSE_PREFIX_X", str(dense_prefix_x))) * target_tokens
@@ -244,7 +247,8 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         _timer("mid")
     sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
                             indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
-                            page_table=getattr(index, "kv_page_table", None), q_order=order, attended=attended,
+                            page_table=getattr(index, "kv_page_table", None), q_order=order,
+                            attended=attended[2:] if attended is not None and attended.numel() >= 4 else attended,
                             partial=partial, cta_order=cta_order)
     if _timer:
         _timer("stop")

@@ -32,28 +32,71 @@ def q_head_shard(num_q_heads: int, num_kv_heads: int, rank: int, world: int) -> 
 
 
 class HeadGather:
-    """Gathers per-rank outputs [T, Hq / world, D] into [T, Hq, D] with one all-gather.
+    """The all-gather of per-rank outputs [T, Hq / world, D].
 
-    The receive buffer is kept between calls (fixed address: the call can sit inside a captured
-    graph when the backend supports it)."""
+    The gathered tensor is kept rank-major, ``[world, T, Hq / world, D]`` (what one NCCL
+    all-gather writes): head ``r * Hq / world + j`` of token ``t`` is ``full[r, t, j]``, and
+    :meth:`as_heads` gives the ``[T, Hq, D]`` view of it without moving a byte.  A consumer that
+    wants the heads of a token contiguous (an output projection reading ``[T, Hq * D]``) copies
+    once, or better reads the view.
+
+    ``issue`` runs the collective on a communication stream behind an event recorded on the
+    caller's stream, so the next chunk computes while this one travels; ``wait`` makes the
+    caller's stream wait for everything issued.  On CPU tensors (gloo) both are synchronous."""
 
     def __init__(self, group=None) -> None:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self._stage = None
+        self._comm = None
+        self._pending = False
+
+    @staticmethod
+    def as_heads(full: torch.Tensor) -> torch.Tensor:
+        """[world, T, Hl, D] -> the [T, world * Hl, D] view (strided, no copy)."""
+        w, t, hl, d = full.shape
+        return full.permute(1, 0, 2, 3).reshape(t, w * hl, d) if w == 1 else full.permute(1, 0, 2, 3).flatten(1, 2)
+
+    def issue(self, local: torch.Tensor, full: torch.Tensor) -> None:
+        """Gather ``local`` [T, Hl, D] (contiguous) from every rank into ``full`` [world, T, Hl, D].
+        ``local`` and ``full`` must stay untouched until :meth:`wait`."""
+        if tuple(full.shape) != (self.world,) + tuple(local.shape) or not full.is_contiguous() \
+                or not local.is_contiguous():
+            raise ValueError("full must be a contiguous [world, T, Hl, D] and local a contiguous [T, Hl, D]")
+        if self.world == 1:
+            full[0].copy_(local)
+            return
+        if not local.is_cuda:
+            dist.all_gather_into_tensor(full.flatten(0, 1), local, group=self.group)
+            return
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=local.device)
+        ready = torch.cuda.Event()
+        ready.record()
+        self._comm.wait_event(ready)
+        with torch.cuda.stream(self._comm):
+            dist.all_gather_into_tensor(full.flatten(0, 1), local, group=self.group)
+        self._pending = True
+
+    def wait(self) -> None:
+        if self._pending:
+            torch.cuda.current_stream().wait_stream(self._comm)
+            self._pending = False
 
     def __call__(self, local: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Synchronous form: returns (or fills) the [T, Hq, D] tensor."""
         if self.world == 1:
             if out is None:
                 return local
             out.copy_(local)
             return out
         t, hl, d = local.shape
-        if self._stage is None or self._stage.shape != (self.world * t, hl, d) or self._stage.dtype != local.dtype \
+        if self._stage is None or self._stage.shape != (self.world, t, hl, d) or self._stage.dtype != local.dtype \
                 or self._stage.device != local.device:
-            self._stage = torch.empty(self.world * t, hl, d, dtype=local.dtype, device=local.device)
-        dist.all_gather_into_tensor(self._stage, local.contiguous(), group=self.group)   # rank-major rows
-        full = self._stage.view(self.world, t, hl, d).permute(1, 0, 2, 3).reshape(t, self.world * hl, d)
+            self._stage = torch.empty(self.world, t, hl, d, dtype=local.dtype, device=local.device)
+        self.issue(local.contiguous(), self._stage)
+        self.wait()
+        full = self.as_heads(self._stage)
         if out is None:
             return full.contiguous()
         out.copy_(full)
