@@ -279,7 +279,34 @@ int semblo_decode_step(const void* q_post, const void* q_pre, const void* k_post
                        int head_dim, int num_clusters, float temperature, float beta,
                        int target_tokens, int sink_tokens, int iters, float sm_scale, int num_splits,
                        void* workspace, int64_t workspace_bytes, void* output, int32_t* status,
-                       int stage_mask, void* stream);
+                       int stage_mask, float* lse_out /* [Hq] natural-log LSE of the result, or NULL */,
+                       int flags /* bit 0: q_pre already holds the routing vectors */, void* stream);
+
+/* semblo/vllm_plugin/paged_attention.py:961-1128 (paged_posting_attention) for one query:
+ * attention over the positions listed by posting tiles (tile k of KV head h covers
+ * posting_positions[h, tile_starts[h, k] + (0 .. tile_lengths[h, k]))), each kept only if it is at or
+ * before the query's position, read from a vLLM-style paged cache [2, blocks, block_size, Hkv, D]
+ * through block_table [block_table_len].  Writes output [Hq, D] bf16 and, if lse_out is given, the
+ * natural-log log-sum-exp [Hq].  No logit soft cap.  The workspace (size from
+ * semblo_paged_attention_workspace_bytes) must be zeroed once before its first use. */
+int64_t semblo_paged_attention_workspace_bytes(int num_q_heads, int num_kv_heads, int head_dim,
+                                               int num_splits);
+int semblo_paged_posting_attention(const void* q, const void* q_position, int pos_is_int64,
+                                   const void* kv_cache, int64_t cache_blocks, int block_size,
+                                   const int32_t* block_table, int block_table_len,
+                                   const int32_t* posting_positions, int64_t posting_stride,
+                                   const int32_t* tile_starts, const int32_t* tile_lengths,
+                                   const int32_t* tile_counts, int tile_stride, int token_tile,
+                                   int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
+                                   int num_splits, void* workspace, int64_t workspace_bytes,
+                                   void* output, float* lse_out, int32_t* status, void* stream);
+
+/* semblo/vllm_plugin/paged_attention.py:50-78 (merge_paged_attention_results): exact merge of two
+ * attention states computed over disjoint key sets; out_* [rows, head_dim] bf16, lse_* [rows] fp32
+ * (natural log, -inf for an empty state). */
+int semblo_merge_attention_states(const void* out_a, const float* lse_a, const void* out_b,
+                                  const float* lse_b, int64_t rows, int head_dim, void* out,
+                                  float* lse, void* stream);
 
 #ifdef __cplusplus
 }

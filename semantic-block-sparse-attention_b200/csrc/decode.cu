@@ -77,6 +77,18 @@ struct DecodeArgs {
   int32_t* tickets;     // [Hkv]
   __nv_bfloat16* vectors;   // [Hq, D] routing vectors (kept for inspection)
   __nv_bfloat16* out;
+  float* lse_out;           // [Hq] natural-log log-sum-exp of the result, or null
+  int vectors_given;        // q_pre already holds the routing vectors (no router pass)
+  // paged_posting_attention: when tile_starts is set the attend kernel reads, instead of the selected
+  // rows and the suffix store, the positions listed by posting tiles through a block table
+  const int32_t *tile_starts, *tile_lengths, *tile_counts;   // [Hkv, T], [Hkv, T], [Hkv] of this query
+  int tile_stride, token_tile;
+  const int32_t* tile_posting;                               // [Hkv, Lp] positions
+  int64_t tile_posting_stride;
+  const __nv_bfloat16* cache;                                // [2, blocks, block_size, Hkv, D]
+  int64_t cache_plane;
+  const int32_t* block_table;
+  int block_size, block_table_len;
   int* status;
 };
 
@@ -189,6 +201,15 @@ decode_score_kernel(const DecodeArgs a) {
   // router: normalise in fp32, round to bf16, normalise again, round again
   for (int t = warp; t < G; t += 8) {
     const __nv_bfloat16* src = a.q_pre + (int64_t)(h * G + t) * D;
+    if (a.vectors_given) {                             // the caller ran the router: take the vectors as they are
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) {
+        const int d = lane + 32 * i;
+        qv[t * D + d] = __bfloat162float(src[d]);
+        if (blk == 0) a.vectors[(int64_t)(h * G + t) * D + d] = src[d];
+      }
+      continue;
+    }
     float v[D / 32];
     double ss = 0.0;
 #pragma unroll
@@ -672,7 +693,7 @@ decode_attend_kernel(const DecodeArgs a) {
 
   // everything that does not depend on the selection comes before the wait
   const long long q_pos = load_pos(a);
-  const int plen = *a.prompt_length;
+  const int plen = a.prompt_length ? *a.prompt_length : 0;
   // Q as the 16 x 16 row-major operand of every 16-dim step: rows = query heads (rows >= G are zero)
   uint32_t qa[KSTEPS][2];
 #pragma unroll
@@ -696,10 +717,14 @@ decode_attend_kernel(const DecodeArgs a) {
   const int32_t* posting = a.posting + (int64_t)h * a.packed_width;
   pdl_wait();                                          // the selection is complete
 
-  const int4 rec = __ldcg(reinterpret_cast<const int4*>(a.split_start) + (int64_t)h * nsplit + split);
+  const bool tile_mode = a.tile_starts != nullptr;
+  int4 rec = make_int4(0, 0, 0, 0);
+  if (!tile_mode) rec = __ldcg(reinterpret_cast<const int4*>(a.split_start) + (int64_t)h * nsplit + split);
   const int n_prompt = min(rec.z, (int)a.packed_width);
   const int n_entries = rec.w;
-  const int n_suffix = (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
+  // the slots after the selected rows: the live suffix positions, or every slot of the posting tiles
+  const int n_suffix = tile_mode ? __ldg(a.tile_counts + h) * a.token_tile
+                                 : (int)max(0LL, min(q_pos - plen + 1, (long long)a.suffix_blocks * a.suffix_block));
   const int total = n_prompt + n_suffix;
   const int per_split = max(1, (int)ceil_div(total, nsplit));
   const int lo = split * per_split, hi = min(total, lo + per_split);
@@ -758,6 +783,19 @@ decode_attend_kernel(const DecodeArgs a) {
         vp = kp + pk_plane;
         post = __ldg(posting + row);
         is_prompt = true;
+      } else if (tid < n && tile_mode) {
+        // slot -> (tile, offset) -> logical position -> block table -> cache row (paged_attention.py:445-815)
+        const int slot = base + tid, k = slot / a.token_tile, o = slot - k * a.token_tile;
+        if (o < __ldg(a.tile_lengths + (int64_t)h * a.tile_stride + k)) {
+          const long long pos = __ldg(a.tile_posting + (int64_t)h * a.tile_posting_stride +
+                                      __ldg(a.tile_starts + (int64_t)h * a.tile_stride + k) + o);
+          const long long block = pos / a.block_size;
+          if (pos >= 0 && pos <= q_pos && block < a.block_table_len) {
+            const long long phys = a.block_table[block];
+            kp = a.cache + (((phys * a.block_size + (pos - block * a.block_size)) * a.num_kv_heads) + h) * D;
+            vp = kp + a.cache_plane;
+          }
+        }
       } else if (tid < n) {
         const long long pos = (long long)plen + (base + tid - n_prompt);
         const long long block = pos / a.suffix_block;
@@ -964,6 +1002,7 @@ decode_attend_kernel(const DecodeArgs a) {
       packed.x = *reinterpret_cast<uint32_t*>(&o01);
       packed.y = *reinterpret_cast<uint32_t*>(&o23);
       *reinterpret_cast<uint2*>(a.out + (int64_t)(h * G + t) * D + d) = packed;
+      if (a.lse_out && d == 0) a.lse_out[h * G + t] = den > 0.f ? (s_mx[t] + log2f(den)) * LN2 : -INFINITY;
     }
   }
 }
@@ -1061,10 +1100,11 @@ extern "C" int semblo_decode_step(
     int num_q_heads, int num_kv_heads, int head_dim, int num_clusters,
     float temperature, float beta, int target_tokens, int sink_tokens, int iters, float sm_scale,
     int num_splits, void* workspace, int64_t workspace_bytes, void* output, int32_t* status,
-    int stage_mask, void* stream) {
+    int stage_mask, float* lse_out, int flags, void* stream) {
   SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
   const int g = num_q_heads / num_kv_heads;
   SEMBLO_REQUIRE(g <= MAX_G, "at most %d query heads per KV head", MAX_G);
+  SEMBLO_REQUIRE(prompt_length != nullptr, "the prompt length scalar is required");
   SEMBLO_REQUIRE(head_dim == 128 || head_dim == 256, "head_dim %d must be 128 or 256", head_dim);
   SEMBLO_REQUIRE(num_clusters >= 32 && num_clusters % 32 == 0 && num_clusters <= SEL_MAX_CLUSTERS,
                  "cluster count %d must be a multiple of 32 in [32, %d]", num_clusters, SEL_MAX_CLUSTERS);
@@ -1104,6 +1144,10 @@ extern "C" int semblo_decode_step(
   a.pacc = (float*)(ws + w.pacc); a.pml = (float*)(ws + w.pml);
   a.tickets = (int32_t*)(ws + w.tickets); a.vectors = (__nv_bfloat16*)(ws + w.vectors);
   a.out = (__nv_bfloat16*)output; a.status = status;
+  a.lse_out = lse_out; a.vectors_given = flags & 1;
+  a.tile_starts = a.tile_lengths = a.tile_counts = a.tile_posting = nullptr;
+  a.tile_stride = a.token_tile = 0; a.tile_posting_stride = 0;
+  a.cache = nullptr; a.cache_plane = 0; a.block_table = nullptr; a.block_size = 1; a.block_table_len = 0;
   cudaStream_t st = (cudaStream_t)stream;
   // bit 3 of the stage mask turns the overlapped (programmatic dependent) launches off; a stage
   // launched alone has no predecessor of this step to overlap with
@@ -1131,6 +1175,99 @@ extern "C" int semblo_decode_step(
     else return semblo::fail(semblo::SEMBLO_EINVAL, "decode attention supports head_dim 256 with 4, or 128 with 4 or 8, query heads per KV head (got %d, %d)", head_dim, g);
     if (rc) return rc;
   }
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------- paged posting attention
+namespace {
+
+// Exact merge of two attention states over disjoint key sets (paged_attention.py:50-78): one thread
+// per output element pair.
+__global__ void merge_states_kernel(const __nv_bfloat16* __restrict__ out_a, const float* __restrict__ lse_a,
+                                    const __nv_bfloat16* __restrict__ out_b, const float* __restrict__ lse_b,
+                                    int64_t rows, int dim, __nv_bfloat16* __restrict__ out, float* __restrict__ lse) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int half = dim / 2;
+  if (idx >= rows * half) return;
+  const int64_t r = idx / half;
+  const int c = (int)(idx % half) * 2;
+  const float la = lse_a[r], lb = lse_b[r];
+  const float m = fmaxf(la, lb);
+  float wa = 0.f, wb = 0.f, merged = -INFINITY;
+  if (m != -INFINITY) {
+    const float ea = expf(la - m), eb = expf(lb - m);
+    merged = m + logf(ea + eb);
+    wa = ea / (ea + eb);
+    wb = eb / (ea + eb);
+  }
+  const float2 a2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(out_a + r * dim + c));
+  const float2 b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(out_b + r * dim + c));
+  *reinterpret_cast<__nv_bfloat162*>(out + r * dim + c) = __floats2bfloat162_rn(a2.x * wa + b2.x * wb, a2.y * wa + b2.y * wb);
+  if (c == 0) lse[r] = merged;
+}
+
+}  // namespace
+
+extern "C" int semblo_merge_attention_states(const void* out_a, const float* lse_a, const void* out_b,
+                                             const float* lse_b, int64_t rows, int head_dim, void* out,
+                                             float* lse, void* stream) {
+  SEMBLO_REQUIRE(out_a && out_b && lse_a && lse_b && out && lse, "both states and the two outputs are required");
+  SEMBLO_REQUIRE(head_dim > 0 && head_dim % 2 == 0, "head_dim %d must be even", head_dim);
+  if (rows == 0) return 0;
+  const int64_t n = rows * (head_dim / 2);
+  merge_states_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)out_a, lse_a, (const __nv_bfloat16*)out_b, lse_b, rows, head_dim, (__nv_bfloat16*)out, lse);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int64_t semblo_paged_attention_workspace_bytes(int num_q_heads, int num_kv_heads, int head_dim, int num_splits) {
+  return ws_layout(num_q_heads, num_kv_heads, head_dim, 32, num_splits, 1).total;
+}
+
+extern "C" int semblo_paged_posting_attention(
+    const void* q, const void* q_position, int pos_is_int64, const void* kv_cache, int64_t cache_blocks,
+    int block_size, const int32_t* block_table, int block_table_len, const int32_t* posting_positions,
+    int64_t posting_stride, const int32_t* tile_starts, const int32_t* tile_lengths, const int32_t* tile_counts,
+    int tile_stride, int token_tile, int num_q_heads, int num_kv_heads, int head_dim, float sm_scale,
+    int num_splits, void* workspace, int64_t workspace_bytes, void* output, float* lse_out, int32_t* status,
+    void* stream) {
+  SEMBLO_REQUIRE(num_kv_heads > 0 && num_q_heads % num_kv_heads == 0, "query heads must be a multiple of the KV heads");
+  const int g = num_q_heads / num_kv_heads;
+  SEMBLO_REQUIRE(q && q_position && kv_cache && block_table && posting_positions && tile_starts && tile_lengths &&
+                     tile_counts && output && status,
+                 "query, position, cache, block table, posting tiles, output and status word are required");
+  SEMBLO_REQUIRE(block_size > 0 && token_tile > 0 && num_splits > 0 && tile_stride >= 0, "bad block, tile or split size");
+  SEMBLO_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv_cache)) & 15) == 0,
+                 "the query and the cache must be 16-byte aligned");
+  const WsLayout w = ws_layout(num_q_heads, num_kv_heads, head_dim, 32, num_splits, 1);
+  SEMBLO_REQUIRE(workspace_bytes >= w.total, "workspace has %lld bytes, %lld needed", (long long)workspace_bytes,
+                 (long long)w.total);
+  uint8_t* ws = (uint8_t*)workspace;
+  DecodeArgs a = {};
+  a.num_q_heads = num_q_heads; a.num_kv_heads = num_kv_heads; a.head_dim = head_dim; a.num_clusters = 32; a.group = g;
+  a.q_post = (const __nv_bfloat16*)q;
+  a.positions = q_position; a.pos_is_int64 = pos_is_int64;
+  a.packed_width = 0; a.suffix_blocks = 0; a.suffix_block = 1; a.table_len = 0; a.prompt_length = nullptr;
+  a.sm_scale_log2 = sm_scale * LOG2E; a.num_splits = num_splits;
+  a.split_start = (int32_t*)(ws + w.split); a.rstart = (int32_t*)(ws + w.rstart); a.rlen = (int32_t*)(ws + w.rlen);
+  a.pacc = (float*)(ws + w.pacc); a.pml = (float*)(ws + w.pml); a.tickets = (int32_t*)(ws + w.tickets);
+  a.out = (__nv_bfloat16*)output; a.lse_out = lse_out; a.status = status;
+  a.tile_starts = tile_starts; a.tile_lengths = tile_lengths; a.tile_counts = tile_counts;
+  a.tile_stride = tile_stride; a.token_tile = token_tile;
+  a.tile_posting = posting_positions; a.tile_posting_stride = posting_stride;
+  a.cache = (const __nv_bfloat16*)kv_cache;
+  a.cache_plane = cache_blocks * (int64_t)block_size * num_kv_heads * head_dim;
+  a.block_table = block_table; a.block_size = block_size; a.block_table_len = block_table_len;
+  const dim3 grid(num_kv_heads, num_splits);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  if (head_dim == 256 && g == 4) rc = launch_attend<256, 4>(a, grid, st, 0);
+  else if (head_dim == 128 && g == 4) rc = launch_attend<128, 4>(a, grid, st, 0);
+  else if (head_dim == 128 && g == 8) rc = launch_attend<128, 8>(a, grid, st, 0);
+  else return semblo::fail(semblo::SEMBLO_EINVAL, "paged posting attention supports head_dim 256 with 4, or 128 with 4 or 8, query heads per KV head (got %d, %d)", head_dim, g);
+  if (rc) return rc;
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

@@ -417,13 +417,19 @@ select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ s
   float lo = warp_min(mn) - 1e-6f;
   lo = fminf(lo, hi - 1e-5f);
   const bool all_fit = warp_sumf(tot) < target_tokens;
+  // The sums of sizes are sums of small integers: exact in any order and in either type, so they are
+  // kept as integers in four independent chains and folded with one warp reduction per step.
+  int ni[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) ni[i] = (int)nn[i];
+  const int target_i = (int)target_tokens;
   for (int it = 0; it < iters; ++it) {
     const float mid = (lo + hi) * 0.5f;
-    float above = 0.f;
+    int ab[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int i = 0; i < PER; ++i) above += sc[i] >= mid ? nn[i] : 0.f;
-    above = warp_sumf(above);
-    const bool reach = above >= target_tokens;
+    for (int i = 0; i < PER; ++i) ab[i & 3] += sc[i] >= mid ? ni[i] : 0;
+    const int above = __reduce_add_sync(0xffffffffu, (ab[0] + ab[1]) + (ab[2] + ab[3]));
+    const bool reach = above >= target_i;
     lo = reach ? mid : lo;
     hi = reach ? hi : mid;
   }
@@ -531,16 +537,16 @@ select_kernel_cta(const float* __restrict__ score, const int32_t* __restrict__ s
     const bool all_fit = tot < target_tokens;
     for (int it = 0; it < iters; ++it) {
       const float mid = (lo + hi) * 0.5f;
-      float above = 0.f;
+      float ab[4] = {0.f, 0.f, 0.f, 0.f};              // four independent chains (sums of small integers: exact)
 #pragma unroll
       for (int j = 0; j < PER / 4; ++j) {
         const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
-        above += sc[4 * j] >= mid ? n4.x : 0.f;
-        above += sc[4 * j + 1] >= mid ? n4.y : 0.f;
-        above += sc[4 * j + 2] >= mid ? n4.z : 0.f;
-        above += sc[4 * j + 3] >= mid ? n4.w : 0.f;
+        ab[0] += sc[4 * j] >= mid ? n4.x : 0.f;
+        ab[1] += sc[4 * j + 1] >= mid ? n4.y : 0.f;
+        ab[2] += sc[4 * j + 2] >= mid ? n4.z : 0.f;
+        ab[3] += sc[4 * j + 3] >= mid ? n4.w : 0.f;
       }
-      above = warp_sumf(above);
+      float above = warp_sumf((ab[0] + ab[1]) + (ab[2] + ab[3]));
       if (lane == 0) red_f[flip][0][warp] = above;
       __syncthreads();
       above = warp_sumf(lane < 8 ? red_f[flip][0][lane] : 0.f);

@@ -66,7 +66,10 @@ _SIGNATURES = {
     "semblo_window_prefill": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_decode_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int64, c_int]),
     "semblo_decode_workspace_offsets": (c_int, [c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
-    "semblo_decode_step": (c_int, [c_void_p] * 6 + [c_int] + [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int] * 3 + [c_void_p] + [c_int] * 4 + [c_float, c_float, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p]),
+    "semblo_decode_step": (c_int, [c_void_p] * 6 + [c_int] + [c_void_p] * 5 + [c_int64] + [c_void_p] * 3 + [c_int] * 3 + [c_void_p] + [c_int] * 4 + [c_float, c_float, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "semblo_paged_attention_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
+    "semblo_paged_posting_attention": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "semblo_merge_attention_states": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p]),
 }
 
 

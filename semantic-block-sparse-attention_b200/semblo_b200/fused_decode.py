@@ -60,13 +60,15 @@ def fused_decode_step(layer, arena, *, q_post: torch.Tensor, q_pre: torch.Tensor
                       k_post: torch.Tensor | None, v_states: torch.Tensor | None,
                       k_pre: torch.Tensor | None = None, output: torch.Tensor, temperature: float,
                       beta: float, target_tokens: int, sm_scale: float, num_splits: int, iters: int = 16,
-                      stage_mask: int = 7) -> None:
+                      stage_mask: int = 7, lse_out: torch.Tensor | None = None, vectors_given: bool = False) -> None:
     """The whole decode step of one layer over ``arena`` into ``output`` [1, Hq * D].
 
     ``layer`` needs ``num_heads``, ``num_kv_heads`` and ``head_dim``.  The sink rule follows
     SEMBLO_SINK_TOKENS as in the reference (fused_prefill._fitted_sink_tokens).  ``stage_mask``:
     1 score, 2 select, 4 attend (7 = the whole step); adding 8 launches the stages strictly one
-    after the other instead of overlapping each with the end of its predecessor."""
+    after the other instead of overlapping each with the end of its predecessor.  ``lse_out`` [Hq]
+    fp32 receives the natural-log log-sum-exp of the result; ``vectors_given`` says that ``q_pre``
+    already holds routing vectors (the step then skips its router)."""
     require_cuda(q_post, q_pre, output)
     hq, hkv, d = int(layer.num_heads), int(layer.num_kv_heads), int(layer.head_dim)
     sink = int(os.environ.get("SEMBLO_SINK_TOKENS", "0") or "0")
@@ -94,5 +96,5 @@ def fused_decode_step(layer, arena, *, q_post: torch.Tensor, q_pre: torch.Tensor
         int(arena.suffix_blocks), int(arena.suffix_block), int(arena.suffix_table.shape[1]),
         ptr(arena.prompt_length_t), hq, hkv, d, c, float(temperature), float(beta), int(target_tokens), sink,
         int(iters), float(sm_scale), splits, ptr(ws.buffer), ws.bytes, ptr(output), ptr(status.word),
-        int(stage_mask), stream_ptr()))
+        int(stage_mask), ptr(lse_out), 1 if vectors_given else 0, stream_ptr()))
     status.poll()          # non-blocking; a step learns of the previous step's device-side condition

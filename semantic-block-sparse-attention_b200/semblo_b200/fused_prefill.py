@@ -254,3 +254,50 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         _timer("stop")
     status.poll()
     return out
+
+
+def fused_decode_attention(q_chunk: torch.Tensor, query_state, index, q_positions: torch.Tensor, *,
+                           temperature: float, beta: float, target_tokens: int, sm_scale: float, iters: int = 16,
+                           num_splits: int = 16):
+    """Decode over the packed prompt of a request's own index (fused_prefill.py:625-718): select the single
+    query's clusters over the full sizes with the sink rule, attend their rows, and return the output with
+    its log-sum-exp; the caller merges the generated suffix (paged_attention.paged_posting_attention,
+    merge_paged_attention_results).  Served by the kernels of the fused decode step run over the index's
+    own buffers, with the routing vectors taken from ``query_state`` as they are."""
+    from .fused_decode import FusedDecodeWorkspace
+    from .paged_attention import PagedSparseAttentionResult
+    require_cuda(q_chunk, index.codebooks, index.packed_kv)
+    if q_chunk.ndim != 3 or q_chunk.shape[0] != 1:
+        raise ValueError("the decode body takes one query: q_chunk [1, Hq, D]")
+    _, hq, d = q_chunk.shape
+    hkv, c = int(index.num_kv_heads), int(index.num_buckets)
+    vectors = query_state.vectors[0].reshape(1, hq, -1).contiguous()
+    if vectors.shape[-1] != d or vectors.dtype != torch.bfloat16:
+        raise RuntimeError("the decode body routes with one whole bf16 vector per head (index_dim == head_dim)")
+    width = int(index.packed_kv.shape[1])
+    posting = index.posting_positions
+    if int(posting.shape[1]) != width or not posting.is_contiguous():
+        # the kernel reads posting and packed rows with one stride
+        padded = torch.zeros(hkv, width, dtype=torch.int32, device=posting.device)
+        padded[:, :posting.shape[1]] = posting
+        posting = padded
+    splits = max(1, int(num_splits))
+    ws = getattr(index, "_decode_ws", None)
+    key = (hq, hkv, d, c, width, splits)
+    if ws is None or ws.shape_key != key:
+        ws = FusedDecodeWorkspace(num_q_heads=hq, num_kv_heads=hkv, head_dim=d, num_clusters=c, packed_width=width,
+                                  num_splits=splits, device=q_chunk.device)
+        index._decode_ws = ws
+        index._no_suffix = torch.full((1,), 2 ** 30, dtype=torch.int32, device=q_chunk.device)
+    out = torch.empty(1, hq, d, dtype=torch.bfloat16, device=q_chunk.device)
+    lse = torch.empty(1, hq, dtype=torch.float32, device=q_chunk.device)
+    sink = _fitted_sink_tokens()
+    status = _lib.status_for(q_chunk.device)
+    positions = q_positions if q_positions.dtype in (torch.int32, torch.int64) else q_positions.to(torch.int32)
+    check(lib().semblo_decode_step(
+        ptr(q_chunk.contiguous()), ptr(vectors), None, None, None, ptr(positions),
+        1 if positions.dtype == torch.int64 else 0, ptr(index.codebooks), ptr(index.bucket_sizes),
+        ptr(index.bucket_indptr), ptr(posting), ptr(index.packed_kv), width, None, None, None, 0, 1, 0,
+        ptr(index._no_suffix), hq, hkv, d, c, float(temperature), float(beta), int(target_tokens), sink, int(iters),
+        float(sm_scale), splits, ptr(ws.buffer), ws.bytes, ptr(out), ptr(status.word), 7, ptr(lse), 1, stream_ptr()))
+    return PagedSparseAttentionResult(output=out, logsumexp=lse)

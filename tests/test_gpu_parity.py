@@ -539,3 +539,99 @@ def test_threshold_selection_on_given_scores_is_exact(dev, clusters):
     assert torch.equal(counts.cpu(), want.sum(-1).int())
     assert torch.equal(tokens.cpu(), (want * sizes[None]).sum(-1).int())
     assert torch.equal(top1.cpu().long().t(), score.argmax(-1))
+
+
+# ---------------------------------------------------------------------- decode without an arena
+def test_decode_over_the_index_paged_suffix_and_merge(dev):
+    """The decode path of a request that has no arena (fused_prefill.py:625-718, paged_attention.py:50-78,
+    961-1128): sparse attention over the packed prompt with its log-sum-exp, attention over the generated
+    suffix read from a paged cache through a block table, and their exact merge - each against the oracle,
+    and the merged result against the oracle's whole decode step."""
+    from types import SimpleNamespace
+    from semblo_b200.fused_prefill import fused_decode_attention
+    from semblo_b200.paged_attention import (PagedSparseAttentionResult, PostingTiles, merge_paged_attention_results,
+                                             paged_posting_attention)
+    from semblo_b200.trivial_router import trivial_router_vectors
+    dim, hq, hkv, sink, length, target, gen = 128, 8, 2, 64, 6000, 512, 37
+    data, index = _small_problem(length + gen + 1, hq, hkv, dim, 24, 3, 32, 7, sink)
+    prompt = {k: v[:length] for k, v in data.items()}
+    index = O.build_flat(O.routing_normalize(prompt["k_pre"]), unit_tokens=32, min_clusters_log2=7,
+                         kmeans_sample_size=1024, fit_iters=4, seed=0, sink=sink, page_align=16)
+    O.pack_prompt_kv(index, prompt["k_post"], prompt["v"])
+    gi = _gpu_index(index, dev)
+    clusters = index.bucket_sizes.shape[1]
+    pos = length + gen                                   # the query's position: `gen` generated tokens before it
+    q_post, q_pre = data["q_post"][pos], data["q_pre"][pos]
+    sm_scale = dim ** -0.5
+    os.environ["SEMBLO_SINK_TOKENS"] = str(sink)
+    try:
+        qv = trivial_router_vectors(q_pre[None].to(dev))
+        state = SimpleNamespace(vectors=qv.view(1, 1, hq, 1, dim))
+        res = fused_decode_attention(q_post[None].to(dev), state, gi, torch.tensor([pos], dtype=torch.int32, device=dev),
+                                     temperature=0.1, beta=0.25, target_tokens=target, sm_scale=sm_scale, num_splits=6)
+        _status_ok(dev)
+    finally:
+        os.environ.pop("SEMBLO_SINK_TOKENS", None)
+    # the oracle on the kernel's own selection: an arena without suffix is the index itself
+    ref = O.make_arena(capacity=8192, num_clusters=clusters, num_kv_heads=hkv, head_dim=dim, page_align=16, reserve=256,
+                       kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16)
+    O.arena_adopt(ref, index)
+    ws = gi._decode_ws
+    sel = torch.zeros(hkv, clusters, dtype=torch.bool)
+    for h in range(hkv):
+        n = int(ws.rcount[h])
+        ids = torch.searchsorted(ref.indptr[h].contiguous(), ws.rstart[h, :n].cpu(), right=True) - 1
+        sel[h, ids] = True
+    sel_ref, _, margin = O.decode_select(O.trivial_router_vectors(q_pre), ref, temperature=0.1, beta=0.25,
+                                         target_tokens=target, sink=sink, return_margin=True)
+    assert bool((margin[(sel != sel_ref).any(-1)] < 1e-4).all())
+    group = hq // hkv
+    want_p = torch.empty(hq, dim, dtype=torch.float64)
+    lse_p = torch.empty(hq, dtype=torch.float64)
+    for h in range(hkv):
+        rows = torch.cat([torch.arange(int(ref.indptr[h, c]), int(ref.indptr[h, c]) + int(ref.sizes[h, c]))
+                          for c in torch.nonzero(sel[h]).flatten().tolist()])
+        o, l = O._masked_attention(q_post[None, h * group:(h + 1) * group], ref.packed_kv[0, rows, h],
+                                   ref.packed_kv[1, rows, h], torch.ones(1, rows.numel(), dtype=torch.bool), sm_scale)
+        want_p[h * group:(h + 1) * group], lse_p[h * group:(h + 1) * group] = o[0], l[0]
+    _close_attention(res.output[0], want_p, "decode over the index")
+    torch.testing.assert_close(res.logsumexp[0].cpu().double(), lse_p, atol=2e-3, rtol=0)
+    # the generated suffix in a paged cache with 16-token blocks behind a permuted block table
+    block, n_blocks = 16, (length + gen + 1 + 15) // 16 + 3
+    perm = torch.randperm(n_blocks, generator=torch.Generator().manual_seed(8))
+    cache = torch.zeros(2, n_blocks, block, hkv, dim, dtype=torch.bfloat16)
+    for p in range(length, pos + 1):
+        cache[0, perm[p // block], p % block] = data["k_post"][p]
+        cache[1, perm[p // block], p % block] = data["v"][p]
+    reserve = 64                                          # the tiles cover reserved ground past the query too
+    spos = torch.arange(length, length + reserve, dtype=torch.int32)
+    tile = 16
+    slots = reserve // tile
+    tiles = PostingTiles(starts=(torch.arange(slots, dtype=torch.int32) * tile).view(1, 1, -1).expand(1, hkv, -1).contiguous().to(dev),
+                         lengths=torch.full((1, hkv, slots), tile, dtype=torch.int32, device=dev),
+                         counts=torch.full((1, hkv), slots, dtype=torch.int32, device=dev),
+                         selected_tokens=torch.full((1, hkv), reserve, dtype=torch.int32, device=dev))
+    sres = paged_posting_attention(q_post[None].to(dev), cache.to(dev), spos[None].expand(hkv, -1).contiguous().to(dev),
+                                   tiles, torch.tensor([pos], dtype=torch.int32, device=dev),
+                                   torch.zeros(1, dtype=torch.int32, device=dev), perm.int()[None].to(dev),
+                                   block_size=block, sm_scale=sm_scale, softcap=None, token_tile=tile, num_splits=2,
+                                   return_logsumexp=True)
+    _status_ok(dev)
+    ks, vs = data["k_post"][length:pos + 1], data["v"][length:pos + 1]
+    want_s = torch.empty(hq, dim, dtype=torch.float64)
+    lse_s = torch.empty(hq, dtype=torch.float64)
+    for h in range(hkv):
+        o, l = O._masked_attention(q_post[None, h * group:(h + 1) * group], ks[:, h], vs[:, h],
+                                   torch.ones(1, ks.shape[0], dtype=torch.bool), sm_scale)
+        want_s[h * group:(h + 1) * group], lse_s[h * group:(h + 1) * group] = o[0], l[0]
+    _close_attention(sres.output[0], want_s, "suffix through the block table")
+    torch.testing.assert_close(sres.logsumexp[0].cpu().double(), lse_s, atol=2e-3, rtol=0)
+    merged = merge_paged_attention_results(res, sres)
+    want_m, lse_m = O.merge_states(want_p, lse_p, want_s, lse_s)
+    _close_attention(merged.output[0], want_m, "merged decode")
+    torch.testing.assert_close(merged.logsumexp[0].cpu().double(), lse_m, atol=2e-3, rtol=0)
+    # a state with nothing attended merges as the other one
+    empty = PagedSparseAttentionResult(output=torch.zeros_like(res.output),
+                                       logsumexp=torch.full_like(res.logsumexp, float("-inf")))
+    again = merge_paged_attention_results(empty, sres)
+    assert torch.equal(again.output, sres.output)
