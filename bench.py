@@ -662,8 +662,8 @@ def cpu_config1_full(threads=None):
 def cpu_reference_sample(cfg, threads=None):
     """The reference path on the host cores on a bounded sample of the prefill workload (about 10-20 s of
     CPU work), scaled to tokens per second of the whole 131072-token step: for one of the KV heads the
-    normalisation, all eight k-means iterations on the full sample, assignment, layout and packing; 256
-    queries of a dense chunk and 512 of a sparse chunk, spread over the chunk so the window lengths
+    normalisation, all eight k-means iterations on the full sample, assignment, layout and packing; 2048
+    queries of a dense chunk and 4096 of a sparse chunk, spread over the chunk so the window lengths
     average as in the whole chunk.  Returns (tok/s, text)."""
     from oracle import semblo_oracle as O
     if threads:
@@ -683,7 +683,7 @@ def cpu_reference_sample(cfg, threads=None):
     sm = dim ** -0.5
     chunk = cfg["chunk"]
     # a dense chunk: 256 queries spread over the second chunk
-    nq_d = 256
+    nq_d = 2048
     cs_d = chunk
     pick = torch.arange(0, chunk, chunk // nq_d) + cs_d
     t0 = time.perf_counter()
@@ -695,7 +695,7 @@ def cpu_reference_sample(cfg, threads=None):
     dense_pairs = sum(float((torch.arange(c, c + chunk) + 1).sum()) for c in dense_chunks)
     dense_s = hkv * t_dense * dense_pairs / dense_pairs_sample
     # a sparse chunk in the middle of the prompt: 512 queries spread over it
-    nq_s = 512
+    nq_s = 4096
     cs = 9 * chunk
     ws = cs - cfg["local"]
     picks = torch.arange(0, chunk, chunk // nq_s) + cs

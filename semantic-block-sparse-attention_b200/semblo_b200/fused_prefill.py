@@ -7,12 +7,24 @@ theta_select_bitmask_flat (fused_select.py:806-863).  No host synchronisation in
 the chunk loop."""
 from __future__ import annotations
 
+import contextlib
 import os
 
 import torch
 
 from . import _lib
 from ._lib import check, lib, ptr, require_cuda, stream_ptr
+
+
+# Profiler labels of the attention launches, with the reference's names and switch
+# (kv_outer.py:243-252, fused_prefill.py:183); off by default: a label costs a little per call.
+_ATTEND_PARTS = os.environ.get("SEMBLO_PROFILE_ATTEND_PARTS") == "1"
+
+
+def _attend_part(name: str):
+    if not _ATTEND_PARTS:
+        return contextlib.nullcontext()
+    return torch.profiler.record_function(name)
 
 
 def _fitted_sink_tokens() -> int:
@@ -184,8 +196,9 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         if _timer:
             _timer("start")
         k_w, v_w = window_rows(0)
-        res = window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=0, local_start=0,
-                               sm_scale=sm_scale, out=out, attended=attended)
+        with _attend_part("semblo::attend_dense_prefix"):
+            res = window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=0,
+                                   local_start=0, sm_scale=sm_scale, out=out, attended=attended)
         if _timer:
             _timer("stop")
         return res
@@ -241,15 +254,18 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
         _timer("start")
     # the exact window [wstart, q] in position order, then the selected clusters merged into it
     k_w, v_w = window_rows(wstart)
-    window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=wstart, local_start=wstart,
-                     sm_scale=sm_scale, out=out, lse=lse, attended=attended, partial=partial)
+    with _attend_part("semblo::attend_current_chunk"):
+        window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=wstart,
+                         local_start=wstart, sm_scale=sm_scale, out=out, lse=lse, attended=attended, partial=partial)
     if _timer:
         _timer("mid")
-    sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
-                            indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
-                            page_table=getattr(index, "kv_page_table", None), q_order=order,
-                            attended=attended[2:] if attended is not None and attended.numel() >= 4 else attended,
-                            partial=partial, cta_order=cta_order)
+    # the kernel gathers the selected rows itself: the reference's gather_kv label has no launch of its own here
+    with _attend_part("semblo::attend_selected_clusters"):
+        sparse_gather_attention(q_chunk, packed_kv=index.packed_kv, qmask=qmask, causal_sizes=base,
+                                indptr=index.bucket_indptr, sm_scale=sm_scale, out=out, lse=lse, merge=True,
+                                page_table=getattr(index, "kv_page_table", None), q_order=order,
+                                attended=attended[2:] if attended is not None and attended.numel() >= 4 else attended,
+                                partial=partial, cta_order=cta_order)
     if _timer:
         _timer("stop")
     status.poll()

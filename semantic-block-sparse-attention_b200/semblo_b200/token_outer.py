@@ -19,7 +19,7 @@ import torch
 from . import _lib
 from ._lib import check, lib, ptr, require_cuda, stream_ptr
 from .flat_index import routing_normalize
-from .fused_prefill import CausalSnapshot, fused_chunk_attention, window_attention
+from .fused_prefill import CausalSnapshot, _attend_part, fused_chunk_attention, window_attention
 from .state import ProductPostingIndex, flat_num_clusters
 from .trivial_router import trivial_router_vectors
 
@@ -177,6 +177,11 @@ class TokenOuterPrefillSession:
         require_cuda(q_post, q_pre, k_post, v_states, k_pre)
         if stop - start != q_post.shape[0] or stop - start > self.chunk:
             raise ValueError("a slice holds at most one chunk of consecutive positions")
+        # labelled with the operator's name, as the reference's slice is (token_outer_prefill.py:186)
+        with torch.profiler.record_function("semblo::attention"):
+            return self._slice(q_post, q_pre, k_post, v_states, k_pre, start, stop, out)
+
+    def _slice(self, q_post, q_pre, k_post, v_states, k_pre, start, stop, out):
         if self.index is None and start >= self.fit_at:
             self._fit_and_pack()
         if out is None:
@@ -192,7 +197,8 @@ class TokenOuterPrefillSession:
         if start <= self.cap:
             # read densely through the inverse permutation
             rows = self.index._inverse_positions[:, :stop]
-            local = gather_kv(self.index.packed_kv, rows) + (0,)
+            with _attend_part("semblo::gather_kv"):
+                local = gather_kv(self.index.packed_kv, rows) + (0,)
         else:
             local = (k_post, v_states, start)
         return fused_chunk_attention(q_post, state, self.index, self.positions32[start:stop], self.snapshot, start,
