@@ -683,7 +683,7 @@ def cpu_reference_sample(cfg, threads=None):
     sm = dim ** -0.5
     chunk = cfg["chunk"]
     # a dense chunk: 256 queries spread over the second chunk
-    nq_d = 2048
+    nq_d = 8192
     cs_d = chunk
     pick = torch.arange(0, chunk, chunk // nq_d) + cs_d
     t0 = time.perf_counter()
@@ -695,7 +695,7 @@ def cpu_reference_sample(cfg, threads=None):
     dense_pairs = sum(float((torch.arange(c, c + chunk) + 1).sum()) for c in dense_chunks)
     dense_s = hkv * t_dense * dense_pairs / dense_pairs_sample
     # a sparse chunk in the middle of the prompt: 512 queries spread over it
-    nq_s = 4096
+    nq_s = 16384
     cs = 9 * chunk
     ws = cs - cfg["local"]
     picks = torch.arange(0, chunk, chunk // nq_s) + cs

@@ -236,8 +236,9 @@ int semblo_sparse_prefill_gather(const void* q, int num_queries, int num_q_heads
 
 /* Launch order for semblo_sparse_prefill_gather: the rows each (tile, head) will gather (the
  * union of the tile's selections; tiles of 128 / G queries in q_order) go to work
- * [tiles * Hkv], and order_out [tiles * Hkv] lists tile * Hkv + head by descending work, so
- * that the longest CTAs start first and the launch ends evenly.  No reference counterpart (the
+ * [tiles * Hkv], and order_out [tiles * Hkv] lists tile * Hkv + head one KV head after the
+ * other, each head's pairs by descending work: CTAs that run together gather from one head's
+ * rows (a working set the L2 holds) and the longest start first.  No reference counterpart (the
  * reference's kernels are scheduled by Triton's grid order). */
 int semblo_gather_launch_order(const int32_t* q_order, const int32_t* qmask,
                                const int32_t* causal_sizes, int num_queries, int num_q_heads,

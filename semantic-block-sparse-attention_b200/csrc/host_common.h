@@ -54,6 +54,9 @@ inline int fail(int code, const char* fmt, ...) {
 int make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                          const uint64_t* strides_bytes, const uint32_t* box);
 
+// Multiprocessors of the current device (148 if the query fails): persistent grids are sized by it.
+int sm_count();
+
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 }  // namespace semblo

@@ -619,26 +619,29 @@ __global__ void tile_work_kernel(const int32_t* __restrict__ q_order, const int3
   if (lane == 0) work[item] = total;
 }
 
-// order[] = the items by descending work, in 256 classes of equal width (one block).
-__global__ void tile_order_kernel(const int32_t* __restrict__ work, int n, int32_t* __restrict__ order) {
+// order[] = the items (tile * heads + head) head by head, each head's by descending work in
+// `classes` classes of equal width (one block; heads * classes <= 1024).  CTAs that run at the same
+// time then gather from one head's rows, a working set the L2 can hold.  heads = 1: one global order.
+__global__ void tile_order_kernel(const int32_t* __restrict__ work, int n, int heads, int classes,
+                                  int32_t* __restrict__ order) {
   __shared__ int s_max;
-  __shared__ int s_hist[256];
+  __shared__ int s_hist[1024];
   if (threadIdx.x == 0) s_max = 0;
-  if (threadIdx.x < 256) s_hist[threadIdx.x] = 0;
+  s_hist[threadIdx.x] = 0;
   __syncthreads();
   int m = 0;
   for (int i = threadIdx.x; i < n; i += blockDim.x) m = max(m, work[i]);
   atomicMax(&s_max, m);
   __syncthreads();
   const long long top = (long long)s_max + 1;
+  const int bins = heads * classes;
   for (int i = threadIdx.x; i < n; i += blockDim.x)
-    atomicAdd(&s_hist[255 - (int)((long long)work[i] * 256 / top)], 1);
+    atomicAdd(&s_hist[(i % heads) * classes + classes - 1 - (int)((long long)work[i] * classes / top)], 1);
   __syncthreads();
-  if (threadIdx.x < 32) {                 // exclusive scan of the 256 classes: eight per lane
+  if (threadIdx.x < 32) {                 // exclusive scan of up to 1024 bins: 32 per lane
     const int lane = threadIdx.x;
-    int c[8], sum = 0;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { c[k] = s_hist[lane * 8 + k]; sum += c[k]; }
+    int sum = 0;
+    for (int k = 0; k < 32; ++k) sum += lane * 32 + k < bins ? s_hist[lane * 32 + k] : 0;
     int incl = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -646,12 +649,13 @@ __global__ void tile_order_kernel(const int32_t* __restrict__ work, int n, int32
       if (lane >= o) incl += up;
     }
     int run = incl - sum;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { s_hist[lane * 8 + k] = run; run += c[k]; }
+    for (int k = 0; k < 32; ++k) {
+      if (lane * 32 + k < bins) { const int c = s_hist[lane * 32 + k]; s_hist[lane * 32 + k] = run; run += c; }
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x)
-    order[atomicAdd(&s_hist[255 - (int)((long long)work[i] * 256 / top)], 1)] = i;
+    order[atomicAdd(&s_hist[(i % heads) * classes + classes - 1 - (int)((long long)work[i] * classes / top)], 1)] = i;
 }
 
 template <int D, int G>
@@ -733,7 +737,9 @@ extern "C" int semblo_gather_launch_order(const int32_t* q_order, const int32_t*
   cudaStream_t st = (cudaStream_t)stream;
   tile_work_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, st>>>(q_order, qmask, causal_sizes, num_queries, num_kv_heads,
                                                              num_clusters, qt, tiles, work);
-  tile_order_kernel<<<1, 1024, 0, st>>>(work, n, order_out);
+  SEMBLO_REQUIRE(num_kv_heads <= 128, "at most 128 KV heads");
+  const int classes = std::min(64, 1024 / num_kv_heads);
+  tile_order_kernel<<<1, 1024, 0, st>>>(work, n, num_kv_heads, classes, order_out);
   SEMBLO_LAUNCH_CHECK();
   return 0;
 }

@@ -18,10 +18,12 @@
 #include "../../include/semblo_b200.h"
 #include "host_common.h"
 #include "attn_common.cuh"
+#include <cstdlib>
 #include "sm100.cuh"
 
 using namespace sm100;
 using semblo::ceil_div;
+using semblo::sm_count;
 
 namespace {
 
@@ -376,85 +378,122 @@ __global__ void select_kernel(const float* __restrict__ score,      // [Q, Hkv, 
   }
 }
 
-// Register-resident form for C = 32 * PER <= 2048: the warp keeps the whole score row and the
-// sizes in registers, so each bisection step is a compare and a predicated add per cluster.
+// acc += n where s >= mid: one compare (integer pipe) and one predicated fp32 add (FMA pipe).
+__device__ __forceinline__ void add_if_ge(float& acc, float s, float mid, float n) {
+  asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %1, %2;\n\t@p add.f32 %0, %0, %3;\n\t}" : "+f"(acc) : "f"(s), "f"(mid), "f"(n));
+}
+
+constexpr int SELECT_REG_WARPS = 4;
+
+// Register-resident form for C = 32 * PER <= 2048: a warp keeps a whole score row and the sizes in
+// registers, so a bisection step is a compare and a predicated add per cluster.  The kernel is bound
+// by the integer pipe (compares, selects, votes), so everything that is the same for all rows of a
+// head is tabulated once per block in shared memory — the size term of the tile-order key, the sizes
+// as fp32 and a 0 / -inf mask of the empty clusters that is added to the scores once — and a block
+// walks over many rows.
 template <int PER>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(SELECT_REG_WARPS * 32, PER >= 64 ? 3 : 4)
 select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
                   int num_kv_heads, float target_tokens, int iters, int force_sink, float key_beta,
                   int32_t* __restrict__ qmask, int32_t* __restrict__ counts,
                   int32_t* __restrict__ tokens, int32_t* __restrict__ top1) {
   constexpr int C = PER * 32;
+  __shared__ float s_pen[C], s_ninf[C], s_size[C];
+  __shared__ unsigned s_bits[SELECT_REG_WARPS][PER];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
-  const int q = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (q >= num_queries) return;
-  const float* row = score + ((int64_t)q * num_kv_heads + h) * C;
   const int32_t* sz = sizes + (int64_t)h * C;
-  float sc[PER], nn[PER];
-  float mx = -INFINITY, mn = 3.4e38f, tot = 0.f, kmx = -INFINITY;
-  int arg = 0;
-#pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int c = i * 32 + lane;
-    sc[i] = row[c];
-    nn[i] = (float)sz[c];
-    const float key = tile_key(sc[i], nn[i], key_beta);
-    if (key > kmx) { kmx = key; arg = c; }
-    mx = fmaxf(mx, sc[i]);
-    mn = fminf(mn, nn[i] > 0.f ? sc[i] : 3.4e38f);
-    tot += nn[i] > 0.f ? nn[i] : 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float n = (float)sz[c];
+    s_size[c] = n;
+    s_ninf[c] = n > 0.f ? 0.f : -INFINITY;
+    s_pen[c] = key_beta != 0.f && n > 0.f ? key_beta * __logf(1.0f + n) : 0.f;
   }
-  const float best = warp_max(mx);
-  if (top1) {
-    const float kbest = warp_max(kmx);
-    int cand = kmx == kbest ? arg : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
-    if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
-  }
-  float hi = best + 1e-6f;
-  float lo = warp_min(mn) - 1e-6f;
-  lo = fminf(lo, hi - 1e-5f);
-  const bool all_fit = warp_sumf(tot) < target_tokens;
-  // The sums of sizes are sums of small integers: exact in any order and in either type, so they are
-  // kept as integers in four independent chains and folded with one warp reduction per step.
-  int ni[PER];
-#pragma unroll
-  for (int i = 0; i < PER; ++i) ni[i] = (int)nn[i];
+  __syncthreads();
   const int target_i = (int)target_tokens;
-  for (int it = 0; it < iters; ++it) {
-    const float mid = (lo + hi) * 0.5f;
-    int ab[4] = {0, 0, 0, 0};
+  for (int q = blockIdx.x * SELECT_REG_WARPS + warp; q < num_queries; q += gridDim.x * SELECT_REG_WARPS) {
+    const float* row = score + ((int64_t)q * num_kv_heads + h) * C;
+    float sc[PER], nn[PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) ab[i & 3] += sc[i] >= mid ? ni[i] : 0;
-    const int above = __reduce_add_sync(0xffffffffu, (ab[0] + ab[1]) + (ab[2] + ab[3]));
-    const bool reach = above >= target_i;
-    lo = reach ? mid : lo;
-    hi = reach ? hi : mid;
-  }
-  const float theta = all_fit ? NEG_BIG : lo;
-  int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * PER;
-  int n_sel = 0;
-  float n_tok = 0.f;
-  unsigned mine = 0;
+    for (int i = 0; i < PER; ++i) sc[i] = __ldcs(row + i * 32 + lane);       // read once
+    float mx = -INFINITY, mn = INFINITY, tot = 0.f, kmx = -INFINITY;
+    int arg = 0;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const bool sel = nn[i] > 0.f && sc[i] >= theta;
-    unsigned bits = __ballot_sync(0xffffffffu, sel);
-    n_sel += __popc(bits);
-    n_tok += sel ? nn[i] : 0.f;
-    if (i == 0 && force_sink) bits |= 1u;
-    if ((i & 31) == lane) mine = bits;
-    if ((i & 31) == 31 || i == PER - 1) {
-      const int w = (i & ~31) + lane;
-      if (w <= i) qm[w] = (int32_t)mine;
+    for (int i = 0; i < PER; ++i) {
+      const int c = i * 32 + lane;
+      const float s = sc[i], ninf = s_ninf[c];
+      nn[i] = s_size[c];
+      const float key = s + s_pen[c];
+      if (key > kmx) { kmx = key; arg = i; }        // ascending ids: the first maximum stays
+      mx = fmaxf(mx, s);
+      mn = fminf(mn, s - ninf);                     // +inf for an empty cluster
+      tot += nn[i];
+      sc[i] = s + ninf;                             // -inf for an empty cluster: never above a threshold
     }
-  }
-  n_tok = warp_sumf(n_tok);
-  if (lane == 0) {
-    if (counts) counts[(int64_t)q * num_kv_heads + h] = n_sel;
-    if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)n_tok;
+    const float best = warp_max(mx);
+    if (top1) {
+      const float kbest = warp_max(kmx);
+      int cand = kmx == kbest ? arg * 32 + lane : 0x7fffffff;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+      if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
+    }
+    float hi = best + 1e-6f;
+    float lo = warp_min(mn) - 1e-6f;
+    lo = fminf(lo, hi - 1e-5f);
+    const float row_total = warp_sumf(tot);
+    const bool all_fit = row_total < target_tokens;
+    // The sums of sizes are sums of small integers: exact in any order, and exact in fp32 while the
+    // row's total stays below 2^24; longer rows take the same loop on integers.
+    if (row_total < 16777216.f) {
+      for (int it = 0; it < iters; ++it) {
+        const float mid = (lo + hi) * 0.5f;
+        float ab[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < PER; ++i) add_if_ge(ab[i & 3], sc[i], mid, nn[i]);
+        const int above = __reduce_add_sync(0xffffffffu, (int)((ab[0] + ab[1]) + (ab[2] + ab[3])));
+        const bool reach = above >= target_i;
+        lo = reach ? mid : lo;
+        hi = reach ? hi : mid;
+      }
+    } else {
+      for (int it = 0; it < iters; ++it) {
+        const float mid = (lo + hi) * 0.5f;
+        int ab[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < PER; ++i) ab[i & 3] += sc[i] >= mid ? __ldg(sz + i * 32 + lane) : 0;
+        const int above = __reduce_add_sync(0xffffffffu, (ab[0] + ab[1]) + (ab[2] + ab[3]));
+        const bool reach = above >= target_i;
+        lo = reach ? mid : lo;
+        hi = reach ? hi : mid;
+      }
+    }
+    const float theta = all_fit ? NEG_BIG : lo;
+    float n_tok = 0.f;
+    __syncwarp();                                   // the previous row's words have been read
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const unsigned bits = __ballot_sync(0xffffffffu, sc[i] >= theta);
+      add_if_ge(n_tok, sc[i], theta, nn[i]);
+      if (lane == 0) s_bits[warp][i] = bits;
+    }
+    __syncwarp();
+    int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * PER;
+    int n_sel = 0;
+    for (int w = lane; w < PER; w += 32) {
+      unsigned bits = s_bits[warp][w];
+      n_sel += __popc(bits);
+      if (w == 0 && force_sink) bits |= 1u;
+      qm[w] = (int32_t)bits;
+    }
+    if (counts || tokens) {
+      n_sel = __reduce_add_sync(0xffffffffu, n_sel);
+      n_tok = warp_sumf(n_tok);
+      if (lane == 0) {
+        if (counts) counts[(int64_t)q * num_kv_heads + h] = n_sel;
+        if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)n_tok;
+      }
+    }
   }
 }
 
@@ -465,7 +504,6 @@ select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ s
 // of one head, so the sizes are staged once.  Same arithmetic as select_kernel: the sums are sums of
 // integers below 2^24 in fp32, exact in any order.
 constexpr int SELECT_CTA_ROWS = 8;
-
 template <int PER>
 __global__ void __launch_bounds__(256, 2)
 select_kernel_cta(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
@@ -541,10 +579,10 @@ select_kernel_cta(const float* __restrict__ score, const int32_t* __restrict__ s
 #pragma unroll
       for (int j = 0; j < PER / 4; ++j) {
         const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
-        ab[0] += sc[4 * j] >= mid ? n4.x : 0.f;
-        ab[1] += sc[4 * j + 1] >= mid ? n4.y : 0.f;
-        ab[2] += sc[4 * j + 2] >= mid ? n4.z : 0.f;
-        ab[3] += sc[4 * j + 3] >= mid ? n4.w : 0.f;
+        add_if_ge(ab[0], sc[4 * j], mid, n4.x);
+        add_if_ge(ab[1], sc[4 * j + 1], mid, n4.y);
+        add_if_ge(ab[2], sc[4 * j + 2], mid, n4.z);
+        add_if_ge(ab[3], sc[4 * j + 3], mid, n4.w);
       }
       float above = warp_sumf((ab[0] + ab[1]) + (ab[2] + ab[3]));
       if (lane == 0) red_f[flip][0][warp] = above;
@@ -659,10 +697,11 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   cudaStream_t st_sel = (cudaStream_t)stream;
 #define SEMBLO_SELECT_REG(PER)                                                                      \
   if (num_clusters == PER * 32) {                                                                   \
-    dim3 grid_r((unsigned)ceil_div(num_queries, 8), num_kv_heads);                                  \
-    select_kernel_reg<PER><<<grid_r, 256, 0, st_sel>>>(score, select_sizes, num_queries, num_kv_heads, \
-                                                      (float)target_tokens, iters, force_sink,      \
-                                                      tile_key_beta, qmask, counts, tokens, top1);  \
+    const int per_head = std::max(1, sm_count() * (PER >= 64 ? 3 : 4) / num_kv_heads);              \
+    dim3 grid_r((unsigned)std::min<int64_t>(ceil_div(num_queries, SELECT_REG_WARPS), per_head), num_kv_heads); \
+    select_kernel_reg<PER><<<grid_r, SELECT_REG_WARPS * 32, 0, st_sel>>>(                           \
+        score, select_sizes, num_queries, num_kv_heads, (float)target_tokens, iters, force_sink,    \
+        tile_key_beta, qmask, counts, tokens, top1);                                                \
     SEMBLO_LAUNCH_CHECK();                                                                          \
     return 0;                                                                                       \
   }

@@ -35,7 +35,8 @@ class SembloVllmConfig:
     fa3_page_align: int = 16
     kv_outer: bool = True
     query_chunk_size: int = 8192
-    packed_decode_num_splits: int = 32
+    decode_num_splits: int = 8                # splits of the generated-suffix attention
+    packed_decode_num_splits: int = 32        # splits of the selected-cluster attention (doubled by the layer)
     triton_token_tile: int = 16
     runtime_checks: bool = True
 

@@ -293,9 +293,12 @@ def fused_decode_attention(q_chunk: torch.Tensor, query_state, index, q_position
     width = int(index.packed_kv.shape[1])
     posting = index.posting_positions
     if int(posting.shape[1]) != width or not posting.is_contiguous():
-        # the kernel reads posting and packed rows with one stride
-        padded = torch.zeros(hkv, width, dtype=torch.int32, device=posting.device)
-        padded[:, :posting.shape[1]] = posting
+        # the kernel reads posting and packed rows with one stride: a padded copy, made once per index
+        padded = getattr(index, "_decode_posting", None)
+        if padded is None or int(padded.shape[1]) != width:
+            padded = torch.zeros(hkv, width, dtype=torch.int32, device=posting.device)
+            padded[:, :posting.shape[1]] = posting
+            index._decode_posting = padded
         posting = padded
     splits = max(1, int(num_splits))
     ws = getattr(index, "_decode_ws", None)
@@ -316,4 +319,5 @@ def fused_decode_attention(q_chunk: torch.Tensor, query_state, index, q_position
         ptr(index.bucket_indptr), ptr(posting), ptr(index.packed_kv), width, None, None, None, 0, 1, 0,
         ptr(index._no_suffix), hq, hkv, d, c, float(temperature), float(beta), int(target_tokens), sink, int(iters),
         float(sm_scale), splits, ptr(ws.buffer), ws.bytes, ptr(out), ptr(status.word), 7, ptr(lse), 1, stream_ptr()))
+    status.poll()
     return PagedSparseAttentionResult(output=out, logsumexp=lse)

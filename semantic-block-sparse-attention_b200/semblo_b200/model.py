@@ -2,12 +2,17 @@
 
 Mirror of the hot-path half of semblo/vllm_plugin/model.py (SembloAttention):
 ``_init_semblo_runtime`` 302-354, ``_fit_index`` / ``_build_or_append_index`` 378-430,
-``_query_state`` 432-489, ``_arena`` 618-661, ``_adopt_into_arena`` 663-676,
-``_full_graph_decode_step`` 708-747, ``_run_product_attention`` 856-1008,
-``_sparse_layer_forward`` 1130-1167, ``attention_forward`` 1169-1269 and
-``_ingest_prompt_kv`` 1301-1382, for the configuration the kernels serve: flat partition,
+``_query_state`` 432-489, ``_decode_buffers`` / ``_decode_body`` 556-616, ``_arena`` 618-661,
+``_adopt_into_arena`` 663-676, ``_full_graph_decode_step`` 708-747, ``_captured_decode_step`` 788-854,
+``_run_product_attention`` 856-1008, ``_ensure_own_suffix_store`` / ``_write_own_suffix`` 1384-1429,
+``_sparse_layer_forward`` 1130-1167, ``attention_forward`` 1169-1269,
+``begin_streamed_prefill`` / ``begin_token_outer_prefill`` 1271-1287, ``_ingest_prompt_kv`` 1301-1382
+and ``StreamedPrefillSession`` 1431-1529, for the configuration the kernels serve: flat partition,
 identity routing map with whole-vector normalisation, the layer's own cluster-ordered prompt
-copy (own_prompt_cache), the fused decode step over the decode arena.  The model-specific
+copy (own_prompt_cache); generated tokens go through the fused decode step over the decode arena
+(SEMBLO_FULL_GRAPH_DECODE=1) or, without an arena, through the decode kernels over the request's own
+index plus the layer's store of generated K/V, recorded once per request as a CUDA graph
+(decode_graph.DecodeStepGraph).  The model-specific
 subclass sets ``num_heads / num_kv_heads / head_dim / scaling / is_kv_shared_layer`` and
 ``attn.layer_name``, implements ``_project_qkv`` and ``_finish_output``, and calls
 ``_init_semblo_runtime``; everything that differs from the served configuration raises."""
@@ -27,6 +32,8 @@ from . import fused_decode as _fused_decode
 from . import fused_prefill as _fused_prefill
 from .attention_op import register_layer, sparse_attention_op
 from .config import SembloVllmConfig
+from .decode_graph import DecodeStepGraph, tensor_signature
+from .paged_attention import PostingTiles, merge_paged_attention_results, paged_posting_attention
 from .flat_index import routing_normalize
 from .state import ProductPostingIndex, SembloRuntimeState
 from .trivial_router import trivial_router_vectors
@@ -58,6 +65,8 @@ class SembloAttention(nn.Module):
             if self.layer_idx in runtime_config.layer_target_tokens or not runtime_config.decode_target_tokens
             else runtime_config.decode_target_tokens)
         self._effective_target = self.layer_target_tokens
+        self._decode_graph = DecodeStepGraph(f"layer {self.layer_idx}")
+        self._decode_buffers_cache = None
         if not hasattr(self, "is_kv_shared_layer"):
             self.is_kv_shared_layer = False
         if self.builds_product_index:
@@ -110,6 +119,94 @@ class SembloAttention(nn.Module):
         queries, heads, dim = q_pre_rope.shape
         vectors = trivial_router_vectors(q_pre_rope).view(1, queries, heads, 1, dim)
         return SimpleNamespace(vectors=vectors, mixture_weights=None)
+
+    # ---- one generated token without an arena ------------------------------------------------
+    def _decode_buffers(self, q: torch.Tensor) -> tuple:
+        """Output, query position and request id of the recorded step: made once per shape and
+        rewritten in place, since a recording replays the addresses it was taken with."""
+        cached = self._decode_buffers_cache
+        if cached is None or cached[0] != tuple(q.shape) or cached[1].device != q.device:
+            cached = (tuple(q.shape), torch.empty_like(q),
+                      torch.empty(q.shape[0], dtype=torch.int32, device=q.device),
+                      torch.zeros(q.shape[0], dtype=torch.int32, device=q.device))
+            self._decode_buffers_cache = cached
+            self._decode_graph.reset()
+        return cached[1], cached[2], cached[3]
+
+    def _paged_context(self):
+        """Where the generated K/V of this layer's source live: the runtime state's suffix store,
+        addressed by absolute position through its block table like a paged cache."""
+        state = self.runtime_state
+        buf = state.suffix_kv.get(self.source_layer_idx)
+        if buf is None or state.suffix_block_table is None:
+            raise RuntimeError("own_prompt_cache: the suffix store is read before any generated token was "
+                               "written to it")
+        return SimpleNamespace(kv_cache=buf, block_table=state.suffix_block_table,
+                               block_size=int(state.suffix_block_size))
+
+    def _decode_body(self, q, q_pre_rope, positions, index, context, source, out, q_positions, request_ids,
+                     posting, suffix_tiles) -> None:
+        """One generated token into ``out``: selected clusters of the prompt, the generated suffix,
+        merged by their log-sum-exp.  Straight-line, no host read: this is what gets recorded."""
+        q_positions.copy_(positions)
+        query_state = self._query_state(q_pre_rope, source)
+        cfg = self.runtime_config
+        prompt_result = _fused_prefill.fused_decode_attention(
+            q, query_state, index, q_positions, temperature=cfg.selection_temperature,
+            beta=cfg.bucket_size_penalty, target_tokens=int(self._effective_target), sm_scale=self.scaling,
+            num_splits=cfg.packed_decode_num_splits * 2)
+        suffix_result = paged_posting_attention(
+            q, context.kv_cache, posting, suffix_tiles, q_positions, request_ids, context.block_table,
+            block_size=context.block_size, sm_scale=self.scaling, softcap=self.attention_logits_soft_cap,
+            token_tile=cfg.triton_token_tile, num_splits=cfg.decode_num_splits, return_logsumexp=True)
+        out.copy_(merge_paged_attention_results(prompt_result, suffix_result).output)
+
+    def _captured_decode_step(self, q, q_pre_rope, positions, index, context, source) -> torch.Tensor:
+        """The chunk loop's decode branch without the loop: one query, no allocation that varies and
+        no host-side value that changes from step to step, recorded once and replayed."""
+        out, q_positions, request_ids = self._decode_buffers(q)
+        posting, starts, lengths, counts, selected = self.runtime_state.suffix_tiles_for_step(
+            index, num_kv_heads=self.num_kv_heads, tile_size=self.runtime_config.triton_token_tile)
+        suffix_tiles = PostingTiles(starts, lengths, counts, selected)
+
+        def body() -> None:
+            self._decode_body(q, q_pre_rope, positions, index, context, source, out, q_positions, request_ids,
+                              posting, suffix_tiles)
+
+        self._decode_graph.run(
+            (("num_buckets", int(index.num_buckets)), ("target", int(self._effective_target)),
+             tensor_signature(q=q, q_pre=q_pre_rope, positions=positions, out=out, q_positions=q_positions,
+                              request_ids=request_ids, packed_kv=index.packed_kv,
+                              posting_positions=index.posting_positions, codebooks=index.codebooks,
+                              bucket_sizes=index.bucket_sizes, bucket_indptr=index.bucket_indptr,
+                              kv_cache=context.kv_cache, block_table=context.block_table, suffix_posting=posting,
+                              suffix_starts=starts, suffix_lengths=lengths, suffix_counts=counts)),
+            body)
+        return out
+
+    def _ensure_own_suffix_store(self, index, like) -> None:
+        """The layer's store of generated K/V, sized by what the request can still generate."""
+        prompt_length = int(index.prompt_length)
+        limit = int(self.runtime_state.max_model_len)
+        if limit <= prompt_length:
+            raise RuntimeError(f"own_prompt_cache: max_model_len {limit} leaves no room for a suffix after a "
+                               f"{prompt_length}-token prompt")
+        previous = self.runtime_state.suffix_kv.get(self.source_layer_idx)
+        buf = self.runtime_state.ensure_suffix_store(
+            self.source_layer_idx, prompt_length=prompt_length, max_model_len=limit, num_kv_heads=self.num_kv_heads,
+            head_dim=self.head_dim, dtype=like.dtype, device=like.device)
+        if previous is not buf:
+            self._decode_graph.reset()            # the recording would read the previous request's store
+
+    def _write_own_suffix(self, k_post, v_states, positions) -> None:
+        """One generated token's K/V into the layer's store (prompt positions live in the
+        cluster-ordered copy only)."""
+        index = self.runtime_state.source_indexes.get(self.source_layer_idx)
+        if index is None or int(self.runtime_state.step_first_position) < int(index.prompt_length):
+            return
+        self.runtime_state.write_suffix_kv(
+            self.source_layer_idx, positions, k_post.view(-1, self.num_kv_heads, self.head_dim),
+            v_states.view(-1, self.num_kv_heads, self.head_dim))
 
     # ---- arena ---------------------------------------------------------------------------
     def _arena(self, like: torch.Tensor):
@@ -179,6 +276,9 @@ class SembloAttention(nn.Module):
         if k_pre is None:
             raise RuntimeError("a product-index source must produce pre-RoPE keys")
         index = self._build_or_append_index(k_pre, positions)
+        if index.packed_kv is not None and self.runtime_state.step_first_position >= int(index.prompt_length):
+            self._write_own_suffix(k_post, v_states, positions)
+            return
         if index.packed_kv is None:
             k3 = k_post.view(-1, self.num_kv_heads, self.head_dim)
             v3 = v_states.view(-1, self.num_kv_heads, self.head_dim)
@@ -187,6 +287,8 @@ class SembloAttention(nn.Module):
                 index.original_kv = (k3, v3)
             if _arena.full_graph_decode_enabled():
                 self._arena(k_post).install_suffix_store(int(index.prompt_length))
+            else:
+                self._ensure_own_suffix_store(index, k_post)
 
     def _run_product_attention(self, q_post_rope, q_pre_rope, positions, out=None, query_offset: int = 0):
         """Sparse attention for the given prompt queries, written into ``out`` if given.
@@ -196,10 +298,17 @@ class SembloAttention(nn.Module):
         index = self.runtime_state.get(self.source_layer_idx)
         q = q_post_rope.view(-1, self.num_heads, self.head_dim)
         q_pre = q_pre_rope.view(-1, self.num_heads, self.head_dim)
-        if self.runtime_state.step_first_position >= int(index.prompt_length):
-            raise RuntimeError("generated tokens go through the decode arena (SEMBLO_FULL_GRAPH_DECODE=1)")
-        self._effective_target = self._target_for_step(False)
         output = out.view(-1, self.num_heads, self.head_dim) if out is not None else torch.empty_like(q)
+        if self.runtime_state.step_first_position >= int(index.prompt_length):
+            if positions.numel() != 1:
+                raise RuntimeError("one generated token per step")
+            self.runtime_state.record_decode_positions(index, 1)
+            self._effective_target = self._target_for_step(True)
+            step_out = self._captured_decode_step(q.contiguous(), q_pre.contiguous(), positions, index,
+                                                  source._paged_context(), source)
+            output.copy_(step_out)
+            return output.flatten(-2, -1)
+        self._effective_target = self._target_for_step(False)
         step = self.runtime_config.query_chunk_size
         n_queries = positions.numel()
         fused_snapshot = None
@@ -236,3 +345,132 @@ class SembloAttention(nn.Module):
             output.copy_(sparse_output.view(output.shape))
         if _arena.full_graph_decode_enabled() and positions.numel() > 1:
             self._adopt_into_arena()
+
+    # ---- prefill outside the traced model: the prompt arrives in slices -------------------------
+    def begin_streamed_prefill(self, positions: torch.Tensor) -> "StreamedPrefillSession":
+        """Layer-major streaming: ``keys`` for every slice, ``ingest`` once, ``queries`` for every slice."""
+        return StreamedPrefillSession(self, positions)
+
+    def begin_token_outer_prefill(self, positions: torch.Tensor, chunk: int) -> "LayerTokenOuterSession":
+        """Token-order streaming: every slice passes once, with the index fitted on the prompt's head."""
+        return LayerTokenOuterSession(self, positions, chunk)
+
+    @staticmethod
+    def _slice_positions(rope_positions: torch.Tensor, start: int, stop: int):
+        """Rows [start, stop) of a plain [T] position row or of an [n, T] rotary grid."""
+        if rope_positions.ndim == 2:
+            return rope_positions[:, start:stop]
+        return rope_positions[start:stop]
+
+
+class StreamedPrefillSession:
+    """One sparse layer's share of a layer-major streamed prefill (model.py:1431-1529 of the reference).
+
+    The streamer hands the layer the prompt twice, a slice at a time: ``keys`` projects a slice and
+    keeps only its K, V and pre-RoPE K until the whole prompt is staged; ``ingest`` fits the index on
+    every key, packs the cluster-ordered copy and drops the staging; ``queries`` projects a slice
+    again, keeps Q and the gate, selects, attends and finishes the slice's rows of the layer output.
+    The index is fitted on the whole prompt, so the clusters are those of the one-call prefill."""
+
+    def __init__(self, layer: SembloAttention, positions: torch.Tensor) -> None:
+        self.layer = layer
+        self.positions = positions
+        self.tokens = int(positions.numel())
+        self.k_post = self.v = self.k_pre = None
+        layer.runtime_state.maybe_begin_prompt(layer.layer_idx, positions,
+                                               engage_above_tokens=layer.runtime_config.engage_above_tokens)
+        if layer.runtime_state.dense_request:
+            raise RuntimeError("a dense request is not streamed through the sparse layer")
+
+    def keys(self, rope_positions, hidden_states, start: int, stop: int) -> None:
+        layer = self.layer
+        if hasattr(layer, "_project_kv"):
+            k_post, v_states, k_pre = layer._project_kv(rope_positions, hidden_states)
+        else:
+            _q, k_post, v_states, _qp, k_pre, _g = layer._project_qkv(rope_positions, hidden_states)
+        if k_post is None or v_states is None or k_pre is None:
+            raise RuntimeError("the streamed prefill needs a layer with its own K/V")
+        if self.k_post is None:
+            self.k_post = k_post.new_empty((self.tokens,) + tuple(k_post.shape[1:]))
+            self.v = v_states.new_empty((self.tokens,) + tuple(v_states.shape[1:]))
+            self.k_pre = k_pre.new_empty((self.tokens,) + tuple(k_pre.shape[1:]))
+        self.k_post[start:stop] = k_post
+        self.v[start:stop] = v_states
+        self.k_pre[start:stop] = k_pre
+
+    def ingest(self) -> None:
+        if self.k_post is None:
+            raise RuntimeError("no slice was projected before the index was asked for")
+        with torch.profiler.record_function("semblo::attention"):
+            # the staging is the prompt-order copy the chunks read their exact window from; it is
+            # dropped with the session (the reference's FlashAttention body gathers the window from
+            # the packed copy instead and frees the staging here)
+            self.layer._ingest_prompt_kv(self.k_post, self.v, self.k_pre, self.positions, prompt_order_views=True)
+        self.k_pre = None
+        # one running snapshot for all the slices (they arrive in order)
+        index = self.layer.runtime_state.get(self.layer.source_layer_idx)
+        index._token_outer_snapshot = _fused_prefill.CausalSnapshot(index)
+
+    def queries(self, rope_positions, positions, hidden_states, start: int) -> torch.Tensor:
+        layer = self.layer
+        q_post, _k, _v, q_pre, _kp, gate = layer._project_qkv(rope_positions, hidden_states)
+        index = layer.runtime_state.get(layer.source_layer_idx)
+        if getattr(index, "original_kv", None) is None and self.k_post is not None:
+            index.original_kv = (self.k_post.view(-1, layer.num_kv_heads, layer.head_dim),
+                                 self.v.view(-1, layer.num_kv_heads, layer.head_dim))
+        with torch.profiler.record_function("semblo::attention"):
+            attn = layer._run_product_attention(q_post, q_pre, positions, query_offset=start)
+        return layer._finish_output(attn.view(hidden_states.shape[0], -1), gate)
+
+    def finish(self) -> None:
+        index = self.layer.runtime_state.source_indexes.get(self.layer.source_layer_idx)
+        if index is not None:
+            index.original_kv = None
+            index._token_outer_snapshot = None
+        self.k_post = self.v = None
+        if _arena.full_graph_decode_enabled():
+            self.layer._adopt_into_arena()
+
+
+class LayerTokenOuterSession:
+    """The layer's side of a token-order prefill (token_outer_prefill.py:127-212 of the reference):
+    projects each slice and hands it to the streamed store (token_outer.TokenOuterPrefillSession);
+    at the end the index becomes the request's index and, with an arena, moves into it."""
+
+    def __init__(self, layer: SembloAttention, positions: torch.Tensor, chunk: int) -> None:
+        from .token_outer import TokenOuterPrefillSession
+        self.layer = layer
+        cfg = layer.runtime_config
+        self.rope_positions, self.flat = layer._positions_for_runtime(positions)
+        layer.runtime_state.maybe_begin_prompt(layer.layer_idx, self.flat)
+        self.inner = TokenOuterPrefillSession(
+            total_tokens=int(self.flat.numel()), chunk=int(chunk), num_q_heads=layer.num_heads,
+            num_kv_heads=layer.num_kv_heads, head_dim=layer.head_dim, target_tokens=int(layer._target_for_step(False)),
+            temperature=cfg.selection_temperature, beta=cfg.bucket_size_penalty, sm_scale=layer.scaling,
+            flat_unit_tokens=int(os.environ.get("SEMBLO_FLAT_UNIT_TOKENS", cfg.flat_unit_tokens)),
+            flat_min_clusters_log2=max(3, int(os.environ.get("SEMBLO_FLAT_MIN_CLUSTERS_LOG2",
+                                                             cfg.flat_min_clusters_log2))),
+            page_align=int(os.environ.get("SEMBLO_FA3_ALIGN", cfg.fa3_page_align)), device=self.flat.device,
+            kmeans_sample_size=cfg.kmeans_sample_size, codebook_seed=cfg.codebook_seed + layer.source_layer_idx,
+            query_chunk_size=cfg.query_chunk_size)
+
+    def slice(self, hidden_states: torch.Tensor, start: int, stop: int) -> torch.Tensor:
+        layer = self.layer
+        rope = layer._slice_positions(self.rope_positions, start, stop)
+        q_post, k_post, v_states, q_pre, k_pre, gate = layer._project_qkv(rope, hidden_states)
+        if k_post is None or v_states is None or k_pre is None:
+            raise RuntimeError("the token-outer prefill needs a layer with its own K/V")
+        hq, hkv, d = layer.num_heads, layer.num_kv_heads, layer.head_dim
+        attn = self.inner.slice(q_post.view(-1, hq, d), q_pre.view(-1, hq, d), k_post.view(-1, hkv, d),
+                                v_states.view(-1, hkv, d), k_pre.view(-1, hkv, d), start, stop)
+        return layer._finish_output(attn.view(hidden_states.shape[0], -1), gate)
+
+    def finish(self) -> None:
+        self.inner.finish()
+        layer = self.layer
+        layer.runtime_state.put(layer.source_layer_idx, self.inner.index)
+        if _arena.full_graph_decode_enabled():
+            layer._arena(self.inner.index.packed_kv).install_suffix_store(int(self.inner.index.prompt_length))
+            layer._adopt_into_arena()
+        else:
+            layer._ensure_own_suffix_store(self.inner.index, self.inner.index.packed_kv)

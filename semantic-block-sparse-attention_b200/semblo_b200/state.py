@@ -201,6 +201,59 @@ class ProductPostingIndex:
     def inverse_positions(self) -> torch.Tensor:
         return self._inverse_positions
 
+    # ---- generated suffix (state.py:1000-1128 of the reference) --------------------------------
+    def record_generated_positions(self, first_position: int, count: int = 1) -> None:
+        """The next ``count`` generated positions, which must continue the sequence.  Tracked on the
+        host from the step's first position: no device value is read."""
+        expected = int(self.max_position) + 1
+        if int(first_position) != expected:
+            raise ValueError(f"generated suffix must be contiguous: expected {expected}, got {int(first_position)}")
+        self.max_position = expected + int(count) - 1
+
+    def _suffix_position_buffer(self, length: int) -> torch.Tensor:
+        """Absolute positions prompt_length, prompt_length + 1, ... over a reservation of the next
+        power of two at or above ``length`` (at least 64): made once per size, never rewritten."""
+        capacity = 64
+        while capacity < int(length):
+            capacity *= 2
+        buf = getattr(self, "_suffix_positions", None)
+        if buf is None or int(buf.numel()) != capacity:
+            buf = torch.arange(int(self.prompt_length), int(self.prompt_length) + capacity, dtype=torch.int32,
+                               device=self.codebooks.device)
+            self._suffix_positions = buf
+            self.suffix_tiles = None
+        return buf
+
+    def generated_positions(self, device=None) -> torch.Tensor:
+        length = int(self.max_position) + 1 - int(self.prompt_length)
+        return self._suffix_position_buffer(max(length, 1))[:max(length, 0)]
+
+    def generated_suffix_tiles(self, *, num_kv_heads: int, tile_size: int):
+        """Tiles over the whole reservation of the generated suffix: (posting [Hkv, cap], starts,
+        lengths [1, Hkv, slots], counts, selected [1, Hkv]).  Nothing in them changes while the suffix
+        grows inside its reservation, because the attention kernel keeps a listed position only when
+        it is at or before the query's own; the step therefore has no host value that varies."""
+        length = int(self.max_position) + 1 - int(self.prompt_length)
+        if length <= 0:
+            raise ValueError("there is no generated suffix yet")
+        buf = self._suffix_position_buffer(length)
+        capacity = int(buf.numel())
+        slots = -(-capacity // int(tile_size))
+        cached = getattr(self, "suffix_tiles", None)
+        if (cached is None or int(cached[0].shape[-1]) != slots or int(cached[4]) != int(tile_size)
+                or int(cached[0].shape[1]) != int(num_kv_heads)):
+            dev = buf.device
+            starts = (torch.arange(slots, device=dev, dtype=torch.int32) * int(tile_size)).view(1, 1, -1) \
+                .expand(1, num_kv_heads, -1).contiguous()
+            lengths = torch.full((1, num_kv_heads, slots), int(tile_size), dtype=torch.int32, device=dev)
+            counts = torch.full((1, num_kv_heads), slots, dtype=torch.int32, device=dev)
+            selected = torch.full_like(counts, capacity)
+            posting = buf.unsqueeze(0).expand(num_kv_heads, -1)          # every KV head reads the same positions
+            cached = (starts, lengths, counts, selected, int(tile_size), posting)
+            self.suffix_tiles = cached
+        starts, lengths, counts, selected, _, posting = cached
+        return posting, starts, lengths, counts, selected
+
 
 class SembloRuntimeState:
     """Request-local state shared by the sparse layers of one model: the prompt's indexes by
@@ -219,6 +272,73 @@ class SembloRuntimeState:
         self.prompt_epoch = 0
         self.dense_request = False
         self.suffix_block_size = 256
+        self.suffix_kv: dict = {}
+        self.suffix_block_table = None
+        self.suffix_base_block = -1
+        self.step_suffix_key = None
+        self.step_suffix_tiles = None
+        self.step_recorded_key = None
+
+    # ---- the layers' own store of generated K/V (state.py:1239-1284 of the reference) ----------
+    def ensure_suffix_store(self, layer_idx, *, prompt_length, max_model_len, num_kv_heads, head_dim, dtype,
+                            device) -> torch.Tensor:
+        """[2, blocks, 256, Hkv, D] for what this request can still generate, addressed by absolute
+        position through ``suffix_block_table`` [1, blocks of the whole sequence] like a paged cache."""
+        block = int(self.suffix_block_size)
+        base = int(prompt_length) // block
+        n_blocks = max(1, (int(max_model_len) + block - 1) // block - base)
+        if self.suffix_block_table is None or self.suffix_base_block != base \
+                or self.suffix_block_table.device != torch.device(device):
+            table = torch.zeros(1, base + n_blocks, dtype=torch.int32, device=device)
+            table[0, base:] = torch.arange(n_blocks, dtype=torch.int32, device=device)
+            self.suffix_block_table = table
+            self.suffix_base_block = base
+            self.suffix_kv.clear()
+        buf = self.suffix_kv.get(int(layer_idx))
+        if buf is None:
+            buf = torch.zeros(2, n_blocks, block, num_kv_heads, head_dim, dtype=dtype, device=device)
+            self.suffix_kv[int(layer_idx)] = buf
+        return buf
+
+    def write_suffix_kv(self, layer_idx, positions, key, value) -> None:
+        """One step's K/V at its own absolute position."""
+        buf = self.suffix_kv[int(layer_idx)]
+        block = int(self.suffix_block_size)
+        rel = positions.to(torch.int64) - self.suffix_base_block * block
+        b, off = rel // block, rel % block
+        buf[0, b, off] = key.to(buf.dtype)
+        buf[1, b, off] = value.to(buf.dtype)
+
+    def pooled_like(self, key: str, like: torch.Tensor) -> torch.Tensor:
+        return self.pooled_buffer(key, tuple(like.shape), like.dtype, like.device)
+
+    def record_decode_positions(self, index: "ProductPostingIndex", count: int) -> None:
+        """Once per step (the sparse layers of a step share the index bookkeeping per source layer)."""
+        key = (self.prompt_epoch, self.step_first_position, id(index))
+        if self.step_recorded_key != key:
+            index.record_generated_positions(self.step_first_position, count)
+            self.step_recorded_key = key
+
+    def suffix_tiles_for_step(self, index: "ProductPostingIndex", *, num_kv_heads: int, tile_size: int,
+                              pool: bool = False):
+        """The generated-suffix tiles of the current step, built once for all sparse layers;
+        ``pool`` copies them into engine-lifetime buffers so that a recorded decode step of the
+        previous request still finds them at the same addresses."""
+        key = (self.prompt_epoch, self.step_first_position, num_kv_heads, tile_size)
+        if self.step_suffix_key != key:
+            tiles = index.generated_suffix_tiles(num_kv_heads=num_kv_heads, tile_size=tile_size)
+            if pool:
+                names = ("suffix_posting", "suffix_starts", "suffix_lengths", "suffix_counts", "suffix_selected")
+                moved = []
+                for name, tensor in zip(names, tiles):
+                    buffer = self.pooled_like(name, tensor)
+                    if buffer.data_ptr() != tensor.data_ptr():
+                        buffer.copy_(tensor)
+                    moved.append(buffer)
+                tiles = tuple(moved)
+            self.step_suffix_tiles = tiles
+            self.step_suffix_key = key
+        return self.step_suffix_tiles
 
     def register_source_module(self, layer_idx: int, module) -> None:
         self.source_modules[int(layer_idx)] = module

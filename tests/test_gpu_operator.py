@@ -44,6 +44,13 @@ def _make_layer(data, dev, *, hq, hkv, dim, cfg, state, name):
             idx = positions.long()
             d = {k: v[idx] for k, v in data.items()}
             n = idx.numel()
+            if n == 1:
+                # a serving engine hands the decode step the same buffers every time
+                if getattr(self, "_step_buffers", None) is None:
+                    self._step_buffers = {k: torch.empty_like(v) for k, v in d.items()}
+                for k, v in d.items():
+                    self._step_buffers[k].copy_(v)
+                d = self._step_buffers
             return (d["q_post"].reshape(n, hq * dim), d["k_post"].reshape(n, hkv * dim), d["v"], d["q_pre"],
                     d["k_pre"], None)
 
@@ -134,6 +141,169 @@ def test_prompt_and_decode_through_the_operator(dev):
         torch.cuda.synchronize()
         assert layer._arena(data["q_post"]).packed_kv.data_ptr() == ptr_before
         assert torch.equal(out2, out)
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
+def test_decode_without_an_arena_is_recorded_and_replayed(dev):
+    """Without SEMBLO_FULL_GRAPH_DECODE the generated tokens go through the decode kernels over the
+    request's own index plus the layer's store of generated K/V, merged by log-sum-exp
+    (model.py:579-616, 788-854 of the reference), and the step is recorded after two eager steps
+    and replayed (decode_graph.py:125-249)."""
+    from semblo_b200 import _lib
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.state import SembloRuntimeState
+    dim, hq, hkv, sink, length, target, local, chunk, steps = 128, 8, 2, 64, 5120, 256, 128, 1024, 7
+    # eight rows beyond the generated tokens: the out-of-sequence position below is still a valid row
+    cpu = O.mixture_inputs(length=length + steps + 8, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=9)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    state = SembloRuntimeState(max_model_len=8192)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL=str(local), SEMBLO_FLAT_UNIT_TOKENS="32",
+               SEMBLO_FA3_ALIGN="16")
+    os.environ.update(env)
+    os.environ.pop("SEMBLO_FULL_GRAPH_DECODE", None)
+    try:
+        layer = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=state, name="model.layers.1.self_attn.attn")
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        layer._sparse_layer_forward(torch.arange(length, device=dev), hidden)
+        index = state.get(0)
+        store = state.suffix_kv[0]
+        assert store.shape[1] == (8192 + 255) // 256 - length // 256
+        oidx = O.FlatIndex(codebooks=index.codebooks.cpu(), posting_positions=index.posting_positions.cpu(),
+                           bucket_indptr=index.bucket_indptr.cpu(), bucket_sizes=index.bucket_sizes.cpu(),
+                           inverse_positions=index.inverse_positions().cpu(), assign=index.orig_bucket.cpu().long(),
+                           prompt_length=length, page_align=16, packed_kv=index.packed_kv.cpu())
+        clusters = int(index.num_buckets)
+        aref = O.make_arena(capacity=8192, num_clusters=clusters, num_kv_heads=hkv, head_dim=dim, page_align=16,
+                            reserve=1024, kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16)
+        O.arena_adopt(aref, oidx)
+        step_pos = torch.zeros(1, dtype=torch.int64, device=dev)          # the engine's own position buffer
+        for s in range(steps):
+            pos = length + s
+            step_pos.fill_(pos)
+            o = layer._sparse_layer_forward(step_pos, hidden[:1]).view(hq, dim).clone()
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            assert layer._decode_graph.captured == (s >= 2)
+            ws = index._decode_ws
+            sel = torch.zeros(hkv, clusters, dtype=torch.bool)
+            for h in range(hkv):
+                n = int(ws.rcount[h])
+                ids = torch.searchsorted(oidx.bucket_indptr[h].contiguous(), ws.rstart[h, :n].cpu(), right=True) - 1
+                sel[h, ids] = True
+            wd, _, _ = O.decode_step(aref, q_post=cpu["q_post"][pos], q_pre=cpu["q_pre"][pos], pos=pos,
+                                     k_post=cpu["k_post"][pos], v=cpu["v"][pos], temperature=0.1, beta=0.25,
+                                     target_tokens=target, sink=sink, sm_scale=dim ** -0.5, sel=sel)
+            d = (o.cpu().double() - wd).abs()
+            assert float(d.max()) <= 2e-2 and float(d.mean()) <= 1e-3, (s, float(d.max()))
+        assert layer._decode_graph.replays == steps - 3                   # steps 3.. reuse the recording of step 2
+        assert int(index.max_position) == length + steps - 1
+        # the store holds the generated K/V at their absolute positions
+        rel = length - (length // 256) * 256
+        assert torch.equal(store[0, 0, rel:rel + steps].cpu(), cpu["k_post"][length:length + steps])
+        # a position out of sequence is refused on the host
+        step_pos.fill_(length + steps + 5)
+        state.expected_next_position = 0                                  # force the host to read the position
+        with pytest.raises(ValueError):
+            layer._sparse_layer_forward(step_pos, hidden[:1])
+        # a new prompt drops the recording (its store and index are new memory)
+        layer._sparse_layer_forward(torch.arange(length, device=dev), hidden)
+        assert not layer._decode_graph.captured or state.suffix_kv[0] is store
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
+def test_streamed_sessions_through_the_layer(dev):
+    """The two prefill routes that bypass the operator (model.py:1271-1287, 1431-1529 and
+    token_outer_prefill.py:127-212 of the reference): the layer-major session gives the bytes of
+    the one-call prefill; the token-order session gives the bytes of the streamed store driven
+    directly, leaves its index with the runtime state, and generated tokens follow."""
+    from semblo_b200 import _lib
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.state import SembloRuntimeState
+    from semblo_b200.token_outer import TokenOuterPrefillSession
+    dim, hq, hkv, sink, length, target, chunk, steps = 128, 8, 2, 64, 6144, 256, 1024, 3
+    cpu = O.mixture_inputs(length=length + steps, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=21)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL="0", SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16")
+    os.environ.update(env)
+    os.environ.pop("SEMBLO_FULL_GRAPH_DECODE", None)
+    try:
+        positions = torch.arange(length, device=dev)
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        one = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192),
+                          name="model.layers.2.self_attn.attn")
+        want = one._sparse_layer_forward(positions, hidden).clone()
+        # ---- layer-major: keys for every slice, ingest, queries for every slice
+        state = SembloRuntimeState(max_model_len=8192)
+        layer = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=state, name="model.layers.3.self_attn.attn")
+        sess = layer.begin_streamed_prefill(positions)
+        with pytest.raises(RuntimeError):
+            sess.ingest()                                               # nothing staged yet
+        for s0 in range(0, length, chunk):
+            sess.keys(positions[s0:s0 + chunk], hidden[s0:s0 + chunk], s0, s0 + chunk)
+        sess.ingest()
+        got = torch.cat([sess.queries(positions[s0:s0 + chunk], positions[s0:s0 + chunk], hidden[s0:s0 + chunk], s0)
+                         for s0 in range(0, length, chunk)])
+        sess.finish()
+        torch.cuda.synchronize()
+        _lib.status_for(dev).raise_if_set()
+        assert torch.equal(got, want)
+        assert state.get(0).original_kv is None and 0 in state.suffix_kv
+        # ---- token order: one pass, the index fitted on the prompt's head
+        state2 = SembloRuntimeState(max_model_len=8192)
+        layer2 = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=state2, name="model.layers.4.self_attn.attn")
+        sess2 = layer2.begin_token_outer_prefill(positions, chunk)
+        direct = TokenOuterPrefillSession(total_tokens=length, chunk=chunk, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim,
+                                          target_tokens=target, temperature=0.1, beta=0.25, sm_scale=dim ** -0.5,
+                                          flat_unit_tokens=32, flat_min_clusters_log2=7, page_align=16, device=dev,
+                                          kmeans_sample_size=1024, codebook_seed=0, query_chunk_size=chunk)
+        for s0 in range(0, length, chunk):
+            sl = slice(s0, s0 + chunk)
+            a = sess2.slice(hidden[sl], s0, s0 + chunk).view(chunk, hq, dim)
+            b = direct.slice(data["q_post"][sl], data["q_pre"][sl], data["k_post"][sl], data["v"][sl], data["k_pre"][sl],
+                             s0, s0 + chunk)
+            assert torch.equal(a, b), s0
+        sess2.finish()
+        direct.finish()
+        index = state2.get(0)
+        assert index is sess2.inner.index and torch.equal(index.bucket_sizes, direct.index.bucket_sizes)
+        assert int(index.bucket_sizes.sum()) == length * hkv
+        # generated tokens over the streamed index
+        oidx = O.FlatIndex(codebooks=index.codebooks.cpu(), posting_positions=index.posting_positions.cpu(),
+                           bucket_indptr=index.bucket_indptr.cpu(), bucket_sizes=index.bucket_sizes.cpu(),
+                           inverse_positions=index.inverse_positions().cpu(), assign=index.orig_bucket.cpu().long(),
+                           prompt_length=length, page_align=16, packed_kv=index.packed_kv.cpu())
+        clusters = int(index.num_buckets)
+        aref = O.make_arena(capacity=16384, num_clusters=clusters, num_kv_heads=hkv, head_dim=dim, page_align=16,
+                            reserve=1024, kv_dtype=torch.bfloat16, desc_dtype=torch.bfloat16)
+        O.arena_adopt(aref, oidx)
+        step_pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        for s in range(steps):
+            pos = length + s
+            step_pos.fill_(pos)
+            o = layer2._sparse_layer_forward(step_pos, hidden[:1]).view(hq, dim).clone()
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            ws = index._decode_ws
+            sel = torch.zeros(hkv, clusters, dtype=torch.bool)
+            for h in range(hkv):
+                n = int(ws.rcount[h])
+                ids = torch.searchsorted(oidx.bucket_indptr[h].contiguous(), ws.rstart[h, :n].cpu(), right=True) - 1
+                sel[h, ids] = True
+            wd, _, _ = O.decode_step(aref, q_post=cpu["q_post"][pos], q_pre=cpu["q_pre"][pos], pos=pos,
+                                     k_post=cpu["k_post"][pos], v=cpu["v"][pos], temperature=0.1, beta=0.25,
+                                     target_tokens=target, sink=sink, sm_scale=dim ** -0.5, sel=sel)
+            d = (o.cpu().double() - wd).abs()
+            assert float(d.max()) <= 2e-2 and float(d.mean()) <= 1e-3, (s, float(d.max()))
     finally:
         for k in env:
             os.environ.pop(k, None)

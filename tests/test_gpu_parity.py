@@ -359,7 +359,8 @@ def test_sparse_chunk_attention_matches_oracle_on_the_same_selection(dev, dim, h
 
 def test_gather_launch_order_counts_union_rows(dev):
     """work[tile, head] = rows in the union of the tile's selections; the order is a permutation of
-    the (tile, head) pairs by descending work class (256 classes of equal width)."""
+    the (tile, head) pairs, one KV head after the other, each head's by descending work class
+    (64 classes of equal width)."""
     from semblo_b200.fused_prefill import gather_launch_order
     q_count, hkv, clusters, hq = 1000, 2, 256, 8             # G = 4: tiles of 32 queries, the last one ragged
     g = torch.Generator().manual_seed(11)
@@ -379,8 +380,10 @@ def test_gather_launch_order_counts_union_rows(dev):
     assert torch.equal(work.cpu().long().view(tiles, hkv), want)
     for o in (got.cpu().long(), got2.cpu().long()):
         assert sorted(o.tolist()) == list(range(tiles * hkv))
-        cls = want.view(-1)[o] * 256 // (int(want.max()) + 1)
-        assert bool((cls[:-1] >= cls[1:]).all())
+        classes = min(64, 1024 // hkv)
+        cls = want.view(-1)[o] * classes // (int(want.max()) + 1)
+        key = (o % hkv) * classes + (classes - 1 - cls)             # head-major, then descending work
+        assert bool((key[:-1] <= key[1:]).all())
     # without a tile order the tiles are consecutive queries
     got3 = gather_launch_order(None, O.pack_bits(sel).to(dev), sizes.to(dev), hq, work=work)
     want3 = torch.stack([torch.stack([(sel[32 * t:32 * t + 32, h].any(0).long() * sizes[h].long()).sum()
