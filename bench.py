@@ -51,7 +51,7 @@ PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_l
                sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
 # command, keyed by (kernel, prompt length): a record of a past capture, not something a run produces
-DRAM_TRAFFIC_PER_LAUNCH = {("sparse_gather_prefill_kernel<256,4>", 131072): 1.307e9}
+DRAM_TRAFFIC_PER_LAUNCH = {("sparse_gather_prefill_kernel<256,4>", 131072): 1.094e9}
 
 HEAD_SHARDED = dict(length=1048576, hq=32, hkv=8, dim=128, centres=1024, unit=64, min_log2=7, target=8192,
                     sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16, reserve=1024,
@@ -271,6 +271,28 @@ def kernel_launches(calls: dict, clusters: int) -> int:
                 "semblo_argsort_keys": 3 * passes,
                 "semblo_decode_step": 3}
     return sum(per_call.get(k, 0) * v for k, v in calls.items())
+
+
+# ------------------------------------------------------------------------- selection alone
+def select_measure(device, clusters=2048, queries=8192, heads=4, target=4096, reps=4):
+    """One chunk's selection launch on seeded scores (a small case for profiling the kernel)."""
+    from semblo_b200._lib import lib, ptr, check, stream_ptr
+    g = torch.Generator(device=device).manual_seed(1)
+    score = (torch.randn(queries, heads, clusters, device=device, generator=g) * 8 - 20).float()
+    sizes = torch.randint(0, 130, (heads, clusters), device=device, generator=g, dtype=torch.int32)
+    qmask = torch.empty(queries, heads, clusters // 32, dtype=torch.int32, device=device)
+    top1 = torch.empty(heads, queries, dtype=torch.int32, device=device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    us = []
+    for _ in range(reps):
+        e0.record()
+        check(lib().semblo_select_clusters(ptr(score), ptr(sizes), queries, heads, clusters, target, 16, 0, ptr(qmask),
+                                           None, None, ptr(top1), 0.25, stream_ptr()))
+        e1.record()
+        torch.cuda.synchronize()
+        us.append(round(e0.elapsed_time(e1) * 1e3, 1))
+    return {"metric": "select_us_per_chunk", "clusters": clusters, "queries": queries, "kv_heads": heads,
+            "launch_us": us, "score_bytes": score.numel() * 4}
 
 
 # ------------------------------------------------------------------------- decode measurement
@@ -683,7 +705,7 @@ def cpu_reference_sample(cfg, threads=None):
     sm = dim ** -0.5
     chunk = cfg["chunk"]
     # a dense chunk: 256 queries spread over the second chunk
-    nq_d = 8192
+    nq_d = 4096
     cs_d = chunk
     pick = torch.arange(0, chunk, chunk // nq_d) + cs_d
     t0 = time.perf_counter()
@@ -694,25 +716,28 @@ def cpu_reference_sample(cfg, threads=None):
     dense_chunks = [c for c in range(0, L, chunk) if O.chunk_plan(c, cfg["target"], cfg["local"]) == 0]
     dense_pairs = sum(float((torch.arange(c, c + chunk) + 1).sum()) for c in dense_chunks)
     dense_s = hkv * t_dense * dense_pairs / dense_pairs_sample
-    # a sparse chunk in the middle of the prompt: 512 queries spread over it
-    nq_s = 16384
-    cs = 9 * chunk
-    ws = cs - cfg["local"]
-    picks = torch.arange(0, chunk, chunk // nq_s) + cs
-    t0 = time.perf_counter()
-    sizes = O.causal_sizes_at(index, ws - 1)
-    vectors = O.trivial_router_vectors(data["q_pre"][picks, :g])
-    sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=cfg["temperature"], beta=cfg["beta"],
-                            target_tokens=cfg["target"], sink=cfg["sink"])
-    O.sparse_chunk_attention_gather(data["q_post"][picks, :g], index, sel, sizes, picks, data["k_post"][ws:cs + chunk, :1],
-                                    data["v"][ws:cs + chunk, :1], ws, sm)
-    t_sparse = time.perf_counter() - t0
+    # two sparse chunks (an early and a late one), every query of each
+    nq_s = chunk
+    sparse_at = (5 * chunk, 13 * chunk)
+    t_sparse = 0.0
+    for cs in sparse_at:
+        ws = cs - cfg["local"]
+        picks = torch.arange(0, chunk, chunk // nq_s) + cs
+        t0 = time.perf_counter()
+        sizes = O.causal_sizes_at(index, ws - 1)
+        vectors = O.trivial_router_vectors(data["q_pre"][picks, :g])
+        sel = O.select_clusters(vectors, index.codebooks, sizes, temperature=cfg["temperature"], beta=cfg["beta"],
+                                target_tokens=cfg["target"], sink=cfg["sink"])
+        O.sparse_chunk_attention_gather(data["q_post"][picks, :g], index, sel, sizes, picks,
+                                        data["k_post"][ws:cs + chunk, :1], data["v"][ws:cs + chunk, :1], ws, sm)
+        t_sparse += time.perf_counter() - t0
+    t_sparse /= len(sparse_at)
     n_sparse = (L // chunk) - len(dense_chunks)
     sparse_s = hkv * n_sparse * (chunk / nq_s) * t_sparse
     total = build_s + dense_s + sparse_s
     text = (f"1 of {hkv} KV heads in full for the index (normalise, 8 k-means iterations, assignment, layout, pack: "
-            f"{t_build:.1f}s), {nq_d} queries spread over a dense chunk ({t_dense:.1f}s) and {nq_s} over a sparse chunk "
-            f"({t_sparse:.1f}s); scaled to the whole step (build {build_s:.1f}s + dense {dense_s:.1f}s + sparse "
+            f"{t_build:.1f}s), {nq_d} queries spread over a dense chunk ({t_dense:.1f}s) and all {nq_s} queries of two "
+            f"sparse chunks ({t_sparse:.1f}s each); scaled to the whole step (build {build_s:.1f}s + dense {dense_s:.1f}s + sparse "
             f"{sparse_s:.1f}s); sample wall {time.perf_counter() - t_all:.1f}s")
     return L / total, text
 
@@ -769,6 +794,8 @@ def main():
     ap.add_argument("--length", type=int, default=0, help="override the prompt length (profiling on a small case)")
     ap.add_argument("--decode-only", action="store_true",
                     help="run only the decode measurement and print its record (profiling the decode kernels)")
+    ap.add_argument("--select-only", type=int, default=0, metavar="CLUSTERS",
+                    help="run only one chunk's selection launch at this cluster count (profiling the kernel)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -786,6 +813,9 @@ def main():
     pk = peaks()
     if args.decode_only:
         print(json.dumps(decode_measure(device, pk)))
+        return
+    if args.select_only:
+        print(json.dumps(select_measure(device, clusters=args.select_only, heads=8 if args.select_only >= 16384 else 4)))
         return
     if args.head_sharded_only:
         rec = head_sharded_measure(device, rank, world, pk, length=args.length or None)
