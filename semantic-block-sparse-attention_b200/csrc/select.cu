@@ -27,7 +27,7 @@ using semblo::sm_count;
 
 namespace {
 
-constexpr int SC_BN = 128;
+constexpr int SC_BN = 64;                 // centroids per accumulator: two CTAs share an SM (tensor memory 2 x 256 columns)
 constexpr int SC_STAGES = 2;
 constexpr float NEG_BIG = -3.4e38f;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -38,7 +38,7 @@ struct ScoreSmem {
   static constexpr int B_BYTES = SC_BN * D * 2;
   static constexpr int BAR_OFF = SC_STAGES * B_BYTES;
   static constexpr int Q_COL = 2 * SC_BN;            // TMEM: two accumulators, then the routing vectors (D / 2 columns)
-  static constexpr int TMEM_COLS = 512;              // allocation (a power of two >= Q_COL + D / 2)
+  static constexpr int TMEM_COLS = Q_COL + D / 2 <= 256 ? 256 : 512;   // allocation: a power of two
   static_assert(Q_COL + D / 2 <= TMEM_COLS, "tensor memory budget");
   static constexpr int XCHG_OFF = BAR_OFF + 256;               // float [2][128][2]: (max, sum) of a half-row
   static constexpr int TOTAL = XCHG_OFF + 2048 + 1024;
@@ -69,7 +69,7 @@ __device__ __forceinline__ int head_butterfly(float (&v)[32], int lane) {
 }
 
 template <int D, int G>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(320, SC_BN <= 64 ? 2 : 1)
 score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
              const __grid_constant__ CUtensorMap tmap_cb,   // codebooks [Hkv*2, C, D/2] bf16, box (64, 128, 1)
              int num_queries, int num_clusters, const int32_t* __restrict__ sizes,   // [Hkv, C]
@@ -152,7 +152,8 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
     }
   } else {
     // epilogue warps 0-7: thread = (half, row); query i = row / G, head t = row % G.  The two
-    // warps that share 32 rows split every 128-cluster chunk: half 0 takes its first 64 columns.
+    // warps that share 32 rows split every chunk of SC_BN clusters: half 0 takes its first columns.
+    constexpr int CC = SC_BN / 64;                 // 32-column groups per thread and chunk
     const int hf = warp >> 2;
     const int row = threadIdx.x & 127;
     const int qi = q0 + row / G;
@@ -185,13 +186,13 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
       const int c0 = (j % chunks) * SC_BN;
       const bool full_chunk = c0 + SC_BN <= num_clusters;
       // sizes of this thread's output clusters, fetched before the accumulator is awaited
-      int nsz[2][OUT];
+      int nsz[CC][OUT];
       if (pass == 1) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc)
+        for (int cc = 0; cc < CC; ++cc)
 #pragma unroll
           for (int i = 0; i < OUT; ++i) {
-            const int c = c0 + (2 * hf + cc) * 32 + col_off + i;
+            const int c = c0 + (CC * hf + cc) * 32 + col_off + i;
             nsz[cc][i] = c < num_clusters ? sz[c] : 0;
           }
       }
@@ -213,8 +214,8 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
       }
       const float neg_ref = pass == 0 ? -m_run : -lse2;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c4 = 2 * hf + cc;
+      for (int cc = 0; cc < CC; ++cc) {
+        const int c4 = CC * hf + cc;
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + b * SC_BN + c4 * 32, r);
         tmem_ld_wait();

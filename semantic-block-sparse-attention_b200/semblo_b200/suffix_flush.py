@@ -63,16 +63,24 @@ def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
     d = int(arena.packed_kv.shape[-1])
     width = int(arena.packed_kv.shape[1])
     ws_bytes = int(lib().semblo_flush_workspace_bytes(n, hkv, c))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    old_packed = torch.empty_like(arena.packed_kv)
-    old_posting = torch.empty_like(arena.posting)
+    # the copy of the old store and the workspace live with the arena: a flush between two decode
+    # steps allocates nothing of the store's size and the arena's addresses stay what they were
+    scratch = getattr(arena, "_flush_scratch", None)
+    if scratch is None or scratch[0].shape != arena.packed_kv.shape or scratch[0].device != dev:
+        scratch = (torch.empty_like(arena.packed_kv), torch.empty_like(arena.posting))
+        arena._flush_scratch = scratch
+    old_packed, old_posting = scratch
+    ws = getattr(arena, "_flush_ws", None)
+    if ws is None or ws.numel() < ws_bytes or ws.device != dev:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        arena._flush_ws = ws
     # the flush has a status word of its own: a stale code of another call cannot gate it, and the
     # host-side state below is committed only after the device has accepted the new layout
     status = _lib.DeviceStatus(dev)
     check(lib().semblo_flush_repack(ptr(arena.packed_kv), arena.packed_kv.stride(0), width, ptr(arena.posting),
                                     arena.posting.stride(0), ptr(arena.sizes), ptr(arena.indptr), c, hkv, d, align,
                                     ptr(k), ptr(v), ptr(pos.to(torch.int32)), ptr(assign), n, ptr(old_packed),
-                                    ptr(old_posting), ptr(ws), ws_bytes, ptr(status.word), stream_ptr()))
+                                    ptr(old_posting), ptr(ws), ws.numel(), ptr(status.word), stream_ptr()))
     status.raise_if_set()        # refused (the result would not fit): the store is unchanged, as after the
                                  # reference's repack_apply, which raises before it moves anything
     arena.prompt_length_t.fill_(int(to))
