@@ -157,11 +157,109 @@ def gather_launch_order(q_order, qmask: torch.Tensor, causal_sizes: torch.Tensor
     return out[:n]
 
 
+def chunk_window_start(chunk_start: int, target_tokens: int, dense_prefix_x: int = 4) -> int:
+    """First position of a chunk's exact window: 0 for a dense-prefix chunk (fused_prefill.py:250-279)."""
+    cap = int(os.environ.get("SEMBLO_FA3_DENSE_PREFIX_X", str(dense_prefix_x))) * int(target_tokens)
+    local = int(os.environ.get("SEMBLO_FA3_LOCAL", "0"))
+    return 0 if chunk_start <= cap else max(0, chunk_start - local)
+
+
+class WindowAhead:
+    """The part of a prompt's attention that needs no index, issued ahead on a stream of its own.
+
+    A dense-prefix chunk and the exact local window of every later chunk read only the
+    position-ordered K/V, so they can run while the index is still being built and fill the
+    multiprocessors that the build's many short kernels and host round trips leave idle.  ``ahead``
+    chunks are in flight at most (one fp32 partial [chunk, Hq, D] and one LSE each); ``take`` makes
+    the calling stream wait for a chunk's launch and hands over its partial, ``release`` lets the
+    buffer be used again.  No reference counterpart: the reference runs the three launches of a
+    chunk in order on one stream (kv_outer.py:632-805)."""
+
+    def __init__(self, q: torch.Tensor, q_positions: torch.Tensor, ordered_k: torch.Tensor, ordered_v: torch.Tensor, *,
+                 chunk: int, target_tokens: int, sm_scale: float, out: torch.Tensor, dense_prefix_x: int = 4,
+                 attended=None, ahead: int = 16, before_launch=None) -> None:
+        self.q, self.pos, self.k, self.v, self.out = q, q_positions, ordered_k, ordered_v, out
+        self.chunk, self.target, self.sm_scale, self.x = int(chunk), int(target_tokens), float(sm_scale), dense_prefix_x
+        self.attended, self.before_launch = attended, before_launch
+        self.starts = list(range(0, int(q.shape[0]), self.chunk))
+        self.stream = torch.cuda.Stream(device=q.device)
+        self.depth = max(1, min(int(ahead), len(self.starts)))
+        n_sparse = sum(1 for cs in self.starts if chunk_window_start(cs, self.target, self.x) > 0)
+        slots = max(1, min(self.depth, n_sparse))
+        hq, d = int(q.shape[1]), int(q.shape[2])
+        self.partial = torch.empty(slots, self.chunk, hq, d, dtype=torch.float32, device=q.device)
+        self.lse = torch.empty(slots, self.chunk, hq, dtype=torch.float32, device=q.device)
+        self.done: dict = {}            # chunk start -> event recorded behind its launch
+        self.slot_of: dict = {}
+        self.free = [(s, None) for s in range(slots)]     # (slot, event after which it may be rewritten)
+        self.issued = 0
+        self.stream.wait_stream(torch.cuda.current_stream(q.device))
+        self._issue(self.depth)
+
+    def _issue(self, upto: int) -> None:
+        from contextlib import nullcontext
+        while self.issued < min(upto, len(self.starts)):
+            cs = self.starts[self.issued]
+            ce = min(int(self.q.shape[0]), cs + self.chunk) - 1
+            wstart = chunk_window_start(cs, self.target, self.x)
+            if wstart > 0 and not self.free:
+                return                                     # every partial is still waiting for its sparse launch
+            with torch.cuda.stream(self.stream):
+                if self.before_launch is not None:
+                    self.before_launch(cs, ce)
+                k_w, v_w = self.k[wstart:ce + 1], self.v[wstart:ce + 1]
+                if wstart == 0:
+                    with _attend_part("semblo::attend_dense_prefix"):
+                        window_attention(self.q[cs:ce + 1], self.pos[cs:ce + 1], ordered_k=k_w, ordered_v=v_w,
+                                         ordered_pos0=0, local_start=0, sm_scale=self.sm_scale, out=self.out[cs:ce + 1],
+                                         attended=self.attended)
+                else:
+                    slot, reusable = self.free.pop(0)
+                    if reusable is not None:
+                        self.stream.wait_event(reusable)
+                    n = ce - cs + 1
+                    with _attend_part("semblo::attend_current_chunk"):
+                        window_attention(self.q[cs:ce + 1], self.pos[cs:ce + 1], ordered_k=k_w, ordered_v=v_w,
+                                         ordered_pos0=wstart, local_start=wstart, sm_scale=self.sm_scale,
+                                         out=self.out[cs:ce + 1], lse=self.lse[slot, :n], attended=self.attended,
+                                         partial=self.partial[slot, :n])
+                    self.slot_of[cs] = slot
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+                self.done[cs] = ev
+            self.issued += 1
+
+    def take(self, chunk_start: int):
+        """The calling stream waits for the chunk's launch; returns (partial, lse) or None (dense prefix)."""
+        if chunk_start not in self.done:
+            self._issue(self.starts.index(chunk_start) + 1)
+        torch.cuda.current_stream(self.q.device).wait_event(self.done.pop(chunk_start))
+        slot = self.slot_of.get(chunk_start)
+        if slot is None:
+            return None
+        n = min(int(self.q.shape[0]), chunk_start + self.chunk) - chunk_start
+        return self.partial[slot, :n], self.lse[slot, :n]
+
+    def release(self, chunk_start: int) -> None:
+        """The chunk's sparse launch has been issued on the calling stream: its partial may be reused
+        once that launch is over, and the next chunks' windows are issued."""
+        slot = self.slot_of.pop(chunk_start, None)
+        if slot is not None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.q.device))
+            self.free.append((slot, ev))
+        self._issue(self.starts.index(chunk_start) + 1 + self.depth)
+
+    def finish(self) -> None:
+        torch.cuda.current_stream(self.q.device).wait_stream(self.stream)
+
+
 def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions: torch.Tensor,
                           snapshot_state: CausalSnapshot, chunk_start: int, chunk_end: int, *,
                           temperature: float, beta: float, target_tokens: int, queries_per_block: int = 32,
                           sm_scale: float, iters: int = 16, dense_prefix_x: int = 4, out=None,
-                          attended=None, local_kv=None, _timer=None, **unused) -> torch.Tensor:
+                          attended=None, local_kv=None, window: "WindowAhead | None" = None, _timer=None,
+                          **unused) -> torch.Tensor:
     """Attention of one query chunk (fused_prefill.py:219-482, default path).
 
     ``query_state.vectors`` [1, Q, Hq, 1, D] routing vectors; ``index.original_kv`` must hold
@@ -170,13 +268,24 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     keeps no prompt-order copy, hands over the rows of the window it has gathered).
     ``attended`` (int64, optional) accumulates the attended (query, key) pairs of the dense / window
     launch in [0]; with four or more elements the sparse launch counts its pairs in [2] and the rows
-    it gathered in [3], otherwise in [0] and [1]."""
+    it gathered in [3], otherwise in [0] and [1].  ``window`` (a WindowAhead over the same prompt) has
+    issued the dense / window launch already: this call waits for it and merges."""
     import semblo_b200
     semblo_b200.SPARSE_ATTENTION_CALLS += 1
-    cap = int(os.environ.get("SEMBLO_FA3_DENSE_PREFIX_X", str(dense_prefix_x))) * target_tokens
-    local = int(os.environ.get("SEMBLO_FA3_LOCAL", "0"))
-    wstart = 0 if chunk_start <= cap else max(0, chunk_start - local)
-    if local_kv is not None:
+    wstart = chunk_window_start(chunk_start, target_tokens, dense_prefix_x)
+    if window is not None:
+        if local_kv is not None:
+            raise RuntimeError("windows issued ahead read the prompt-order K/V, not rows handed over per call")
+        ahead = window.take(chunk_start)
+        if (ahead is None) != (wstart == 0):
+            raise RuntimeError("the windows issued ahead were planned with another budget or window")
+        if out is not None and out.data_ptr() != window.out[chunk_start:chunk_end + 1].data_ptr():
+            raise RuntimeError("the windows issued ahead write into their own output buffer: pass its rows as out")
+        if wstart == 0:
+            return window.out[chunk_start:chunk_end + 1]
+        k_loc = v_loc = None
+        pos0 = 0
+    elif local_kv is not None:
         k_loc, v_loc, pos0 = local_kv
         if pos0 > wstart or pos0 + k_loc.shape[0] <= chunk_end:
             raise RuntimeError(f"the window [{wstart}, {chunk_end}] is not inside the rows handed over "
@@ -192,7 +301,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     def window_rows(first):
         return k_loc[first - pos0:chunk_end + 1 - pos0], v_loc[first - pos0:chunk_end + 1 - pos0]
 
-    if wstart == 0:
+    if wstart == 0:                                        # (not reached with windows issued ahead)
         if _timer:
             _timer("start")
         k_w, v_w = window_rows(0)
@@ -248,15 +357,19 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                                     out=snap.cta_order[:n_cta])
     if out is None:
         out = torch.empty_like(q_chunk)
-    lse = snap.lse[:q_count]
-    partial = snap.partial[:q_count]
     if _timer:
         _timer("start")
-    # the exact window [wstart, q] in position order, then the selected clusters merged into it
-    k_w, v_w = window_rows(wstart)
-    with _attend_part("semblo::attend_current_chunk"):
-        window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=wstart,
-                         local_start=wstart, sm_scale=sm_scale, out=out, lse=lse, attended=attended, partial=partial)
+    if window is not None:
+        partial, lse = ahead
+    else:
+        lse = snap.lse[:q_count]
+        partial = snap.partial[:q_count]
+        # the exact window [wstart, q] in position order, then the selected clusters merged into it
+        k_w, v_w = window_rows(wstart)
+        with _attend_part("semblo::attend_current_chunk"):
+            window_attention(q_chunk, q_positions, ordered_k=k_w, ordered_v=v_w, ordered_pos0=wstart,
+                             local_start=wstart, sm_scale=sm_scale, out=out, lse=lse, attended=attended,
+                             partial=partial)
     if _timer:
         _timer("mid")
     # the kernel gathers the selected rows itself: the reference's gather_kv label has no launch of its own here
@@ -268,6 +381,8 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
                                 partial=partial, cta_order=cta_order)
     if _timer:
         _timer("stop")
+    if window is not None:
+        window.release(chunk_start)
     status.poll()
     return out
 

@@ -290,9 +290,11 @@ class SembloAttention(nn.Module):
             else:
                 self._ensure_own_suffix_store(index, k_post)
 
-    def _run_product_attention(self, q_post_rope, q_pre_rope, positions, out=None, query_offset: int = 0):
+    def _run_product_attention(self, q_post_rope, q_pre_rope, positions, out=None, query_offset: int = 0,
+                               window=None):
         """Sparse attention for the given prompt queries, written into ``out`` if given.
-        ``query_offset`` is where these queries start in the prompt."""
+        ``query_offset`` is where these queries start in the prompt; ``window`` (a
+        fused_prefill.WindowAhead over these queries and ``out``) has issued the index-free launches."""
         semblo_b200.SPARSE_ATTENTION_CALLS += 1
         source = self._source_module()
         index = self.runtime_state.get(self.source_layer_idx)
@@ -323,7 +325,9 @@ class SembloAttention(nn.Module):
                 end - 1 + query_offset, temperature=self.runtime_config.selection_temperature,
                 beta=self.runtime_config.bucket_size_penalty, target_tokens=int(self._effective_target),
                 queries_per_block=self.runtime_config.fused_select_block_queries, sm_scale=self.scaling,
-                dense_prefix_x=4, out=output[start:end])
+                dense_prefix_x=4, out=output[start:end], window=window)
+        if window is not None:
+            window.finish()
         if getattr(index, "original_kv", None) is not None:
             index.original_kv = None                  # the views are dropped once the prompt has been attended
         _lib.status_for(q.device).poll()
@@ -339,12 +343,43 @@ class SembloAttention(nn.Module):
         if self.runtime_state.dense_request or not self.uses_sparse_attention:
             raise RuntimeError("this layer serves the sparse path only: the stock attention of a dense request "
                                "stays with the model's own attention layer")
-        self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
-        sparse_output = self._run_product_attention(q_post, q_pre, positions, out=output)
-        if sparse_output.data_ptr() != output.data_ptr():
-            output.copy_(sparse_output.view(output.shape))
+        if positions.numel() > 1 and self._windows_ahead_enabled(k_post, v_states):
+            self._prompt_with_windows_ahead(positions, q_post, k_post, v_states, q_pre, k_pre, output)
+        else:
+            self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
+            sparse_output = self._run_product_attention(q_post, q_pre, positions, out=output)
+            if sparse_output.data_ptr() != output.data_ptr():
+                output.copy_(sparse_output.view(output.shape))
         if _arena.full_graph_decode_enabled() and positions.numel() > 1:
             self._adopt_into_arena()
+
+    def _windows_ahead_enabled(self, k_post, v_states) -> bool:
+        """``SEMBLO_WINDOWS_AHEAD=0`` keeps the three launches of a chunk in order on the caller's stream."""
+        return (os.environ.get("SEMBLO_WINDOWS_AHEAD", "1") == "1" and not self.is_kv_shared_layer
+                and k_post is not None and v_states is not None and self.runtime_state.step_first_position == 0)
+
+    def _prompt_with_windows_ahead(self, positions, q_post, k_post, v_states, q_pre, k_pre, output) -> None:
+        """A whole prompt in one call: the dense-prefix chunks and every chunk's exact window need no
+        index, so they are issued first, on a stream of normal priority, while the index build and the
+        chunk loop run on a high-priority stream (joined with the caller's stream at both ends).  The
+        multiprocessors that the build's short kernels and host round trips leave idle are then busy
+        with window tiles.  Same launches on the same data as the in-order path: identical bytes."""
+        dev = q_post.device
+        caller = torch.cuda.current_stream(dev)
+        if getattr(self, "_prompt_stream", None) is None or self._prompt_stream.device != dev:
+            self._prompt_stream = torch.cuda.Stream(device=dev, priority=-1)
+        chain = self._prompt_stream
+        chain.wait_stream(caller)
+        with torch.cuda.stream(chain):
+            q3 = q_post.view(-1, self.num_heads, self.head_dim)
+            out3 = output.view(-1, self.num_heads, self.head_dim)
+            window = _fused_prefill.WindowAhead(
+                q3, positions.to(torch.int32), k_post.view(-1, self.num_kv_heads, self.head_dim),
+                v_states.view(-1, self.num_kv_heads, self.head_dim), chunk=self.runtime_config.query_chunk_size,
+                target_tokens=int(self._target_for_step(False)), sm_scale=self.scaling, out=out3, dense_prefix_x=4)
+            self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
+            self._run_product_attention(q_post, q_pre, positions, out=output, window=window)
+        caller.wait_stream(chain)
 
     # ---- prefill outside the traced model: the prompt arrives in slices -------------------------
     def begin_streamed_prefill(self, positions: torch.Tensor) -> "StreamedPrefillSession":
