@@ -549,9 +549,24 @@ __global__ void centroid_update_kernel(const float* __restrict__ sample, const i
   const int d = threadIdx.x;
   float acc = 0.f;
   if (hi > lo) {
-    for (int i = lo; i < hi; ++i) {
-      const float* row = sample + (int64_t)order[i] * dim;
-      if (d < dim) acc += row[d];
+    // member ids through shared memory, eight rows in flight; the additions stay in index order
+    __shared__ int32_t ids[256];
+    for (int base = lo; base < hi; base += 256) {
+      const int n = min(256, hi - base);
+      __syncthreads();
+      for (int t = threadIdx.x; t < n; t += blockDim.x) ids[t] = order[base + t];
+      __syncthreads();
+      if (d < dim) {
+        int i = 0;
+        for (; i + 8 <= n; i += 8) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = __ldg(sample + (int64_t)ids[i + u] * dim + d);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) acc += v[u];
+        }
+        for (; i < n; ++i) acc += __ldg(sample + (int64_t)ids[i] * dim + d);
+      }
     }
     acc = acc / (float)(hi - lo);
   } else if (repl != nullptr && d < dim) {

@@ -498,140 +498,205 @@ select_kernel_reg(const float* __restrict__ score, const int32_t* __restrict__ s
   }
 }
 
-// Block-per-row form for C = 256 * PER (4096, 8192, 16384 clusters): the 256 threads of a CTA hold
-// one (query, head) score row in registers (PER scores each, four consecutive clusters per 16-byte
-// load), the head's sizes sit in shared memory, and every bisection step is PER predicated adds per
-// thread and one block-wide sum with a single barrier.  A CTA walks ROWS_PER_CTA consecutive queries
-// of one head, so the sizes are staged once.  Same arithmetic as select_kernel: the sums are sums of
-// integers below 2^24 in fp32, exact in any order.
-constexpr int SELECT_CTA_ROWS = 8;
-template <int PER>
-__global__ void __launch_bounds__(256, 2)
-select_kernel_cta(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
-                  int num_kv_heads, float target_tokens, int iters, int force_sink, float key_beta,
-                  int32_t* __restrict__ qmask, int32_t* __restrict__ counts, int32_t* __restrict__ tokens,
-                  int32_t* __restrict__ top1) {
-  constexpr int C = PER * 256;
-  extern __shared__ float s_size[];                       // [C]
-  __shared__ float red_f[2][3][8];                        // alternating buffers: a fast warp's next write
-  __shared__ int red_i[2][8];                             // cannot overtake a slow warp's read
+// Wide form for C = 512 * PER (4096, 8192, 16384 clusters): the 512 threads of a CTA hold ROWS
+// (query, head) score rows at once (PER scores of each per thread, four consecutive clusters per
+// 16-byte load) and the head's sizes once, all in registers; a bisection step is one compare and one
+// predicated fp32 add per cluster and row, and the block-wide sums of all ROWS rows share one barrier.
+// The per-head tables (the 0 / -inf mask of the empty clusters, the size term of the tile key) are made
+// once per CTA, which then walks groups of rows.  Same arithmetic as select_kernel_reg: sums of
+// integers below 2^24 in fp32 are exact in any order (heads with a larger total take integer sums).
+constexpr int SELECT_WIDE_THREADS = 512;
+constexpr int SELECT_WIDE_WARPS = SELECT_WIDE_THREADS / 32;
+template <int PER, int ROWS>
+__global__ void __launch_bounds__(SELECT_WIDE_THREADS, 1)
+select_kernel_wide(const float* __restrict__ score, const int32_t* __restrict__ sizes, int num_queries,
+                   int num_kv_heads, float target_tokens, int iters, int force_sink, float key_beta,
+                   int32_t* __restrict__ qmask, int32_t* __restrict__ counts, int32_t* __restrict__ tokens,
+                   int32_t* __restrict__ top1) {
+  constexpr int T = SELECT_WIDE_THREADS;
+  constexpr int C = PER * T;
+  constexpr int W = SELECT_WIDE_WARPS;
+  extern __shared__ float s_tab[];                         // [2][C]: size term of the key, empty-cluster mask
+  float* s_pen = s_tab;
+  float* s_ninf = s_tab + C;
+  __shared__ float red_f[2][ROWS][3][W];                   // [flip][row][max, min, key][warp]
+  __shared__ int red_i[2][ROWS][W];                        // [flip][row][warp]
+  __shared__ float s_total;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
-  for (int c = tid; c < C; c += 256) s_size[c] = (float)sizes[(int64_t)h * C + c];
-  __syncthreads();
-  int flip = 0;
-  for (int r = 0; r < SELECT_CTA_ROWS; ++r) {
-    const int q = blockIdx.x * SELECT_CTA_ROWS + r;
-    if (q >= num_queries) break;                          // uniform over the CTA
-    const float4* row = reinterpret_cast<const float4*>(score + ((int64_t)q * num_kv_heads + h) * C);
-    float sc[PER];
+  const int32_t* sz = sizes + (int64_t)h * C;
+  float nn[PER];
+  float tot = 0.f;
 #pragma unroll
-    for (int j = 0; j < PER / 4; ++j) {
-      const float4 v = __ldcs(row + j * 256 + tid);       // clusters j * 1024 + 4 tid .. + 3, read once
-      sc[4 * j] = v.x; sc[4 * j + 1] = v.y; sc[4 * j + 2] = v.z; sc[4 * j + 3] = v.w;
+  for (int j = 0; j < PER / 4; ++j) {
+    const int4 n4 = *reinterpret_cast<const int4*>(sz + j * 4 * T + tid * 4);
+    const int ni[4] = {n4.x, n4.y, n4.z, n4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int c = j * 4 * T + tid * 4 + e;
+      const float n = (float)ni[e];
+      nn[4 * j + e] = n;
+      tot += n;
+      s_ninf[c] = n > 0.f ? 0.f : -INFINITY;
+      s_pen[c] = key_beta != 0.f && n > 0.f ? key_beta * __logf(1.0f + n) : 0.f;
     }
-    float mx = -INFINITY, mn = 3.4e38f, tot = 0.f, kmx = -INFINITY;
-    int arg = 0;
+  }
+  tot = warp_sumf(tot);
+  if (lane == 0) red_f[0][0][0][warp] = tot;
+  __syncthreads();
+  if (warp == 0) {
+    const float t = warp_sumf(lane < W ? red_f[0][0][0][lane] : 0.f);
+    if (lane == 0) s_total = t;
+  }
+  __syncthreads();
+  const float row_total = s_total;
+  const bool all_fit = row_total < target_tokens;
+  const bool float_sums = row_total < 16777216.f;
+  const int target_i = (int)target_tokens;
+  int flip = 1;
+  for (int q0 = blockIdx.x * ROWS; q0 < num_queries; q0 += gridDim.x * ROWS) {
+    const int live = min(ROWS, num_queries - q0);          // uniform over the CTA
+    float sc[ROWS][PER];
 #pragma unroll
-    for (int j = 0; j < PER / 4; ++j) {
-      const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
-      const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
+    for (int r = 0; r < ROWS; ++r) {
+      const int q = r < live ? q0 + r : q0;                // rows past the end repeat the first, unwritten
+      const float4* row = reinterpret_cast<const float4*>(score + ((int64_t)q * num_kv_heads + h) * C);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float s = sc[4 * j + e], n = nn[e];
-        const float key = tile_key(s, n, key_beta);
-        if (key > kmx) { kmx = key; arg = j * 1024 + tid * 4 + e; }     // ascending ids: the first maximum stays
-        mx = fmaxf(mx, s);
-        mn = fminf(mn, n > 0.f ? s : 3.4e38f);
-        tot += n > 0.f ? n : 0.f;
+      for (int j = 0; j < PER / 4; ++j) {
+        const float4 v = __ldcs(row + j * T + tid);
+        sc[r][4 * j] = v.x; sc[r][4 * j + 1] = v.y; sc[r][4 * j + 2] = v.z; sc[r][4 * j + 3] = v.w;
       }
     }
-    // block statistics with one barrier
-    mx = warp_max(mx); mn = warp_min(mn); tot = warp_sumf(tot);
-    {
-      const float kbest = warp_max(kmx);
-      int cand = kmx == kbest ? arg : 0x7fffffff;
+    float mx[ROWS], mn[ROWS], kmx[ROWS];
+    int arg[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) { mx[r] = -INFINITY; mn[r] = INFINITY; kmx[r] = -INFINITY; arg[r] = 0; }
+#pragma unroll
+    for (int j = 0; j < PER / 4; ++j) {
+      const float4 p4 = *reinterpret_cast<const float4*>(s_pen + j * 4 * T + tid * 4);
+      const float4 m4 = *reinterpret_cast<const float4*>(s_ninf + j * 4 * T + tid * 4);
+      const float pen[4] = {p4.x, p4.y, p4.z, p4.w}, ninf[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float s = sc[r][4 * j + e];
+          const float key = s + pen[e];
+          if (key > kmx[r]) { kmx[r] = key; arg[r] = j * 4 * T + tid * 4 + e; }   // ascending ids
+          mx[r] = fmaxf(mx[r], s);
+          mn[r] = fminf(mn[r], s - ninf[e]);               // +inf for an empty cluster
+          sc[r][4 * j + e] = s + ninf[e];                  // -inf for an empty cluster
+        }
+    }
+    // block statistics of all rows behind one barrier
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float wmx = warp_max(mx[r]), wmn = warp_min(mn[r]), wk = warp_max(kmx[r]);
+      int cand = kmx[r] == wk ? arg[r] : 0x7fffffff;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
-      if (lane == 0) { red_f[flip][0][warp] = mx; red_f[flip][1][warp] = mn; red_f[flip][2][warp] = tot;
-                       red_i[flip][warp] = cand; s_size[C + 8 * flip + warp] = kbest; }
+      if (lane == 0) {
+        red_f[flip][r][0][warp] = wmx; red_f[flip][r][1][warp] = wmn; red_f[flip][r][2][warp] = wk;
+        red_i[flip][r][warp] = cand;
+      }
     }
     __syncthreads();
-    {
-      float a = lane < 8 ? red_f[flip][0][lane] : -INFINITY, b = lane < 8 ? red_f[flip][1][lane] : 3.4e38f;
-      float c2 = lane < 8 ? red_f[flip][2][lane] : 0.f;
-      mx = warp_max(a); mn = warp_min(b); tot = warp_sumf(c2);
-      if (top1 && warp == 0) {
-        const float kb = lane < 8 ? s_size[C + 8 * flip + lane] : -INFINITY;
+    float lo[ROWS], hi[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float bmx = warp_max(lane < W ? red_f[flip][r][0][lane] : -INFINITY);
+      const float bmn = warp_min(lane < W ? red_f[flip][r][1][lane] : INFINITY);
+      hi[r] = bmx + 1e-6f;
+      lo[r] = fminf(bmn - 1e-6f, hi[r] - 1e-5f);
+      if (top1 && warp == r && r < live) {
+        const float kb = lane < W ? red_f[flip][r][2][lane] : -INFINITY;
         const float kbest = warp_max(kb);
-        int cand = (lane < 8 && kb == kbest) ? red_i[flip][lane] : 0x7fffffff;
+        int cand = (lane < W && kb == kbest) ? red_i[flip][r][lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
-        if (lane == 0) top1[(int64_t)h * num_queries + q] = cand;
+        if (lane == 0) top1[(int64_t)h * num_queries + q0 + r] = cand;
       }
     }
     flip ^= 1;
-    float hi = mx + 1e-6f;
-    float lo = fminf(mn - 1e-6f, hi - 1e-5f);
-    const bool all_fit = tot < target_tokens;
     for (int it = 0; it < iters; ++it) {
-      const float mid = (lo + hi) * 0.5f;
-      float ab[4] = {0.f, 0.f, 0.f, 0.f};              // four independent chains (sums of small integers: exact)
+      float mid[ROWS];
+      int part[ROWS];
 #pragma unroll
-      for (int j = 0; j < PER / 4; ++j) {
-        const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
-        add_if_ge(ab[0], sc[4 * j], mid, n4.x);
-        add_if_ge(ab[1], sc[4 * j + 1], mid, n4.y);
-        add_if_ge(ab[2], sc[4 * j + 2], mid, n4.z);
-        add_if_ge(ab[3], sc[4 * j + 3], mid, n4.w);
-      }
-      float above = warp_sumf((ab[0] + ab[1]) + (ab[2] + ab[3]));
-      if (lane == 0) red_f[flip][0][warp] = above;
-      __syncthreads();
-      above = warp_sumf(lane < 8 ? red_f[flip][0][lane] : 0.f);
-      flip ^= 1;
-      const bool reach = above >= target_tokens;
-      lo = reach ? mid : lo;
-      hi = reach ? hi : mid;
-    }
-    const float theta = all_fit ? NEG_BIG : lo;
-    int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * (C / 32);
-    int n_sel = 0;
-    float n_tok = 0.f;
+      for (int r = 0; r < ROWS; ++r) mid[r] = (lo[r] + hi[r]) * 0.5f;
+      if (float_sums) {
+        float acc[ROWS][2];
 #pragma unroll
-    for (int j = 0; j < PER / 4; ++j) {
-      const float4 n4 = *reinterpret_cast<const float4*>(s_size + j * 1024 + tid * 4);
-      const float nn[4] = {n4.x, n4.y, n4.z, n4.w};
-      unsigned nib = 0;
+        for (int r = 0; r < ROWS; ++r) acc[r][0] = acc[r][1] = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const bool sel = nn[e] > 0.f && sc[4 * j + e] >= theta;
-        nib |= sel ? (1u << e) : 0u;
-        n_sel += sel;
-        n_tok += sel ? nn[e] : 0.f;
-      }
-      // a 32-bit word holds the nibbles of eight consecutive threads
-      unsigned word = nib << (4 * (lane & 7));
-      word |= __shfl_xor_sync(0xffffffffu, word, 1);
-      word |= __shfl_xor_sync(0xffffffffu, word, 2);
-      word |= __shfl_xor_sync(0xffffffffu, word, 4);
-      if (j == 0 && tid == 0 && force_sink) word |= 1u;
-      if ((lane & 7) == 0) qm[j * 32 + (tid >> 3)] = (int32_t)word;
-    }
-    if (counts || tokens) {
-      n_sel = __reduce_add_sync(0xffffffffu, n_sel);
-      n_tok = warp_sumf(n_tok);
-      if (lane == 0) { red_i[flip][warp] = n_sel; red_f[flip][0][warp] = n_tok; }
-      __syncthreads();
-      if (warp == 0) {
-        const int ns = __reduce_add_sync(0xffffffffu, lane < 8 ? red_i[flip][lane] : 0);
-        const float nt = warp_sumf(lane < 8 ? red_f[flip][0][lane] : 0.f);
-        if (lane == 0) {
-          if (counts) counts[(int64_t)q * num_kv_heads + h] = ns;
-          if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)nt;
+        for (int i = 0; i < PER; ++i)
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) add_if_ge(acc[r][i & 1], sc[r][i], mid[r], nn[i]);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) part[r] = (int)(acc[r][0] + acc[r][1]);
+      } else {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          part[r] = 0;
+#pragma unroll
+          for (int i = 0; i < PER; ++i) part[r] += sc[r][i] >= mid[r] ? (int)nn[i] : 0;
         }
       }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        part[r] = __reduce_add_sync(0xffffffffu, part[r]);
+        if (lane == 0) red_i[flip][r][warp] = part[r];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int above = __reduce_add_sync(0xffffffffu, lane < W ? red_i[flip][r][lane] : 0);
+        const bool reach = above >= target_i;
+        lo[r] = reach ? mid[r] : lo[r];
+        hi[r] = reach ? hi[r] : mid[r];
+      }
       flip ^= 1;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (r >= live) break;
+      const int q = q0 + r;
+      const float theta = all_fit ? NEG_BIG : lo[r];
+      int32_t* qm = qmask + ((int64_t)q * num_kv_heads + h) * (C / 32);
+      int n_sel = 0;
+      float n_tok = 0.f;
+#pragma unroll
+      for (int j = 0; j < PER / 4; ++j) {
+        unsigned nib = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const bool sel = sc[r][4 * j + e] >= theta;
+          nib |= sel ? (1u << e) : 0u;
+          n_sel += sel;
+          n_tok += sel ? nn[4 * j + e] : 0.f;
+        }
+        // a 32-bit word holds the nibbles of eight consecutive threads
+        unsigned word = nib << (4 * (lane & 7));
+        word |= __shfl_xor_sync(0xffffffffu, word, 1);
+        word |= __shfl_xor_sync(0xffffffffu, word, 2);
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        if (j == 0 && tid == 0 && force_sink) word |= 1u;
+        if ((lane & 7) == 0) qm[j * (T / 8) + (tid >> 3)] = (int32_t)word;
+      }
+      if (counts || tokens) {
+        n_sel = __reduce_add_sync(0xffffffffu, n_sel);
+        n_tok = warp_sumf(n_tok);
+        if (lane == 0) { red_i[flip][0][warp] = n_sel; red_f[flip][0][0][warp] = n_tok; }
+        __syncthreads();
+        if (warp == 0) {
+          const int ns = __reduce_add_sync(0xffffffffu, lane < W ? red_i[flip][0][lane] : 0);
+          const float nt = warp_sumf(lane < W ? red_f[flip][0][0][lane] : 0.f);
+          if (lane == 0) {
+            if (counts) counts[(int64_t)q * num_kv_heads + h] = ns;
+            if (tokens) tokens[(int64_t)q * num_kv_heads + h] = (int)nt;
+          }
+        }
+        flip ^= 1;
+      }
     }
   }
 }
@@ -712,21 +777,22 @@ extern "C" int semblo_select_clusters(const float* score, const int32_t* select_
   SEMBLO_SELECT_REG(32)
   SEMBLO_SELECT_REG(64)
 #undef SEMBLO_SELECT_REG
-#define SEMBLO_SELECT_CTA(PER)                                                                      \
-  if (num_clusters == PER * 256) {                                                                  \
-    const size_t smem_c = (size_t)(PER * 256 + 16) * 4;                                             \
-    SEMBLO_CUDA(cudaFuncSetAttribute(select_kernel_cta<PER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c)); \
-    dim3 grid_c((unsigned)ceil_div(num_queries, SELECT_CTA_ROWS), num_kv_heads);                    \
-    select_kernel_cta<PER><<<grid_c, 256, smem_c, st_sel>>>(score, select_sizes, num_queries, num_kv_heads, \
-                                                          (float)target_tokens, iters, force_sink,  \
-                                                          tile_key_beta, qmask, counts, tokens, top1); \
+#define SEMBLO_SELECT_WIDE(PER, ROWS)                                                               \
+  if (num_clusters == PER * SELECT_WIDE_THREADS) {                                                  \
+    const size_t smem_w = (size_t)2 * PER * SELECT_WIDE_THREADS * 4;                                \
+    SEMBLO_CUDA(cudaFuncSetAttribute(select_kernel_wide<PER, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_w)); \
+    const int per_head = std::max(1, sm_count() / num_kv_heads);                                    \
+    dim3 grid_w((unsigned)std::min<int64_t>(ceil_div(num_queries, ROWS), per_head), num_kv_heads);  \
+    select_kernel_wide<PER, ROWS><<<grid_w, SELECT_WIDE_THREADS, smem_w, st_sel>>>(                 \
+        score, select_sizes, num_queries, num_kv_heads, (float)target_tokens, iters, force_sink,    \
+        tile_key_beta, qmask, counts, tokens, top1);                                                \
     SEMBLO_LAUNCH_CHECK();                                                                          \
     return 0;                                                                                       \
   }
-  SEMBLO_SELECT_CTA(16)
-  SEMBLO_SELECT_CTA(32)
-  SEMBLO_SELECT_CTA(64)
-#undef SEMBLO_SELECT_CTA
+  SEMBLO_SELECT_WIDE(8, 4)
+  SEMBLO_SELECT_WIDE(16, 4)
+  SEMBLO_SELECT_WIDE(32, 2)
+#undef SEMBLO_SELECT_WIDE
   int warps = 8;
   while (warps > 1 && (size_t)(warps + 1) * num_clusters * 4 > 200 * 1024) warps >>= 1;
   const size_t smem = (size_t)(warps + 1) * num_clusters * 4;
