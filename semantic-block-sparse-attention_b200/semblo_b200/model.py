@@ -219,6 +219,8 @@ class SembloAttention(nn.Module):
         reserve = _arena.suffix_reserve(room)
         extra = dict(reserve=reserve)
         if _flush.enabled():
+            if os.environ.get("SEMBLO_ROUTING_CENTER") == "1":
+                raise RuntimeError("the suffix flush does not re-centre keys (SEMBLO_ROUTING_CENTER=1)")
             if _flush.keep_exact() + _flush.flush_every() > reserve:
                 raise RuntimeError("SEMBLO_SUFFIX_KEEP_EXACT + SEMBLO_SUFFIX_FLUSH_EVERY must not exceed the "
                                    f"suffix reserve ({reserve})")

@@ -21,7 +21,7 @@ def _sink_tokens() -> int:
     return int(os.environ.get("SEMBLO_SINK_TOKENS", "0") or "0")
 
 
-_UNSUPPORTED_ENV = ("SEMBLO_BLOCK_TOKENS", "SEMBLO_FIXED_CODEBOOK", "SEMBLO_ROUTING_CENTER",
+_UNSUPPORTED_ENV = ("SEMBLO_BLOCK_TOKENS", "SEMBLO_FIXED_CODEBOOK",
                     "SEMBLO_FLAT_MIN_TOKENS", "SEMBLO_FLAT_MAX_TOKENS", "SEMBLO_HIER_SPAN",
                     "SEMBLO_PAGE_CLUSTERS", "SEMBLO_FIT_PREFIX_TOKENS")
 
@@ -128,10 +128,19 @@ class ProductPostingIndex:
         assign = torch.empty(num_kv_heads, length, dtype=torch.int32, device=device)
         if per_head_seed and codebook_seed is None:
             raise ValueError("per_head_seed needs a codebook_seed")
+        center = os.environ.get("SEMBLO_ROUTING_CENTER") == "1"
+        if center and centroids is not None:
+            raise RuntimeError("SEMBLO_ROUTING_CENTER re-centres the keys per prompt; given centroids were fitted "
+                               "without it")
         for h in range(num_kv_heads):
             if per_head_seed:
                 generator.manual_seed(int(codebook_seed) + HEAD_SEED_STRIDE * (int(head_offset) + h))
             keys = product_keys[:, h]
+            if center:
+                # state.py:649-670 of the reference: keys without a rotary embedding share one dominant
+                # direction, and after normalisation k-means would put the prompt in one cluster; taking
+                # the prompt's mean key out changes no token's rank under any query
+                keys = (keys.float() - keys.float().mean(dim=0, keepdim=True)).to(keys.dtype)
             _, space_f32, space_bf16 = flat_index._normalize_space(keys)
             if sink:
                 if centroids is None:

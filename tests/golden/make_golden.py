@@ -132,6 +132,28 @@ def main(ref_root: str) -> None:
         out[f"{tag}_sortwalk"] = f32(theta_select_reference(pen, sizes, 256).to(torch.int32))
     os.environ.pop("SEMBLO_SINK_TOKENS", None)
 
+    # ---- the same build with the prompt's mean key taken out (SEMBLO_ROUTING_CENTER=1): keys that
+    # share one dominant direction, as those of a model without a rotary embedding do
+    length, hkv, dim = 1024, 2, 32
+    gd = torch.Generator().manual_seed(123)
+    keys = (mixture_keys(length, hkv, dim, 24, 91, torch.float32)
+            + 6.0 * torch.randn(1, hkv, dim, generator=gd)).to(torch.bfloat16)
+    product = SembloKeyRouter(hkv, dim, dim)(keys.unsqueeze(0))[0]
+    os.environ["SEMBLO_ROUTING_CENTER"] = "1"
+    try:
+        index = ProductPostingIndex.build(
+            product, torch.arange(length), num_centroids=0, kmeans_iters=4, kmeans_sample_size=512,
+            codebook_seed=5, flat_unit_tokens=16, flat_min_clusters_log2=5, page_align=16)
+    finally:
+        os.environ.pop("SEMBLO_ROUTING_CENTER", None)
+    out["c0_keys"] = f32(keys)
+    out["c0_meta"] = np.array([0, length, hkv, dim, index.flat_clusters, 1], dtype=np.int64)
+    out["c0_codebooks"] = f32(index.codebooks)
+    out["c0_posting"] = f32(index.posting_positions)
+    out["c0_indptr"] = f32(index.bucket_indptr)
+    out["c0_sizes"] = f32(index.bucket_sizes)
+    out["c0_inverse"] = f32(index.inverse_positions())
+
     # ---- k-means pieces -----------------------------------------------------------
     xs = torch.nn.functional.normalize(torch.randn(700, 48, generator=g), dim=-1)
     cs = torch.nn.functional.normalize(torch.randn(40, 48, generator=g), dim=-1)

@@ -198,6 +198,43 @@ def test_pack_and_snapshot_are_bit_identical(dev):
         assert torch.equal(got, want)
 
 
+def test_centred_build(dev):
+    """SEMBLO_ROUTING_CENTER=1: the prompt's mean key is taken out per head before the space is
+    normalised (state.py:649-670 of the reference); given centroids are refused with it."""
+    from semblo_b200.state import ProductPostingIndex
+    length, heads, dim = 4096, 2, 128
+    g = torch.Generator().manual_seed(5)
+    keys = O.mixture_inputs(length=length, num_q_heads=heads, num_kv_heads=heads, head_dim=dim, centres=20,
+                            seed=13)["k_pre"]
+    keys = (keys.float() + 6.0 * torch.randn(1, heads, dim, generator=g)).to(torch.bfloat16)   # one dominant direction
+    product = O.routing_normalize(keys)
+    env = dict(SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_ROUTING_CENTER="1")
+    os.environ.update(env)
+    try:
+        kw = dict(flat_unit_tokens=32, flat_min_clusters_log2=6, page_align=16, kmeans_sample_size=1024, codebook_seed=3)
+        index = ProductPostingIndex.build(product.to(dev), torch.arange(length, device=dev), **kw)
+        with pytest.raises(RuntimeError):
+            ProductPostingIndex.build(product.to(dev), torch.arange(length, device=dev),
+                                      centroids=[_unit(128, dim, 1).to(dev)] * heads, **kw)
+        os.environ.pop("SEMBLO_ROUTING_CENTER")
+        plain = ProductPostingIndex.build(product.to(dev), torch.arange(length, device=dev), **kw)
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+    _status_ok(dev)
+    clusters = int(index.num_buckets)
+    assert int((plain.bucket_sizes > 0).sum()) < int((index.bucket_sizes > 0).sum())
+    # the oracle's assignment of the centred keys to the kernel's own centroids
+    cents = [torch.cat([index.codebooks[h, 0], index.codebooks[h, 1]], dim=-1).cpu().float() for h in range(heads)]
+    ref = O.build_flat(product, unit_tokens=32, min_clusters_log2=6, page_align=16, centroids=cents, center=True)
+    assign = index.orig_bucket.cpu().long()
+    assert float((assign != ref.assign).float().mean()) < 1e-2
+    for h in range(heads):
+        order, ip, counts, inv = O.layout_from_assign(assign[h], clusters, 16)
+        assert torch.equal(index.bucket_sizes[h].cpu(), counts)
+        assert torch.equal(index.posting_positions[h, :order.numel()].cpu(), order)
+
+
 # ---------------------------------------------------------------------- scoring + selection
 def _small_problem(length, hq, hkv, dim, centres, seed, unit, min_log2, sink):
     data = O.mixture_inputs(length=length, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=centres, seed=seed)

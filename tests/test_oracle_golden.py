@@ -58,6 +58,24 @@ def test_index_build_is_bit_identical(golden, tag):
         assert torch.equal(O.causal_sizes_at(index, p), T(want).int())
 
 
+def test_centred_index_build_is_bit_identical(golden):
+    """SEMBLO_ROUTING_CENTER=1 (state.py:649-670): the prompt's mean key is taken out per head."""
+    sink, length, hkv, dim, clusters, _ = golden["c0_meta"].tolist()
+    keys = T(golden["c0_keys"], torch.bfloat16)
+    product = O.routing_normalize(keys)
+    index = O.build_flat(product, unit_tokens=16, min_clusters_log2=5, kmeans_sample_size=512, seed=5,
+                         sink=sink, page_align=16, center=True)
+    assert torch.equal(index.codebooks.float(), T(golden["c0_codebooks"]))
+    assert torch.equal(index.bucket_sizes, T(golden["c0_sizes"]).int())
+    assert torch.equal(index.bucket_indptr, T(golden["c0_indptr"]).int())
+    assert torch.equal(index.posting_positions, T(golden["c0_posting"]).int())
+    assert torch.equal(index.inverse_positions, T(golden["c0_inverse"]).int())
+    # without centring the same keys crowd into fewer clusters and leave the others empty
+    plain = O.build_flat(product, unit_tokens=16, min_clusters_log2=5, kmeans_sample_size=512, seed=5,
+                         sink=sink, page_align=16)
+    assert int((plain.bucket_sizes > 0).sum()) < int((index.bucket_sizes > 0).sum())
+
+
 @pytest.mark.parametrize("tag", ["b0", "b1", "b2"])
 def test_scores_and_sort_walk_selector(golden, tag):
     sink, length, hkv, dim, clusters, _ = golden[f"{tag}_meta"].tolist()
