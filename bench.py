@@ -522,7 +522,9 @@ def head_sharded_measure(device, rank, world, pk, steps=2, warmup=1, length=None
     step.attended.zero_()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    index = None
     for _ in range(steps):
+        index = None                 # the previous step's index is dropped before the next one is built
         index = step.run(xp, out)
     e1.record()
     barrier()
@@ -874,7 +876,9 @@ def main():
     barrier()
     e0.record()
     marks = [e0]
+    index = None
     for _ in range(args.steps):
+        index = None                 # the previous step's index is dropped before the next one is built
         index = step.run(x, out)
         marks.append(torch.cuda.Event(enable_timing=True))
         marks[-1].record()
