@@ -156,7 +156,7 @@ class PrefillStep:
         if self.windows_ahead and not self.time_attention:
             window = WindowAhead(x["q_post"], self.positions32, x["k_post"], x["v"], chunk=chunk,
                                  target_tokens=cfg["target"], sm_scale=sm_scale, out=out, attended=self.attended,
-                                 ahead=16, before_launch=before_chunk)
+                                 ahead=16, before_launch=before_chunk, router_input=x["q_pre"])
         product = routing_normalize(x["k_pre"])
         index = ProductPostingIndex.build(product, self.positions, kmeans_sample_size=8192, codebook_seed=0,
                                           flat_unit_tokens=cfg["unit"], flat_min_clusters_log2=cfg["min_log2"],
@@ -177,8 +177,11 @@ class PrefillStep:
             n = ce - cs + 1
             if before_chunk is not None:
                 before_chunk(cs, ce)
-            qv = trivial_router_vectors(x["q_pre"][cs:ce + 1])
-            state = SimpleNamespace(vectors=qv.view(1, n, hq, 1, dim))
+            if window is not None:
+                state = SimpleNamespace(vectors=window.vectors_for(cs))        # made ahead; None for a dense chunk
+            else:
+                qv = trivial_router_vectors(x["q_pre"][cs:ce + 1])
+                state = SimpleNamespace(vectors=qv.view(1, n, hq, 1, dim))
             fused_chunk_attention(x["q_post"][cs:ce + 1], state, index, self.positions32[cs:ce + 1], snap, cs, ce,
                                   temperature=cfg["temperature"], beta=cfg["beta"], target_tokens=cfg["target"],
                                   sm_scale=sm_scale, out=out[cs:ce + 1], attended=self.attended, window=window,

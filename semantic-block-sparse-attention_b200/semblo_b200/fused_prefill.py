@@ -177,7 +177,7 @@ class WindowAhead:
 
     def __init__(self, q: torch.Tensor, q_positions: torch.Tensor, ordered_k: torch.Tensor, ordered_v: torch.Tensor, *,
                  chunk: int, target_tokens: int, sm_scale: float, out: torch.Tensor, dense_prefix_x: int = 4,
-                 attended=None, ahead: int = 16, before_launch=None) -> None:
+                 attended=None, ahead: int = 16, before_launch=None, router_input: torch.Tensor | None = None) -> None:
         self.q, self.pos, self.k, self.v, self.out = q, q_positions, ordered_k, ordered_v, out
         self.chunk, self.target, self.sm_scale, self.x = int(chunk), int(target_tokens), float(sm_scale), dense_prefix_x
         self.attended, self.before_launch = attended, before_launch
@@ -189,6 +189,12 @@ class WindowAhead:
         hq, d = int(q.shape[1]), int(q.shape[2])
         self.partial = torch.empty(slots, self.chunk, hq, d, dtype=torch.float32, device=q.device)
         self.lse = torch.empty(slots, self.chunk, hq, dtype=torch.float32, device=q.device)
+        # the routing vectors of a sparse chunk need no index either: with ``router_input`` ([n, Hq, D]
+        # pre-RoPE queries) they are made ahead too, in front of the chunk's window launch
+        self.router_input = router_input
+        self.vectors = None if router_input is None else torch.empty(slots, self.chunk, hq, router_input.shape[2],
+                                                                     dtype=router_input.dtype, device=q.device)
+        self.routed: dict = {}          # chunk start -> event recorded behind its routing vectors
         self.done: dict = {}            # chunk start -> event recorded behind its launch
         self.slot_of: dict = {}
         self.free = [(s, None) for s in range(slots)]     # (slot, event after which it may be rewritten)
@@ -218,6 +224,12 @@ class WindowAhead:
                     if reusable is not None:
                         self.stream.wait_event(reusable)
                     n = ce - cs + 1
+                    if self.vectors is not None:
+                        from .trivial_router import trivial_router_vectors
+                        trivial_router_vectors(self.router_input[cs:ce + 1], out=self.vectors[slot, :n])
+                        ev = torch.cuda.Event()
+                        ev.record(self.stream)
+                        self.routed[cs] = ev
                     with _attend_part("semblo::attend_current_chunk"):
                         window_attention(self.q[cs:ce + 1], self.pos[cs:ce + 1], ordered_k=k_w, ordered_v=v_w,
                                          ordered_pos0=wstart, local_start=wstart, sm_scale=self.sm_scale,
@@ -228,6 +240,23 @@ class WindowAhead:
                 ev.record(self.stream)
                 self.done[cs] = ev
             self.issued += 1
+
+    def is_dense(self, chunk_start: int) -> bool:
+        return chunk_window_start(chunk_start, self.target, self.x) == 0
+
+    def vectors_for(self, chunk_start: int):
+        """Routing vectors [1, n, Hq, 1, D] of a sparse chunk made ahead (the calling stream waits for
+        them), or None for a dense-prefix chunk."""
+        if self.vectors is None:
+            raise RuntimeError("no router input was given")
+        if self.is_dense(chunk_start):
+            return None
+        if chunk_start not in self.routed:
+            self._issue(self.starts.index(chunk_start) + 1)
+        torch.cuda.current_stream(self.q.device).wait_event(self.routed.pop(chunk_start))
+        n = min(int(self.q.shape[0]), chunk_start + self.chunk) - chunk_start
+        v = self.vectors[self.slot_of[chunk_start], :n]
+        return v.view(1, n, v.shape[1], 1, v.shape[2])
 
     def take(self, chunk_start: int):
         """The calling stream waits for the chunk's launch; returns (partial, lse) or None (dense prefix)."""
@@ -276,12 +305,12 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if window is not None:
         if local_kv is not None:
             raise RuntimeError("windows issued ahead read the prompt-order K/V, not rows handed over per call")
-        ahead = window.take(chunk_start)
-        if (ahead is None) != (wstart == 0):
+        if window.is_dense(chunk_start) != (wstart == 0):
             raise RuntimeError("the windows issued ahead were planned with another budget or window")
         if out is not None and out.data_ptr() != window.out[chunk_start:chunk_end + 1].data_ptr():
             raise RuntimeError("the windows issued ahead write into their own output buffer: pass its rows as out")
         if wstart == 0:
+            window.take(chunk_start)
             return window.out[chunk_start:chunk_end + 1]
         k_loc = v_loc = None
         pos0 = 0
@@ -360,7 +389,7 @@ def fused_chunk_attention(q_chunk: torch.Tensor, query_state, index, q_positions
     if _timer:
         _timer("start")
     if window is not None:
-        partial, lse = ahead
+        partial, lse = window.take(chunk_start)            # waited for only now: scoring and selection need no window
     else:
         lse = snap.lse[:q_count]
         partial = snap.partial[:q_count]

@@ -319,7 +319,10 @@ class SembloAttention(nn.Module):
         for start in range(0, n_queries, step):
             end = min(n_queries, start + step)
             q_positions = positions[start:end].to(torch.int32)
-            query_state = self._query_state(q_pre[start:end], source)
+            if window is not None and window.vectors is not None:
+                query_state = SimpleNamespace(vectors=window.vectors_for(start), mixture_weights=None)
+            else:
+                query_state = self._query_state(q_pre[start:end], source)
             if fused_snapshot is None:
                 fused_snapshot = getattr(index, "_token_outer_snapshot", None) or _fused_prefill.CausalSnapshot(index)
             _fused_prefill.fused_chunk_attention(
@@ -378,7 +381,8 @@ class SembloAttention(nn.Module):
             window = _fused_prefill.WindowAhead(
                 q3, positions.to(torch.int32), k_post.view(-1, self.num_kv_heads, self.head_dim),
                 v_states.view(-1, self.num_kv_heads, self.head_dim), chunk=self.runtime_config.query_chunk_size,
-                target_tokens=int(self._target_for_step(False)), sm_scale=self.scaling, out=out3, dense_prefix_x=4)
+                target_tokens=int(self._target_for_step(False)), sm_scale=self.scaling, out=out3, dense_prefix_x=4,
+                router_input=q_pre.view(-1, self.num_heads, self.head_dim))
             self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
             self._run_product_attention(q_post, q_pre, positions, out=output, window=window)
         caller.wait_stream(chain)
