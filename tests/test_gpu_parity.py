@@ -439,6 +439,62 @@ def test_argsort_and_top1_keys(dev):
         assert torch.equal(got, want)
 
 
+def test_launches_issued_ahead_give_the_same_bytes(dev):
+    """fused_prefill.WindowAhead: the dense-prefix chunks, the windows and the routing vectors made
+    ahead on a second stream, with fewer buffers than chunks so that every buffer is used again."""
+    from types import SimpleNamespace
+    from semblo_b200.fused_prefill import CausalSnapshot, WindowAhead, fused_chunk_attention
+    from semblo_b200.trivial_router import trivial_router_vectors
+    dim, hq, hkv, sink, length, target, local, chunk = 128, 8, 2, 64, 6144, 128, 128, 512
+    data, index = _small_problem(length, hq, hkv, dim, 24, 9, 32, 7, sink)
+    gi = _gpu_index(index, dev)
+    q, qp = data["q_post"].to(dev), data["q_pre"].to(dev)
+    k, v = data["k_post"].to(dev), data["v"].to(dev)
+    pos = torch.arange(length, dtype=torch.int32, device=dev)
+    os.environ["SEMBLO_SINK_TOKENS"] = str(sink)
+    os.environ["SEMBLO_FA3_LOCAL"] = str(local)
+    sm_scale = dim ** -0.5
+    try:
+        outs = []
+        for ahead in (0, 2, 16):
+            gi.original_kv = (k, v)
+            snap = CausalSnapshot(gi)
+            out = torch.zeros(length, hq, dim, dtype=torch.bfloat16, device=dev)
+            window = None
+            if ahead:
+                window = WindowAhead(q, pos, k, v, chunk=chunk, target_tokens=target, sm_scale=sm_scale, out=out,
+                                     ahead=ahead, router_input=qp)
+                assert window.partial.shape[0] == min(ahead, 10)        # 12 chunks, the first two are dense
+            for cs in range(0, length, chunk):
+                ce = cs + chunk - 1
+                if window is not None:
+                    vec = window.vectors_for(cs)
+                    assert (vec is None) == (cs <= 4 * target)
+                else:
+                    vec = trivial_router_vectors(qp[cs:ce + 1]).view(1, chunk, hq, 1, dim)
+                fused_chunk_attention(q[cs:ce + 1], SimpleNamespace(vectors=vec), gi, pos[cs:ce + 1], snap, cs, ce,
+                                      temperature=0.1, beta=0.25, target_tokens=target, sm_scale=sm_scale,
+                                      out=out[cs:ce + 1], window=window)
+            if window is not None:
+                window.finish()
+            torch.cuda.synchronize()
+            _status_ok(dev)
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        # a window planned with another budget is refused
+        window = WindowAhead(q, pos, k, v, chunk=chunk, target_tokens=4 * target, sm_scale=sm_scale,
+                             out=torch.empty_like(outs[0]), ahead=2)
+        with pytest.raises(RuntimeError):
+            fused_chunk_attention(q[1024:1536], SimpleNamespace(vectors=None), gi, pos[1024:1536], CausalSnapshot(gi),
+                                  1024, 1535, temperature=0.1, beta=0.25, target_tokens=target, sm_scale=sm_scale,
+                                  out=window.out[1024:1536], window=window)
+        window.finish()
+        torch.cuda.synchronize()
+    finally:
+        os.environ.pop("SEMBLO_SINK_TOKENS", None)
+        os.environ.pop("SEMBLO_FA3_LOCAL", None)
+
+
 def test_prefill_chunk_loop_end_to_end(dev):
     """The reference's chunk loop (dense prefix chunks, then selection + sparse body) through the
     mirrored Python entry points, against the oracle evaluated on the kernel's own selections."""
