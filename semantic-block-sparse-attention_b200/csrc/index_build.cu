@@ -171,9 +171,11 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int64_t*
 }
 
 // ------------------------------------------------------------------ assignment GEMM
-// One CTA owns 128 rows of x and streams the codebook in chunks of 128 centroids.
-// warp 4: TMA producer, warp 5: UMMA issuer, warps 0-3: epilogue (thread = row).
-constexpr int ASG_BN = 128;        // centroids per chunk
+// One CTA owns 128 rows of x and streams the codebook in chunks of 64 centroids: two accumulators
+// and the key tile then take 256 columns of tensor memory, so two CTAs share a multiprocessor and
+// one's epilogue runs under the other's products.
+// warp 4: TMA producer, warp 5: UMMA issuer, warps 0-3 and 6-9: epilogue (two threads per row).
+constexpr int ASG_BN = 64;         // centroids per chunk
 constexpr int ASG_STAGES = 2;
 
 template <int D>
@@ -183,7 +185,7 @@ struct AssignSmem {
   static constexpr int B_BYTES = ASG_BN * D * 2;
   static constexpr int BAR_OFF = A_BYTES + ASG_STAGES * B_BYTES;
   static constexpr int X_COL = 2 * ASG_BN;           // TMEM: two accumulators, then the keys
-  static constexpr int TMEM_COLS = A_TMEM ? 512 : 256;
+  static constexpr int TMEM_COLS = (A_TMEM && X_COL + D / 2 > 256) ? 512 : 256;
   static constexpr int XCHG_OFF = BAR_OFF + 256;       // (value, id) of the upper-half epilogue threads: [128] float + [128] int
   static constexpr int TOTAL = XCHG_OFF + 1024 + 1024; // + alignment slack
 };
@@ -192,7 +194,7 @@ struct AssignSmem {
 // half) instead of [C][D], the similarity is compared in fp32 as it comes out of the tensor
 // core (no bf16 rounding), and centroids whose bit is set in dead_bits are never chosen.
 template <int D, bool SPLIT>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(320, 2)
 assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bfloat16* __restrict__ x,
                      int64_t x_stride,
                      const __grid_constant__ CUtensorMap tmap_c, int64_t n, int num_centroids,
@@ -310,11 +312,11 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bflo
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c4 = 0; c4 < ASG_BN / 64; ++c4) {
+      for (int c4 = 0; c4 < ASG_BN / 64; ++c4) {   // each of a row's two threads takes half of the chunk
         uint32_t r[32];
-        tmem_ld32(tmem_base + lane_addr + b * ASG_BN + hf * 64 + c4 * 32, r);
+        tmem_ld32(tmem_base + lane_addr + b * ASG_BN + hf * (ASG_BN / 2) + c4 * 32, r);
         tmem_ld_wait();
-        const int cbase = j * ASG_BN + hf * 64 + c4 * 32;
+        const int cbase = j * ASG_BN + hf * (ASG_BN / 2) + c4 * 32;
         uint32_t dead = 0u;
         if (SPLIT && dead_bits != nullptr && cbase < num_centroids) dead = __ldg(dead_bits + (cbase >> 5));
         if (full && dead == 0u) {
@@ -683,11 +685,12 @@ int launch_assign(const void* x, int64_t n, int64_t x_stride_elems, const void* 
   if (SPLIT) {
     uint64_t dc[3] = {(uint64_t)D / 2, (uint64_t)num_centroids, 2};
     uint64_t sc[2] = {(uint64_t)D, (uint64_t)num_centroids * D};          // bytes: row, half
-    uint32_t bc[3] = {64, 128, 1};
+    uint32_t bc[3] = {64, (uint32_t)ASG_BN, 1};
     rc = semblo::make_tensor_map_bf16(&mc, cent, 3, dc, sc, bc);
   } else {
     uint64_t dc[2] = {(uint64_t)D, (uint64_t)num_centroids}, sc[1] = {(uint64_t)D * 2};
-    rc = semblo::make_tensor_map_bf16(&mc, cent, 2, dc, sc, box);
+    uint32_t bc2[2] = {64, (uint32_t)ASG_BN};
+    rc = semblo::make_tensor_map_bf16(&mc, cent, 2, dc, sc, bc2);
   }
   if (rc) return rc;
   auto kern = assign_argmax_kernel<D, SPLIT>;
