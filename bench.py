@@ -51,7 +51,10 @@ PREFILL = dict(length=131072, hq=16, hkv=4, dim=256, centres=256, unit=64, min_l
                sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16)
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one-pass ncu captures of this file's own
 # command, keyed by (kernel, prompt length): a record of a past capture, not something a run produces
-DRAM_TRAFFIC_PER_LAUNCH = {("sparse_gather_prefill_kernel<256,4>", 131072): 1.094e9}
+DRAM_TRAFFIC_PER_LAUNCH = {("sparse_gather_prefill_kernel<256,4>", 131072): 1.094e9,
+                           ("decode_attend_kernel<256,4>", 524288): 17.78e6,
+                           ("decode_score_kernel<256,4>", 524288): 16.85e6,
+                           ("decode_select_kernel", 524288): 0.84e6}
 
 HEAD_SHARDED = dict(length=1048576, hq=32, hkv=8, dim=128, centres=1024, unit=64, min_log2=7, target=8192,
                     sink=128, local=512, chunk=8192, temperature=0.1, beta=0.25, page=16, reserve=1024,
@@ -443,10 +446,12 @@ def decode_measure(device, pk):
         "selected_rows": n_rows, "gathered_bytes": gathered, "codebook_bytes": codebook,
         "roofline_attend": {"bound": "hbm", "achieved": gathered / (med(attend_us) * 1e-6) / 1e9, "peak": pk["hbm"],
                             "unit": "GB/s", "frac": gathered / (med(attend_us) * 1e-6) / 1e9 / pk["hbm"],
-                            "traffic": None},
+                            "traffic": DRAM_TRAFFIC_PER_LAUNCH.get(("decode_attend_kernel<256,4>", L))},
         "roofline_step": {"bound": "hbm", "achieved": (gathered + codebook) / (med(graph_us) * 1e-6) / 1e9,
                           "peak": pk["hbm"], "unit": "GB/s",
-                          "frac": (gathered + codebook) / (med(graph_us) * 1e-6) / 1e9 / pk["hbm"], "traffic": None},
+                          "frac": (gathered + codebook) / (med(graph_us) * 1e-6) / 1e9 / pk["hbm"],
+                          "traffic": sum(DRAM_TRAFFIC_PER_LAUNCH.get((k, L), 0.0) for k in (
+                              "decode_score_kernel<256,4>", "decode_select_kernel", "decode_attend_kernel<256,4>")) or None},
     }
 
 
