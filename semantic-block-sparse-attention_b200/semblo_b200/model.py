@@ -34,6 +34,7 @@ from .attention_op import register_layer, sparse_attention_op
 from .config import SembloVllmConfig
 from .decode_graph import DecodeStepGraph, tensor_signature
 from .paged_attention import PostingTiles, merge_paged_attention_results, paged_posting_attention
+from .routing_map import SembloKeyRouter
 from .flat_index import routing_normalize
 from .state import ProductPostingIndex, SembloRuntimeState
 from .trivial_router import trivial_router_vectors
@@ -51,7 +52,8 @@ class SembloAttention(nn.Module):
         if attention_logits_soft_cap:
             raise RuntimeError("the fused sparse path has no logit soft cap")
         if int(runtime_config.index_dim) != int(self.head_dim):
-            raise RuntimeError("the routing map is the identity: index_dim must equal head_dim")
+            raise RuntimeError("the kernels route in a space of the head dimension: index_dim must equal head_dim "
+                               "(the identity map, or a loaded square map)")
         self.layer_idx = int(layer_idx)
         self.source_layer_idx = int(source_layer_idx)
         self.uses_sparse_attention = bool(uses_sparse_attention)
@@ -70,6 +72,9 @@ class SembloAttention(nn.Module):
         if not hasattr(self, "is_kv_shared_layer"):
             self.is_kv_shared_layer = False
         if self.builds_product_index:
+            # the routing map of this layer's keys and of the queries of every layer that reads its index:
+            # the identity until a map is loaded into ``semblo_key_router.weight``
+            self.semblo_key_router = SembloKeyRouter(self.num_kv_heads, self.head_dim, int(runtime_config.index_dim))
             runtime_state.register_source_module(self.layer_idx, self)
         layer_name = getattr(getattr(self, "attn", None), "layer_name", None)
         if layer_name is not None:
@@ -106,18 +111,29 @@ class SembloAttention(nn.Module):
             raise RuntimeError("only layers with their own K/V can build an index")
         if self.runtime_state.step_first_position != 0:
             return self.runtime_state.get(self.source_layer_idx)
-        # SembloKeyRouter with the identity map: unit-normalise the whole key (routing_map.py:35-94)
-        product = routing_normalize(k_pre_rope.view(-1, self.num_kv_heads, self.head_dim))
+        # SembloKeyRouter (routing_map.py:35-94): the map, then unit-normalise the whole vector
+        router = self._router(k_pre_rope.device)
+        keys = k_pre_rope.view(-1, self.num_kv_heads, self.head_dim)
+        product = routing_normalize(keys) if router.is_identity() else router(keys[None])[0]
         index = self._fit_index(product, positions)
         self.runtime_state.put(self.source_layer_idx, index)
         return index
 
+    def _router(self, device) -> SembloKeyRouter:
+        router = self.semblo_key_router
+        if router.weight.device != torch.device(device):
+            router.to(device)
+        return router
+
     def _query_state(self, q_pre_rope: torch.Tensor, source: "SembloAttention"):
-        """Routing vectors of [Q, Hq, D] pre-RoPE queries: one per head, uniform mixture."""
+        """Routing vectors of [Q, Hq, D] pre-RoPE queries: a query goes through the map of its KV head
+        in the source layer and is normalised like the keys; one per head, uniform mixture."""
         if (os.environ.get("SEMBLO_ROUTING_NORMALIZE", "whole") or "whole") != "whole":
             raise RuntimeError("only SEMBLO_ROUTING_NORMALIZE=whole is implemented")
         queries, heads, dim = q_pre_rope.shape
-        vectors = trivial_router_vectors(q_pre_rope).view(1, queries, heads, 1, dim)
+        router = source._router(q_pre_rope.device)
+        projected = q_pre_rope if router.is_identity() else router.project_queries(q_pre_rope).contiguous()
+        vectors = trivial_router_vectors(projected).view(1, queries, heads, 1, dim)
         return SimpleNamespace(vectors=vectors, mixture_weights=None)
 
     # ---- one generated token without an arena ------------------------------------------------
@@ -221,6 +237,8 @@ class SembloAttention(nn.Module):
         if _flush.enabled():
             if os.environ.get("SEMBLO_ROUTING_CENTER") == "1":
                 raise RuntimeError("the suffix flush does not re-centre keys (SEMBLO_ROUTING_CENTER=1)")
+            if not self._router(like.device).is_identity():
+                raise RuntimeError("the suffix flush assigns by the keys themselves: it serves the identity routing map")
             if _flush.keep_exact() + _flush.flush_every() > reserve:
                 raise RuntimeError("SEMBLO_SUFFIX_KEEP_EXACT + SEMBLO_SUFFIX_FLUSH_EVERY must not exceed the "
                                    f"suffix reserve ({reserve})")
@@ -255,6 +273,11 @@ class SembloAttention(nn.Module):
             raise RuntimeError("physical sparse layers must produce K/V")
         self._effective_target = self._target_for_step(True)
         shared = self.is_kv_shared_layer
+        source = self._source_module()
+        given = not source._router(q_post.device).is_identity()
+        if given:                                     # a loaded map: the step is handed the routing vectors
+            q_pre = self._query_state(q_pre.view(-1, self.num_heads, self.head_dim), source).vectors \
+                .view(-1, self.num_heads, self.head_dim).contiguous()
         _fused_decode.fused_decode_step(
             self, arena, q_post=q_post, q_pre=q_pre, positions=positions,
             k_post=None if shared else k_post.view(-1, self.num_kv_heads, self.head_dim),
@@ -262,7 +285,7 @@ class SembloAttention(nn.Module):
             k_pre=None if shared or k_pre is None else k_pre.view(-1, self.num_kv_heads, self.head_dim),
             output=output, temperature=self.runtime_config.selection_temperature,
             beta=self.runtime_config.bucket_size_penalty, target_tokens=int(self._effective_target),
-            sm_scale=self.scaling, num_splits=self.runtime_config.packed_decode_num_splits * 2)
+            sm_scale=self.scaling, num_splits=self.runtime_config.packed_decode_num_splits * 2, vectors_given=given)
 
     # ---- prompt --------------------------------------------------------------------------
     def _ingest_prompt_kv(self, k_post, v_states, k_pre, positions, *, prompt_order_views: bool = True) -> None:
@@ -382,7 +405,8 @@ class SembloAttention(nn.Module):
                 q3, positions.to(torch.int32), k_post.view(-1, self.num_kv_heads, self.head_dim),
                 v_states.view(-1, self.num_kv_heads, self.head_dim), chunk=self.runtime_config.query_chunk_size,
                 target_tokens=int(self._target_for_step(False)), sm_scale=self.scaling, out=out3, dense_prefix_x=4,
-                router_input=q_pre.view(-1, self.num_heads, self.head_dim))
+                router_input=q_pre.view(-1, self.num_heads, self.head_dim)
+                if self._source_module()._router(dev).is_identity() else None)
             self._ingest_prompt_kv(k_post, v_states, k_pre, positions)
             self._run_product_attention(q_post, q_pre, positions, out=output, window=window)
         caller.wait_stream(chain)
@@ -482,6 +506,8 @@ class LayerTokenOuterSession:
         from .token_outer import TokenOuterPrefillSession
         self.layer = layer
         cfg = layer.runtime_config
+        if not layer._router(positions.device).is_identity():
+            raise RuntimeError("the token-outer prefill assigns by the keys themselves: it serves the identity routing map")
         self.rope_positions, self.flat = layer._positions_for_runtime(positions)
         layer.runtime_state.maybe_begin_prompt(layer.layer_idx, self.flat)
         self.inner = TokenOuterPrefillSession(

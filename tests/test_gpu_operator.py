@@ -309,6 +309,67 @@ def test_streamed_sessions_through_the_layer(dev):
             os.environ.pop(k, None)
 
 
+@pytest.mark.parametrize("arena_mode", [True, False])
+def test_loaded_routing_map(dev, arena_mode):
+    """A square linear routing map (routing_map.py:67-94, model.py:432-489 of the reference): keys and
+    queries go through it before they are normalised.  The layer with the map loaded gives the bytes of
+    a layer with the identity map that is handed the projected pre-RoPE tensors, prompt and decode."""
+    from semblo_b200 import _lib
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.state import SembloRuntimeState
+    dim, hq, hkv, sink, length, target, local, chunk, steps = 128, 8, 2, 64, 4096, 256, 128, 1024, 4
+    cpu = O.mixture_inputs(length=length + steps, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=31)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL=str(local), SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16")
+    if arena_mode:
+        env["SEMBLO_FULL_GRAPH_DECODE"] = "1"
+    os.environ.update(env)
+    if not arena_mode:
+        os.environ.pop("SEMBLO_FULL_GRAPH_DECODE", None)
+    try:
+        mapped = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192 + 512),
+                             name=f"model.layers.{5 + arena_mode}.self_attn.attn")
+        g = torch.Generator().manual_seed(3)
+        w = torch.linalg.qr(torch.randn(hkv, dim, dim, generator=g))[0] + 0.05 * torch.randn(hkv, dim, dim, generator=g)
+        mapped.semblo_key_router.load_weight(w)
+        router = mapped._router(dev)
+        assert not router.is_identity()
+        projected = dict(data)
+        projected["k_pre"] = router.project(data["k_pre"]).contiguous()
+        projected["q_pre"] = router.project_queries(data["q_pre"]).contiguous()
+        plain = _make_layer(projected, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg,
+                            state=SembloRuntimeState(max_model_len=8192 + 512), name=f"model.layers.{7 + arena_mode}.self_attn.attn")
+        assert plain._router(dev).is_identity()
+        positions = torch.arange(length, device=dev)
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        a = mapped._sparse_layer_forward(positions, hidden)
+        b = plain._sparse_layer_forward(positions, hidden)
+        torch.cuda.synchronize()
+        _lib.status_for(dev).raise_if_set()
+        assert torch.equal(a, b)
+        assert torch.equal(mapped.runtime_state.get(0).bucket_sizes, plain.runtime_state.get(0).bucket_sizes)
+        # and not the partition of the unprojected keys
+        third = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192 + 512),
+                            name=f"model.layers.{9 + arena_mode}.self_attn.attn")
+        third._sparse_layer_forward(positions, hidden)
+        assert not torch.equal(third.runtime_state.get(0).bucket_sizes, plain.runtime_state.get(0).bucket_sizes)
+        pa, pb = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+        for s_ in range(steps):
+            pa.fill_(length + s_)
+            pb.fill_(length + s_)
+            oa = mapped._sparse_layer_forward(pa, hidden[:1]).clone()
+            ob = plain._sparse_layer_forward(pb, hidden[:1]).clone()
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            assert torch.equal(oa, ob), s_
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
 def test_operator_refuses_what_it_does_not_serve(dev):
     from semblo_b200.attention_op import registered_layer
     from semblo_b200.config import SembloVllmConfig

@@ -140,3 +140,26 @@ def test_gather_form_of_the_prefill_body_agrees_with_the_masked_form():
                                           data["k_post"][ws:ce + 1], data["v"][ws:ce + 1], ws, 32 ** -0.5,
                                           dtype=torch.float64)
     torch.testing.assert_close(got, want, atol=1e-9, rtol=1e-9)
+
+
+def test_routing_map_projection_and_identity_detection():
+    """routing_map.SembloKeyRouter (routing_map.py:67-94 of the reference): identity by default, a query
+    goes through the map of its KV head, and a loaded weight is noticed."""
+    from semblo_b200.routing_map import SembloKeyRouter
+    hkv, hq, dim = 2, 8, 16
+    router = SembloKeyRouter(hkv, dim, dim)
+    assert router.is_identity()
+    g = torch.Generator().manual_seed(0)
+    keys = torch.randn(5, hkv, dim, generator=g)
+    queries = torch.randn(7, hq, dim, generator=g)
+    assert torch.equal(router.project(keys), keys) and torch.equal(router.project_queries(queries), queries)
+    w = torch.randn(hkv, dim, dim, generator=g)
+    router.load_weight(w)
+    assert not router.is_identity()
+    torch.testing.assert_close(router.project(keys), torch.einsum("lhd,hid->lhi", keys, w))
+    want_q = torch.stack([queries[:, t] @ w[t // (hq // hkv)].T for t in range(hq)], dim=1)
+    torch.testing.assert_close(router.project_queries(queries), want_q)
+    with pytest.raises(ValueError):
+        SembloKeyRouter(hkv, dim, 0)
+    with pytest.raises(ValueError):
+        router(keys)                       # [B, L, Hkv, D] is required
