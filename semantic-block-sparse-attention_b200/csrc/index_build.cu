@@ -361,6 +361,37 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bflo
 }
 
 // ------------------------------------------------------------------ counts
+// Exclusive prefix of one int per thread over the block (up to 1024 threads); `total` receives the
+// block's sum.  warp_tot: 32 ints of shared memory.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_tot, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    const int t = lane < nw ? warp_tot[lane] : 0;
+    int ti = t;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, ti, o);
+      if (lane >= o) ti += up;
+    }
+    warp_tot[lane] = ti - t;                       // exclusive prefix of the warp totals
+    if (lane == 31) warp_tot[32] = ti;             // the block's sum
+  }
+  __syncthreads();
+  total = warp_tot[32];
+  const int r = warp_tot[warp] + incl - v;
+  __syncthreads();                                 // warp_tot may be reused by the caller's next scan
+  return r;
+}
+
 __global__ void count_kernel(const int32_t* __restrict__ assign, int64_t n, int64_t head_stride,
                              int num_clusters, int32_t* __restrict__ counts) {
   const int h = blockIdx.y;
@@ -378,7 +409,7 @@ __global__ void scan_counts_kernel(const int32_t* __restrict__ counts, int num_c
                                    int32_t* __restrict__ ip_pad,      // [H, C+1] or null
                                    int32_t* __restrict__ empty_rank,  // [H, C] or null
                                    int32_t* __restrict__ n_empty) {   // [H] or null
-  __shared__ int s_a[1024], s_b[1024], s_c[1024];
+  __shared__ int warp_tot[33];
   const int h = blockIdx.x;
   const int* cnt = counts + (int64_t)h * num_clusters;
   const int per = (num_clusters + blockDim.x - 1) / blockDim.x;
@@ -390,21 +421,15 @@ __global__ void scan_counts_kernel(const int32_t* __restrict__ counts, int num_c
     b += align > 1 ? ((v + align - 1) / align) * align : v;
     e += v == 0;
   }
-  s_a[threadIdx.x] = a; s_b[threadIdx.x] = b; s_c[threadIdx.x] = e;
-  __syncthreads();
+  int ra, rb, rc;
+  a = block_exclusive_scan(a, warp_tot, ra);
+  b = block_exclusive_scan(b, warp_tot, rb);
+  e = block_exclusive_scan(e, warp_tot, rc);
   if (threadIdx.x == 0) {
-    int ra = 0, rb = 0, rc = 0;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      int ta = s_a[t], tb = s_b[t], tc = s_c[t];
-      s_a[t] = ra; s_b[t] = rb; s_c[t] = rc;
-      ra += ta; rb += tb; rc += tc;
-    }
     ip_orig[(int64_t)h * (num_clusters + 1) + num_clusters] = ra;
     if (ip_pad) ip_pad[(int64_t)h * (num_clusters + 1) + num_clusters] = rb;
     if (n_empty) n_empty[h] = rc;
   }
-  __syncthreads();
-  a = s_a[threadIdx.x]; b = s_b[threadIdx.x]; e = s_c[threadIdx.x];
   for (int c = lo; c < hi; ++c) {
     int v = cnt[c];
     ip_orig[(int64_t)h * (num_clusters + 1) + c] = a;
@@ -438,20 +463,14 @@ __global__ void sort_hist_kernel(const int32_t* __restrict__ keys, int64_t n, in
 
 // exclusive scan of [256 * ntiles] ints per head, in place (digit-major order)
 __global__ void sort_scan_kernel(int32_t* __restrict__ tile_hist, int total) {
-  __shared__ int part[1024];
+  __shared__ int warp_tot[33];
   int32_t* a = tile_hist + (int64_t)blockIdx.x * total;
   const int per = (total + blockDim.x - 1) / blockDim.x;
   const int lo = min(total, (int)threadIdx.x * per), hi = min(total, lo + per);
   int s = 0;
   for (int i = lo; i < hi; ++i) s += a[i];
-  part[threadIdx.x] = s;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int r = 0;
-    for (int t = 0; t < (int)blockDim.x; ++t) { int v = part[t]; part[t] = r; r += v; }
-  }
-  __syncthreads();
-  s = part[threadIdx.x];
+  int sum;
+  s = block_exclusive_scan(s, warp_tot, sum);
   for (int i = lo; i < hi; ++i) { int v = a[i]; a[i] = s; s += v; }
 }
 
