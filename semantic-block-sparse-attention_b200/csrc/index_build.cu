@@ -441,6 +441,52 @@ __global__ void scan_counts_kernel(const int32_t* __restrict__ counts, int num_c
   }
 }
 
+// The two kernels above in one block per head, for short inputs (a k-means sample): the histogram is
+// taken in shared memory (num_clusters ints, dynamic) and scanned in place.
+__global__ void count_scan_small_kernel(const int32_t* __restrict__ assign, int64_t n, int64_t head_stride,
+                                        int num_clusters, int align, int32_t* __restrict__ counts,
+                                        int32_t* __restrict__ ip_orig, int32_t* __restrict__ ip_pad,
+                                        int32_t* __restrict__ empty_rank, int32_t* __restrict__ n_empty) {
+  extern __shared__ int s_hist[];
+  __shared__ int warp_tot[33];
+  const int h = blockIdx.x;
+  for (int c = threadIdx.x; c < num_clusters; c += blockDim.x) s_hist[c] = 0;
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const int c = assign[h * head_stride + i];
+    if ((unsigned)c < (unsigned)num_clusters) atomicAdd(&s_hist[c], 1);
+  }
+  __syncthreads();
+  const int per = (num_clusters + blockDim.x - 1) / blockDim.x;
+  const int lo = min(num_clusters, (int)threadIdx.x * per), hi = min(num_clusters, lo + per);
+  int a = 0, b = 0, e = 0;
+  for (int c = lo; c < hi; ++c) {
+    const int v = s_hist[c];
+    a += v;
+    b += align > 1 ? ((v + align - 1) / align) * align : v;
+    e += v == 0;
+  }
+  int ra, rb, rc;
+  a = block_exclusive_scan(a, warp_tot, ra);
+  b = block_exclusive_scan(b, warp_tot, rb);
+  e = block_exclusive_scan(e, warp_tot, rc);
+  if (threadIdx.x == 0) {
+    ip_orig[(int64_t)h * (num_clusters + 1) + num_clusters] = ra;
+    if (ip_pad) ip_pad[(int64_t)h * (num_clusters + 1) + num_clusters] = rb;
+    if (n_empty) n_empty[h] = rc;
+  }
+  for (int c = lo; c < hi; ++c) {
+    const int v = s_hist[c];
+    counts[(int64_t)h * num_clusters + c] = v;
+    ip_orig[(int64_t)h * (num_clusters + 1) + c] = a;
+    if (ip_pad) ip_pad[(int64_t)h * (num_clusters + 1) + c] = b;
+    if (empty_rank) empty_rank[(int64_t)h * num_clusters + c] = v == 0 ? e : -1;
+    a += v;
+    b += align > 1 ? ((v + align - 1) / align) * align : v;
+    e += v == 0;
+  }
+}
+
 // ------------------------------------------------------------------ stable radix sort by cluster id
 constexpr int SORT_THREADS = 256;
 constexpr int SORT_ITEMS = 8;
@@ -831,6 +877,12 @@ extern "C" int semblo_cluster_counts(const int32_t* assign, int64_t n, int64_t h
                                      int32_t* ip_pad, int32_t* empty_rank, int32_t* n_empty,
                                      void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
+  if (n > 0 && n <= 131072 && num_clusters <= 12288) {       // one launch: histogram and scans in shared memory
+    count_scan_small_kernel<<<heads, 1024, (size_t)num_clusters * sizeof(int), st>>>(
+        assign, n, head_stride, num_clusters, align, counts, ip_orig, ip_pad, empty_rank, n_empty);
+    SEMBLO_LAUNCH_CHECK();
+    return 0;
+  }
   SEMBLO_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (size_t)heads * num_clusters, st));
   if (n > 0) {
     dim3 grid((unsigned)std::min<int64_t>(ceil_div(n, 256), 1184), heads);
