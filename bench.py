@@ -281,7 +281,8 @@ def kernel_launches(calls: dict, clusters: int) -> int:
     passes = 1 if clusters <= 256 else 2
     counts = 1                                      # histogram and scans in one launch up to 131072 keys
     per_call = {"semblo_routing_normalize": 1, "semblo_gather_rows": 1, "semblo_assign_argmax": 1,
-                "semblo_cluster_counts": counts, "semblo_kmeans_update": 3 * passes + 1, "semblo_split_descriptor": 1,
+                "semblo_cluster_counts": counts, "semblo_kmeans_update": 3 * passes + 1, "semblo_kmeans_sort_members": 3 * passes,
+                "semblo_kmeans_update_sorted": 1, "semblo_split_descriptor": 1,
                 "semblo_build_layout": counts + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
                 "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_window_prefill": 1, "semblo_sparse_prefill_gather": 1, "semblo_gather_launch_order": 2,
                 "semblo_argsort_keys": 3 * passes,

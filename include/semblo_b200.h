@@ -68,6 +68,17 @@ int semblo_kmeans_update(const float* sample, const int32_t* assign, int64_t n, 
                          const int64_t* repl, float* cent_f32, void* cent_bf16, void* workspace,
                          int64_t workspace_bytes, void* stream);
 
+/* The same update in two calls, for a caller that reads n_empty on the host between them: the member
+ * lists do not depend on the restart draws, so they can be sorted (semblo_kmeans_sort_members, into
+ * `workspace`) while that read is on its way, and semblo_kmeans_update_sorted then takes `repl` and the
+ * workspace as the first call left it. */
+int semblo_kmeans_sort_members(const int32_t* assign, int64_t n, int num_clusters, void* workspace,
+                               int64_t workspace_bytes, void* stream);
+int semblo_kmeans_update_sorted(const float* sample, int64_t n, int num_clusters, int dim,
+                                const int32_t* ip_orig, const int32_t* empty_rank, const int64_t* repl,
+                                float* cent_f32, void* cent_bf16, const void* workspace,
+                                int64_t workspace_bytes, void* stream);
+
 /* semblo/vllm_plugin/state.py:877-886: codebooks [2, C, dim/2] (bf16) = halves of
  * normalize(cents); cluster c takes row c - row_offset of cents, zero outside [0, num_rows). */
 int semblo_split_descriptor(const float* cents, int num_rows, int row_offset, int num_clusters,

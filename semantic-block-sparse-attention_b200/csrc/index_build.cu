@@ -911,6 +911,26 @@ extern "C" int semblo_kmeans_update(const float* sample, const int32_t* assign, 
   return 0;
 }
 
+extern "C" int semblo_kmeans_sort_members(const int32_t* assign, int64_t n, int num_clusters, void* workspace,
+                                          int64_t workspace_bytes, void* stream) {
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, 1), "workspace too small");
+  int32_t* ws = (int32_t*)workspace;
+  return sort_by_cluster(assign, n, n, 1, num_clusters, ws, ws + n, ws + 2 * n, ws + 3 * n, ws + 4 * n,
+                         (cudaStream_t)stream);
+}
+
+extern "C" int semblo_kmeans_update_sorted(const float* sample, int64_t n, int num_clusters, int dim,
+                                           const int32_t* ip_orig, const int32_t* empty_rank,
+                                           const int64_t* repl, float* cent_f32, void* cent_bf16,
+                                           const void* workspace, int64_t workspace_bytes, void* stream) {
+  SEMBLO_REQUIRE(dim <= 256 && dim % 32 == 0, "dim %d must be a multiple of 32 up to 256", dim);
+  SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, 1), "workspace too small");
+  centroid_update_kernel<<<num_clusters, dim, 0, (cudaStream_t)stream>>>(
+      sample, (const int32_t*)workspace, ip_orig, empty_rank, repl, dim, cent_f32, (__nv_bfloat16*)cent_bf16);
+  SEMBLO_LAUNCH_CHECK();
+  return 0;
+}
+
 extern "C" int semblo_split_descriptor(const float* cents, int num_rows, int row_offset,
                                        int num_clusters, int dim, void* codebook_bf16, void* stream) {
   split_descriptor_kernel<<<(unsigned)ceil_div(num_clusters, 8), 256, 0, (cudaStream_t)stream>>>(

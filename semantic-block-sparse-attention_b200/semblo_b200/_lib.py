@@ -44,6 +44,8 @@ _SIGNATURES = {
     "semblo_assign_argmax": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "semblo_cluster_counts": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "semblo_kmeans_update": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "semblo_kmeans_sort_members": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p]),
+    "semblo_kmeans_update_sorted": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "semblo_split_descriptor": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "semblo_layout_workspace_bytes": (c_int64, [c_int64, c_int]),
     "semblo_build_layout": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),

@@ -88,6 +88,12 @@ class _FitWorkspace:
         self.cent_bf16 = torch.empty(num_clusters, dim, dtype=torch.bfloat16, device=device)
         self.ws_bytes = int(lib().semblo_layout_workspace_bytes(n, 1))
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=device)
+        # the host reads n_empty through a pinned word, copied on a stream of its own behind the counts, so
+        # that the sort of the member lists (which needs no restart draws) runs while the read is on its way
+        self.n_empty_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.read_stream = torch.cuda.Stream(device=device)
+        self.counted = torch.cuda.Event()
+        self.read_done = torch.cuda.Event()
 
 
 def _assign(x_bf16: torch.Tensor, cent_bf16: torch.Tensor, out: torch.Tensor, id_offset: int = 0) -> None:
@@ -122,12 +128,19 @@ def fit_flat_codebook(space_f32: torch.Tensor, space_bf16: torch.Tensor, num_clu
         _assign(sample_bf16, w.cent_bf16, w.assign)
         check(lib().semblo_cluster_counts(ptr(w.assign), fit_n, fit_n, 1, num_clusters, 1, ptr(w.counts),
                                           ptr(w.ip), None, ptr(w.empty_rank), ptr(w.n_empty), stream_ptr()))
+        w.counted.record()
+        w.read_stream.wait_event(w.counted)
+        with torch.cuda.stream(w.read_stream):
+            w.n_empty_host.copy_(w.n_empty, non_blocking=True)
+            w.read_done.record()
+        check(lib().semblo_kmeans_sort_members(ptr(w.assign), fit_n, num_clusters, ptr(w.ws), w.ws_bytes, stream_ptr()))
+        w.read_done.synchronize()
         repl = None
-        if int(w.n_empty.item()) > 0:
+        if int(w.n_empty_host[0]) > 0:
             repl = torch.randperm(fit_n, device=device, generator=generator).contiguous()
-        check(lib().semblo_kmeans_update(ptr(sample_f32), ptr(w.assign), fit_n, num_clusters, dim, ptr(w.ip),
-                                         ptr(w.empty_rank), ptr(repl), ptr(w.cent_f32), ptr(w.cent_bf16),
-                                         ptr(w.ws), w.ws_bytes, stream_ptr()))
+        check(lib().semblo_kmeans_update_sorted(ptr(sample_f32), fit_n, num_clusters, dim, ptr(w.ip),
+                                                ptr(w.empty_rank), ptr(repl), ptr(w.cent_f32), ptr(w.cent_bf16),
+                                                ptr(w.ws), w.ws_bytes, stream_ptr()))
     return w.cent_f32
 
 
