@@ -277,15 +277,16 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------- launch accounting
-def kernel_launches(calls: dict, clusters: int) -> int:
+def kernel_launches(calls: dict, clusters: int, chunk: int) -> int:
     passes = 1 if clusters <= 256 else 2
+    order_sort = 1 if chunk <= 8192 and clusters <= 2048 else 3 * passes   # short key lists sort in one launch
     counts = 1                                      # histogram and scans in one launch up to 131072 keys
     per_call = {"semblo_routing_normalize": 1, "semblo_gather_rows": 1, "semblo_assign_argmax": 1,
                 "semblo_cluster_counts": counts, "semblo_kmeans_update": 3 * passes + 1, "semblo_kmeans_sort_members": 3 * passes,
                 "semblo_kmeans_update_sorted": 1, "semblo_split_descriptor": 1,
                 "semblo_build_layout": counts + 3 * passes + 1, "semblo_pack_kv": 1, "semblo_snapshot_advance": 1,
                 "semblo_score_clusters": 1, "semblo_select_clusters": 1, "semblo_window_prefill": 1, "semblo_sparse_prefill_gather": 1, "semblo_gather_launch_order": 2,
-                "semblo_argsort_keys": 3 * passes,
+                "semblo_argsort_keys": order_sort,
                 "semblo_decode_step": 3}
     return sum(per_call.get(k, 0) * v for k, v in calls.items())
 
@@ -901,7 +902,7 @@ def main():
     _lib.status_for(device).raise_if_set()
     calls = dict(_lib.CALLS)
     clusters = int(index.num_buckets)
-    launches = kernel_launches(calls, clusters) // args.steps
+    launches = kernel_launches(calls, clusters, int(cfg["chunk"])) // args.steps
     counts = [int(v) // args.steps for v in step.attended.tolist()]
     attended = counts[0] + counts[2]                       # dense prefix + windows, selected clusters
     sparse_pairs, gathered_rows = counts[2], counts[3]

@@ -570,6 +570,70 @@ __global__ void sort_scatter_kernel(const int32_t* __restrict__ keys_in,
   }
 }
 
+// Stable arg-sort of up to 8192 keys below `bins` (a power of two up to 2048) per head in one block:
+// warp w owns keys [1024 w, 1024 w + 1024) and ranks them in 32 rounds of 32 consecutive keys against
+// its own counters; the counters are then turned into start offsets (over the keys, then over the warps).
+constexpr int SMALL_SORT_MAX_N = 8192;
+__global__ void __launch_bounds__(256)
+small_argsort_kernel(const int32_t* __restrict__ keys, int n, int64_t head_stride, int bins,
+                     int32_t* __restrict__ order) {
+  extern __shared__ int cnt[];                     // [8 warps][bins], then [bins] totals
+  __shared__ int warp_tot[33];
+  int* tot = cnt + 8 * bins;
+  const int h = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t* k = keys + (int64_t)h * head_stride;
+  for (int i = threadIdx.x; i < 8 * bins; i += 256) cnt[i] = 0;
+  __syncthreads();
+  int key[32], rank[32];
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int p = warp * 1024 + r * 32 + lane;
+    const bool live = p < n;
+    key[r] = live ? k[p] : 0;
+    const int d = live ? (key[r] & (bins - 1)) : bins + lane;      // dead lanes match nobody
+    const unsigned m = __match_any_sync(0xffffffffu, d);
+    const int leader = __ffs(m) - 1;
+    int old = 0;
+    if (live && lane == leader) { old = cnt[warp * bins + d]; cnt[warp * bins + d] = old + __popc(m); }
+    old = __shfl_sync(0xffffffffu, old, leader);
+    rank[r] = old + __popc(m & ((1u << lane) - 1));
+    __syncwarp();
+  }
+  __syncthreads();
+  // totals per key, their exclusive scan over the keys, then per key the prefix over the warps
+  const int per = bins / 256 > 0 ? bins / 256 : 1;
+  int mine = 0;
+  for (int j = 0; j < per; ++j) {
+    const int d = threadIdx.x * per + j;
+    int t = 0;
+    if (d < bins) {
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += cnt[w * bins + d];
+      tot[d] = t;
+    }
+    mine += t;
+  }
+  int all;
+  int run = block_exclusive_scan(mine, warp_tot, all);
+  for (int j = 0; j < per; ++j) {
+    const int d = threadIdx.x * per + j;
+    if (d < bins) {
+      int start = run;
+      run += tot[d];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) { const int v = cnt[w * bins + d]; cnt[w * bins + d] = start; start += v; }
+    }
+  }
+  __syncthreads();
+  int32_t* o = order + (int64_t)h * head_stride;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    const int p = warp * 1024 + r * 32 + lane;
+    if (p < n) o[cnt[warp * bins + (key[r] & (bins - 1))] + rank[r]] = p;
+  }
+}
+
 // posting[h][row] for every padded row, and the position -> row map.
 __global__ void fill_layout_kernel(const int32_t* __restrict__ order, int64_t n, int64_t head_stride,
                                    const int32_t* __restrict__ counts,
@@ -1000,6 +1064,16 @@ extern "C" int semblo_argsort_keys(const int32_t* keys, int64_t n, int heads, in
   SEMBLO_REQUIRE(max_key > 0 && max_key <= 65536, "keys must be below 65536");
   SEMBLO_REQUIRE(workspace_bytes >= semblo_layout_workspace_bytes(n, heads), "workspace too small");
   if (n == 0) return 0;
+  if (n <= SMALL_SORT_MAX_N && max_key <= 2048) {           // one launch: a block per head
+    int bins = 32;
+    while (bins < max_key) bins <<= 1;
+    const size_t smem = (size_t)9 * bins * sizeof(int);
+    if (smem > 48 * 1024)
+      SEMBLO_CUDA(cudaFuncSetAttribute(small_argsort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    small_argsort_kernel<<<heads, 256, smem, (cudaStream_t)stream>>>(keys, (int)n, n, bins, order);
+    SEMBLO_LAUNCH_CHECK();
+    return 0;
+  }
   int32_t* ws = (int32_t*)workspace;
   const int64_t hn = (int64_t)heads * n;
   return sort_by_cluster(keys, n, n, heads, max_key, order, ws, ws + hn, ws + 2 * hn, ws + 3 * hn,

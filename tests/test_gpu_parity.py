@@ -432,7 +432,8 @@ def test_gather_launch_order_counts_union_rows(dev):
 def test_argsort_and_top1_keys(dev):
     from semblo_b200.fused_prefill import argsort_keys
     g = torch.Generator().manual_seed(1)
-    for n, heads, mx in ((5000, 3, 2048), (333, 1, 200), (8192, 4, 16384)):
+    for n, heads, mx in ((5000, 3, 2048), (333, 1, 200), (8192, 4, 16384), (8192, 8, 2048), (8193, 2, 2048),
+                         (1, 2, 1), (31, 1, 2), (1025, 3, 33), (4096, 2, 1000)):
         keys = torch.randint(0, mx, (heads, n), generator=g).int()
         got = argsort_keys(keys.to(dev), mx).cpu().long()
         want = torch.argsort(keys.long(), dim=1, stable=True)
