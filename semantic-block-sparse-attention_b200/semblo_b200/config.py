@@ -13,7 +13,7 @@ class SembloVllmConfig:
     token_capacity: int                       # longest prompt a layer's decode arena is shaped for
     target_tokens: int                        # selection budget per query and KV head
     flat_unit_tokens: int                     # mean tokens per block: C = L / flat_unit_tokens
-    index_dim: int                            # routing dimension (= head_dim: identity routing map)
+    index_dim: int                            # routing dimension (head_dim: identity or square map; less: a narrowing map)
     mode: str = "sparse"
     num_factors: int = 1
     num_centroids: int = 0

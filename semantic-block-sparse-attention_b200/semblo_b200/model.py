@@ -51,9 +51,10 @@ class SembloAttention(nn.Module):
         runtime_config.validate()
         if attention_logits_soft_cap:
             raise RuntimeError("the fused sparse path has no logit soft cap")
-        if int(runtime_config.index_dim) != int(self.head_dim):
-            raise RuntimeError("the kernels route in a space of the head dimension: index_dim must equal head_dim "
-                               "(the identity map, or a loaded square map)")
+        if int(runtime_config.index_dim) > int(self.head_dim):
+            raise RuntimeError("the kernels route in a space of the head dimension: index_dim must not exceed "
+                               "head_dim (the identity map, a loaded square map, or a map into fewer dimensions, "
+                               "which is padded with zeros)")
         self.layer_idx = int(layer_idx)
         self.source_layer_idx = int(source_layer_idx)
         self.uses_sparse_attention = bool(uses_sparse_attention)
@@ -132,7 +133,7 @@ class SembloAttention(nn.Module):
             raise RuntimeError("only SEMBLO_ROUTING_NORMALIZE=whole is implemented")
         queries, heads, dim = q_pre_rope.shape
         router = source._router(q_pre_rope.device)
-        projected = q_pre_rope if router.is_identity() else router.project_queries(q_pre_rope).contiguous()
+        projected = q_pre_rope if router.is_identity() else router.widen(router.project_queries(q_pre_rope)).contiguous()
         vectors = trivial_router_vectors(projected).view(1, queries, heads, 1, dim)
         return SimpleNamespace(vectors=vectors, mixture_weights=None)
 
@@ -251,7 +252,7 @@ class SembloAttention(nn.Module):
         return _arena.arena_for(
             self.runtime_state, self.source_layer_idx, capacity=int(cfg.token_capacity), unit_tokens=unit_tokens,
             min_clusters_log2=max(3, int(os.environ.get("SEMBLO_FLAT_MIN_CLUSTERS_LOG2", cfg.flat_min_clusters_log2))),
-            num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, index_dim=int(cfg.index_dim),
+            num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, index_dim=self.head_dim,   # the routed width
             page_align=int(os.environ.get("SEMBLO_FA3_ALIGN", cfg.fa3_page_align)), kv_dtype=like.dtype,
             desc_dtype=like.dtype, device=like.device, **extra)
 

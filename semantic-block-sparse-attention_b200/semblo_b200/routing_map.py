@@ -5,14 +5,17 @@ Mirror of semblo/vllm_plugin/routing_map.py (``SembloQueryState`` 21-30, ``routi
 is the identity by default; a linear map W [Hkv, I, D] per layer and KV head can be loaded instead
 (the reference's routing-key comparisons: non-rotary dimensions, PCA, random projections).  Keys and
 queries go through the same map and the result is normalised over the whole vector.  The projection
-is a plain batched GEMM (torch); the kernels behind it route in a space of the head dimension, so a
-loaded map must be square (I == D)."""
+is a plain batched GEMM (torch).  The kernels behind it route in a space of the head dimension, so a
+map into fewer dimensions (I < D) is followed by zero padding up to D: zeros change neither a norm
+nor a dot product nor a mean, so the clusters, the scores and the selection are those of the
+I-dimensional space.  A map into more dimensions than the head has is refused."""
 from __future__ import annotations
 
 from dataclasses import dataclass
 
 import torch
 from torch import nn
+from torch.nn import functional as F
 
 from .flat_index import routing_normalize
 
@@ -31,6 +34,8 @@ class SembloKeyRouter(nn.Module):
         super().__init__()
         if index_dim <= 0 or index_dim % max(int(num_factors), 1) != 0:
             raise ValueError("index_dim must be positive and divisible by num_factors")
+        if index_dim > head_dim:
+            raise ValueError("the kernels route in a space of the head dimension: index_dim must not exceed head_dim")
         self.num_kv_heads, self.head_dim, self.index_dim = int(num_kv_heads), int(head_dim), int(index_dim)
         self.num_factors = int(num_factors)
         self.weight = nn.Parameter(torch.zeros(num_kv_heads, index_dim, head_dim), requires_grad=False)
@@ -69,6 +74,12 @@ class SembloKeyRouter(nn.Module):
         per_q = self.weight.to(dtype=q_pre.dtype).index_select(0, q_to_kv)
         return torch.einsum("qhd,hid->qhi", q_pre, per_q)
 
+    def widen(self, projected: torch.Tensor) -> torch.Tensor:
+        """[..., I] -> [..., D]: the projection in the width the kernels route in (zeros after dimension I)."""
+        if self.index_dim == self.head_dim:
+            return projected
+        return F.pad(projected, (0, self.head_dim - self.index_dim))
+
     def forward(self, keys: torch.Tensor) -> torch.Tensor:
         if keys.ndim != 4:
             raise ValueError("keys must have shape [B,L,Hkv,D]")
@@ -77,5 +88,5 @@ class SembloKeyRouter(nn.Module):
         if self.is_identity():
             return routing_normalize(keys[0])[None] if keys.shape[0] == 1 else torch.stack(
                 [routing_normalize(k) for k in keys])
-        projected = self.project(keys)
+        projected = self.widen(self.project(keys))
         return torch.stack([routing_normalize(p.contiguous()) for p in projected])

@@ -309,20 +309,24 @@ def test_streamed_sessions_through_the_layer(dev):
             os.environ.pop(k, None)
 
 
-@pytest.mark.parametrize("arena_mode", [True, False])
-def test_loaded_routing_map(dev, arena_mode):
-    """A square linear routing map (routing_map.py:67-94, model.py:432-489 of the reference): keys and
-    queries go through it before they are normalised.  The layer with the map loaded gives the bytes of
-    a layer with the identity map that is handed the projected pre-RoPE tensors, prompt and decode."""
+@pytest.mark.parametrize("arena_mode,index_dim", [(True, 128), (False, 128), (True, 96), (False, 64)])
+def test_loaded_routing_map(dev, arena_mode, index_dim):
+    """A linear routing map (routing_map.py:67-94, model.py:432-489 of the reference), square or into
+    fewer dimensions: keys and queries go through it before they are normalised.  The layer with the
+    map loaded gives the bytes of a layer with the identity map that is handed the projected pre-RoPE
+    tensors (followed by zeros up to the head dimension, which change no norm and no dot product),
+    prompt and decode."""
     from semblo_b200 import _lib
     from semblo_b200.config import SembloVllmConfig
     from semblo_b200.state import SembloRuntimeState
     dim, hq, hkv, sink, length, target, local, chunk, steps = 128, 8, 2, 64, 4096, 256, 128, 1024, 4
     cpu = O.mixture_inputs(length=length + steps, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=31)
     data = {k: v.to(dev) for k, v in cpu.items()}
+    import dataclasses
     cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
                            flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
                            packed_decode_num_splits=4, decode_num_splits=2)
+    cfg_map = dataclasses.replace(cfg, index_dim=index_dim)
     env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL=str(local), SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16")
     if arena_mode:
         env["SEMBLO_FULL_GRAPH_DECODE"] = "1"
@@ -330,16 +334,17 @@ def test_loaded_routing_map(dev, arena_mode):
     if not arena_mode:
         os.environ.pop("SEMBLO_FULL_GRAPH_DECODE", None)
     try:
-        mapped = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192 + 512),
+        mapped = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg_map, state=SembloRuntimeState(max_model_len=8192 + 512),
                              name=f"model.layers.{5 + arena_mode}.self_attn.attn")
         g = torch.Generator().manual_seed(3)
         w = torch.linalg.qr(torch.randn(hkv, dim, dim, generator=g))[0] + 0.05 * torch.randn(hkv, dim, dim, generator=g)
-        mapped.semblo_key_router.load_weight(w)
+        mapped.semblo_key_router.load_weight(w[:, :index_dim])
         router = mapped._router(dev)
         assert not router.is_identity()
+        assert tuple(router.project(data["k_pre"]).shape[-2:]) == (hkv, index_dim)
         projected = dict(data)
-        projected["k_pre"] = router.project(data["k_pre"]).contiguous()
-        projected["q_pre"] = router.project_queries(data["q_pre"]).contiguous()
+        projected["k_pre"] = router.widen(router.project(data["k_pre"])).contiguous()
+        projected["q_pre"] = router.widen(router.project_queries(data["q_pre"])).contiguous()
         plain = _make_layer(projected, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg,
                             state=SembloRuntimeState(max_model_len=8192 + 512), name=f"model.layers.{7 + arena_mode}.self_attn.attn")
         assert plain._router(dev).is_identity()

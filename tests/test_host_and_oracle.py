@@ -163,3 +163,30 @@ def test_routing_map_projection_and_identity_detection():
         SembloKeyRouter(hkv, dim, 0)
     with pytest.raises(ValueError):
         router(keys)                       # [B, L, Hkv, D] is required
+    # a map into fewer dimensions: the kernels get the projection followed by zeros, which leaves the
+    # partition of the oracle's build where it is (norms, dot products and means ignore the zeros)
+    narrow = SembloKeyRouter(hkv, dim, 10)
+    assert not narrow.is_identity()
+    narrow.load_weight(w[:, :10])
+    proj = narrow.project(keys)
+    assert tuple(proj.shape) == (5, hkv, 10)
+    wide = narrow.widen(proj)
+    assert tuple(wide.shape) == (5, hkv, dim) and torch.equal(wide[..., :10], proj) and not wide[..., 10:].any()
+    with pytest.raises(ValueError):
+        SembloKeyRouter(hkv, dim, dim + 2)
+
+
+def test_zero_padded_routing_space_gives_the_same_index():
+    """What a narrowing routing map relies on: the oracle's index build on I-dimensional routing keys and on
+    the same keys followed by zeros is the same partition."""
+    length, hkv, idim, dim = 1024, 2, 24, 32
+    data = O.mixture_inputs(length=length, num_q_heads=4, num_kv_heads=hkv, head_dim=dim, centres=12, seed=5)
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(hkv, idim, dim, generator=g)
+    proj = torch.einsum("lhd,hid->lhi", data["k_pre"].float(), w)
+    proj = torch.nn.functional.normalize(proj, dim=-1).to(torch.bfloat16)
+    padded = torch.nn.functional.pad(proj, (0, dim - idim))
+    a = O.build_flat(proj, unit_tokens=32, min_clusters_log2=3, kmeans_sample_size=512, fit_iters=4, seed=7)
+    b = O.build_flat(padded, unit_tokens=32, min_clusters_log2=3, kmeans_sample_size=512, fit_iters=4, seed=7)
+    same = (a.assign == b.assign).float().mean().item()
+    assert same > 0.995, same
