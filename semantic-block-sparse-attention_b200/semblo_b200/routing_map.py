@@ -90,3 +90,46 @@ class SembloKeyRouter(nn.Module):
                 [routing_normalize(k) for k in keys])
         projected = self.widen(self.project(keys))
         return torch.stack([routing_normalize(p.contiguous()) for p in projected])
+
+
+# ---------------------------------------------------------------------------------- map makers
+# The maps of the reference's routing-key comparisons (scripts/make_routing_map.py:44-120 there), as
+# [Hkv, I, D] fp32 tensors ready for ``SembloKeyRouter.load_weight`` or ``runtime_weights.write_runtime_weights``.
+
+def non_rotary_map(num_kv_heads: int, head_dim: int, rotary_dims: int) -> torch.Tensor:
+    """The identity with the first ``rotary_dims`` (rotated) dimensions zeroed: routing on the
+    dimensions that RoPE leaves alone.  Square."""
+    if not 0 <= rotary_dims <= head_dim:
+        raise ValueError("rotary_dims must lie in [0, head_dim]")
+    eye = torch.eye(head_dim, dtype=torch.float32)
+    eye[:rotary_dims] = 0
+    return eye.expand(num_kv_heads, head_dim, head_dim).contiguous()
+
+
+def random_map(num_kv_heads: int, head_dim: int, index_dim: int, generator: torch.Generator) -> torch.Tensor:
+    """Per KV head a random map with orthonormal rows (index_dim <= head_dim): the Q factor of a
+    float64 Gaussian matrix, transposed."""
+    if not 0 < index_dim <= head_dim:
+        raise ValueError("index_dim must lie in (0, head_dim]")
+    maps = []
+    for _ in range(num_kv_heads):
+        q, _r = torch.linalg.qr(torch.randn(head_dim, index_dim, generator=generator, dtype=torch.float64))
+        maps.append(q.T.contiguous().to(torch.float32))
+    return torch.stack(maps)
+
+
+def pca_map(keys: torch.Tensor, index_dim: int, rank: int | None = None) -> torch.Tensor:
+    """Per KV head the top ``rank`` eigenvectors of the uncentred Gram matrix of pre-RoPE keys
+    [L, Hkv, D] (float64 eigendecomposition, largest eigenvalue first) as rows of [Hkv, index_dim, D];
+    rows past ``rank`` are zero."""
+    length, heads, dim = keys.shape
+    rank = index_dim if rank is None else int(rank)
+    if not 0 < rank <= index_dim <= dim:
+        raise ValueError("need 0 < rank <= index_dim <= head_dim")
+    x = keys.detach().to(torch.float32).permute(1, 0, 2).contiguous()          # [Hkv, L, D]
+    gram = torch.matmul(x.transpose(1, 2), x).to(torch.float64).cpu()          # [Hkv, D, D]
+    out = torch.zeros(heads, index_dim, dim, dtype=torch.float64)
+    for h in range(heads):
+        _vals, vecs = torch.linalg.eigh(gram[h])                               # ascending eigenvalues
+        out[h, :rank] = vecs[:, -rank:].flip(1).T
+    return out.to(torch.float32)

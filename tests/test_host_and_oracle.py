@@ -176,6 +176,39 @@ def test_routing_map_projection_and_identity_detection():
         SembloKeyRouter(hkv, dim, dim + 2)
 
 
+def test_routing_map_makers():
+    """The maps of the reference's routing-key comparisons (scripts/make_routing_map.py:44-120)."""
+    from semblo_b200.routing_map import SembloKeyRouter, non_rotary_map, pca_map, random_map
+    hkv, dim = 2, 16
+    w = non_rotary_map(hkv, dim, 4)
+    assert tuple(w.shape) == (hkv, dim, dim) and not w[:, :4].any() and torch.equal(w[0, 4:, 4:], torch.eye(12))
+    g = torch.Generator().manual_seed(4)
+    r = random_map(hkv, dim, 6, g)
+    assert tuple(r.shape) == (hkv, 6, dim)
+    torch.testing.assert_close(r @ r.transpose(1, 2), torch.eye(6).expand(hkv, 6, 6), atol=1e-5, rtol=0)
+    assert not torch.allclose(r[0], r[1])
+    # keys that live in a 3-dimensional subspace per head: the top 3 rows span it, the 4th explains nothing
+    basis = torch.linalg.qr(torch.randn(hkv, dim, 3, generator=g))[0]                      # [Hkv, D, 3]
+    coef = torch.randn(200, hkv, 3, generator=g) * torch.tensor([5.0, 2.0, 1.0])
+    keys = torch.einsum("lhr,hdr->lhd", coef, basis)
+    p = pca_map(keys, 8, rank=4)
+    assert tuple(p.shape) == (hkv, 8, dim) and not p[:, 4:].any()
+    torch.testing.assert_close(p[:, :4] @ p[:, :4].transpose(1, 2), torch.eye(4).expand(hkv, 4, 4), atol=1e-5, rtol=0)
+    inside = torch.einsum("hid,hdr->hir", p[:, :3], basis)                                # rows 0-2 lie in the span
+    torch.testing.assert_close((inside ** 2).sum(-1), torch.ones(hkv, 3), atol=1e-4, rtol=0)
+    explained = torch.einsum("lhd,hid->lhi", keys, p).pow(2).sum(0)                       # [Hkv, 8]
+    assert (explained[:, 0] > explained[:, 1]).all() and (explained[:, 1] > explained[:, 2]).all()
+    assert (explained[:, 3] < 1e-3 * explained[:, 2]).all()
+    for made in (w, r, p):
+        router = SembloKeyRouter(hkv, dim, made.shape[1])
+        router.load_weight(made)
+        assert not router.is_identity()
+    with pytest.raises(ValueError):
+        random_map(hkv, dim, dim + 1, g)
+    with pytest.raises(ValueError):
+        pca_map(keys, 4, rank=5)
+
+
 def test_zero_padded_routing_space_gives_the_same_index():
     """What a narrowing routing map relies on: the oracle's index build on I-dimensional routing keys and on
     the same keys followed by zeros is the same partition."""
