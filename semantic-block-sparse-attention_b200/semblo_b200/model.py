@@ -238,8 +238,6 @@ class SembloAttention(nn.Module):
         if _flush.enabled():
             if os.environ.get("SEMBLO_ROUTING_CENTER") == "1":
                 raise RuntimeError("the suffix flush does not re-centre keys (SEMBLO_ROUTING_CENTER=1)")
-            if not self._router(like.device).is_identity():
-                raise RuntimeError("the suffix flush assigns by the keys themselves: it serves the identity routing map")
             if _flush.keep_exact() + _flush.flush_every() > reserve:
                 raise RuntimeError("SEMBLO_SUFFIX_KEEP_EXACT + SEMBLO_SUFFIX_FLUSH_EVERY must not exceed the "
                                    f"suffix reserve ({reserve})")
@@ -507,8 +505,9 @@ class LayerTokenOuterSession:
         from .token_outer import TokenOuterPrefillSession
         self.layer = layer
         cfg = layer.runtime_config
-        if not layer._router(positions.device).is_identity():
-            raise RuntimeError("the token-outer prefill assigns by the keys themselves: it serves the identity routing map")
+        # a loaded routing map: the streamed store is handed the projected pre-RoPE tensors (it uses them
+        # for routing only), which is the identity map's path on those tensors
+        self.router = layer._router(positions.device)
         self.rope_positions, self.flat = layer._positions_for_runtime(positions)
         layer.runtime_state.maybe_begin_prompt(layer.layer_idx, self.flat)
         self.inner = TokenOuterPrefillSession(
@@ -529,8 +528,12 @@ class LayerTokenOuterSession:
         if k_post is None or v_states is None or k_pre is None:
             raise RuntimeError("the token-outer prefill needs a layer with its own K/V")
         hq, hkv, d = layer.num_heads, layer.num_kv_heads, layer.head_dim
-        attn = self.inner.slice(q_post.view(-1, hq, d), q_pre.view(-1, hq, d), k_post.view(-1, hkv, d),
-                                v_states.view(-1, hkv, d), k_pre.view(-1, hkv, d), start, stop)
+        q_pre, k_pre = q_pre.view(-1, hq, d), k_pre.view(-1, hkv, d)
+        if not self.router.is_identity():
+            q_pre = self.router.widen(self.router.project_queries(q_pre)).contiguous()
+            k_pre = self.router.widen(self.router.project(k_pre)).contiguous()
+        attn = self.inner.slice(q_post.view(-1, hq, d), q_pre, k_post.view(-1, hkv, d),
+                                v_states.view(-1, hkv, d), k_pre, start, stop)
         return layer._finish_output(attn.view(hidden_states.shape[0], -1), gate)
 
     def finish(self) -> None:

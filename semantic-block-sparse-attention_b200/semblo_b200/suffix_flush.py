@@ -37,12 +37,14 @@ def flush_range(prompt_len: int, written: int, plen_cur: int, keep: int, every: 
     return None
 
 
-def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
+def flush_arena(arena, frm: int, to: int, align: int | None = None, router=None) -> int:
     """Move suffix positions [frm, to) into their nearest clusters (suffix_flush.py:172-208).
 
-    Reads the rows from the suffix store, assigns each to a cluster per KV head, re-packs the
-    arena's store in place, advances the prompt length and extends the ring table.  Returns the
-    widest packed length after the flush (one host read, as the reference's own return value)."""
+    Reads the rows from the suffix store, assigns each to a cluster per KV head in the routing space
+    the prefill used (``router``: the layer's SembloKeyRouter, none or the identity for routing on the
+    keys themselves; then the whole-vector normalisation), re-packs the arena's store in place,
+    advances the prompt length and extends the ring table.  Returns the widest packed length after
+    the flush (one host read, as the reference's own return value)."""
     n = int(to) - int(frm)
     if n <= 0:
         return 0
@@ -57,7 +59,10 @@ def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
     kpre = arena.suffix_kpre[phys, off].contiguous()                    # [n, Hkv, D]
     k = arena.suffix_kv[0, phys, off].contiguous()
     v = arena.suffix_kv[1, phys, off].contiguous()
-    product = routing_normalize(kpre)
+    if router is None or router.is_identity():
+        product = routing_normalize(kpre)
+    else:
+        product = router(kpre[None])[0]                                  # the map, zero padding, normalisation
     assign = nearest_cluster(product, arena.codebooks)                   # [Hkv, n]
     hkv, c = int(arena.sizes.shape[0]), int(arena.sizes.shape[1])
     d = int(arena.packed_kv.shape[-1])
@@ -86,3 +91,11 @@ def flush_arena(arena, frm: int, to: int, align: int | None = None) -> int:
     arena.prompt_length_t.fill_(int(to))
     arena.extend_suffix_table(int(to) + arena.reserve - 1)
     return int(arena.indptr[:, -1].max().item())
+
+
+def flush_layer(arena, module, frm: int, to: int, tmp=None) -> int:
+    """``flush_arena`` for a layer (suffix_flush.py:172-208 of the reference, which is handed the
+    module for its key router; ``tmp`` is the reference's scratch tensor and is not needed here: the
+    scratch lives with the arena)."""
+    return flush_arena(arena, frm, to, router=getattr(module, "semblo_key_router", None))
+

@@ -375,6 +375,84 @@ def test_loaded_routing_map(dev, arena_mode, index_dim):
             os.environ.pop(k, None)
 
 
+def test_loaded_routing_map_in_the_token_order_session_and_the_flush(dev):
+    """The two other users of the key router (token_outer_prefill.py:258 and suffix_flush.py:193 of the
+    reference): with a map loaded (here into fewer dimensions) the token-order session and the suffix flush
+    give the bytes of a layer with the identity map that is handed the projected pre-RoPE tensors."""
+    import dataclasses
+    from semblo_b200 import _lib
+    from semblo_b200 import suffix_flush as F
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.state import SembloRuntimeState
+    dim, index_dim, hq, hkv, sink, length, target, chunk, steps, keep = 128, 80, 8, 2, 64, 6144, 256, 1024, 24, 8
+    cpu = O.mixture_inputs(length=length + steps + 4, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=33)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    cfg_map = dataclasses.replace(cfg, index_dim=index_dim)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL="0", SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16",
+               SEMBLO_FULL_GRAPH_DECODE="1", SEMBLO_SUFFIX_FLUSH_EVERY="16", SEMBLO_SUFFIX_KEEP_EXACT=str(keep))
+    os.environ.update(env)
+    try:
+        g = torch.Generator().manual_seed(5)
+        w = torch.linalg.qr(torch.randn(hkv, dim, dim, generator=g))[0][:, :index_dim]
+        mapped = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg_map, state=SembloRuntimeState(max_model_len=8192 + 512),
+                             name="model.layers.11.self_attn.attn")
+        mapped.semblo_key_router.load_weight(w)
+        router = mapped._router(dev)
+        projected = dict(data)
+        projected["k_pre"] = router.widen(router.project(data["k_pre"])).contiguous()
+        projected["q_pre"] = router.widen(router.project_queries(data["q_pre"])).contiguous()
+        plain = _make_layer(projected, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192 + 512),
+                            name="model.layers.12.self_attn.attn")
+        positions = torch.arange(length, device=dev)
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        sa, sb = mapped.begin_token_outer_prefill(positions, chunk), plain.begin_token_outer_prefill(positions, chunk)
+        for s0 in range(0, length, chunk):
+            a = sa.slice(hidden[s0:s0 + chunk], s0, s0 + chunk)
+            b = sb.slice(hidden[s0:s0 + chunk], s0, s0 + chunk)
+            assert torch.equal(a, b), s0
+        sa.finish()
+        sb.finish()
+        torch.cuda.synchronize()
+        _lib.status_for(dev).raise_if_set()
+        assert torch.equal(mapped.runtime_state.get(0).bucket_sizes, plain.runtime_state.get(0).bucket_sizes)
+        pa, pb = torch.zeros(1, dtype=torch.int64, device=dev), torch.zeros(1, dtype=torch.int64, device=dev)
+
+        def step(s_):
+            pa.fill_(length + s_)
+            pb.fill_(length + s_)
+            oa = mapped._sparse_layer_forward(pa, hidden[:1]).clone()
+            ob = plain._sparse_layer_forward(pb, hidden[:1]).clone()
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            assert torch.equal(oa, ob), s_
+
+        for s_ in range(steps):
+            step(s_)
+        frm, to = F.flush_range(length, steps, length, keep, 16)
+        arena_a, arena_b = mapped._arena(data["q_post"]), plain._arena(data["q_post"])
+        # the stored pre-RoPE keys are the layer's inputs: raw under the map, projected in the plain layer
+        wa = F.flush_layer(arena_a, mapped, frm, to)
+        wb = F.flush_arena(arena_b, frm, to)
+        torch.cuda.synchronize()
+        assert wa == wb and int(arena_a.prompt_length_t.item()) == to
+        assert torch.equal(arena_a.sizes, arena_b.sizes) and torch.equal(arena_a.indptr, arena_b.indptr)
+        assert torch.equal(arena_a.posting[:, :wa], arena_b.posting[:, :wa])
+        assert torch.equal(arena_a.packed_kv[:, :wa], arena_b.packed_kv[:, :wa])
+        assert int(arena_a.sizes.sum()) == hkv * to
+        # and not the assignment of the unprojected keys
+        moved = F.nearest_cluster(F.routing_normalize(data["k_pre"][frm:to].contiguous()), arena_a.codebooks)
+        routed = F.nearest_cluster(router(data["k_pre"][frm:to][None])[0], arena_a.codebooks)
+        assert not torch.equal(moved, routed)
+        for s_ in range(steps, steps + 4):
+            step(s_)
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
 def test_operator_refuses_what_it_does_not_serve(dev):
     from semblo_b200.attention_op import registered_layer
     from semblo_b200.config import SembloVllmConfig
