@@ -1,7 +1,7 @@
 """Suffix flush: move the older part of the exact generated suffix into the clusters.
 
-Mirrors semblo/vllm_plugin/suffix_flush.py (flush_range 140-151, flush_layer 172-208 with the
-identity routing map, repack_apply 97-133) on a DecodeArena.  It runs between decode steps,
+Mirrors semblo/vllm_plugin/suffix_flush.py (flush_range 140-151, flush_layer 172-208, repack_apply
+97-133) on a DecodeArena.  It runs between decode steps,
 eagerly, on the arena's own buffers."""
 from __future__ import annotations
 
