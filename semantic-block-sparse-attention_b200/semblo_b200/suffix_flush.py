@@ -88,6 +88,8 @@ def flush_arena(arena, frm: int, to: int, align: int | None = None, router=None)
                                     ptr(old_posting), ptr(ws), ws.numel(), ptr(status.word), stream_ptr()))
     status.raise_if_set()        # refused (the result would not fit): the store is unchanged, as after the
                                  # reference's repack_apply, which raises before it moves anything
+    arena.index.prompt_length = int(to)
+    arena.index.max_position = int(to)
     arena.prompt_length_t.fill_(int(to))
     arena.extend_suffix_table(int(to) + arena.reserve - 1)
     return int(arena.indptr[:, -1].max().item())
@@ -98,4 +100,75 @@ def flush_layer(arena, module, frm: int, to: int, tmp=None) -> int:
     module for its key router; ``tmp`` is the reference's scratch tensor and is not needed here: the
     scratch lives with the arena)."""
     return flush_arena(arena, frm, to, router=getattr(module, "semblo_key_router", None))
+
+
+class SuffixFlusher:
+    """When to flush, across decode steps (suffix_flush.py:211-283 of the reference): one instance per
+    process, called on the host before every engine step -- a recorded decode step runs no Python, so
+    this is where the flush happens, before the step is replayed on the same buffers.
+
+    ``before_step(runner, scheduler_output)`` reads ``total_num_scheduled_tokens`` and
+    ``num_scheduled_tokens`` of the scheduler's output: a step that is not one token of one request
+    (a prefill chunk, several requests, nothing) only marks that the next single-token step starts a
+    fresh count.  On a single-token step the tokens written since the prompt are counted, and when the
+    exact suffix has grown to ``keep + every`` positions all but the newest ``keep`` are moved into
+    the clusters of every layer's arena (``flush_layer``).  The runtime state is found on the runner's
+    model (``runtime_state`` / ``semblo_runtime_state`` of any module) or handed to the constructor."""
+
+    def __init__(self, state=None) -> None:
+        self.keep, self.every = keep_exact(), flush_every()
+        self.state = state
+        self.epoch = None
+        self.prompt_len = self.written = self.flushes = 0
+        self.pending_reset = True
+        self.log = os.environ.get("SEMBLO_SUFFIX_FLUSH_LOG", "0") == "1"
+
+    def _find_state(self, runner):
+        if self.state is None:
+            model = getattr(runner, "model", None)
+            for _ in range(4):                      # an engine may wrap the model (a graph wrapper, say)
+                if model is None or hasattr(model, "modules"):
+                    break
+                model = getattr(model, "model", getattr(model, "runnable", None))
+            if model is not None and hasattr(model, "modules"):
+                for module in model.modules():
+                    found = getattr(module, "semblo_runtime_state", None) or getattr(module, "runtime_state", None)
+                    if found is not None:
+                        self.state = found
+                        break
+        return self.state
+
+    def _arenas(self) -> list:
+        return sorted(((int(key[1]), value) for key, value in self.state.index_buffers.items()
+                       if isinstance(key, tuple) and len(key) == 2 and key[0] == "arena"), key=lambda kv: kv[0])
+
+    def before_step(self, runner, scheduler_output) -> None:
+        total = int(getattr(scheduler_output, "total_num_scheduled_tokens", 0))
+        per_request = getattr(scheduler_output, "num_scheduled_tokens", None) or {}
+        if total != 1 or len(per_request) != 1:
+            self.pending_reset = True
+            return
+        state = self._find_state(runner)
+        if state is None:
+            return
+        arenas = self._arenas()
+        if not arenas or any(getattr(arena, "suffix_kpre", None) is None for _, arena in arenas):
+            return
+        first = arenas[0][1]
+        if self.pending_reset or self.epoch != state.prompt_epoch:
+            self.pending_reset, self.epoch = False, state.prompt_epoch
+            self.prompt_len, self.written = int(first.index.prompt_length), 0
+        due = flush_range(self.prompt_len, self.written, int(first.index.prompt_length), self.keep, self.every)
+        if due is not None:
+            frm, to = due
+            for layer, arena in arenas:
+                module = state.source_modules.get(layer)
+                if module is None:
+                    raise RuntimeError(f"no source module registered for layer {layer}")
+                flush_layer(arena, module, frm, to)
+            self.flushes += 1
+            if self.log:
+                print(f"[semblo] suffix flush {self.flushes}: positions [{frm}, {to}) of {len(arenas)} layers moved "
+                      f"into the clusters; exact suffix now {self.prompt_len + self.written - to} tokens", flush=True)
+        self.written += 1
 

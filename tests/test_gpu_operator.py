@@ -453,6 +453,56 @@ def test_loaded_routing_map_in_the_token_order_session_and_the_flush(dev):
             os.environ.pop(k, None)
 
 
+def test_suffix_flusher_drives_the_layer_arena(dev):
+    """suffix_flush.SuffixFlusher called before every engine step, as the reference's execute_model hook does
+    (suffix_flush.py:211-283): the prompt step resets the count, the decode steps are counted, and when the
+    exact suffix reaches keep + every its older part moves into the arena's clusters; decode goes on."""
+    from semblo_b200 import _lib
+    from semblo_b200 import suffix_flush as F
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.state import SembloRuntimeState
+    dim, hq, hkv, sink, length, target, chunk, steps, keep, every = 128, 8, 2, 64, 4096, 256, 1024, 44, 8, 16
+    cpu = O.mixture_inputs(length=length + steps, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=35)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL="128", SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16",
+               SEMBLO_FULL_GRAPH_DECODE="1", SEMBLO_SUFFIX_FLUSH_EVERY=str(every), SEMBLO_SUFFIX_KEEP_EXACT=str(keep))
+    os.environ.update(env)
+    try:
+        state = SembloRuntimeState(max_model_len=8192 + 512)
+        layer = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=state, name="model.layers.13.self_attn.attn")
+        model = torch.nn.Module()
+        model.layer = layer
+        runner = SimpleNamespace(model=model)
+        flusher = F.SuffixFlusher()
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        flusher.before_step(runner, SimpleNamespace(total_num_scheduled_tokens=length, num_scheduled_tokens={"r": length}))
+        layer._sparse_layer_forward(torch.arange(length, device=dev), hidden)
+        arena = layer._arena(data["q_post"])
+        one = SimpleNamespace(total_num_scheduled_tokens=1, num_scheduled_tokens={"r": 1})
+        pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        want_len, flushes = length, 0
+        for s_ in range(steps):
+            due = F.flush_range(length, s_, want_len, keep, every)
+            flusher.before_step(runner, one)
+            if due is not None:
+                want_len, flushes = due[1], flushes + 1
+            assert flusher.state is state and flusher.flushes == flushes
+            assert int(arena.prompt_length_t.item()) == want_len == int(arena.index.prompt_length)
+            assert int(arena.sizes.sum()) == hkv * want_len
+            pos.fill_(length + s_)
+            out = layer._sparse_layer_forward(pos, hidden[:1])
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            assert bool(torch.isfinite(out.float()).all())
+        assert flushes == 2 and want_len == length + 32
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
 def test_operator_refuses_what_it_does_not_serve(dev):
     from semblo_b200.attention_op import registered_layer
     from semblo_b200.config import SembloVllmConfig

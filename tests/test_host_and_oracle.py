@@ -223,3 +223,64 @@ def test_zero_padded_routing_space_gives_the_same_index():
     b = O.build_flat(padded, unit_tokens=32, min_clusters_log2=3, kmeans_sample_size=512, fit_iters=4, seed=7)
     same = (a.assign == b.assign).float().mean().item()
     assert same > 0.995, same
+
+
+def test_suffix_flusher_bookkeeping(monkeypatch):
+    """suffix_flush.SuffixFlusher (suffix_flush.py:211-283 of the reference) with the flush itself replaced
+    by a recorder: counting starts at the first single-token step after anything else, a flush is due when
+    the exact suffix reaches keep + every, it moves all but the newest `keep` positions of every arena, and a
+    new prompt starts a new count."""
+    from types import SimpleNamespace
+    from semblo_b200 import suffix_flush as F
+    monkeypatch.setenv("SEMBLO_SUFFIX_FLUSH_EVERY", "4")
+    monkeypatch.setenv("SEMBLO_SUFFIX_KEEP_EXACT", "3")
+    calls = []
+
+    def fake_flush(arena, module, frm, to, tmp=None):
+        calls.append((module, frm, to))
+        arena.index.prompt_length = to
+        return 0
+
+    monkeypatch.setattr(F, "flush_layer", fake_flush)
+    arenas = {l: SimpleNamespace(index=SimpleNamespace(prompt_length=100), suffix_kpre=object()) for l in (2, 5)}
+    state = SimpleNamespace(index_buffers={("arena", 2): arenas[2], ("arena", 5): arenas[5], "other": 1,
+                                           (("arena", 2), "sig"): 0},
+                            prompt_epoch=1, source_modules={2: "m2", 5: "m5"})
+    holder = SimpleNamespace(modules=lambda: [SimpleNamespace(), SimpleNamespace(runtime_state=state)])
+    runner = SimpleNamespace(model=SimpleNamespace(model=holder))          # wrapped once
+    one = SimpleNamespace(total_num_scheduled_tokens=1, num_scheduled_tokens={"r": 1})
+    chunk = SimpleNamespace(total_num_scheduled_tokens=100, num_scheduled_tokens={"r": 100})
+    fl = F.SuffixFlusher()
+    assert (fl.keep, fl.every) == (3, 4)
+    fl.before_step(runner, chunk)
+    assert fl.pending_reset and fl.state is None and not calls
+    for step in range(7):                       # 7 tokens written before the 8th step: suffix 7 = keep + every
+        fl.before_step(runner, one)
+        assert not calls, step
+    fl.before_step(runner, one)
+    assert calls == [("m2", 100, 104), ("m5", 100, 104)] and fl.flushes == 1 and fl.written == 8
+    for step in range(3):
+        fl.before_step(runner, one)
+    assert len(calls) == 2
+    fl.before_step(runner, one)                 # 11 written, suffix 111 - 104 = 7 again
+    assert calls[2:] == [("m2", 104, 108), ("m5", 104, 108)]
+    # two requests in a step, then a new prompt of 50 tokens
+    fl.before_step(runner, SimpleNamespace(total_num_scheduled_tokens=2, num_scheduled_tokens={"a": 1, "b": 1}))
+    assert fl.pending_reset
+    state.prompt_epoch = 2
+    for a in arenas.values():
+        a.index.prompt_length = 50
+    fl.before_step(runner, one)
+    assert (fl.prompt_len, fl.written) == (50, 1) and len(calls) == 4
+    # an arena without stored pre-RoPE keys cannot be flushed: nothing happens
+    arenas[5].suffix_kpre = None
+    before = fl.written
+    fl.before_step(runner, one)
+    assert fl.written == before
+    arenas[5].suffix_kpre = object()
+    state.source_modules.pop(5)
+    fl.written = 6
+    fl.before_step(runner, one)
+    with pytest.raises(RuntimeError):
+        fl.before_step(runner, one)
+
