@@ -453,6 +453,62 @@ def test_loaded_routing_map_in_the_token_order_session_and_the_flush(dev):
             os.environ.pop(k, None)
 
 
+def test_side_car_maps_load_into_the_layers(dev, tmp_path):
+    """runtime_weights: a PCA map of the prompt's own keys is written as a side-car, verified and loaded into
+    a model whose layer sits at ``model.layers.4.self_attn``; the layer then routes exactly as with the map
+    loaded by hand.  With two ranks' worth of heads in the file, a rank's layer gets its block of heads."""
+    from semblo_b200 import _lib
+    from semblo_b200 import runtime_weights as RW
+    from semblo_b200.config import SembloVllmConfig
+    from semblo_b200.routing_map import pca_map
+    from semblo_b200.state import SembloRuntimeState
+    dim, index_dim, hq, hkv, sink, length, target, chunk = 128, 48, 8, 2, 64, 4096, 256, 1024
+    cpu = O.mixture_inputs(length=length, num_q_heads=hq, num_kv_heads=hkv, head_dim=dim, centres=24, seed=37)
+    data = {k: v.to(dev) for k, v in cpu.items()}
+    cfg = SembloVllmConfig(token_capacity=8192, target_tokens=target, flat_unit_tokens=32, index_dim=index_dim,
+                           flat_min_clusters_log2=7, kmeans_sample_size=1024, query_chunk_size=chunk,
+                           packed_decode_num_splits=4, decode_num_splits=2)
+    env = dict(SEMBLO_SINK_TOKENS=str(sink), SEMBLO_FA3_LOCAL="128", SEMBLO_FLAT_UNIT_TOKENS="32", SEMBLO_FA3_ALIGN="16")
+    os.environ.update(env)
+    os.environ.pop("SEMBLO_FULL_GRAPH_DECODE", None)
+    try:
+        w = pca_map(cpu["k_pre"], index_dim, rank=40)                     # [Hkv, 48, 128], rows 40.. zero
+        other = torch.randn(hkv, index_dim, dim)                          # the heads of a second rank
+        name = "layers.4.self_attn.semblo_key_router.weight"
+        RW.write_runtime_weights(tmp_path / "one", {name: w}, {"semblo_index_dim": index_dim}, "test")
+        RW.write_runtime_weights(tmp_path / "two", {name: torch.cat([other, w])}, {"semblo_index_dim": index_dim}, "test")
+
+        def model_with_layer(tag):
+            layer = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192),
+                                name=f"model.layers.{tag}.self_attn.attn")
+            holders = torch.nn.ModuleList([torch.nn.Module() for _ in range(5)])
+            holders[4].self_attn = layer
+            model = torch.nn.Module()
+            model.model = torch.nn.Module()
+            model.model.layers = holders
+            return model, layer
+
+        by_hand = _make_layer(data, dev, hq=hq, hkv=hkv, dim=dim, cfg=cfg, state=SembloRuntimeState(max_model_len=8192),
+                              name="model.layers.20.self_attn.attn")
+        by_hand.semblo_key_router.load_weight(w)
+        positions = torch.arange(length, device=dev)
+        hidden = torch.zeros(length, 8, dtype=torch.bfloat16, device=dev)
+        want = by_hand._sparse_layer_forward(positions, hidden).clone()
+        for tag, directory, kw in ((21, "one", {}), (22, "two", dict(tp_rank=1, tp_size=2))):
+            model, layer = model_with_layer(tag)
+            assert layer._router(dev).is_identity() is False            # zeros [Hkv, 48, 128] until loaded
+            written = RW.load_runtime_weights_into_module(model, tmp_path / directory, **kw)
+            assert written == {"model.layers.4.self_attn.semblo_key_router.weight"}
+            got = layer._sparse_layer_forward(positions, hidden)
+            torch.cuda.synchronize()
+            _lib.status_for(dev).raise_if_set()
+            assert torch.equal(got, want), directory
+            assert torch.equal(layer.runtime_state.get(0).bucket_sizes, by_hand.runtime_state.get(0).bucket_sizes)
+    finally:
+        for k in env:
+            os.environ.pop(k, None)
+
+
 def test_suffix_flusher_drives_the_layer_arena(dev):
     """suffix_flush.SuffixFlusher called before every engine step, as the reference's execute_model hook does
     (suffix_flush.py:211-283): the prompt step resets the count, the decode steps are counted, and when the
