@@ -63,8 +63,10 @@ __device__ __forceinline__ void stage_q_half(const __nv_bfloat16* qrow_half, int
 // attend to (64: all; columns from `lim` on, which include those of pages the product did not
 // write, count as -inf).  `pages` is the tile's count of 16-key groups.  The two threads of a row
 // exchange their half maxima through mx (float [2][2][128]: tile parity, half, row) and
-// bar_pair, the barrier of the two warps that share these 32 rows (count 64), in phase j.
-// Arrives on bar_pfull_b when P is stored.  Returns false after a wait timed out.
+// bar_pair, the barrier of the two warps that share these 32 rows (count 2: a warp arrives once, by
+// lane 0 after a __syncwarp -- 32 arrivals of a warp on one barrier are taken one after the other),
+// in phase j.  Arrives on bar_pfull_b (count: the softmax warps) when P is stored.  Returns false
+// after a wait timed out.
 template <int D, int O_COL>
 __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, int row, uint32_t lane_addr,
                                              uint32_t tmem_base, uint32_t s_col, float* mx, uint32_t bar_pair,
@@ -94,7 +96,8 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
   }
   float* slot = mx + (j & 1) * 256;
   slot[hf * 128 + row] = hm;
-  mbar_arrive(bar_pair);
+  __syncwarp();                                        // one arrival per warp: the barrier counts warps
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar_pair);
   if (!mbar_wait(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
   float tmax = fmaxf(hm, slot[(hf ^ 1) * 128 + row]);
   if (tmax < -1e29f) tmax = -INFINITY;               // only keys rejected through the selection operand
@@ -144,7 +147,8 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
   }
   tmem_st_wait();
   tc_fence_before();
-  mbar_arrive(bar_pfull_b);
+  __syncwarp();                                        // every lane's P is stored: one arrival per warp
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar_pfull_b);
   return true;
 }
 

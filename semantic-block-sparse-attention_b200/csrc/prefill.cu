@@ -106,10 +106,10 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
     mbar_init(bar(B_QFULL), 256);
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
-    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 64);   // the two warps that share 32 rows
+    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 2);    // the two warps that share 32 rows
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(B_SFULL + b), 1);
-      mbar_init(bar(B_PFULL + b), 256);
+      mbar_init(bar(B_PFULL + b), 8);         // the softmax warps
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < STAGES; ++s) {

@@ -177,10 +177,10 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     mbar_init(bar(B_OREADY), 1);
     mbar_init(bar(B_EPI), 256);
     mbar_init(bar(B_QHI), 1);
-    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 64);   // the two warps that share 32 rows
+    for (int i = 0; i < 4; ++i) mbar_init(bar(B_PAIR + i), 2);    // the two warps that share 32 rows
     for (int b = 0; b < NSB; ++b) {
       mbar_init(bar(B_SFULL + b), 2);          // the issuer's own arrival (after the page count) + its commit
-      mbar_init(bar(B_PFULL + b), 256);
+      mbar_init(bar(B_PFULL + b), 8);          // the softmax warps
       mbar_init(bar(B_PVDONE + b), 1);
     }
     for (int s = 0; s < K_STAGES; ++s) {
@@ -550,7 +550,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
       if (!ok) break;
       const int np = tile_pages[b];
       if (np == 0) {                        // end of the stream: tell the P V issuer
-        mbar_arrive(bar(B_PFULL + b));
+        if (lane == 0) mbar_arrive(bar(B_PFULL + b));
         break;
       }
       tc_fence_after();
