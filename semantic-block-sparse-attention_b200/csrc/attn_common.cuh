@@ -98,7 +98,7 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
   slot[hf * 128 + row] = hm;
   __syncwarp();                                        // one arrival per warp: the barrier counts warps
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar_pair);
-  if (!mbar_wait(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+  if (!mbar_wait_warp(bar_pair, (uint32_t)(j & 1), abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
   float tmax = fmaxf(hm, slot[(hf ^ 1) * 128 + row]);
   if (tmax < -1e29f) tmax = -INFINITY;               // only keys rejected through the selection operand
   tmax *= scale_log2;
@@ -114,7 +114,7 @@ __device__ __forceinline__ bool softmax_tile(int pages, int lim, int j, int hf, 
   }
   if (__any_sync(0xffffffffu, need)) {
     // O must be quiescent: the previous tile's P V has to be complete
-    if (!mbar_wait(bar_pvdone_prev, pvdone_prev_parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
+    if (!mbar_wait_warp(bar_pvdone_prev, pvdone_prev_parity, abort_flag, status, STATUS_TIMEOUT_SOFTMAX)) return false;
     tc_fence_after();
 #pragma unroll 1
     for (int c = 0; c < D / 64; ++c) {

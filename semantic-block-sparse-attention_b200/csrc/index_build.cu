@@ -222,7 +222,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bflo
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
       mbar_init(smem_u32(&bars[5 + s]), 1);
-      mbar_init(smem_u32(&bars[7 + s]), 256);
+      mbar_init(smem_u32(&bars[7 + s]), 8);        // the epilogue warps (one arrival each, by lane 0)
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -308,7 +308,7 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bflo
     const bool full = (num_centroids % ASG_BN) == 0;
     for (int j = 0; j < num_chunks && ok; ++j) {
       const int b = j & 1;
-      ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+      ok = mbar_wait_warp(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
@@ -339,7 +339,8 @@ assign_argmax_kernel(const __grid_constant__ CUtensorMap tmap_x, const __nv_bflo
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars[7 + b]));
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&bars[7 + b]));
     }
     float* xv = reinterpret_cast<float*>(smem + L::XCHG_OFF);
     int* xi = reinterpret_cast<int*>(smem + L::XCHG_OFF + 512);

@@ -238,14 +238,14 @@ window_prefill_kernel(const __grid_constant__ CUtensorMap tmap_ok,
                                     bar(B_QFULL));
     for (;; ++j) {
       const int b = j & 1;
-      ok = mbar_wait(bar(B_KVFULL + s), kv_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      ok = mbar_wait_warp(bar(B_KVFULL + s), kv_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       const int np = info[s].npages;
       const int rows = info[s].rows, kpos0 = info[s].kpos0;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_KVEMPTY + s));
       if (np == 0) break;                              // end of the stream
-      ok = mbar_wait(bar(B_SFULL + b), (uint32_t)((j >> 1) & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      ok = mbar_wait_warp(bar(B_SFULL + b), (uint32_t)((j >> 1) & 1), abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       tc_fence_after();
       // keys at or before the row's position; a tile wholly below the diagonal for every row of

@@ -546,7 +546,7 @@ sparse_gather_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const G
     attn::stage_q_half<C::Q_TMEM_DIMS, C::Q_COL>(qvalid ? a.q + hidx * D + hf * (C::Q_TMEM_DIMS / 2) : nullptr, hf,
                                                  lane_addr, tmem_base, bar(B_QFULL));
     for (;; ++j) {
-      ok = mbar_wait(bar(B_SFULL + b), s_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
+      ok = mbar_wait_warp(bar(B_SFULL + b), s_par, abort_flag, a.status, STATUS_TIMEOUT_SOFTMAX);
       if (!ok) break;
       const int np = tile_pages[b];
       if (np == 0) {                        // end of the stream: tell the P V issuer

@@ -101,7 +101,7 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
       mbar_init(smem_u32(&bars[1 + s]), 1);
       mbar_init(smem_u32(&bars[3 + s]), 1);
       mbar_init(smem_u32(&bars[5 + s]), 1);
-      mbar_init(smem_u32(&bars[7 + s]), 256);
+      mbar_init(smem_u32(&bars[7 + s]), 8);        // the epilogue warps (one arrival each, by lane 0)
     }
     mbar_init(smem_u32(&bars[9]), 256);
     *abort_flag = 0;
@@ -196,7 +196,7 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
             nsz[cc][i] = c < num_clusters ? sz[c] : 0;
           }
       }
-      ok = mbar_wait(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+      ok = mbar_wait_warp(smem_u32(&bars[5 + b]), (j >> 1) & 1, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
       if (!ok) break;
       tc_fence_after();
       if (j == chunks) {
@@ -204,7 +204,7 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
         xchg[(hf * 128 + row) * 2] = m_run;
         xchg[(hf * 128 + row) * 2 + 1] = l_run;
         mbar_arrive(smem_u32(&bars[9]));
-        ok = mbar_wait(smem_u32(&bars[9]), 0, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
+        ok = mbar_wait_warp(smem_u32(&bars[9]), 0, abort_flag, status, STATUS_TIMEOUT_EPILOGUE);
         if (!ok) break;
         const float m_o = xchg[((hf ^ 1) * 128 + row) * 2], l_o = xchg[((hf ^ 1) * 128 + row) * 2 + 1];
         const float mx = fmaxf(m_run, m_o);
@@ -272,7 +272,8 @@ score_kernel(const __nv_bfloat16* __restrict__ vectors,      // [Q, Hq, D] bf16
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&bars[7 + b]));
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&bars[7 + b]));
     }
   }
   __syncthreads();

@@ -123,6 +123,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait for a whole (converged) warp, with one answer for all its lanes: code that goes on to a
+// __syncwarp must not lose some of its lanes to a wait that gave up.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
+}
+
 // ---------------------------------------------------------------- dependent launches
 // In a kernel launched as a programmatic dependent: wait until the preceding kernel of the stream
 // has completed and its writes are visible (a no-op in a plain launch).
