@@ -199,10 +199,10 @@ int semblo_flush_repack(void* packed, int64_t kv_stride_elems, int64_t packed_ro
  * frozen its memory pool, or under an allocator they do not own).  Limits: heads * n <=
  * semblo_argsort_keys_static_max_keys() (65536) and heads <= 64; larger inputs are refused
  * with an error and belong to semblo_argsort_keys.  The first call on a device, with that
- * device current, resolves the array's address (this may load the module): make it before any
- * stream capture begins.  All calls on a device share the one array, so two calls whose kernels
- * can overlap (different streams or threads) race; order them on one stream.  Nothing in the
- * array has to be cleared between calls. */
+ * device current, resolves the array's address (this may load the module).  All calls on a
+ * device share the one array, so two calls whose kernels can overlap (different streams or
+ * threads) race; order them on one stream.  Nothing in the array has to be cleared between
+ * calls. */
 int64_t semblo_argsort_keys_static_max_keys(void);
 int semblo_argsort_keys_static(const int32_t* keys, int64_t n, int heads, int max_key,
                                int32_t* order, void* stream);
