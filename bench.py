@@ -232,11 +232,12 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.busy = []                      # clocks of the samples taken while the GPU reported work
         self.proc = None
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,utilization.gpu")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -260,6 +261,11 @@ class ClockSampler:
             for n, v in zip(names, parts[2:6]):
                 if v.lower().startswith("active"):
                     self.reasons.add(n)
+            try:
+                if len(parts) > 6 and float(parts[6]) >= 30.0:
+                    self.busy.append(float(parts[0]))
+            except ValueError:
+                pass
 
     def stop(self):
         if self.proc is None:
@@ -269,11 +275,13 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        s = sorted(self.samples)
-        # the median over the samples taken while the GPU was busy (upper half of the readings)
-        busy = s[len(s) // 2:] if s else []
-        med = busy[len(busy) // 2] if busy else None
-        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        # the median over the samples taken under load (reported utilisation of at least 30 %; an idle
+        # GPU with a context sits at its maximum clock, so the idle readings are the high ones); all
+        # samples if none qualified (a run shorter than the tool's update period)
+        s = sorted(self.busy) if self.busy else sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples_under_load": len(self.busy), "samples": len(self.samples)}
 
 
 # ------------------------------------------------------------------------- launch accounting
@@ -898,7 +906,6 @@ def main():
     gc.enable()
     ms = e0.elapsed_time(e1) / args.steps
     step_ms = [round(marks[i].elapsed_time(marks[i + 1]), 2) for i in range(args.steps)]
-    clocks = sampler.stop()
     _lib.status_for(device).raise_if_set()
     calls = dict(_lib.CALLS)
     clusters = int(index.num_buckets)
@@ -1009,6 +1016,7 @@ def main():
     barrier()
     gc.enable()
     e2e_ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()          # sampled through both timed regions (device-resident and end to end)
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([e2e_ms], device=device)
